@@ -1,0 +1,227 @@
+/*
+ * fusor_b200 — C ABI of the B200 (sm_100a) backend for Fusor's quantized-inference path.
+ *
+ * Every entry point mirrors one operation of the `fusor` crate of floneum/kalosm (cited per
+ * function as file:line inside that project). A Rust `extern "C"` block binding these symbols
+ * is what `fusor::Device::Gpu`, `fusor::QMatrix::Gpu` and `fusor::Tensor::Gpu` would call.
+ *
+ * Conventions
+ *  - Plain pointers and sizes only. Pointers named *_dev are device pointers (from
+ *    fb200_malloc or any CUDA allocation on the handle's device); *_host are host pointers.
+ *  - Every function returns an fb200_status (0 = OK, negative = error). The text of the last
+ *    error of a device handle is available from fb200_last_error(). Nothing aborts, traps or
+ *    unwinds across this boundary (the reference mixes Result and panics,
+ *    fusor-ml/fusor/src/error.rs:4-15 and src/lib.rs:1133-1138; both become status codes).
+ *  - Work is enqueued on the handle's CUDA stream and is asynchronous; fb200_download,
+ *    fb200_device_synchronize and the *_host entry points block. One host thread drives a
+ *    device handle at a time (the reference serialises a forward pass per session,
+ *    models/kalosm-llama/src/model/inference.rs:47-50).
+ *  - There is no CPU fallback: without a CUDA device every call fails with FB200_ERR_CUDA.
+ */
+#ifndef FUSOR_B200_H
+#define FUSOR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define FB200_API __attribute__((visibility("default")))
+#else
+#define FB200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum fb200_status {
+  FB200_OK = 0,
+  FB200_ERR_INVALID_SHAPE = -1,
+  FB200_ERR_UNSUPPORTED_DTYPE = -2,
+  FB200_ERR_CAPACITY = -3,
+  FB200_ERR_CUDA = -4,
+  FB200_ERR_INVALID_ARGUMENT = -5,
+  FB200_ERR_TIMEOUT = -6,
+  FB200_ERR_DEVICE_MISMATCH = -7
+} fb200_status;
+
+/* ggml type ids, fusor-ml/gguf/src/lib.rs:35-50 */
+typedef enum fb200_ggml_type {
+  FB200_F32 = 0, FB200_F16 = 1, FB200_Q4_0 = 2, FB200_Q5_0 = 6, FB200_Q8_0 = 8,
+  FB200_Q4_K = 12, FB200_Q5_K = 13, FB200_Q6_K = 14
+} fb200_ggml_type;
+
+typedef struct fb200_device fb200_device;
+typedef struct fb200_qmatrix fb200_qmatrix;
+typedef struct fb200_kv_cache fb200_kv_cache;
+typedef struct fb200_llama fb200_llama;
+
+/* ---- device: fusor::Device::gpu(), fusor-ml/fusor/src/device.rs:29-40 -------------------------
+ * One CUDA device + one stream per handle. `stream` may be an existing cudaStream_t (the
+ * handle then enqueues on it and does not own it) or NULL (the handle creates its own). */
+FB200_API int fb200_device_create(int ordinal, void* stream, fb200_device** out);
+FB200_API int fb200_device_destroy(fb200_device* dev);
+FB200_API int fb200_device_synchronize(fb200_device* dev);
+FB200_API const char* fb200_last_error(const fb200_device* dev);
+/* Number of kernels this library has launched through the handle since creation. */
+FB200_API uint64_t fb200_launch_count(const fb200_device* dev);
+/* Device-side status word: 0 unless a kernel recorded a fault it recovered from (bounded
+ * wait ran out, bad index skipped). Reading it synchronises the stream. */
+FB200_API int fb200_device_status(fb200_device* dev, int* status_out);
+
+/* ---- tensors: Tensor::from_slice / as_slice, fusor-ml/fusor/src/lib.rs:356-368 -----------------
+ * Tensors are contiguous row-major device buffers; shapes travel as arguments. */
+FB200_API int fb200_malloc(fb200_device* dev, size_t bytes, void** out_dev);
+FB200_API int fb200_free(fb200_device* dev, void* ptr_dev);
+FB200_API int fb200_upload(fb200_device* dev, void* dst_dev, const void* src_host, size_t bytes);
+FB200_API int fb200_download(fb200_device* dev, void* dst_host, const void* src_dev, size_t bytes);
+FB200_API int fb200_memset(fb200_device* dev, void* dst_dev, int value, size_t bytes);
+
+/* ---- QMatrix: fusor-ml/fusor/src/quantized.rs:80-284 -------------------------------------------
+ * from_raw_bytes (quantized.rs:183-231): `bytes` are raw GGUF blocks of the logical [N, K]
+ * weight (row-major blocks along K, fusor-ml/cpu/src/quantized.rs:293-294), copied during the
+ * call. K must be a multiple of the block size (else FB200_ERR_INVALID_SHAPE, where the
+ * reference panics, cpu/src/quantized.rs:54-69); unknown types give
+ * FB200_ERR_UNSUPPORTED_DTYPE (GgufReadError::UnsupportedDType). F32/F16 are accepted as dense.
+ * On the device the blocks are stored in a tile-interleaved order (same bytes, permuted) so
+ * that warps read them with coalesced 128-bit loads. */
+FB200_API int fb200_qmatrix_from_raw_bytes(fb200_device* dev, const uint64_t* shape, int rank,
+                                 const void* bytes_host, size_t nbytes, uint32_t ggml_type,
+                                 fb200_qmatrix** out);
+FB200_API int fb200_qmatrix_free(fb200_qmatrix* q);
+/* quantized.rs:115-175 */
+FB200_API int fb200_qmatrix_shape(const fb200_qmatrix* q, uint64_t* n_out, uint64_t* k_out);
+FB200_API int fb200_qmatrix_ggml_type(const fb200_qmatrix* q, uint32_t* type_out);
+/* Raw GGUF byte count of the matrix (the algorithmic bytes one product streams). */
+FB200_API int fb200_qmatrix_nbytes(const fb200_qmatrix* q, uint64_t* nbytes_out);
+/* QMatrix::dequantize, quantized.rs:233-284: f32 [N, K] into out_dev, bit-exact with
+ * GgufBlock::dequantize (fusor-ml/gguf/src/lib.rs:828,1046,1284,1526,1819,2034). */
+FB200_API int fb200_qmatrix_dequantize(const fb200_qmatrix* q, float* out_dev);
+/* QMatrix::concat_rows, quantized.rs:102-112 / core/src/quantized/mod.rs:312-386: same type
+ * and same K required; otherwise FB200_ERR_INVALID_SHAPE and *out = NULL (the reference
+ * returns None). Every N but the last must be a multiple of 16. */
+FB200_API int fb200_qmatrix_concat_rows(const fb200_qmatrix* const* ms, int n, fb200_qmatrix** out);
+
+/* ---- q_mat_mul: Tensor::q_mat_mul, fusor-ml/fusor/src/lib.rs:1132-1223 --------------------------
+ * y[M, N] = x[M, K] . W^T (+ epilogue), x and y f32 contiguous; rank-1 x is M = 1.
+ * Epilogues mirror the fused forms the reference's GPU path recognises:
+ *   FB200_EPI_RESIDUAL  y = (W.x + r1) + r2          (r2 may be NULL) — down/O projection with
+ *                       residual adds, models/kalosm-llama/src/raw/attention_layer.rs:147-174
+ *   FB200_EPI_SWIGLU    W is [gate; up] row-concatenated (2F rows); y[M, F] =
+ *                       silu(gate.x) * (up.x) — attention_layer.rs:184-196 */
+typedef enum fb200_epilogue_kind {
+  FB200_EPI_NONE = 0, FB200_EPI_RESIDUAL = 1, FB200_EPI_SWIGLU = 2
+} fb200_epilogue_kind;
+
+typedef struct fb200_epilogue {
+  int kind;
+  const float* r1_dev; /* [M, N] */
+  const float* r2_dev; /* [M, N] or NULL */
+} fb200_epilogue;
+
+FB200_API int fb200_q_mat_mul(fb200_device* dev, const float* x_dev, size_t m, const fb200_qmatrix* w,
+                    float* y_dev, const fb200_epilogue* epilogue);
+/* Same product with host buffers: uploads x, runs, downloads y, synchronises. */
+FB200_API int fb200_q_mat_mul_host(fb200_device* dev, const float* x_host, size_t m,
+                         const fb200_qmatrix* w, float* y_host);
+
+/* ---- elementwise / composite ops ---------------------------------------------------------------
+ * rms_norm_fused / rms_norm_residual_fused, fusor-ml/fusor/src/composite/normalization.rs:287-402:
+ * y = v / sqrt(mean(v^2) + eps) * w (+ bias), v = x (+ residual); f32; rows x n. */
+FB200_API int fb200_rms_norm(fb200_device* dev, const float* x_dev, const float* residual_dev,
+                   const float* weight_dev, const float* bias_dev, float eps, size_t rows,
+                   size_t n, float* y_dev);
+/* silu(gate) * up, fusor-ml/fusor/src/composite/activations.rs:47-64 */
+FB200_API int fb200_silu_mul(fb200_device* dev, const float* gate_dev, const float* up_dev, size_t n,
+                   float* out_dev);
+/* RoPE tables [ctx, head_dim/2]: base_inverse_frequency (composite/rope.rs:241-246) and the
+ * Llama-3 scaling of models/kalosm-llama/src/raw/rope.rs:21-38 (factor <= 0 disables it).
+ * Computed on the host in f32 exactly as the reference does, then uploaded. */
+FB200_API int fb200_rope_tables(fb200_device* dev, int head_dim, int ctx, float theta, float factor,
+                      float low_freq_factor, float high_freq_factor, int original_ctx,
+                      float* cos_dev, float* sin_dev);
+/* RopeCache::forward / forward_interleaved, composite/rope.rs:284-329: q [B,H,S,D] and
+ * k [B,Hkv,S,D] rotated in place with table rows start_pos .. start_pos + S. */
+FB200_API int fb200_rope_pair(fb200_device* dev, float* q_dev, float* k_dev, int b, int h, int hkv, int s,
+                    int d, const float* cos_dev, const float* sin_dev, int start_pos,
+                    int interleaved);
+/* Embedding::forward, fusor-ml/fusor/src/layers/embedding.rs:43-107: dequantised rows of W. */
+FB200_API int fb200_embedding_lookup(fb200_device* dev, const fb200_qmatrix* w, const uint32_t* ids_dev,
+                           size_t n_ids, float* out_dev);
+/* Tensor::top_k_pairs, fusor-ml/fusor/src/lib.rs:416-453 with k = 1 per row: highest finite
+ * logit, ties -> higher token id. ids_dev [rows] u32, vals_dev [rows] f32 (may be NULL). */
+FB200_API int fb200_argmax(fb200_device* dev, const float* logits_dev, size_t rows, size_t n,
+                 uint32_t* ids_dev, float* vals_dev);
+
+/* ---- KV cache: KvCache / TensorCache, fusor-ml/fusor/src/cache/kv_cache.rs:12-68 ----------------
+ * Layout [B, Hkv, capacity, D], fp16 on the device (the reference's cache is f32). Capacity
+ * follows tensor_cache.rs:304-312 (next power of two, at least 256, at most max_seq_len) and
+ * grows by reallocation + copy. Appending beyond max_seq_len returns FB200_ERR_CAPACITY (the
+ * reference evicts the oldest entries, tensor_cache.rs:175-202). */
+FB200_API int fb200_kv_cache_create(fb200_device* dev, int batch, int n_kv_head, int head_dim,
+                          int max_seq_len, fb200_kv_cache** out);
+FB200_API int fb200_kv_cache_free(fb200_kv_cache* c);
+FB200_API int fb200_kv_cache_reset(fb200_kv_cache* c);
+FB200_API int fb200_kv_cache_len(const fb200_kv_cache* c, int* len_out, int* capacity_out);
+/* k, v f32 [B, Hkv, S, D]; rounded to fp16 and stored at positions len .. len + S. */
+FB200_API int fb200_kv_cache_append(fb200_kv_cache* c, const float* k_dev, const float* v_dev, int s);
+/* Device pointers of the fp16 K and V buffers ([B, Hkv, capacity, D]). */
+FB200_API int fb200_kv_cache_buffers(const fb200_kv_cache* c, const void** k_dev, const void** v_dev);
+
+/* ---- attention: Tensor::flash_attention, fusor-ml/fusor/src/composite/flash_attention.rs:58-236 --
+ * out = softmax(q.k^T * scale + mask).v, GQA by kv_head = head / (H / Hkv). q, out f32
+ * [B,H,Sq,D]; k, v fp16 [B,Hkv,*,D] with kv_capacity rows allocated per head and the first
+ * skv rows valid. mask_kind: 0 none, 1 causal (query row i sees keys 0 .. i + skv - sq;
+ * AttentionMask::causal, cache/attention_mask.rs:45-65 with the left padding of
+ * mask_cache.rs:74-85), 2 additive f32 [Sq, Skv], 3 additive f32 [B, Skv]. */
+FB200_API int fb200_flash_attention(fb200_device* dev, const float* q_dev, const void* k_dev,
+                          const void* v_dev, int b, int h, int hkv, int sq, int skv,
+                          int kv_capacity, int d, float scale, const float* mask_dev,
+                          int mask_kind, float* out_dev);
+
+/* ---- whole model: Model::forward, models/kalosm-llama/src/raw/mod.rs:851-1049 -------------------
+ * Llama-architecture decoder (separate q/k/v, SiLU-gated FFN, interleaved RoPE, raw/mod.rs:488-490).
+ * The model owns its KV caches, activation buffers and the CUDA graph of a decode step. */
+typedef struct fb200_llama_config {
+  int n_layer, hidden, ffn, n_head, n_kv_head, head_dim, vocab;
+  int max_seq_len; /* context_length */
+  int max_batch;
+  float rms_eps;    /* llama.attention.layer_norm_rms_epsilon, raw/mod.rs:383 */
+  float rope_theta; /* llama.rope.freq_base */
+  float rope_factor, rope_low_freq_factor, rope_high_freq_factor;
+  int rope_original_ctx;
+} fb200_llama_config;
+
+typedef enum fb200_llama_tensor {
+  FB200_T_TOKEN_EMBD = 0, FB200_T_OUTPUT = 1, FB200_T_ATTN_Q = 2, FB200_T_ATTN_K = 3,
+  FB200_T_ATTN_V = 4, FB200_T_ATTN_OUTPUT = 5, FB200_T_FFN_GATE = 6, FB200_T_FFN_UP = 7,
+  FB200_T_FFN_DOWN = 8, FB200_T_ATTN_NORM = 9, FB200_T_FFN_NORM = 10, FB200_T_OUTPUT_NORM = 11
+} fb200_llama_tensor;
+
+FB200_API int fb200_llama_create(fb200_device* dev, const fb200_llama_config* cfg, fb200_llama** out);
+FB200_API int fb200_llama_free(fb200_llama* m);
+/* Tensor names of raw/mod.rs:473-646: blk.{i}.attn_q.weight ... ; norms are f32 vectors
+ * (ggml_type FB200_F32), everything else raw GGUF blocks of shape [N, K]. `layer` is ignored
+ * for the three model-level tensors. Missing FB200_T_OUTPUT ties it to the embedding
+ * (raw/mod.rs:480-486). */
+FB200_API int fb200_llama_set_tensor(fb200_llama* m, int layer, int which, uint32_t ggml_type,
+                           uint64_t n, uint64_t k, const void* bytes_host, size_t nbytes);
+FB200_API int fb200_llama_reset(fb200_llama* m);
+FB200_API int fb200_llama_position(const fb200_llama* m, int* pos_out);
+/* tokens_host [batch, seq] u32. Runs the forward pass over `seq` new positions and writes the
+ * logits of the last position, f32 [batch, vocab], to logits_host if not NULL, and the greedy
+ * token per batch row to next_host if not NULL (tie -> higher id). Blocks until done. */
+FB200_API int fb200_llama_forward(fb200_llama* m, const uint32_t* tokens_host, int batch, int seq,
+                        float* logits_host, uint32_t* next_host);
+/* Greedy decode: feeds tokens_host [batch] and then its own argmax for `steps` steps entirely
+ * on the device (replaying the captured CUDA graph); out_host [batch, steps] receives the
+ * generated ids. Only the ids cross PCIe. */
+FB200_API int fb200_llama_generate_greedy(fb200_llama* m, const uint32_t* tokens_host, int batch,
+                                int steps, uint32_t* out_host);
+/* Device pointer of the last forward pass's logits, f32 [batch, vocab]. */
+FB200_API int fb200_llama_logits_dev(const fb200_llama* m, const float** logits_dev);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FUSOR_B200_H */

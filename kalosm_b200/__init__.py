@@ -1,0 +1,479 @@
+"""kalosm_b200 — host-side mirror of Fusor's operator API over ``libfusor_b200.so``.
+
+The shared library (hand-written sm_100a CUDA behind a C ABI, ``include/fusor_b200.h``) is the
+product; this module is the thin Python binding the tests and the benchmark drive it with.
+Class and method names follow the ``fusor`` crate of floneum/kalosm: ``Device``, ``Tensor``,
+``QMatrix.from_raw_bytes``, ``Tensor.q_mat_mul``, ``KvCache.append``, ``flash_attention`` …
+There is no CPU fallback: importing works anywhere, but creating a ``Device`` without the
+compiled library or without a CUDA GPU raises ``FusorError``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional, Sequence
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfusor_b200.so")
+
+# ggml type ids (fusor-ml/gguf/src/lib.rs:35-50)
+F32, F16, Q4_0, Q5_0, Q8_0, Q4_K, Q5_K, Q6_K = 0, 1, 2, 6, 8, 12, 13, 14
+BLOCK = {F32: (1, 4), F16: (1, 2), Q4_0: (32, 18), Q5_0: (32, 22), Q8_0: (32, 34),
+         Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210)}
+
+OK = 0
+ERR_INVALID_SHAPE, ERR_UNSUPPORTED_DTYPE, ERR_CAPACITY, ERR_CUDA = -1, -2, -3, -4
+ERR_INVALID_ARGUMENT, ERR_TIMEOUT, ERR_DEVICE_MISMATCH = -5, -6, -7
+EPI_NONE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+MASK_NONE, MASK_CAUSAL, MASK_QK, MASK_BATCH_KEY = 0, 1, 2, 3
+
+
+class FusorError(RuntimeError):
+    """An fb200_* call returned a negative status (mirrors fusor::Error, fusor/src/error.rs:4-15)."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"fb200 status {code}: {message}")
+        self.code = code
+
+
+class _Epilogue(C.Structure):
+    _fields_ = [("kind", C.c_int), ("r1", C.c_void_p), ("r2", C.c_void_p)]
+
+
+class LlamaConfig(C.Structure):
+    """fb200_llama_config; field meanings follow the GGUF keys of kalosm-llama raw/mod.rs:377-415."""
+    _fields_ = [("n_layer", C.c_int), ("hidden", C.c_int), ("ffn", C.c_int), ("n_head", C.c_int),
+                ("n_kv_head", C.c_int), ("head_dim", C.c_int), ("vocab", C.c_int),
+                ("max_seq_len", C.c_int), ("max_batch", C.c_int), ("rms_eps", C.c_float),
+                ("rope_theta", C.c_float), ("rope_factor", C.c_float),
+                ("rope_low_freq_factor", C.c_float), ("rope_high_freq_factor", C.c_float),
+                ("rope_original_ctx", C.c_int)]
+
+
+EXPORTS = [
+    "fb200_device_create", "fb200_device_destroy", "fb200_device_synchronize", "fb200_last_error",
+    "fb200_launch_count", "fb200_device_status", "fb200_malloc", "fb200_free", "fb200_upload",
+    "fb200_download", "fb200_memset", "fb200_qmatrix_from_raw_bytes", "fb200_qmatrix_free",
+    "fb200_qmatrix_shape", "fb200_qmatrix_ggml_type", "fb200_qmatrix_nbytes",
+    "fb200_qmatrix_dequantize", "fb200_qmatrix_concat_rows", "fb200_q_mat_mul",
+    "fb200_q_mat_mul_host", "fb200_rms_norm", "fb200_silu_mul", "fb200_rope_tables",
+    "fb200_rope_pair", "fb200_embedding_lookup", "fb200_argmax", "fb200_kv_cache_create",
+    "fb200_kv_cache_free", "fb200_kv_cache_reset", "fb200_kv_cache_len", "fb200_kv_cache_append",
+    "fb200_kv_cache_buffers", "fb200_flash_attention", "fb200_llama_create", "fb200_llama_free",
+    "fb200_llama_set_tensor", "fb200_llama_reset", "fb200_llama_position", "fb200_llama_forward",
+    "fb200_llama_generate_greedy", "fb200_llama_logits_dev",
+]
+
+_lib = None
+
+
+def load_library():
+    """dlopen libfusor_b200.so and declare the signatures. Raises FusorError if it is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise FusorError(ERR_CUDA, f"{LIB_PATH} is not built (run `python -m kalosm_b200.build`); "
+                                   "there is no CPU fallback")
+    L = C.CDLL(LIB_PATH)
+    vp, sz, i32, u32, u64, f32 = C.c_void_p, C.c_size_t, C.c_int, C.c_uint32, C.c_uint64, C.c_float
+    pp = C.POINTER(C.c_void_p)
+    sig = {
+        "fb200_device_create": (i32, [i32, vp, pp]),
+        "fb200_device_destroy": (i32, [vp]),
+        "fb200_device_synchronize": (i32, [vp]),
+        "fb200_last_error": (C.c_char_p, [vp]),
+        "fb200_launch_count": (u64, [vp]),
+        "fb200_device_status": (i32, [vp, C.POINTER(i32)]),
+        "fb200_malloc": (i32, [vp, sz, pp]),
+        "fb200_free": (i32, [vp, vp]),
+        "fb200_upload": (i32, [vp, vp, vp, sz]),
+        "fb200_download": (i32, [vp, vp, vp, sz]),
+        "fb200_memset": (i32, [vp, vp, i32, sz]),
+        "fb200_qmatrix_from_raw_bytes": (i32, [vp, C.POINTER(u64), i32, vp, sz, u32, pp]),
+        "fb200_qmatrix_free": (i32, [vp]),
+        "fb200_qmatrix_shape": (i32, [vp, C.POINTER(u64), C.POINTER(u64)]),
+        "fb200_qmatrix_ggml_type": (i32, [vp, C.POINTER(u32)]),
+        "fb200_qmatrix_nbytes": (i32, [vp, C.POINTER(u64)]),
+        "fb200_qmatrix_dequantize": (i32, [vp, vp]),
+        "fb200_qmatrix_concat_rows": (i32, [pp, i32, pp]),
+        "fb200_q_mat_mul": (i32, [vp, vp, sz, vp, vp, C.POINTER(_Epilogue)]),
+        "fb200_q_mat_mul_host": (i32, [vp, vp, sz, vp, vp]),
+        "fb200_rms_norm": (i32, [vp, vp, vp, vp, vp, f32, sz, sz, vp]),
+        "fb200_silu_mul": (i32, [vp, vp, vp, sz, vp]),
+        "fb200_rope_tables": (i32, [vp, i32, i32, f32, f32, f32, f32, i32, vp, vp]),
+        "fb200_rope_pair": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32]),
+        "fb200_embedding_lookup": (i32, [vp, vp, vp, sz, vp]),
+        "fb200_argmax": (i32, [vp, vp, sz, sz, vp, vp]),
+        "fb200_kv_cache_create": (i32, [vp, i32, i32, i32, i32, pp]),
+        "fb200_kv_cache_free": (i32, [vp]),
+        "fb200_kv_cache_reset": (i32, [vp]),
+        "fb200_kv_cache_len": (i32, [vp, C.POINTER(i32), C.POINTER(i32)]),
+        "fb200_kv_cache_append": (i32, [vp, vp, vp, i32]),
+        "fb200_kv_cache_buffers": (i32, [vp, pp, pp]),
+        "fb200_flash_attention": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp,
+                                        i32, vp]),
+        "fb200_llama_create": (i32, [vp, C.POINTER(LlamaConfig), pp]),
+        "fb200_llama_free": (i32, [vp]),
+        "fb200_llama_set_tensor": (i32, [vp, i32, i32, u32, u64, u64, vp, sz]),
+        "fb200_llama_reset": (i32, [vp]),
+        "fb200_llama_position": (i32, [vp, C.POINTER(i32)]),
+        "fb200_llama_forward": (i32, [vp, vp, i32, i32, vp, vp]),
+        "fb200_llama_generate_greedy": (i32, [vp, vp, i32, i32, vp]),
+        "fb200_llama_logits_dev": (i32, [vp, pp]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(L, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = L
+    return L
+
+
+def _hp(a: Optional[np.ndarray]):
+    return None if a is None else a.ctypes.data
+
+
+class Tensor:
+    """A contiguous row-major device buffer with a shape and dtype (fusor::Tensor::Gpu)."""
+
+    def __init__(self, device: "Device", shape: Sequence[int], dtype=np.float32, ptr: Optional[int] = None):
+        self.device = device
+        self.shape = tuple(int(s) for s in shape)
+        self.dtype = np.dtype(dtype)
+        self.nbytes = int(np.prod(self.shape, dtype=np.int64)) * self.dtype.itemsize
+        self._owned = ptr is None
+        if ptr is None:
+            out = C.c_void_p()
+            device._check(device.lib.fb200_malloc(device.h, max(self.nbytes, 1), C.byref(out)))
+            ptr = out.value
+        self.ptr = ptr
+
+    @classmethod
+    def from_slice(cls, device: "Device", array, dtype=None) -> "Tensor":
+        """Tensor::from_slice (fusor/src/lib.rs:356-362): upload a host array."""
+        a = np.ascontiguousarray(array, dtype=dtype)
+        t = cls(device, a.shape, a.dtype)
+        device._check(device.lib.fb200_upload(device.h, t.ptr, _hp(a), a.nbytes))
+        return t
+
+    def as_slice(self) -> np.ndarray:
+        """Tensor::as_slice (fusor/src/lib.rs:364-368): the synchronising read-back."""
+        out = np.empty(self.shape, dtype=self.dtype)
+        self.device._check(self.device.lib.fb200_download(self.device.h, _hp(out), self.ptr, self.nbytes))
+        return out
+
+    def fill_bytes(self, value: int) -> None:
+        self.device._check(self.device.lib.fb200_memset(self.device.h, self.ptr, value, self.nbytes))
+
+    def q_mat_mul(self, w: "QMatrix", epilogue: int = EPI_NONE, r1: "Tensor" = None,
+                  r2: "Tensor" = None, out: "Tensor" = None) -> "Tensor":
+        """Tensor::q_mat_mul (fusor/src/lib.rs:1132-1223): self [.., K] . W[N, K]^T."""
+        k = self.shape[-1]
+        n, wk = w.shape
+        if k != wk:
+            raise FusorError(ERR_INVALID_SHAPE, f"lhs columns ({k}) != weight in_features ({wk})")
+        m = int(np.prod(self.shape[:-1], dtype=np.int64)) if len(self.shape) > 1 else 1
+        n_out = n // 2 if epilogue == EPI_SWIGLU else n
+        out_shape = (self.shape[:-1] if len(self.shape) > 1 else ()) + (n_out,)
+        y = out if out is not None else Tensor(self.device, out_shape, np.float32)
+        ep = _Epilogue(epilogue, r1.ptr if r1 is not None else None, r2.ptr if r2 is not None else None)
+        d = self.device
+        d._check(d.lib.fb200_q_mat_mul(d.h, self.ptr, m, w.h, y.ptr, C.byref(ep)))
+        return y
+
+    def free(self) -> None:
+        if self._owned and self.ptr:
+            self.device.lib.fb200_free(self.device.h, self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Device:
+    """fusor::Device::gpu() (fusor/src/device.rs:29-40): one CUDA device and stream."""
+
+    def __init__(self, ordinal: int = 0, stream: Optional[int] = None):
+        self.lib = load_library()
+        out = C.c_void_p()
+        rc = self.lib.fb200_device_create(ordinal, stream, C.byref(out))
+        if rc:
+            raise FusorError(rc, self.lib.fb200_last_error(None).decode())
+        self.h = out.value
+        self.ordinal = ordinal
+
+    def _check(self, rc: int) -> None:
+        if rc:
+            raise FusorError(rc, self.lib.fb200_last_error(self.h).decode())
+
+    def synchronize(self) -> None:
+        self._check(self.lib.fb200_device_synchronize(self.h))
+
+    @property
+    def launch_count(self) -> int:
+        return int(self.lib.fb200_launch_count(self.h))
+
+    def status(self) -> int:
+        s = C.c_int()
+        self._check(self.lib.fb200_device_status(self.h, C.byref(s)))
+        return s.value
+
+    def tensor(self, array, dtype=None) -> Tensor:
+        return Tensor.from_slice(self, array, dtype)
+
+    def empty(self, shape, dtype=np.float32) -> Tensor:
+        return Tensor(self, shape, dtype)
+
+    # ---- composite ops -------------------------------------------------------------------
+    def rms_norm(self, x: Tensor, weight: Tensor, eps: float, residual: Tensor = None,
+                 bias: Tensor = None) -> Tensor:
+        n = x.shape[-1]
+        rows = x.nbytes // 4 // n
+        y = Tensor(self, x.shape)
+        self._check(self.lib.fb200_rms_norm(self.h, x.ptr, residual.ptr if residual else None,
+                                            weight.ptr, bias.ptr if bias else None, eps, rows, n, y.ptr))
+        return y
+
+    def silu_mul(self, gate: Tensor, up: Tensor) -> Tensor:
+        y = Tensor(self, gate.shape)
+        self._check(self.lib.fb200_silu_mul(self.h, gate.ptr, up.ptr, gate.nbytes // 4, y.ptr))
+        return y
+
+    def argmax(self, logits: Tensor):
+        n = logits.shape[-1]
+        rows = logits.nbytes // 4 // n
+        ids, vals = Tensor(self, (rows,), np.uint32), Tensor(self, (rows,), np.float32)
+        self._check(self.lib.fb200_argmax(self.h, logits.ptr, rows, n, ids.ptr, vals.ptr))
+        return ids, vals
+
+    def flash_attention(self, q: Tensor, k: Tensor, v: Tensor, scale: float, skv: int = None,
+                        mask: Tensor = None, mask_kind: int = MASK_NONE) -> Tensor:
+        """Tensor::flash_attention (fusor/src/composite/flash_attention.rs:58-109).
+        q f32 [B,H,Sq,D]; k, v fp16 [B,Hkv,cap,D] of which the first `skv` rows are valid."""
+        b, h, sq, d = q.shape
+        _, hkv, cap, _ = k.shape
+        skv = cap if skv is None else skv
+        out = Tensor(self, q.shape)
+        self._check(self.lib.fb200_flash_attention(self.h, q.ptr, k.ptr, v.ptr, b, h, hkv, sq, skv,
+                                                   cap, d, scale, mask.ptr if mask else None,
+                                                   mask_kind, out.ptr))
+        return out
+
+    def close(self) -> None:
+        if self.h:
+            self.lib.fb200_device_destroy(self.h)
+            self.h = None
+
+
+class QMatrix:
+    """fusor::QMatrix (fusor/src/quantized.rs:80-284) on the device."""
+
+    def __init__(self, device: Device, handle: int):
+        self.device, self.h = device, handle
+        n, k = C.c_uint64(), C.c_uint64()
+        device.lib.fb200_qmatrix_shape(handle, C.byref(n), C.byref(k))
+        self.shape = (n.value, k.value)
+
+    @classmethod
+    def from_raw_bytes(cls, device: Device, shape: Sequence[int], raw, ggml_type: int) -> "QMatrix":
+        raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+        shp = (C.c_uint64 * len(shape))(*[int(s) for s in shape])
+        out = C.c_void_p()
+        device._check(device.lib.fb200_qmatrix_from_raw_bytes(device.h, shp, len(shape), _hp(raw),
+                                                              raw.size, ggml_type, C.byref(out)))
+        return cls(device, out.value)
+
+    @classmethod
+    def concat_rows(cls, mats: Sequence["QMatrix"]) -> Optional["QMatrix"]:
+        arr = (C.c_void_p * len(mats))(*[m.h for m in mats])
+        out = C.c_void_p()
+        rc = mats[0].device.lib.fb200_qmatrix_concat_rows(arr, len(mats), C.byref(out))
+        if rc == ERR_INVALID_SHAPE:
+            return None  # the reference returns None for mismatched parts
+        mats[0].device._check(rc)
+        return cls(mats[0].device, out.value)
+
+    @property
+    def ggml_type(self) -> int:
+        t = C.c_uint32()
+        self.device.lib.fb200_qmatrix_ggml_type(self.h, C.byref(t))
+        return t.value
+
+    @property
+    def nbytes(self) -> int:
+        n = C.c_uint64()
+        self.device.lib.fb200_qmatrix_nbytes(self.h, C.byref(n))
+        return n.value
+
+    def dequantize(self) -> Tensor:
+        out = Tensor(self.device, self.shape, np.float32)
+        self.device._check(self.device.lib.fb200_qmatrix_dequantize(self.h, out.ptr))
+        return out
+
+    def embedding(self, ids: Tensor) -> Tensor:
+        n_ids = ids.nbytes // 4
+        out = Tensor(self.device, ids.shape + (self.shape[1],), np.float32)
+        d = self.device
+        d._check(d.lib.fb200_embedding_lookup(d.h, self.h, ids.ptr, n_ids, out.ptr))
+        return out
+
+    def q_mat_mul_host(self, x: np.ndarray) -> np.ndarray:
+        """Product with host buffers (copies inside the call)."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        m = x.size // self.shape[1]
+        y = np.empty(x.shape[:-1] + (self.shape[0],), dtype=np.float32)
+        d = self.device
+        d._check(d.lib.fb200_q_mat_mul_host(d.h, _hp(x), m, self.h, _hp(y)))
+        return y
+
+    def free(self) -> None:
+        if self.h:
+            self.device.lib.fb200_qmatrix_free(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class RopeCache:
+    """fusor::RopeCache (fusor/src/composite/rope.rs:233-340): cos/sin tables on the device."""
+
+    def __init__(self, device: Device, head_dim: int, ctx: int, theta: float, scaling=None):
+        self.device, self.head_dim, self.ctx = device, head_dim, ctx
+        self.cos = Tensor(device, (ctx, head_dim // 2))
+        self.sin = Tensor(device, (ctx, head_dim // 2))
+        factor, low, high, orig = (0.0, 1.0, 4.0, ctx) if scaling is None else scaling
+        device._check(device.lib.fb200_rope_tables(device.h, head_dim, ctx, theta, factor, low, high,
+                                                   orig, self.cos.ptr, self.sin.ptr))
+
+    def forward(self, q: Tensor, k: Tensor, start_pos: int = 0, interleaved: bool = False):
+        """In place on q [B,H,S,D] and k [B,Hkv,S,D]."""
+        b, h, s, d = q.shape
+        hkv = k.shape[1]
+        dv = self.device
+        dv._check(dv.lib.fb200_rope_pair(dv.h, q.ptr, k.ptr, b, h, hkv, s, d, self.cos.ptr,
+                                         self.sin.ptr, start_pos, 1 if interleaved else 0))
+        return q, k
+
+    def forward_interleaved(self, q: Tensor, k: Tensor, start_pos: int = 0):
+        return self.forward(q, k, start_pos, True)
+
+
+class KvCache:
+    """fusor::KvCache (fusor/src/cache/kv_cache.rs:12-68) with an fp16 device buffer."""
+
+    def __init__(self, device: Device, batch: int, n_kv_head: int, head_dim: int, max_seq_len: int):
+        self.device = device
+        self.batch, self.n_kv_head, self.head_dim = batch, n_kv_head, head_dim
+        out = C.c_void_p()
+        device._check(device.lib.fb200_kv_cache_create(device.h, batch, n_kv_head, head_dim,
+                                                       max_seq_len, C.byref(out)))
+        self.h = out.value
+
+    def append(self, k: Tensor, v: Tensor):
+        """Appends k, v [B,Hkv,S,D]; returns (K, V) views of the whole buffers plus the length."""
+        self.device._check(self.device.lib.fb200_kv_cache_append(self.h, k.ptr, v.ptr, k.shape[2]))
+        kp, vp = C.c_void_p(), C.c_void_p()
+        self.device.lib.fb200_kv_cache_buffers(self.h, C.byref(kp), C.byref(vp))
+        shape = (self.batch, self.n_kv_head, self.capacity, self.head_dim)
+        return (Tensor(self.device, shape, np.float16, kp.value),
+                Tensor(self.device, shape, np.float16, vp.value), self.current_seq_len)
+
+    def reset(self):
+        self.device.lib.fb200_kv_cache_reset(self.h)
+
+    @property
+    def current_seq_len(self) -> int:
+        n, c = C.c_int(), C.c_int()
+        self.device.lib.fb200_kv_cache_len(self.h, C.byref(n), C.byref(c))
+        return n.value
+
+    @property
+    def capacity(self) -> int:
+        n, c = C.c_int(), C.c_int()
+        self.device.lib.fb200_kv_cache_len(self.h, C.byref(n), C.byref(c))
+        return c.value
+
+    def __del__(self):
+        try:
+            if self.h:
+                self.device.lib.fb200_kv_cache_free(self.h)
+                self.h = None
+        except Exception:
+            pass
+
+
+class Llama:
+    """Llama-architecture decoder (kalosm-llama Model::forward, raw/mod.rs:851-1049)."""
+
+    TENSORS = {"token_embd": 0, "output": 1, "attn_q": 2, "attn_k": 3, "attn_v": 4,
+               "attn_output": 5, "ffn_gate": 6, "ffn_up": 7, "ffn_down": 8, "attn_norm": 9,
+               "ffn_norm": 10, "output_norm": 11}
+
+    def __init__(self, device: Device, *, n_layer, hidden, ffn, n_head, n_kv_head, head_dim, vocab,
+                 max_seq_len, max_batch=1, rms_eps=1e-5, rope_theta=500000.0, rope_scaling=None):
+        self.device = device
+        factor, low, high, orig = (0.0, 1.0, 4.0, max_seq_len) if rope_scaling is None else rope_scaling
+        self.cfg = LlamaConfig(n_layer, hidden, ffn, n_head, n_kv_head, head_dim, vocab, max_seq_len,
+                               max_batch, rms_eps, rope_theta, factor, low, high, orig)
+        out = C.c_void_p()
+        device._check(device.lib.fb200_llama_create(device.h, C.byref(self.cfg), C.byref(out)))
+        self.h = out.value
+        self.vocab = vocab
+
+    def set_tensor(self, name: str, layer: int, ggml_type: int, shape, raw) -> None:
+        raw = np.ascontiguousarray(raw)
+        raw8 = raw.view(np.uint8).reshape(-1)
+        n = int(shape[0])
+        k = int(shape[1]) if len(shape) > 1 else 1
+        d = self.device
+        d._check(d.lib.fb200_llama_set_tensor(self.h, layer, self.TENSORS[name], ggml_type, n, k,
+                                              _hp(raw8), raw8.size))
+
+    def reset(self) -> None:
+        self.device._check(self.device.lib.fb200_llama_reset(self.h))
+
+    @property
+    def position(self) -> int:
+        p = C.c_int()
+        self.device.lib.fb200_llama_position(self.h, C.byref(p))
+        return p.value
+
+    def forward(self, tokens, want_logits: bool = True):
+        """tokens [batch, seq] -> (logits [batch, vocab] or None, greedy ids [batch])."""
+        t = np.ascontiguousarray(tokens, dtype=np.uint32)
+        if t.ndim == 1:
+            t = t[None, :]
+        batch, seq = t.shape
+        logits = np.empty((batch, self.vocab), dtype=np.float32) if want_logits else None
+        nxt = np.empty(batch, dtype=np.uint32)
+        d = self.device
+        d._check(d.lib.fb200_llama_forward(self.h, _hp(t), batch, seq, _hp(logits), _hp(nxt)))
+        return logits, nxt
+
+    def generate_greedy(self, tokens, steps: int) -> np.ndarray:
+        t = np.ascontiguousarray(tokens, dtype=np.uint32).reshape(-1)
+        out = np.empty((t.size, steps), dtype=np.uint32)
+        d = self.device
+        d._check(d.lib.fb200_llama_generate_greedy(self.h, _hp(t), t.size, steps, _hp(out)))
+        return out
+
+    def free(self) -> None:
+        if self.h:
+            self.device.lib.fb200_llama_free(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass

@@ -1,0 +1,369 @@
+// C ABI: device handles, tensors, QMatrix and q_mat_mul.
+#include <cstdarg>
+#include <cstring>
+
+#include "common.cuh"
+
+size_t fb200_xpack_bytes(int mp, uint64_t kp);
+int fb200_qgemv_chunk(fb200_device* dev, const fb200_qmatrix* w, const float* x, int mc, float* y,
+                      int epi, const float* r1, const float* r2, void* scratch);
+int fb200_dense_matmul(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_t m, float* y);
+int fb200_qgemm(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_t m, float* y);
+
+static thread_local std::string g_global_err;
+
+int fb200_fail(fb200_device* dev, int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  if (dev) dev->err = buf;
+  else g_global_err = buf;
+  return code;
+}
+
+int fb200_bind(fb200_device* dev) {
+  if (!dev) return fb200_fail(nullptr, FB200_ERR_INVALID_ARGUMENT, "null device handle");
+  FB_CUDA(dev, cudaSetDevice(dev->ordinal));
+  return FB200_OK;
+}
+
+int fb200_ensure(fb200_device* dev, void** buf, size_t* cur, size_t bytes) {
+  if (*cur >= bytes) return FB200_OK;
+  if (*buf) {
+    FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+    FB_CUDA(dev, cudaFree(*buf));
+    *buf = nullptr;
+    *cur = 0;
+  }
+  size_t want = bytes + bytes / 4 + 4096;
+  FB_CUDA(dev, cudaMalloc(buf, want));
+  *cur = want;
+  return FB200_OK;
+}
+
+extern "C" {
+
+int fb200_device_create(int ordinal, void* stream, fb200_device** out) {
+  if (!out) return fb200_fail(nullptr, FB200_ERR_INVALID_ARGUMENT, "out is null");
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || ordinal < 0 || ordinal >= count)
+    return fb200_fail(nullptr, FB200_ERR_CUDA, "no CUDA device %d (%s); this backend has no CPU fallback",
+                      ordinal, e != cudaSuccess ? cudaGetErrorString(e) : "ordinal out of range");
+  fb200_device* d = new fb200_device();
+  d->ordinal = ordinal;
+  if ((e = cudaSetDevice(ordinal)) != cudaSuccess) {
+    delete d;
+    return fb200_fail(nullptr, FB200_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
+  }
+  if (stream) {
+    d->stream = (cudaStream_t)stream;
+  } else {
+    if ((e = cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking)) != cudaSuccess) {
+      delete d;
+      return fb200_fail(nullptr, FB200_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e));
+    }
+    d->own_stream = true;
+  }
+  cudaDeviceGetAttribute(&d->sm_count, cudaDevAttrMultiProcessorCount, ordinal);
+  if ((e = cudaMalloc(&d->status, sizeof(int))) != cudaSuccess ||
+      (e = cudaMemsetAsync(d->status, 0, sizeof(int), d->stream)) != cudaSuccess) {
+    delete d;
+    return fb200_fail(nullptr, FB200_ERR_CUDA, "status word: %s", cudaGetErrorString(e));
+  }
+  *out = d;
+  return FB200_OK;
+}
+
+int fb200_device_destroy(fb200_device* dev) {
+  if (!dev) return FB200_OK;
+  cudaSetDevice(dev->ordinal);
+  cudaStreamSynchronize(dev->stream);
+  if (dev->xpack) cudaFree(dev->xpack);
+  if (dev->stage) cudaFree(dev->stage);
+  if (dev->status) cudaFree(dev->status);
+  if (dev->own_stream) cudaStreamDestroy(dev->stream);
+  delete dev;
+  return FB200_OK;
+}
+
+int fb200_device_synchronize(fb200_device* dev) {
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  return FB200_OK;
+}
+
+const char* fb200_last_error(const fb200_device* dev) {
+  return dev ? dev->err.c_str() : g_global_err.c_str();
+}
+
+uint64_t fb200_launch_count(const fb200_device* dev) { return dev ? dev->launches : 0; }
+
+int fb200_device_status(fb200_device* dev, int* status_out) {
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  FB_CUDA(dev, cudaMemcpyAsync(status_out, dev->status, sizeof(int), cudaMemcpyDeviceToHost, dev->stream));
+  FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  return FB200_OK;
+}
+
+int fb200_malloc(fb200_device* dev, size_t bytes, void** out_dev) {
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  if (!out_dev) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "out_dev is null");
+  *out_dev = nullptr;
+  if (bytes == 0) return FB200_OK;
+  FB_CUDA(dev, cudaMalloc(out_dev, bytes));
+  return FB200_OK;
+}
+
+int fb200_free(fb200_device* dev, void* ptr_dev) {
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  if (!ptr_dev) return FB200_OK;
+  FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  FB_CUDA(dev, cudaFree(ptr_dev));
+  return FB200_OK;
+}
+
+int fb200_upload(fb200_device* dev, void* dst_dev, const void* src_host, size_t bytes) {
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  if (bytes == 0) return FB200_OK;
+  FB_CUDA(dev, cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, dev->stream));
+  // Pageable sources are staged before the call returns; pinned ones are read asynchronously,
+  // so wait: the caller may reuse the buffer right away.
+  FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  return FB200_OK;
+}
+
+int fb200_download(fb200_device* dev, void* dst_host, const void* src_dev, size_t bytes) {
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  if (bytes)
+    FB_CUDA(dev, cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, dev->stream));
+  FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  return FB200_OK;
+}
+
+int fb200_memset(fb200_device* dev, void* dst_dev, int value, size_t bytes) {
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  if (bytes) FB_CUDA(dev, cudaMemsetAsync(dst_dev, value, bytes, dev->stream));
+  return FB200_OK;
+}
+
+// ---- QMatrix -----------------------------------------------------------------------------------
+
+int fb200_qmatrix_from_raw_bytes(fb200_device* dev, const uint64_t* shape, int rank,
+                                 const void* bytes_host, size_t nbytes, uint32_t ggml_type,
+                                 fb200_qmatrix** out) {
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  if (!out) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "out is null");
+  *out = nullptr;
+  if (rank != 2 || !shape)
+    return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "QMatrix needs a rank-2 shape, got rank %d", rank);
+  int be, bb;
+  if (!block_geom(ggml_type, &be, &bb))
+    return fb200_fail(dev, FB200_ERR_UNSUPPORTED_DTYPE, "unsupported ggml type %u", ggml_type);
+  const uint64_t n = shape[0], k = shape[1];
+  if (k % (uint64_t)be != 0)
+    return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "K = %llu is not a multiple of the block size %d",
+                      (unsigned long long)k, be);
+  const uint64_t expect = n * (k / be) * (uint64_t)bb;
+  if (expect != nbytes)
+    return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "shape [%llu, %llu] of type %u needs %llu bytes, got %zu",
+                      (unsigned long long)n, (unsigned long long)k, ggml_type,
+                      (unsigned long long)expect, nbytes);
+  if (n >= (1ull << 31) || k >= (1ull << 31))
+    return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "dimension too large");
+  fb200_qmatrix* q = new fb200_qmatrix();
+  q->dev = dev; q->type = ggml_type; q->n = n; q->k = k; q->raw_nbytes = nbytes;
+  TileGeom g;
+  uint8_t* raw_dev = nullptr;
+  auto cleanup = [&](int code) {
+    if (raw_dev) cudaFree(raw_dev);
+    if (q->data) cudaFree(q->data);
+    delete q;
+    return code;
+  };
+  if (tile_geom(ggml_type, &g)) {
+    q->tiled = true;
+    q->ntiles = (int)((n + 15) / 16);
+    q->ngroups = (int)((k + g.group_elems - 1) / g.group_elems);
+    q->data_bytes = (size_t)q->ntiles * q->ngroups * g.tg_bytes;
+    if (q->data_bytes) {
+      cudaError_t e = cudaMalloc(&raw_dev, nbytes ? nbytes : 1);
+      if (e == cudaSuccess) e = cudaMalloc(&q->data, q->data_bytes);
+      if (e == cudaSuccess && nbytes)
+        e = cudaMemcpyAsync(raw_dev, bytes_host, nbytes, cudaMemcpyHostToDevice, dev->stream);
+      if (e != cudaSuccess)
+        return cleanup(fb200_fail(dev, FB200_ERR_CUDA, "QMatrix upload: %s", cudaGetErrorString(e)));
+      rc = fb200_launch_repack(dev, ggml_type, raw_dev, n, k, q->data, q->ntiles, q->ngroups, 0);
+      if (rc) return cleanup(rc);
+      e = cudaStreamSynchronize(dev->stream);
+      if (e != cudaSuccess)
+        return cleanup(fb200_fail(dev, FB200_ERR_CUDA, "QMatrix repack: %s", cudaGetErrorString(e)));
+      cudaFree(raw_dev);
+      raw_dev = nullptr;
+    }
+  } else {
+    q->tiled = false;
+    q->data_bytes = nbytes;
+    if (nbytes) {
+      cudaError_t e = cudaMalloc(&q->data, nbytes);
+      if (e == cudaSuccess)
+        e = cudaMemcpyAsync(q->data, bytes_host, nbytes, cudaMemcpyHostToDevice, dev->stream);
+      if (e == cudaSuccess) e = cudaStreamSynchronize(dev->stream);
+      if (e != cudaSuccess)
+        return cleanup(fb200_fail(dev, FB200_ERR_CUDA, "QMatrix upload: %s", cudaGetErrorString(e)));
+    }
+  }
+  *out = q;
+  return FB200_OK;
+}
+
+int fb200_qmatrix_free(fb200_qmatrix* q) {
+  if (!q) return FB200_OK;
+  fb200_device* dev = q->dev;
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  cudaStreamSynchronize(dev->stream);
+  if (q->data) cudaFree(q->data);
+  delete q;
+  return FB200_OK;
+}
+
+int fb200_qmatrix_shape(const fb200_qmatrix* q, uint64_t* n_out, uint64_t* k_out) {
+  if (!q) return FB200_ERR_INVALID_ARGUMENT;
+  if (n_out) *n_out = q->n;
+  if (k_out) *k_out = q->k;
+  return FB200_OK;
+}
+
+int fb200_qmatrix_ggml_type(const fb200_qmatrix* q, uint32_t* type_out) {
+  if (!q || !type_out) return FB200_ERR_INVALID_ARGUMENT;
+  *type_out = q->type;
+  return FB200_OK;
+}
+
+int fb200_qmatrix_nbytes(const fb200_qmatrix* q, uint64_t* nbytes_out) {
+  if (!q || !nbytes_out) return FB200_ERR_INVALID_ARGUMENT;
+  *nbytes_out = q->raw_nbytes;
+  return FB200_OK;
+}
+
+int fb200_qmatrix_dequantize(const fb200_qmatrix* q, float* out_dev) {
+  if (!q) return FB200_ERR_INVALID_ARGUMENT;
+  int rc = fb200_bind(q->dev);
+  if (rc) return rc;
+  return fb200_launch_dequantize(q->dev, q, out_dev);
+}
+
+int fb200_qmatrix_concat_rows(const fb200_qmatrix* const* ms, int n, fb200_qmatrix** out) {
+  if (!out) return FB200_ERR_INVALID_ARGUMENT;
+  *out = nullptr;
+  if (!ms || n <= 0 || !ms[0]) return FB200_ERR_INVALID_ARGUMENT;
+  fb200_device* dev = ms[0]->dev;
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  uint64_t total_n = 0, raw = 0;
+  for (int i = 0; i < n; ++i) {
+    if (!ms[i] || ms[i]->dev != dev)
+      return fb200_fail(dev, FB200_ERR_DEVICE_MISMATCH, "concat_rows: matrices on different devices");
+    if (ms[i]->type != ms[0]->type || ms[i]->k != ms[0]->k || !ms[i]->tiled)
+      return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "concat_rows: needs one quantised type and one K");
+    if (i + 1 < n && ms[i]->n % 16 != 0)
+      return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "concat_rows: N of part %d is not a multiple of 16", i);
+    total_n += ms[i]->n;
+    raw += ms[i]->raw_nbytes;
+  }
+  fb200_qmatrix* q = new fb200_qmatrix(*ms[0]);
+  q->n = total_n;
+  q->raw_nbytes = raw;
+  q->ntiles = 0;
+  q->data_bytes = 0;
+  for (int i = 0; i < n; ++i) { q->ntiles += ms[i]->ntiles; q->data_bytes += ms[i]->data_bytes; }
+  q->data = nullptr;
+  cudaError_t e = cudaMalloc(&q->data, q->data_bytes ? q->data_bytes : 1);
+  size_t off = 0;
+  for (int i = 0; i < n && e == cudaSuccess; ++i) {
+    if (ms[i]->data_bytes)
+      e = cudaMemcpyAsync(q->data + off, ms[i]->data, ms[i]->data_bytes, cudaMemcpyDeviceToDevice, dev->stream);
+    off += ms[i]->data_bytes;
+  }
+  if (e != cudaSuccess) {
+    if (q->data) cudaFree(q->data);
+    delete q;
+    return fb200_fail(dev, FB200_ERR_CUDA, "concat_rows: %s", cudaGetErrorString(e));
+  }
+  *out = q;
+  return FB200_OK;
+}
+
+// ---- q_mat_mul ---------------------------------------------------------------------------------
+
+int fb200_q_mat_mul(fb200_device* dev, const float* x_dev, size_t m, const fb200_qmatrix* w,
+                    float* y_dev, const fb200_epilogue* ep) {
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  if (!w || !x_dev || !y_dev) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "q_mat_mul: null argument");
+  if (w->dev != dev)
+    return fb200_fail(dev, FB200_ERR_DEVICE_MISMATCH, "q_mat_mul: weight lives on another device handle");
+  const int epi = ep ? ep->kind : FB200_EPI_NONE;
+  if (epi < 0 || epi > 2) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "q_mat_mul: epilogue kind %d", epi);
+  if (epi == FB200_EPI_RESIDUAL && !ep->r1_dev)
+    return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "q_mat_mul: residual epilogue without r1");
+  if (m == 0 || w->n == 0) return FB200_OK;
+  if (!w->tiled) {
+    if (epi != FB200_EPI_NONE)
+      return fb200_fail(dev, FB200_ERR_UNSUPPORTED_DTYPE, "q_mat_mul: epilogues need Q4_0/Q8_0/Q4_K/Q6_K weights");
+    return fb200_dense_matmul(dev, w, x_dev, m, y_dev);
+  }
+  if (epi == FB200_EPI_SWIGLU && (w->ntiles % 2 != 0 || w->n % 32 != 0))
+    return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "q_mat_mul: SwiGLU needs N = 2F with F a multiple of 16");
+  if (epi == FB200_EPI_NONE && m > 32) {
+    rc = fb200_qgemm(dev, w, x_dev, m, y_dev);
+    if (rc != 1) return rc;  // 1 = shape not covered by the tensor-core GEMM; fall through
+  }
+  TileGeom g;
+  tile_geom(w->type, &g);
+  const uint64_t kp = (uint64_t)w->ngroups * g.group_elems;
+  rc = fb200_ensure(dev, &dev->xpack, &dev->xpack_bytes, fb200_xpack_bytes(32, kp));
+  if (rc) return rc;
+  const size_t n_out = epi == FB200_EPI_SWIGLU ? w->n / 2 : w->n;
+  for (size_t m0 = 0; m0 < m; m0 += 32) {
+    const int mc = (int)((m - m0) < 32 ? (m - m0) : 32);
+    rc = fb200_qgemv_chunk(dev, w, x_dev + m0 * w->k, mc, y_dev + m0 * n_out, epi,
+                           ep && ep->r1_dev ? ep->r1_dev + m0 * n_out : nullptr,
+                           ep && ep->r2_dev ? ep->r2_dev + m0 * n_out : nullptr, dev->xpack);
+    if (rc) return rc;
+  }
+  return FB200_OK;
+}
+
+int fb200_q_mat_mul_host(fb200_device* dev, const float* x_host, size_t m, const fb200_qmatrix* w,
+                         float* y_host) {
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  if (!w || !x_host || !y_host) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "q_mat_mul_host: null argument");
+  const size_t xb = m * w->k * sizeof(float), yb = m * w->n * sizeof(float);
+  const size_t xoff = (xb + 255) & ~(size_t)255;
+  rc = fb200_ensure(dev, &dev->stage, &dev->stage_bytes, xoff + yb);
+  if (rc) return rc;
+  float* xd = (float*)dev->stage;
+  float* yd = (float*)((uint8_t*)dev->stage + xoff);
+  if (xb) FB_CUDA(dev, cudaMemcpyAsync(xd, x_host, xb, cudaMemcpyHostToDevice, dev->stream));
+  rc = fb200_q_mat_mul(dev, xd, m, w, yd, nullptr);
+  if (rc) return rc;
+  if (yb) FB_CUDA(dev, cudaMemcpyAsync(y_host, yd, yb, cudaMemcpyDeviceToHost, dev->stream));
+  FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  return FB200_OK;
+}
+
+}  // extern "C"

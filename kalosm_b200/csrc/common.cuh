@@ -1,0 +1,111 @@
+// Internal definitions shared by the translation units of libfusor_b200.so.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <vector>
+
+#include "../../include/fusor_b200.h"
+
+// Device handle: one CUDA device, one stream, reusable scratch buffers.
+struct fb200_device {
+  int ordinal = 0;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  int sm_count = 148;
+  std::string err;
+  uint64_t launches = 0;
+  // scratch for packed activations (fp16 fragments, group sums, row scales); grown on demand
+  void* xpack = nullptr;
+  size_t xpack_bytes = 0;
+  // staging for the *_host entry points
+  void* stage = nullptr;
+  size_t stage_bytes = 0;
+  // device status word (set by kernels that recover from a fault)
+  int* status = nullptr;
+};
+
+// Quantised (or dense) weight matrix [N, K] in tile-interleaved device storage.
+struct fb200_qmatrix {
+  fb200_device* dev = nullptr;
+  uint32_t type = 0;
+  uint64_t n = 0, k = 0;
+  uint64_t raw_nbytes = 0;  // size of the GGUF byte stream this matrix was built from
+  // tiled storage
+  uint8_t* data = nullptr;
+  size_t data_bytes = 0;
+  int ntiles = 0;   // ceil(N / 16)
+  int ngroups = 0;  // K groups per tile (128 weights for 32-element blocks, 256 for K-quants)
+  bool tiled = false;  // false: `data` holds raw row-major bytes (F32/F16/Q5_0/Q5_K)
+};
+
+int fb200_fail(fb200_device* dev, int code, const char* fmt, ...);
+
+#define FB_CUDA(dev, expr)                                                              \
+  do {                                                                                  \
+    cudaError_t e__ = (expr);                                                           \
+    if (e__ != cudaSuccess)                                                             \
+      return fb200_fail((dev), FB200_ERR_CUDA, "%s: %s (%s:%d)", #expr,                 \
+                        cudaGetErrorString(e__), __FILE__, __LINE__);                   \
+  } while (0)
+
+#define FB_LAUNCH_CHECK(dev)                                                            \
+  do {                                                                                  \
+    (dev)->launches++;                                                                  \
+    cudaError_t e__ = cudaGetLastError();                                               \
+    if (e__ != cudaSuccess)                                                             \
+      return fb200_fail((dev), FB200_ERR_CUDA, "kernel launch: %s (%s:%d)",             \
+                        cudaGetErrorString(e__), __FILE__, __LINE__);                   \
+  } while (0)
+
+// Makes the handle's device current for the calling thread.
+int fb200_bind(fb200_device* dev);
+// Ensures a scratch buffer of at least `bytes` (never shrinks).
+int fb200_ensure(fb200_device* dev, void** buf, size_t* cur, size_t bytes);
+
+// ---- geometry of the tiled storage ----------------------------------------------------------
+// A tile is 16 consecutive rows of W; a tile-group is the bytes of those rows for one K group.
+// Inside a tile-group the quant bytes are ordered so that lane (g = lane / 4, t = lane % 4) of
+// a warp reads, with one 16-byte load per 512-byte plane, exactly the bytes it feeds to
+// mma.m16n8k16 for rows g (plane h = 0) and g + 8 (plane h = 1).
+struct TileGeom {
+  int block_elems;  // GGUF block size (32 or 256)
+  int block_bytes;  // GGUF block bytes
+  int group_elems;  // K elements per tile-group
+  int tg_bytes;     // bytes per tile-group = 16 rows * group_elems / block_elems * block_bytes
+};
+
+inline bool tile_geom(uint32_t type, TileGeom* g) {
+  switch (type) {
+    case FB200_Q4_0: *g = {32, 18, 128, 1152}; return true;
+    case FB200_Q8_0: *g = {32, 34, 128, 2176}; return true;
+    case FB200_Q4_K: *g = {256, 144, 256, 2304}; return true;
+    case FB200_Q6_K: *g = {256, 210, 256, 3360}; return true;
+    default: return false;
+  }
+}
+
+inline bool block_geom(uint32_t type, int* elems, int* bytes) {
+  switch (type) {
+    case FB200_Q4_0: *elems = 32; *bytes = 18; return true;
+    case FB200_Q5_0: *elems = 32; *bytes = 22; return true;
+    case FB200_Q8_0: *elems = 32; *bytes = 34; return true;
+    case FB200_Q4_K: *elems = 256; *bytes = 144; return true;
+    case FB200_Q5_K: *elems = 256; *bytes = 176; return true;
+    case FB200_Q6_K: *elems = 256; *bytes = 210; return true;
+    case FB200_F32: *elems = 1; *bytes = 4; return true;
+    case FB200_F16: *elems = 1; *bytes = 2; return true;
+    default: return false;
+  }
+}
+
+// internal launchers (defined in the .cu files)
+int fb200_launch_repack(fb200_device* dev, uint32_t type, const uint8_t* raw_dev, uint64_t n,
+                        uint64_t k, uint8_t* tiled_dev, int ntiles, int ngroups, int tile0);
+int fb200_launch_dequantize(fb200_device* dev, const fb200_qmatrix* q, float* out_dev);
+int fb200_launch_dequantize_rows(fb200_device* dev, const fb200_qmatrix* q,
+                                 const uint32_t* ids_dev, size_t n_ids, float* out_dev);

@@ -1,0 +1,502 @@
+// Whole-model host code: Llama-architecture decoder on one device.
+//
+// Order of operations follows Model::forward_last_hidden_from_embeddings
+// (models/kalosm-llama/src/raw/mod.rs:925-1049): pre-norm -> attention -> residual + norm ->
+// SiLU-gated FFN -> + attention output + residual; final norm; only the last position reaches
+// the output projection (:1046). Attention block: LlamaAttention::forward
+// (raw/attention_layer.rs:514-573) with separate q/k/v projections (:281-427), interleaved RoPE
+// (raw/mod.rs:488-490) and a KV cache per layer (raw/cache.rs:14-46).
+// The reference's lazy graph + resolver (fusor-ml/core/src/compute_graph/resolve/run.rs:29-135)
+// is replaced by a fixed kernel sequence on one CUDA stream; a single-token step is captured
+// into a CUDA graph whose kernels read the position from device memory, so it replays as is.
+#include <cstring>
+#include <memory>
+
+#include "common.cuh"
+
+void fb200_rope_tables_host(int head_dim, int ctx, float theta, float factor, float low_ff,
+                            float high_ff, int original_ctx, std::vector<float>& cs,
+                            std::vector<float>& sn);
+int fb200_launch_rms_norm_strided(fb200_device* dev, const float* x, size_t x_stride,
+                                  const float* res, const float* w, float eps, size_t rows,
+                                  size_t n, float* y);
+int fb200_launch_argmax(fb200_device* dev, const float* logits, size_t rows, size_t n,
+                        uint32_t* ids, float* vals);
+int fb200_launch_attention(fb200_device* dev, const float* q, const __half* k, const __half* v,
+                           int b, int h, int hkv, int sq, int skv, const int* skv_dev, int cap,
+                           int d, float scale, const float* mask, int mask_kind, float* out,
+                           float* part, int nsplit, int bshd);
+int fb200_attention_nsplit(const fb200_device* dev, int b, int hkv, int groups, int sq, int skv);
+int fb200_attention_scratch_bytes(int b, int h, int sq, int d, int nsplit, size_t* out);
+
+namespace {
+
+struct LayerW {
+  fb200_qmatrix *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr;
+  fb200_qmatrix *gate = nullptr, *up = nullptr, *down = nullptr, *gate_up = nullptr;
+  float *attn_norm = nullptr, *ffn_norm = nullptr;
+  __half *kc = nullptr, *vc = nullptr;  // [max_batch, Hkv, max_seq, D]
+};
+
+// q [rows, H*D] rotated in place; k rotated and v copied into the fp16 cache at position
+// *pos + s. Row = b * S + s. RoPE pairs are interleaved (2p, 2p+1) as in
+// fusor-ml/fusor/src/composite/rope.rs:77-108; append as KvCache::append
+// (fusor-ml/fusor/src/cache/kv_cache.rs:50-62).
+__global__ void rope_append_kernel(float* __restrict__ q, const float* __restrict__ k,
+                                   const float* __restrict__ v, __half* __restrict__ kc,
+                                   __half* __restrict__ vc, const float* __restrict__ cs,
+                                   const float* __restrict__ sn, const int* __restrict__ pos_dev,
+                                   int s_len, int h, int hkv, int d, int cap, size_t total) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int half = d >> 1;
+  const int per_row = (h + 2 * hkv) * half;
+  const size_t row = i / per_row;
+  int rem = (int)(i % per_row);
+  const int b = (int)(row / s_len), s = (int)(row % s_len);
+  const int pos = *pos_dev + s;
+  if (rem < h * half) {
+    const int head = rem / half, p = rem % half;
+    float* x = q + (row * h + head) * d;
+    const float c = cs[(size_t)pos * half + p], sv = sn[(size_t)pos * half + p];
+    const float x0 = x[2 * p], x1 = x[2 * p + 1];
+    x[2 * p] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sv));
+    x[2 * p + 1] = __fadd_rn(__fmul_rn(x0, sv), __fmul_rn(x1, c));
+    return;
+  }
+  rem -= h * half;
+  const bool is_v = rem >= hkv * half;
+  if (is_v) rem -= hkv * half;
+  const int head = rem / half, p = rem % half;
+  const size_t dst = (((size_t)b * hkv + head) * cap + pos) * d + 2 * p;
+  if (is_v) {
+    const float* x = v + (row * hkv + head) * d;
+    *reinterpret_cast<__half2*>(vc + dst) = __floats2half2_rn(x[2 * p], x[2 * p + 1]);
+  } else {
+    const float* x = k + (row * hkv + head) * d;
+    const float c = cs[(size_t)pos * half + p], sv = sn[(size_t)pos * half + p];
+    const float x0 = x[2 * p], x1 = x[2 * p + 1];
+    const float y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sv));
+    const float y1 = __fadd_rn(__fmul_rn(x0, sv), __fmul_rn(x1, c));
+    *reinterpret_cast<__half2*>(kc + dst) = __floats2half2_rn(y0, y1);
+  }
+}
+
+// After a greedy step: record the new ids, feed them back, advance the position.
+__global__ void advance_kernel(const uint32_t* __restrict__ next, uint32_t* __restrict__ ids,
+                               uint32_t* __restrict__ hist, int* pos_dev, int* step_dev, int batch,
+                               int max_steps, int advance) {
+  const int b = threadIdx.x;
+  const int step = *step_dev;
+  if (b < batch) {
+    ids[b] = next[b];
+    if (hist && step < max_steps) hist[(size_t)b * max_steps + step] = next[b];
+  }
+  __syncthreads();
+  if (b == 0) {
+    *pos_dev += advance;
+    *step_dev = step + 1;
+  }
+}
+
+}  // namespace
+
+struct fb200_llama {
+  fb200_device* dev = nullptr;
+  fb200_llama_config cfg{};
+  fb200_qmatrix *token_embd = nullptr, *output = nullptr;
+  float* output_norm = nullptr;
+  std::vector<LayerW> layers;
+  float *rope_cos = nullptr, *rope_sin = nullptr;
+  bool finalized = false;
+  int pos = 0;
+  // activation buffers, sized for `rows_cap` rows
+  size_t rows_cap = 0;
+  float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr,
+        *attn_out = nullptr, *hbuf = nullptr, *gbuf = nullptr, *last = nullptr, *logits = nullptr;
+  float* att_part = nullptr;
+  size_t att_part_bytes = 0;
+  uint32_t *ids = nullptr, *next = nullptr, *hist = nullptr;
+  int hist_cap = 0;
+  int *pos_dev = nullptr, *step_dev = nullptr;
+  // CUDA graph of a single-token step, per batch size
+  cudaGraphExec_t graph_exec = nullptr;
+  int graph_batch = 0;
+  uint64_t graph_kernels = 0;  // kernels inside the captured step
+};
+
+namespace {
+
+int alloc_f(fb200_device* dev, float** p, size_t n) {
+  if (*p) { cudaFree(*p); *p = nullptr; }
+  FB_CUDA(dev, cudaMalloc(p, (n ? n : 1) * sizeof(float)));
+  return FB200_OK;
+}
+
+int ensure_rows(fb200_llama* m, size_t rows) {
+  if (rows <= m->rows_cap) return FB200_OK;
+  fb200_device* dev = m->dev;
+  const auto& c = m->cfg;
+  FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  if (m->graph_exec) { cudaGraphExecDestroy(m->graph_exec); m->graph_exec = nullptr; }
+  int rc;
+  if ((rc = alloc_f(dev, &m->x, rows * c.hidden))) return rc;
+  if ((rc = alloc_f(dev, &m->xn, rows * c.hidden))) return rc;
+  if ((rc = alloc_f(dev, &m->q, rows * c.n_head * c.head_dim))) return rc;
+  if ((rc = alloc_f(dev, &m->k, rows * c.n_kv_head * c.head_dim))) return rc;
+  if ((rc = alloc_f(dev, &m->v, rows * c.n_kv_head * c.head_dim))) return rc;
+  if ((rc = alloc_f(dev, &m->att, rows * c.n_head * c.head_dim))) return rc;
+  if ((rc = alloc_f(dev, &m->attn_out, rows * c.hidden))) return rc;
+  if ((rc = alloc_f(dev, &m->hbuf, rows * c.ffn))) return rc;
+  if ((rc = alloc_f(dev, &m->gbuf, rows * c.ffn))) return rc;
+  if (m->ids) cudaFree(m->ids);
+  FB_CUDA(dev, cudaMalloc(&m->ids, rows * sizeof(uint32_t)));
+  m->rows_cap = rows;
+  return FB200_OK;
+}
+
+int finalize(fb200_llama* m) {
+  if (m->finalized) return FB200_OK;
+  fb200_device* dev = m->dev;
+  const auto& c = m->cfg;
+  if (!m->token_embd || !m->output_norm)
+    return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "llama: token_embd / output_norm not set");
+  for (int i = 0; i < c.n_layer; ++i) {
+    LayerW& L = m->layers[i];
+    if (!L.wq || !L.wk || !L.wv || !L.wo || !L.gate || !L.up || !L.down || !L.attn_norm || !L.ffn_norm)
+      return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "llama: layer %d is missing a tensor", i);
+    if (!L.gate_up) {
+      // QMatrix::concat_rows (fusor-ml/fusor/src/quantized.rs:102-112): gate and up share one
+      // launch with the SwiGLU epilogue when their types match.
+      const fb200_qmatrix* pair[2] = {L.gate, L.up};
+      fb200_qmatrix* gu = nullptr;
+      if (L.gate->tiled && L.gate->type == L.up->type && L.gate->n == L.up->n && L.gate->n % 16 == 0 &&
+          fb200_qmatrix_concat_rows(pair, 2, &gu) == FB200_OK) {
+        L.gate_up = gu;
+        fb200_qmatrix_free(L.gate);
+        fb200_qmatrix_free(L.up);
+        L.gate = L.up = nullptr;
+      }
+    }
+  }
+  m->finalized = true;
+  return FB200_OK;
+}
+
+// One forward pass over `seq` new positions per batch row; ids are already in m->ids.
+// Leaves logits [batch, vocab] in m->logits and the greedy ids in m->next.
+int run_forward(fb200_llama* m, int batch, int seq) {
+  fb200_device* dev = m->dev;
+  const auto& c = m->cfg;
+  const size_t rows = (size_t)batch * seq;
+  const int E = c.hidden, H = c.n_head, HK = c.n_kv_head, D = c.head_dim;
+  int rc;
+  if ((rc = fb200_embedding_lookup(dev, m->token_embd, m->ids, rows, m->x))) return rc;
+  const float scale = (float)(1.0 / sqrt((double)D));  // attention_layer.rs:674
+  const int nsplit = fb200_attention_nsplit(dev, batch, HK, H / HK, seq, seq > 1 ? seq : c.max_seq_len);
+  size_t part_bytes;
+  fb200_attention_scratch_bytes(batch, H, seq, D, nsplit, &part_bytes);
+  if (part_bytes > m->att_part_bytes)
+    return fb200_fail(dev, FB200_ERR_CAPACITY, "llama: attention scratch too small");
+  for (int li = 0; li < c.n_layer; ++li) {
+    LayerW& L = m->layers[li];
+    if ((rc = fb200_launch_rms_norm_strided(dev, m->x, E, nullptr, L.attn_norm, c.rms_eps, rows, E, m->xn))) return rc;
+    if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wq, m->q, nullptr))) return rc;
+    if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wk, m->k, nullptr))) return rc;
+    if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wv, m->v, nullptr))) return rc;
+    {
+      const size_t total = rows * (size_t)(H + 2 * HK) * (D / 2);
+      rope_append_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(
+          m->q, m->k, m->v, L.kc, L.vc, m->rope_cos, m->rope_sin, m->pos_dev, seq, H, HK, D,
+          c.max_seq_len, total);
+      FB_LAUNCH_CHECK(dev);
+    }
+    // mask only when seq_len > 1 (raw/mod.rs:969); strictly causal over the new positions
+    if ((rc = fb200_launch_attention(dev, m->q, L.kc, L.vc, batch, H, HK, seq, 0, m->pos_dev,
+                                     c.max_seq_len, D, scale, nullptr, seq > 1 ? 1 : 0, m->att,
+                                     m->att_part, nsplit, 1))) return rc;
+    if ((rc = fb200_q_mat_mul(dev, m->att, rows, L.wo, m->attn_out, nullptr))) return rc;
+    // ffn_norm.forward_residual_f32(attn, residual) (raw/mod.rs:1017)
+    if ((rc = fb200_launch_rms_norm_strided(dev, m->attn_out, E, m->x, L.ffn_norm, c.rms_eps, rows, E, m->xn))) return rc;
+    if (L.gate_up) {
+      fb200_epilogue ep{FB200_EPI_SWIGLU, nullptr, nullptr};
+      if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.gate_up, m->hbuf, &ep))) return rc;
+    } else {
+      if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.gate, m->gbuf, nullptr))) return rc;
+      if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.up, m->hbuf, nullptr))) return rc;
+      if ((rc = fb200_silu_mul(dev, m->gbuf, m->hbuf, rows * (size_t)c.ffn, m->hbuf))) return rc;
+    }
+    // (down(h) + attn) + residual, written over the residual stream
+    // (attention_layer.rs:170-172 for one position, raw/mod.rs:1036 otherwise)
+    fb200_epilogue ep{FB200_EPI_RESIDUAL, m->attn_out, m->x};
+    if ((rc = fb200_q_mat_mul(dev, m->hbuf, rows, L.down, m->x, &ep))) return rc;
+  }
+  // final norm on the last position of every batch row, then the output projection
+  if ((rc = fb200_launch_rms_norm_strided(dev, m->x + (size_t)(seq - 1) * E, (size_t)seq * E, nullptr,
+                                          m->output_norm, c.rms_eps, batch, E, m->last))) return rc;
+  fb200_qmatrix* ow = m->output ? m->output : m->token_embd;
+  if ((rc = fb200_q_mat_mul(dev, m->last, batch, ow, m->logits, nullptr))) return rc;
+  if ((rc = fb200_launch_argmax(dev, m->logits, batch, c.vocab, m->next, nullptr))) return rc;
+  return FB200_OK;
+}
+
+int launch_advance(fb200_llama* m, int batch, int advance, bool record) {
+  advance_kernel<<<1, 64 > batch ? 64 : ((batch + 31) / 32) * 32, 0, m->dev->stream>>>(
+      m->next, m->ids, record ? m->hist : nullptr, m->pos_dev, m->step_dev, batch, m->hist_cap, advance);
+  FB_LAUNCH_CHECK(m->dev);
+  return FB200_OK;
+}
+
+// Captures embed -> layers -> logits -> argmax -> advance for one token per batch row.
+int ensure_graph(fb200_llama* m, int batch) {
+  if (m->graph_exec && m->graph_batch == batch) return FB200_OK;
+  fb200_device* dev = m->dev;
+  if (m->graph_exec) { cudaGraphExecDestroy(m->graph_exec); m->graph_exec = nullptr; }
+  // make sure every lazily grown scratch buffer already has its final size
+  int rc = run_forward(m, batch, 1);
+  if (rc) return rc;
+  FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  const uint64_t launches_before = dev->launches;
+  cudaGraph_t graph = nullptr;
+  FB_CUDA(dev, cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeThreadLocal));
+  rc = run_forward(m, batch, 1);
+  if (!rc) rc = launch_advance(m, batch, 1, true);
+  cudaError_t e = cudaStreamEndCapture(dev->stream, &graph);
+  m->graph_kernels = dev->launches - launches_before;
+  dev->launches = launches_before;  // capture enqueues nothing
+  if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
+  if (e != cudaSuccess) return fb200_fail(dev, FB200_ERR_CUDA, "graph capture: %s", cudaGetErrorString(e));
+  e = cudaGraphInstantiate(&m->graph_exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) return fb200_fail(dev, FB200_ERR_CUDA, "graph instantiate: %s", cudaGetErrorString(e));
+  m->graph_batch = batch;
+  return FB200_OK;
+}
+
+}  // namespace
+
+int fb200_launch_rms_norm(fb200_device* dev, const float* x, const float* res, const float* w,
+                          const float* b, float eps, size_t rows, size_t n, float* y);
+
+extern "C" {
+
+int fb200_llama_create(fb200_device* dev, const fb200_llama_config* cfg, fb200_llama** out) {
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  if (!cfg || !out) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "llama_create: null argument");
+  *out = nullptr;
+  const auto& c = *cfg;
+  if (c.n_layer <= 0 || c.hidden <= 0 || c.ffn <= 0 || c.n_head <= 0 || c.n_kv_head <= 0 ||
+      c.head_dim <= 0 || c.vocab <= 0 || c.max_seq_len <= 0 || c.max_batch <= 0 ||
+      c.n_head % c.n_kv_head != 0 || (c.head_dim != 64 && c.head_dim != 128))
+    return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "llama_create: unsupported configuration");
+  auto m = std::unique_ptr<fb200_llama>(new fb200_llama());
+  m->dev = dev;
+  m->cfg = c;
+  m->layers.resize(c.n_layer);
+  std::vector<float> cs, sn;
+  fb200_rope_tables_host(c.head_dim, c.max_seq_len, c.rope_theta, c.rope_factor,
+                         c.rope_low_freq_factor, c.rope_high_freq_factor, c.rope_original_ctx, cs, sn);
+  FB_CUDA(dev, cudaMalloc(&m->rope_cos, cs.size() * 4));
+  FB_CUDA(dev, cudaMalloc(&m->rope_sin, sn.size() * 4));
+  FB_CUDA(dev, cudaMemcpy(m->rope_cos, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice));
+  FB_CUDA(dev, cudaMemcpy(m->rope_sin, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice));
+  const size_t kv = (size_t)c.max_batch * c.n_kv_head * c.max_seq_len * c.head_dim * sizeof(__half);
+  for (auto& L : m->layers) {
+    FB_CUDA(dev, cudaMalloc(&L.kc, kv));
+    FB_CUDA(dev, cudaMalloc(&L.vc, kv));
+    FB_CUDA(dev, cudaMemset(L.kc, 0, kv));
+    FB_CUDA(dev, cudaMemset(L.vc, 0, kv));
+  }
+  FB_CUDA(dev, cudaMalloc(&m->last, (size_t)c.max_batch * c.hidden * 4));
+  FB_CUDA(dev, cudaMalloc(&m->logits, (size_t)c.max_batch * c.vocab * 4));
+  FB_CUDA(dev, cudaMalloc(&m->next, (size_t)c.max_batch * 4));
+  FB_CUDA(dev, cudaMalloc(&m->pos_dev, 4));
+  FB_CUDA(dev, cudaMalloc(&m->step_dev, 4));
+  FB_CUDA(dev, cudaMemset(m->pos_dev, 0, 4));
+  FB_CUDA(dev, cudaMemset(m->step_dev, 0, 4));
+  // attention split scratch: the largest a forward pass can ask for is bounded by 64 splits of
+  // a single-token step or one split set of a whole-context prefill
+  size_t a1, a2;
+  fb200_attention_scratch_bytes(c.max_batch, c.n_head, 1, c.head_dim, 64, &a1);
+  fb200_attention_scratch_bytes(c.max_batch, c.n_head, c.max_seq_len, c.head_dim, 2, &a2);
+  m->att_part_bytes = a1 > a2 ? a1 : a2;
+  FB_CUDA(dev, cudaMalloc(&m->att_part, m->att_part_bytes));
+  *out = m.release();
+  return FB200_OK;
+}
+
+int fb200_llama_free(fb200_llama* m) {
+  if (!m) return FB200_OK;
+  fb200_device* dev = m->dev;
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  cudaStreamSynchronize(dev->stream);
+  if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
+  for (auto& L : m->layers) {
+    fb200_qmatrix* qs[] = {L.wq, L.wk, L.wv, L.wo, L.gate, L.up, L.down, L.gate_up};
+    for (auto* q : qs) if (q) fb200_qmatrix_free(q);
+    float* fs[] = {L.attn_norm, L.ffn_norm};
+    for (auto* f : fs) if (f) cudaFree(f);
+    if (L.kc) cudaFree(L.kc);
+    if (L.vc) cudaFree(L.vc);
+  }
+  if (m->token_embd) fb200_qmatrix_free(m->token_embd);
+  if (m->output) fb200_qmatrix_free(m->output);
+  void* bufs[] = {m->output_norm, m->rope_cos, m->rope_sin, m->x, m->xn, m->q, m->k, m->v, m->att,
+                  m->attn_out, m->hbuf, m->gbuf, m->last, m->logits, m->att_part, m->ids, m->next,
+                  m->hist, m->pos_dev, m->step_dev};
+  for (void* b : bufs) if (b) cudaFree(b);
+  delete m;
+  return FB200_OK;
+}
+
+int fb200_llama_set_tensor(fb200_llama* m, int layer, int which, uint32_t ggml_type, uint64_t n,
+                           uint64_t k, const void* bytes_host, size_t nbytes) {
+  if (!m) return FB200_ERR_INVALID_ARGUMENT;
+  fb200_device* dev = m->dev;
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  const auto& c = m->cfg;
+  if (m->finalized) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "llama: tensors are frozen after the first forward pass");
+  if (which >= FB200_T_ATTN_NORM) {
+    const uint64_t len = n * (k ? k : 1);
+    if (ggml_type != FB200_F32 || len != (uint64_t)c.hidden || nbytes != len * 4)
+      return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "llama: norm weights are f32 vectors of length hidden");
+    float** dst;
+    if (which == FB200_T_OUTPUT_NORM) dst = &m->output_norm;
+    else {
+      if (layer < 0 || layer >= c.n_layer) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "llama: layer %d", layer);
+      dst = which == FB200_T_ATTN_NORM ? &m->layers[layer].attn_norm : &m->layers[layer].ffn_norm;
+    }
+    if (!*dst) FB_CUDA(dev, cudaMalloc(dst, len * 4));
+    FB_CUDA(dev, cudaMemcpy(*dst, bytes_host, len * 4, cudaMemcpyHostToDevice));
+    return FB200_OK;
+  }
+  uint64_t en = 0, ek = 0;
+  fb200_qmatrix** slot = nullptr;
+  const uint64_t qd = (uint64_t)c.n_head * c.head_dim, kvd = (uint64_t)c.n_kv_head * c.head_dim;
+  if (which == FB200_T_TOKEN_EMBD) { slot = &m->token_embd; en = c.vocab; ek = c.hidden; }
+  else if (which == FB200_T_OUTPUT) { slot = &m->output; en = c.vocab; ek = c.hidden; }
+  else {
+    if (layer < 0 || layer >= c.n_layer) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "llama: layer %d", layer);
+    LayerW& L = m->layers[layer];
+    switch (which) {
+      case FB200_T_ATTN_Q: slot = &L.wq; en = qd; ek = c.hidden; break;
+      case FB200_T_ATTN_K: slot = &L.wk; en = kvd; ek = c.hidden; break;
+      case FB200_T_ATTN_V: slot = &L.wv; en = kvd; ek = c.hidden; break;
+      case FB200_T_ATTN_OUTPUT: slot = &L.wo; en = c.hidden; ek = qd; break;
+      case FB200_T_FFN_GATE: slot = &L.gate; en = c.ffn; ek = c.hidden; break;
+      case FB200_T_FFN_UP: slot = &L.up; en = c.ffn; ek = c.hidden; break;
+      case FB200_T_FFN_DOWN: slot = &L.down; en = c.hidden; ek = c.ffn; break;
+      default: return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "llama: tensor id %d", which);
+    }
+  }
+  if (n != en || k != ek)
+    return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "llama: tensor %d has shape [%llu, %llu], expected [%llu, %llu]",
+                      which, (unsigned long long)n, (unsigned long long)k, (unsigned long long)en, (unsigned long long)ek);
+  if (*slot) { fb200_qmatrix_free(*slot); *slot = nullptr; }
+  const uint64_t shape[2] = {n, k};
+  return fb200_qmatrix_from_raw_bytes(dev, shape, 2, bytes_host, nbytes, ggml_type, slot);
+}
+
+int fb200_llama_reset(fb200_llama* m) {
+  if (!m) return FB200_ERR_INVALID_ARGUMENT;
+  fb200_device* dev = m->dev;
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  m->pos = 0;
+  FB_CUDA(dev, cudaMemsetAsync(m->pos_dev, 0, 4, dev->stream));
+  FB_CUDA(dev, cudaMemsetAsync(m->step_dev, 0, 4, dev->stream));
+  return FB200_OK;
+}
+
+int fb200_llama_position(const fb200_llama* m, int* pos_out) {
+  if (!m || !pos_out) return FB200_ERR_INVALID_ARGUMENT;
+  *pos_out = m->pos;
+  return FB200_OK;
+}
+
+int fb200_llama_forward(fb200_llama* m, const uint32_t* tokens_host, int batch, int seq,
+                        float* logits_host, uint32_t* next_host) {
+  if (!m) return FB200_ERR_INVALID_ARGUMENT;
+  fb200_device* dev = m->dev;
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  const auto& c = m->cfg;
+  if (!tokens_host || batch <= 0 || batch > c.max_batch || seq <= 0)
+    return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "llama_forward: batch %d seq %d", batch, seq);
+  if (m->pos + seq > c.max_seq_len)
+    return fb200_fail(dev, FB200_ERR_CAPACITY, "llama_forward: position %d + %d exceeds max_seq_len %d", m->pos, seq, c.max_seq_len);
+  if ((rc = finalize(m))) return rc;
+  const size_t rows = (size_t)batch * seq;
+  if ((rc = ensure_rows(m, rows))) return rc;
+  if (seq == 1) {
+    // single-token step: replay the captured graph (capture leaves the position untouched)
+    if (!m->graph_exec || m->graph_batch != batch) {
+      FB_CUDA(dev, cudaMemcpyAsync(m->ids, tokens_host, rows * 4, cudaMemcpyHostToDevice, dev->stream));
+      if ((rc = ensure_graph(m, batch))) return rc;
+    }
+    FB_CUDA(dev, cudaMemcpyAsync(m->ids, tokens_host, rows * 4, cudaMemcpyHostToDevice, dev->stream));
+    FB_CUDA(dev, cudaGraphLaunch(m->graph_exec, dev->stream));
+    dev->launches += m->graph_kernels;
+  } else {
+    FB_CUDA(dev, cudaMemcpyAsync(m->ids, tokens_host, rows * 4, cudaMemcpyHostToDevice, dev->stream));
+    if ((rc = run_forward(m, batch, seq))) return rc;
+    if ((rc = launch_advance(m, batch, seq, false))) return rc;
+  }
+  m->pos += seq;
+  if (logits_host)
+    FB_CUDA(dev, cudaMemcpyAsync(logits_host, m->logits, (size_t)batch * c.vocab * 4, cudaMemcpyDeviceToHost, dev->stream));
+  if (next_host)
+    FB_CUDA(dev, cudaMemcpyAsync(next_host, m->next, (size_t)batch * 4, cudaMemcpyDeviceToHost, dev->stream));
+  FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  return FB200_OK;
+}
+
+int fb200_llama_generate_greedy(fb200_llama* m, const uint32_t* tokens_host, int batch, int steps,
+                                uint32_t* out_host) {
+  if (!m) return FB200_ERR_INVALID_ARGUMENT;
+  fb200_device* dev = m->dev;
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  const auto& c = m->cfg;
+  if (!tokens_host || !out_host || batch <= 0 || batch > c.max_batch || steps <= 0)
+    return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "generate_greedy: batch %d steps %d", batch, steps);
+  if (m->pos + steps > c.max_seq_len)
+    return fb200_fail(dev, FB200_ERR_CAPACITY, "generate_greedy: position %d + %d exceeds max_seq_len %d", m->pos, steps, c.max_seq_len);
+  if ((rc = finalize(m))) return rc;
+  if ((rc = ensure_rows(m, batch))) return rc;
+  if (m->hist_cap < steps || !m->hist) {
+    FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+    if (m->hist) cudaFree(m->hist);
+    m->hist = nullptr;
+    FB_CUDA(dev, cudaMalloc(&m->hist, (size_t)c.max_batch * steps * 4));
+    m->hist_cap = steps;
+    if (m->graph_exec) { cudaGraphExecDestroy(m->graph_exec); m->graph_exec = nullptr; }
+  }
+  FB_CUDA(dev, cudaMemcpyAsync(m->ids, tokens_host, (size_t)batch * 4, cudaMemcpyHostToDevice, dev->stream));
+  if ((rc = ensure_graph(m, batch))) return rc;
+  FB_CUDA(dev, cudaMemcpyAsync(m->ids, tokens_host, (size_t)batch * 4, cudaMemcpyHostToDevice, dev->stream));
+  FB_CUDA(dev, cudaMemsetAsync(m->step_dev, 0, 4, dev->stream));
+  for (int s = 0; s < steps; ++s) {
+    FB_CUDA(dev, cudaGraphLaunch(m->graph_exec, dev->stream));
+    dev->launches += m->graph_kernels;
+  }
+  m->pos += steps;
+  // hist is [batch, hist_cap]; gather the first `steps` columns
+  std::vector<uint32_t> tmp((size_t)batch * m->hist_cap);
+  FB_CUDA(dev, cudaMemcpyAsync(tmp.data(), m->hist, tmp.size() * 4, cudaMemcpyDeviceToHost, dev->stream));
+  FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  for (int b = 0; b < batch; ++b)
+    std::memcpy(out_host + (size_t)b * steps, tmp.data() + (size_t)b * m->hist_cap, (size_t)steps * 4);
+  return FB200_OK;
+}
+
+int fb200_llama_logits_dev(const fb200_llama* m, const float** logits_dev) {
+  if (!m || !logits_dev) return FB200_ERR_INVALID_ARGUMENT;
+  *logits_dev = m->logits;
+  return FB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,56 @@
+"""Builds the same random-weight Llama model on the GPU (kalosm_b200) and in the oracle."""
+import numpy as np
+
+import kalosm_b200 as kb
+from oracle import oracle as O
+
+
+def tiny_cfg():
+    return dict(n_layer=2, hidden=256, ffn=512, n_head=4, n_kv_head=2, head_dim=64, vocab=1024, ctx=64)
+
+
+def llama3_8b_cfg(ctx=1024):
+    return dict(n_layer=32, hidden=4096, ffn=14336, n_head=32, n_kv_head=8, head_dim=128,
+                vocab=128256, ctx=ctx)
+
+
+def tensor_plan(cfg):
+    """(name, which_layer, ggml type, [N, K]) in Q4_K_M style: Q4_K body, Q6_K for attn_v,
+    ffn_down and the output head (BASELINE configs[3])."""
+    e, f = cfg["hidden"], cfg["ffn"]
+    qd, kvd = cfg["n_head"] * cfg["head_dim"], cfg["n_kv_head"] * cfg["head_dim"]
+    plan = [("token_embd", -1, O.Q4K, (cfg["vocab"], e)), ("output", -1, O.Q6K, (cfg["vocab"], e))]
+    for i in range(cfg["n_layer"]):
+        plan += [("attn_q", i, O.Q4K, (qd, e)), ("attn_k", i, O.Q4K, (kvd, e)),
+                 ("attn_v", i, O.Q6K, (kvd, e)), ("attn_output", i, O.Q4K, (e, qd)),
+                 ("ffn_gate", i, O.Q4K, (f, e)), ("ffn_up", i, O.Q4K, (f, e)),
+                 ("ffn_down", i, O.Q6K, (e, f))]
+    return plan
+
+
+ORACLE_NAMES = {"token_embd": "token_embd", "output": "output", "attn_q": "wq", "attn_k": "wk",
+                "attn_v": "wv", "attn_output": "wo", "ffn_gate": "gate", "ffn_up": "up",
+                "ffn_down": "down"}
+
+
+def build_models(dev, cfg, batch=1, seed=0, want_cpu=True, sigma=0.02):
+    gpu = kb.Llama(dev, n_layer=cfg["n_layer"], hidden=cfg["hidden"], ffn=cfg["ffn"],
+                   n_head=cfg["n_head"], n_kv_head=cfg["n_kv_head"], head_dim=cfg["head_dim"],
+                   vocab=cfg["vocab"], max_seq_len=cfg["ctx"], max_batch=batch)
+    cpu = None
+    if want_cpu:
+        cpu = O.Llama(cfg["n_layer"], cfg["hidden"], cfg["ffn"], cfg["n_head"], cfg["n_kv_head"],
+                      cfg["head_dim"], cfg["vocab"], cfg["ctx"], batch=batch, kv_f16=True)
+    for j, (name, layer, ty, (n, k)) in enumerate(tensor_plan(cfg)):
+        raw = O.random_qweights(seed * 100003 + j, sigma, n * k, ty)
+        gpu.set_tensor(name, layer, ty, (n, k), raw)
+        if cpu:
+            cpu.set_qmatrix(ORACLE_NAMES[name], layer, ty, n, k, raw)
+    rng = np.random.default_rng(seed + 77)
+    for i in range(cfg["n_layer"] + 1):
+        for nm in (("attn_norm", "ffn_norm") if i < cfg["n_layer"] else ("output_norm",)):
+            w = (1.0 + 0.02 * rng.standard_normal(cfg["hidden"])).astype(np.float32)
+            gpu.set_tensor(nm, i if i < cfg["n_layer"] else -1, kb.F32, (cfg["hidden"],), w)
+            if cpu:
+                cpu.set_norm(nm, i if i < cfg["n_layer"] else -1, w)
+    return gpu, cpu

@@ -1,0 +1,169 @@
+"""GPU parity of the elementwise ops, the KV cache and attention against the oracle."""
+import numpy as np
+import pytest
+
+import fixtures as F
+import kalosm_b200 as kb
+from gpu_util import dev, weights  # noqa: F401
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def test_rms_norm(dev):
+    rng = np.random.default_rng(1)
+    for rows, n in [(1, 4096), (5, 64), (3, 8192), (2, 100)]:
+        x = rng.standard_normal((rows, n)).astype(np.float32)
+        r = rng.standard_normal((rows, n)).astype(np.float32)
+        w = (1 + 0.02 * rng.standard_normal(n)).astype(np.float32)
+        b = rng.standard_normal(n).astype(np.float32)
+        y = dev.rms_norm(dev.tensor(x), dev.tensor(w), 1e-5).as_slice()
+        assert np.allclose(y, O.rms_norm(x, w, 1e-5), rtol=1e-5, atol=1e-6)
+        y = dev.rms_norm(dev.tensor(x), dev.tensor(w), 1e-5, residual=dev.tensor(r),
+                         bias=dev.tensor(b)).as_slice()
+        assert np.allclose(y, O.rms_norm(x, w, 1e-5, residual=r, bias=b), rtol=1e-5, atol=1e-5)
+
+
+def test_silu_mul(dev):
+    rng = np.random.default_rng(2)
+    g = (4 * rng.standard_normal(10000)).astype(np.float32)
+    u = rng.standard_normal(10000).astype(np.float32)
+    y = dev.silu_mul(dev.tensor(g), dev.tensor(u)).as_slice()
+    assert np.allclose(y, O.silu_mul(g, u), rtol=1e-5, atol=1e-6)
+
+
+def test_rope_tables_and_apply(dev):
+    # table literals of models/kalosm-llama/src/raw/rope.rs:279-329
+    rc = kb.RopeCache(dev, 2, 6, 5000.0)
+    cos, sin = rc.cos.as_slice(), rc.sin.as_slice()
+    assert np.abs(cos[:, 0] - [1.0, 0.5403, -0.4161, -0.99, -0.6536, 0.2837]).sum() < 1e-2
+    assert np.abs(sin[:, 0] - [0.0, 0.8415, 0.9093, 0.1411, -0.7568, -0.9589]).sum() < 1e-2
+    rng = np.random.default_rng(3)
+    for scaling in (None, (8.0, 1.0, 4.0, 8192)):
+        rc = kb.RopeCache(dev, 128, 64, 500000.0, scaling)
+        ocos, osin = O.rope_tables(128, 64, 500000.0, scaling)
+        assert np.allclose(rc.cos.as_slice(), ocos, atol=1e-6)
+        assert np.allclose(rc.sin.as_slice(), osin, atol=1e-6)
+        q = rng.standard_normal((2, 8, 5, 128)).astype(np.float32)
+        k = rng.standard_normal((2, 2, 5, 128)).astype(np.float32)
+        for inter in (True, False):
+            qt, kt = dev.tensor(q), dev.tensor(k)
+            rc.forward(qt, kt, start_pos=7, interleaved=inter)
+            # tolerance 1e-4 as the reference's RoPE conformance cases (suite/native/rope_ops.rs:170-229)
+            assert np.allclose(qt.as_slice(), O.rope(q, ocos, osin, 7, inter), atol=1e-4)
+            assert np.allclose(kt.as_slice(), O.rope(k, ocos, osin, 7, inter), atol=1e-4)
+
+
+def test_argmax_tie_rule(dev):
+    # fusor-ml/fusor/src/lib.rs:432-443: ties -> higher id; non-finite skipped
+    logits = np.zeros((3, 5000), dtype=np.float32)
+    logits[0, [17, 4000, 4999]] = 3.0
+    logits[1, 10] = np.inf
+    logits[1, 11] = np.nan
+    logits[1, 123] = 1.0
+    logits[2] = -1.0
+    logits[2, 0] = -0.5
+    ids, vals = dev.argmax(dev.tensor(logits))
+    ids, vals = ids.as_slice(), vals.as_slice()
+    for r in range(3):
+        oid, oval = O.top_k(logits[r], 1)
+        assert ids[r] == oid[0] and vals[r] == oval[0]
+    assert ids.tolist() == [4999, 123, 0]
+    rng = np.random.default_rng(4)
+    big = rng.standard_normal((4, 128256)).astype(np.float32)
+    ids, _ = dev.argmax(dev.tensor(big))
+    assert ids.as_slice().tolist() == big.argmax(axis=1).tolist()
+
+
+def test_embedding_lookup(dev):
+    for ty in (O.Q4K, O.Q6K, O.Q8_0, O.Q4_0):
+        n, k = 100, 512
+        raw = weights(ty, n, k, ty)
+        w = kb.QMatrix.from_raw_bytes(dev, (n, k), raw, ty)
+        ids = np.array([[0, 99, 17], [5, 5, 64]], dtype=np.uint32)
+        out = w.embedding(dev.tensor(ids)).as_slice()
+        table = O.dequantize(raw, ty, n * k).reshape(n, k)
+        assert np.array_equal(out.view(np.uint32), table[ids].view(np.uint32))
+
+
+def test_kv_cache_capacity_and_append(dev):
+    # capacity literals of fusor-ml/fusor/src/cache/tensor_cache.rs:319-333
+    rng = np.random.default_rng(5)
+    c = kb.KvCache(dev, 2, 2, 64, 4096)
+    k1 = rng.standard_normal((2, 2, 65, 64)).astype(np.float32)
+    v1 = rng.standard_normal((2, 2, 65, 64)).astype(np.float32)
+    kt, vt, n = c.append(dev.tensor(k1), dev.tensor(v1))
+    assert n == 65 and c.capacity == 256
+    k2 = rng.standard_normal((2, 2, 192, 64)).astype(np.float32)
+    v2 = rng.standard_normal((2, 2, 192, 64)).astype(np.float32)
+    kt, vt, n = c.append(dev.tensor(k2), dev.tensor(v2))
+    assert n == 257 and c.capacity == 512
+    full_k = np.concatenate([k1, k2], axis=2).astype(np.float16)
+    assert np.array_equal(kt.as_slice()[:, :, :257], full_k)
+    assert np.array_equal(vt.as_slice()[:, :, :257], np.concatenate([v1, v2], axis=2).astype(np.float16))
+    small = kb.KvCache(dev, 1, 1, 64, 96)
+    small.append(dev.tensor(k1[:1, :1]), dev.tensor(v1[:1, :1]))
+    assert small.capacity == 96
+    with pytest.raises(kb.FusorError) as e:
+        small.append(dev.tensor(k1[:1, :1]), dev.tensor(v1[:1, :1]))
+    assert e.value.code == kb.ERR_CAPACITY
+    c.reset()
+    assert c.current_seq_len == 0
+
+
+def _attn_case(dev, b, h, hkv, sq, skv, d, causal, seed, tol, repeat=1):
+    rng = np.random.default_rng(seed)
+    q = rng.standard_normal((b, h, sq, d)).astype(np.float32)
+    k = rng.standard_normal((b, hkv, skv, d)).astype(np.float16)
+    v = rng.standard_normal((b, hkv, skv, d)).astype(np.float16)
+    scale = float(1.0 / np.sqrt(d))
+    exp = O.attention(q, k.astype(np.float32), v.astype(np.float32), scale, causal=causal)
+    qt, kt, vt = dev.tensor(q), dev.tensor(k), dev.tensor(v)
+    first = None
+    for _ in range(repeat):
+        out = dev.flash_attention(qt, kt, vt, scale, mask_kind=kb.MASK_CAUSAL if causal else kb.MASK_NONE).as_slice()
+        err = np.max(np.abs(out - exp))
+        assert err < tol, (b, h, hkv, sq, skv, err)
+        assert F.rel_l2(out, exp) < 2e-3
+        if first is None:
+            first = out
+        assert np.array_equal(first, out)
+
+
+@pytest.mark.parametrize("kv", [129, 192, 256, 257, 384, 511, 512, 569, 1025])
+@pytest.mark.parametrize("heads", [(16, 2), (32, 8)])
+def test_decode_attention_tile_boundaries(dev, kv, heads):
+    # conformance/src/suite/native/flash_attention_ops.rs:305-348: decode at tile-boundary KV
+    # lengths, head_dim 128, each repeated 4x; tolerance 1e-3 (5e-3 beyond 1024 keys)
+    h, hkv = heads
+    _attn_case(dev, 1, h, hkv, 1, kv, 128, False, kv, 5e-3 if kv > 1024 else 1e-3, repeat=4)
+
+
+@pytest.mark.parametrize("shape", [(1, 4, 4, 7, 7, 64, True), (2, 8, 2, 33, 33, 128, True),
+                                   (1, 32, 8, 128, 128, 128, True), (2, 8, 8, 5, 40, 64, False),
+                                   (1, 32, 8, 4, 300, 128, True), (8, 32, 8, 1, 1024, 128, False)])
+def test_attention_prefill_and_gqa(dev, shape):
+    b, h, hkv, sq, skv, d, causal = shape
+    _attn_case(dev, b, h, hkv, sq, skv, d, causal, 7, 1e-3)
+
+
+def test_attention_masks_and_cache_capacity(dev):
+    rng = np.random.default_rng(8)
+    b, h, hkv, sq, skv, d, cap = 2, 4, 2, 6, 10, 64, 32
+    q = rng.standard_normal((b, h, sq, d)).astype(np.float32)
+    k = np.zeros((b, hkv, cap, d), np.float16)
+    v = np.zeros((b, hkv, cap, d), np.float16)
+    k[:, :, :skv] = rng.standard_normal((b, hkv, skv, d))
+    v[:, :, :skv] = rng.standard_normal((b, hkv, skv, d))
+    k[:, :, skv:] = 100.0  # rows beyond skv must never be read
+    scale = 0.125
+    kf, vf = k[:, :, :skv].astype(np.float32), v[:, :, :skv].astype(np.float32)
+    qk = (rng.standard_normal((sq, skv)) * 2).astype(np.float32)
+    out = dev.flash_attention(dev.tensor(q), dev.tensor(k), dev.tensor(v), scale, skv=skv,
+                              mask=dev.tensor(qk), mask_kind=kb.MASK_QK).as_slice()
+    assert np.max(np.abs(out - O.attention(q, kf, vf, scale, mask=qk, mask_kind=0))) < 1e-3
+    bk = np.where(rng.random((b, skv)) < 0.3, -np.inf, 0.0).astype(np.float32)
+    bk[:, 0] = 0.0
+    out = dev.flash_attention(dev.tensor(q), dev.tensor(k), dev.tensor(v), scale, skv=skv,
+                              mask=dev.tensor(bk), mask_kind=kb.MASK_BATCH_KEY).as_slice()
+    assert np.max(np.abs(out - O.attention(q, kf, vf, scale, mask=bk, mask_kind=1))) < 1e-3

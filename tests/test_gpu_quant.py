@@ -1,0 +1,192 @@
+"""GPU parity: dequantisation (bit-exact) and q_mat_mul (<= 2e-3 relative L2) against the oracle.
+
+Every test calls the CUDA path through the C ABI (kalosm_b200 is a ctypes binding) on the same
+bytes the oracle sees. Tolerance for products: 2e-3 relative L2 of the fp32 oracle.
+"""
+import numpy as np
+import pytest
+
+import fixtures as F
+import kalosm_b200 as kb
+from gpu_util import TYPES, activations, dev, weights  # noqa: F401
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+def _b(*parts):
+    return np.frombuffer(b"".join(parts), dtype=np.uint8)
+
+
+X32 = np.arange(1, 33, dtype=np.float32)[None, :]
+
+
+def test_known_answers(dev):
+    # fusor-ml/core/src/quantized/matmul/tests.rs:1305-1423
+    cases = [
+        (O.Q4_0, _b(F.f16_bytes(1.0), bytes([0x99]) * 16, F.f16_bytes(1.0), bytes([0x77]) * 16)),
+        (O.Q5_0, _b(F.f16_bytes(1.0), bytes([0xFF] * 4), bytes([0x11]) * 16,
+                    F.f16_bytes(1.0), bytes(4), bytes([0xFF]) * 16)),
+        (O.Q8_0, _b(F.f16_bytes(1.0), bytes([1]) * 32, F.f16_bytes(1.0), bytes([0xFF]) * 32)),
+    ]
+    for ty, raw in cases:
+        w = kb.QMatrix.from_raw_bytes(dev, (2, 32), raw, ty)
+        y = dev.tensor(X32).q_mat_mul(w).as_slice()
+        assert y.shape == (1, 2)
+        assert abs(y[0, 0] - 528.0) < 1e-3 and abs(y[0, 1] + 528.0) < 1e-3, (ty, y)
+    raw = _b(F.f16_bytes(1.0), F.f16_bytes(0.0), bytes([1, 1, 1, 1, 0, 0, 0, 0, 1, 1, 1, 1]),
+             bytes(32), bytes([0x11]) * 128)
+    w = kb.QMatrix.from_raw_bytes(dev, (1, 256), raw, O.Q5K)
+    y = dev.tensor(np.arange(1, 257, dtype=np.float32)[None, :]).q_mat_mul(w).as_slice()
+    assert abs(y[0, 0] - 32896.0) < 1e-2
+
+
+@pytest.mark.parametrize("case", F.CONFORMANCE_CASES, ids=lambda c: c[0])
+def test_conformance_fixtures(dev, case):
+    # dequantize: bit-exact with the oracle; q_mat_mul: the case's absolute tolerance and 2e-3 rel-L2
+    name, ty, (n, k), rows, tol, seed = case
+    raw = F.GEN[ty]((n, k))
+    w = kb.QMatrix.from_raw_bytes(dev, (n, k), raw, ty)
+    assert w.shape == (n, k) and w.ggml_type == ty and w.nbytes == raw.size
+    deq = w.dequantize().as_slice()
+    ref = O.dequantize(raw, ty, n * k).reshape(n, k)
+    assert np.array_equal(deq.view(np.uint32), ref.view(np.uint32)), name
+    x = F.uniform_input(rows, k, seed)
+    y = dev.tensor(x).q_mat_mul(w).as_slice()
+    exp = O.q_mat_mul(x, raw, ty, n, k)
+    assert np.max(np.abs(y - exp)) < tol
+    assert F.rel_l2(y, exp) < TOL, (name, F.rel_l2(y, exp))
+
+
+@pytest.mark.parametrize("tname", list(TYPES))
+@pytest.mark.parametrize("shape", [(48, 512), (16, 256), (33, 1024), (4096, 4096)])
+def test_dequantize_bit_exact_random(dev, tname, shape):
+    ty = TYPES[tname]
+    n, k = shape
+    raw = weights(11 + n, n, k, ty)
+    w = kb.QMatrix.from_raw_bytes(dev, (n, k), raw, ty)
+    deq = w.dequantize().as_slice()
+    ref = O.dequantize(raw, ty, n * k).reshape(n, k)
+    assert np.array_equal(deq.view(np.uint32), ref.view(np.uint32))
+
+
+@pytest.mark.parametrize("tname", list(TYPES))
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 9, 16, 17, 32, 33, 70])
+def test_q_mat_mul_batches(dev, tname, m):
+    ty = TYPES[tname]
+    n, k = 272, 1024
+    raw = weights(5, n, k, ty)
+    w = kb.QMatrix.from_raw_bytes(dev, (n, k), raw, ty)
+    x = activations(m, m, k)
+    y = dev.tensor(x).q_mat_mul(w).as_slice()
+    exp = O.q_mat_mul(x, raw, ty, n, k)
+    assert y.shape == (m, n)
+    assert F.rel_l2(y, exp) < TOL, F.rel_l2(y, exp)
+    # rows are independent: row i of a batch equals the M = 1 product of row i (bitwise)
+    y0 = dev.tensor(x[:1]).q_mat_mul(w).as_slice()
+    assert np.array_equal(y0[0], y[0])
+
+
+@pytest.mark.parametrize("tname,n,k", [("q4_0", 4096, 4096), ("q4k", 4096, 4096), ("q4k", 1024, 4096),
+                                        ("q4k", 14336, 4096), ("q4k", 4096, 14336), ("q8_0", 4096, 4096),
+                                        ("q6k", 1024, 4096), ("q6k", 4096, 14336)])
+def test_q_mat_mul_llama_shapes(dev, tname, n, k):
+    ty = TYPES[tname]
+    raw = weights(n + k, n, k, ty)
+    w = kb.QMatrix.from_raw_bytes(dev, (n, k), raw, ty)
+    for m in (1, 8):
+        x = activations(m + 3, m, k)
+        y = dev.tensor(x).q_mat_mul(w).as_slice()
+        cols = np.random.default_rng(1).choice(n, 256, replace=False)
+        # oracle on a sample of the output columns keeps the CPU time bounded
+        bs, bb = O.BLOCK[ty]
+        row_bytes = k // bs * bb
+        sub = np.concatenate([raw[c * row_bytes:(c + 1) * row_bytes] for c in cols])
+        exp = O.q_mat_mul(x, sub, ty, len(cols), k)
+        assert F.rel_l2(y[:, cols], exp) < TOL, (tname, n, k, m, F.rel_l2(y[:, cols], exp))
+
+
+def test_repeatable_bitwise(dev):
+    # fixed reduction order, no float atomics: repeated launches agree bit for bit
+    ty, n, k = O.Q4K, 1024, 2048
+    raw = weights(3, n, k, ty)
+    w = kb.QMatrix.from_raw_bytes(dev, (n, k), raw, ty)
+    x = dev.tensor(activations(9, 4, k))
+    first = x.q_mat_mul(w).as_slice()
+    for _ in range(4):
+        assert np.array_equal(first, x.q_mat_mul(w).as_slice())
+
+
+def test_linearity_property(dev):
+    # size-independent property: W(ax + by) ~ a Wx + b Wy
+    ty, n, k = O.Q6K, 512, 4096
+    w = kb.QMatrix.from_raw_bytes(dev, (n, k), weights(21, n, k, ty), ty)
+    x, z = activations(1, 1, k), activations(2, 1, k)
+    lhs = dev.tensor(2.0 * x - 0.5 * z).q_mat_mul(w).as_slice()
+    rhs = 2.0 * dev.tensor(x).q_mat_mul(w).as_slice() - 0.5 * dev.tensor(z).q_mat_mul(w).as_slice()
+    assert F.rel_l2(lhs, rhs) < TOL
+
+
+def test_activation_range(dev):
+    # activations far outside the fp16 range still work (per-row power-of-two scaling)
+    ty, n, k = O.Q4K, 64, 512
+    raw = weights(8, n, k, ty)
+    w = kb.QMatrix.from_raw_bytes(dev, (n, k), raw, ty)
+    for mag in (1e-9, 1e9):
+        x = activations(4, 2, k) * np.float32(mag)
+        y = dev.tensor(x).q_mat_mul(w).as_slice()
+        assert F.rel_l2(y, O.q_mat_mul(x, raw, ty, n, k)) < TOL
+
+
+def test_epilogues(dev):
+    ty, f, k = O.Q4K, 96, 512
+    g_raw, u_raw = weights(1, f, k, ty), weights(2, f, k, ty)
+    gate = kb.QMatrix.from_raw_bytes(dev, (f, k), g_raw, ty)
+    up = kb.QMatrix.from_raw_bytes(dev, (f, k), u_raw, ty)
+    gu = kb.QMatrix.concat_rows([gate, up])
+    assert gu is not None and gu.shape == (2 * f, k)
+    for m in (1, 6, 20):
+        x = activations(m, m, k)
+        h = dev.tensor(x).q_mat_mul(gu, epilogue=kb.EPI_SWIGLU).as_slice()
+        exp = O.silu_mul(O.q_mat_mul(x, g_raw, ty, f, k), O.q_mat_mul(x, u_raw, ty, f, k))
+        assert h.shape == (m, f) and F.rel_l2(h, exp) < TOL
+        # concatenated matrix without epilogue = both products side by side
+        both = dev.tensor(x).q_mat_mul(gu).as_slice()
+        assert F.rel_l2(both[:, :f], O.q_mat_mul(x, g_raw, ty, f, k)) < TOL
+        r1, r2 = activations(50 + m, m, f), activations(60 + m, m, f)
+        y = dev.tensor(x).q_mat_mul(gate, epilogue=kb.EPI_RESIDUAL, r1=dev.tensor(r1),
+                                    r2=dev.tensor(r2)).as_slice()
+        assert F.rel_l2(y, (O.q_mat_mul(x, g_raw, ty, f, k) + r1) + r2) < TOL
+    # mismatched parts: None, as QMatrix::concat_rows does
+    other = kb.QMatrix.from_raw_bytes(dev, (f, k), weights(3, f, k, O.Q6K), O.Q6K)
+    assert kb.QMatrix.concat_rows([gate, other]) is None
+
+
+def test_host_buffer_entry_point(dev):
+    ty, n, k = O.Q8_0, 128, 256
+    raw = weights(4, n, k, ty)
+    w = kb.QMatrix.from_raw_bytes(dev, (n, k), raw, ty)
+    x = activations(2, 3, k)
+    assert F.rel_l2(w.q_mat_mul_host(x), O.q_mat_mul(x, raw, ty, n, k)) < TOL
+
+
+def test_error_paths(dev):
+    with pytest.raises(kb.FusorError) as e:  # K not a multiple of the block size
+        kb.QMatrix.from_raw_bytes(dev, (2, 48), np.zeros(54, np.uint8), O.Q4_0)
+    assert e.value.code == kb.ERR_INVALID_SHAPE
+    with pytest.raises(kb.FusorError) as e:  # unknown ggml type
+        kb.QMatrix.from_raw_bytes(dev, (2, 32), np.zeros(36, np.uint8), 99)
+    assert e.value.code == kb.ERR_UNSUPPORTED_DTYPE
+    with pytest.raises(kb.FusorError) as e:  # wrong byte count
+        kb.QMatrix.from_raw_bytes(dev, (2, 32), np.zeros(35, np.uint8), O.Q4_0)
+    assert e.value.code == kb.ERR_INVALID_SHAPE
+    w = kb.QMatrix.from_raw_bytes(dev, (2, 32), np.zeros(36, np.uint8), O.Q4_0)
+    with pytest.raises(kb.FusorError):  # inner dimensions differ
+        dev.tensor(np.zeros((1, 64), np.float32)).q_mat_mul(w)
+    # empty and dense inputs
+    dense = kb.QMatrix.from_raw_bytes(dev, (2, 4), np.arange(8, dtype=np.float32), kb.F32)
+    y = dev.tensor(np.ones((1, 4), np.float32)).q_mat_mul(dense).as_slice()
+    assert np.allclose(y, [[6.0, 22.0]])
+    h16 = kb.QMatrix.from_raw_bytes(dev, (2, 4), np.arange(8, dtype=np.float16), kb.F16)
+    assert np.allclose(h16.dequantize().as_slice(), np.arange(8).reshape(2, 4))
