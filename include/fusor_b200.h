@@ -121,6 +121,16 @@ typedef struct fb200_epilogue {
 
 FB200_API int fb200_q_mat_mul(fb200_device* dev, const float* x_dev, size_t m, const fb200_qmatrix* w,
                     float* y_dev, const fb200_epilogue* epilogue);
+/* RMSNorm feeding a projection, as one call: y = epilogue(W . rms_norm(x (+ residual))).
+ * The reference authors this as rms_norm_fused / rms_norm_residual_fused followed by q_mat_mul
+ * (models/kalosm-llama/src/raw/mod.rs:964,1017 then attention_layer.rs:364-404, 220-235) and
+ * its resolver fuses what it can (fusor-ml/core/src/composite/rms_norm_fused.rs:10-54). For
+ * one activation row the norm runs in the prologue of the product kernel; other shapes
+ * normalise into scratch first. norm_weight_dev is [K]; residual_dev [M, K] or NULL. */
+FB200_API int fb200_rms_norm_q_mat_mul(fb200_device* dev, const float* x_dev,
+                                       const float* residual_dev, const float* norm_weight_dev,
+                                       float eps, size_t m, const fb200_qmatrix* w, float* y_dev,
+                                       const fb200_epilogue* epilogue);
 /* Same product with host buffers: uploads x, runs, downloads y, synchronises. */
 FB200_API int fb200_q_mat_mul_host(fb200_device* dev, const float* x_host, size_t m,
                          const fb200_qmatrix* w, float* y_host);

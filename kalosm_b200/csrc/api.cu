@@ -1,5 +1,6 @@
 // C ABI: device handles, tensors, QMatrix and q_mat_mul.
 #include <cstdarg>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -9,6 +10,11 @@ int fb200_qgemv_chunk(fb200_device* dev, const fb200_qmatrix* w, const float* x,
                       int epi, const float* r1, const float* r2, void* scratch);
 int fb200_dense_matmul(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_t m, float* y);
 int fb200_qgemm(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_t m, float* y);
+bool fb200_qgemv1_fits(const fb200_qmatrix* w);
+int fb200_qgemv1(fb200_device* dev, const fb200_qmatrix* w, const float* x, const float* xres,
+                 const float* norm_w, float eps, float* y, int epi, const float* r1, const float* r2);
+int fb200_launch_rms_norm(fb200_device* dev, const float* x, const float* res, const float* w,
+                          const float* b, float eps, size_t rows, size_t n, float* y);
 
 static thread_local std::string g_global_err;
 
@@ -69,6 +75,7 @@ int fb200_device_create(int ordinal, void* stream, fb200_device** out) {
     d->own_stream = true;
   }
   cudaDeviceGetAttribute(&d->sm_count, cudaDevAttrMultiProcessorCount, ordinal);
+  if (const char* e = getenv("FB200_PDL")) d->pdl = e[0] != '0';
   if ((e = cudaMalloc(&d->status, sizeof(int))) != cudaSuccess ||
       (e = cudaMemsetAsync(d->status, 0, sizeof(int), d->stream)) != cudaSuccess) {
     delete d;
@@ -84,6 +91,7 @@ int fb200_device_destroy(fb200_device* dev) {
   cudaStreamSynchronize(dev->stream);
   if (dev->xpack) cudaFree(dev->xpack);
   if (dev->stage) cudaFree(dev->stage);
+  if (dev->normed) cudaFree(dev->normed);
   if (dev->status) cudaFree(dev->status);
   if (dev->own_stream) cudaStreamDestroy(dev->stream);
   delete dev;
@@ -327,6 +335,9 @@ int fb200_q_mat_mul(fb200_device* dev, const float* x_dev, size_t m, const fb200
   }
   if (epi == FB200_EPI_SWIGLU && (w->ntiles % 2 != 0 || w->n % 32 != 0))
     return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "q_mat_mul: SwiGLU needs N = 2F with F a multiple of 16");
+  if (m == 1 && fb200_qgemv1_fits(w))
+    return fb200_qgemv1(dev, w, x_dev, nullptr, nullptr, 0.f, y_dev, epi, ep ? ep->r1_dev : nullptr,
+                        ep ? ep->r2_dev : nullptr);
   if (epi == FB200_EPI_NONE && m > 32) {
     rc = fb200_qgemm(dev, w, x_dev, m, y_dev);
     if (rc != 1) return rc;  // 1 = shape not covered by the tensor-core GEMM; fall through
@@ -345,6 +356,31 @@ int fb200_q_mat_mul(fb200_device* dev, const float* x_dev, size_t m, const fb200
     if (rc) return rc;
   }
   return FB200_OK;
+}
+
+int fb200_rms_norm_q_mat_mul(fb200_device* dev, const float* x_dev, const float* residual_dev,
+                             const float* norm_weight_dev, float eps, size_t m,
+                             const fb200_qmatrix* w, float* y_dev, const fb200_epilogue* ep) {
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  if (!w || !x_dev || !y_dev || !norm_weight_dev)
+    return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "rms_norm_q_mat_mul: null argument");
+  if (w->dev != dev)
+    return fb200_fail(dev, FB200_ERR_DEVICE_MISMATCH, "rms_norm_q_mat_mul: weight lives on another device handle");
+  const int epi = ep ? ep->kind : FB200_EPI_NONE;
+  if (m == 1 && w->tiled && fb200_qgemv1_fits(w) && epi >= 0 && epi <= 2 &&
+      !(epi == FB200_EPI_SWIGLU && (w->ntiles % 2 != 0 || w->n % 32 != 0)) &&
+      !(epi == FB200_EPI_RESIDUAL && !ep->r1_dev))
+    return fb200_qgemv1(dev, w, x_dev, residual_dev, norm_weight_dev, eps, y_dev, epi,
+                        ep ? ep->r1_dev : nullptr, ep ? ep->r2_dev : nullptr);
+  // general shapes: normalise into scratch, then the plain product
+  const size_t bytes = m * w->k * sizeof(float);
+  rc = fb200_ensure(dev, &dev->normed, &dev->normed_bytes, bytes);
+  if (rc) return rc;
+  rc = fb200_launch_rms_norm(dev, x_dev, residual_dev, norm_weight_dev, nullptr, eps, m, w->k,
+                             (float*)dev->normed);
+  if (rc) return rc;
+  return fb200_q_mat_mul(dev, (const float*)dev->normed, m, w, y_dev, ep);
 }
 
 int fb200_q_mat_mul_host(fb200_device* dev, const float* x_host, size_t m, const fb200_qmatrix* w,

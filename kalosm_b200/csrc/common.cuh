@@ -17,11 +17,15 @@ struct fb200_device {
   cudaStream_t stream = nullptr;
   bool own_stream = false;
   int sm_count = 148;
+  bool pdl = true;  // launch with programmatic stream serialization (FB200_PDL=0 turns it off)
   std::string err;
   uint64_t launches = 0;
   // scratch for packed activations (fp16 fragments, group sums, row scales); grown on demand
   void* xpack = nullptr;
   size_t xpack_bytes = 0;
+  // normalised activations of rms_norm_q_mat_mul when the fused kernel does not apply
+  void* normed = nullptr;
+  size_t normed_bytes = 0;
   // staging for the *_host entry points
   void* stage = nullptr;
   size_t stage_bytes = 0;

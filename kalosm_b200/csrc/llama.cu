@@ -200,10 +200,17 @@ int run_forward(fb200_llama* m, int batch, int seq) {
     return fb200_fail(dev, FB200_ERR_CAPACITY, "llama: attention scratch too small");
   for (int li = 0; li < c.n_layer; ++li) {
     LayerW& L = m->layers[li];
-    if ((rc = fb200_launch_rms_norm_strided(dev, m->x, E, nullptr, L.attn_norm, c.rms_eps, rows, E, m->xn))) return rc;
-    if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wq, m->q, nullptr))) return rc;
-    if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wk, m->k, nullptr))) return rc;
-    if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wv, m->v, nullptr))) return rc;
+    if (rows == 1) {
+      // one activation row: the norm runs in the prologue of each projection kernel
+      if ((rc = fb200_rms_norm_q_mat_mul(dev, m->x, nullptr, L.attn_norm, c.rms_eps, 1, L.wq, m->q, nullptr))) return rc;
+      if ((rc = fb200_rms_norm_q_mat_mul(dev, m->x, nullptr, L.attn_norm, c.rms_eps, 1, L.wk, m->k, nullptr))) return rc;
+      if ((rc = fb200_rms_norm_q_mat_mul(dev, m->x, nullptr, L.attn_norm, c.rms_eps, 1, L.wv, m->v, nullptr))) return rc;
+    } else {
+      if ((rc = fb200_launch_rms_norm_strided(dev, m->x, E, nullptr, L.attn_norm, c.rms_eps, rows, E, m->xn))) return rc;
+      if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wq, m->q, nullptr))) return rc;
+      if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wk, m->k, nullptr))) return rc;
+      if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wv, m->v, nullptr))) return rc;
+    }
     {
       const size_t total = rows * (size_t)(H + 2 * HK) * (D / 2);
       rope_append_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(
@@ -217,11 +224,15 @@ int run_forward(fb200_llama* m, int batch, int seq) {
                                      m->att_part, nsplit, 1))) return rc;
     if ((rc = fb200_q_mat_mul(dev, m->att, rows, L.wo, m->attn_out, nullptr))) return rc;
     // ffn_norm.forward_residual_f32(attn, residual) (raw/mod.rs:1017)
-    if ((rc = fb200_launch_rms_norm_strided(dev, m->attn_out, E, m->x, L.ffn_norm, c.rms_eps, rows, E, m->xn))) return rc;
-    if (L.gate_up) {
+    if (rows == 1 && L.gate_up) {
+      fb200_epilogue ep{FB200_EPI_SWIGLU, nullptr, nullptr};
+      if ((rc = fb200_rms_norm_q_mat_mul(dev, m->attn_out, m->x, L.ffn_norm, c.rms_eps, 1, L.gate_up, m->hbuf, &ep))) return rc;
+    } else if (L.gate_up) {
+      if ((rc = fb200_launch_rms_norm_strided(dev, m->attn_out, E, m->x, L.ffn_norm, c.rms_eps, rows, E, m->xn))) return rc;
       fb200_epilogue ep{FB200_EPI_SWIGLU, nullptr, nullptr};
       if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.gate_up, m->hbuf, &ep))) return rc;
     } else {
+      if ((rc = fb200_launch_rms_norm_strided(dev, m->attn_out, E, m->x, L.ffn_norm, c.rms_eps, rows, E, m->xn))) return rc;
       if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.gate, m->gbuf, nullptr))) return rc;
       if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.up, m->hbuf, nullptr))) return rc;
       if ((rc = fb200_silu_mul(dev, m->gbuf, m->hbuf, rows * (size_t)c.ffn, m->hbuf))) return rc;
@@ -232,10 +243,15 @@ int run_forward(fb200_llama* m, int batch, int seq) {
     if ((rc = fb200_q_mat_mul(dev, m->hbuf, rows, L.down, m->x, &ep))) return rc;
   }
   // final norm on the last position of every batch row, then the output projection
-  if ((rc = fb200_launch_rms_norm_strided(dev, m->x + (size_t)(seq - 1) * E, (size_t)seq * E, nullptr,
-                                          m->output_norm, c.rms_eps, batch, E, m->last))) return rc;
   fb200_qmatrix* ow = m->output ? m->output : m->token_embd;
-  if ((rc = fb200_q_mat_mul(dev, m->last, batch, ow, m->logits, nullptr))) return rc;
+  if (batch == 1) {
+    if ((rc = fb200_rms_norm_q_mat_mul(dev, m->x + (size_t)(seq - 1) * E, nullptr, m->output_norm,
+                                       c.rms_eps, 1, ow, m->logits, nullptr))) return rc;
+  } else {
+    if ((rc = fb200_launch_rms_norm_strided(dev, m->x + (size_t)(seq - 1) * E, (size_t)seq * E, nullptr,
+                                            m->output_norm, c.rms_eps, batch, E, m->last))) return rc;
+    if ((rc = fb200_q_mat_mul(dev, m->last, batch, ow, m->logits, nullptr))) return rc;
+  }
   if ((rc = fb200_launch_argmax(dev, m->logits, batch, c.vocab, m->next, nullptr))) return rc;
   return FB200_OK;
 }
