@@ -7,14 +7,13 @@
 // stages ahead of the math, so tens of KB per SM are in flight without holding registers. The
 // first copies are issued before griddepcontrol.wait: under programmatic dependent launch the
 // weights of this product stream in while the producer of the activations is still running.
-// Each lane then reads its mma.m16n8k16 A-fragment bytes from the stage with conflict-free
-// 128-bit shared loads (the tile-interleaved storage is already in fragment order), expands the
-// 4/6/8-bit quants to exact fp16 integers in registers with logic ops (no int->float
-// conversions), and lets the tensor cores form the integer-weight x activation dot products
-// in fp32. Block scales are applied to the fp32 partial sums per 16- or 32-element group, so
-// the only rounding beyond the reference's f32 path is that of the activations, which are
-// carried as a hi + lo pair of fp16 values (about 22 mantissa bits; two MMAs per fragment),
-// pre-scaled per row by a power of two so their range is never an issue.
+// Each lane reads the quant bytes of its MMA A fragments from the stage with 4-byte shared
+// loads (conflict free in the tile-interleaved storage) and keeps them in the byte domain: one
+// logic op turns four packed nibbles into four u8 operands of mma.sync.m16n8k32
+// (u8 x s8 -> s32, exact). Activations are packed once per call into signed 7-bit limbs
+// (x/scale = (l0 + l1/2^7 [+ l2/2^14 [+ l3/2^21]]) / 64: four limbs, 2^-27, for up to 8 rows;
+// three, 2^-20, for 9..16 rows; two, 2^-13, for 17..32 rows), pre-scaled per row by a power of two. Integer dot products
+// are exact; block scales are applied to them in fp32 per 16- or 32-element group.
 // The batch occupies the N = 8 columns of the MMA, which makes M <= 8 cost the same weight
 // traffic and nearly the same instruction count as M = 1.
 //
@@ -25,6 +24,237 @@
 
 namespace {
 
+constexpr int GEMV_WARPS = 8;
+constexpr int GEMV_THREADS = GEMV_WARPS * 32;
+
+struct GemvArgs {
+  const uint8_t* w;     // tiled weights
+  const uint8_t* xq;    // packed activation limbs [Kp/32][NL][Mp][32]
+  const float* xs16;    // [Kp/16][Mp] sums of the scaled activations (centres and offsets)
+  const float* xscale;  // [Mp] power-of-two output scales
+  float* y;             // [M, Nout]
+  const float* r1;
+  const float* r2;
+  int M, Mp;
+  int n_out;    // logical output columns (N, or N/2 for SwiGLU)
+  int ngroups;  // K groups per tile
+  int pair_tile_offset;  // SwiGLU: tile index distance between the gate and the up tile
+  int nunits;            // work units: tiles, or (gate, up) tile pairs
+  int* status;           // device status word (bounded waits that ran out are recorded here)
+};
+
+__device__ __forceinline__ uint32_t lds4(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
+__device__ __forceinline__ uint4 lds16(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+
+// Limb bytes of 32-element chunk kc for this lane: {elements 4t..4t+3, elements 16+4t..16+4t+3}
+// of batch row 8 nt + g, one uint2 per limb.
+template <int NT, int NL>
+__device__ __forceinline__ void load_b(const GemvArgs& a, int kc, int g, int t, uint2 (&b)[NT][NL]) {
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int m = 8 * nt + g;
+#pragma unroll
+    for (int l = 0; l < NL; ++l) {
+      b[nt][l] = make_uint2(0u, 0u);
+      if (m < a.M)
+        b[nt][l] = __ldg(reinterpret_cast<const uint2*>(a.xq + (((size_t)kc * NL + l) * a.Mp + m) * 32 + t * 8));
+    }
+  }
+}
+
+template <int NT, int NL>
+__device__ __forceinline__ void zero_c(int (&c)[NT][NL][4]) {
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int l = 0; l < NL; ++l)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) c[nt][l][i] = 0;
+}
+
+template <bool SIGNED_A, int NT, int NL>
+__device__ __forceinline__ void mma_all(int (&c)[NT][NL][4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                        uint32_t a3, const uint2 (&b)[NT][NL]) {
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int l = 0; l < NL; ++l) mma_i8_k32<SIGNED_A>(c[nt][l], a0, a1, a2, a3, b[nt][l].x, b[nt][l].y);
+}
+
+// Integer dot products -> fp32 in units of 2^-13 * (w . x/scale).
+template <int NL>
+__device__ __forceinline__ float limbs_f(const int (&c)[NL][4], int i) {
+  float f = (float)(c[0][i] * 128 + c[1][i]);
+  if (NL == 4) f = fmaf((float)(c[2][i] * 128 + c[3][i]), 1.0f / 16384.0f, f);
+  if (NL == 3) f = fmaf((float)c[2][i], 1.0f / 128.0f, f);
+  return f;
+}
+
+// acc += s * (f - centre * xs) - o * xs for the four accumulator slots of every n-tile;
+// xs = sum of the scaled activations over the scale group, per batch column.
+template <int NT, int NL>
+__device__ __forceinline__ void apply(float (&acc)[NT][4], const int (&c)[NT][NL][4], float s_g,
+                                      float s_g8, float o_g, float o_g8, float centre,
+                                      const float* xs_a, const float* xs_b, int t) {
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    float2 sx = make_float2(0.f, 0.f);
+    if (xs_a) {
+      sx = __ldg(reinterpret_cast<const float2*>(xs_a + 8 * nt + 2 * t));
+      if (xs_b) {
+        float2 s2 = __ldg(reinterpret_cast<const float2*>(xs_b + 8 * nt + 2 * t));
+        sx.x += s2.x; sx.y += s2.y;
+      }
+    }
+    acc[nt][0] = fmaf(s_g, limbs_f<NL>(c[nt], 0) - centre * sx.x, fmaf(-o_g, sx.x, acc[nt][0]));
+    acc[nt][1] = fmaf(s_g, limbs_f<NL>(c[nt], 1) - centre * sx.y, fmaf(-o_g, sx.y, acc[nt][1]));
+    acc[nt][2] = fmaf(s_g8, limbs_f<NL>(c[nt], 2) - centre * sx.x, fmaf(-o_g8, sx.x, acc[nt][2]));
+    acc[nt][3] = fmaf(s_g8, limbs_f<NL>(c[nt], 3) - centre * sx.y, fmaf(-o_g8, sx.y, acc[nt][3]));
+  }
+}
+
+// ---- per-format processing of one tile-group by one warp --------------------------------------
+// Standard MMA mapping: one m16n8k32 covers the 32 elements of one scale group (two 16-element
+// groups for Q6_K, done as m16n8k16), the 8 columns are batch rows.
+
+template <int NT, int NL>
+__device__ __forceinline__ void group_q4_0(const GemvArgs& a, const uint8_t* tg, int kg, int lane,
+                                           float (&acc)[NT][4]) {
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int blk = 0; blk < 4; ++blk) {
+    const uint32_t w0 = lds4(tg + g * 64 + blk * 16 + 4 * t);
+    const uint32_t w1 = lds4(tg + 512 + g * 64 + blk * 16 + 4 * t);
+    const int kc = kg * 4 + blk;
+    uint2 b[NT][NL];
+    load_b<NT, NL>(a, kc, g, t, b);
+    int c[NT][NL][4];
+    zero_c<NT, NL>(c);
+    mma_all<false, NT, NL>(c, w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, (w0 >> 4) & 0x0F0F0F0Fu,
+                           (w1 >> 4) & 0x0F0F0F0Fu, b);
+    const float d_g = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 1024 + (g * 4 + blk) * 2));
+    const float d_g8 = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 1024 + ((g + 8) * 4 + blk) * 2));
+    apply<NT, NL>(acc, c, d_g, d_g8, 0.f, 0.f, 8.0f, a.xs16 + (size_t)(2 * kc) * a.Mp,
+                  a.xs16 + (size_t)(2 * kc + 1) * a.Mp, t);
+  }
+}
+
+template <int NT, int NL>
+__device__ __forceinline__ void group_q8_0(const GemvArgs& a, const uint8_t* tg, int kg, int lane,
+                                           float (&acc)[NT][4]) {
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int blk = 0; blk < 4; ++blk) {
+    const int off = g * 64 + blk * 16 + 4 * t;
+    const uint32_t a0 = lds4(tg + off), a2 = lds4(tg + 512 + off);
+    const uint32_t a1 = lds4(tg + 1024 + off), a3 = lds4(tg + 1536 + off);
+    const int kc = kg * 4 + blk;
+    uint2 b[NT][NL];
+    load_b<NT, NL>(a, kc, g, t, b);
+    int c[NT][NL][4];
+    zero_c<NT, NL>(c);
+    mma_all<true, NT, NL>(c, a0, a1, a2, a3, b);
+    const float d_g = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 2048 + (g * 4 + blk) * 2));
+    const float d_g8 = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 2048 + ((g + 8) * 4 + blk) * 2));
+    apply<NT, NL>(acc, c, d_g, d_g8, 0.f, 0.f, 0.f, nullptr, nullptr, t);
+  }
+}
+
+// Q4_K: lane t of each quad decodes the 6-bit (scale, offset) of sub-blocks t and t + 4 for its
+// two rows; the quad shares them by shuffle.
+template <int NT, int NL>
+__device__ __forceinline__ void group_q4k(const GemvArgs& a, const uint8_t* tg, int kg, int lane,
+                                          float (&acc)[NT][4]) {
+  const int g = lane >> 2, t = lane & 3;
+  float sc_f[2][2], mn_f[2][2];  // [row half][sub-block t + 4 i]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint4 hd = lds16(tg + 2048 + (g + 8 * h) * 16);
+    const float d = fb::half_bits_to_float((uint16_t)(hd.x & 0xFFFF));
+    const float dmin = fb::half_bits_to_float((uint16_t)(hd.x >> 16));
+    const uint32_t s0 = hd.y, s1 = hd.z, s2 = hd.w;
+    const uint32_t scB = (s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u);
+    const uint32_t mnB = ((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u);
+    const int sh = 8 * t;
+    sc_f[h][0] = d * (float)((s0 >> sh) & 0x3F);
+    mn_f[h][0] = dmin * (float)((s1 >> sh) & 0x3F);
+    sc_f[h][1] = d * (float)((scB >> sh) & 0xFF);
+    mn_f[h][1] = dmin * (float)((mnB >> sh) & 0xFF);
+  }
+#pragma unroll
+  for (int pair = 0; pair < 4; ++pair) {
+    const int ch = pair >> 1, ps = pair & 1;
+    const int off = g * 32 + ps * 16 + 4 * t;
+    const uint32_t w00 = lds4(tg + ((ch * 2 + 0) * 2 + 0) * 256 + off);  // row g,   elements 4t..
+    const uint32_t w01 = lds4(tg + ((ch * 2 + 0) * 2 + 1) * 256 + off);  // row g,   elements 16+4t..
+    const uint32_t w10 = lds4(tg + ((ch * 2 + 1) * 2 + 0) * 256 + off);  // row g+8
+    const uint32_t w11 = lds4(tg + ((ch * 2 + 1) * 2 + 1) * 256 + off);
+#pragma unroll
+    for (int hi = 0; hi < 2; ++hi) {
+      const int sb = 2 * pair + hi;
+      const uint32_t mask = hi ? 0xF0F0F0F0u : 0x0F0F0F0Fu;
+      const int kc = kg * 8 + sb;
+      uint2 b[NT][NL];
+      load_b<NT, NL>(a, kc, g, t, b);
+      int c[NT][NL][4];
+      zero_c<NT, NL>(c);
+      mma_all<false, NT, NL>(c, w00 & mask, w10 & mask, w01 & mask, w11 & mask, b);
+      const int src = (lane & ~3) | (sb & 3);
+      float s_g = __shfl_sync(0xFFFFFFFFu, sc_f[0][sb >> 2], src);
+      float s_g8 = __shfl_sync(0xFFFFFFFFu, sc_f[1][sb >> 2], src);
+      const float o_g = __shfl_sync(0xFFFFFFFFu, mn_f[0][sb >> 2], src);
+      const float o_g8 = __shfl_sync(0xFFFFFFFFu, mn_f[1][sb >> 2], src);
+      if (hi) { s_g *= 0.0625f; s_g8 *= 0.0625f; }  // high nibbles were used in place as 16 q
+      apply<NT, NL>(acc, c, s_g, s_g8, o_g, o_g8, 0.f, a.xs16 + (size_t)(2 * kc) * a.Mp,
+                    a.xs16 + (size_t)(2 * kc + 1) * a.Mp, t);
+    }
+  }
+}
+
+// Q6_K: sixteen 16-element scale groups per super-block, one m16n8k16 per group and limb.
+template <int NT, int NL>
+__device__ __forceinline__ void group_q6k(const GemvArgs& a, const uint8_t* tg, int kg, int lane,
+                                          float (&acc)[NT][4]) {
+  const int g = lane >> 2, t = lane & 3;
+  const uint4 sc_g = lds16(tg + 3072 + g * 16);
+  const uint4 sc_g8 = lds16(tg + 3072 + (g + 8) * 16);
+  const float d_g = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 3328 + g * 2));
+  const float d_g8 = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 3328 + (g + 8) * 2));
+  const uint32_t scw_g[4] = {sc_g.x, sc_g.y, sc_g.z, sc_g.w};
+  const uint32_t scw_g8[4] = {sc_g8.x, sc_g8.y, sc_g8.z, sc_g8.w};
+#pragma unroll
+  for (int c2 = 0; c2 < 2; ++c2)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      // groups 8c + 2q + u, u = 0, 1, are the two halves of 32-element chunk 4c + q
+      const int kc = kg * 8 + c2 * 4 + q;
+      uint2 b[NT][NL];
+      load_b<NT, NL>(a, kc, g, t, b);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int cu = c2 * 2 + u, grp = 8 * c2 + 2 * q + u;
+        uint32_t af[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t wl = lds4(tg + (cu * 2 + h) * 256 + g * 32 + (q & 1) * 16 + 4 * t);
+          const uint32_t wh = lds4(tg + 2048 + (cu * 2 + h) * 128 + g * 16 + 4 * t);
+          const uint32_t hb = q == 0 ? (wh << 4) : q == 1 ? (wh << 2) : q == 2 ? wh : (wh >> 2);
+          af[h] = (((q >> 1) ? (wl >> 4) : wl) & 0x0F0F0F0Fu) | (hb & 0x30303030u);
+        }
+        int c[NT][NL][4];
+        zero_c<NT, NL>(c);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int l = 0; l < NL; ++l) mma_u8_k16(c[nt][l], af[0], af[1], u ? b[nt][l].y : b[nt][l].x);
+        const float s_g = d_g * (float)(int)(int8_t)((scw_g[grp >> 2] >> (8 * (grp & 3))) & 0xFF);
+        const float s_g8 = d_g8 * (float)(int)(int8_t)((scw_g8[grp >> 2] >> (8 * (grp & 3))) & 0xFF);
+        apply<NT, NL>(acc, c, s_g, s_g8, 0.f, 0.f, 32.0f, a.xs16 + (size_t)(kg * 16 + grp) * a.Mp,
+                      nullptr, t);
+      }
+    }
+}
+
 template <int TYPE>
 struct Ring {
   static constexpr int TG = TYPE == FB200_Q4_0 ? 1152 : TYPE == FB200_Q8_0 ? 2176 : TYPE == FB200_Q4_K ? 2304 : 3360;
@@ -33,6 +263,9 @@ struct Ring {
   static constexpr int RING_BYTES = GEMV_WARPS * STAGES * STRIDE;
   static constexpr int BAR_BYTES = GEMV_WARPS * STAGES * 8;
 };
+
+template <int NT>
+struct Limbs { static constexpr int N = NT == 1 ? 4 : NT == 2 ? 3 : 2; };
 
 template <int TYPE, int NT, int EPI>
 constexpr int gemv_smem_bytes() {
@@ -95,16 +328,20 @@ qgemv_kernel(const GemvArgs a) {
 #pragma unroll
     for (int p = 0; p < NP; ++p) {
       float acc[NT][4];
-      zero_c<NT>(acc);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
       for (int kk = 0; kk < gw; ++kk, ++item) {
         const int st = item % S;
         mbar_wait(my_bar + 8 * st, (uint32_t)((item / S) & 1), a.status);
         const uint8_t* tg = my_ring + st * R::STRIDE;
         const int kg = warp + GEMV_WARPS * kk;
-        if (TYPE == FB200_Q4_0) group_q4_0<NT>(a, tg, kg, lane, acc);
-        else if (TYPE == FB200_Q8_0) group_q8_0<NT>(a, tg, kg, lane, acc);
-        else if (TYPE == FB200_Q4_K) group_q4k<NT>(a, tg, kg, lane, acc);
-        else group_q6k<NT>(a, tg, kg, lane, acc);
+        constexpr int NL = Limbs<NT>::N;
+        if (TYPE == FB200_Q4_0) group_q4_0<NT, NL>(a, tg, kg, lane, acc);
+        else if (TYPE == FB200_Q8_0) group_q8_0<NT, NL>(a, tg, kg, lane, acc);
+        else if (TYPE == FB200_Q4_K) group_q4k<NT, NL>(a, tg, kg, lane, acc);
+        else group_q6k<NT, NL>(a, tg, kg, lane, acc);
         __syncwarp();  // every lane has consumed the stage before it is refilled
         if (lane == 0 && item + S < n_items) issue(item + S);
       }
@@ -146,14 +383,18 @@ qgemv_kernel(const GemvArgs a) {
   }
 }
 
-// x[M, K] f32 -> fp16 MMA B-fragments [Kp/16][Mp][4 lanes t][hi x0 x2 x1 x3 | lo x0 x2 x1 x3],
-// per-32 sums of the scaled values, and the power-of-two row scale.
+// x[M, K] f32 -> int8 limb planes [Kp/32][NL][Mp][32] (inside a 32-element chunk lane t's eight
+// bytes are elements 4t..4t+3 then 16+4t..16+4t+3), per-16 sums of the scaled values and the
+// power-of-two output scale of each row. One CTA per (padded) row.
+template <int NL>
 __global__ void __launch_bounds__(256)
-pack_x_kernel(const float* __restrict__ x, int M, int K, int Kp, int Mp, __half* __restrict__ xt,
-              float* __restrict__ xsum, float* __restrict__ xscale) {
+pack_x_kernel(const float* __restrict__ x, int M, int K, int Kp, int Mp, uint8_t* __restrict__ xq,
+              float* __restrict__ xs16, float* __restrict__ xscale) {
   const int m = blockIdx.x;
   __shared__ float wmax[8];
-  float inv = 1.0f;
+  pdl_launch_dependents();
+  pdl_wait();
+  float inv64 = 0.f;
   if (m < M) {
     float amax = 0.f;
     for (int k = threadIdx.x; k < K; k += 256) amax = fmaxf(amax, fabsf(x[(size_t)m * K + k]));
@@ -166,44 +407,41 @@ pack_x_kernel(const float* __restrict__ x, int M, int K, int Kp, int Mp, __half*
     for (int i = 1; i < 8; ++i) amax = fmaxf(amax, wmax[i]);
     int e = 0;
     if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &e);
-    inv = ldexpf(1.0f, -e);
-    if (threadIdx.x == 0) xscale[m] = ldexpf(1.0f, e);
+    inv64 = ldexpf(64.0f, -e);
+    if (threadIdx.x == 0) xscale[m] = ldexpf(1.0f, e - 13);
   } else if (threadIdx.x == 0) {
     xscale[m] = 1.0f;
   }
-  const int quads = Kp >> 2;
+  const int quads = Kp >> 2;  // a multiple of 32
   for (int q0 = 0; q0 < quads; q0 += 256) {
     const int q = q0 + threadIdx.x;
-    float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
     const int k = q * 4;
+    uint32_t lw[4] = {0u, 0u, 0u, 0u};
+    float sum = 0.f;
     if (q < quads && m < M) {
-      const float* xr = x + (size_t)m * K;
-      if (k + 3 < K) {
-        v0 = xr[k] * inv; v1 = xr[k + 1] * inv; v2 = xr[k + 2] * inv; v3 = xr[k + 3] * inv;
-      } else {
-        if (k < K) v0 = xr[k] * inv;
-        if (k + 1 < K) v1 = xr[k + 1] * inv;
-        if (k + 2 < K) v2 = xr[k + 2] * inv;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float v = (k + i < K) ? x[(size_t)m * K + k + i] * inv64 : 0.f;
+        sum += v;
+        float l0 = rintf(v), r = (v - l0) * 128.0f;
+        float l1 = rintf(r); r = (r - l1) * 128.0f;
+        float l2 = rintf(r); r = (r - l2) * 128.0f;
+        float l3 = rintf(r);
+        lw[0] |= ((uint32_t)(int)l0 & 0xFFu) << (8 * i);
+        lw[1] |= ((uint32_t)(int)l1 & 0xFFu) << (8 * i);
+        lw[2] |= ((uint32_t)(int)l2 & 0xFFu) << (8 * i);
+        lw[3] |= ((uint32_t)(int)l3 & 0xFFu) << (8 * i);
       }
     }
-    float s = (v0 + v1) + (v2 + v3);
-    s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
-    s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
-    s += __shfl_xor_sync(0xFFFFFFFFu, s, 4);
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
     if (q < quads) {
-      __half2 h01 = __floats2half2_rn(v0, v2);
-      __half2 h23 = __floats2half2_rn(v1, v3);
-      float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-      __half2 l01 = __floats2half2_rn(v0 - f01.x, v2 - f01.y);
-      __half2 l23 = __floats2half2_rn(v1 - f23.x, v3 - f23.y);
-      uint4 pk;
-      pk.x = *reinterpret_cast<uint32_t*>(&h01);
-      pk.y = *reinterpret_cast<uint32_t*>(&h23);
-      pk.z = *reinterpret_cast<uint32_t*>(&l01);
-      pk.w = *reinterpret_cast<uint32_t*>(&l23);
-      const int kk = k >> 4, p = k & 15;
-      *reinterpret_cast<uint4*>(xt + ((size_t)kk * Mp + m) * 32 + 2 * p) = pk;
-      if ((threadIdx.x & 7) == 0) xsum[(size_t)(k >> 5) * Mp + m] = s;
+      const int kc = k >> 5, e = k & 31;  // e is a multiple of 4
+      const int pos = e < 16 ? (e >> 2) * 8 : ((e - 16) >> 2) * 8 + 4;
+#pragma unroll
+      for (int l = 0; l < NL; ++l)
+        *reinterpret_cast<uint32_t*>(xq + (((size_t)kc * NL + l) * Mp + m) * 32 + pos) = lw[l];
+      if ((threadIdx.x & 3) == 0) xs16[(size_t)(k >> 4) * Mp + m] = sum * 128.0f;
     }
   }
 }
@@ -255,7 +493,7 @@ int launch_nt(fb200_device* dev, GemvArgs& a, int nt, int epi) {
 
 // Bytes of packed-activation scratch needed for an [M<=32, K] product.
 size_t fb200_xpack_bytes(int mp, uint64_t kp) {
-  return (size_t)(kp / 16) * mp * 32 * sizeof(__half) + (size_t)(kp / 32) * mp * sizeof(float) +
+  return (size_t)(kp / 32) * 4 * mp * 32 + (size_t)(kp / 16) * mp * sizeof(float) +
          (size_t)mp * sizeof(float) + 256;
 }
 
@@ -267,15 +505,18 @@ int fb200_qgemv_chunk(fb200_device* dev, const fb200_qmatrix* w, const float* x,
   const int nt = mc <= 8 ? 1 : mc <= 16 ? 2 : 4;
   const int mp = nt * 8;
   const uint64_t kp = (uint64_t)w->ngroups * geo.group_elems;
-  __half* xt = reinterpret_cast<__half*>(scratch);
-  size_t off = (size_t)(kp / 16) * mp * 32 * sizeof(__half);
-  float* xsum = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + off);
-  off += (size_t)(kp / 32) * mp * sizeof(float);
+  const int nl = nt == 1 ? 4 : nt == 2 ? 3 : 2;
+  uint8_t* xq = reinterpret_cast<uint8_t*>(scratch);
+  size_t off = (size_t)(kp / 32) * nl * mp * 32;
+  float* xs16 = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + off);
+  off += (size_t)(kp / 16) * mp * sizeof(float);
   float* xscale = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + off);
-  pack_x_kernel<<<mp, 256, 0, dev->stream>>>(x, mc, (int)w->k, (int)kp, mp, xt, xsum, xscale);
+  if (nl == 4) pack_x_kernel<4><<<mp, 256, 0, dev->stream>>>(x, mc, (int)w->k, (int)kp, mp, xq, xs16, xscale);
+  else if (nl == 3) pack_x_kernel<3><<<mp, 256, 0, dev->stream>>>(x, mc, (int)w->k, (int)kp, mp, xq, xs16, xscale);
+  else pack_x_kernel<2><<<mp, 256, 0, dev->stream>>>(x, mc, (int)w->k, (int)kp, mp, xq, xs16, xscale);
   FB_LAUNCH_CHECK(dev);
   GemvArgs a;
-  a.w = w->data; a.xt = xt; a.xsum = xsum; a.xscale = xscale; a.y = y; a.r1 = r1; a.r2 = r2;
+  a.w = w->data; a.xq = xq; a.xs16 = xs16; a.xscale = xscale; a.y = y; a.r1 = r1; a.r2 = r2;
   a.M = mc; a.Mp = mp; a.ngroups = w->ngroups;
   a.nunits = w->ntiles;
   a.n_out = (int)w->n;

@@ -8,14 +8,19 @@
 //    per SM are in flight without holding registers; the first copies are issued before
 //    griddepcontrol.wait, i.e. under programmatic dependent launch the weights stream in
 //    while the kernel that produces x is still running;
-//  * the prologue turns x into MMA B fragments in shared memory once per CTA: optional
+//  * the prologue turns x into int8 MMA B operands in shared memory once per CTA: optional
 //    residual add and RMSNorm (so the norm needs no kernel of its own), a power-of-two row
-//    scale, then a hi + lo pair of fp16 values per element (about 22 mantissa bits) and the
-//    per-32 sums Q4_K's offsets need;
-//  * quants are expanded to exact fp16 integers with logic ops and multiplied on the tensor
-//    cores (mma.sync.m16n8k16, fp32 accumulate). With one activation row the 8 MMA columns are
-//    otherwise idle, so hi sits in column 0 and lo in column 1 and one MMA covers both;
-//  * block scales are applied to the fp32 partial sums per 16/32-element group.
+//    scale, then FOUR signed 7-bit limbs per element (x/scale = (l0 + l1/2^7 + l2/2^14 +
+//    l3/2^21) / 64 to 2^-27), plus the per-16 sums the offsets of Q4_K/Q4_0/Q6_K need;
+//  * quants stay in the byte domain: one logic op turns four packed nibbles into four u8
+//    operands of mma.sync.m16n8k32 (u8 x s8 -> s32, exact), so the ALU pipe that limits an
+//    fp16 expansion is nearly idle;
+//  * "scale group per lane": in every MMA lane t of a quad feeds eight elements of scale group
+//    t (for rows g and g+8), and the B operand carries the limbs of group t' only in columns
+//    2t', 2t'+1. The accumulator of lane t then holds exactly its own group's integer dot
+//    products, so each lane decodes and applies ONE scale per chain of MMAs and no data is
+//    exchanged between lanes until the final sum;
+//  * integer dot products are exact; they are scaled and accumulated in fp32.
 //
 // Replaces the reference's qgemv kernels (fusor-ml/tile-ir-kernels/src/kernels/qgemv.rs:356-678,
 // qgemv_q6k.rs:84-385), their SwiGLU and residual epilogues
@@ -45,184 +50,162 @@ struct G1 {
   static constexpr int STRIDE = (TG + 127) / 128 * 128;
 };
 
-// ---- one activation row on an 8-column MMA -----------------------------------------------------
-// Four consecutive scale groups (j = 0..3) of a tile-group form a chain of MMAs into one
-// accumulator: the B operand of the MMAs of group j is non-zero only in columns 2j (hi half of
-// x) and 2j+1 (lo half), so after the chain lane t of every quad holds, for rows g and g+8,
-// the integer-weight dot product of scale group t. Each lane therefore decodes and applies the
-// scale of ONE group per chain (a quarter of the scale work per lane), and each lane loads B
-// data for one group only: lane (g, t) supplies group g/2, half g%2.
-__device__ __forceinline__ uint2 load_bx(const uint8_t* xh, int kk, int g, int t) {
-  return *reinterpret_cast<const uint2*>(xh + kk * 64 + t * 16 + (g & 1) * 8);
-}
+// Per-lane constants of the scale-group-per-lane mapping.
+struct Lane {
+  int g, t;
+  bool mine;     // this lane supplies B data (limbs of group t) in its column g
+  int e;         // which limb pair: column parity (0: limbs 0 and 2, 1: limbs 1 and 3)
+};
 
 __device__ __forceinline__ uint4 lds16(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
 
-__device__ __forceinline__ void mma1(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                     uint2 v, bool mine) {
-  mma16816(c, a0, a1, a2, a3, mine ? v.x : 0u, mine ? v.y : 0u);
+// Limbs of 8-element block kb: 32 bytes = [e = 0: limb0 x8, limb2 x8][e = 1: limb1 x8, limb3 x8].
+__device__ __forceinline__ uint4 load_limbs(const uint8_t* xl, int kb, const Lane& L) {
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  if (L.mine) v = lds16(xl + kb * 32 + L.e * 16);
+  return v;
 }
 
-__device__ __forceinline__ void group1_q4_0(const uint8_t* xh, const uint8_t* tg, int kg, int lane,
-                                            float& acc_g, float& acc_g8) {
-  const int g = lane >> 2, t = lane & 3, jb = g >> 1;
-  const uint4 qa = lds16(tg + lane * 16);
-  const uint4 qb = lds16(tg + 512 + lane * 16);
+// Both limb pairs of one 8-element step.
+template <bool SIGNED_A>
+__device__ __forceinline__ void step(int (&c1)[4], int (&c2)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                     uint32_t a3, const uint4& v) {
+  mma_i8_k32<SIGNED_A>(c1, a0, a1, a2, a3, v.x, v.y);
+  mma_i8_k32<SIGNED_A>(c2, a0, a1, a2, a3, v.z, v.w);
+}
+
+// Integer dot products of one chain -> fp32 in units of 2^-13 * (w . x/scale):
+// (C0 * 128 + C1) + (C2 * 128 + C3) / 2^14.
+__device__ __forceinline__ float limbs_to_float(int c_l0, int c_l1, int c_l2, int c_l3) {
+  return fmaf((float)(c_l2 * 128 + c_l3), 1.0f / 16384.0f, (float)(c_l0 * 128 + c_l1));
+}
+
+__device__ __forceinline__ void group1_q4_0(const uint8_t* xl, const float* xs16, const uint8_t* tg,
+                                            int kg, const Lane& L, float& acc_g, float& acc_g8) {
+  const uint4 qa = lds16(tg + L.g * 64 + L.t * 16);
+  const uint4 qb = lds16(tg + 512 + L.g * 64 + L.t * 16);
+  const float d_g = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 1024 + (L.g * 4 + L.t) * 2));
+  const float d_g8 = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 1024 + ((L.g + 8) * 4 + L.t) * 2));
   const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w};
   const uint32_t wb[4] = {qb.x, qb.y, qb.z, qb.w};
-  // this lane's block is t: its scales for rows g and g+8
-  const float d_g = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 1024 + g * 8 + t * 2));
-  const float d_g8 = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 1024 + (g + 8) * 8 + t * 2));
-  const uint2 v0 = load_bx(xh, (kg * 4 + jb) * 2, g, t);
-  const uint2 v1 = load_bx(xh, (kg * 4 + jb) * 2 + 1, g, t);
-  float c[4] = {0.f, 0.f, 0.f, 0.f};
+  const int blk = kg * 4 + L.t;
+  int c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0};
 #pragma unroll
-  for (int blk = 0; blk < 4; ++blk) {
-    const bool mine = jb == blk;
-    mma1(c, hsub2(lo02(wa[blk]), 0x64086408u), hsub2(lo02(wb[blk]), 0x64086408u),
-         hsub2(lo02(wa[blk] >> 8), 0x64086408u), hsub2(lo02(wb[blk] >> 8), 0x64086408u), v0, mine);
-    mma1(c, hsub2(hi02(wa[blk]), 0x54805480u), hsub2(hi02(wb[blk]), 0x54805480u),
-         hsub2(hi02(wa[blk] >> 8), 0x54805480u), hsub2(hi02(wb[blk] >> 8), 0x54805480u), v1, mine);
+  for (int s = 0; s < 4; ++s) {
+    const uint4 v = load_limbs(xl, blk * 4 + s, L);
+    const int w0 = (s & 1) * 2;
+    if (s < 2)  // elements 0..15: low nibbles
+      step<false>(c1, c2, wa[w0] & 0x0F0F0F0Fu, wb[w0] & 0x0F0F0F0Fu, wa[w0 + 1] & 0x0F0F0F0Fu,
+                  wb[w0 + 1] & 0x0F0F0F0Fu, v);
+    else        // elements 16..31: high nibbles
+      step<false>(c1, c2, (wa[w0] >> 4) & 0x0F0F0F0Fu, (wb[w0] >> 4) & 0x0F0F0F0Fu,
+                  (wa[w0 + 1] >> 4) & 0x0F0F0F0Fu, (wb[w0 + 1] >> 4) & 0x0F0F0F0Fu, v);
   }
-  acc_g = fmaf(d_g, c[0] + c[1], acc_g);
-  acc_g8 = fmaf(d_g8, c[2] + c[3], acc_g8);
+  const float sx8 = 8.0f * (xs16[blk * 2] + xs16[blk * 2 + 1]);  // (q - 8): centre folded into the sum
+  acc_g = fmaf(d_g, limbs_to_float(c1[0], c1[1], c2[0], c2[1]) - sx8, acc_g);
+  acc_g8 = fmaf(d_g8, limbs_to_float(c1[2], c1[3], c2[2], c2[3]) - sx8, acc_g8);
 }
 
-__device__ __forceinline__ void group1_q8_0(const uint8_t* xh, const uint8_t* tg, int kg, int lane,
-                                            float& acc_g, float& acc_g8) {
-  const int g = lane >> 2, t = lane & 3, jb = g >> 1;
-  uint4 q[2][2];
+__device__ __forceinline__ void group1_q8_0(const uint8_t* xl, const uint8_t* tg, int kg,
+                                            const Lane& L, float& acc_g, float& acc_g8) {
+  uint4 q[2][2];  // [h][half]
 #pragma unroll
-  for (int p = 0; p < 2; ++p)
+  for (int h = 0; h < 2; ++h)
 #pragma unroll
-    for (int h = 0; h < 2; ++h) q[p][h] = lds16(tg + (p * 2 + h) * 512 + lane * 16);
-  const float d_g = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 2048 + g * 8 + t * 2));
-  const float d_g8 = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 2048 + (g + 8) * 8 + t * 2));
-  const uint2 v0 = load_bx(xh, (kg * 4 + jb) * 2, g, t);
-  const uint2 v1 = load_bx(xh, (kg * 4 + jb) * 2 + 1, g, t);
-  float c[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int half = 0; half < 2; ++half) q[h][half] = lds16(tg + (h * 2 + half) * 512 + L.g * 64 + L.t * 16);
+  const float d_g = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 2048 + (L.g * 4 + L.t) * 2));
+  const float d_g8 = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 2048 + ((L.g + 8) * 4 + L.t) * 2));
+  const int blk = kg * 4 + L.t;
+  int c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0};
 #pragma unroll
-  for (int blk = 0; blk < 4; ++blk) {
-    const bool mine = jb == blk;
-    const int p = blk >> 1;
-    const uint32_t wa[4] = {q[p][0].x, q[p][0].y, q[p][0].z, q[p][0].w};
-    const uint32_t wb[4] = {q[p][1].x, q[p][1].y, q[p][1].z, q[p][1].w};
-#pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-      const uint32_t xa = wa[(blk & 1) * 2 + hf] ^ 0x80808080u;
-      const uint32_t xb = wb[(blk & 1) * 2 + hf] ^ 0x80808080u;
-      mma1(c, hsub2(__byte_perm(xa, 0x64646464u, 0x4240), 0x64806480u),
-           hsub2(__byte_perm(xb, 0x64646464u, 0x4240), 0x64806480u),
-           hsub2(__byte_perm(xa, 0x64646464u, 0x4341), 0x64806480u),
-           hsub2(__byte_perm(xb, 0x64646464u, 0x4341), 0x64806480u), hf ? v1 : v0, mine);
-    }
+  for (int s = 0; s < 4; ++s) {
+    const uint4 v = load_limbs(xl, blk * 4 + s, L);
+    const uint4 a = q[0][s >> 1], b = q[1][s >> 1];
+    if (s & 1) step<true>(c1, c2, a.z, b.z, a.w, b.w, v);
+    else step<true>(c1, c2, a.x, b.x, a.y, b.y, v);
   }
-  acc_g = fmaf(d_g, c[0] + c[1], acc_g);
-  acc_g8 = fmaf(d_g8, c[2] + c[3], acc_g8);
+  acc_g = fmaf(d_g, limbs_to_float(c1[0], c1[1], c2[0], c2[1]), acc_g);
+  acc_g8 = fmaf(d_g8, limbs_to_float(c1[2], c1[3], c2[2], c2[3]), acc_g8);
 }
 
-// Q4_K: chain ch covers sub-blocks 4ch .. 4ch+3 (pairs of sub-blocks share the qs bytes: even
-// ones are the low nibbles, odd ones the high nibbles). Lane t owns sub-block 4ch + t.
-__device__ __forceinline__ void group1_q4k(const uint8_t* xh, const float* xsum, const uint8_t* tg,
-                                           int kg, int lane, float& acc_g, float& acc_g8) {
-  const int g = lane >> 2, t = lane & 3, jb = g >> 1;
-  // 6-bit scales / offsets of both chains' sub-blocks t and 4 + t, rows g and g+8
+// Q4_K: chain ch covers sub-blocks 4ch .. 4ch+3; lane t owns sub-block 4ch + t, whose quants
+// are the low (t even) or high (t odd) nibbles of qs bytes 32 * (2ch + t/2) .. +32. High
+// nibbles are used in place as 16 * q and the factor goes into the scale.
+__device__ __forceinline__ void group1_q4k(const uint8_t* xl, const float* xs16, const uint8_t* tg,
+                                           int kg, const Lane& L, float& acc_g, float& acc_g8) {
+  const uint32_t mask = (L.t & 1) ? 0xF0F0F0F0u : 0x0F0F0F0Fu;
+  const float nib_scale = (L.t & 1) ? 0.0625f : 1.0f;
   float sc_f[2][2], mn_f[2][2];  // [row half][chain]
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const uint4 hd = lds16(tg + 2048 + (g + 8 * h) * 16);
-    const float d = fb::half_bits_to_float((uint16_t)(hd.x & 0xFFFF));
+    const uint4 hd = lds16(tg + 2048 + (L.g + 8 * h) * 16);
+    const float d = fb::half_bits_to_float((uint16_t)(hd.x & 0xFFFF)) * nib_scale;
     const float dmin = fb::half_bits_to_float((uint16_t)(hd.x >> 16));
     const uint32_t s0 = hd.y, s1 = hd.z, s2 = hd.w;
     const uint32_t scB = (s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u);
     const uint32_t mnB = ((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u);
-    const int sh = 8 * t;
+    const int sh = 8 * L.t;
     sc_f[h][0] = d * (float)((s0 >> sh) & 0x3F);
     mn_f[h][0] = dmin * (float)((s1 >> sh) & 0x3F);
     sc_f[h][1] = d * (float)((scB >> sh) & 0xFF);
     mn_f[h][1] = dmin * (float)((mnB >> sh) & 0xFF);
   }
+  const int slot = L.g * 32 + (L.t >> 1) * 16;
 #pragma unroll
   for (int ch = 0; ch < 2; ++ch) {
-    const uint4 qa = lds16(tg + (ch * 2) * 512 + lane * 16);
-    const uint4 qb = lds16(tg + (ch * 2 + 1) * 512 + lane * 16);
-    const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w};
-    const uint32_t wb[4] = {qb.x, qb.y, qb.z, qb.w};
-    const int kk0 = kg * 16 + (ch * 4 + jb) * 2;
-    const uint2 v0 = load_bx(xh, kk0, g, t);
-    const uint2 v1 = load_bx(xh, kk0 + 1, g, t);
-    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    int c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0};
+    const int sb = kg * 8 + ch * 4 + L.t;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const bool mine = jb == j;
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        const uint32_t ua = wa[(j >> 1) * 2 + hf], ub = wb[(j >> 1) * 2 + hf];
-        if ((j & 1) == 0)
-          mma1(c, hsub2(lo02(ua), 0x64006400u), hsub2(lo02(ub), 0x64006400u),
-               hsub2(lo02(ua >> 8), 0x64006400u), hsub2(lo02(ub >> 8), 0x64006400u), hf ? v1 : v0, mine);
-        else
-          mma1(c, hsub2(hi02(ua), 0x54005400u), hsub2(hi02(ub), 0x54005400u),
-               hsub2(hi02(ua >> 8), 0x54005400u), hsub2(hi02(ub >> 8), 0x54005400u), hf ? v1 : v0, mine);
-      }
+    for (int half = 0; half < 2; ++half) {
+      const uint4 qa = lds16(tg + ((ch * 2 + 0) * 2 + half) * 256 + slot);
+      const uint4 qb = lds16(tg + ((ch * 2 + 1) * 2 + half) * 256 + slot);
+      const uint4 v0 = load_limbs(xl, sb * 4 + half * 2, L);
+      const uint4 v1 = load_limbs(xl, sb * 4 + half * 2 + 1, L);
+      step<false>(c1, c2, qa.x & mask, qb.x & mask, qa.y & mask, qb.y & mask, v0);
+      step<false>(c1, c2, qa.z & mask, qb.z & mask, qa.w & mask, qb.w & mask, v1);
     }
-    const float sx = xsum[kg * 8 + ch * 4 + t];
-    acc_g = fmaf(sc_f[0][ch], c[0] + c[1], fmaf(-mn_f[0][ch], sx, acc_g));
-    acc_g8 = fmaf(sc_f[1][ch], c[2] + c[3], fmaf(-mn_f[1][ch], sx, acc_g8));
+    const float sx = xs16[sb * 2] + xs16[sb * 2 + 1];
+    acc_g = fmaf(sc_f[0][ch], limbs_to_float(c1[0], c1[1], c2[0], c2[1]), fmaf(-mn_f[0][ch], sx, acc_g));
+    acc_g8 = fmaf(sc_f[1][ch], limbs_to_float(c1[2], c1[3], c2[2], c2[3]), fmaf(-mn_f[1][ch], sx, acc_g8));
   }
 }
 
-// Q6_K: chain w = (c = w/2, u = w%2) covers the four groups 8c + 2*qsel + u, qsel = 0..3;
-// lane t owns qsel = t.
-__device__ __forceinline__ void group1_q6k(const uint8_t* xh, const uint8_t* tg, int kg, int lane,
-                                           float& acc_g, float& acc_g8) {
-  const int g = lane >> 2, t = lane & 3, jb = g >> 1;
-  uint4 qla[2], qlb[2], qhh[2], sc4[2];
-  float d[2];
+// Q6_K: chain (c, u) covers the 16-element groups 8c + 2q + u, q = 0..3; lane t owns q = t:
+// nibble t/2 of ql plane slot t%2 and bits 2t, 2t+1 of qh, merged per byte into a u8 in 0..63.
+__device__ __forceinline__ void group1_q6k(const uint8_t* xl, const float* xs16, const uint8_t* tg,
+                                           int kg, const Lane& L, float& acc_g, float& acc_g8) {
+  const int sh4 = 4 * (L.t >> 1);
+  const int rot = (4 - 2 * L.t) & 31;  // rotate-left that brings bits 2t, 2t+1 of each byte to 4, 5
+  const uint4 sc_g = lds16(tg + 3072 + L.g * 16);
+  const uint4 sc_g8 = lds16(tg + 3072 + (L.g + 8) * 16);
+  const float d_g = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 3328 + L.g * 2));
+  const float d_g8 = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 3328 + (L.g + 8) * 2));
+  auto merge = [&](uint32_t wl, uint32_t wh) -> uint32_t {
+    return ((wl >> sh4) & 0x0F0F0F0Fu) | (__funnelshift_l(wh, wh, rot) & 0x30303030u);
+  };
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    qla[h] = lds16(tg + h * 512 + lane * 16);
-    qlb[h] = lds16(tg + 1024 + h * 512 + lane * 16);
-    qhh[h] = lds16(tg + 2048 + h * 512 + lane * 16);
-    sc4[h] = lds16(tg + 3072 + (g + 8 * h) * 16);
-    d[h] = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 3328 + (g + 8 * h) * 2));
-  }
-#pragma unroll
-  for (int w = 0; w < 4; ++w) {
-    const uint32_t la[2] = {w == 0 ? qla[0].x : w == 1 ? qla[0].y : w == 2 ? qla[0].z : qla[0].w,
-                            w == 0 ? qla[1].x : w == 1 ? qla[1].y : w == 2 ? qla[1].z : qla[1].w};
-    const uint32_t lb[2] = {w == 0 ? qlb[0].x : w == 1 ? qlb[0].y : w == 2 ? qlb[0].z : qlb[0].w,
-                            w == 0 ? qlb[1].x : w == 1 ? qlb[1].y : w == 2 ? qlb[1].z : qlb[1].w};
-    const uint32_t hh[2] = {w == 0 ? qhh[0].x : w == 1 ? qhh[0].y : w == 2 ? qhh[0].z : qhh[0].w,
-                            w == 0 ? qhh[1].x : w == 1 ? qhh[1].y : w == 2 ? qhh[1].z : qhh[1].w};
-    const uint2 v = load_bx(xh, kg * 16 + 8 * (w >> 1) + 2 * jb + (w & 1), g, t);
-    float c[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int qsel = 0; qsel < 4; ++qsel) {
-      uint32_t af[4];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t lw = (qsel & 1) ? lb[h] : la[h];
-        if (qsel >= 2) lw >>= 4;
-        const uint32_t hw = hh[h];
-        const uint32_t h02 = (qsel == 0 ? (hw << 4) : qsel == 1 ? (hw << 2) : qsel == 2 ? hw : (hw >> 2)) & 0x00300030u;
-        const uint32_t h13 = (qsel == 0 ? (hw >> 4) : qsel == 1 ? (hw >> 6) : qsel == 2 ? (hw >> 8) : (hw >> 10)) & 0x00300030u;
-        af[h] = hsub2((lw & 0x000F000Fu) | h02 | 0x64006400u, 0x64206420u);
-        af[2 + h] = hsub2(((lw >> 8) & 0x000F000Fu) | h13 | 0x64006400u, 0x64206420u);
-      }
-      mma1(c, af[0], af[1], af[2], af[3], v, jb == qsel);
-    }
-    // scale byte 8c + 2t + u of this lane's group, rows g and g+8
-    float s[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const uint32_t wlo = (w >> 1) ? sc4[h].z : sc4[h].x, whi = (w >> 1) ? sc4[h].w : sc4[h].y;
-      const uint32_t word = (t >> 1) ? whi : wlo;
-      const int sv = (int)(int8_t)((word >> (8 * (2 * (t & 1) + (w & 1)))) & 0xFF);
-      s[h] = d[h] * (float)sv;
-    }
-    acc_g = fmaf(s[0], c[0] + c[1], acc_g);
-    acc_g8 = fmaf(s[1], c[2] + c[3], acc_g8);
+  for (int cu = 0; cu < 4; ++cu) {  // cu = 2c + u
+    const int c = cu >> 1, u = cu & 1;
+    const uint4 la = lds16(tg + (cu * 2 + 0) * 256 + L.g * 32 + (L.t & 1) * 16);
+    const uint4 lb = lds16(tg + (cu * 2 + 1) * 256 + L.g * 32 + (L.t & 1) * 16);
+    const uint4 ha = lds16(tg + 2048 + (cu * 2 + 0) * 128 + L.g * 16);
+    const uint4 hb = lds16(tg + 2048 + (cu * 2 + 1) * 128 + L.g * 16);
+    const int grp = 8 * c + 2 * L.t + u;           // this lane's scale group in the super-block
+    const int kb = (kg * 16 + grp) * 2;
+    const uint4 v0 = load_limbs(xl, kb, L);
+    const uint4 v1 = load_limbs(xl, kb + 1, L);
+    int c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0};
+    step<false>(c1, c2, merge(la.x, ha.x), merge(lb.x, hb.x), merge(la.y, ha.y), merge(lb.y, hb.y), v0);
+    step<false>(c1, c2, merge(la.z, ha.z), merge(lb.z, hb.z), merge(la.w, ha.w), merge(lb.w, hb.w), v1);
+    // int8 scale byte `grp` of rows g and g+8: word grp/4 = 2c + t/2, byte grp%4 = 2(t%2) + u
+    const uint32_t wg = (L.t >> 1) ? (c ? sc_g.w : sc_g.y) : (c ? sc_g.z : sc_g.x);
+    const uint32_t wg8 = (L.t >> 1) ? (c ? sc_g8.w : sc_g8.y) : (c ? sc_g8.z : sc_g8.x);
+    const int bsh = 8 * (2 * (L.t & 1) + u);
+    const float s_g = d_g * (float)(int)(int8_t)((wg >> bsh) & 0xFF);
+    const float s_g8 = d_g8 * (float)(int)(int8_t)((wg8 >> bsh) & 0xFF);
+    const float sx32 = 32.0f * xs16[kg * 16 + grp];  // (q - 32): centre folded into the sum
+    acc_g = fmaf(s_g, limbs_to_float(c1[0], c1[1], c2[0], c2[1]) - sx32, acc_g);
+    acc_g8 = fmaf(s_g8, limbs_to_float(c1[2], c1[3], c2[2], c2[3]) - sx32, acc_g8);
   }
 }
 
@@ -240,9 +223,9 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float* sh, i
   return r;
 }
 
-// EPI: 0 none, 1 residual(s), 2 SwiGLU pair. W = warps per CTA.
-template <int TYPE, int EPI, int W>
-__global__ void __launch_bounds__(W * 32)
+// EPI: 0 none, 1 residual(s), 2 SwiGLU pair. W = warps per CTA, MINB = CTAs per SM to plan for.
+template <int TYPE, int EPI, int W, int MINB>
+__global__ void __launch_bounds__(W * 32, MINB)
 qgemv1_kernel(const Gemv1Args a) {
   using R = G1<TYPE>;
   constexpr int NP = EPI == 2 ? 2 : 1;
@@ -251,13 +234,14 @@ qgemv1_kernel(const Gemv1Args a) {
   const int S = a.stages;
   uint8_t* ring = smem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + W * S * R::STRIDE);
-  uint8_t* xh = smem + W * S * R::STRIDE + W * S * 8;  // multiple of 64 bytes
-  float* xsum = reinterpret_cast<float*>(xh + (size_t)a.Kp * 4);
-  float* red = xsum + a.Kp / 32;   // [NP][W][16]
+  uint8_t* xl = smem + W * S * R::STRIDE + W * S * 8;  // limbs: 4 bytes per element
+  float* xs16 = reinterpret_cast<float*>(xl + (size_t)a.Kp * 4);  // 2^13 * sum(x/scale) per 16
+  float* red = xs16 + a.Kp / 16;   // [NP][W][16]
   float* tmp = red + NP * W * 16;  // [W] block reductions
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane >> 2, t = lane & 3;
+  Lane L;
+  L.g = lane >> 2; L.t = lane & 3; L.mine = (L.g >> 1) == L.t; L.e = L.g & 1;
   uint8_t* my_ring = ring + warp * S * R::STRIDE;
   const uint32_t my_bar = smem_u32(bars + warp * S);
 
@@ -268,27 +252,31 @@ qgemv1_kernel(const Gemv1Args a) {
   }
   __syncwarp();
 
+  // this warp's items in issue order: for each unit of the CTA, for each pass (gate / up), the
+  // K groups warp, warp + W, ...
   const int gw = a.ngroups > warp ? (a.ngroups - warp + W - 1) / W : 0;
   const int my_units = a.nunits > (int)blockIdx.x ? (a.nunits - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  const int per_unit = NP * gw;
-  const int n_items = my_units * per_unit;
-  auto issue = [&](int i, int st) {
-    const int j = i / per_unit, rem = i - j * per_unit;
-    const int p = rem / gw, kk = rem - p * gw;
-    const int tile = (int)blockIdx.x + j * (int)gridDim.x + p * a.pair_tile_offset;
-    const int kg = warp + W * kk;
-    const uint8_t* src = a.w + ((size_t)tile * a.ngroups + kg) * R::TG;
+  const int n_items = my_units * NP * gw;
+  int is_tile = blockIdx.x, is_p = 0, is_kk = 0, issued = 0;  // issue-side cursor
+  auto issue_next = [&](int st) {
+    const int tile = is_tile + is_p * a.pair_tile_offset;
+    const uint8_t* src = a.w + ((size_t)tile * a.ngroups + (warp + W * is_kk)) * R::TG;
     mbar_expect_tx(my_bar + 8 * st, R::TG);
     bulk_g2s(smem_u32(my_ring + st * R::STRIDE), src, R::TG, my_bar + 8 * st);
+    ++issued;
+    if (++is_kk == gw) {
+      is_kk = 0;
+      if (++is_p == NP) { is_p = 0; is_tile += gridDim.x; }
+    }
   };
   if (lane == 0) {
     const int pre = n_items < S ? n_items : S;
-    for (int i = 0; i < pre; ++i) issue(i, i);
+    for (int i = 0; i < pre; ++i) issue_next(i);
   }
   // only weights were touched so far; x comes from the kernel before this one
   pdl_wait();
 
-  // ---- activation prologue: (residual) -> (RMSNorm) -> power-of-two scale -> hi/lo fragments
+  // ---- activation prologue: (residual) -> (RMSNorm) -> power-of-two scale -> int8 limbs
   float ss = 0.f, amax = 0.f;
   for (int k = threadIdx.x; k < a.K; k += THREADS) {
     float v = a.x[k];
@@ -308,40 +296,46 @@ qgemv1_kernel(const Gemv1Args a) {
     }
   }
   amax = block_reduce(amax, true, tmp, W);
-  int e = 0;
-  if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &e);
-  const float inv = ldexpf(1.0f, -e), xscale = ldexpf(1.0f, e);
-  for (int q0 = 0; q0 < (a.Kp >> 2); q0 += THREADS) {
-    const int q = q0 + threadIdx.x;  // Kp / 4 is a multiple of 32, so whole warps stay together
-    const int k = q * 4;
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    if (q < (a.Kp >> 2)) {
+  int ex = 0;
+  if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &ex);  // amax = f * 2^ex, f in [0.5, 1)
+  const float inv64 = ldexpf(64.0f, -ex);               // x * inv64 in (-64, 64)
+  const float out_scale = ldexpf(1.0f, ex - 13);        // 2^ex / (64 * 128)
+  const int nblk = a.Kp >> 3;
+  for (int b0 = 0; b0 < nblk; b0 += THREADS) {
+    const int kb = b0 + threadIdx.x;  // Kp / 8 is a multiple of 32: whole warps stay together
+    uint32_t lw[4][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}, {0u, 0u}};
+    float sum = 0.f;
+    if (kb < nblk) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        if (k + i < a.K) {
-          float u = a.x[k + i];
-          if (a.xres) u += a.xres[k + i];
-          if (a.norm_w) u = (u / rms) * a.norm_w[k + i];
-          v[i] = u * inv;
+      for (int i = 0; i < 8; ++i) {
+        const int k = kb * 8 + i;
+        float v = 0.f;
+        if (k < a.K) {
+          v = a.x[k];
+          if (a.xres) v += a.xres[k];
+          if (a.norm_w) v = (v / rms) * a.norm_w[k];
+          v *= inv64;
         }
+        sum += v;
+        // four signed limbs; every remainder is exact in fp32
+        float l0 = rintf(v), r = (v - l0) * 128.0f;
+        float l1 = rintf(r); r = (r - l1) * 128.0f;
+        float l2 = rintf(r); r = (r - l2) * 128.0f;
+        float l3 = rintf(r);
+        const int sh = 8 * (i & 3);
+        lw[0][i >> 2] |= ((uint32_t)(int)l0 & 0xFFu) << sh;
+        lw[1][i >> 2] |= ((uint32_t)(int)l1 & 0xFFu) << sh;
+        lw[2][i >> 2] |= ((uint32_t)(int)l2 & 0xFFu) << sh;
+        lw[3][i >> 2] |= ((uint32_t)(int)l3 & 0xFFu) << sh;
+      }
     }
-    float s = (v[0] + v[1]) + (v[2] + v[3]);
-    s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
-    s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
-    s += __shfl_xor_sync(0xFFFFFFFFu, s, 4);
-    if (q < (a.Kp >> 2)) {
-      __half2 h01 = __floats2half2_rn(v[0], v[2]);
-      __half2 h23 = __floats2half2_rn(v[1], v[3]);
-      float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-      __half2 l01 = __floats2half2_rn(v[0] - f01.x, v[2] - f01.y);
-      __half2 l23 = __floats2half2_rn(v[1] - f23.x, v[3] - f23.y);
-      uint4 pk;
-      pk.x = *reinterpret_cast<uint32_t*>(&h01);
-      pk.y = *reinterpret_cast<uint32_t*>(&h23);
-      pk.z = *reinterpret_cast<uint32_t*>(&l01);
-      pk.w = *reinterpret_cast<uint32_t*>(&l23);
-      *reinterpret_cast<uint4*>(xh + (size_t)k * 4) = pk;  // chunk k/16 at 64 B, quad (k%16)/4 at 16 B
-      if ((threadIdx.x & 7) == 0) xsum[k >> 5] = s;
+    // per-16 sums in the units of the integer dot products: sum(x * inv64) * 128
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+    if (kb < nblk) {
+      uint4* dst = reinterpret_cast<uint4*>(xl + (size_t)kb * 32);
+      dst[0] = make_uint4(lw[0][0], lw[0][1], lw[2][0], lw[2][1]);
+      dst[1] = make_uint4(lw[1][0], lw[1][1], lw[3][0], lw[3][1]);
+      if ((threadIdx.x & 1) == 0) xs16[kb >> 1] = sum * 128.0f;
     }
   }
   __syncthreads();
@@ -358,12 +352,14 @@ qgemv1_kernel(const Gemv1Args a) {
         mbar_wait(my_bar + 8 * st, phase, a.status);
         const uint8_t* tg = my_ring + st * R::STRIDE;
         const int kg = warp + W * kk;
-        if (TYPE == FB200_Q4_0) group1_q4_0(xh, tg, kg, lane, acc_g, acc_g8);
-        else if (TYPE == FB200_Q8_0) group1_q8_0(xh, tg, kg, lane, acc_g, acc_g8);
-        else if (TYPE == FB200_Q4_K) group1_q4k(xh, xsum, tg, kg, lane, acc_g, acc_g8);
-        else group1_q6k(xh, tg, kg, lane, acc_g, acc_g8);
-        __syncwarp();  // every lane has consumed the stage before it is refilled
-        if (lane == 0 && item + S < n_items) issue(item + S, st);
+        if (TYPE == FB200_Q4_0) group1_q4_0(xl, xs16, tg, kg, L, acc_g, acc_g8);
+        else if (TYPE == FB200_Q8_0) group1_q8_0(xl, tg, kg, L, acc_g, acc_g8);
+        else if (TYPE == FB200_Q4_K) group1_q4k(xl, xs16, tg, kg, L, acc_g, acc_g8);
+        else group1_q6k(xl, xs16, tg, kg, L, acc_g, acc_g8);
+        // Every lane has read the stage (its loads precede this barrier in program order and
+        // shared loads complete long before a refill from global memory can land).
+        __syncwarp();
+        if (lane == 0 && issued < n_items) issue_next(st);
         if (++st == S) { st = 0; phase ^= 1u; }
       }
       // lane t accumulated the scale groups it owns: sum over the quad
@@ -371,9 +367,9 @@ qgemv1_kernel(const Gemv1Args a) {
       acc_g += __shfl_xor_sync(0xFFFFFFFFu, acc_g, 2);
       acc_g8 += __shfl_xor_sync(0xFFFFFFFFu, acc_g8, 1);
       acc_g8 += __shfl_xor_sync(0xFFFFFFFFu, acc_g8, 2);
-      if (t == 0) {
-        red[(p * W + warp) * 16 + g] = acc_g;
-        red[(p * W + warp) * 16 + g + 8] = acc_g8;
+      if (L.t == 0) {
+        red[(p * W + warp) * 16 + L.g] = acc_g;
+        red[(p * W + warp) * 16 + L.g + 8] = acc_g8;
       }
     }
     __syncthreads();
@@ -386,7 +382,7 @@ qgemv1_kernel(const Gemv1Args a) {
         for (int p = 0; p < NP; ++p) {
           float s = 0.f;
           for (int w = 0; w < W; ++w) s += red[(p * W + w) * 16 + r];
-          v[p] = s * xscale;
+          v[p] = s * out_scale;
         }
         float out;
         if (EPI == 2) {
@@ -411,18 +407,18 @@ template <int TYPE, int EPI, int W>
 size_t gemv1_smem(int stages, int kp) {
   constexpr int NP = EPI == 2 ? 2 : 1;
   return (size_t)W * stages * G1<TYPE>::STRIDE + (size_t)W * stages * 8 + (size_t)kp * 4 +
-         (size_t)kp / 32 * 4 + (size_t)NP * W * 16 * 4 + (size_t)W * 4 + 64;
+         (size_t)kp / 16 * 4 + (size_t)NP * W * 16 * 4 + (size_t)W * 4 + 64;
 }
 
-template <int TYPE, int EPI, int W>
-int launch_w(fb200_device* dev, Gemv1Args& a, int ctas_per_sm) {
-  auto kern = qgemv1_kernel<TYPE, EPI, W>;
+template <int TYPE, int EPI, int W, int MINB>
+int launch_w(fb200_device* dev, Gemv1Args& a) {
+  auto kern = qgemv1_kernel<TYPE, EPI, W, MINB>;
   static bool configured[64] = {false};
   if (!configured[dev->ordinal & 63]) {
     FB_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
     configured[dev->ordinal & 63] = true;
   }
-  int grid = dev->sm_count * ctas_per_sm;
+  int grid = dev->sm_count * MINB;
   if (grid > a.nunits) grid = a.nunits;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
@@ -439,21 +435,21 @@ int launch_w(fb200_device* dev, Gemv1Args& a, int ctas_per_sm) {
   return FB200_OK;
 }
 
-// Two 8-warp CTAs per SM when their rings and the activation fragments fit twice in shared
-// memory, otherwise one 16-warp CTA; the ring depth takes what is left, up to 6 stages.
+// Shared memory per SM is split between the activation limbs (4 B per element of K, one copy
+// per CTA) and the weight rings. Prefer many small CTAs (more resident warps hide the MMA and
+// shared-load latency); fall back to fewer, larger CTAs as K grows.
 template <int TYPE, int EPI>
 int launch_cfg(fb200_device* dev, Gemv1Args& a) {
-  const int budget2 = (SMEM_LIMIT - 2048) / 2;
-  for (int s = 6; s >= 2; --s)
-    if ((int)gemv1_smem<TYPE, EPI, 8>(s, a.Kp) <= budget2) {
-      a.stages = s;
-      return launch_w<TYPE, EPI, 8>(dev, a, 2);
-    }
-  for (int s = 6; s >= 1; --s)
-    if ((int)gemv1_smem<TYPE, EPI, 16>(s, a.Kp) <= SMEM_LIMIT - 1024) {
-      a.stages = s;
-      return launch_w<TYPE, EPI, 16>(dev, a, 1);
-    }
+  const int per_sm = SMEM_LIMIT - 4096;
+  auto fits = [&](size_t need, int ctas) { return (need + 1024) * ctas <= (size_t)per_sm; };
+  for (int s = 3; s >= 2; --s)
+    if (fits(gemv1_smem<TYPE, EPI, 8>(s, a.Kp), 4)) { a.stages = s; return launch_w<TYPE, EPI, 8, 4>(dev, a); }
+  for (int s = 4; s >= 2; --s)
+    if (fits(gemv1_smem<TYPE, EPI, 8>(s, a.Kp), 3)) { a.stages = s; return launch_w<TYPE, EPI, 8, 3>(dev, a); }
+  for (int s = 4; s >= 2; --s)
+    if (fits(gemv1_smem<TYPE, EPI, 8>(s, a.Kp), 2)) { a.stages = s; return launch_w<TYPE, EPI, 8, 2>(dev, a); }
+  for (int s = 4; s >= 1; --s)
+    if (fits(gemv1_smem<TYPE, EPI, 16>(s, a.Kp), 1)) { a.stages = s; return launch_w<TYPE, EPI, 16, 1>(dev, a); }
   return fb200_fail(dev, FB200_ERR_CAPACITY, "qgemv1: K = %d does not fit in shared memory", a.K);
 }
 
@@ -466,12 +462,12 @@ int launch_epi1(fb200_device* dev, Gemv1Args& a, int epi) {
 
 }  // namespace
 
-// Largest K the single-row kernel takes (activation fragments live in shared memory).
+// Largest K the single-row kernel takes (activation limbs live in shared memory).
 bool fb200_qgemv1_fits(const fb200_qmatrix* w) {
   TileGeom geo;
   if (!tile_geom(w->type, &geo)) return false;
   const uint64_t kp = (uint64_t)w->ngroups * geo.group_elems;
-  return kp * 4 + kp / 8 + 16 * 3456 + 4096 <= (uint64_t)SMEM_LIMIT;
+  return kp * 4 + kp / 4 + 16 * 3456 + 8192 <= (uint64_t)SMEM_LIMIT;
 }
 
 // y[n_out] = epilogue(W . act(x)); act = optional residual add + RMSNorm (norm_w != null).
