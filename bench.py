@@ -1,0 +1,372 @@
+#!/usr/bin/env python
+"""Benchmark: Llama-3-8B-shaped Q4_K_M-style greedy decode on B200 through libfusor_b200.so.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch B]
+
+A step is one decode step (one new token per sequence) after a 512-token prompt. Prints ONE JSON
+line. `value` = tokens/s of the device-resident greedy loop (CUDA-graph replays, only token ids
+leave the GPU at the end); `e2e` = the same metric with the token id uploaded from pinned host
+memory and the next id read back every step through fb200_llama_forward. With --gpus N > 1
+(under torchrun) every rank runs an independent replica of the model on its own GPU (the model
+fits one GPU, so the path does not shard: replicas only, no collective on the data path).
+
+--impl reference times the reference's CPU algorithm (the C++ restatement under oracle/, the
+reference itself is Rust and cannot be built here) on the host cores: each step is 1/32 of a
+decode step's work (one transformer layer + 1/32 of the output head rows).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG = dict(n_layer=32, hidden=4096, ffn=14336, n_head=32, n_kv_head=8, head_dim=128, vocab=128256)
+PROMPT = 512
+Q4_K, Q6_K, F32 = 12, 14, 0
+BLOCK_BYTES = {Q4_K: 144, Q6_K: 210}
+METRIC = "Llama-3-8B Q4_K decode tok/s @1 GPU; quant GEMV HBM GB/s vs ~8 TB/s peak"
+
+
+def tensor_plan(cfg):
+    """Q4_K_M-style: Q4_K body, Q6_K for attn_v, ffn_down and the output head."""
+    e, f = cfg["hidden"], cfg["ffn"]
+    qd, kvd = cfg["n_head"] * cfg["head_dim"], cfg["n_kv_head"] * cfg["head_dim"]
+    plan = [("token_embd", -1, Q4_K, (cfg["vocab"], e)), ("output", -1, Q6_K, (cfg["vocab"], e))]
+    for i in range(cfg["n_layer"]):
+        plan += [("attn_q", i, Q4_K, (qd, e)), ("attn_k", i, Q4_K, (kvd, e)),
+                 ("attn_v", i, Q6_K, (kvd, e)), ("attn_output", i, Q4_K, (e, qd)),
+                 ("ffn_gate", i, Q4_K, (f, e)), ("ffn_up", i, Q4_K, (f, e)),
+                 ("ffn_down", i, Q6_K, (e, f))]
+    return plan
+
+
+def qbytes(ty, n, k):
+    return n * k // 256 * BLOCK_BYTES[ty]
+
+
+def weight_bytes_per_step(cfg):
+    """Algorithmic bytes one decode step streams: every matrix but the embedding table."""
+    return sum(qbytes(ty, *shape) for name, _l, ty, shape in tensor_plan(cfg) if name != "token_embd")
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.lines, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [l.split(", ") for ts, l in self.lines if t0 - 0.05 <= ts <= t1 + 0.15] or \
+               [l.split(", ") for _ts, l in self.lines]
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+                for nm, v in zip(names, r[5:9]):
+                    if v.strip().lower().startswith("active"):
+                        reasons.add(nm)
+            except (ValueError, IndexError):
+                pass
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def build_gpu_model(dev, torch, cfg, batch, ctx, seed, keep=None):
+    """Random Q4_K_M-style weights generated and encoded on the GPU (kalosm_b200.synth)."""
+    import kalosm_b200 as kb
+    from kalosm_b200 import synth
+    m = kb.Llama(dev, n_layer=cfg["n_layer"], hidden=cfg["hidden"], ffn=cfg["ffn"], n_head=cfg["n_head"],
+                 n_kv_head=cfg["n_kv_head"], head_dim=cfg["head_dim"], vocab=cfg["vocab"], max_seq_len=ctx,
+                 max_batch=batch)
+    for j, (name, layer, ty, (n, k)) in enumerate(tensor_plan(cfg)):
+        raw = synth.random_qweights(seed * 100003 + j, 0.02, n, k, ty, device="cuda").cpu().numpy()
+        m.set_tensor(name, layer, ty, (n, k), raw)
+        if keep is not None and (layer <= 0):
+            keep[(name, layer)] = raw
+    g = torch.Generator().manual_seed(seed + 77)
+    for i in range(cfg["n_layer"] + 1):
+        for nm in (("attn_norm", "ffn_norm") if i < cfg["n_layer"] else ("output_norm",)):
+            w = (1.0 + 0.02 * torch.randn(cfg["hidden"], generator=g)).numpy().astype(np.float32)
+            m.set_tensor(nm, i if i < cfg["n_layer"] else -1, F32, (cfg["hidden"],), w)
+            if keep is not None and i in (0, cfg["n_layer"]):
+                keep[(nm, i if i < cfg["n_layer"] else -1)] = w
+    return m
+
+
+def cpu_layer_sample(cfg, keep, threads=None, min_seconds=0.0, steps=None, warmup=0):
+    """Times the oracle's decode step on a 1-layer slice: one transformer layer plus 1/32 of the
+    output head rows = 1/32 of a full decode step's weight bytes. Returns seconds per slice."""
+    from oracle import oracle as O
+    if threads:
+        O.set_threads(threads)
+    vocab_slice = cfg["vocab"] // cfg["n_layer"] // 256 * 256
+    m = O.Llama(1, cfg["hidden"], cfg["ffn"], cfg["n_head"], cfg["n_kv_head"], cfg["head_dim"], vocab_slice,
+                64, batch=1, kv_f16=True)
+    names = {"attn_q": "wq", "attn_k": "wk", "attn_v": "wv", "attn_output": "wo", "ffn_gate": "gate",
+             "ffn_up": "up", "ffn_down": "down"}
+    for name, layer, ty, (n, k) in tensor_plan(cfg):
+        if layer == 0:
+            m.set_qmatrix(names[name], 0, ty, n, k, keep[(name, 0)])
+    row_bytes = cfg["hidden"] // 256
+    m.set_qmatrix("token_embd", 0, Q4_K, vocab_slice, cfg["hidden"],
+                  keep[("token_embd", -1)][: vocab_slice * row_bytes * 144])
+    m.set_qmatrix("output", 0, Q6_K, vocab_slice, cfg["hidden"],
+                  keep[("output", -1)][: vocab_slice * row_bytes * 210])
+    m.set_norm("attn_norm", 0, keep[("attn_norm", 0)])
+    m.set_norm("ffn_norm", 0, keep[("ffn_norm", 0)])
+    m.set_norm("output_norm", -1, keep[("output_norm", -1)])
+    tok = np.array([[1]], dtype=np.uint32)
+    for _ in range(max(warmup, 1)):
+        m.forward(tok)
+    times = []
+    t_start = time.perf_counter()
+    while True:
+        if m.pos >= 60:
+            m.reset()
+        t0 = time.perf_counter()
+        m.forward(tok)
+        times.append(time.perf_counter() - t0)
+        if steps is not None and len(times) >= steps:
+            break
+        if steps is None and time.perf_counter() - t_start >= min_seconds and len(times) >= 3:
+            break
+    return times, O.num_threads()
+
+
+def host_weights(cfg, seed):
+    """Layer-0 and model-level tensors on the host for the CPU arm (torch CPU generator)."""
+    from kalosm_b200 import synth
+    import torch
+    keep = {}
+    for j, (name, layer, ty, (n, k)) in enumerate(tensor_plan(cfg)):
+        if layer == 0:
+            keep[(name, 0)] = synth.random_qweights(seed * 100003 + j, 0.02, n, k, ty).numpy()
+        elif layer < 0:
+            n_s = cfg["vocab"] // cfg["n_layer"] // 256 * 256
+            keep[(name, -1)] = synth.random_qweights(seed * 100003 + j, 0.02, n_s, k, ty).numpy()
+    g = torch.Generator().manual_seed(seed + 77)
+    for key in (("attn_norm", 0), ("ffn_norm", 0), ("output_norm", -1)):
+        keep[key] = (1.0 + 0.02 * torch.randn(cfg["hidden"], generator=g)).numpy().astype(np.float32)
+    return keep
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    keep = host_weights(CFG, 1)
+    times, threads = cpu_layer_sample(CFG, keep, steps=args.steps, warmup=args.warmup)
+    total = float(np.sum(times))
+    step_ms = total / len(times) * 1e3
+    tok_s = 1.0 / (CFG["n_layer"] * total / len(times))
+    sample = ("each step = 1 transformer layer + 1/32 of the output-head rows of the 8B-shaped model "
+              "(1/32 of a decode step's weight bytes), batch 1, short context; tok/s = 1 / (32 x step time)")
+    line = {"impl": "reference", "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"llama3-8b-shaped Q4_K_M-style greedy decode, batch 1, prompt {PROMPT}, "
+                                   f"{args.steps} decode steps per replica", "batch": 1, "prompt": PROMPT,
+                       "note": "CPU arm: C++ restatement of Fusor's f32-dequantize q_mat_mul path, bounded sample"},
+            "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import kalosm_b200 as kb
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    dev = kb.Device(local, stream.cuda_stream)
+    batch, steps, warmup = args.batch, args.steps, max(args.warmup, 3)
+    ctx = PROMPT + 2 * (steps + warmup) + 64
+    keep = {} if rank == 0 else None
+    model = build_gpu_model(dev, torch, CFG, batch, ctx, seed=1 + rank, keep=keep)
+    rng = np.random.default_rng(rank)
+    prompt = rng.integers(0, CFG["vocab"], size=(batch, PROMPT), dtype=np.uint32)
+    _, nxt = model.forward(prompt, want_logits=False)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident loop (value) ----------------------------------------------------
+    model.generate_greedy(nxt, warmup)
+    last = model.generate_greedy(nxt, 1)[:, -1]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.3)
+    barrier()
+    launches0 = dev.launch_count
+    t0 = time.time()
+    e0.record(stream)
+    toks = model.generate_greedy(last, steps)
+    e1.record(stream)
+    barrier()
+    t1 = time.time()
+    launches = dev.launch_count - launches0
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop(t0, t1)
+    status = dev.status()
+
+    # ---- end to end: one fb200_llama_forward per step, ids through pinned host memory -------
+    pinned = torch.empty(batch, dtype=torch.int32).pin_memory()
+    pinned.copy_(torch.from_numpy(toks[:, -1].astype(np.int32)))
+    tok = pinned.numpy().view(np.uint32)
+    for _ in range(3):
+        _, n2 = model.forward(tok.reshape(batch, 1), want_logits=False)
+        tok[:] = n2
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record(stream)
+    for _ in range(steps):
+        _, n2 = model.forward(tok.reshape(batch, 1), want_logits=False)
+        tok[:] = n2
+    f1.record(stream)
+    barrier()
+    ms_e2e = f0.elapsed_time(f1)
+
+    # ---- dominant kernel alone: single-row GEMV over the gate/up matrices (SwiGLU epilogue) ----
+    roof = None
+    if rank == 0:
+        from kalosm_b200 import synth
+        f, e = CFG["ffn"], CFG["hidden"]
+        mats = []
+        for i in range(16):  # 16 x 66 MB: larger than L2, every launch streams from HBM
+            raw = synth.random_qweights(900 + i, 0.02, 2 * f, e, Q4_K, device="cuda").cpu().numpy()
+            mats.append(kb.QMatrix.from_raw_bytes(dev, (2 * f, e), raw, Q4_K))
+        x = dev.tensor(np.random.default_rng(5).standard_normal((1, e)).astype(np.float32))
+        y = dev.empty((1, f))
+        for w in mats:
+            x.q_mat_mul(w, epilogue=kb.EPI_SWIGLU, out=y)
+        torch.cuda.synchronize()
+        reps = 8
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record(stream)
+        for _ in range(reps):
+            for w in mats:
+                x.q_mat_mul(w, epilogue=kb.EPI_SWIGLU, out=y)
+        g1.record(stream)
+        torch.cuda.synchronize()
+        us = g0.elapsed_time(g1) * 1e3 / (reps * len(mats))
+        kbytes = qbytes(Q4_K, 2 * f, e)
+        peak, which = peaks()
+        achieved = kbytes / us / 1e3
+        roof = {"bound": "hbm", "kernel": "qgemv1_kernel<Q4_K, SwiGLU> on ffn gate+up [28672 x 4096]",
+                "achieved": achieved, "peak": peak, "peak_source": which, "unit": "GB/s",
+                "frac": achieved / peak, "us_per_launch": us, "bytes_per_launch": kbytes, "traffic": None}
+        for w in mats:
+            w.free()
+
+    t_all = [ms, ms_e2e]
+    if world > 1:
+        tt = torch.tensor(t_all, device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = tt.tolist()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    tok_s = world * batch * steps / (ms / 1e3)
+    tok_s_e2e = world * batch * steps / (ms_e2e / 1e3)
+    wb = weight_bytes_per_step(CFG)
+    kv = 2 * CFG["n_layer"] * CFG["n_kv_head"] * CFG["head_dim"] * 2 * (PROMPT + warmup + steps // 2) * batch
+    peak, which = peaks()
+    step_gbs = (wb + kv) / (ms / steps / 1e3) / 1e9
+    # CPU baseline beside it (rank 0, N = 1 only): bounded sample of the oracle's decode step
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        times, threads = cpu_layer_sample(CFG, keep, min_seconds=10.0)
+        per_tok = CFG["n_layer"] * float(np.median(times))
+        cpu = {"value": 1.0 / per_tok, "unit": "tok/s", "cores": threads, "kind": "port",
+               "sample": f"{len(times)} timed decode steps of a 1-layer slice (1 transformer layer + 1/32 of the "
+                         "output-head rows = 1/32 of a step's weight bytes), scaled x32; C++ restatement of "
+                         "Fusor's CPU q_mat_mul path"}
+    line = {"metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 x int8 -> s32 tensor-core dot products of GGUF quants and 4 x 7-bit activation limbs, "
+                     "f32 scales and accumulation",
+            "data": "synthetic (seeded N(0, 0.02) weights encoded as Q4_K / Q6_K blocks on the GPU, uniform-random "
+                    "token ids)",
+            "config": {"workload": f"llama3-8b-shaped Q4_K_M-style greedy decode, batch {batch}, prompt {PROMPT}, "
+                                   f"{steps} decode steps per replica", "batch": batch, "prompt": PROMPT,
+                       "l2": "4.9 GB of weights per step, far larger than L2",
+                       "parallelism": "replicas only" if world > 1 else "single GPU"},
+            "e2e": {"value": tok_s_e2e, "unit": "tok/s", "h2d_bytes_per_step": 4 * batch,
+                    "d2h_bytes_per_step": 4 * batch, "ms_per_step": ms_e2e / steps},
+            "gpu_launches": int(launches), "device_status": status, "clocks": clocks,
+            "roofline": roof,
+            "step_hbm": {"bytes_per_step": wb + kv, "achieved_gbs": step_gbs, "frac_of_peak": step_gbs / peak,
+                         "peak_source": which},
+            "cpu_baseline": cpu}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -329,6 +329,8 @@ int fb200_llama_create(fb200_device* dev, const fb200_llama_config* cfg, fb200_l
   FB_CUDA(dev, cudaMalloc(&m->next, (size_t)c.max_batch * 4));
   FB_CUDA(dev, cudaMalloc(&m->pos_dev, 4));
   FB_CUDA(dev, cudaMalloc(&m->step_dev, 4));
+  m->hist_cap = c.max_seq_len;
+  FB_CUDA(dev, cudaMalloc(&m->hist, (size_t)c.max_batch * m->hist_cap * 4));
   FB_CUDA(dev, cudaMemset(m->pos_dev, 0, 4));
   FB_CUDA(dev, cudaMemset(m->step_dev, 0, 4));
   // attention split scratch: the largest a forward pass can ask for is bounded by 64 splits of

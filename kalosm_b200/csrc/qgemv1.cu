@@ -53,17 +53,18 @@ struct G1 {
 // Per-lane constants of the scale-group-per-lane mapping.
 struct Lane {
   int g, t;
-  bool mine;     // this lane supplies B data (limbs of group t) in its column g
-  int e;         // which limb pair: column parity (0: limbs 0 and 2, 1: limbs 1 and 3)
+  // B data: lanes with g / 2 == t supply the limbs of group t in column g (limb pair g % 2:
+  // 0 -> limbs 0 and 2, 1 -> limbs 1 and 3); every other lane reads 16 zero bytes. Encoded as a
+  // base pointer and a stride so the load needs no branch: address = xb + block * xstep.
+  const uint8_t* xb;
+  int xstep;
 };
 
 __device__ __forceinline__ uint4 lds16(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
 
 // Limbs of 8-element block kb: 32 bytes = [e = 0: limb0 x8, limb2 x8][e = 1: limb1 x8, limb3 x8].
-__device__ __forceinline__ uint4 load_limbs(const uint8_t* xl, int kb, const Lane& L) {
-  uint4 v = make_uint4(0u, 0u, 0u, 0u);
-  if (L.mine) v = lds16(xl + kb * 32 + L.e * 16);
-  return v;
+__device__ __forceinline__ uint4 load_limbs(const uint8_t* /*xl*/, int kb, const Lane& L) {
+  return lds16(L.xb + kb * L.xstep);
 }
 
 // Both limb pairs of one 8-element step.
@@ -238,10 +239,17 @@ qgemv1_kernel(const Gemv1Args a) {
   float* xs16 = reinterpret_cast<float*>(xl + (size_t)a.Kp * 4);  // 2^13 * sum(x/scale) per 16
   float* red = xs16 + a.Kp / 16;   // [NP][W][16]
   float* tmp = red + NP * W * 16;  // [W] block reductions
+  uint8_t* zero16 = reinterpret_cast<uint8_t*>(tmp + W + (4 - (W & 3)) % 4);  // 16 zero bytes
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   Lane L;
-  L.g = lane >> 2; L.t = lane & 3; L.mine = (L.g >> 1) == L.t; L.e = L.g & 1;
+  L.g = lane >> 2; L.t = lane & 3;
+  {
+    const bool mine = (L.g >> 1) == L.t;
+    L.xb = mine ? xl + (L.g & 1) * 16 : zero16;
+    L.xstep = mine ? 32 : 0;
+  }
+  if (threadIdx.x < 4) reinterpret_cast<uint32_t*>(zero16)[threadIdx.x] = 0u;
   uint8_t* my_ring = ring + warp * S * R::STRIDE;
   const uint32_t my_bar = smem_u32(bars + warp * S);
 
@@ -407,7 +415,7 @@ template <int TYPE, int EPI, int W>
 size_t gemv1_smem(int stages, int kp) {
   constexpr int NP = EPI == 2 ? 2 : 1;
   return (size_t)W * stages * G1<TYPE>::STRIDE + (size_t)W * stages * 8 + (size_t)kp * 4 +
-         (size_t)kp / 16 * 4 + (size_t)NP * W * 16 * 4 + (size_t)W * 4 + 64;
+         (size_t)kp / 16 * 4 + (size_t)NP * W * 16 * 4 + (size_t)W * 4 + 96;
 }
 
 template <int TYPE, int EPI, int W, int MINB>
@@ -436,19 +444,18 @@ int launch_w(fb200_device* dev, Gemv1Args& a) {
 }
 
 // Shared memory per SM is split between the activation limbs (4 B per element of K, one copy
-// per CTA) and the weight rings. Prefer many small CTAs (more resident warps hide the MMA and
-// shared-load latency); fall back to fewer, larger CTAs as K grows.
+// per CTA, built by every CTA in its prologue) and the weight rings: 32 resident warps per SM
+// either way, in as few CTAs as the limbs allow.
 template <int TYPE, int EPI>
 int launch_cfg(fb200_device* dev, Gemv1Args& a) {
-  const int per_sm = SMEM_LIMIT - 4096;
+  const int per_sm = SMEM_LIMIT - 2048;
   auto fits = [&](size_t need, int ctas) { return (need + 1024) * ctas <= (size_t)per_sm; };
+  // two 16-warp CTAs per SM while two copies of the limbs fit, else one 32-warp CTA
   for (int s = 3; s >= 2; --s)
-    if (fits(gemv1_smem<TYPE, EPI, 8>(s, a.Kp), 4)) { a.stages = s; return launch_w<TYPE, EPI, 8, 4>(dev, a); }
-  for (int s = 4; s >= 2; --s)
-    if (fits(gemv1_smem<TYPE, EPI, 8>(s, a.Kp), 3)) { a.stages = s; return launch_w<TYPE, EPI, 8, 3>(dev, a); }
-  for (int s = 4; s >= 2; --s)
-    if (fits(gemv1_smem<TYPE, EPI, 8>(s, a.Kp), 2)) { a.stages = s; return launch_w<TYPE, EPI, 8, 2>(dev, a); }
-  for (int s = 4; s >= 1; --s)
+    if (fits(gemv1_smem<TYPE, EPI, 16>(s, a.Kp), 2)) { a.stages = s; return launch_w<TYPE, EPI, 16, 2>(dev, a); }
+  for (int s = 2; s >= 1; --s)
+    if (fits(gemv1_smem<TYPE, EPI, 32>(s, a.Kp), 1)) { a.stages = s; return launch_w<TYPE, EPI, 32, 1>(dev, a); }
+  for (int s = 2; s >= 1; --s)
     if (fits(gemv1_smem<TYPE, EPI, 16>(s, a.Kp), 1)) { a.stages = s; return launch_w<TYPE, EPI, 16, 1>(dev, a); }
   return fb200_fail(dev, FB200_ERR_CAPACITY, "qgemv1: K = %d does not fit in shared memory", a.K);
 }
@@ -467,7 +474,7 @@ bool fb200_qgemv1_fits(const fb200_qmatrix* w) {
   TileGeom geo;
   if (!tile_geom(w->type, &geo)) return false;
   const uint64_t kp = (uint64_t)w->ngroups * geo.group_elems;
-  return kp * 4 + kp / 4 + 16 * 3456 + 8192 <= (uint64_t)SMEM_LIMIT;
+  return kp * 4 + kp / 4 + 16 * 3456 + 8192 <= (uint64_t)SMEM_LIMIT - 2048;
 }
 
 // y[n_out] = epilogue(W . act(x)); act = optional residual add + RMSNorm (norm_w != null).
