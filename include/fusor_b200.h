@@ -131,6 +131,26 @@ FB200_API int fb200_rms_norm_q_mat_mul(fb200_device* dev, const float* x_dev,
                                        const float* residual_dev, const float* norm_weight_dev,
                                        float eps, size_t m, const fb200_qmatrix* w, float* y_dev,
                                        const fb200_epilogue* epilogue);
+/* The same product for callers that must not allocate. This entry point has no counterpart in
+ * the reference. fb200_q_mat_mul grows a device scratch buffer (for the activations repacked
+ * as integer limbs) with cudaMalloc when a larger product arrives; hosts that cannot enter the
+ * CUDA allocator at call time -- a serving loop whose memory budget is frozen after start-up,
+ * a callback running on a thread that holds a lock the allocator needs, an embedding
+ * application that forbids allocation after initialisation -- call this instead. The scratch is
+ * a fixed 4 MiB array inside the library image (every GPU that loads the library carries it
+ * until the process exits); neither this function nor anything it calls allocates or frees
+ * device or host memory.
+ *   - y[M, N] = x[M, K] . W^T, 1 <= M <= 32, W of type Q4_0 / Q8_0 / Q4_K / Q6_K, no epilogue.
+ *   - FB200_ERR_CAPACITY when M > 32 or when the packed activations (about 136 bytes per
+ *     element of K for 17..32 rows, 68 for 9..16, 34 for 1..8) exceed the 4 MiB array.
+ *   - The first call on a device looks up the array's device address; make that call before
+ *     starting any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents; each call
+ *     rewrites everything it reads, so nothing needs clearing, but two calls whose kernels
+ *     overlap on the GPU (different streams or device handles) race on it. Keep calls on one
+ *     stream, or otherwise ordered. */
+FB200_API int fb200_q_mat_mul_noalloc(fb200_device* dev, const float* x_dev, size_t m,
+                                      const fb200_qmatrix* w, float* y_dev);
 /* Same product with host buffers: uploads x, runs, downloads y, synchronises. */
 FB200_API int fb200_q_mat_mul_host(fb200_device* dev, const float* x_host, size_t m,
                          const fb200_qmatrix* w, float* y_host);

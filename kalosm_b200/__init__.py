@@ -58,7 +58,7 @@ EXPORTS = [
     "fb200_download", "fb200_memset", "fb200_qmatrix_from_raw_bytes", "fb200_qmatrix_free",
     "fb200_qmatrix_shape", "fb200_qmatrix_ggml_type", "fb200_qmatrix_nbytes",
     "fb200_qmatrix_dequantize", "fb200_qmatrix_concat_rows", "fb200_q_mat_mul",
-    "fb200_q_mat_mul_host", "fb200_rms_norm_q_mat_mul", "fb200_rms_norm", "fb200_silu_mul", "fb200_rope_tables",
+    "fb200_q_mat_mul_host", "fb200_q_mat_mul_noalloc", "fb200_rms_norm_q_mat_mul", "fb200_rms_norm", "fb200_silu_mul", "fb200_rope_tables",
     "fb200_rope_pair", "fb200_embedding_lookup", "fb200_argmax", "fb200_kv_cache_create",
     "fb200_kv_cache_free", "fb200_kv_cache_reset", "fb200_kv_cache_len", "fb200_kv_cache_append",
     "fb200_kv_cache_buffers", "fb200_flash_attention", "fb200_llama_create", "fb200_llama_free",
@@ -101,6 +101,7 @@ def load_library():
         "fb200_qmatrix_concat_rows": (i32, [pp, i32, pp]),
         "fb200_q_mat_mul": (i32, [vp, vp, sz, vp, vp, C.POINTER(_Epilogue)]),
         "fb200_q_mat_mul_host": (i32, [vp, vp, sz, vp, vp]),
+        "fb200_q_mat_mul_noalloc": (i32, [vp, vp, sz, vp, vp]),
         "fb200_rms_norm_q_mat_mul": (i32, [vp, vp, vp, vp, f32, sz, vp, vp, C.POINTER(_Epilogue)]),
         "fb200_rms_norm": (i32, [vp, vp, vp, vp, vp, f32, sz, sz, vp]),
         "fb200_silu_mul": (i32, [vp, vp, vp, sz, vp]),
@@ -184,6 +185,18 @@ class Tensor:
         d = self.device
         d._check(d.lib.fb200_q_mat_mul(d.h, self.ptr, m, w.h, y.ptr, C.byref(ep)))
         return y
+
+    def q_mat_mul_noalloc(self, w: "QMatrix", out: "Tensor") -> "Tensor":
+        """self [M <= 32, K] . W^T into the caller's `out`, through the entry point that never
+        allocates (its scratch is a fixed array inside the library). Both tensors must exist
+        before the call; see fb200_q_mat_mul_noalloc in include/fusor_b200.h for the limits."""
+        k = self.shape[-1]
+        if k != w.shape[1]:
+            raise FusorError(ERR_INVALID_SHAPE, f"lhs columns ({k}) != weight in_features ({w.shape[1]})")
+        m = int(np.prod(self.shape[:-1], dtype=np.int64)) if len(self.shape) > 1 else 1
+        d = self.device
+        d._check(d.lib.fb200_q_mat_mul_noalloc(d.h, self.ptr, m, w.h, out.ptr))
+        return out
 
     def rms_norm_q_mat_mul(self, norm_weight: "Tensor", eps: float, w: "QMatrix",
                            residual: "Tensor" = None, epilogue: int = EPI_NONE, r1: "Tensor" = None,

@@ -534,3 +534,62 @@ int fb200_qgemv_chunk(fb200_device* dev, const fb200_qmatrix* w, const float* x,
     default: return launch_nt<FB200_Q6_K>(dev, a, nt, epi);
   }
 }
+
+// ---- product without any allocation ------------------------------------------------------------
+// Some hosts may not allocate device memory at the moment they need a product: code that runs
+// inside a region where the CUDA allocator must not be entered (a latency-critical serving
+// loop that has pinned its memory budget, a callback on a thread that holds locks the
+// allocator also takes, a plug-in sandbox that forbids cudaMalloc after start-up). The regular
+// entry point grows a scratch buffer for the packed activation limbs on demand; this variant
+// keeps that scratch in a fixed array that is part of the library image instead.
+//
+// FB200_STATIC_SCRATCH_BYTES of device memory per GPU that loads the library, held until exit.
+constexpr size_t FB200_STATIC_SCRATCH_BYTES = 4u << 20;
+static __device__ __align__(256) uint8_t g_static_xpack[FB200_STATIC_SCRATCH_BYTES];
+
+namespace {
+// Device address of g_static_xpack per device ordinal. In host code the array's name is only a
+// handle for the runtime; the address a kernel can use comes from cudaGetSymbolAddress, asked
+// once per device with that device current.
+void* g_static_xpack_addr[64] = {nullptr};
+}  // namespace
+
+extern "C" int fb200_q_mat_mul_noalloc(fb200_device* dev, const float* x_dev, size_t m,
+                                       const fb200_qmatrix* w, float* y_dev) {
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  if (!w || !x_dev || !y_dev)
+    return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "q_mat_mul_noalloc: null argument");
+  if (w->dev != dev)
+    return fb200_fail(dev, FB200_ERR_DEVICE_MISMATCH, "q_mat_mul_noalloc: weight lives on another device handle");
+  if (!w->tiled)
+    return fb200_fail(dev, FB200_ERR_UNSUPPORTED_DTYPE,
+                      "q_mat_mul_noalloc: only Q4_0, Q8_0, Q4_K and Q6_K weights are supported");
+  if (m == 0 || w->n == 0) return FB200_OK;
+  if (m > 32)
+    return fb200_fail(dev, FB200_ERR_CAPACITY, "q_mat_mul_noalloc: %zu activation rows, at most 32 per call", m);
+  if (dev->ordinal < 0 || dev->ordinal >= 64)
+    return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "q_mat_mul_noalloc: device ordinal %d out of range", dev->ordinal);
+  TileGeom geo;
+  tile_geom(w->type, &geo);
+  const uint64_t kp = (uint64_t)w->ngroups * geo.group_elems;
+  const int mp = m <= 8 ? 8 : m <= 16 ? 16 : 32;
+  const size_t need = fb200_xpack_bytes(mp, kp);
+  if (need > FB200_STATIC_SCRATCH_BYTES)
+    return fb200_fail(dev, FB200_ERR_CAPACITY,
+                      "q_mat_mul_noalloc: %zu rows x K = %llu need %zu bytes of packed activations, the "
+                      "built-in scratch holds %zu",
+                      m, (unsigned long long)w->k, need, (size_t)FB200_STATIC_SCRATCH_BYTES);
+  void*& scratch = g_static_xpack_addr[dev->ordinal];
+  if (!scratch) {
+    // first call on this device: resolve the array's device address (device is current)
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_xpack);
+    if (e != cudaSuccess || !p)
+      return fb200_fail(dev, FB200_ERR_CUDA, "q_mat_mul_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    scratch = p;
+  }
+  // Nothing in the scratch has to start at zero: the pack kernel rewrites every byte the
+  // product kernel reads (limbs of padded rows are never loaded, their sums are written as 0).
+  return fb200_qgemv_chunk(dev, w, x_dev, (int)m, y_dev, FB200_EPI_NONE, nullptr, nullptr, scratch);
+}
