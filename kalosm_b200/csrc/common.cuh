@@ -66,6 +66,29 @@ int fb200_fail(fb200_device* dev, int code, const char* fmt, ...);
                         cudaGetErrorString(e__), __FILE__, __LINE__);                   \
   } while (0)
 
+// Launches a kernel on the handle's stream, optionally with programmatic stream serialization
+// (the kernel may then start while its predecessor is still running and must execute
+// griddepcontrol.wait before touching anything the predecessor produces).
+template <typename... KArgs, typename... Args>
+inline int fb200_launch(fb200_device* dev, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                        bool pdl, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = dev->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (pdl && dev->pdl) ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess)
+    return fb200_fail(dev, FB200_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(e));
+  dev->launches++;
+  return FB200_OK;
+}
+
 // Makes the handle's device current for the calling thread.
 int fb200_bind(fb200_device* dev);
 // Ensures a scratch buffer of at least `bytes` (never shrinks).

@@ -8,8 +8,11 @@
 //    per SM are in flight without holding registers; the first copies are issued before
 //    griddepcontrol.wait, i.e. under programmatic dependent launch the weights stream in
 //    while the kernel that produces x is still running;
+//  * one launch may carry up to three matrices that share the activation row (the q, k and v
+//    projections), of different quant types;
 //  * the prologue turns x into int8 MMA B operands in shared memory once per CTA: optional
-//    residual add and RMSNorm (so the norm needs no kernel of its own), a power-of-two row
+//    merge of split-KV attention partials, residual add and RMSNorm (so neither the attention
+//    combine nor the norm needs a kernel of its own), a power-of-two row
 //    scale, then FOUR signed 7-bit limbs per element (x/scale = (l0 + l1/2^7 + l2/2^14 +
 //    l3/2^21) / 64 to 2^-27), plus the per-16 sums the offsets of Q4_K/Q4_0/Q6_K need;
 //  * quants stay in the byte domain: one logic op turns four packed nibbles into four u8
@@ -28,26 +31,42 @@
 // (fusor-ml/core/src/composite/rms_norm_fused.rs:10-54) in front of a projection.
 #include "qgemv_common.cuh"
 
+// Optional extras of a single-row product.
+struct fb200_gemv1_extra {
+  const float* att_part = nullptr;  // x = merge of split-KV attention partials [nsplit][heads][d + 2]
+  int att_nsplit = 0, att_heads = 0, att_d = 0;
+  unsigned long long* argmax_key = nullptr;  // running argmax key of the outputs
+};
+
 namespace {
 
-struct Gemv1Args {
+// One weight matrix of a launch. A launch may carry up to three matrices that share the
+// activation row (q, k and v projections), possibly of different quant types.
+struct Seg {
   const uint8_t* w;
+  float* y;
+  int type;      // ggml type id
+  int tg;        // bytes per tile-group
+  int units;     // tiles (or gate/up tile pairs) of this matrix
+  int n_out;
+};
+
+struct Gemv1Args {
+  Seg seg[3];
+  int nseg;
   const float* x;       // [K]
   const float* xres;    // optional [K]: v = x + xres
   const float* norm_w;  // optional [K]: activation = v / sqrt(mean(v^2) + eps) * norm_w
+  // optional: x is the merge of split-KV attention partials [nsplit][heads][D + 2] (o, m, l)
+  const float* att_part;
+  int att_nsplit, att_heads, att_d;
   float eps;
   int K, Kp;            // logical and padded (ngroups * group_elems) inner size
-  float* y;             // [n_out]
   const float* r1;
   const float* r2;
-  int n_out, ngroups, nunits, pair_tile_offset, stages;
+  unsigned long long* argmax_key;  // optional: running (value, index) maximum of seg[0]'s outputs
+  int ngroups, nunits, pair_tile_offset, stages, stride;
   int* status;
-};
-
-template <int TYPE>
-struct G1 {
-  static constexpr int TG = TYPE == FB200_Q4_0 ? 1152 : TYPE == FB200_Q8_0 ? 2176 : TYPE == FB200_Q4_K ? 2304 : 3360;
-  static constexpr int STRIDE = (TG + 127) / 128 * 128;
 };
 
 // Per-lane constants of the scale-group-per-lane mapping.
@@ -210,36 +229,31 @@ __device__ __forceinline__ void group1_q6k(const uint8_t* xl, const float* xs16,
   }
 }
 
-__device__ __forceinline__ float block_reduce(float v, bool is_max, float* sh, int nwarps) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    float u = __shfl_xor_sync(0xFFFFFFFFu, v, o);
-    v = is_max ? fmaxf(v, u) : v + u;
-  }
-  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
-  __syncthreads();
-  float r = sh[0];
-  for (int i = 1; i < nwarps; ++i) r = is_max ? fmaxf(r, sh[i]) : r + sh[i];
-  __syncthreads();
-  return r;
+// Orderable key of (finite value, index): larger value wins, equal values -> larger index
+// (the tie rule of Tensor::top_k_pairs, fusor-ml/fusor/src/lib.rs:432-443). 0 = nothing yet.
+__device__ __forceinline__ unsigned long long argmax_key_of(float v, uint32_t idx) {
+  if (!isfinite(v)) return 0ull;
+  uint32_t b = __float_as_uint(v);
+  b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+  return ((unsigned long long)b << 32) | (unsigned long long)idx;
 }
 
 // EPI: 0 none, 1 residual(s), 2 SwiGLU pair. W = warps per CTA, MINB = CTAs per SM to plan for.
-template <int TYPE, int EPI, int W, int MINB>
+template <int EPI, int W, int MINB>
 __global__ void __launch_bounds__(W * 32, MINB)
 qgemv1_kernel(const Gemv1Args a) {
-  using R = G1<TYPE>;
   constexpr int NP = EPI == 2 ? 2 : 1;
   constexpr int THREADS = W * 32;
   extern __shared__ __align__(128) uint8_t smem[];
   const int S = a.stages;
   uint8_t* ring = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + W * S * R::STRIDE);
-  uint8_t* xl = smem + W * S * R::STRIDE + W * S * 8;  // limbs: 4 bytes per element
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + W * S * a.stride);
+  uint8_t* xl = smem + W * S * a.stride + W * S * 8;  // first raw f32 x, then limbs (4 B / element)
+  float* xf = reinterpret_cast<float*>(xl);
   float* xs16 = reinterpret_cast<float*>(xl + (size_t)a.Kp * 4);  // 2^13 * sum(x/scale) per 16
   float* red = xs16 + a.Kp / 16;   // [NP][W][16]
-  float* tmp = red + NP * W * 16;  // [W] block reductions
-  uint8_t* zero16 = reinterpret_cast<uint8_t*>(tmp + W + (4 - (W & 3)) % 4);  // 16 zero bytes
+  float* tmp = red + NP * W * 16;  // [2 W] block reductions
+  uint8_t* zero16 = reinterpret_cast<uint8_t*>(tmp + 2 * W);  // 16 zero bytes (W is a multiple of 8)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   Lane L;
@@ -250,7 +264,7 @@ qgemv1_kernel(const Gemv1Args a) {
     L.xstep = mine ? 32 : 0;
   }
   if (threadIdx.x < 4) reinterpret_cast<uint32_t*>(zero16)[threadIdx.x] = 0u;
-  uint8_t* my_ring = ring + warp * S * R::STRIDE;
+  uint8_t* my_ring = ring + warp * S * a.stride;
   const uint32_t my_bar = smem_u32(bars + warp * S);
 
   pdl_launch_dependents();
@@ -265,16 +279,24 @@ qgemv1_kernel(const Gemv1Args a) {
   const int gw = a.ngroups > warp ? (a.ngroups - warp + W - 1) / W : 0;
   const int my_units = a.nunits > (int)blockIdx.x ? (a.nunits - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   const int n_items = my_units * NP * gw;
-  int is_tile = blockIdx.x, is_p = 0, is_kk = 0, issued = 0;  // issue-side cursor
+  // unit -> (matrix, tile inside it)
+  auto locate = [&](int unit, int& sidx, int& tile) {
+    sidx = 0; tile = unit;
+    if (a.nseg > 1 && tile >= a.seg[0].units) { tile -= a.seg[0].units; sidx = 1; }
+    if (a.nseg > 2 && sidx == 1 && tile >= a.seg[1].units) { tile -= a.seg[1].units; sidx = 2; }
+  };
+  int is_unit = blockIdx.x, is_p = 0, is_kk = 0, issued = 0;  // issue-side cursor (lane 0)
   auto issue_next = [&](int st) {
-    const int tile = is_tile + is_p * a.pair_tile_offset;
-    const uint8_t* src = a.w + ((size_t)tile * a.ngroups + (warp + W * is_kk)) * R::TG;
-    mbar_expect_tx(my_bar + 8 * st, R::TG);
-    bulk_g2s(smem_u32(my_ring + st * R::STRIDE), src, R::TG, my_bar + 8 * st);
+    int sidx, tile;
+    locate(is_unit, sidx, tile);
+    const Seg& sg = a.seg[sidx];
+    const uint8_t* src = sg.w + ((size_t)(tile + is_p * a.pair_tile_offset) * a.ngroups + (warp + W * is_kk)) * sg.tg;
+    mbar_expect_tx(my_bar + 8 * st, sg.tg);
+    bulk_g2s(smem_u32(my_ring + st * a.stride), src, sg.tg, my_bar + 8 * st);
     ++issued;
     if (++is_kk == gw) {
       is_kk = 0;
-      if (++is_p == NP) { is_p = 0; is_tile += gridDim.x; }
+      if (++is_p == NP) { is_p = 0; is_unit += gridDim.x; }
     }
   };
   if (lane == 0) {
@@ -284,46 +306,73 @@ qgemv1_kernel(const Gemv1Args a) {
   // only weights were touched so far; x comes from the kernel before this one
   pdl_wait();
 
-  // ---- activation prologue: (residual) -> (RMSNorm) -> power-of-two scale -> int8 limbs
+  // ---- activation prologue ------------------------------------------------------------------
+  // pass 1: v = x (+ residual) (or the merged attention partials) -> shared memory as f32;
+  //         sum of squares and max |v * norm_w| in one block reduction
   float ss = 0.f, amax = 0.f;
-  for (int k = threadIdx.x; k < a.K; k += THREADS) {
-    float v = a.x[k];
-    if (a.xres) v += a.xres[k];
-    ss = fmaf(v, v, ss);
-    if (!a.norm_w) amax = fmaxf(amax, fabsf(v));
+  for (int k = threadIdx.x; k < a.Kp; k += THREADS) {
+    float v = 0.f;
+    if (k < a.K) {
+      if (a.att_part) {
+        // merge of split-KV partials, as attn_combine_kernel: weights exp(m_s - max m) in
+        // split order, normalised by the merged sum
+        const int head = k / a.att_d, e = k - head * a.att_d;
+        const int pd = a.att_d + 2;
+        float mx = -INFINITY;
+        for (int s = 0; s < a.att_nsplit; ++s) mx = fmaxf(mx, a.att_part[((size_t)s * a.att_heads + head) * pd + a.att_d]);
+        float l = 0.f, o = 0.f;
+        for (int s = 0; s < a.att_nsplit; ++s) {
+          const float* pp = a.att_part + ((size_t)s * a.att_heads + head) * pd;
+          const float m = pp[a.att_d];
+          const float wgt = (m == -INFINITY) ? 0.f : __expf(m - mx);
+          l = fmaf(pp[a.att_d + 1], wgt, l);
+          o = fmaf(pp[e], wgt, o);
+        }
+        v = l > 0.f ? o / l : 0.f;
+      } else {
+        v = a.x[k];
+        if (a.xres) v += a.xres[k];
+      }
+      ss = fmaf(v, v, ss);
+      amax = fmaxf(amax, fabsf(a.norm_w ? v * a.norm_w[k] : v));
+    }
+    xf[k] = v;
   }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+  }
+  if (lane == 0) { tmp[warp] = ss; tmp[W + warp] = amax; }
+  __syncthreads();
+  ss = 0.f; amax = 0.f;
+  for (int i = 0; i < W; ++i) { ss += tmp[i]; amax = fmaxf(amax, tmp[W + i]); }
   float rms = 1.f;
   if (a.norm_w) {
     // rms_norm_fused_cpu_impl, fusor-ml/fusor/src/composite/normalization.rs:404-461
-    ss = block_reduce(ss, false, tmp, W);
     rms = sqrtf(ss / (float)a.K + a.eps);
-    for (int k = threadIdx.x; k < a.K; k += THREADS) {
-      float v = a.x[k];
-      if (a.xres) v += a.xres[k];
-      amax = fmaxf(amax, fabsf((v / rms) * a.norm_w[k]));
-    }
+    amax = amax / rms * 1.0000005f;  // bound of |(v / rms) * w| with rounding slack
   }
-  amax = block_reduce(amax, true, tmp, W);
   int ex = 0;
   if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &ex);  // amax = f * 2^ex, f in [0.5, 1)
   const float inv64 = ldexpf(64.0f, -ex);               // x * inv64 in (-64, 64)
   const float out_scale = ldexpf(1.0f, ex - 13);        // 2^ex / (64 * 128)
+  // pass 2: each thread turns whole 8-element blocks, in place, into four int8 limbs per element
   const int nblk = a.Kp >> 3;
   for (int b0 = 0; b0 < nblk; b0 += THREADS) {
-    const int kb = b0 + threadIdx.x;  // Kp / 8 is a multiple of 32: whole warps stay together
+    const int kb = b0 + threadIdx.x;
     uint32_t lw[4][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}, {0u, 0u}};
     float sum = 0.f;
     if (kb < nblk) {
+      const float4 va = *reinterpret_cast<const float4*>(xf + kb * 8);
+      const float4 vb = *reinterpret_cast<const float4*>(xf + kb * 8 + 4);
+      const float vin[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int k = kb * 8 + i;
-        float v = 0.f;
-        if (k < a.K) {
-          v = a.x[k];
-          if (a.xres) v += a.xres[k];
-          if (a.norm_w) v = (v / rms) * a.norm_w[k];
-          v *= inv64;
-        }
+        float v = vin[i];
+        if (a.norm_w && k < a.K) v = (v / rms) * a.norm_w[k];
+        v *= inv64;
         sum += v;
         // four signed limbs; every remainder is exact in fp32
         float l0 = rintf(v), r = (v - l0) * 128.0f;
@@ -352,18 +401,21 @@ qgemv1_kernel(const Gemv1Args a) {
   uint32_t phase = 0;
   for (int j = 0; j < my_units; ++j) {
     const int unit = (int)blockIdx.x + j * (int)gridDim.x;
+    int sidx, tile;
+    locate(unit, sidx, tile);
+    const Seg& sg = a.seg[sidx];
     if (j > 0) __syncthreads();  // the previous unit's reduction has read `red`
 #pragma unroll
     for (int p = 0; p < NP; ++p) {
       float acc_g = 0.f, acc_g8 = 0.f;
       for (int kk = 0; kk < gw; ++kk, ++item) {
         mbar_wait(my_bar + 8 * st, phase, a.status);
-        const uint8_t* tg = my_ring + st * R::STRIDE;
+        const uint8_t* tg = my_ring + st * a.stride;
         const int kg = warp + W * kk;
-        if (TYPE == FB200_Q4_0) group1_q4_0(xl, xs16, tg, kg, L, acc_g, acc_g8);
-        else if (TYPE == FB200_Q8_0) group1_q8_0(xl, tg, kg, L, acc_g, acc_g8);
-        else if (TYPE == FB200_Q4_K) group1_q4k(xl, xs16, tg, kg, L, acc_g, acc_g8);
-        else group1_q6k(xl, xs16, tg, kg, L, acc_g, acc_g8);
+        if (sg.type == FB200_Q4_K) group1_q4k(xl, xs16, tg, kg, L, acc_g, acc_g8);
+        else if (sg.type == FB200_Q6_K) group1_q6k(xl, xs16, tg, kg, L, acc_g, acc_g8);
+        else if (sg.type == FB200_Q8_0) group1_q8_0(xl, tg, kg, L, acc_g, acc_g8);
+        else group1_q4_0(xl, xs16, tg, kg, L, acc_g, acc_g8);
         // Every lane has read the stage (its loads precede this barrier in program order and
         // shared loads complete long before a refill from global memory can land).
         __syncwarp();
@@ -383,8 +435,8 @@ qgemv1_kernel(const Gemv1Args a) {
     __syncthreads();
     if (threadIdx.x < 16) {
       const int r = threadIdx.x;
-      const int n = unit * 16 + r;
-      if (n < a.n_out) {
+      const int n = tile * 16 + r;
+      if (n < sg.n_out) {
         float v[NP];
 #pragma unroll
         for (int p = 0; p < NP; ++p) {
@@ -403,7 +455,8 @@ qgemv1_kernel(const Gemv1Args a) {
         } else {
           out = v[0];
         }
-        a.y[n] = out;
+        sg.y[n] = out;
+        if (a.argmax_key && sidx == 0) atomicMax(a.argmax_key, argmax_key_of(out, (uint32_t)n));
       }
     }
   }
@@ -411,16 +464,16 @@ qgemv1_kernel(const Gemv1Args a) {
 
 constexpr int SMEM_LIMIT = 227 * 1024;
 
-template <int TYPE, int EPI, int W>
-size_t gemv1_smem(int stages, int kp) {
+template <int EPI, int W>
+size_t gemv1_smem(int stages, int stride, int kp) {
   constexpr int NP = EPI == 2 ? 2 : 1;
-  return (size_t)W * stages * G1<TYPE>::STRIDE + (size_t)W * stages * 8 + (size_t)kp * 4 +
-         (size_t)kp / 16 * 4 + (size_t)NP * W * 16 * 4 + (size_t)W * 4 + 96;
+  return (size_t)W * stages * stride + (size_t)W * stages * 8 + (size_t)kp * 4 + (size_t)kp / 16 * 4 +
+         (size_t)NP * W * 16 * 4 + (size_t)2 * W * 4 + 16 + 64;
 }
 
-template <int TYPE, int EPI, int W, int MINB>
+template <int EPI, int W, int MINB>
 int launch_w(fb200_device* dev, Gemv1Args& a) {
-  auto kern = qgemv1_kernel<TYPE, EPI, W, MINB>;
+  auto kern = qgemv1_kernel<EPI, W, MINB>;
   static bool configured[64] = {false};
   if (!configured[dev->ordinal & 63]) {
     FB_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
@@ -431,7 +484,7 @@ int launch_w(fb200_device* dev, Gemv1Args& a) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3(W * 32);
-  cfg.dynamicSmemBytes = gemv1_smem<TYPE, EPI, W>(a.stages, a.Kp);
+  cfg.dynamicSmemBytes = gemv1_smem<EPI, W>(a.stages, a.stride, a.Kp);
   cfg.stream = dev->stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -444,27 +497,23 @@ int launch_w(fb200_device* dev, Gemv1Args& a) {
 }
 
 // Shared memory per SM is split between the activation limbs (4 B per element of K, one copy
-// per CTA, built by every CTA in its prologue) and the weight rings: 32 resident warps per SM
-// either way, in as few CTAs as the limbs allow.
-template <int TYPE, int EPI>
+// per CTA, built by every CTA in its prologue) and the weight rings. More, smaller CTAs give
+// deeper rings per warp and more independent tiles in flight; larger K forces fewer CTAs.
+template <int EPI>
 int launch_cfg(fb200_device* dev, Gemv1Args& a) {
   const int per_sm = SMEM_LIMIT - 2048;
   auto fits = [&](size_t need, int ctas) { return (need + 1024) * ctas <= (size_t)per_sm; };
-  // two 16-warp CTAs per SM while two copies of the limbs fit, else one 32-warp CTA
   for (int s = 3; s >= 2; --s)
-    if (fits(gemv1_smem<TYPE, EPI, 16>(s, a.Kp), 2)) { a.stages = s; return launch_w<TYPE, EPI, 16, 2>(dev, a); }
+    if (fits(gemv1_smem<EPI, 8>(s, a.stride, a.Kp), 4)) { a.stages = s; return launch_w<EPI, 8, 4>(dev, a); }
+  for (int s = 3; s >= 2; --s)
+    if (fits(gemv1_smem<EPI, 8>(s, a.stride, a.Kp), 3)) { a.stages = s; return launch_w<EPI, 8, 3>(dev, a); }
+  for (int s = 3; s >= 2; --s)
+    if (fits(gemv1_smem<EPI, 16>(s, a.stride, a.Kp), 2)) { a.stages = s; return launch_w<EPI, 16, 2>(dev, a); }
   for (int s = 2; s >= 1; --s)
-    if (fits(gemv1_smem<TYPE, EPI, 32>(s, a.Kp), 1)) { a.stages = s; return launch_w<TYPE, EPI, 32, 1>(dev, a); }
+    if (fits(gemv1_smem<EPI, 32>(s, a.stride, a.Kp), 1)) { a.stages = s; return launch_w<EPI, 32, 1>(dev, a); }
   for (int s = 2; s >= 1; --s)
-    if (fits(gemv1_smem<TYPE, EPI, 16>(s, a.Kp), 1)) { a.stages = s; return launch_w<TYPE, EPI, 16, 1>(dev, a); }
+    if (fits(gemv1_smem<EPI, 16>(s, a.stride, a.Kp), 1)) { a.stages = s; return launch_w<EPI, 16, 1>(dev, a); }
   return fb200_fail(dev, FB200_ERR_CAPACITY, "qgemv1: K = %d does not fit in shared memory", a.K);
-}
-
-template <int TYPE>
-int launch_epi1(fb200_device* dev, Gemv1Args& a, int epi) {
-  if (epi == FB200_EPI_SWIGLU) return launch_cfg<TYPE, 2>(dev, a);
-  if (epi == FB200_EPI_RESIDUAL) return launch_cfg<TYPE, 1>(dev, a);
-  return launch_cfg<TYPE, 0>(dev, a);
 }
 
 }  // namespace
@@ -477,27 +526,51 @@ bool fb200_qgemv1_fits(const fb200_qmatrix* w) {
   return kp * 4 + kp / 4 + 16 * 3456 + 8192 <= (uint64_t)SMEM_LIMIT - 2048;
 }
 
-// y[n_out] = epilogue(W . act(x)); act = optional residual add + RMSNorm (norm_w != null).
+// ys[i][n_i] = epilogue(W_i . act(x)) for up to three matrices that share K and the group size;
+// act = optional residual add + RMSNorm (norm_w != null). Epilogues apply to one matrix only.
+int fb200_qgemv1_multi(fb200_device* dev, const fb200_qmatrix* const* ws, float* const* ys, int nw,
+                       const float* x, const float* xres, const float* norm_w, float eps, int epi,
+                       const float* r1, const float* r2, const fb200_gemv1_extra* extra) {
+  if (nw < 1 || nw > 3 || (epi != FB200_EPI_NONE && nw != 1))
+    return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "qgemv1: %d matrices with epilogue %d", nw, epi);
+  Gemv1Args a = {};
+  TileGeom geo0;
+  tile_geom(ws[0]->type, &geo0);
+  a.nseg = nw;
+  a.stride = 0;
+  a.nunits = 0;
+  for (int i = 0; i < nw; ++i) {
+    TileGeom geo;
+    if (!tile_geom(ws[i]->type, &geo) || geo.group_elems != geo0.group_elems || ws[i]->k != ws[0]->k)
+      return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "qgemv1: matrices of one launch must share K and the group size");
+    a.seg[i].w = ws[i]->data; a.seg[i].y = ys[i]; a.seg[i].type = (int)ws[i]->type; a.seg[i].tg = geo.tg_bytes;
+    a.seg[i].units = ws[i]->ntiles; a.seg[i].n_out = (int)ws[i]->n;
+    a.nunits += ws[i]->ntiles;
+    const int st = (geo.tg_bytes + 127) / 128 * 128;
+    if (st > a.stride) a.stride = st;
+  }
+  a.x = x; a.xres = xres; a.norm_w = norm_w; a.eps = eps;
+  a.K = (int)ws[0]->k; a.Kp = ws[0]->ngroups * geo0.group_elems;
+  a.r1 = r1; a.r2 = r2;
+  a.ngroups = ws[0]->ngroups; a.pair_tile_offset = 0;
+  a.stages = 2; a.status = dev->status;
+  if (extra) {
+    a.att_part = extra->att_part; a.att_nsplit = extra->att_nsplit; a.att_heads = extra->att_heads;
+    a.att_d = extra->att_d; a.argmax_key = extra->argmax_key;
+  }
+  if (epi == FB200_EPI_SWIGLU) {
+    a.seg[0].units = ws[0]->ntiles / 2;
+    a.nunits = a.seg[0].units;
+    a.seg[0].n_out = (int)(ws[0]->n / 2);
+    a.pair_tile_offset = ws[0]->ntiles / 2;
+    return launch_cfg<2>(dev, a);
+  }
+  if (epi == FB200_EPI_RESIDUAL) return launch_cfg<1>(dev, a);
+  return launch_cfg<0>(dev, a);
+}
+
 int fb200_qgemv1(fb200_device* dev, const fb200_qmatrix* w, const float* x, const float* xres,
                  const float* norm_w, float eps, float* y, int epi, const float* r1,
                  const float* r2) {
-  TileGeom geo;
-  tile_geom(w->type, &geo);
-  Gemv1Args a;
-  a.w = w->data; a.x = x; a.xres = xres; a.norm_w = norm_w; a.eps = eps;
-  a.K = (int)w->k; a.Kp = w->ngroups * geo.group_elems;
-  a.y = y; a.r1 = r1; a.r2 = r2;
-  a.ngroups = w->ngroups; a.nunits = w->ntiles; a.n_out = (int)w->n; a.pair_tile_offset = 0;
-  a.stages = 2; a.status = dev->status;
-  if (epi == FB200_EPI_SWIGLU) {
-    a.nunits = w->ntiles / 2;
-    a.n_out = (int)(w->n / 2);
-    a.pair_tile_offset = w->ntiles / 2;
-  }
-  switch (w->type) {
-    case FB200_Q4_0: return launch_epi1<FB200_Q4_0>(dev, a, epi);
-    case FB200_Q8_0: return launch_epi1<FB200_Q8_0>(dev, a, epi);
-    case FB200_Q4_K: return launch_epi1<FB200_Q4_K>(dev, a, epi);
-    default: return launch_epi1<FB200_Q6_K>(dev, a, epi);
-  }
+  return fb200_qgemv1_multi(dev, &w, &y, 1, x, xres, norm_w, eps, epi, r1, r2, nullptr);
 }
