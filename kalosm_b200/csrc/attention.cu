@@ -39,7 +39,20 @@ struct AttnArgs {
   int mask_kind;       // 0 none, 1 causal, 2 [Sq,Skv], 3 [B,Skv]
   int nsplit, row_tiles;  // row tiles per (b, kv head)
   float scale;
+  // Fused single-position mode (sq == 1, one row tile): q is rotated here, and the CTA whose key
+  // range holds the new position rotates k_new, rounds k_new / v_new to fp16 and appends them
+  // to the cache before attending. k_new, v_new are [B, Hkv, D] f32; tables [ctx, D/2].
+  const float* k_new;
+  const float* v_new;
+  __half* k_cache_w;
+  __half* v_cache_w;
+  const float* rope_cos;
+  const float* rope_sin;
+  int always_partial;  // write (o, m, l) partials even for a single split
 };
+
+__device__ __forceinline__ void att_pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void att_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 template <int D>
 __global__ void __launch_bounds__(ATT_THREADS)
@@ -54,6 +67,8 @@ attn_rows_kernel(const AttnArgs a) {
   static_assert(D == 64 || D == 128, "head_dim 64 or 128");
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  att_pdl_launch();
+  att_pdl_wait();
   const int skv = a.skv_dev ? (*a.skv_dev + a.sq) : a.skv;
   int bid = blockIdx.x;
   const int split = bid % a.nsplit; bid /= a.nsplit;
@@ -75,7 +90,17 @@ attn_rows_kernel(const AttnArgs a) {
   for (int i = tid; i < ROWS * D; i += ATT_THREADS) {
     int r = i / D, e = i % D;
     float v = 0.f;
-    if (r < nrows) v = a.q[row_index(r) * D + e];
+    if (r < nrows) {
+      v = a.q[row_index(r) * D + e];
+      if (a.rope_cos) {
+        // interleaved RoPE at the new position (fusor-ml/fusor/src/composite/rope.rs:77-108)
+        const float other = a.q[row_index(r) * D + (e ^ 1)];
+        const float c = a.rope_cos[(size_t)(skv - 1) * (D / 2) + (e >> 1)];
+        const float sn = a.rope_sin[(size_t)(skv - 1) * (D / 2) + (e >> 1)];
+        v = (e & 1) ? __fadd_rn(__fmul_rn(other, sn), __fmul_rn(v, c))
+                    : __fsub_rn(__fmul_rn(v, c), __fmul_rn(other, sn));
+      }
+    }
     qs[r][e] = v;
   }
   if (tid < ROWS) { row_m[tid] = -INFINITY; row_l[tid] = 0.f; }
@@ -92,6 +117,22 @@ attn_rows_kernel(const AttnArgs a) {
 
   const __half* kb = a.k + ((size_t)bi * a.hkv + kvh) * (size_t)a.cap * D;
   const __half* vb = a.v + ((size_t)bi * a.hkv + kvh) * (size_t)a.cap * D;
+  if (a.k_new && kbeg <= skv - 1 && skv - 1 < kend) {
+    // append the new position (KvCache::append, fusor-ml/fusor/src/cache/kv_cache.rs:50-62)
+    const int pos = skv - 1;
+    const float* kn = a.k_new + ((size_t)bi * a.hkv + kvh) * D;
+    const float* vn = a.v_new + ((size_t)bi * a.hkv + kvh) * D;
+    __half* kw = a.k_cache_w + (((size_t)bi * a.hkv + kvh) * (size_t)a.cap + pos) * D;
+    __half* vw = a.v_cache_w + (((size_t)bi * a.hkv + kvh) * (size_t)a.cap + pos) * D;
+    for (int p = tid; p < D / 2; p += ATT_THREADS) {
+      const float c = a.rope_cos[(size_t)pos * (D / 2) + p], sn = a.rope_sin[(size_t)pos * (D / 2) + p];
+      const float x0 = kn[2 * p], x1 = kn[2 * p + 1];
+      const float y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn));
+      const float y1 = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c));
+      *reinterpret_cast<__half2*>(kw + 2 * p) = __floats2half2_rn(y0, y1);
+      *reinterpret_cast<__half2*>(vw + 2 * p) = __floats2half2_rn(vn[2 * p], vn[2 * p + 1]);
+    }
+  }
 
   float o[ROWS][DV];
 #pragma unroll
@@ -113,7 +154,7 @@ attn_rows_kernel(const AttnArgs a) {
         const uint4* kp = reinterpret_cast<const uint4*>(kb + (size_t)(c0 + j) * D + sub * DL);
 #pragma unroll
         for (int v8 = 0; v8 < DL / 8; ++v8) {
-          uint4 raw = __ldg(kp + v8);
+          uint4 raw = kp[v8];
           const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
           float kf[8];
 #pragma unroll
@@ -190,12 +231,12 @@ attn_rows_kernel(const AttnArgs a) {
       float vf[DV];
       const __half* vp = vb + (size_t)(c0 + j) * D + lane * DV;
       if constexpr (DV == 4) {
-        uint2 raw = __ldg(reinterpret_cast<const uint2*>(vp));
+        uint2 raw = *reinterpret_cast<const uint2*>(vp);
         const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
         float2 f0 = __half22float2(h2[0]), f1 = __half22float2(h2[1]);
         vf[0] = f0.x; vf[1] = f0.y; vf[2] = f1.x; vf[3] = f1.y;
       } else {
-        float2 f0 = __half22float2(__ldg(reinterpret_cast<const __half2*>(vp)));
+        float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(vp));
         vf[0] = f0.x; vf[1] = f0.y;
       }
 #pragma unroll
@@ -221,7 +262,7 @@ attn_rows_kernel(const AttnArgs a) {
 #pragma unroll
     for (int w = 0; w < ATT_THREADS / 32; ++w) s += ored[w][r][e];
     const size_t grow = row_index(r);
-    if (a.nsplit == 1) {
+    if (a.nsplit == 1 && !a.always_partial) {
       const float l = row_l[r];
       a.out[grow * D + e] = l > 0.f ? s / l : 0.f;
     } else {
@@ -304,7 +345,7 @@ int fb200_launch_attention(fb200_device* dev, const float* q, const __half* k, c
                            float* part, int nsplit, int bshd) {
   if (h % hkv) return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "attention: %d heads not divisible by %d kv heads", h, hkv);
   if (d != 64 && d != 128) return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "attention: head_dim %d (64 or 128 supported)", d);
-  AttnArgs a;
+  AttnArgs a = {};
   a.q = q; a.k = k; a.v = v; a.out = out; a.part = part; a.mask = mask; a.skv_dev = skv_dev;
   a.b = b; a.h = h; a.hkv = hkv; a.sq = sq; a.skv = skv; a.cap = cap; a.groups = h / hkv;
   a.mask_kind = mask_kind; a.nsplit = nsplit; a.scale = scale; a.bshd = bshd;
@@ -312,9 +353,10 @@ int fb200_launch_attention(fb200_device* dev, const float* q, const __half* k, c
   const long grid = (long)b * hkv * a.row_tiles * nsplit;
   if (grid <= 0) return FB200_OK;
   if (grid >= (1L << 31)) return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "attention: grid too large");
-  if (d == 128) attn_rows_kernel<128><<<(unsigned)grid, ATT_THREADS, 0, dev->stream>>>(a);
-  else attn_rows_kernel<64><<<(unsigned)grid, ATT_THREADS, 0, dev->stream>>>(a);
-  FB_LAUNCH_CHECK(dev);
+  int rc;
+  if (d == 128) rc = fb200_launch(dev, attn_rows_kernel<128>, dim3((unsigned)grid), dim3(ATT_THREADS), 0, false, a);
+  else rc = fb200_launch(dev, attn_rows_kernel<64>, dim3((unsigned)grid), dim3(ATT_THREADS), 0, false, a);
+  if (rc) return rc;
   if (nsplit > 1) {
     const size_t rows = (size_t)b * h * sq;
     if (d == 128) attn_combine_kernel<128><<<(unsigned)rows, 128, 0, dev->stream>>>(part, nsplit, rows, out);
@@ -322,6 +364,28 @@ int fb200_launch_attention(fb200_device* dev, const float* q, const __half* k, c
     FB_LAUNCH_CHECK(dev);
   }
   return FB200_OK;
+}
+
+// One new position per sequence: RoPE(q), RoPE(k) + fp16 append, split-KV attention over the
+// cache. Writes (o, m, l) partials [nsplit][B * H][D + 2] for the consumer to merge. Needs
+// H / Hkv <= 8 (one row tile per KV head). The position is read from pos_dev.
+int fb200_launch_attention_decode(fb200_device* dev, const float* q, const float* k_new,
+                                  const float* v_new, __half* kc, __half* vc, int b, int h, int hkv,
+                                  const int* pos_dev, int cap, int d, float scale,
+                                  const float* rope_cos, const float* rope_sin, float* part,
+                                  int nsplit) {
+  if (h % hkv || h / hkv > ROWS || (d != 64 && d != 128))
+    return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "attention_decode: unsupported head layout");
+  AttnArgs a = {};
+  a.q = q; a.k = kc; a.v = vc; a.out = nullptr; a.part = part; a.mask = nullptr; a.skv_dev = pos_dev;
+  a.b = b; a.h = h; a.hkv = hkv; a.sq = 1; a.skv = 0; a.cap = cap; a.groups = h / hkv;
+  a.mask_kind = 0; a.nsplit = nsplit; a.scale = scale; a.bshd = 1;
+  a.row_tiles = 1;
+  a.k_new = k_new; a.v_new = v_new; a.k_cache_w = kc; a.v_cache_w = vc;
+  a.rope_cos = rope_cos; a.rope_sin = rope_sin; a.always_partial = 1;
+  const unsigned grid = (unsigned)(b * hkv * nsplit);
+  if (d == 128) return fb200_launch(dev, attn_rows_kernel<128>, dim3(grid), dim3(ATT_THREADS), 0, true, a);
+  return fb200_launch(dev, attn_rows_kernel<64>, dim3(grid), dim3(ATT_THREADS), 0, true, a);
 }
 
 int fb200_launch_kv_append(fb200_device* dev, const float* k, const float* v, __half* kc, __half* vc,

@@ -27,6 +27,20 @@ int fb200_launch_attention(fb200_device* dev, const float* q, const __half* k, c
                            int d, float scale, const float* mask, int mask_kind, float* out,
                            float* part, int nsplit, int bshd);
 int fb200_attention_nsplit(const fb200_device* dev, int b, int hkv, int groups, int sq, int skv);
+int fb200_launch_attention_decode(fb200_device* dev, const float* q, const float* k_new,
+                                  const float* v_new, __half* kc, __half* vc, int b, int h, int hkv,
+                                  const int* pos_dev, int cap, int d, float scale,
+                                  const float* rope_cos, const float* rope_sin, float* part,
+                                  int nsplit);
+struct fb200_gemv1_extra {
+  const float* att_part = nullptr;
+  int att_nsplit = 0, att_heads = 0, att_d = 0;
+  unsigned long long* argmax_key = nullptr;
+};
+int fb200_qgemv1_multi(fb200_device* dev, const fb200_qmatrix* const* ws, float* const* ys, int nw,
+                       const float* x, const float* xres, const float* norm_w, float eps, int epi,
+                       const float* r1, const float* r2, const fb200_gemv1_extra* extra);
+bool fb200_qgemv1_fits(const fb200_qmatrix* w);
 int fb200_attention_scratch_bytes(int b, int h, int sq, int d, int nsplit, size_t* out);
 
 namespace {
@@ -83,11 +97,20 @@ __global__ void rope_append_kernel(float* __restrict__ q, const float* __restric
 }
 
 // After a greedy step: record the new ids, feed them back, advance the position.
-__global__ void advance_kernel(const uint32_t* __restrict__ next, uint32_t* __restrict__ ids,
+__global__ void advance_kernel(uint32_t* __restrict__ next, uint32_t* __restrict__ ids,
                                uint32_t* __restrict__ hist, int* pos_dev, int* step_dev, int batch,
-                               int max_steps, int advance) {
+                               int max_steps, int advance, unsigned long long* argmax_key) {
   const int b = threadIdx.x;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int step = *step_dev;
+  if (argmax_key && b == 0) {
+    // the output projection kept a running (value, index) maximum; 0 means no finite logit
+    const unsigned long long key = *argmax_key;
+    next[0] = key ? (uint32_t)(key & 0xFFFFFFFFull) : 0xFFFFFFFFu;
+    *argmax_key = 0ull;
+  }
+  __syncthreads();
   if (b < batch) {
     ids[b] = next[b];
     if (hist && step < max_steps) hist[(size_t)b * max_steps + step] = next[b];
@@ -119,6 +142,8 @@ struct fb200_llama {
   uint32_t *ids = nullptr, *next = nullptr, *hist = nullptr;
   int hist_cap = 0;
   int *pos_dev = nullptr, *step_dev = nullptr;
+  unsigned long long* argmax_key = nullptr;
+  bool used_key = false;  // the last forward pass left its greedy id in argmax_key, not in next
   // CUDA graph of a single-token step, per batch size
   cudaGraphExec_t graph_exec = nullptr;
   int graph_batch = 0;
@@ -183,9 +208,81 @@ int finalize(fb200_llama* m) {
   return FB200_OK;
 }
 
+// Single sequence, single new position: five kernels per layer, all launched with programmatic
+// stream serialization so that each product streams its weights into shared memory while its
+// predecessor is still running:
+//   q, k, v projections in one launch, RMSNorm in its prologue
+//   RoPE(q, k) + fp16 KV append + split-KV attention (partials)
+//   output projection, merging the attention partials in its prologue
+//   gate/up projection with SwiGLU epilogue, residual add + RMSNorm in its prologue
+//   down projection with both residual adds in its epilogue
+// The output head keeps a running argmax key, so greedy decoding needs no argmax kernel.
+bool decode1_supported(const fb200_llama* m) {
+  const auto& c = m->cfg;
+  if (c.n_head / c.n_kv_head > 8) return false;
+  for (const auto& L : m->layers) {
+    if (!L.gate_up) return false;
+    const fb200_qmatrix* qs[] = {L.wq, L.wk, L.wv, L.wo, L.gate_up, L.down};
+    for (auto* q : qs) if (!q->tiled || !fb200_qgemv1_fits(q)) return false;
+    TileGeom a, b, cc;
+    tile_geom(L.wq->type, &a); tile_geom(L.wk->type, &b); tile_geom(L.wv->type, &cc);
+    if (a.group_elems != b.group_elems || a.group_elems != cc.group_elems) return false;
+  }
+  const fb200_qmatrix* ow = m->output ? m->output : m->token_embd;
+  return ow->tiled && fb200_qgemv1_fits(ow);
+}
+
+int run_decode1(fb200_llama* m) {
+  fb200_device* dev = m->dev;
+  const auto& c = m->cfg;
+  const int H = c.n_head, HK = c.n_kv_head, D = c.head_dim;
+  int rc;
+  if ((rc = fb200_embedding_lookup(dev, m->token_embd, m->ids, 1, m->x))) return rc;
+  const float scale = (float)(1.0 / sqrt((double)D));
+  int nsplit = (c.max_seq_len + 127) / 128;
+  if (nsplit > 32) nsplit = 32;
+  if (nsplit < 1) nsplit = 1;
+  if ((size_t)nsplit * H * (D + 2) * sizeof(float) > m->att_part_bytes)
+    return fb200_fail(dev, FB200_ERR_CAPACITY, "llama: attention scratch too small");
+  for (int li = 0; li < c.n_layer; ++li) {
+    LayerW& L = m->layers[li];
+    const fb200_qmatrix* qkv[3] = {L.wq, L.wk, L.wv};
+    float* qkv_out[3] = {m->q, m->k, m->v};
+    if ((rc = fb200_qgemv1_multi(dev, qkv, qkv_out, 3, m->x, nullptr, L.attn_norm, c.rms_eps, FB200_EPI_NONE,
+                                 nullptr, nullptr, nullptr))) return rc;
+    if ((rc = fb200_launch_attention_decode(dev, m->q, m->k, m->v, L.kc, L.vc, 1, H, HK, m->pos_dev,
+                                            c.max_seq_len, D, scale, m->rope_cos, m->rope_sin, m->att_part,
+                                            nsplit))) return rc;
+    fb200_gemv1_extra ex;
+    ex.att_part = m->att_part; ex.att_nsplit = nsplit; ex.att_heads = H; ex.att_d = D;
+    const fb200_qmatrix* wo = L.wo;
+    float* wo_out = m->attn_out;
+    if ((rc = fb200_qgemv1_multi(dev, &wo, &wo_out, 1, nullptr, nullptr, nullptr, 0.f, FB200_EPI_NONE, nullptr,
+                                 nullptr, &ex))) return rc;
+    const fb200_qmatrix* gu = L.gate_up;
+    float* gu_out = m->hbuf;
+    if ((rc = fb200_qgemv1_multi(dev, &gu, &gu_out, 1, m->attn_out, m->x, L.ffn_norm, c.rms_eps,
+                                 FB200_EPI_SWIGLU, nullptr, nullptr, nullptr))) return rc;
+    const fb200_qmatrix* dn = L.down;
+    float* dn_out = m->x;
+    if ((rc = fb200_qgemv1_multi(dev, &dn, &dn_out, 1, m->hbuf, nullptr, nullptr, 0.f, FB200_EPI_RESIDUAL,
+                                 m->attn_out, m->x, nullptr))) return rc;
+  }
+  const fb200_qmatrix* ow = m->output ? m->output : m->token_embd;
+  float* lg = m->logits;
+  fb200_gemv1_extra ex;
+  ex.argmax_key = m->argmax_key;
+  if ((rc = fb200_qgemv1_multi(dev, &ow, &lg, 1, m->x, nullptr, m->output_norm, c.rms_eps, FB200_EPI_NONE,
+                               nullptr, nullptr, &ex))) return rc;
+  m->used_key = true;
+  return FB200_OK;
+}
+
 // One forward pass over `seq` new positions per batch row; ids are already in m->ids.
 // Leaves logits [batch, vocab] in m->logits and the greedy ids in m->next.
 int run_forward(fb200_llama* m, int batch, int seq) {
+  m->used_key = false;
+  if (batch == 1 && seq == 1 && decode1_supported(m)) return run_decode1(m);
   fb200_device* dev = m->dev;
   const auto& c = m->cfg;
   const size_t rows = (size_t)batch * seq;
@@ -257,10 +354,10 @@ int run_forward(fb200_llama* m, int batch, int seq) {
 }
 
 int launch_advance(fb200_llama* m, int batch, int advance, bool record) {
-  advance_kernel<<<1, 64 > batch ? 64 : ((batch + 31) / 32) * 32, 0, m->dev->stream>>>(
-      m->next, m->ids, record ? m->hist : nullptr, m->pos_dev, m->step_dev, batch, m->hist_cap, advance);
-  FB_LAUNCH_CHECK(m->dev);
-  return FB200_OK;
+  const unsigned threads = 64 > batch ? 64 : ((batch + 31) / 32) * 32;
+  unsigned long long* key = m->used_key ? m->argmax_key : nullptr;
+  return fb200_launch(m->dev, advance_kernel, dim3(1), dim3(threads), 0, m->used_key, m->next, m->ids,
+                      record ? m->hist : nullptr, m->pos_dev, m->step_dev, batch, m->hist_cap, advance, key);
 }
 
 // Captures embed -> layers -> logits -> argmax -> advance for one token per batch row.
@@ -271,6 +368,7 @@ int ensure_graph(fb200_llama* m, int batch) {
   // make sure every lazily grown scratch buffer already has its final size
   int rc = run_forward(m, batch, 1);
   if (rc) return rc;
+  FB_CUDA(dev, cudaMemsetAsync(m->argmax_key, 0, 8, dev->stream));  // the warm-up pass left its maximum there
   FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
   const uint64_t launches_before = dev->launches;
   cudaGraph_t graph = nullptr;
@@ -333,6 +431,8 @@ int fb200_llama_create(fb200_device* dev, const fb200_llama_config* cfg, fb200_l
   FB_CUDA(dev, cudaMalloc(&m->hist, (size_t)c.max_batch * m->hist_cap * 4));
   FB_CUDA(dev, cudaMemset(m->pos_dev, 0, 4));
   FB_CUDA(dev, cudaMemset(m->step_dev, 0, 4));
+  FB_CUDA(dev, cudaMalloc(&m->argmax_key, 8));
+  FB_CUDA(dev, cudaMemset(m->argmax_key, 0, 8));
   // attention split scratch: the largest a forward pass can ask for is bounded by 64 splits of
   // a single-token step or one split set of a whole-context prefill
   size_t a1, a2;
@@ -363,7 +463,7 @@ int fb200_llama_free(fb200_llama* m) {
   if (m->output) fb200_qmatrix_free(m->output);
   void* bufs[] = {m->output_norm, m->rope_cos, m->rope_sin, m->x, m->xn, m->q, m->k, m->v, m->att,
                   m->attn_out, m->hbuf, m->gbuf, m->last, m->logits, m->att_part, m->ids, m->next,
-                  m->hist, m->pos_dev, m->step_dev};
+                  m->hist, m->pos_dev, m->step_dev, m->argmax_key};
   for (void* b : bufs) if (b) cudaFree(b);
   delete m;
   return FB200_OK;
