@@ -49,6 +49,9 @@ struct AttnArgs {
   const float* rope_cos;
   const float* rope_sin;
   int always_partial;  // write (o, m, l) partials even for a single split
+  // Merge by the last split to finish (fused mode): per (batch, kv head) arrival counters,
+  // zero before the launch and reset by the merging CTA.
+  int* done;
 };
 
 __device__ __forceinline__ void att_pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -271,6 +274,39 @@ attn_rows_kernel(const AttnArgs a) {
       if (e == 0) { pp[D] = row_m[r]; pp[D + 1] = row_l[r]; }
     }
   }
+  if (a.done) {
+    // The split that arrives last merges all partials of this (batch, kv head) in split order
+    // (weights exp(m_s - max m), normalised by the merged sum) and writes the final rows.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const int old = atomicAdd(a.done + bi * a.hkv + kvh, 1);
+      is_last = (old == a.nsplit - 1);
+      if (is_last) a.done[bi * a.hkv + kvh] = 0;
+    }
+    __syncthreads();
+    if (is_last) {
+      __threadfence();
+      const size_t rows_all = (size_t)a.b * a.h * a.sq;
+      for (int i = tid; i < nrows * D; i += ATT_THREADS) {
+        const int r = i / D, e = i % D;
+        const size_t grow = row_index(r);
+        float mx = -INFINITY;
+        for (int s0 = 0; s0 < a.nsplit; ++s0) mx = fmaxf(mx, __ldcg(a.part + ((size_t)s0 * rows_all + grow) * (D + 2) + D));
+        float l = 0.f, o = 0.f;
+#pragma unroll 4
+        for (int s0 = 0; s0 < a.nsplit; ++s0) {
+          const float* pp = a.part + ((size_t)s0 * rows_all + grow) * (D + 2);
+          const float m = __ldcg(pp + D);
+          const float wgt = (m == -INFINITY) ? 0.f : __expf(m - mx);
+          l = fmaf(__ldcg(pp + D + 1), wgt, l);
+          o = fmaf(__ldcg(pp + e), wgt, o);
+        }
+        a.out[grow * D + e] = l > 0.f ? o / l : 0.f;
+      }
+    }
+  }
 }
 
 template <int D>
@@ -367,17 +403,20 @@ int fb200_launch_attention(fb200_device* dev, const float* q, const __half* k, c
 }
 
 // One new position per sequence: RoPE(q), RoPE(k) + fp16 append, split-KV attention over the
-// cache. Writes (o, m, l) partials [nsplit][B * H][D + 2] for the consumer to merge. Needs
-// H / Hkv <= 8 (one row tile per KV head). The position is read from pos_dev.
+// cache. Every split writes (o, m, l) partials [nsplit][B * H][D + 2]; the last split of a
+// (batch, kv head) to finish merges them into out [B, H * D] (`done`: zeroed arrival counters,
+// one per (batch, kv head)). Needs H / Hkv <= 8 (one row tile per KV head). The position is
+// read from pos_dev.
 int fb200_launch_attention_decode(fb200_device* dev, const float* q, const float* k_new,
                                   const float* v_new, __half* kc, __half* vc, int b, int h, int hkv,
                                   const int* pos_dev, int cap, int d, float scale,
                                   const float* rope_cos, const float* rope_sin, float* part,
-                                  int nsplit) {
+                                  int nsplit, int* done, float* out) {
   if (h % hkv || h / hkv > ROWS || (d != 64 && d != 128))
     return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "attention_decode: unsupported head layout");
   AttnArgs a = {};
-  a.q = q; a.k = kc; a.v = vc; a.out = nullptr; a.part = part; a.mask = nullptr; a.skv_dev = pos_dev;
+  a.q = q; a.k = kc; a.v = vc; a.out = out; a.part = part; a.mask = nullptr; a.skv_dev = pos_dev;
+  a.done = done;
   a.b = b; a.h = h; a.hkv = hkv; a.sq = 1; a.skv = 0; a.cap = cap; a.groups = h / hkv;
   a.mask_kind = 0; a.nsplit = nsplit; a.scale = scale; a.bshd = 1;
   a.row_tiles = 1;

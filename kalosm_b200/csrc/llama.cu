@@ -31,10 +31,8 @@ int fb200_launch_attention_decode(fb200_device* dev, const float* q, const float
                                   const float* v_new, __half* kc, __half* vc, int b, int h, int hkv,
                                   const int* pos_dev, int cap, int d, float scale,
                                   const float* rope_cos, const float* rope_sin, float* part,
-                                  int nsplit);
+                                  int nsplit, int* done, float* out);
 struct fb200_gemv1_extra {
-  const float* att_part = nullptr;
-  int att_nsplit = 0, att_heads = 0, att_d = 0;
   unsigned long long* argmax_key = nullptr;
 };
 int fb200_qgemv1_multi(fb200_device* dev, const fb200_qmatrix* const* ws, float* const* ys, int nw,
@@ -143,6 +141,7 @@ struct fb200_llama {
   int hist_cap = 0;
   int *pos_dev = nullptr, *step_dev = nullptr;
   unsigned long long* argmax_key = nullptr;
+  int* att_done = nullptr;  // arrival counters of the attention splits, one per (batch, kv head)
   bool used_key = false;  // the last forward pass left its greedy id in argmax_key, not in next
   // CUDA graph of a single-token step, per batch size
   cudaGraphExec_t graph_exec = nullptr;
@@ -212,8 +211,8 @@ int finalize(fb200_llama* m) {
 // stream serialization so that each product streams its weights into shared memory while its
 // predecessor is still running:
 //   q, k, v projections in one launch, RMSNorm in its prologue
-//   RoPE(q, k) + fp16 KV append + split-KV attention (partials)
-//   output projection, merging the attention partials in its prologue
+//   RoPE(q, k) + fp16 KV append + split-KV attention, merged by the last split to finish
+//   output projection
 //   gate/up projection with SwiGLU epilogue, residual add + RMSNorm in its prologue
 //   down projection with both residual adds in its epilogue
 // The output head keeps a running argmax key, so greedy decoding needs no argmax kernel.
@@ -252,13 +251,11 @@ int run_decode1(fb200_llama* m) {
                                  nullptr, nullptr, nullptr))) return rc;
     if ((rc = fb200_launch_attention_decode(dev, m->q, m->k, m->v, L.kc, L.vc, 1, H, HK, m->pos_dev,
                                             c.max_seq_len, D, scale, m->rope_cos, m->rope_sin, m->att_part,
-                                            nsplit))) return rc;
-    fb200_gemv1_extra ex;
-    ex.att_part = m->att_part; ex.att_nsplit = nsplit; ex.att_heads = H; ex.att_d = D;
+                                            nsplit, m->att_done, m->att))) return rc;
     const fb200_qmatrix* wo = L.wo;
     float* wo_out = m->attn_out;
-    if ((rc = fb200_qgemv1_multi(dev, &wo, &wo_out, 1, nullptr, nullptr, nullptr, 0.f, FB200_EPI_NONE, nullptr,
-                                 nullptr, &ex))) return rc;
+    if ((rc = fb200_qgemv1_multi(dev, &wo, &wo_out, 1, m->att, nullptr, nullptr, 0.f, FB200_EPI_NONE, nullptr,
+                                 nullptr, nullptr))) return rc;
     const fb200_qmatrix* gu = L.gate_up;
     float* gu_out = m->hbuf;
     if ((rc = fb200_qgemv1_multi(dev, &gu, &gu_out, 1, m->attn_out, m->x, L.ffn_norm, c.rms_eps,
@@ -431,6 +428,8 @@ int fb200_llama_create(fb200_device* dev, const fb200_llama_config* cfg, fb200_l
   FB_CUDA(dev, cudaMalloc(&m->hist, (size_t)c.max_batch * m->hist_cap * 4));
   FB_CUDA(dev, cudaMemset(m->pos_dev, 0, 4));
   FB_CUDA(dev, cudaMemset(m->step_dev, 0, 4));
+  FB_CUDA(dev, cudaMalloc(&m->att_done, (size_t)c.max_batch * c.n_kv_head * sizeof(int)));
+  FB_CUDA(dev, cudaMemset(m->att_done, 0, (size_t)c.max_batch * c.n_kv_head * sizeof(int)));
   FB_CUDA(dev, cudaMalloc(&m->argmax_key, 8));
   FB_CUDA(dev, cudaMemset(m->argmax_key, 0, 8));
   // attention split scratch: the largest a forward pass can ask for is bounded by 64 splits of
@@ -463,7 +462,7 @@ int fb200_llama_free(fb200_llama* m) {
   if (m->output) fb200_qmatrix_free(m->output);
   void* bufs[] = {m->output_norm, m->rope_cos, m->rope_sin, m->x, m->xn, m->q, m->k, m->v, m->att,
                   m->attn_out, m->hbuf, m->gbuf, m->last, m->logits, m->att_part, m->ids, m->next,
-                  m->hist, m->pos_dev, m->step_dev, m->argmax_key};
+                  m->hist, m->pos_dev, m->step_dev, m->argmax_key, m->att_done};
   for (void* b : bufs) if (b) cudaFree(b);
   delete m;
   return FB200_OK;

@@ -11,10 +11,10 @@
 //  * one launch may carry up to three matrices that share the activation row (the q, k and v
 //    projections), of different quant types;
 //  * the prologue turns x into int8 MMA B operands in shared memory once per CTA: optional
-//    merge of split-KV attention partials, residual add and RMSNorm (so neither the attention
-//    combine nor the norm needs a kernel of its own), a power-of-two row
-//    scale, then FOUR signed 7-bit limbs per element (x/scale = (l0 + l1/2^7 + l2/2^14 +
-//    l3/2^21) / 64 to 2^-27), plus the per-16 sums the offsets of Q4_K/Q4_0/Q6_K need;
+//    residual add and RMSNorm (so the norm needs no kernel of its own), a power-of-two row
+//    scale, then FOUR 7-bit limbs per element, the bit fields of q = rint(x/scale * 2^27)
+//    (x/scale = (l0 + u1/2^7 + u2/2^14 + u3/2^21) / 64 to 2^-28, l0 signed, u 0..127), plus the
+//    per-16 sums the offsets of Q4_K/Q4_0/Q6_K need;
 //  * quants stay in the byte domain: one logic op turns four packed nibbles into four u8
 //    operands of mma.sync.m16n8k32 (u8 x s8 -> s32, exact), so the ALU pipe that limits an
 //    fp16 expansion is nearly idle;
@@ -33,8 +33,6 @@
 
 // Optional extras of a single-row product.
 struct fb200_gemv1_extra {
-  const float* att_part = nullptr;  // x = merge of split-KV attention partials [nsplit][heads][d + 2]
-  int att_nsplit = 0, att_heads = 0, att_d = 0;
   unsigned long long* argmax_key = nullptr;  // running argmax key of the outputs
 };
 
@@ -57,9 +55,6 @@ struct Gemv1Args {
   const float* x;       // [K]
   const float* xres;    // optional [K]: v = x + xres
   const float* norm_w;  // optional [K]: activation = v / sqrt(mean(v^2) + eps) * norm_w
-  // optional: x is the merge of split-KV attention partials [nsplit][heads][D + 2] (o, m, l)
-  const float* att_part;
-  int att_nsplit, att_heads, att_d;
   float eps;
   int K, Kp;            // logical and padded (ngroups * group_elems) inner size
   const float* r1;
@@ -238,8 +233,9 @@ __device__ __forceinline__ unsigned long long argmax_key_of(float v, uint32_t id
   return ((unsigned long long)b << 32) | (unsigned long long)idx;
 }
 
-// EPI: 0 none, 1 residual(s), 2 SwiGLU pair. W = warps per CTA, MINB = CTAs per SM to plan for.
-template <int EPI, int W, int MINB>
+// TYPE: ggml type of the (single) matrix, or 0 = several matrices whose types are read at run
+// time. EPI: 0 none, 1 residual(s), 2 SwiGLU pair. W = warps per CTA, MINB = CTAs per SM.
+template <int TYPE, int EPI, int W, int MINB>
 __global__ void __launch_bounds__(W * 32, MINB)
 qgemv1_kernel(const Gemv1Args a) {
   constexpr int NP = EPI == 2 ? 2 : 1;
@@ -282,17 +278,22 @@ qgemv1_kernel(const Gemv1Args a) {
   // unit -> (matrix, tile inside it)
   auto locate = [&](int unit, int& sidx, int& tile) {
     sidx = 0; tile = unit;
-    if (a.nseg > 1 && tile >= a.seg[0].units) { tile -= a.seg[0].units; sidx = 1; }
-    if (a.nseg > 2 && sidx == 1 && tile >= a.seg[1].units) { tile -= a.seg[1].units; sidx = 2; }
+    if (TYPE == 0) {
+      if (a.nseg > 1 && tile >= a.seg[0].units) { tile -= a.seg[0].units; sidx = 1; }
+      if (a.nseg > 2 && sidx == 1 && tile >= a.seg[1].units) { tile -= a.seg[1].units; sidx = 2; }
+    }
   };
   int is_unit = blockIdx.x, is_p = 0, is_kk = 0, issued = 0;  // issue-side cursor (lane 0)
   auto issue_next = [&](int st) {
     int sidx, tile;
     locate(is_unit, sidx, tile);
-    const Seg& sg = a.seg[sidx];
-    const uint8_t* src = sg.w + ((size_t)(tile + is_p * a.pair_tile_offset) * a.ngroups + (warp + W * is_kk)) * sg.tg;
-    mbar_expect_tx(my_bar + 8 * st, sg.tg);
-    bulk_g2s(smem_u32(my_ring + st * a.stride), src, sg.tg, my_bar + 8 * st);
+    const uint8_t* wbase = a.seg[0].w;
+    int tgb = a.seg[0].tg;
+    if (TYPE == 0 && sidx == 1) { wbase = a.seg[1].w; tgb = a.seg[1].tg; }
+    if (TYPE == 0 && sidx == 2) { wbase = a.seg[2].w; tgb = a.seg[2].tg; }
+    const uint8_t* src = wbase + ((size_t)(tile + is_p * a.pair_tile_offset) * a.ngroups + (warp + W * is_kk)) * tgb;
+    mbar_expect_tx(my_bar + 8 * st, tgb);
+    bulk_g2s(smem_u32(my_ring + st * a.stride), src, tgb, my_bar + 8 * st);
     ++issued;
     if (++is_kk == gw) {
       is_kk = 0;
@@ -307,36 +308,20 @@ qgemv1_kernel(const Gemv1Args a) {
   pdl_wait();
 
   // ---- activation prologue ------------------------------------------------------------------
-  // pass 1: v = x (+ residual) (or the merged attention partials) -> shared memory as f32;
+  // pass 1: v = x (+ residual) -> shared memory as f32;
   //         sum of squares and max |v * norm_w| in one block reduction
   float ss = 0.f, amax = 0.f;
-  for (int k = threadIdx.x; k < a.Kp; k += THREADS) {
-    float v = 0.f;
-    if (k < a.K) {
-      if (a.att_part) {
-        // merge of split-KV partials, as attn_combine_kernel: weights exp(m_s - max m) in
-        // split order, normalised by the merged sum
-        const int head = k / a.att_d, e = k - head * a.att_d;
-        const int pd = a.att_d + 2;
-        float mx = -INFINITY;
-        for (int s = 0; s < a.att_nsplit; ++s) mx = fmaxf(mx, a.att_part[((size_t)s * a.att_heads + head) * pd + a.att_d]);
-        float l = 0.f, o = 0.f;
-        for (int s = 0; s < a.att_nsplit; ++s) {
-          const float* pp = a.att_part + ((size_t)s * a.att_heads + head) * pd;
-          const float m = pp[a.att_d];
-          const float wgt = (m == -INFINITY) ? 0.f : __expf(m - mx);
-          l = fmaf(pp[a.att_d + 1], wgt, l);
-          o = fmaf(pp[e], wgt, o);
-        }
-        v = l > 0.f ? o / l : 0.f;
-      } else {
+  {
+    for (int k = threadIdx.x; k < a.Kp; k += THREADS) {
+      float v = 0.f;
+      if (k < a.K) {
         v = a.x[k];
         if (a.xres) v += a.xres[k];
+        ss = fmaf(v, v, ss);
+        amax = fmaxf(amax, fabsf(a.norm_w ? v * a.norm_w[k] : v));
       }
-      ss = fmaf(v, v, ss);
-      amax = fmaxf(amax, fabsf(a.norm_w ? v * a.norm_w[k] : v));
+      xf[k] = v;
     }
-    xf[k] = v;
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -357,53 +342,65 @@ qgemv1_kernel(const Gemv1Args a) {
   if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &ex);  // amax = f * 2^ex, f in [0.5, 1)
   const float inv64 = ldexpf(64.0f, -ex);               // x * inv64 in (-64, 64)
   const float out_scale = ldexpf(1.0f, ex - 13);        // 2^ex / (64 * 128)
-  // pass 2: each thread turns whole 8-element blocks, in place, into four int8 limbs per element
+  // pass 2: each thread turns whole 8-element blocks, in place, into four int8 limbs per element:
+  // q = rint(v * 2^21) (|q| <= 2^27), l0 = q >> 21 (signed), u1, u2, u3 = the next three 7-bit
+  // fields (0..127), so v = (l0 + u1/2^7 + u2/2^14 + u3/2^21) up to 2^-22.
+  const float qscale = inv64 * 2097152.0f;
+  const float inv_rms = 1.0f / rms;  // v * (1/rms) instead of v / rms: within 1.5 ulp of the division
   const int nblk = a.Kp >> 3;
   for (int b0 = 0; b0 < nblk; b0 += THREADS) {
     const int kb = b0 + threadIdx.x;
-    uint32_t lw[4][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}, {0u, 0u}};
     float sum = 0.f;
+    uint32_t wl[2][4];  // [half of the block][limb 3, 2, 1, 0] four elements per word
     if (kb < nblk) {
       const float4 va = *reinterpret_cast<const float4*>(xf + kb * 8);
       const float4 vb = *reinterpret_cast<const float4*>(xf + kb * 8 + 4);
       const float vin[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+      uint32_t r[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int k = kb * 8 + i;
         float v = vin[i];
-        if (a.norm_w && k < a.K) v = (v / rms) * a.norm_w[k];
-        v *= inv64;
-        sum += v;
-        // four signed limbs; every remainder is exact in fp32
-        float l0 = rintf(v), r = (v - l0) * 128.0f;
-        float l1 = rintf(r); r = (r - l1) * 128.0f;
-        float l2 = rintf(r); r = (r - l2) * 128.0f;
-        float l3 = rintf(r);
-        const int sh = 8 * (i & 3);
-        lw[0][i >> 2] |= ((uint32_t)(int)l0 & 0xFFu) << sh;
-        lw[1][i >> 2] |= ((uint32_t)(int)l1 & 0xFFu) << sh;
-        lw[2][i >> 2] |= ((uint32_t)(int)l2 & 0xFFu) << sh;
-        lw[3][i >> 2] |= ((uint32_t)(int)l3 & 0xFFu) << sh;
+        if (a.norm_w && k < a.K) v = (v * inv_rms) * a.norm_w[k];
+        const int q = __float2int_rn(v * qscale);
+        sum += (float)q;
+        // fields at bits 0, 7, 14, 21 -> bytes 0..3 (byte 3 = bits 21..28 = l0 as s8)
+        r[i] = ((uint32_t)q & 0x7Fu) | (((uint32_t)q << 1) & 0x7F00u) | (((uint32_t)q << 2) & 0x7F0000u) |
+               (((uint32_t)q << 3) & 0xFF000000u);
+      }
+#pragma unroll
+      for (int hb = 0; hb < 2; ++hb) {
+        // 4 x 4 byte transpose: word j = byte j of the four elements
+        const uint32_t t01l = __byte_perm(r[4 * hb], r[4 * hb + 1], 0x5140), t23l = __byte_perm(r[4 * hb + 2], r[4 * hb + 3], 0x5140);
+        const uint32_t t01h = __byte_perm(r[4 * hb], r[4 * hb + 1], 0x7362), t23h = __byte_perm(r[4 * hb + 2], r[4 * hb + 3], 0x7362);
+        wl[hb][0] = __byte_perm(t01l, t23l, 0x5410);  // u3
+        wl[hb][1] = __byte_perm(t01l, t23l, 0x7632);  // u2
+        wl[hb][2] = __byte_perm(t01h, t23h, 0x5410);  // u1
+        wl[hb][3] = __byte_perm(t01h, t23h, 0x7632);  // l0
       }
     }
-    // per-16 sums in the units of the integer dot products: sum(x * inv64) * 128
+    // per-16 sums in the units of the integer dot products (128 * sum(v) = sum(q) / 2^14)
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
     if (kb < nblk) {
       uint4* dst = reinterpret_cast<uint4*>(xl + (size_t)kb * 32);
-      dst[0] = make_uint4(lw[0][0], lw[0][1], lw[2][0], lw[2][1]);
-      dst[1] = make_uint4(lw[1][0], lw[1][1], lw[3][0], lw[3][1]);
-      if ((threadIdx.x & 1) == 0) xs16[kb >> 1] = sum * 128.0f;
+      dst[0] = make_uint4(wl[0][3], wl[1][3], wl[0][1], wl[1][1]);  // limb 0, limb 2
+      dst[1] = make_uint4(wl[0][2], wl[1][2], wl[0][0], wl[1][0]);  // limb 1, limb 3
+      if ((threadIdx.x & 1) == 0) xs16[kb >> 1] = sum * (1.0f / 16384.0f);
     }
   }
   __syncthreads();
 
   int item = 0, st = 0;
   uint32_t phase = 0;
+  unsigned long long best_key = 0ull;
   for (int j = 0; j < my_units; ++j) {
     const int unit = (int)blockIdx.x + j * (int)gridDim.x;
     int sidx, tile;
     locate(unit, sidx, tile);
-    const Seg& sg = a.seg[sidx];
+    int type = TYPE ? TYPE : a.seg[0].type, n_out = a.seg[0].n_out;
+    float* yout = a.seg[0].y;
+    if (TYPE == 0 && sidx == 1) { type = a.seg[1].type; n_out = a.seg[1].n_out; yout = a.seg[1].y; }
+    if (TYPE == 0 && sidx == 2) { type = a.seg[2].type; n_out = a.seg[2].n_out; yout = a.seg[2].y; }
     if (j > 0) __syncthreads();  // the previous unit's reduction has read `red`
 #pragma unroll
     for (int p = 0; p < NP; ++p) {
@@ -412,9 +409,9 @@ qgemv1_kernel(const Gemv1Args a) {
         mbar_wait(my_bar + 8 * st, phase, a.status);
         const uint8_t* tg = my_ring + st * a.stride;
         const int kg = warp + W * kk;
-        if (sg.type == FB200_Q4_K) group1_q4k(xl, xs16, tg, kg, L, acc_g, acc_g8);
-        else if (sg.type == FB200_Q6_K) group1_q6k(xl, xs16, tg, kg, L, acc_g, acc_g8);
-        else if (sg.type == FB200_Q8_0) group1_q8_0(xl, tg, kg, L, acc_g, acc_g8);
+        if (type == FB200_Q4_K) group1_q4k(xl, xs16, tg, kg, L, acc_g, acc_g8);
+        else if (type == FB200_Q6_K) group1_q6k(xl, xs16, tg, kg, L, acc_g, acc_g8);
+        else if (type == FB200_Q8_0) group1_q8_0(xl, tg, kg, L, acc_g, acc_g8);
         else group1_q4_0(xl, xs16, tg, kg, L, acc_g, acc_g8);
         // Every lane has read the stage (its loads precede this barrier in program order and
         // shared loads complete long before a refill from global memory can land).
@@ -436,7 +433,7 @@ qgemv1_kernel(const Gemv1Args a) {
     if (threadIdx.x < 16) {
       const int r = threadIdx.x;
       const int n = tile * 16 + r;
-      if (n < sg.n_out) {
+      if (n < n_out) {
         float v[NP];
 #pragma unroll
         for (int p = 0; p < NP; ++p) {
@@ -455,10 +452,22 @@ qgemv1_kernel(const Gemv1Args a) {
         } else {
           out = v[0];
         }
-        sg.y[n] = out;
-        if (a.argmax_key && sidx == 0) atomicMax(a.argmax_key, argmax_key_of(out, (uint32_t)n));
+        yout[n] = out;
+        if (a.argmax_key && sidx == 0) {
+          const unsigned long long key = argmax_key_of(out, (uint32_t)n);
+          if (key > best_key) best_key = key;
+        }
       }
     }
+  }
+  if (a.argmax_key && threadIdx.x < 32) {
+    // threads 0..15 carry the maxima of the rows they wrote; one atomic per CTA
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, best_key, o);
+      if (other > best_key) best_key = other;
+    }
+    if (threadIdx.x == 0 && best_key) atomicMax(a.argmax_key, best_key);
   }
 }
 
@@ -471,9 +480,9 @@ size_t gemv1_smem(int stages, int stride, int kp) {
          (size_t)NP * W * 16 * 4 + (size_t)2 * W * 4 + 16 + 64;
 }
 
-template <int EPI, int W, int MINB>
+template <int TYPE, int EPI, int W, int MINB>
 int launch_w(fb200_device* dev, Gemv1Args& a) {
-  auto kern = qgemv1_kernel<EPI, W, MINB>;
+  auto kern = qgemv1_kernel<TYPE, EPI, W, MINB>;
   static bool configured[64] = {false};
   if (!configured[dev->ordinal & 63]) {
     FB_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
@@ -481,6 +490,9 @@ int launch_w(fb200_device* dev, Gemv1Args& a) {
   }
   int grid = dev->sm_count * MINB;
   if (grid > a.nunits) grid = a.nunits;
+  // same number of units for every CTA where the unit count allows it
+  const int rounds = (a.nunits + grid - 1) / grid;
+  grid = (a.nunits + rounds - 1) / rounds;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3(W * 32);
@@ -499,21 +511,26 @@ int launch_w(fb200_device* dev, Gemv1Args& a) {
 // Shared memory per SM is split between the activation limbs (4 B per element of K, one copy
 // per CTA, built by every CTA in its prologue) and the weight rings. More, smaller CTAs give
 // deeper rings per warp and more independent tiles in flight; larger K forces fewer CTAs.
-template <int EPI>
+template <int TYPE, int EPI>
 int launch_cfg(fb200_device* dev, Gemv1Args& a) {
   const int per_sm = SMEM_LIMIT - 2048;
   auto fits = [&](size_t need, int ctas) { return (need + 1024) * ctas <= (size_t)per_sm; };
   for (int s = 3; s >= 2; --s)
-    if (fits(gemv1_smem<EPI, 8>(s, a.stride, a.Kp), 4)) { a.stages = s; return launch_w<EPI, 8, 4>(dev, a); }
+    if (fits(gemv1_smem<EPI, 8>(s, a.stride, a.Kp), 4)) { a.stages = s; return launch_w<TYPE, EPI, 8, 4>(dev, a); }
   for (int s = 3; s >= 2; --s)
-    if (fits(gemv1_smem<EPI, 8>(s, a.stride, a.Kp), 3)) { a.stages = s; return launch_w<EPI, 8, 3>(dev, a); }
+    if (fits(gemv1_smem<EPI, 8>(s, a.stride, a.Kp), 3)) { a.stages = s; return launch_w<TYPE, EPI, 8, 3>(dev, a); }
   for (int s = 3; s >= 2; --s)
-    if (fits(gemv1_smem<EPI, 16>(s, a.stride, a.Kp), 2)) { a.stages = s; return launch_w<EPI, 16, 2>(dev, a); }
+    if (fits(gemv1_smem<EPI, 16>(s, a.stride, a.Kp), 2)) { a.stages = s; return launch_w<TYPE, EPI, 16, 2>(dev, a); }
   for (int s = 2; s >= 1; --s)
-    if (fits(gemv1_smem<EPI, 32>(s, a.stride, a.Kp), 1)) { a.stages = s; return launch_w<EPI, 32, 1>(dev, a); }
-  for (int s = 2; s >= 1; --s)
-    if (fits(gemv1_smem<EPI, 16>(s, a.stride, a.Kp), 1)) { a.stages = s; return launch_w<EPI, 16, 1>(dev, a); }
+    if (fits(gemv1_smem<EPI, 32>(s, a.stride, a.Kp), 1)) { a.stages = s; return launch_w<TYPE, EPI, 32, 1>(dev, a); }
   return fb200_fail(dev, FB200_ERR_CAPACITY, "qgemv1: K = %d does not fit in shared memory", a.K);
+}
+
+template <int TYPE>
+int launch_typed(fb200_device* dev, Gemv1Args& a, int epi) {
+  if (epi == FB200_EPI_SWIGLU) return launch_cfg<TYPE, 2>(dev, a);
+  if (epi == FB200_EPI_RESIDUAL) return launch_cfg<TYPE, 1>(dev, a);
+  return launch_cfg<TYPE, 0>(dev, a);
 }
 
 }  // namespace
@@ -554,19 +571,20 @@ int fb200_qgemv1_multi(fb200_device* dev, const fb200_qmatrix* const* ws, float*
   a.r1 = r1; a.r2 = r2;
   a.ngroups = ws[0]->ngroups; a.pair_tile_offset = 0;
   a.stages = 2; a.status = dev->status;
-  if (extra) {
-    a.att_part = extra->att_part; a.att_nsplit = extra->att_nsplit; a.att_heads = extra->att_heads;
-    a.att_d = extra->att_d; a.argmax_key = extra->argmax_key;
-  }
+  if (extra) a.argmax_key = extra->argmax_key;
   if (epi == FB200_EPI_SWIGLU) {
     a.seg[0].units = ws[0]->ntiles / 2;
     a.nunits = a.seg[0].units;
     a.seg[0].n_out = (int)(ws[0]->n / 2);
     a.pair_tile_offset = ws[0]->ntiles / 2;
-    return launch_cfg<2>(dev, a);
   }
-  if (epi == FB200_EPI_RESIDUAL) return launch_cfg<1>(dev, a);
-  return launch_cfg<0>(dev, a);
+  if (nw > 1) return launch_cfg<0, 0>(dev, a);
+  switch (ws[0]->type) {
+    case FB200_Q4_K: return launch_typed<FB200_Q4_K>(dev, a, epi);
+    case FB200_Q6_K: return launch_typed<FB200_Q6_K>(dev, a, epi);
+    case FB200_Q8_0: return launch_typed<FB200_Q8_0>(dev, a, epi);
+    default: return launch_typed<FB200_Q4_0>(dev, a, epi);
+  }
 }
 
 int fb200_qgemv1(fb200_device* dev, const fb200_qmatrix* w, const float* x, const float* xres,
