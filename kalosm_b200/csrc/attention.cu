@@ -11,6 +11,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "packed_act.cuh"
 
 struct fb200_kv_cache {
   fb200_device* dev = nullptr;
@@ -309,6 +310,7 @@ struct DecArgs {
   float* part;          // [nsplit][B * H][D + 2]
   float* out;           // [B, H * D]
   int* done;            // [B * Hkv] arrival counters, zero between launches
+  fb200_packed_act out_packed;  // optional: the merged rows also in packed form (row of H * D)
   int b, h, hkv, groups, cap, nsplit;
   float scale;
 };
@@ -563,14 +565,21 @@ attn_decode_kernel(const DecArgs a) {
     if (lane == 0) inv_l[r] = l > 0.f ? 1.0f / l : 0.f;
   }
   __syncthreads();
-  for (int i = tid; i < nrows * D; i += ATT_THREADS) {
-    const int r = i / D, e = i % D;
+  for (int i0 = 0; i0 < nrows * D; i0 += ATT_THREADS) {
+    const int i = i0 + tid;
+    const bool valid = i < nrows * D;
+    const int r = valid ? i / D : 0, e = i % D;
     const size_t grow = (size_t)bi * a.h + kvh * a.groups + r;
     float acc = 0.f;
+    if (valid) {
 #pragma unroll 8
-    for (int s0 = 0; s0 < a.nsplit; ++s0)
-      acc = fmaf(__ldcg(a.part + ((size_t)s0 * rows_all + grow) * (D + 2) + e), wsplit[r][s0], acc);
-    a.out[grow * D + e] = acc * inv_l[r];
+      for (int s0 = 0; s0 < a.nsplit; ++s0)
+        acc = fmaf(__ldcg(a.part + ((size_t)s0 * rows_all + grow) * (D + 2) + e), wsplit[r][s0], acc);
+      acc *= inv_l[r];
+      if (a.out) a.out[grow * D + e] = acc;
+    }
+    if (a.out_packed.limbs && bi == 0)  // packed rows are single-sequence
+      emit_packed16(a.out_packed, (int)(grow * D) + e, acc, acc, valid, 0xFFFFFFFFu);
   }
 }
 
@@ -626,12 +635,13 @@ int fb200_launch_attention_decode(fb200_device* dev, const float* q, const float
                                   const float* v_new, __half* kc, __half* vc, int b, int h, int hkv,
                                   const int* pos_dev, int cap, int d, float scale,
                                   const float* rope_cos, const float* rope_sin, float* part,
-                                  int nsplit, int* done, float* out) {
+                                  int nsplit, int* done, float* out, const fb200_packed_act* out_packed) {
   if (h % hkv || h / hkv > ROWS || (d != 64 && d != 128) || nsplit < 1 || nsplit > 32)
     return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "attention_decode: unsupported head layout");
   DecArgs a = {};
   a.q = q; a.k_new = k_new; a.v_new = v_new; a.kc = kc; a.vc = vc; a.rope_cos = rope_cos; a.rope_sin = rope_sin;
   a.pos_dev = pos_dev; a.part = part; a.out = out; a.done = done;
+  if (out_packed) a.out_packed = *out_packed;
   a.b = b; a.h = h; a.hkv = hkv; a.groups = h / hkv; a.cap = cap; a.nsplit = nsplit; a.scale = scale;
   const unsigned grid = (unsigned)(b * hkv * nsplit);
   const size_t smem = (size_t)2 * DEC_CH * (d * 2 + 64) + (size_t)ROWS * d * 4 + (size_t)ROWS * DEC_CH * 4;

@@ -13,6 +13,7 @@
 #include <memory>
 
 #include "common.cuh"
+#include "packed_act.cuh"
 
 void fb200_rope_tables_host(int head_dim, int ctx, float theta, float factor, float low_ff,
                             float high_ff, int original_ctx, std::vector<float>& cs,
@@ -31,14 +32,8 @@ int fb200_launch_attention_decode(fb200_device* dev, const float* q, const float
                                   const float* v_new, __half* kc, __half* vc, int b, int h, int hkv,
                                   const int* pos_dev, int cap, int d, float scale,
                                   const float* rope_cos, const float* rope_sin, float* part,
-                                  int nsplit, int* done, float* out);
-struct fb200_gemv1_extra {
-  unsigned long long* argmax_key = nullptr;
-};
-int fb200_qgemv1_multi(fb200_device* dev, const fb200_qmatrix* const* ws, float* const* ys, int nw,
-                       const float* x, const float* xres, const float* norm_w, float eps, int epi,
-                       const float* r1, const float* r2, const fb200_gemv1_extra* extra);
-bool fb200_qgemv1_fits(const fb200_qmatrix* w);
+                                  int nsplit, int* done, float* out,
+                                  const fb200_packed_act* out_packed);
 int fb200_attention_scratch_bytes(int b, int h, int sq, int d, int nsplit, size_t* out);
 
 namespace {
@@ -142,6 +137,8 @@ struct fb200_llama {
   int *pos_dev = nullptr, *step_dev = nullptr;
   unsigned long long* argmax_key = nullptr;
   int* att_done = nullptr;  // arrival counters of the attention splits, one per (batch, kv head)
+  // single-row step: activation rows travel between kernels in the products' operand form
+  fb200_packed_act px, patt, pv, ph;  // residual stream, attention output, attn_out + x, SwiGLU output
   bool used_key = false;  // the last forward pass left its greedy id in argmax_key, not in next
   // CUDA graph of a single-token step, per batch size
   cudaGraphExec_t graph_exec = nullptr;
@@ -247,29 +244,44 @@ int run_decode1(fb200_llama* m) {
     LayerW& L = m->layers[li];
     const fb200_qmatrix* qkv[3] = {L.wq, L.wk, L.wv};
     float* qkv_out[3] = {m->q, m->k, m->v};
+    fb200_gemv1_extra e_qkv;
+    if (li > 0) { e_qkv.x_packed = &m->px; e_qkv.x_packed_norm = true; }  // layer 0 packs the embedding row itself
     if ((rc = fb200_qgemv1_multi(dev, qkv, qkv_out, 3, m->x, nullptr, L.attn_norm, c.rms_eps, FB200_EPI_NONE,
-                                 nullptr, nullptr, nullptr))) return rc;
+                                 nullptr, nullptr, &e_qkv))) return rc;
     if ((rc = fb200_launch_attention_decode(dev, m->q, m->k, m->v, L.kc, L.vc, 1, H, HK, m->pos_dev,
                                             c.max_seq_len, D, scale, m->rope_cos, m->rope_sin, m->att_part,
-                                            nsplit, m->att_done, m->att))) return rc;
+                                            nsplit, m->att_done, nullptr, &m->patt))) return rc;
+    // output projection; its epilogue also packs attn_out + x times the FFN norm weight
     const fb200_qmatrix* wo = L.wo;
     float* wo_out = m->attn_out;
-    if ((rc = fb200_qgemv1_multi(dev, &wo, &wo_out, 1, m->att, nullptr, nullptr, 0.f, FB200_EPI_NONE, nullptr,
-                                 nullptr, nullptr))) return rc;
+    fb200_gemv1_extra e_wo;
+    e_wo.x_packed = &m->patt;
+    e_wo.y_packed = &m->pv; e_wo.y_packed_add = m->x; e_wo.y_packed_norm_w = L.ffn_norm;
+    if ((rc = fb200_qgemv1_multi(dev, &wo, &wo_out, 1, nullptr, nullptr, nullptr, c.rms_eps, FB200_EPI_NONE,
+                                 nullptr, nullptr, &e_wo))) return rc;
     const fb200_qmatrix* gu = L.gate_up;
-    float* gu_out = m->hbuf;
-    if ((rc = fb200_qgemv1_multi(dev, &gu, &gu_out, 1, m->attn_out, m->x, L.ffn_norm, c.rms_eps,
-                                 FB200_EPI_SWIGLU, nullptr, nullptr, nullptr))) return rc;
+    float* gu_out = nullptr;  // the SwiGLU row is only needed packed
+    fb200_gemv1_extra e_gu;
+    e_gu.x_packed = &m->pv; e_gu.x_packed_norm = true;
+    e_gu.y_packed = &m->ph;
+    if ((rc = fb200_qgemv1_multi(dev, &gu, &gu_out, 1, nullptr, nullptr, nullptr, c.rms_eps,
+                                 FB200_EPI_SWIGLU, nullptr, nullptr, &e_gu))) return rc;
+    // down projection + both residuals -> residual stream, also packed for the next norm
     const fb200_qmatrix* dn = L.down;
     float* dn_out = m->x;
-    if ((rc = fb200_qgemv1_multi(dev, &dn, &dn_out, 1, m->hbuf, nullptr, nullptr, 0.f, FB200_EPI_RESIDUAL,
-                                 m->attn_out, m->x, nullptr))) return rc;
+    fb200_gemv1_extra e_dn;
+    e_dn.x_packed = &m->ph;
+    e_dn.y_packed = &m->px;
+    e_dn.y_packed_norm_w = li + 1 < c.n_layer ? m->layers[li + 1].attn_norm : m->output_norm;
+    if ((rc = fb200_qgemv1_multi(dev, &dn, &dn_out, 1, nullptr, nullptr, nullptr, c.rms_eps, FB200_EPI_RESIDUAL,
+                                 m->attn_out, m->x, &e_dn))) return rc;
   }
   const fb200_qmatrix* ow = m->output ? m->output : m->token_embd;
   float* lg = m->logits;
   fb200_gemv1_extra ex;
   ex.argmax_key = m->argmax_key;
-  if ((rc = fb200_qgemv1_multi(dev, &ow, &lg, 1, m->x, nullptr, m->output_norm, c.rms_eps, FB200_EPI_NONE,
+  ex.x_packed = &m->px; ex.x_packed_norm = true;
+  if ((rc = fb200_qgemv1_multi(dev, &ow, &lg, 1, nullptr, nullptr, nullptr, c.rms_eps, FB200_EPI_NONE,
                                nullptr, nullptr, &ex))) return rc;
   m->used_key = true;
   return FB200_OK;
@@ -432,6 +444,25 @@ int fb200_llama_create(fb200_device* dev, const fb200_llama_config* cfg, fb200_l
   FB_CUDA(dev, cudaMemset(m->att_done, 0, (size_t)c.max_batch * c.n_kv_head * sizeof(int)));
   FB_CUDA(dev, cudaMalloc(&m->argmax_key, 8));
   FB_CUDA(dev, cudaMemset(m->argmax_key, 0, 8));
+  {
+    // packed rows, zero beyond the logical length up to the next multiple of 256 (and one
+    // 16-row tile of slack for the producers' last tile)
+    auto packed = [&](fb200_packed_act* p, size_t n) -> int {
+      const size_t np = (n + 255) / 256 * 256 + 256;
+      FB_CUDA(dev, cudaMalloc(&p->limbs, np * 4));
+      FB_CUDA(dev, cudaMemset(p->limbs, 0, np * 4));
+      float** fs[3] = {&p->xsc, &p->xss, &p->sumsq};
+      for (float** f : fs) {
+        FB_CUDA(dev, cudaMalloc(f, np / 16 * 4));
+        FB_CUDA(dev, cudaMemset(*f, 0, np / 16 * 4));
+      }
+      return FB200_OK;
+    };
+    int prc;
+    if ((prc = packed(&m->px, c.hidden)) || (prc = packed(&m->pv, c.hidden)) ||
+        (prc = packed(&m->patt, (size_t)c.n_head * c.head_dim)) || (prc = packed(&m->ph, c.ffn)))
+      return prc;
+  }
   // attention split scratch: the largest a forward pass can ask for is bounded by 64 splits of
   // a single-token step or one split set of a whole-context prefill
   size_t a1, a2;
@@ -464,6 +495,10 @@ int fb200_llama_free(fb200_llama* m) {
                   m->attn_out, m->hbuf, m->gbuf, m->last, m->logits, m->att_part, m->ids, m->next,
                   m->hist, m->pos_dev, m->step_dev, m->argmax_key, m->att_done};
   for (void* b : bufs) if (b) cudaFree(b);
+  for (fb200_packed_act* p : {&m->px, &m->patt, &m->pv, &m->ph}) {
+    void* pb[] = {p->limbs, p->xsc, p->xss, p->sumsq};
+    for (void* b : pb) if (b) cudaFree(b);
+  }
   delete m;
   return FB200_OK;
 }

@@ -1,0 +1,69 @@
+// Activation rows handed from one kernel to the next in the operand form of the single-row
+// product (int8 limbs + per-16 scales and sums), so that the consumer needs no packing pass.
+#pragma once
+
+#include "common.cuh"
+
+// An activation row in the form the single-row product consumes directly (all device pointers;
+// K padded to a multiple of 256 with zero limbs).
+struct fb200_packed_act {
+  uint8_t* limbs = nullptr;  // [Kp/8][32]: per 8 elements limb 0, limb 2, limb 1, limb 3 (8 bytes each)
+  float* xsc = nullptr;      // [Kp/16] power-of-two scale of each 16-element block
+  float* xss = nullptr;      // [Kp/16] sum of the 16 activations
+  float* sumsq = nullptr;    // [Kp/16] sums of squares of the un-weighted values (RMSNorm consumers)
+};
+
+
+// ---- packed activations between kernels ---------------------------------------------------------
+// A producer kernel can hand its output row to the next product already in MMA-operand form:
+// limbs [K/8][32] (the shared-memory layout of the consumer), per-16 power-of-two scales and
+// per-16 sums, optionally multiplied by the consumer's RMSNorm weight, plus per-unit partial
+// sums of squares (the consumer adds them in index order and applies 1/rms as one final factor).
+// Sixteen consecutive lanes call this with sixteen consecutive elements.
+__device__ __forceinline__ void emit_packed16(const fb200_packed_act& pk, int n, float value,
+                                              float norm_value, bool valid, uint32_t mask) {
+  // value: what the consumer multiplies (after the optional norm weight); norm_value: what
+  // enters the sum of squares
+  float amax = valid ? fabsf(value) : 0.f;
+  float sq = valid ? norm_value * norm_value : 0.f;
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(mask, amax, o, 16));
+    sq += __shfl_xor_sync(mask, sq, o, 16);
+  }
+  int ex = 0;
+  if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &ex);
+  const int q = valid ? __float2int_rn(value * ldexpf(64.0f * 2097152.0f, -ex)) : 0;
+  float qsum = (float)q;
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) qsum += __shfl_xor_sync(mask, qsum, o, 16);
+  uint8_t* blk = pk.limbs + (size_t)(n >> 3) * 32 + (n & 7);
+  blk[0] = (uint8_t)(q >> 21);           // limb 0 (signed)
+  blk[8] = (uint8_t)((q >> 7) & 0x7F);   // limb 2
+  blk[16] = (uint8_t)((q >> 14) & 0x7F); // limb 1
+  blk[24] = (uint8_t)(q & 0x7F);         // limb 3
+  if ((n & 15) == 0) {
+    const float sc = ldexpf(1.0f, ex - 13);
+    pk.xsc[n >> 4] = sc;
+    pk.xss[n >> 4] = qsum * (1.0f / 16384.0f) * sc;
+    if (pk.sumsq) pk.sumsq[n >> 4] = sq;
+  }
+}
+
+
+// Optional extras of a single-row product.
+struct fb200_gemv1_extra {
+  unsigned long long* argmax_key = nullptr;  // running argmax key of the outputs
+  const fb200_packed_act* x_packed = nullptr;  // take the activation row from here instead of x
+  bool x_packed_norm = false;                  // ... and divide by its RMS (weight already applied)
+  const fb200_packed_act* y_packed = nullptr;  // also emit the output row in packed form
+  const float* y_packed_norm_w = nullptr;      // multiplied by this RMSNorm weight (the next layer's)
+  const float* y_packed_add = nullptr;         // after adding this row (residual)
+};
+
+// ys[i][n_i] = epilogue(W_i . act(x)) for up to three matrices that share K and the group size
+// (single activation row); defined with the single-row kernel.
+int fb200_qgemv1_multi(fb200_device* dev, const fb200_qmatrix* const* ws, float* const* ys, int nw,
+                       const float* x, const float* xres, const float* norm_w, float eps, int epi,
+                       const float* r1, const float* r2, const fb200_gemv1_extra* extra);
+bool fb200_qgemv1_fits(const fb200_qmatrix* w);

@@ -29,12 +29,8 @@
 // qgemv_q6k.rs:84-385), their SwiGLU and residual epilogues
 // (fusor-ml/core/src/quantized/matmul/mod.rs:435-439, 666-722) and the fused RMSNorm cluster
 // (fusor-ml/core/src/composite/rms_norm_fused.rs:10-54) in front of a projection.
+#include "packed_act.cuh"
 #include "qgemv_common.cuh"
-
-// Optional extras of a single-row product.
-struct fb200_gemv1_extra {
-  unsigned long long* argmax_key = nullptr;  // running argmax key of the outputs
-};
 
 namespace {
 
@@ -60,6 +56,11 @@ struct Gemv1Args {
   const float* r1;
   const float* r2;
   unsigned long long* argmax_key;  // optional: running (value, index) maximum of seg[0]'s outputs
+  fb200_packed_act xp;   // optional (xp.limbs != null): the activation row, already packed
+  int xp_norm;           // ... to be divided by its RMS (weights already applied by the producer)
+  fb200_packed_act yp;   // optional: also emit seg[0]'s output row in packed form
+  const float* yp_norm_w;
+  const float* yp_add;
   int ngroups, nunits, pair_tile_offset, stages, stride;
   int* status;
 };
@@ -95,8 +96,13 @@ __device__ __forceinline__ float limbs_to_float(int c_l0, int c_l1, int c_l2, in
   return fmaf((float)(c_l2 * 128 + c_l3), 1.0f / 16384.0f, (float)(c_l0 * 128 + c_l1));
 }
 
-__device__ __forceinline__ void group1_q4_0(const uint8_t* xl, const float* xs16, const uint8_t* tg,
-                                            int kg, const Lane& L, float& acc_g, float& acc_g8) {
+// The four group functions below take, besides the limbs `xl`, two per-16-element arrays:
+// xsc[b] = power-of-two scale of x-block b (true x = limb value * xsc[b] * 2^13 / 128 ...,
+// folded so that f * xsc[b] is the true partial dot product) and xss[b] = true sum of the 16
+// activations (for the quant centres and offsets).
+__device__ __forceinline__ void group1_q4_0(const uint8_t* xl, const float* xsc, const float* xss,
+                                            const uint8_t* tg, int kg, const Lane& L, float& acc_g,
+                                            float& acc_g8) {
   const uint4 qa = lds16(tg + L.g * 64 + L.t * 16);
   const uint4 qb = lds16(tg + 512 + L.g * 64 + L.t * 16);
   const float d_g = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 1024 + (L.g * 4 + L.t) * 2));
@@ -104,25 +110,32 @@ __device__ __forceinline__ void group1_q4_0(const uint8_t* xl, const float* xs16
   const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w};
   const uint32_t wb[4] = {qb.x, qb.y, qb.z, qb.w};
   const int blk = kg * 4 + L.t;
-  int c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0};
+  float f_g = 0.f, f_g8 = 0.f;
 #pragma unroll
-  for (int s = 0; s < 4; ++s) {
-    const uint4 v = load_limbs(xl, blk * 4 + s, L);
-    const int w0 = (s & 1) * 2;
-    if (s < 2)  // elements 0..15: low nibbles
-      step<false>(c1, c2, wa[w0] & 0x0F0F0F0Fu, wb[w0] & 0x0F0F0F0Fu, wa[w0 + 1] & 0x0F0F0F0Fu,
-                  wb[w0 + 1] & 0x0F0F0F0Fu, v);
-    else        // elements 16..31: high nibbles
-      step<false>(c1, c2, (wa[w0] >> 4) & 0x0F0F0F0Fu, (wb[w0] >> 4) & 0x0F0F0F0Fu,
-                  (wa[w0 + 1] >> 4) & 0x0F0F0F0Fu, (wb[w0 + 1] >> 4) & 0x0F0F0F0Fu, v);
+  for (int hf = 0; hf < 2; ++hf) {  // elements 0..15 = low nibbles, 16..31 = high nibbles
+    int c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int sw = 0; sw < 2; ++sw) {
+      const uint4 v = load_limbs(xl, blk * 4 + hf * 2 + sw, L);
+      const int w0 = sw * 2;
+      if (hf == 0)
+        step<false>(c1, c2, wa[w0] & 0x0F0F0F0Fu, wb[w0] & 0x0F0F0F0Fu, wa[w0 + 1] & 0x0F0F0F0Fu,
+                    wb[w0 + 1] & 0x0F0F0F0Fu, v);
+      else
+        step<false>(c1, c2, (wa[w0] >> 4) & 0x0F0F0F0Fu, (wb[w0] >> 4) & 0x0F0F0F0Fu,
+                    (wa[w0 + 1] >> 4) & 0x0F0F0F0Fu, (wb[w0 + 1] >> 4) & 0x0F0F0F0Fu, v);
+    }
+    const float xs = xsc[blk * 2 + hf];
+    f_g = fmaf(limbs_to_float(c1[0], c1[1], c2[0], c2[1]), xs, f_g);
+    f_g8 = fmaf(limbs_to_float(c1[2], c1[3], c2[2], c2[3]), xs, f_g8);
   }
-  const float sx8 = 8.0f * (xs16[blk * 2] + xs16[blk * 2 + 1]);  // (q - 8): centre folded into the sum
-  acc_g = fmaf(d_g, limbs_to_float(c1[0], c1[1], c2[0], c2[1]) - sx8, acc_g);
-  acc_g8 = fmaf(d_g8, limbs_to_float(c1[2], c1[3], c2[2], c2[3]) - sx8, acc_g8);
+  const float sx8 = 8.0f * (xss[blk * 2] + xss[blk * 2 + 1]);  // (q - 8): centre folded into the sum
+  acc_g = fmaf(d_g, f_g - sx8, acc_g);
+  acc_g8 = fmaf(d_g8, f_g8 - sx8, acc_g8);
 }
 
-__device__ __forceinline__ void group1_q8_0(const uint8_t* xl, const uint8_t* tg, int kg,
-                                            const Lane& L, float& acc_g, float& acc_g8) {
+__device__ __forceinline__ void group1_q8_0(const uint8_t* xl, const float* xsc, const uint8_t* tg,
+                                            int kg, const Lane& L, float& acc_g, float& acc_g8) {
   uint4 q[2][2];  // [h][half]
 #pragma unroll
   for (int h = 0; h < 2; ++h)
@@ -131,23 +144,27 @@ __device__ __forceinline__ void group1_q8_0(const uint8_t* xl, const uint8_t* tg
   const float d_g = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 2048 + (L.g * 4 + L.t) * 2));
   const float d_g8 = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 2048 + ((L.g + 8) * 4 + L.t) * 2));
   const int blk = kg * 4 + L.t;
-  int c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0};
+  float f_g = 0.f, f_g8 = 0.f;
 #pragma unroll
-  for (int s = 0; s < 4; ++s) {
-    const uint4 v = load_limbs(xl, blk * 4 + s, L);
-    const uint4 a = q[0][s >> 1], b = q[1][s >> 1];
-    if (s & 1) step<true>(c1, c2, a.z, b.z, a.w, b.w, v);
-    else step<true>(c1, c2, a.x, b.x, a.y, b.y, v);
+  for (int hf = 0; hf < 2; ++hf) {
+    int c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0};
+    const uint4 a = q[0][hf], b = q[1][hf];
+    step<true>(c1, c2, a.x, b.x, a.y, b.y, load_limbs(xl, blk * 4 + hf * 2, L));
+    step<true>(c1, c2, a.z, b.z, a.w, b.w, load_limbs(xl, blk * 4 + hf * 2 + 1, L));
+    const float xs = xsc[blk * 2 + hf];
+    f_g = fmaf(limbs_to_float(c1[0], c1[1], c2[0], c2[1]), xs, f_g);
+    f_g8 = fmaf(limbs_to_float(c1[2], c1[3], c2[2], c2[3]), xs, f_g8);
   }
-  acc_g = fmaf(d_g, limbs_to_float(c1[0], c1[1], c2[0], c2[1]), acc_g);
-  acc_g8 = fmaf(d_g8, limbs_to_float(c1[2], c1[3], c2[2], c2[3]), acc_g8);
+  acc_g = fmaf(d_g, f_g, acc_g);
+  acc_g8 = fmaf(d_g8, f_g8, acc_g8);
 }
 
 // Q4_K: chain ch covers sub-blocks 4ch .. 4ch+3; lane t owns sub-block 4ch + t, whose quants
 // are the low (t even) or high (t odd) nibbles of qs bytes 32 * (2ch + t/2) .. +32. High
 // nibbles are used in place as 16 * q and the factor goes into the scale.
-__device__ __forceinline__ void group1_q4k(const uint8_t* xl, const float* xs16, const uint8_t* tg,
-                                           int kg, const Lane& L, float& acc_g, float& acc_g8) {
+__device__ __forceinline__ void group1_q4k(const uint8_t* xl, const float* xsc, const float* xss,
+                                           const uint8_t* tg, int kg, const Lane& L, float& acc_g,
+                                           float& acc_g8) {
   const uint32_t mask = (L.t & 1) ? 0xF0F0F0F0u : 0x0F0F0F0Fu;
   const float nib_scale = (L.t & 1) ? 0.0625f : 1.0f;
   float sc_f[2][2], mn_f[2][2];  // [row half][chain]
@@ -168,27 +185,32 @@ __device__ __forceinline__ void group1_q4k(const uint8_t* xl, const float* xs16,
   const int slot = L.g * 32 + (L.t >> 1) * 16;
 #pragma unroll
   for (int ch = 0; ch < 2; ++ch) {
-    int c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0};
     const int sb = kg * 8 + ch * 4 + L.t;
+    float f_g = 0.f, f_g8 = 0.f;
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
+    for (int half = 0; half < 2; ++half) {  // elements 0..15 and 16..31 of the sub-block
+      int c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0};
       const uint4 qa = lds16(tg + ((ch * 2 + 0) * 2 + half) * 256 + slot);
       const uint4 qb = lds16(tg + ((ch * 2 + 1) * 2 + half) * 256 + slot);
       const uint4 v0 = load_limbs(xl, sb * 4 + half * 2, L);
       const uint4 v1 = load_limbs(xl, sb * 4 + half * 2 + 1, L);
       step<false>(c1, c2, qa.x & mask, qb.x & mask, qa.y & mask, qb.y & mask, v0);
       step<false>(c1, c2, qa.z & mask, qb.z & mask, qa.w & mask, qb.w & mask, v1);
+      const float xs = xsc[sb * 2 + half];
+      f_g = fmaf(limbs_to_float(c1[0], c1[1], c2[0], c2[1]), xs, f_g);
+      f_g8 = fmaf(limbs_to_float(c1[2], c1[3], c2[2], c2[3]), xs, f_g8);
     }
-    const float sx = xs16[sb * 2] + xs16[sb * 2 + 1];
-    acc_g = fmaf(sc_f[0][ch], limbs_to_float(c1[0], c1[1], c2[0], c2[1]), fmaf(-mn_f[0][ch], sx, acc_g));
-    acc_g8 = fmaf(sc_f[1][ch], limbs_to_float(c1[2], c1[3], c2[2], c2[3]), fmaf(-mn_f[1][ch], sx, acc_g8));
+    const float sx = xss[sb * 2] + xss[sb * 2 + 1];
+    acc_g = fmaf(sc_f[0][ch], f_g, fmaf(-mn_f[0][ch], sx, acc_g));
+    acc_g8 = fmaf(sc_f[1][ch], f_g8, fmaf(-mn_f[1][ch], sx, acc_g8));
   }
 }
 
 // Q6_K: chain (c, u) covers the 16-element groups 8c + 2q + u, q = 0..3; lane t owns q = t:
 // nibble t/2 of ql plane slot t%2 and bits 2t, 2t+1 of qh, merged per byte into a u8 in 0..63.
-__device__ __forceinline__ void group1_q6k(const uint8_t* xl, const float* xs16, const uint8_t* tg,
-                                           int kg, const Lane& L, float& acc_g, float& acc_g8) {
+__device__ __forceinline__ void group1_q6k(const uint8_t* xl, const float* xsc, const float* xss,
+                                           const uint8_t* tg, int kg, const Lane& L, float& acc_g,
+                                           float& acc_g8) {
   const int sh4 = 4 * (L.t >> 1);
   const int rot = (4 - 2 * L.t) & 31;  // rotate-left that brings bits 2t, 2t+1 of each byte to 4, 5
   const uint4 sc_g = lds16(tg + 3072 + L.g * 16);
@@ -218,9 +240,10 @@ __device__ __forceinline__ void group1_q6k(const uint8_t* xl, const float* xs16,
     const int bsh = 8 * (2 * (L.t & 1) + u);
     const float s_g = d_g * (float)(int)(int8_t)((wg >> bsh) & 0xFF);
     const float s_g8 = d_g8 * (float)(int)(int8_t)((wg8 >> bsh) & 0xFF);
-    const float sx32 = 32.0f * xs16[kg * 16 + grp];  // (q - 32): centre folded into the sum
-    acc_g = fmaf(s_g, limbs_to_float(c1[0], c1[1], c2[0], c2[1]) - sx32, acc_g);
-    acc_g8 = fmaf(s_g8, limbs_to_float(c1[2], c1[3], c2[2], c2[3]) - sx32, acc_g8);
+    const float xs = xsc[kg * 16 + grp];
+    const float sx32 = 32.0f * xss[kg * 16 + grp];  // (q - 32): centre folded into the sum
+    acc_g = fmaf(s_g, fmaf(limbs_to_float(c1[0], c1[1], c2[0], c2[1]), xs, -sx32), acc_g);
+    acc_g8 = fmaf(s_g8, fmaf(limbs_to_float(c1[2], c1[3], c2[2], c2[3]), xs, -sx32), acc_g8);
   }
 }
 
@@ -246,10 +269,12 @@ qgemv1_kernel(const Gemv1Args a) {
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + W * S * a.stride);
   uint8_t* xl = smem + W * S * a.stride + W * S * 8;  // first raw f32 x, then limbs (4 B / element)
   float* xf = reinterpret_cast<float*>(xl);
-  float* xs16 = reinterpret_cast<float*>(xl + (size_t)a.Kp * 4);  // 2^13 * sum(x/scale) per 16
-  float* red = xs16 + a.Kp / 16;   // [NP][W][16]
+  float* xsc = reinterpret_cast<float*>(xl + (size_t)a.Kp * 4);  // per-16 scale of the limbs
+  float* xss = xsc + a.Kp / 16;    // per-16 sum of the activations
+  float* red = xss + a.Kp / 16;    // [NP][W][16]
   float* tmp = red + NP * W * 16;  // [2 W] block reductions
   uint8_t* zero16 = reinterpret_cast<uint8_t*>(tmp + 2 * W);  // 16 zero bytes (W is a multiple of 8)
+  uint64_t* xbar = reinterpret_cast<uint64_t*>(zero16 + 16);  // arrival of a packed activation row
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   Lane L;
@@ -266,6 +291,7 @@ qgemv1_kernel(const Gemv1Args a) {
   pdl_launch_dependents();
   if (lane == 0) {
     for (int s = 0; s < S; ++s) mbar_init(my_bar + 8 * s, 1);
+    if (warp == 0) mbar_init(smem_u32(xbar), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncwarp();
@@ -308,85 +334,116 @@ qgemv1_kernel(const Gemv1Args a) {
   pdl_wait();
 
   // ---- activation prologue ------------------------------------------------------------------
+  float final_scale = 1.0f;
+  if (a.xp.limbs) {
+    // The producer already packed the row: three bulk copies bring limbs, scales and sums into
+    // shared memory; for an RMSNorm consumer the per-16 sums of squares are added in index
+    // order and 1/rms becomes the final factor.
+    __syncthreads();  // xbar initialised
+    if (threadIdx.x == 0) {
+      const uint32_t nb = (uint32_t)a.Kp * 4u, ns = (uint32_t)(a.Kp / 16) * 4u;
+      mbar_expect_tx(smem_u32(xbar), nb + 2u * ns);
+      bulk_g2s(smem_u32(xl), a.xp.limbs, nb, smem_u32(xbar));
+      bulk_g2s(smem_u32(xsc), a.xp.xsc, ns, smem_u32(xbar));
+      bulk_g2s(smem_u32(xss), a.xp.xss, ns, smem_u32(xbar));
+    }
+    if (a.xp_norm) {
+      float ss = 0.f;
+      for (int i = threadIdx.x; i < (a.K + 15) / 16; i += THREADS) ss += a.xp.sumsq[i];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+      if (lane == 0) tmp[warp] = ss;
+      __syncthreads();
+      ss = 0.f;
+      for (int i = 0; i < W; ++i) ss += tmp[i];
+      final_scale = 1.0f / sqrtf(ss / (float)a.K + a.eps);
+    }
+    mbar_wait(smem_u32(xbar), 0u, a.status);
+  } else {
   // pass 1: v = x (+ residual) -> shared memory as f32;
-  //         sum of squares and max |v * norm_w| in one block reduction
-  float ss = 0.f, amax = 0.f;
-  {
-    for (int k = threadIdx.x; k < a.Kp; k += THREADS) {
-      float v = 0.f;
-      if (k < a.K) {
-        v = a.x[k];
-        if (a.xres) v += a.xres[k];
-        ss = fmaf(v, v, ss);
-        amax = fmaxf(amax, fabsf(a.norm_w ? v * a.norm_w[k] : v));
-      }
-      xf[k] = v;
-    }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
-    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-  }
-  if (lane == 0) { tmp[warp] = ss; tmp[W + warp] = amax; }
-  __syncthreads();
-  ss = 0.f; amax = 0.f;
-  for (int i = 0; i < W; ++i) { ss += tmp[i]; amax = fmaxf(amax, tmp[W + i]); }
-  float rms = 1.f;
-  if (a.norm_w) {
-    // rms_norm_fused_cpu_impl, fusor-ml/fusor/src/composite/normalization.rs:404-461
-    rms = sqrtf(ss / (float)a.K + a.eps);
-    amax = amax / rms * 1.0000005f;  // bound of |(v / rms) * w| with rounding slack
-  }
-  int ex = 0;
-  if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &ex);  // amax = f * 2^ex, f in [0.5, 1)
-  const float inv64 = ldexpf(64.0f, -ex);               // x * inv64 in (-64, 64)
-  const float out_scale = ldexpf(1.0f, ex - 13);        // 2^ex / (64 * 128)
-  // pass 2: each thread turns whole 8-element blocks, in place, into four int8 limbs per element:
-  // q = rint(v * 2^21) (|q| <= 2^27), l0 = q >> 21 (signed), u1, u2, u3 = the next three 7-bit
-  // fields (0..127), so v = (l0 + u1/2^7 + u2/2^14 + u3/2^21) up to 2^-22.
-  const float qscale = inv64 * 2097152.0f;
-  const float inv_rms = 1.0f / rms;  // v * (1/rms) instead of v / rms: within 1.5 ulp of the division
-  const int nblk = a.Kp >> 3;
-  for (int b0 = 0; b0 < nblk; b0 += THREADS) {
-    const int kb = b0 + threadIdx.x;
-    float sum = 0.f;
-    uint32_t wl[2][4];  // [half of the block][limb 3, 2, 1, 0] four elements per word
-    if (kb < nblk) {
-      const float4 va = *reinterpret_cast<const float4*>(xf + kb * 8);
-      const float4 vb = *reinterpret_cast<const float4*>(xf + kb * 8 + 4);
-      const float vin[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
-      uint32_t r[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int k = kb * 8 + i;
-        float v = vin[i];
-        if (a.norm_w && k < a.K) v = (v * inv_rms) * a.norm_w[k];
-        const int q = __float2int_rn(v * qscale);
-        sum += (float)q;
-        // fields at bits 0, 7, 14, 21 -> bytes 0..3 (byte 3 = bits 21..28 = l0 as s8)
-        r[i] = ((uint32_t)q & 0x7Fu) | (((uint32_t)q << 1) & 0x7F00u) | (((uint32_t)q << 2) & 0x7F0000u) |
-               (((uint32_t)q << 3) & 0xFF000000u);
-      }
-#pragma unroll
-      for (int hb = 0; hb < 2; ++hb) {
-        // 4 x 4 byte transpose: word j = byte j of the four elements
-        const uint32_t t01l = __byte_perm(r[4 * hb], r[4 * hb + 1], 0x5140), t23l = __byte_perm(r[4 * hb + 2], r[4 * hb + 3], 0x5140);
-        const uint32_t t01h = __byte_perm(r[4 * hb], r[4 * hb + 1], 0x7362), t23h = __byte_perm(r[4 * hb + 2], r[4 * hb + 3], 0x7362);
-        wl[hb][0] = __byte_perm(t01l, t23l, 0x5410);  // u3
-        wl[hb][1] = __byte_perm(t01l, t23l, 0x7632);  // u2
-        wl[hb][2] = __byte_perm(t01h, t23h, 0x5410);  // u1
-        wl[hb][3] = __byte_perm(t01h, t23h, 0x7632);  // l0
+    //         sum of squares and max |v * norm_w| in one block reduction
+    float ss = 0.f, amax = 0.f;
+    {
+      for (int k = threadIdx.x; k < a.Kp; k += THREADS) {
+        float v = 0.f;
+        if (k < a.K) {
+          v = a.x[k];
+          if (a.xres) v += a.xres[k];
+          ss = fmaf(v, v, ss);
+          amax = fmaxf(amax, fabsf(a.norm_w ? v * a.norm_w[k] : v));
+        }
+        xf[k] = v;
       }
     }
-    // per-16 sums in the units of the integer dot products (128 * sum(v) = sum(q) / 2^14)
-    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
-    if (kb < nblk) {
-      uint4* dst = reinterpret_cast<uint4*>(xl + (size_t)kb * 32);
-      dst[0] = make_uint4(wl[0][3], wl[1][3], wl[0][1], wl[1][1]);  // limb 0, limb 2
-      dst[1] = make_uint4(wl[0][2], wl[1][2], wl[0][0], wl[1][0]);  // limb 1, limb 3
-      if ((threadIdx.x & 1) == 0) xs16[kb >> 1] = sum * (1.0f / 16384.0f);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+      amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
     }
+    if (lane == 0) { tmp[warp] = ss; tmp[W + warp] = amax; }
+    __syncthreads();
+    ss = 0.f; amax = 0.f;
+    for (int i = 0; i < W; ++i) { ss += tmp[i]; amax = fmaxf(amax, tmp[W + i]); }
+    float rms = 1.f;
+    if (a.norm_w) {
+      // rms_norm_fused_cpu_impl, fusor-ml/fusor/src/composite/normalization.rs:404-461
+      rms = sqrtf(ss / (float)a.K + a.eps);
+      amax = amax / rms * 1.0000005f;  // bound of |(v / rms) * w| with rounding slack
+    }
+    int ex = 0;
+    if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &ex);  // amax = f * 2^ex, f in [0.5, 1)
+    const float inv64 = ldexpf(64.0f, -ex);               // x * inv64 in (-64, 64)
+    const float out_scale = ldexpf(1.0f, ex - 13);        // 2^ex / (64 * 128)
+    // pass 2: each thread turns whole 8-element blocks, in place, into four int8 limbs per element:
+    // q = rint(v * 2^21) (|q| <= 2^27), l0 = q >> 21 (signed), u1, u2, u3 = the next three 7-bit
+    // fields (0..127), so v = (l0 + u1/2^7 + u2/2^14 + u3/2^21) up to 2^-22.
+    const float qscale = inv64 * 2097152.0f;
+    const float inv_rms = 1.0f / rms;  // v * (1/rms) instead of v / rms: within 1.5 ulp of the division
+    const int nblk = a.Kp >> 3;
+    for (int b0 = 0; b0 < nblk; b0 += THREADS) {
+      const int kb = b0 + threadIdx.x;
+      float sum = 0.f;
+      uint32_t wl[2][4];  // [half of the block][limb 3, 2, 1, 0] four elements per word
+      if (kb < nblk) {
+        const float4 va = *reinterpret_cast<const float4*>(xf + kb * 8);
+        const float4 vb = *reinterpret_cast<const float4*>(xf + kb * 8 + 4);
+        const float vin[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+        uint32_t r[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int k = kb * 8 + i;
+          float v = vin[i];
+          if (a.norm_w && k < a.K) v = (v * inv_rms) * a.norm_w[k];
+          const int q = __float2int_rn(v * qscale);
+          sum += (float)q;
+          // fields at bits 0, 7, 14, 21 -> bytes 0..3 (byte 3 = bits 21..28 = l0 as s8)
+          r[i] = ((uint32_t)q & 0x7Fu) | (((uint32_t)q << 1) & 0x7F00u) | (((uint32_t)q << 2) & 0x7F0000u) |
+                 (((uint32_t)q << 3) & 0xFF000000u);
+        }
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {
+          // 4 x 4 byte transpose: word j = byte j of the four elements
+          const uint32_t t01l = __byte_perm(r[4 * hb], r[4 * hb + 1], 0x5140), t23l = __byte_perm(r[4 * hb + 2], r[4 * hb + 3], 0x5140);
+          const uint32_t t01h = __byte_perm(r[4 * hb], r[4 * hb + 1], 0x7362), t23h = __byte_perm(r[4 * hb + 2], r[4 * hb + 3], 0x7362);
+          wl[hb][0] = __byte_perm(t01l, t23l, 0x5410);  // u3
+          wl[hb][1] = __byte_perm(t01l, t23l, 0x7632);  // u2
+          wl[hb][2] = __byte_perm(t01h, t23h, 0x5410);  // u1
+          wl[hb][3] = __byte_perm(t01h, t23h, 0x7632);  // l0
+        }
+      }
+      // per-16 sums in the units of the integer dot products (128 * sum(v) = sum(q) / 2^14)
+      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+      if (kb < nblk) {
+        uint4* dst = reinterpret_cast<uint4*>(xl + (size_t)kb * 32);
+        dst[0] = make_uint4(wl[0][3], wl[1][3], wl[0][1], wl[1][1]);  // limb 0, limb 2
+        dst[1] = make_uint4(wl[0][2], wl[1][2], wl[0][0], wl[1][0]);  // limb 1, limb 3
+        if ((threadIdx.x & 1) == 0) {
+          xsc[kb >> 1] = out_scale;
+          xss[kb >> 1] = sum * (1.0f / 16384.0f) * out_scale;
+        }
+      }
+    }
+    __syncthreads();
   }
   __syncthreads();
 
@@ -409,10 +466,10 @@ qgemv1_kernel(const Gemv1Args a) {
         mbar_wait(my_bar + 8 * st, phase, a.status);
         const uint8_t* tg = my_ring + st * a.stride;
         const int kg = warp + W * kk;
-        if (type == FB200_Q4_K) group1_q4k(xl, xs16, tg, kg, L, acc_g, acc_g8);
-        else if (type == FB200_Q6_K) group1_q6k(xl, xs16, tg, kg, L, acc_g, acc_g8);
-        else if (type == FB200_Q8_0) group1_q8_0(xl, tg, kg, L, acc_g, acc_g8);
-        else group1_q4_0(xl, xs16, tg, kg, L, acc_g, acc_g8);
+        if (type == FB200_Q4_K) group1_q4k(xl, xsc, xss, tg, kg, L, acc_g, acc_g8);
+        else if (type == FB200_Q6_K) group1_q6k(xl, xsc, xss, tg, kg, L, acc_g, acc_g8);
+        else if (type == FB200_Q8_0) group1_q8_0(xl, xsc, tg, kg, L, acc_g, acc_g8);
+        else group1_q4_0(xl, xsc, xss, tg, kg, L, acc_g, acc_g8);
         // Every lane has read the stage (its loads precede this barrier in program order and
         // shared loads complete long before a refill from global memory can land).
         __syncwarp();
@@ -433,15 +490,16 @@ qgemv1_kernel(const Gemv1Args a) {
     if (threadIdx.x < 16) {
       const int r = threadIdx.x;
       const int n = tile * 16 + r;
-      if (n < n_out) {
-        float v[NP];
+      const bool valid = n < n_out;
+      float v[NP];
 #pragma unroll
-        for (int p = 0; p < NP; ++p) {
-          float s = 0.f;
-          for (int w = 0; w < W; ++w) s += red[(p * W + w) * 16 + r];
-          v[p] = s * out_scale;
-        }
-        float out;
+      for (int p = 0; p < NP; ++p) {
+        float s = 0.f;
+        for (int w = 0; w < W; ++w) s += red[(p * W + w) * 16 + r];
+        v[p] = s * final_scale;
+      }
+      float out = 0.f;
+      if (valid) {
         if (EPI == 2) {
           // silu(gate) * up, fusor-ml/fusor/src/composite/activations.rs:47-64
           const float gate = v[0];
@@ -452,11 +510,18 @@ qgemv1_kernel(const Gemv1Args a) {
         } else {
           out = v[0];
         }
-        yout[n] = out;
+        if (yout) yout[n] = out;
         if (a.argmax_key && sidx == 0) {
           const unsigned long long key = argmax_key_of(out, (uint32_t)n);
           if (key > best_key) best_key = key;
         }
+      }
+      if (a.yp.limbs && sidx == 0) {
+        float pv = out;
+        if (valid && a.yp_add) pv += a.yp_add[n];
+        const float nv = pv;
+        if (valid && a.yp_norm_w) pv *= a.yp_norm_w[n];
+        emit_packed16(a.yp, n, pv, nv, valid, 0x0000FFFFu);
       }
     }
   }
@@ -477,7 +542,7 @@ template <int EPI, int W>
 size_t gemv1_smem(int stages, int stride, int kp) {
   constexpr int NP = EPI == 2 ? 2 : 1;
   return (size_t)W * stages * stride + (size_t)W * stages * 8 + (size_t)kp * 4 + (size_t)kp / 16 * 4 +
-         (size_t)NP * W * 16 * 4 + (size_t)2 * W * 4 + 16 + 64;
+         (size_t)kp / 16 * 4 + (size_t)NP * W * 16 * 4 + (size_t)2 * W * 4 + 16 + 8 + 64;
 }
 
 template <int TYPE, int EPI, int W, int MINB>
@@ -571,7 +636,11 @@ int fb200_qgemv1_multi(fb200_device* dev, const fb200_qmatrix* const* ws, float*
   a.r1 = r1; a.r2 = r2;
   a.ngroups = ws[0]->ngroups; a.pair_tile_offset = 0;
   a.stages = 2; a.status = dev->status;
-  if (extra) a.argmax_key = extra->argmax_key;
+  if (extra) {
+    a.argmax_key = extra->argmax_key;
+    if (extra->x_packed) { a.xp = *extra->x_packed; a.xp_norm = extra->x_packed_norm ? 1 : 0; }
+    if (extra->y_packed) { a.yp = *extra->y_packed; a.yp_norm_w = extra->y_packed_norm_w; a.yp_add = extra->y_packed_add; }
+  }
   if (epi == FB200_EPI_SWIGLU) {
     a.seg[0].units = ws[0]->ntiles / 2;
     a.nunits = a.seg[0].units;
