@@ -32,6 +32,9 @@ sys.path.insert(0, ROOT)
 
 CFG = dict(n_layer=32, hidden=4096, ffn=14336, n_head=32, n_kv_head=8, head_dim=128, vocab=128256)
 PROMPT = 512
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the
+# profiler capture summarised under profiles/ (None until a capture of the current kernel exists)
+GEMV_TRAFFIC_BYTES = None
 Q4_K, Q6_K, F32 = 12, 14, 0
 BLOCK_BYTES = {Q4_K: 144, Q6_K: 210}
 METRIC = "Llama-3-8B Q4_K decode tok/s @1 GPU; quant GEMV HBM GB/s vs ~8 TB/s peak"
@@ -211,6 +214,50 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def gemv_roofline(kb, dev, torch, stream, reps):
+    """The dominant kernel timed alone: single-row product with SwiGLU epilogue over 16 distinct
+    gate+up matrices (16 x 66 MB, larger than L2, so every launch streams from HBM)."""
+    from kalosm_b200 import synth
+    f, e = CFG["ffn"], CFG["hidden"]
+    mats = []
+    for i in range(16):
+        raw = synth.random_qweights(900 + i, 0.02, 2 * f, e, Q4_K, device="cuda").cpu().numpy()
+        mats.append(kb.QMatrix.from_raw_bytes(dev, (2 * f, e), raw, Q4_K))
+    x = dev.tensor(np.random.default_rng(5).standard_normal((1, e)).astype(np.float32))
+    y = dev.empty((1, f))
+    for w in mats:
+        x.q_mat_mul(w, epilogue=kb.EPI_SWIGLU, out=y)
+    torch.cuda.synchronize()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record(stream)
+    for _ in range(reps):
+        for w in mats:
+            x.q_mat_mul(w, epilogue=kb.EPI_SWIGLU, out=y)
+    g1.record(stream)
+    torch.cuda.synchronize()
+    us = g0.elapsed_time(g1) * 1e3 / (reps * len(mats))
+    kbytes = qbytes(Q4_K, 2 * f, e)
+    peak, which = peaks()
+    achieved = kbytes / us / 1e3
+    for w in mats:
+        w.free()
+    return {"bound": "hbm", "kernel": "qgemv1_kernel<Q4_K, SwiGLU> on ffn gate+up [28672 x 4096]",
+            "achieved": achieved, "peak": peak, "peak_source": which, "unit": "GB/s",
+            "frac": achieved / peak, "us_per_launch": us, "bytes_per_launch": kbytes,
+            "traffic": GEMV_TRAFFIC_BYTES}
+
+
+def run_gemv_only(args):
+    """Only the dominant-kernel leg (1 GB on the device): the small case profiler captures use."""
+    import torch
+    import kalosm_b200 as kb
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    dev = kb.Device(0, stream.cuda_stream)
+    print(json.dumps({"roofline": gemv_roofline(kb, dev, torch, stream, max(1, args.gemv_reps))}), flush=True)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -276,36 +323,7 @@ def run_ours(args):
     ms_e2e = f0.elapsed_time(f1)
 
     # ---- dominant kernel alone: single-row GEMV over the gate/up matrices (SwiGLU epilogue) ----
-    roof = None
-    if rank == 0:
-        from kalosm_b200 import synth
-        f, e = CFG["ffn"], CFG["hidden"]
-        mats = []
-        for i in range(16):  # 16 x 66 MB: larger than L2, every launch streams from HBM
-            raw = synth.random_qweights(900 + i, 0.02, 2 * f, e, Q4_K, device="cuda").cpu().numpy()
-            mats.append(kb.QMatrix.from_raw_bytes(dev, (2 * f, e), raw, Q4_K))
-        x = dev.tensor(np.random.default_rng(5).standard_normal((1, e)).astype(np.float32))
-        y = dev.empty((1, f))
-        for w in mats:
-            x.q_mat_mul(w, epilogue=kb.EPI_SWIGLU, out=y)
-        torch.cuda.synchronize()
-        reps = 8
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record(stream)
-        for _ in range(reps):
-            for w in mats:
-                x.q_mat_mul(w, epilogue=kb.EPI_SWIGLU, out=y)
-        g1.record(stream)
-        torch.cuda.synchronize()
-        us = g0.elapsed_time(g1) * 1e3 / (reps * len(mats))
-        kbytes = qbytes(Q4_K, 2 * f, e)
-        peak, which = peaks()
-        achieved = kbytes / us / 1e3
-        roof = {"bound": "hbm", "kernel": "qgemv1_kernel<Q4_K, SwiGLU> on ffn gate+up [28672 x 4096]",
-                "achieved": achieved, "peak": peak, "peak_source": which, "unit": "GB/s",
-                "frac": achieved / peak, "us_per_launch": us, "bytes_per_launch": kbytes, "traffic": None}
-        for w in mats:
-            w.free()
+    roof = gemv_roofline(kb, dev, torch, stream, 8) if rank == 0 else None
 
     t_all = [ms, ms_e2e]
     if world > 1:
@@ -338,7 +356,9 @@ def run_ours(args):
             "data": "synthetic (seeded N(0, 0.02) weights encoded as Q4_K / Q6_K blocks on the GPU, uniform-random "
                     "token ids)",
             "config": {"workload": f"llama3-8b-shaped Q4_K_M-style greedy decode, batch {batch}, prompt {PROMPT}, "
-                                   f"{steps} decode steps per replica", "batch": batch, "prompt": PROMPT,
+                                   f"{steps} decode steps per replica" +
+                                   ("" if CFG["n_layer"] == 32 else f" (PROFILING CASE: {CFG['n_layer']} layers)"),
+                       "batch": batch, "prompt": PROMPT,
                        "l2": "4.9 GB of weights per step, far larger than L2",
                        "parallelism": "replicas only" if world > 1 else "single GPU"},
             "e2e": {"value": tok_s_e2e, "unit": "tok/s", "h2d_bytes_per_step": 4 * batch,
@@ -361,9 +381,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--layers", type=int, default=CFG["n_layer"],
+                    help="decoder layers of the model (fewer than 32 only for profiler captures; not a bench value)")
+    ap.add_argument("--gemv-only", action="store_true", help="run only the dominant-kernel leg")
+    ap.add_argument("--gemv-reps", type=int, default=8)
     args = ap.parse_args()
+    CFG["n_layer"] = args.layers
     if args.impl == "reference":
         run_reference(args)
+    elif args.gemv_only:
+        run_gemv_only(args)
     else:
         run_ours(args)
 

@@ -93,6 +93,7 @@ int fb200_device_destroy(fb200_device* dev) {
   if (dev->stage) cudaFree(dev->stage);
   if (dev->normed) cudaFree(dev->normed);
   if (dev->status) cudaFree(dev->status);
+  if (dev->fused) cudaFree(dev->fused);
   if (dev->own_stream) cudaStreamDestroy(dev->stream);
   delete dev;
   return FB200_OK;

@@ -298,291 +298,6 @@ int kv_capacity_rule(int required, int max_len) {
 // earlier decode steps, never by the kernels just before this one) into shared memory with
 // cp.async BEFORE griddepcontrol.wait, so the cache streams in while the q/k/v projection is
 // still running; only q and the new k, v rows are read after the wait.
-struct DecArgs {
-  const float* q;       // [B, H, D]   (not yet rotated)
-  const float* k_new;   // [B, Hkv, D] (not yet rotated)
-  const float* v_new;   // [B, Hkv, D]
-  __half* kc;           // [B, Hkv, cap, D]
-  __half* vc;
-  const float* rope_cos;  // [ctx, D/2]
-  const float* rope_sin;
-  const int* pos_dev;   // position of the new token = number of cached keys
-  float* part;          // [nsplit][B * H][D + 2]
-  float* out;           // [B, H * D]
-  int* done;            // [B * Hkv] arrival counters, zero between launches
-  fb200_packed_act out_packed;  // optional: the merged rows also in packed form (row of H * D)
-  int b, h, hkv, groups, cap, nsplit;
-  float scale;
-};
-
-constexpr int DEC_CH = 128;  // keys per shared-memory chunk
-
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
-  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() {
-  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
-}
-
-template <int D>
-__global__ void __launch_bounds__(ATT_THREADS)
-attn_decode_kernel(const DecArgs a) {
-  constexpr int KSTR = D * 2 + 64;   // bytes per staged row: consecutive keys land 64 B apart mod 128
-  constexpr int DV = D / 32;
-  constexpr int NC = D / 8;          // 16-byte chunks per row
-  extern __shared__ __align__(128) uint8_t dsm[];
-  uint8_t* kbuf = dsm;                                   // [DEC_CH][KSTR]
-  uint8_t* vbuf = dsm + DEC_CH * KSTR;                   // [DEC_CH][KSTR]
-  float (*qs)[D] = reinterpret_cast<float (*)[D]>(dsm + 2 * DEC_CH * KSTR);          // [ROWS][D]
-  float (*sc)[DEC_CH] = reinterpret_cast<float (*)[DEC_CH]>(qs + ROWS);              // [ROWS][DEC_CH]
-  float (*ored)[ROWS][D] = reinterpret_cast<float (*)[ROWS][D]>(dsm);                // aliases kbuf/vbuf
-  __shared__ float alpha[ROWS], row_m[ROWS], row_l[ROWS];
-  __shared__ float wsplit[ROWS][32], inv_l[ROWS];
-  __shared__ int is_last;
-  static_assert((ATT_THREADS / 32) * ROWS * D * 4 <= 2 * DEC_CH * KSTR, "reduction buffer must fit the staging area");
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  att_pdl_launch();
-  int bid = blockIdx.x;
-  const int split = bid % a.nsplit; bid /= a.nsplit;
-  const int kvh = bid % a.hkv;
-  const int bi = bid / a.hkv;
-  const int nrows = a.groups;
-  const int pos = *a.pos_dev;
-  const int skv = pos + 1;
-  const int per = (skv + a.nsplit - 1) / a.nsplit;
-  const int kbeg = min(skv, split * per), kend = min(skv, kbeg + per);
-  __half* kb = a.kc + ((size_t)bi * a.hkv + kvh) * (size_t)a.cap * D;
-  __half* vb = a.vc + ((size_t)bi * a.hkv + kvh) * (size_t)a.cap * D;
-
-  // stage chunk [c0, c0 + cn) of the cached rows (the new row `pos` is filled in separately)
-  auto stage = [&](int c0, int cn) {
-    for (int i = tid; i < cn * NC * 2; i += ATT_THREADS) {
-      const int which = i / (cn * NC), rem = i - which * (cn * NC);
-      const int j = rem / NC, c = rem - j * NC;
-      if (c0 + j == pos) continue;
-      const __half* src = (which ? vb : kb) + (size_t)(c0 + j) * D + c * 8;
-      cp_async16((which ? vbuf : kbuf) + j * KSTR + c * 16, src);
-    }
-  };
-  const int cn0 = min(DEC_CH, kend - kbeg);
-  if (cn0 > 0) stage(kbeg, cn0);
-  if (tid < ROWS) { row_m[tid] = -INFINITY; row_l[tid] = 0.f; }
-
-  att_pdl_wait();  // q, k_new, v_new come from the projection kernel before this one
-
-  for (int i = tid; i < ROWS * D; i += ATT_THREADS) {
-    const int r = i / D, e = i % D;
-    float v = 0.f;
-    if (r < nrows) {
-      const float* qr = a.q + ((size_t)bi * a.h + kvh * a.groups + r) * D;
-      // interleaved RoPE at the new position (fusor-ml/fusor/src/composite/rope.rs:77-108)
-      const float self = qr[e], other = qr[e ^ 1];
-      const float c = a.rope_cos[(size_t)pos * (D / 2) + (e >> 1)];
-      const float sn = a.rope_sin[(size_t)pos * (D / 2) + (e >> 1)];
-      v = (e & 1) ? __fadd_rn(__fmul_rn(other, sn), __fmul_rn(self, c))
-                  : __fsub_rn(__fmul_rn(self, c), __fmul_rn(other, sn));
-    }
-    qs[r][e] = v;
-  }
-  const bool has_new = kbeg <= pos && pos < kend;
-  if (has_new && tid < D / 2) {
-    // append the new position (KvCache::append, fusor-ml/fusor/src/cache/kv_cache.rs:50-62)
-    const int p = tid;
-    const float* kn = a.k_new + ((size_t)bi * a.hkv + kvh) * D;
-    const float* vn = a.v_new + ((size_t)bi * a.hkv + kvh) * D;
-    const float c = a.rope_cos[(size_t)pos * (D / 2) + p], sn = a.rope_sin[(size_t)pos * (D / 2) + p];
-    const float x0 = kn[2 * p], x1 = kn[2 * p + 1];
-    const __half2 kh = __floats2half2_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn)),
-                                         __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c)));
-    const __half2 vh = __floats2half2_rn(vn[2 * p], vn[2 * p + 1]);
-    *reinterpret_cast<__half2*>(kb + (size_t)pos * D + 2 * p) = kh;
-    *reinterpret_cast<__half2*>(vb + (size_t)pos * D + 2 * p) = vh;
-    if (pos - kbeg < DEC_CH) {
-      *reinterpret_cast<__half2*>(kbuf + (pos - kbeg) * KSTR + 4 * p) = kh;
-      *reinterpret_cast<__half2*>(vbuf + (pos - kbeg) * KSTR + 4 * p) = vh;
-    }
-  }
-
-  float o[ROWS][DV];
-#pragma unroll
-  for (int r = 0; r < ROWS; ++r)
-#pragma unroll
-    for (int e = 0; e < DV; ++e) o[r][e] = 0.f;
-
-  for (int c0 = kbeg; c0 < kend; c0 += DEC_CH) {
-    const int cn = min(DEC_CH, kend - c0);
-    if (c0 > kbeg) {
-      __syncthreads();  // the previous chunk has been consumed
-      stage(c0, cn);
-      if (has_new && pos >= c0 && pos < c0 + cn && tid < D / 2) {
-        *reinterpret_cast<__half2*>(kbuf + (pos - c0) * KSTR + 4 * tid) =
-            *reinterpret_cast<const __half2*>(kb + (size_t)pos * D + 2 * tid);
-        *reinterpret_cast<__half2*>(vbuf + (pos - c0) * KSTR + 4 * tid) =
-            *reinterpret_cast<const __half2*>(vb + (size_t)pos * D + 2 * tid);
-      }
-    }
-    cp_async_wait_all();
-    __syncthreads();
-    // ---- scores: 4 lanes per key (16-byte chunks sub, sub + 4, ...), 64 keys per CTA pass
-    for (int j0 = 0; j0 < cn; j0 += 64) {
-      const int j = j0 + warp * 8 + (lane >> 2);
-      const int sub = lane & 3;
-      float acc[ROWS];
-#pragma unroll
-      for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
-      if (j < cn) {
-#pragma unroll
-        for (int v8 = 0; v8 < NC / 4; ++v8) {
-          const int c = v8 * 4 + sub;
-          const uint4 raw = *reinterpret_cast<const uint4*>(kbuf + j * KSTR + c * 16);
-          const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
-          float kf[8];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 f = __half22float2(h2[i]);
-            kf[2 * i] = f.x; kf[2 * i + 1] = f.y;
-          }
-#pragma unroll
-          for (int r = 0; r < ROWS; ++r) {
-            const float* qr = &qs[r][c * 8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[r] = fmaf(qr[i], kf[i], acc[r]);
-          }
-        }
-      }
-#pragma unroll
-      for (int r = 0; r < ROWS; ++r) {
-        acc[r] += __shfl_xor_sync(0xFFFFFFFFu, acc[r], 1);
-        acc[r] += __shfl_xor_sync(0xFFFFFFFFu, acc[r], 2);
-      }
-      if (j < cn && sub == 0) {
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) sc[r][j] = acc[r] * a.scale;
-      }
-    }
-    __syncthreads();
-    // ---- online softmax statistics, warp r owns row r
-    {
-      const int r = warp;
-      float mx = -INFINITY;
-      for (int j = lane; j < cn; j += 32) mx = fmaxf(mx, sc[r][j]);
-#pragma unroll
-      for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o2));
-      const float m_old = row_m[r];
-      const float m_new = fmaxf(m_old, mx);
-      float sum = 0.f;
-      for (int j = lane; j < cn; j += 32) {
-        const float p = (m_new == -INFINITY) ? 0.f : __expf(sc[r][j] - m_new);
-        sc[r][j] = p;
-        sum += p;
-      }
-#pragma unroll
-      for (int o2 = 16; o2 > 0; o2 >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o2);
-      if (lane == 0) {
-        const float al = (m_old == -INFINITY) ? 0.f : __expf(m_old - m_new);
-        alpha[r] = al;
-        row_l[r] = row_l[r] * al + sum;
-        row_m[r] = m_new;
-      }
-    }
-    __syncthreads();
-    // ---- o = o * alpha + p . v; warp w takes keys w, w + 8, ...; lane owns DV dims
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-      const float al = alpha[r];
-#pragma unroll
-      for (int e = 0; e < DV; ++e) o[r][e] *= al;
-    }
-    for (int j = warp; j < cn; j += ATT_THREADS / 32) {
-      float vf[DV];
-      const uint8_t* vp = vbuf + j * KSTR + lane * DV * 2;
-      if constexpr (DV == 4) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(vp);
-        const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
-        const float2 f0 = __half22float2(h2[0]), f1 = __half22float2(h2[1]);
-        vf[0] = f0.x; vf[1] = f0.y; vf[2] = f1.x; vf[3] = f1.y;
-      } else {
-        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(vp));
-        vf[0] = f0.x; vf[1] = f0.y;
-      }
-#pragma unroll
-      for (int r = 0; r < ROWS; ++r) {
-        const float p = sc[r][j];
-#pragma unroll
-        for (int e = 0; e < DV; ++e) o[r][e] = fmaf(p, vf[e], o[r][e]);
-      }
-    }
-  }
-  __syncthreads();  // staging area is free: reuse it for the cross-warp reduction
-#pragma unroll
-  for (int r = 0; r < ROWS; ++r)
-#pragma unroll
-    for (int e = 0; e < DV; ++e) ored[warp][r][lane * DV + e] = o[r][e];
-  __syncthreads();
-  const size_t rows_all = (size_t)a.b * a.h;
-  for (int i = tid; i < nrows * D; i += ATT_THREADS) {
-    const int r = i / D, e = i % D;
-    float s = 0.f;
-#pragma unroll
-    for (int w = 0; w < ATT_THREADS / 32; ++w) s += ored[w][r][e];
-    const size_t grow = (size_t)bi * a.h + kvh * a.groups + r;
-    float* pp = a.part + ((size_t)split * rows_all + grow) * (D + 2);
-    pp[e] = s;
-    if (e == 0) { pp[D] = row_m[r]; pp[D + 1] = row_l[r]; }
-  }
-  // ---- the split that arrives last merges all partials of this (batch, kv head) in split order
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const int old = atomicAdd(a.done + bi * a.hkv + kvh, 1);
-    is_last = (old == a.nsplit - 1);
-    if (is_last) a.done[bi * a.hkv + kvh] = 0;
-  }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  for (int i = tid; i < nrows * 32; i += ATT_THREADS) {
-    const int r = i >> 5, s0 = i & 31;
-    const size_t grow = (size_t)bi * a.h + kvh * a.groups + r;
-    wsplit[r][s0] = s0 < a.nsplit ? __ldcg(a.part + ((size_t)s0 * rows_all + grow) * (D + 2) + D) : -INFINITY;
-  }
-  __syncthreads();
-  if (warp < nrows) {
-    // warp r: weights exp(m_s - max m) and the merged normaliser of row r
-    const int r = warp;
-    const size_t grow = (size_t)bi * a.h + kvh * a.groups + r;
-    const float m = wsplit[r][lane];
-    float mx = m;
-#pragma unroll
-    for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o2));
-    const float wgt = (m == -INFINITY) ? 0.f : __expf(m - mx);
-    float l = lane < a.nsplit ? __ldcg(a.part + ((size_t)lane * rows_all + grow) * (D + 2) + D + 1) * wgt : 0.f;
-#pragma unroll
-    for (int o2 = 16; o2 > 0; o2 >>= 1) l += __shfl_xor_sync(0xFFFFFFFFu, l, o2);
-    wsplit[r][lane] = wgt;
-    if (lane == 0) inv_l[r] = l > 0.f ? 1.0f / l : 0.f;
-  }
-  __syncthreads();
-  for (int i0 = 0; i0 < nrows * D; i0 += ATT_THREADS) {
-    const int i = i0 + tid;
-    const bool valid = i < nrows * D;
-    const int r = valid ? i / D : 0, e = i % D;
-    const size_t grow = (size_t)bi * a.h + kvh * a.groups + r;
-    float acc = 0.f;
-    if (valid) {
-#pragma unroll 8
-      for (int s0 = 0; s0 < a.nsplit; ++s0)
-        acc = fmaf(__ldcg(a.part + ((size_t)s0 * rows_all + grow) * (D + 2) + e), wsplit[r][s0], acc);
-      acc *= inv_l[r];
-      if (a.out) a.out[grow * D + e] = acc;
-    }
-    if (a.out_packed.limbs && bi == 0)  // packed rows are single-sequence
-      emit_packed16(a.out_packed, (int)(grow * D) + e, acc, acc, valid, 0xFFFFFFFFu);
-  }
-}
-
 }  // namespace
 
 int fb200_attention_scratch_bytes(int b, int h, int sq, int d, int nsplit, size_t* out) {
@@ -624,35 +339,6 @@ int fb200_launch_attention(fb200_device* dev, const float* q, const __half* k, c
     FB_LAUNCH_CHECK(dev);
   }
   return FB200_OK;
-}
-
-// One new position per sequence: RoPE(q), RoPE(k) + fp16 append, split-KV attention over the
-// cache. Every split writes (o, m, l) partials [nsplit][B * H][D + 2]; the last split of a
-// (batch, kv head) to finish merges them into out [B, H * D] (`done`: zeroed arrival counters,
-// one per (batch, kv head)). Needs H / Hkv <= 8 (one row tile per KV head). The position is
-// read from pos_dev.
-int fb200_launch_attention_decode(fb200_device* dev, const float* q, const float* k_new,
-                                  const float* v_new, __half* kc, __half* vc, int b, int h, int hkv,
-                                  const int* pos_dev, int cap, int d, float scale,
-                                  const float* rope_cos, const float* rope_sin, float* part,
-                                  int nsplit, int* done, float* out, const fb200_packed_act* out_packed) {
-  if (h % hkv || h / hkv > ROWS || (d != 64 && d != 128) || nsplit < 1 || nsplit > 32)
-    return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "attention_decode: unsupported head layout");
-  DecArgs a = {};
-  a.q = q; a.k_new = k_new; a.v_new = v_new; a.kc = kc; a.vc = vc; a.rope_cos = rope_cos; a.rope_sin = rope_sin;
-  a.pos_dev = pos_dev; a.part = part; a.out = out; a.done = done;
-  if (out_packed) a.out_packed = *out_packed;
-  a.b = b; a.h = h; a.hkv = hkv; a.groups = h / hkv; a.cap = cap; a.nsplit = nsplit; a.scale = scale;
-  const unsigned grid = (unsigned)(b * hkv * nsplit);
-  const size_t smem = (size_t)2 * DEC_CH * (d * 2 + 64) + (size_t)ROWS * d * 4 + (size_t)ROWS * DEC_CH * 4;
-  static bool configured[64] = {false};
-  if (!configured[dev->ordinal & 63]) {
-    FB_CUDA(dev, cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
-    FB_CUDA(dev, cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
-    configured[dev->ordinal & 63] = true;
-  }
-  if (d == 128) return fb200_launch(dev, attn_decode_kernel<128>, dim3(grid), dim3(ATT_THREADS), smem, true, a);
-  return fb200_launch(dev, attn_decode_kernel<64>, dim3(grid), dim3(ATT_THREADS), smem, true, a);
 }
 
 int fb200_launch_kv_append(fb200_device* dev, const float* k, const float* v, __half* kc, __half* vc,

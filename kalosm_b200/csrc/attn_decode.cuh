@@ -1,0 +1,322 @@
+// Decode-time attention for one new position per sequence, as a device function shared by the
+// stand-alone kernel and the fused decode-step kernel: RoPE(q), RoPE(k) + fp16 append,
+// split-KV online softmax over the cache, partials merged by the split that arrives last.
+// Attention math as fusor-ml/fusor/src/composite/attention.rs (scaled q.k, softmax, .v) with
+// interleaved RoPE (fusor-ml/fusor/src/composite/rope.rs:77-108) and the KV append of
+// fusor-ml/fusor/src/cache/kv_cache.rs:50-62. Everything another CTA may have written during
+// the same kernel is read through L2 (ld.global.cg / cp.async.cg).
+#pragma once
+
+#include "common.cuh"
+#include "packed_act.cuh"
+
+// Arguments of one decode-attention launch / phase (all device pointers).
+struct fb200_dec_args {
+  const float* q;       // [B, H, D]   (not yet rotated)
+  const float* k_new;   // [B, Hkv, D] (not yet rotated)
+  const float* v_new;   // [B, Hkv, D]
+  __half* kc;           // [B, Hkv, cap, D]
+  __half* vc;
+  const float* rope_cos;  // [ctx, D/2]
+  const float* rope_sin;
+  const int* pos_dev;   // position of the new token = number of cached keys
+  float* part;          // [nsplit][B * H][D + 2]
+  float* out;           // [B, H * D]
+  int* done;            // [B * Hkv] arrival counters, zero between launches
+  fb200_packed_act out_packed;  // optional: the merged rows also in packed form (row of H * D)
+  int b, h, hkv, groups, cap, nsplit;
+  float scale;
+};
+
+namespace {
+
+using DecArgs = fb200_dec_args;
+
+constexpr int DEC_ROWS = 8;       // query rows per KV head (H / Hkv <= 8)
+constexpr int DEC_THREADS = 256;  // threads per item
+
+
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+// Bytes of dynamic shared memory one item needs.
+__host__ __device__ constexpr size_t dec_smem_bytes(int d, int dec_ch) {
+  return (size_t)2 * dec_ch * (d * 2 + 64) + (size_t)DEC_ROWS * d * 4 + (size_t)DEC_ROWS * dec_ch * 4;
+}
+
+// Barrier of the 256 threads that work on an item: the whole CTA (BAR = 0) or a named barrier
+// when the CTA has more warps than the team.
+template <int BAR>
+__device__ __forceinline__ void dec_sync() {
+  if (BAR == 0) dec_sync<BAR>();
+  else asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(DEC_THREADS) : "memory");
+}
+
+// One (batch, kv head, split) item, executed by DEC_THREADS threads (tid = 0 .. DEC_THREADS - 1).
+// DEC_CH = keys per shared-memory chunk. PDL: the caller is a kernel launched with programmatic
+// stream serialization, whose predecessor produced q, k_new and v_new.
+template <int D, int DEC_CH, int BAR, bool PDL>
+__device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int tid) {
+  constexpr int ROWS = DEC_ROWS;
+  constexpr int ATT_THREADS = DEC_THREADS;
+  constexpr int KSTR = D * 2 + 64;   // bytes per staged row: consecutive keys land 64 B apart mod 128
+  constexpr int DV = D / 32;
+  constexpr int NC = D / 8;          // 16-byte chunks per row
+  uint8_t* kbuf = dsm;                                   // [DEC_CH][KSTR]
+  uint8_t* vbuf = dsm + DEC_CH * KSTR;                   // [DEC_CH][KSTR]
+  float (*qs)[D] = reinterpret_cast<float (*)[D]>(dsm + 2 * DEC_CH * KSTR);          // [ROWS][D]
+  float (*sc)[DEC_CH] = reinterpret_cast<float (*)[DEC_CH]>(qs + ROWS);              // [ROWS][DEC_CH]
+  float (*ored)[ROWS][D] = reinterpret_cast<float (*)[ROWS][D]>(dsm);                // aliases kbuf/vbuf
+  __shared__ float alpha[ROWS], row_m[ROWS], row_l[ROWS];
+  __shared__ float wsplit[ROWS][32], inv_l[ROWS];
+  __shared__ int is_last;
+  static_assert((ATT_THREADS / 32) * ROWS * D * 4 <= 2 * DEC_CH * KSTR, "reduction buffer must fit the staging area");
+
+  const int warp = tid >> 5, lane = tid & 31;
+  int bid = item;
+  const int split = bid % a.nsplit; bid /= a.nsplit;
+  const int kvh = bid % a.hkv;
+  const int bi = bid / a.hkv;
+  const int nrows = a.groups;
+  const int pos = __ldcg(a.pos_dev);
+  const int skv = pos + 1;
+  const int per = (skv + a.nsplit - 1) / a.nsplit;
+  const int kbeg = min(skv, split * per), kend = min(skv, kbeg + per);
+  __half* kb = a.kc + ((size_t)bi * a.hkv + kvh) * (size_t)a.cap * D;
+  __half* vb = a.vc + ((size_t)bi * a.hkv + kvh) * (size_t)a.cap * D;
+
+  // stage chunk [c0, c0 + cn) of the cached rows (the new row `pos` is filled in separately)
+  auto stage = [&](int c0, int cn) {
+    for (int i = tid; i < cn * NC * 2; i += ATT_THREADS) {
+      const int which = i / (cn * NC), rem = i - which * (cn * NC);
+      const int j = rem / NC, c = rem - j * NC;
+      if (c0 + j == pos) continue;
+      const __half* src = (which ? vb : kb) + (size_t)(c0 + j) * D + c * 8;
+      cp_async16((which ? vbuf : kbuf) + j * KSTR + c * 16, src);
+    }
+  };
+  const int cn0 = min(DEC_CH, kend - kbeg);
+  if (cn0 > 0) stage(kbeg, cn0);
+  if (tid < ROWS) { row_m[tid] = -INFINITY; row_l[tid] = 0.f; }
+
+  if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");  // q, k_new, v_new come from the kernel before this one
+
+  for (int i = tid; i < ROWS * D; i += ATT_THREADS) {
+    const int r = i / D, e = i % D;
+    float v = 0.f;
+    if (r < nrows) {
+      const float* qr = a.q + ((size_t)bi * a.h + kvh * a.groups + r) * D;
+      // interleaved RoPE at the new position (fusor-ml/fusor/src/composite/rope.rs:77-108)
+      const float self = __ldcg(qr + e), other = __ldcg(qr + (e ^ 1));
+      const float c = a.rope_cos[(size_t)pos * (D / 2) + (e >> 1)];
+      const float sn = a.rope_sin[(size_t)pos * (D / 2) + (e >> 1)];
+      v = (e & 1) ? __fadd_rn(__fmul_rn(other, sn), __fmul_rn(self, c))
+                  : __fsub_rn(__fmul_rn(self, c), __fmul_rn(other, sn));
+    }
+    qs[r][e] = v;
+  }
+  const bool has_new = kbeg <= pos && pos < kend;
+  if (has_new && tid < D / 2) {
+    // append the new position (KvCache::append, fusor-ml/fusor/src/cache/kv_cache.rs:50-62)
+    const int p = tid;
+    const float* kn = a.k_new + ((size_t)bi * a.hkv + kvh) * D;
+    const float* vn = a.v_new + ((size_t)bi * a.hkv + kvh) * D;
+    const float c = a.rope_cos[(size_t)pos * (D / 2) + p], sn = a.rope_sin[(size_t)pos * (D / 2) + p];
+    const float x0 = __ldcg(kn + 2 * p), x1 = __ldcg(kn + 2 * p + 1);
+    const __half2 kh = __floats2half2_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn)),
+                                         __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c)));
+    const __half2 vh = __floats2half2_rn(__ldcg(vn + 2 * p), __ldcg(vn + 2 * p + 1));
+    *reinterpret_cast<__half2*>(kb + (size_t)pos * D + 2 * p) = kh;
+    *reinterpret_cast<__half2*>(vb + (size_t)pos * D + 2 * p) = vh;
+    if (pos - kbeg < DEC_CH) {
+      *reinterpret_cast<__half2*>(kbuf + (pos - kbeg) * KSTR + 4 * p) = kh;
+      *reinterpret_cast<__half2*>(vbuf + (pos - kbeg) * KSTR + 4 * p) = vh;
+    }
+  }
+
+  float o[ROWS][DV];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+    for (int e = 0; e < DV; ++e) o[r][e] = 0.f;
+
+  for (int c0 = kbeg; c0 < kend; c0 += DEC_CH) {
+    const int cn = min(DEC_CH, kend - c0);
+    if (c0 > kbeg) {
+      dec_sync<BAR>();  // the previous chunk has been consumed
+      stage(c0, cn);
+      if (has_new && pos >= c0 && pos < c0 + cn && tid < D / 2) {
+        *reinterpret_cast<__half2*>(kbuf + (pos - c0) * KSTR + 4 * tid) =
+            *reinterpret_cast<const __half2*>(kb + (size_t)pos * D + 2 * tid);
+        *reinterpret_cast<__half2*>(vbuf + (pos - c0) * KSTR + 4 * tid) =
+            *reinterpret_cast<const __half2*>(vb + (size_t)pos * D + 2 * tid);
+      }
+    }
+    cp_async_wait_all();
+    dec_sync<BAR>();
+    // ---- scores: 4 lanes per key (16-byte chunks sub, sub + 4, ...), 64 keys per CTA pass
+    for (int j0 = 0; j0 < cn; j0 += 64) {
+      const int j = j0 + warp * 8 + (lane >> 2);
+      const int sub = lane & 3;
+      float acc[ROWS];
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
+      if (j < cn) {
+#pragma unroll
+        for (int v8 = 0; v8 < NC / 4; ++v8) {
+          const int c = v8 * 4 + sub;
+          const uint4 raw = *reinterpret_cast<const uint4*>(kbuf + j * KSTR + c * 16);
+          const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+          float kf[8];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h2[i]);
+            kf[2 * i] = f.x; kf[2 * i + 1] = f.y;
+          }
+#pragma unroll
+          for (int r = 0; r < ROWS; ++r) {
+            const float* qr = &qs[r][c * 8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[r] = fmaf(qr[i], kf[i], acc[r]);
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        acc[r] += __shfl_xor_sync(0xFFFFFFFFu, acc[r], 1);
+        acc[r] += __shfl_xor_sync(0xFFFFFFFFu, acc[r], 2);
+      }
+      if (j < cn && sub == 0) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) sc[r][j] = acc[r] * a.scale;
+      }
+    }
+    dec_sync<BAR>();
+    // ---- online softmax statistics, warp r owns row r
+    {
+      const int r = warp;
+      float mx = -INFINITY;
+      for (int j = lane; j < cn; j += 32) mx = fmaxf(mx, sc[r][j]);
+#pragma unroll
+      for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o2));
+      const float m_old = row_m[r];
+      const float m_new = fmaxf(m_old, mx);
+      float sum = 0.f;
+      for (int j = lane; j < cn; j += 32) {
+        const float p = (m_new == -INFINITY) ? 0.f : __expf(sc[r][j] - m_new);
+        sc[r][j] = p;
+        sum += p;
+      }
+#pragma unroll
+      for (int o2 = 16; o2 > 0; o2 >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o2);
+      if (lane == 0) {
+        const float al = (m_old == -INFINITY) ? 0.f : __expf(m_old - m_new);
+        alpha[r] = al;
+        row_l[r] = row_l[r] * al + sum;
+        row_m[r] = m_new;
+      }
+    }
+    dec_sync<BAR>();
+    // ---- o = o * alpha + p . v; warp w takes keys w, w + 8, ...; lane owns DV dims
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const float al = alpha[r];
+#pragma unroll
+      for (int e = 0; e < DV; ++e) o[r][e] *= al;
+    }
+    for (int j = warp; j < cn; j += ATT_THREADS / 32) {
+      float vf[DV];
+      const uint8_t* vp = vbuf + j * KSTR + lane * DV * 2;
+      if constexpr (DV == 4) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(vp);
+        const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+        const float2 f0 = __half22float2(h2[0]), f1 = __half22float2(h2[1]);
+        vf[0] = f0.x; vf[1] = f0.y; vf[2] = f1.x; vf[3] = f1.y;
+      } else {
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(vp));
+        vf[0] = f0.x; vf[1] = f0.y;
+      }
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        const float p = sc[r][j];
+#pragma unroll
+        for (int e = 0; e < DV; ++e) o[r][e] = fmaf(p, vf[e], o[r][e]);
+      }
+    }
+  }
+  dec_sync<BAR>();  // staging area is free: reuse it for the cross-warp reduction
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+    for (int e = 0; e < DV; ++e) ored[warp][r][lane * DV + e] = o[r][e];
+  dec_sync<BAR>();
+  const size_t rows_all = (size_t)a.b * a.h;
+  for (int i = tid; i < nrows * D; i += ATT_THREADS) {
+    const int r = i / D, e = i % D;
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATT_THREADS / 32; ++w) s += ored[w][r][e];
+    const size_t grow = (size_t)bi * a.h + kvh * a.groups + r;
+    float* pp = a.part + ((size_t)split * rows_all + grow) * (D + 2);
+    pp[e] = s;
+    if (e == 0) { pp[D] = row_m[r]; pp[D + 1] = row_l[r]; }
+  }
+  // ---- the split that arrives last merges all partials of this (batch, kv head) in split order
+  __threadfence();
+  dec_sync<BAR>();
+  if (tid == 0) {
+    const int old = atomicAdd(a.done + bi * a.hkv + kvh, 1);
+    is_last = (old == a.nsplit - 1);
+    if (is_last) a.done[bi * a.hkv + kvh] = 0;
+  }
+  dec_sync<BAR>();
+  if (!is_last) return;
+  __threadfence();
+  for (int i = tid; i < nrows * 32; i += ATT_THREADS) {
+    const int r = i >> 5, s0 = i & 31;
+    const size_t grow = (size_t)bi * a.h + kvh * a.groups + r;
+    wsplit[r][s0] = s0 < a.nsplit ? __ldcg(a.part + ((size_t)s0 * rows_all + grow) * (D + 2) + D) : -INFINITY;
+  }
+  dec_sync<BAR>();
+  if (warp < nrows) {
+    // warp r: weights exp(m_s - max m) and the merged normaliser of row r
+    const int r = warp;
+    const size_t grow = (size_t)bi * a.h + kvh * a.groups + r;
+    const float m = wsplit[r][lane];
+    float mx = m;
+#pragma unroll
+    for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o2));
+    const float wgt = (m == -INFINITY) ? 0.f : __expf(m - mx);
+    float l = lane < a.nsplit ? __ldcg(a.part + ((size_t)lane * rows_all + grow) * (D + 2) + D + 1) * wgt : 0.f;
+#pragma unroll
+    for (int o2 = 16; o2 > 0; o2 >>= 1) l += __shfl_xor_sync(0xFFFFFFFFu, l, o2);
+    wsplit[r][lane] = wgt;
+    if (lane == 0) inv_l[r] = l > 0.f ? 1.0f / l : 0.f;
+  }
+  dec_sync<BAR>();
+  for (int i0 = 0; i0 < nrows * D; i0 += ATT_THREADS) {
+    const int i = i0 + tid;
+    const bool valid = i < nrows * D;
+    const int r = valid ? i / D : 0, e = i % D;
+    const size_t grow = (size_t)bi * a.h + kvh * a.groups + r;
+    float acc = 0.f;
+    if (valid) {
+#pragma unroll 8
+      for (int s0 = 0; s0 < a.nsplit; ++s0)
+        acc = fmaf(__ldcg(a.part + ((size_t)s0 * rows_all + grow) * (D + 2) + e), wsplit[r][s0], acc);
+      acc *= inv_l[r];
+      if (a.out) a.out[grow * D + e] = acc;
+    }
+    // packed rows are single-sequence; nrows * D is a multiple of 32, so `valid` is warp-uniform
+    if (a.out_packed.limbs && bi == 0 && valid)
+      emit_packed16(a.out_packed, (int)(grow * D) + e, acc, acc, true, 0xFFFFFFFFu);
+  }
+}
+
+}  // namespace

@@ -31,6 +31,9 @@ struct fb200_device {
   size_t stage_bytes = 0;
   // device status word (set by kernels that recover from a fault)
   int* status = nullptr;
+  // scratch of the fused decode-step kernel: grid barrier word, split-unit partials, counters
+  void* fused = nullptr;
+  size_t fused_bytes = 0;
 };
 
 // Quantised (or dense) weight matrix [N, K] in tile-interleaved device storage.

@@ -1,0 +1,729 @@
+// Fused decode step: one persistent cooperative kernel, one CTA per SM, runs a whole single-token
+// forward pass (or several in a row) as a program of phases separated by grid-wide barriers.
+//
+// Replaces, for one new position of one sequence, the reference's per-operation graph execution
+// (fusor-ml/core/src/compute_graph/resolve/run.rs:29-135) of the Llama decoder
+// (models/kalosm-llama/src/raw/mod.rs:925-1049): embedding, per layer q/k/v projections,
+// RoPE + KV append + attention, output projection, SwiGLU FFN with both residual adds, final
+// norm + output head + greedy argmax.
+//
+// Product phases stream the quantised weights exactly once from HBM:
+//  * stream-K: the tile-groups (16 rows x one K group) of all matrices of a phase form one
+//    list; every CTA takes an equal contiguous share and every warp an equal contiguous share
+//    of that, whatever the matrix shapes. A unit (16 output rows, or a gate/up pair of tiles)
+//    that straddles warps is summed through shared memory in warp order; one that straddles
+//    CTAs is summed in CTA order by the CTA that arrives last (arrival counter per unit), so
+//    results do not depend on timing;
+//  * each warp owns a ring of shared-memory slots filled by 1-D TMA bulk copies and mbarriers;
+//    when a warp has consumed its share it immediately fetches the first slots of its share of
+//    the NEXT product phase, so the weight stream continues across the grid barrier;
+//  * activations arrive packed (int8 limbs, per-16 scales and sums) and are copied to shared
+//    memory once per CTA; the per-tile-group math is that of the single-row kernel.
+// Everything another CTA wrote during the kernel is read through L2 (ld.global.cg).
+// All waits are bounded: a wait that gives up sets the device status word and the kernel runs to
+// its end without waiting again.
+#include <algorithm>
+#include <cstdlib>
+
+#include "fused_step.cuh"
+#include "qgemv1_groups.cuh"
+
+namespace {
+
+constexpr int FW = 16;             // warps per CTA
+constexpr int FT = FW * 32;        // threads per CTA
+constexpr int RING_BYTES = 6912;   // ring bytes per warp: 3 x 2304 (Q4_K) or 2 x 3456 (Q6_K)
+constexpr int MAX_STAGES = 4;
+constexpr int FUSED_DEC_CH = 64;   // keys per shared-memory chunk of the attention phase
+constexpr int SMEM_LIMIT = 227 * 1024;
+constexpr int STATIC_SMEM_RESERVE = 4096;  // static shared memory of the attention phase
+constexpr int DESC_WORDS = (int)((sizeof(fb200_fused_phase) + 15) / 16 * 4);  // 32-bit words per descriptor slot
+
+struct FusedArgs {
+  const fb200_fused_phase* prog;
+  int nphases, nsteps, record, first_gemv;
+  int xregion;     // bytes of the activation region (limbs, scales, sums; aliased by attention)
+  unsigned* bar;   // grid barrier arrival counter, zero at launch
+  float* gp;       // [grid][2][32] partial sums of units split across CTAs
+  int* counters;   // arrival counters per unit, zero between uses
+  int* status;
+  unsigned long long* trace;  // optional [nphases][8] time stamps of CTA 0 in the last step (ns)
+};
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Grid-wide barrier: every CTA adds one to a counter that only grows; generation n is complete
+// when the counter reaches n * gridDim.x. Bounded: after ~2^24 polls (seconds) or as soon as
+// another wait has given up, the CTA records the timeout and carries on.
+__device__ __forceinline__ void grid_barrier(const FusedArgs& A, unsigned& target, unsigned long long* arrive_max) {
+  __syncthreads();
+  target += gridDim.x;
+  if (threadIdx.x == 0) {
+    if (arrive_max) atomicMax(arrive_max, global_ns());
+    __threadfence();
+    atomicAdd(A.bar, 1u);
+    unsigned polls = 0;
+    while ((int)(ld_acquire_u32(A.bar) - target) < 0) {
+      ++polls;
+      if ((polls & 1023u) == 0u && __ldcg(A.status) != 0) break;
+      if (polls > (1u << 24)) { atomicExch(A.status, FB200_ERR_TIMEOUT); break; }
+    }
+    __threadfence();
+  }
+  __syncthreads();
+}
+
+// floor(i / d) for 0 <= i < 2^21 with rcp = 1 / d rounded to float: (i + 0.5) / d is at least
+// 0.5 / d away from every integer, far more than the rounding errors of the product.
+__device__ __forceinline__ int fdiv(int i, float rcp) { return __float2int_rz(((float)i + 0.5f) * rcp); }
+
+// The fields of a product phase the inner loops use, read once into registers.
+struct PhaseLocal {
+  int ng, npass, ipu, stride, stages, total, chunk, pair_off;
+  float rcp_ipu, rcp_ng;
+};
+__device__ __forceinline__ PhaseLocal phase_local(const fb200_fused_phase& P) {
+  PhaseLocal q;
+  q.ng = P.ngroups; q.npass = P.epi == FB200_EPI_SWIGLU ? 2 : 1; q.ipu = P.ipu; q.stride = P.stride;
+  q.stages = P.stages; q.total = P.total; q.chunk = P.chunk; q.pair_off = P.pair_off;
+  q.rcp_ipu = P.rcp_ipu; q.rcp_ng = P.rcp_ng;
+  return q;
+}
+
+// A CTA's and a warp's share of the items of a product phase.
+struct Range {
+  int c0, c1;  // CTA
+  int per;     // items per warp (last warps may have fewer or none)
+  int w0, w1;  // warp
+};
+__device__ __forceinline__ Range warp_range(int total, int chunk, int warp) {
+  Range r;
+  r.c0 = min((int)blockIdx.x * chunk, total);
+  r.c1 = min(r.c0 + chunk, total);
+  const int n = r.c1 - r.c0;
+  r.per = n > 0 ? (n + FW - 1) / FW : 1;
+  r.w0 = min(r.c0 + warp * r.per, r.c1);
+  r.w1 = min(r.w0 + r.per, r.c1);
+  return r;
+}
+
+// Position in the item list: item i = (unit u, pass p, K group kg), plus where its bytes are.
+struct Cursor {
+  int i, u, p, kg;
+  int type, tgb;
+  const uint8_t* src;
+};
+__device__ __forceinline__ void unit_locate(const fb200_fused_phase& P, int u, int& sidx, int& tile) {
+  sidx = 0; tile = u;
+  if (P.nseg > 1 && tile >= P.seg[0].units) { tile -= P.seg[0].units; sidx = 1; }
+  if (P.nseg > 2 && sidx == 1 && tile >= P.seg[1].units) { tile -= P.seg[1].units; sidx = 2; }
+}
+__device__ __forceinline__ void cur_locate(const fb200_fused_phase& P, const PhaseLocal& q, Cursor& c) {
+  int sidx, tile;
+  unit_locate(P, c.u, sidx, tile);
+  c.type = P.seg[sidx].type;
+  c.tgb = P.seg[sidx].tg;
+  c.src = P.seg[sidx].w + ((size_t)(tile + c.p * q.pair_off) * q.ng + c.kg) * (size_t)c.tgb;
+}
+__device__ __forceinline__ void cur_init(const fb200_fused_phase& P, const PhaseLocal& q, Cursor& c, int i) {
+  c.i = i;
+  c.u = fdiv(i, q.rcp_ipu);
+  const int rem = i - c.u * q.ipu;
+  c.p = fdiv(rem, q.rcp_ng);
+  c.kg = rem - c.p * q.ng;
+  cur_locate(P, q, c);
+}
+__device__ __forceinline__ void cur_next(const fb200_fused_phase& P, const PhaseLocal& q, Cursor& c) {
+  ++c.i;
+  c.src += c.tgb;
+  if (++c.kg == q.ng) {
+    c.kg = 0;
+    if (++c.p == q.npass) { c.p = 0; ++c.u; }
+    if (c.i < q.total) cur_locate(P, q, c);
+  }
+}
+
+struct WarpRing {
+  uint32_t base;   // shared address of this warp's ring
+  uint32_t bar0;   // shared address of its first mbarrier
+  uint32_t par;    // bit s = parity of the next completion of slot s
+  uint8_t* ptr;    // generic pointer to the ring
+};
+
+__device__ __forceinline__ void ring_issue(const WarpRing& R, int slot, int stride, const Cursor& c) {
+  mbar_expect_tx(R.bar0 + 8 * slot, (uint32_t)c.tgb);
+  bulk_g2s(R.base + slot * stride, c.src, (uint32_t)c.tgb, R.bar0 + 8 * slot);
+}
+
+// What a warp carries from the prefetch of a product phase into that phase.
+struct Carry {
+  Cursor cc;  // first item of the warp's share
+  Cursor ic;  // next item to fetch
+  int n;      // items already in flight, in slots 0 .. n-1 (0: nothing was prefetched)
+};
+
+// First slots of this warp's share of product phase P (weights only, nothing to wait for).
+__device__ __forceinline__ void prefetch_phase(const fb200_fused_phase& P, const WarpRing& R, int warp, int lane,
+                                               Carry& C) {
+  const PhaseLocal q = phase_local(P);
+  const Range r = warp_range(q.total, q.chunk, warp);
+  C.n = 0;
+  if (r.w0 >= r.w1) return;
+  cur_init(P, q, C.cc, r.w0);
+  C.ic = C.cc;
+  const int n = min(q.stages, r.w1 - r.w0);
+  for (int j = 0; j < n; ++j) {
+    if (lane == 0) ring_issue(R, j, q.stride, C.ic);
+    cur_next(P, q, C.ic);
+  }
+  C.n = n;
+}
+
+struct EpiCtx {
+  float final_scale;
+  unsigned long long best_key;
+};
+
+// Epilogue of one unit; lanes 0..15 call it with the sums of row `lane` (pass 0 / pass 1).
+__device__ __noinline__ void unit_epilogue(const fb200_fused_phase& P, int unit, float s0, float s1, int lane,
+                                              EpiCtx& E) {
+  int sidx, tile;
+  unit_locate(P, unit, sidx, tile);
+  const int n = tile * 16 + lane;
+  const bool valid = n < P.seg[sidx].n_out;
+  float* yout = P.seg[sidx].y;
+  const float v0 = s0 * E.final_scale, v1 = s1 * E.final_scale;
+  // every operand the epilogue may need, fetched together (one trip to L2 instead of a chain)
+  const bool pack = P.yp.limbs && sidx == 0;
+  const float res1 = valid && P.epi == FB200_EPI_RESIDUAL ? __ldcg(P.r1 + n) : 0.f;
+  const float res2 = valid && P.epi == FB200_EPI_RESIDUAL && P.r2 ? __ldcg(P.r2 + n) : 0.f;
+  const float padd = valid && pack && P.yp_add ? __ldcg(P.yp_add + n) : 0.f;
+  const float pw = valid && pack && P.yp_norm_w ? P.yp_norm_w[n] : 1.0f;
+  float out = 0.f;
+  if (valid) {
+    if (P.epi == FB200_EPI_SWIGLU) {
+      // silu(gate) * up, fusor-ml/fusor/src/composite/activations.rs:47-64
+      out = (v0 / (1.0f + expf(-v0))) * v1;
+    } else if (P.epi == FB200_EPI_RESIDUAL) {
+      out = v0 + res1;
+      if (P.r2) out += res2;
+    } else {
+      out = v0;
+    }
+    if (yout) yout[n] = out;
+    if (P.argmax_key && sidx == 0) {
+      const unsigned long long key = argmax_key_of(out, (uint32_t)n);
+      if (key > E.best_key) E.best_key = key;
+    }
+  }
+  if (pack) {
+    const float nv = out + padd;
+    emit_packed16(P.yp, n, nv * pw, nv, valid, 0x0000FFFFu);
+  }
+}
+
+struct Smem {
+  uint8_t* xl;
+  float* xsc;
+  float* xss;
+  float* pieces;              // [FW][2][32]
+  float* tmp;                 // [FW]
+  unsigned long long* keys;   // [FW]
+};
+
+__device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused_phase& P, const fb200_fused_phase* Pnext,
+                           const Smem& S, WarpRing& R, Carry& C, unsigned long long* tr) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int K = P.K, Kp = P.Kp;
+
+  // ---- activation row: limbs, scales, sums -> shared memory (asynchronous 16-byte copies through
+  // L2, all in flight at once); 1/rms from the producer's sums of squares
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(P.xp.limbs);
+    uint4* dst = reinterpret_cast<uint4*>(S.xl);
+    // 32-byte limb blocks are placed as limb_block() says: bits 1-2 of the 16-byte chunk index
+    // are XOR-ed with bits 3-4
+    for (int i = tid; i < Kp / 4; i += FT) cp_async16(dst + (i ^ (((i >> 3) & 3) << 1)), src + i);
+    const uint4* s1 = reinterpret_cast<const uint4*>(P.xp.xsc);
+    const uint4* s2 = reinterpret_cast<const uint4*>(P.xp.xss);
+    uint4* d1 = reinterpret_cast<uint4*>(S.xsc);
+    uint4* d2 = reinterpret_cast<uint4*>(S.xss);
+    for (int i = tid; i < Kp / 64; i += FT) { cp_async16(d1 + i, s1 + i); cp_async16(d2 + i, s2 + i); }
+  }
+  EpiCtx E;
+  E.final_scale = 1.0f;
+  E.best_key = 0ull;
+  if (P.xp_norm) {
+    float ss = 0.f;
+    for (int i = tid; i < (K + 15) / 16; i += FT) ss += __ldcg(P.xp.sumsq + i);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+    if (lane == 0) S.tmp[warp] = ss;
+    __syncthreads();
+    ss = 0.f;
+    for (int i = 0; i < FW; ++i) ss += S.tmp[i];
+    E.final_scale = 1.0f / sqrtf(ss / (float)K + P.eps);
+  }
+  cp_async_wait_all();
+  __syncthreads();
+  if (tr) tr[1] = global_ns();
+
+  // ---- this warp's share: runs of items inside one (unit, pass), K group after K group
+  const PhaseLocal q = phase_local(P);
+  const Range r = warp_range(q.total, q.chunk, warp);
+  const Lane L = make_lane(lane);
+  if (r.w0 < r.w1) {
+    if (C.n == 0) prefetch_phase(P, R, warp, lane, C);  // nothing was fetched ahead
+    Cursor cc = C.cc, ic = C.ic;
+    const int u_first = cc.u;
+    const int blocks16 = (cc.type == FB200_Q4_K || cc.type == FB200_Q6_K) ? 16 : 8;  // 16-element blocks per K group
+    int i = r.w0, unit_first_item = r.w0, slot = 0;
+    float pv0 = 0.f, pv1 = 0.f;
+    while (i < r.w1) {
+      const int kend = min(q.ng, cc.kg + (r.w1 - i));
+      float acc_g = 0.f, acc_g8 = 0.f;
+      GroupPtrs G = group_ptrs(L, S.xl, S.xsc, S.xss, cc.kg, blocks16);
+      auto run = [&](auto group_fn) {
+        for (int kg = cc.kg; kg < kend; ++kg) {
+          mbar_wait(R.bar0 + 8 * slot, (R.par >> slot) & 1u, A.status);
+          group_fn(R.ptr + slot * q.stride);
+          __syncwarp();
+          if (ic.i < r.w1) {  // refill the slot just consumed
+            if (lane == 0) ring_issue(R, slot, q.stride, ic);
+            cur_next(P, q, ic);
+          }
+          R.par ^= 1u << slot;
+          slot = slot + 1 == q.stages ? 0 : slot + 1;
+          group_ptrs_next(G, blocks16);
+        }
+      };
+      switch (cc.type) {
+        case FB200_Q4_K: run([&](const uint8_t* tg) { group1_q4k(G.xq, G.xscp, G.xssp, tg, L, acc_g, acc_g8); }); break;
+        case FB200_Q6_K: run([&](const uint8_t* tg) { group1_q6k(G.xq, G.xscp, G.xssp, tg, L, acc_g, acc_g8); }); break;
+        case FB200_Q8_0: run([&](const uint8_t* tg) { group1_q8_0(G.xq, G.xscp, tg, L, acc_g, acc_g8); }); break;
+        default: run([&](const uint8_t* tg) { group1_q4_0(G.xq, G.xscp, G.xssp, tg, L, acc_g, acc_g8); }); break;
+      }
+      i += kend - cc.kg;
+      const int u_done = cc.u, p_done = cc.p;
+      cc.kg = kend;
+      if (kend == q.ng) {
+        cc.kg = 0;
+        if (++cc.p == q.npass) {
+          cc.p = 0;
+          ++cc.u;
+          if (i < r.w1 && P.nseg > 1) {
+            int sidx, tile;
+            unit_locate(P, cc.u, sidx, tile);
+            cc.type = P.seg[sidx].type;
+          }
+        }
+      }
+      // the pass, or this warp's share of it, ends here: rows 0..7 sit in acc_g of lanes 0, 4, ..,
+      // rows 8..15 in acc_g8; lane (r & 15) takes row r
+      acc_g += __shfl_xor_sync(0xFFFFFFFFu, acc_g, 1);
+      acc_g += __shfl_xor_sync(0xFFFFFFFFu, acc_g, 2);
+      acc_g8 += __shfl_xor_sync(0xFFFFFFFFu, acc_g8, 1);
+      acc_g8 += __shfl_xor_sync(0xFFFFFFFFu, acc_g8, 2);
+      const float lo = __shfl_sync(0xFFFFFFFFu, acc_g, (lane & 7) * 4);
+      const float hi = __shfl_sync(0xFFFFFFFFu, acc_g8, (lane & 7) * 4);
+      const float row = (lane & 8) ? hi : lo;
+      if (p_done == 0) pv0 = row; else pv1 = row;
+      if (cc.u != u_done || i == r.w1) {  // the unit, or this warp's share of it, ends here
+        const bool complete = unit_first_item == u_done * q.ipu && i == (u_done + 1) * q.ipu;
+        if (lane < 16) {
+          if (complete) {
+            unit_epilogue(P, u_done, pv0, pv1, lane, E);
+          } else {
+            float* pc = S.pieces + (warp * 2 + (u_done == u_first ? 0 : 1)) * 32;
+            pc[lane] = pv0;
+            pc[16 + lane] = pv1;
+          }
+        }
+        __syncwarp();
+        pv0 = 0.f; pv1 = 0.f;
+        unit_first_item = i;
+      }
+    }
+  }
+  if (tr) tr[4] = global_ns();
+  // ---- the ring is free: fetch the first slots of the next product phase
+  C.n = 0;
+  if (Pnext) prefetch_phase(*Pnext, R, warp, lane, C);
+  __syncthreads();
+  if (tr) tr[2] = global_ns();
+
+  // ---- units shared by several warps (summed in warp order) or several CTAs (in CTA order)
+  if (r.c0 < r.c1) {
+    const float rcp_per = 1.0f / (float)r.per, rcp_chunk = 1.0f / (float)q.chunk;
+    const int ua = fdiv(r.c0, q.rcp_ipu), ub = fdiv(r.c1 - 1, q.rcp_ipu);
+    for (int m = ua + warp; m <= ub; m += FW) {
+      const int ib = max(m * q.ipu, r.c0), ie = min((m + 1) * q.ipu, r.c1);
+      const int wlo = fdiv(ib - r.c0, rcp_per), whi = fdiv(ie - 1 - r.c0, rcp_per);
+      const bool cta_whole = ib == m * q.ipu && ie == (m + 1) * q.ipu;
+      if (wlo == whi && cta_whole) continue;  // one warp had the whole unit and finished it
+      float s0 = 0.f, s1 = 0.f;
+      if (lane < 16) {
+        for (int w = wlo; w <= whi; ++w) {
+          const int wfirst = fdiv(r.c0 + w * r.per, q.rcp_ipu);  // first unit of warp w
+          const float* pc = S.pieces + (w * 2 + (m == wfirst ? 0 : 1)) * 32;
+          s0 += pc[lane];
+          s1 += pc[16 + lane];
+        }
+      }
+      if (tr && m == ua) tr[6] = global_ns();
+      if (cta_whole) {
+        if (lane < 16) unit_epilogue(P, m, s0, s1, lane, E);
+        __syncwarp();
+        if (tr && m == ua) tr[7] = global_ns();
+        continue;
+      }
+      float* mine = A.gp + ((size_t)blockIdx.x * 2 + (m == ua ? 0 : 1)) * 32;
+      if (lane < 16) { mine[lane] = s0; mine[16 + lane] = s1; }
+      __threadfence();
+      __syncwarp();
+      const int clo = fdiv(m * q.ipu, rcp_chunk), chi = fdiv((m + 1) * q.ipu - 1, rcp_chunk);
+      int last = 0;
+      if (lane == 0) {
+        const int old = atomicAdd(A.counters + m, 1);
+        last = old == chi - clo;
+        if (last) A.counters[m] = 0;
+      }
+      last = __shfl_sync(0xFFFFFFFFu, last, 0);
+      if (!last) continue;
+      __threadfence();
+      if (lane < 16) {
+        float t0 = 0.f, t1 = 0.f;
+        for (int c = clo; c <= chi; ++c) {
+          const int cfirst = fdiv(c * q.chunk, q.rcp_ipu);  // first unit of CTA c
+          const float* pc = A.gp + ((size_t)c * 2 + (m == cfirst ? 0 : 1)) * 32;
+          t0 += __ldcg(pc + lane);
+          t1 += __ldcg(pc + 16 + lane);
+        }
+        unit_epilogue(P, m, t0, t1, lane, E);
+      }
+      __syncwarp();
+    }
+  }
+  if (tr) tr[5] = global_ns();
+  if (P.argmax_key) {
+    // one atomic per CTA: lanes -> warp -> CTA maximum of the running keys
+    unsigned long long k = E.best_key;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, k, o);
+      if (other > k) k = other;
+    }
+    if (lane == 0) S.keys[warp] = k;
+    __syncthreads();
+    if (tid == 0) {
+      for (int i = 1; i < FW; ++i) if (S.keys[i] > k) k = S.keys[i];
+      if (k) atomicMax(P.argmax_key, k);
+    }
+  }
+}
+
+// value of element n of the row a PACK / EMBED phase packs
+__device__ __forceinline__ float pack_source(const fb200_fused_phase& P, uint32_t id, int n) {
+  if (P.kind == FB200_PH_EMBED) {
+    if ((unsigned long long)id >= P.emb_n) return 0.f;
+    if (P.emb_tiled) {
+      const int kg = n / P.emb_ge, i = n - kg * P.emb_ge;
+      const uint8_t* tg = P.emb + ((size_t)(id >> 4) * P.emb_ngroups + kg) * (size_t)P.emb_tgb;
+      return fb::tile_dequant((uint32_t)P.emb_type, tg, (int)(id & 15u), i);
+    }
+    return fb::raw_elem((uint32_t)P.emb_type, P.emb, (uint64_t)id * (uint64_t)P.K + n);
+  }
+  float v = __ldcg(P.src + n);
+  if (P.src_add) v += __ldcg(P.src_add + n);
+  return v;
+}
+
+__device__ __noinline__ void pack_phase(const fb200_fused_phase& P) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nblk = (P.K + 31) / 32;
+  const uint32_t id = P.kind == FB200_PH_EMBED ? __ldcg(P.ids) : 0u;
+  for (int b = (int)blockIdx.x * FW + warp; b < nblk; b += (int)gridDim.x * FW) {
+    const int n = b * 32 + lane;
+    const bool valid = n < P.K;
+    float v = valid ? pack_source(P, id, n) : 0.f;
+    if (valid && P.xout) P.xout[n] = v;
+    const float nv = v;
+    if (valid && P.yp_norm_w) v *= P.yp_norm_w[n];
+    emit_packed16(P.yp, n, v, nv, valid, 0xFFFFFFFFu);
+  }
+}
+
+__device__ __noinline__ void advance_phase(const FusedArgs& A, const fb200_fused_phase& P) {
+  if (blockIdx.x != 0 || threadIdx.x != 0) return;
+  // the output head kept a running (value, index) maximum; 0 means no finite logit
+  const unsigned long long key = __ldcg(P.argmax_key);
+  const uint32_t tok = key ? (uint32_t)(key & 0xFFFFFFFFull) : 0xFFFFFFFFu;
+  *P.argmax_key = 0ull;
+  P.next[0] = tok;
+  P.ids_w[0] = tok;
+  const int step = __ldcg(P.step_dev);
+  if (A.record && P.hist && step < P.hist_cap) P.hist[step] = tok;
+  *P.pos_dev = __ldcg(P.pos_dev) + 1;
+  *P.step_dev = step + 1;
+}
+
+template <int D>
+__device__ __noinline__ void attn_phase(const fb200_fused_phase& P, uint8_t* dsm) {
+  const int tid = threadIdx.x;
+  if (tid >= DEC_THREADS) return;
+  const fb200_dec_args a = P.att;
+  const int nitems = a.b * a.hkv * a.nsplit;
+  for (int item = (int)blockIdx.x; item < nitems; item += (int)gridDim.x) {
+    attn_decode_item<D, FUSED_DEC_CH, 1, false>(a, item, dsm, tid);
+    dec_sync<1>();
+  }
+}
+
+__global__ void __launch_bounds__(FT, 1)
+fused_step_kernel(const FusedArgs A) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint8_t* ring = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FW * RING_BYTES);
+  uint8_t* xreg = smem + FW * RING_BYTES + FW * MAX_STAGES * 8;
+  Smem S;
+  S.xl = xreg;
+  S.pieces = reinterpret_cast<float*>(xreg + A.xregion);
+  S.tmp = S.pieces + FW * 2 * 32;
+  S.keys = reinterpret_cast<unsigned long long*>(S.tmp + 32);
+  WarpRing R;
+  R.ptr = ring + warp * RING_BYTES;
+  R.base = smem_u32(R.ptr);
+  R.bar0 = smem_u32(bars + warp * MAX_STAGES);
+  R.par = 0u;
+  if (lane == 0) {
+    for (int s = 0; s < MAX_STAGES; ++s) mbar_init(R.bar0 + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  // Phase descriptors live in shared memory: a window of four consecutive phases (the current one
+  // and the next three, which always include the next product phase), refilled one per phase.
+  uint32_t* sdesc = reinterpret_cast<uint32_t*>(S.keys + 32);
+  const int total_phases = A.nsteps * A.nphases;
+  auto desc_of = [&](int g) { return reinterpret_cast<const fb200_fused_phase*>(sdesc + (g & 3) * DESC_WORDS); };
+  auto load_desc = [&](int g) {
+    if (g >= total_phases) return;
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(A.prog + g % A.nphases);
+    uint32_t* dst = sdesc + (g & 3) * DESC_WORDS;
+    for (int i = tid; i < DESC_WORDS; i += FT) dst[i] = src[i];
+  };
+  for (int g = 0; g < 4; ++g) load_desc(g);
+  __syncthreads();
+
+  unsigned target = 0u;
+  Carry C;
+  C.n = 0;
+  if (A.first_gemv >= 0 && A.first_gemv < 4) prefetch_phase(*desc_of(A.first_gemv), R, warp, lane, C);
+  int g = 0;
+  for (int step = 0; step < A.nsteps; ++step) {
+    for (int ph = 0; ph < A.nphases; ++ph, ++g) {
+      if (g) {
+        grid_barrier(A, target, A.trace && step == A.nsteps - 1 ? A.trace + (size_t)A.nphases * 8 + ph : nullptr);
+        load_desc(g + 3);  // into the slot of the phase that has just ended
+      }
+      const fb200_fused_phase& P = *desc_of(g);
+      unsigned long long* tr = A.trace && blockIdx.x == 0 && tid == 0 && step == A.nsteps - 1 ? A.trace + ph * 8 : nullptr;
+      if (tr) tr[0] = global_ns();
+      switch (P.kind) {
+        case FB200_PH_GEMV: {
+          S.xsc = reinterpret_cast<float*>(S.xl + (size_t)P.Kp * 4);
+          S.xss = S.xsc + P.Kp / 16;
+          const int ahead = P.next_gemv < 0 ? -1 : (P.next_gemv > ph ? P.next_gemv - ph : P.next_gemv + A.nphases - ph);
+          const bool has_next = ahead > 0 && ahead <= 3 && g + ahead < total_phases;
+          gemv_phase(A, P, has_next ? desc_of(g + ahead) : nullptr, S, R, C, tr);
+          break;
+        }
+        case FB200_PH_ATTN:
+          if (P.att_d == 128) attn_phase<128>(P, xreg);
+          else attn_phase<64>(P, xreg);
+          break;
+        case FB200_PH_PACK:
+        case FB200_PH_EMBED:
+          pack_phase(P);
+          break;
+        default:
+          advance_phase(A, P);
+          break;
+      }
+      if (tr) tr[3] = global_ns();
+    }
+  }
+}
+
+size_t x_region_need(const fb200_fused_phase* prog, int nphases) {
+  size_t need = 0;
+  for (int i = 0; i < nphases; ++i) {
+    const auto& p = prog[i];
+    if (p.kind == FB200_PH_GEMV) need = std::max(need, (size_t)p.Kp * 4 + (size_t)p.Kp / 16 * 8);
+    if (p.kind == FB200_PH_ATTN) need = std::max(need, dec_smem_bytes(p.att_d, FUSED_DEC_CH));
+  }
+  return (need + 127) / 128 * 128;
+}
+
+size_t smem_total(size_t xregion) {
+  return (size_t)FW * RING_BYTES + (size_t)FW * MAX_STAGES * 8 + xregion + (size_t)FW * 2 * 32 * 4 + 32 * 4 +
+         32 * 8 + 4 * DESC_WORDS * 4;
+}
+
+}  // namespace
+
+int fb200_fused_grid(const fb200_device* dev) { return dev->sm_count; }
+
+bool fb200_fused_gemv_phase(fb200_fused_phase* p, const fb200_qmatrix* const* ws, float* const* ys, int nw,
+                            int epi, int grid) {
+  if (nw < 1 || nw > 3 || (epi != FB200_EPI_NONE && nw != 1)) return false;
+  TileGeom geo0;
+  if (!tile_geom(ws[0]->type, &geo0)) return false;
+  p->kind = FB200_PH_GEMV;
+  p->nseg = nw;
+  p->epi = epi;
+  p->stride = 0;
+  p->nunits = 0;
+  for (int i = 0; i < nw; ++i) {
+    TileGeom geo;
+    if (!ws[i]->tiled || !tile_geom(ws[i]->type, &geo) || geo.group_elems != geo0.group_elems ||
+        ws[i]->k != ws[0]->k)
+      return false;
+    p->seg[i].w = ws[i]->data;
+    p->seg[i].y = ys[i];
+    p->seg[i].type = (int)ws[i]->type;
+    p->seg[i].tg = geo.tg_bytes;
+    p->seg[i].units = ws[i]->ntiles;
+    p->seg[i].n_out = (int)ws[i]->n;
+    p->nunits += ws[i]->ntiles;
+    p->stride = std::max(p->stride, (geo.tg_bytes + 127) / 128 * 128);
+  }
+  p->K = (int)ws[0]->k;
+  p->ngroups = ws[0]->ngroups;
+  p->Kp = p->ngroups * geo0.group_elems;
+  p->pair_off = 0;
+  int npass = 1;
+  if (epi == FB200_EPI_SWIGLU) {
+    if (ws[0]->ntiles % 2) return false;
+    npass = 2;
+    p->seg[0].units = ws[0]->ntiles / 2;
+    p->nunits = p->seg[0].units;
+    p->seg[0].n_out = (int)(ws[0]->n / 2);
+    p->pair_off = ws[0]->ntiles / 2;
+  }
+  p->ipu = npass * p->ngroups;
+  const long long total = (long long)p->nunits * p->ipu;
+  if (total <= 0 || total > (1ll << 21)) return false;  // bound of the reciprocal divisions in the kernel
+  p->rcp_ipu = (float)(1.0 / (double)p->ipu);
+  p->rcp_ng = (float)(1.0 / (double)p->ngroups);
+  p->total = (int)total;
+  p->chunk = (int)((total + grid - 1) / grid);
+  // Whole units per CTA when that costs at most a fifth more items for the busiest CTA: no unit
+  // is then shared between CTAs and nothing has to be merged through global memory.
+  const long long aligned = (long long)((p->nunits + grid - 1) / grid) * p->ipu;
+  if (aligned * 5 <= (long long)p->chunk * 6) p->chunk = (int)aligned;
+  p->stages = std::min(MAX_STAGES, RING_BYTES / p->stride);
+  return p->stages >= 1;
+}
+
+size_t fb200_fused_smem_bytes(const fb200_fused_phase* prog_host, int nphases) {
+  const size_t total = smem_total(x_region_need(prog_host, nphases));
+  return total + STATIC_SMEM_RESERVE <= (size_t)SMEM_LIMIT ? total : 0;
+}
+
+int fb200_fused_launch(fb200_device* dev, const fb200_fused_phase* prog_dev, const fb200_fused_phase* prog_host,
+                       int nphases, int nsteps, bool record_history) {
+  if (nphases <= 0 || nsteps <= 0) return FB200_OK;
+  const int grid = fb200_fused_grid(dev);
+  const size_t xregion = x_region_need(prog_host, nphases);
+  const size_t smem = fb200_fused_smem_bytes(prog_host, nphases);
+  if (!smem) return fb200_fail(dev, FB200_ERR_CAPACITY, "fused step: the program does not fit in shared memory");
+  int max_units = 1, first = -1;
+  for (int i = 0; i < nphases; ++i)
+    if (prog_host[i].kind == FB200_PH_GEMV) {
+      max_units = std::max(max_units, prog_host[i].nunits);
+      if (first < 0) first = i;
+    }
+  // scratch: [barrier word, padded to 256 B][gp: grid * 64 floats][counters: max_units ints]
+  const size_t gp_off = 256, cnt_off = gp_off + (size_t)grid * 64 * 4;
+  const size_t need = cnt_off + (size_t)max_units * 4;
+  if (need > dev->fused_bytes) {
+    FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+    if (dev->fused) cudaFree(dev->fused);
+    dev->fused = nullptr;
+    dev->fused_bytes = 0;
+    const size_t cap = need + (64 << 10);
+    FB_CUDA(dev, cudaMalloc(&dev->fused, cap));
+    FB_CUDA(dev, cudaMemsetAsync(dev->fused, 0, cap, dev->stream));
+    dev->fused_bytes = cap;
+  }
+  static bool configured[64] = {false};
+  if (!configured[dev->ordinal & 63]) {
+    FB_CUDA(dev, cudaFuncSetAttribute(fused_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      SMEM_LIMIT - STATIC_SMEM_RESERVE));
+    configured[dev->ordinal & 63] = true;
+  }
+  FusedArgs a = {};
+  a.prog = prog_dev;
+  a.nphases = nphases;
+  a.nsteps = nsteps;
+  a.record = record_history ? 1 : 0;
+  a.first_gemv = first;
+  a.xregion = (int)xregion;
+  a.bar = reinterpret_cast<unsigned*>(dev->fused);
+  a.gp = reinterpret_cast<float*>((uint8_t*)dev->fused + gp_off);
+  a.counters = reinterpret_cast<int*>((uint8_t*)dev->fused + cnt_off);
+  a.status = dev->status;
+  FB_CUDA(dev, cudaMemsetAsync(a.bar, 0, 4, dev->stream));
+  // FB200_FUSED_TRACE=1: per-phase time stamps of CTA 0, printed to stderr after the launch
+  static const bool want_trace = getenv("FB200_FUSED_TRACE") && getenv("FB200_FUSED_TRACE")[0] == '1';
+  unsigned long long* trace_dev = nullptr;
+  if (want_trace) {
+    FB_CUDA(dev, cudaMalloc(&trace_dev, (size_t)nphases * 9 * 8));
+    FB_CUDA(dev, cudaMemsetAsync(trace_dev, 0, (size_t)nphases * 9 * 8, dev->stream));
+    a.trace = trace_dev;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(FT);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = dev->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;  // all CTAs resident at once, or the launch fails
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  FB_CUDA(dev, cudaLaunchKernelEx(&cfg, fused_step_kernel, a));
+  dev->launches++;
+  if (trace_dev) {
+    std::vector<unsigned long long> t((size_t)nphases * 9);
+    FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+    FB_CUDA(dev, cudaMemcpy(t.data(), trace_dev, t.size() * 8, cudaMemcpyDeviceToHost));
+    cudaFree(trace_dev);
+    fprintf(stderr, "fused step trace (CTA 0, last of %d steps): phase kind start_us [last CTA arrived before] load_us work_us tail_us\n", nsteps);
+    for (int i = 0; i < nphases; ++i) {
+      const unsigned long long* q = t.data() + (size_t)i * 8;
+      const double t0 = (double)(q[0] - t[0]) / 1e3;
+      const double ta = i ? ((double)q[0] - (double)t[(size_t)nphases * 8 + i]) / 1e3 : 0.0;
+      if (prog_host[i].kind == FB200_PH_GEMV)
+        fprintf(stderr, "  %3d gemv  %9.2f [%5.2f] %7.2f %7.2f %7.2f  (items %d, K %d; own loop %.2f, sync %.2f, merge %.2f = sum %.2f + epilogue %.2f + rest)\n",
+                i, t0, ta, (double)(q[1] - q[0]) / 1e3, (double)(q[2] - q[1]) / 1e3, (double)(q[3] - q[2]) / 1e3,
+                prog_host[i].total, prog_host[i].K, (double)(q[4] - q[1]) / 1e3, (double)(q[2] - q[4]) / 1e3,
+                (double)(q[5] - q[2]) / 1e3, (double)(q[6] - q[2]) / 1e3, (double)(q[7] - q[6]) / 1e3);
+      else
+        fprintf(stderr, "  %3d kind%d %9.2f [%5.2f] %7.2f\n", i, prog_host[i].kind, t0, ta, (double)(q[3] - q[0]) / 1e3);
+    }
+  }
+  return FB200_OK;
+}

@@ -1,0 +1,85 @@
+// Program of the fused decode-step kernel: a list of phases that one persistent cooperative
+// kernel (one CTA per SM) executes in order, with a grid-wide barrier between phases. The
+// weight stream never leaves the TMA-fed shared-memory rings: at the end of a product phase
+// every warp already fetches its first tile-groups of the next product phase, so HBM stays busy
+// across the barrier, the attention phase and the activation reload.
+#pragma once
+
+#include "attn_decode.cuh"
+#include "common.cuh"
+#include "packed_act.cuh"
+
+enum fb200_fused_kind {
+  FB200_PH_GEMV = 0,     // single-row quantised product(s), stream-K over tile-groups
+  FB200_PH_ATTN = 1,     // RoPE + KV append + split-KV attention for the new position
+  FB200_PH_PACK = 2,     // float row (+ row) -> packed row (optionally times a norm weight)
+  FB200_PH_EMBED = 3,    // embedding row of ids[0] -> float row + packed row
+  FB200_PH_ADVANCE = 4,  // greedy id from the argmax key -> ids, history; position + 1
+};
+
+struct fb200_fused_seg {
+  const uint8_t* w;  // tiled weight bytes
+  float* y;          // optional float output row
+  int type;          // ggml type id
+  int tg;            // bytes per tile-group
+  int units;         // tiles (tile pairs for SwiGLU) of this matrix
+  int n_out;         // logical outputs
+};
+
+struct fb200_fused_phase {
+  int kind;
+  int next_gemv;  // index of the next product phase in execution order (may wrap to the next step), -1: none
+  // ---- FB200_PH_GEMV: up to three matrices that share the activation row
+  fb200_fused_seg seg[3];
+  int nseg;
+  int epi;          // FB200_EPI_*
+  int K, Kp;        // logical and padded inner size
+  int ngroups;      // K groups per tile
+  int nunits;       // tiles (tile pairs) over all matrices
+  int ipu;          // items (tile-groups) per unit = passes * ngroups
+  int total;        // nunits * ipu
+  int chunk;        // items per CTA
+  int pair_off;     // SwiGLU: tile distance between a gate tile and its up tile
+  int stride;       // ring slot bytes (largest tile-group of the phase, rounded up to 128)
+  int stages;       // ring slots per warp in this phase
+  float rcp_ipu, rcp_ng;  // 1 / ipu, 1 / ngroups (the kernel divides item indices by multiplication)
+  fb200_packed_act xp;  // activation row
+  int xp_norm;          // divide by its RMS (norm weights were applied by the producer)
+  float eps;
+  const float* r1;      // residual epilogue
+  const float* r2;
+  fb200_packed_act yp;  // optional packed output (also the output of PACK / EMBED)
+  const float* yp_norm_w;
+  const float* yp_add;
+  unsigned long long* argmax_key;
+  // ---- FB200_PH_ATTN
+  fb200_dec_args att;
+  int att_d;
+  // ---- FB200_PH_PACK / FB200_PH_EMBED
+  const float* src;
+  const float* src_add;
+  float* xout;         // optional float copy of the row
+  const uint8_t* emb;  // embedding matrix bytes
+  int emb_type, emb_tiled, emb_ngroups, emb_ge, emb_tgb;
+  unsigned long long emb_n;
+  const uint32_t* ids;
+  // ---- FB200_PH_ADVANCE
+  uint32_t* next;
+  uint32_t* ids_w;
+  uint32_t* hist;
+  int* pos_dev;
+  int* step_dev;
+  int hist_cap;
+};
+
+// Fills the derived fields of a product phase (units, items, chunk, ring geometry) from its
+// matrices; `grid` = CTAs of the launch. Returns false if the matrices cannot share a phase.
+bool fb200_fused_gemv_phase(fb200_fused_phase* p, const fb200_qmatrix* const* ws, float* const* ys, int nw,
+                            int epi, int grid);
+// Shared memory the program needs; 0 if it does not fit.
+size_t fb200_fused_smem_bytes(const fb200_fused_phase* prog_host, int nphases);
+// Number of CTAs of a launch on this device.
+int fb200_fused_grid(const fb200_device* dev);
+// Runs `nsteps` passes over the program (device copy `prog_dev` of `prog_host`).
+int fb200_fused_launch(fb200_device* dev, const fb200_fused_phase* prog_dev, const fb200_fused_phase* prog_host,
+                       int nphases, int nsteps, bool record_history);

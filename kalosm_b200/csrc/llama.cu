@@ -13,6 +13,7 @@
 #include <memory>
 
 #include "common.cuh"
+#include "fused_step.cuh"
 #include "packed_act.cuh"
 
 void fb200_rope_tables_host(int head_dim, int ctx, float theta, float factor, float low_ff,
@@ -28,12 +29,7 @@ int fb200_launch_attention(fb200_device* dev, const float* q, const __half* k, c
                            int d, float scale, const float* mask, int mask_kind, float* out,
                            float* part, int nsplit, int bshd);
 int fb200_attention_nsplit(const fb200_device* dev, int b, int hkv, int groups, int sq, int skv);
-int fb200_launch_attention_decode(fb200_device* dev, const float* q, const float* k_new,
-                                  const float* v_new, __half* kc, __half* vc, int b, int h, int hkv,
-                                  const int* pos_dev, int cap, int d, float scale,
-                                  const float* rope_cos, const float* rope_sin, float* part,
-                                  int nsplit, int* done, float* out,
-                                  const fb200_packed_act* out_packed);
+bool fb200_qgemv1_fits(const fb200_qmatrix* w);
 int fb200_attention_scratch_bytes(int b, int h, int sq, int d, int nsplit, size_t* out);
 
 namespace {
@@ -144,6 +140,12 @@ struct fb200_llama {
   cudaGraphExec_t graph_exec = nullptr;
   int graph_batch = 0;
   uint64_t graph_kernels = 0;  // kernels inside the captured step
+  // single-sequence step as one persistent kernel: its program (host and device copies)
+  bool fused_enabled = true;   // FB200_FUSED=0 keeps the multi-kernel step
+  bool fused_valid = false;    // the program matches the current buffers
+  bool fused_usable = false;
+  std::vector<fb200_fused_phase> prog_host;
+  fb200_fused_phase* prog_dev = nullptr;
 };
 
 namespace {
@@ -160,6 +162,7 @@ int ensure_rows(fb200_llama* m, size_t rows) {
   const auto& c = m->cfg;
   FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
   if (m->graph_exec) { cudaGraphExecDestroy(m->graph_exec); m->graph_exec = nullptr; }
+  m->fused_valid = false;  // the program holds pointers into these buffers
   int rc;
   if ((rc = alloc_f(dev, &m->x, rows * c.hidden))) return rc;
   if ((rc = alloc_f(dev, &m->xn, rows * c.hidden))) return rc;
@@ -204,15 +207,9 @@ int finalize(fb200_llama* m) {
   return FB200_OK;
 }
 
-// Single sequence, single new position: five kernels per layer, all launched with programmatic
-// stream serialization so that each product streams its weights into shared memory while its
-// predecessor is still running:
-//   q, k, v projections in one launch, RMSNorm in its prologue
-//   RoPE(q, k) + fp16 KV append + split-KV attention, merged by the last split to finish
-//   output projection
-//   gate/up projection with SwiGLU epilogue, residual add + RMSNorm in its prologue
-//   down projection with both residual adds in its epilogue
-// The output head keeps a running argmax key, so greedy decoding needs no argmax kernel.
+// Shapes the fused single-sequence step takes: gate and up concatenated, every matrix tiled and
+// small enough for its activation row to sit in shared memory, q/k/v with one K group size,
+// at most 8 query heads per KV head.
 bool decode1_supported(const fb200_llama* m) {
   const auto& c = m->cfg;
   if (c.n_head / c.n_kv_head > 8) return false;
@@ -228,62 +225,138 @@ bool decode1_supported(const fb200_llama* m) {
   return ow->tiled && fb200_qgemv1_fits(ow);
 }
 
-int run_decode1(fb200_llama* m) {
+// One new position of one sequence as the program of the persistent fused kernel:
+//   embedding -> packed row (times the first attention norm weight)
+//   per layer: q/k/v product | RoPE + append + attention | output projection (packs attn_out + x
+//   times the FFN norm weight) | gate/up product with SwiGLU | down product with both residuals
+//   (packs the new residual stream times the next norm weight)
+//   output head with running argmax key | greedy id, position + 1
+int build_fused_program(fb200_llama* m) {
+  if (m->fused_valid) return FB200_OK;
   fb200_device* dev = m->dev;
   const auto& c = m->cfg;
+  m->fused_usable = false;
+  m->fused_valid = true;
+  if (!m->fused_enabled || !decode1_supported(m)) return FB200_OK;
+  const int grid = fb200_fused_grid(dev);
   const int H = c.n_head, HK = c.n_kv_head, D = c.head_dim;
-  int rc;
-  if ((rc = fb200_embedding_lookup(dev, m->token_embd, m->ids, 1, m->x))) return rc;
-  const float scale = (float)(1.0 / sqrt((double)D));
-  int nsplit = (c.max_seq_len + 127) / 128;
+  std::vector<fb200_fused_phase> prog;
+  auto blank = [] { fb200_fused_phase p; std::memset(&p, 0, sizeof(p)); p.next_gemv = -1; return p; };
+  {
+    fb200_fused_phase p = blank();
+    p.kind = FB200_PH_EMBED;
+    p.K = c.hidden;
+    p.emb = m->token_embd->data;
+    p.emb_type = (int)m->token_embd->type;
+    p.emb_tiled = m->token_embd->tiled ? 1 : 0;
+    p.emb_n = m->token_embd->n;
+    if (m->token_embd->tiled) {
+      TileGeom g;
+      tile_geom(m->token_embd->type, &g);
+      p.emb_ngroups = m->token_embd->ngroups; p.emb_ge = g.group_elems; p.emb_tgb = g.tg_bytes;
+    }
+    p.ids = m->ids;
+    p.xout = m->x;
+    p.yp = m->px;
+    p.yp_norm_w = m->layers[0].attn_norm;
+    prog.push_back(p);
+  }
+  int nsplit = grid / HK;
   if (nsplit > 32) nsplit = 32;
   if (nsplit < 1) nsplit = 1;
-  if ((size_t)nsplit * H * (D + 2) * sizeof(float) > m->att_part_bytes)
-    return fb200_fail(dev, FB200_ERR_CAPACITY, "llama: attention scratch too small");
+  if ((size_t)nsplit * H * (D + 2) * sizeof(float) > m->att_part_bytes) return FB200_OK;
+  auto gemv = [&](const fb200_qmatrix* const* ws, float* const* ys, int nw, int epi, fb200_fused_phase& p) {
+    p = blank();
+    p.eps = c.rms_eps;
+    return fb200_fused_gemv_phase(&p, ws, ys, nw, epi, grid);
+  };
   for (int li = 0; li < c.n_layer; ++li) {
     LayerW& L = m->layers[li];
+    fb200_fused_phase p;
     const fb200_qmatrix* qkv[3] = {L.wq, L.wk, L.wv};
     float* qkv_out[3] = {m->q, m->k, m->v};
-    fb200_gemv1_extra e_qkv;
-    if (li > 0) { e_qkv.x_packed = &m->px; e_qkv.x_packed_norm = true; }  // layer 0 packs the embedding row itself
-    if ((rc = fb200_qgemv1_multi(dev, qkv, qkv_out, 3, m->x, nullptr, L.attn_norm, c.rms_eps, FB200_EPI_NONE,
-                                 nullptr, nullptr, &e_qkv))) return rc;
-    if ((rc = fb200_launch_attention_decode(dev, m->q, m->k, m->v, L.kc, L.vc, 1, H, HK, m->pos_dev,
-                                            c.max_seq_len, D, scale, m->rope_cos, m->rope_sin, m->att_part,
-                                            nsplit, m->att_done, nullptr, &m->patt))) return rc;
-    // output projection; its epilogue also packs attn_out + x times the FFN norm weight
+    if (!gemv(qkv, qkv_out, 3, FB200_EPI_NONE, p)) return FB200_OK;
+    p.xp = m->px; p.xp_norm = 1;
+    prog.push_back(p);
+
+    p = blank();
+    p.kind = FB200_PH_ATTN;
+    p.att_d = D;
+    p.att.q = m->q; p.att.k_new = m->k; p.att.v_new = m->v; p.att.kc = L.kc; p.att.vc = L.vc;
+    p.att.rope_cos = m->rope_cos; p.att.rope_sin = m->rope_sin; p.att.pos_dev = m->pos_dev;
+    p.att.part = m->att_part; p.att.out = nullptr; p.att.done = m->att_done; p.att.out_packed = m->patt;
+    p.att.b = 1; p.att.h = H; p.att.hkv = HK; p.att.groups = H / HK; p.att.cap = c.max_seq_len;
+    p.att.nsplit = nsplit; p.att.scale = (float)(1.0 / sqrt((double)D));
+    prog.push_back(p);
+
     const fb200_qmatrix* wo = L.wo;
     float* wo_out = m->attn_out;
-    fb200_gemv1_extra e_wo;
-    e_wo.x_packed = &m->patt;
-    e_wo.y_packed = &m->pv; e_wo.y_packed_add = m->x; e_wo.y_packed_norm_w = L.ffn_norm;
-    if ((rc = fb200_qgemv1_multi(dev, &wo, &wo_out, 1, nullptr, nullptr, nullptr, c.rms_eps, FB200_EPI_NONE,
-                                 nullptr, nullptr, &e_wo))) return rc;
+    if (!gemv(&wo, &wo_out, 1, FB200_EPI_NONE, p)) return FB200_OK;
+    p.xp = m->patt;
+    p.yp = m->pv; p.yp_add = m->x; p.yp_norm_w = L.ffn_norm;
+    prog.push_back(p);
+
     const fb200_qmatrix* gu = L.gate_up;
-    float* gu_out = nullptr;  // the SwiGLU row is only needed packed
-    fb200_gemv1_extra e_gu;
-    e_gu.x_packed = &m->pv; e_gu.x_packed_norm = true;
-    e_gu.y_packed = &m->ph;
-    if ((rc = fb200_qgemv1_multi(dev, &gu, &gu_out, 1, nullptr, nullptr, nullptr, c.rms_eps,
-                                 FB200_EPI_SWIGLU, nullptr, nullptr, &e_gu))) return rc;
-    // down projection + both residuals -> residual stream, also packed for the next norm
+    float* gu_out = nullptr;
+    if (!gemv(&gu, &gu_out, 1, FB200_EPI_SWIGLU, p)) return FB200_OK;
+    p.xp = m->pv; p.xp_norm = 1;
+    p.yp = m->ph;
+    prog.push_back(p);
+
     const fb200_qmatrix* dn = L.down;
     float* dn_out = m->x;
-    fb200_gemv1_extra e_dn;
-    e_dn.x_packed = &m->ph;
-    e_dn.y_packed = &m->px;
-    e_dn.y_packed_norm_w = li + 1 < c.n_layer ? m->layers[li + 1].attn_norm : m->output_norm;
-    if ((rc = fb200_qgemv1_multi(dev, &dn, &dn_out, 1, nullptr, nullptr, nullptr, c.rms_eps, FB200_EPI_RESIDUAL,
-                                 m->attn_out, m->x, &e_dn))) return rc;
+    if (!gemv(&dn, &dn_out, 1, FB200_EPI_RESIDUAL, p)) return FB200_OK;
+    p.xp = m->ph;
+    p.r1 = m->attn_out; p.r2 = m->x;
+    p.yp = m->px;
+    p.yp_norm_w = li + 1 < c.n_layer ? m->layers[li + 1].attn_norm : m->output_norm;
+    prog.push_back(p);
   }
-  const fb200_qmatrix* ow = m->output ? m->output : m->token_embd;
-  float* lg = m->logits;
-  fb200_gemv1_extra ex;
-  ex.argmax_key = m->argmax_key;
-  ex.x_packed = &m->px; ex.x_packed_norm = true;
-  if ((rc = fb200_qgemv1_multi(dev, &ow, &lg, 1, nullptr, nullptr, nullptr, c.rms_eps, FB200_EPI_NONE,
-                               nullptr, nullptr, &ex))) return rc;
-  m->used_key = true;
+  {
+    fb200_fused_phase p;
+    const fb200_qmatrix* ow = m->output ? m->output : m->token_embd;
+    float* lg = m->logits;
+    if (!gemv(&ow, &lg, 1, FB200_EPI_NONE, p)) return FB200_OK;
+    p.xp = m->px; p.xp_norm = 1;
+    p.argmax_key = m->argmax_key;
+    prog.push_back(p);
+    p = blank();
+    p.kind = FB200_PH_ADVANCE;
+    p.argmax_key = m->argmax_key;
+    p.next = m->next; p.ids_w = m->ids; p.hist = m->hist; p.pos_dev = m->pos_dev; p.step_dev = m->step_dev;
+    p.hist_cap = m->hist_cap;
+    prog.push_back(p);
+  }
+  // chain the product phases (the last one wraps to the first, used when several steps run in one launch)
+  int first = -1, prev = -1;
+  for (int i = 0; i < (int)prog.size(); ++i) {
+    if (prog[i].kind != FB200_PH_GEMV) continue;
+    if (first < 0) first = i;
+    if (prev >= 0) prog[prev].next_gemv = i;
+    prev = i;
+  }
+  if (prev >= 0) prog[prev].next_gemv = first;
+  if (!fb200_fused_smem_bytes(prog.data(), (int)prog.size())) return FB200_OK;
+  FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  if (m->prog_dev) { cudaFree(m->prog_dev); m->prog_dev = nullptr; }
+  FB_CUDA(dev, cudaMalloc(&m->prog_dev, prog.size() * sizeof(fb200_fused_phase)));
+  FB_CUDA(dev, cudaMemcpy(m->prog_dev, prog.data(), prog.size() * sizeof(fb200_fused_phase), cudaMemcpyHostToDevice));
+  m->prog_host = std::move(prog);
+  m->fused_usable = true;
+  return FB200_OK;
+}
+
+// `steps` greedy single-token steps of one sequence in fused launches; ids are already in m->ids.
+int run_fused(fb200_llama* m, int steps, bool record) {
+  fb200_device* dev = m->dev;
+  FB_CUDA(dev, cudaMemsetAsync(m->argmax_key, 0, 8, dev->stream));
+  int rc;
+  for (int done = 0; done < steps;) {
+    const int n = std::min(steps - done, 256);  // bounded kernel run time
+    if ((rc = fb200_fused_launch(dev, m->prog_dev, m->prog_host.data(), (int)m->prog_host.size(), n, record)))
+      return rc;
+    done += n;
+  }
   return FB200_OK;
 }
 
@@ -291,7 +364,6 @@ int run_decode1(fb200_llama* m) {
 // Leaves logits [batch, vocab] in m->logits and the greedy ids in m->next.
 int run_forward(fb200_llama* m, int batch, int seq) {
   m->used_key = false;
-  if (batch == 1 && seq == 1 && decode1_supported(m)) return run_decode1(m);
   fb200_device* dev = m->dev;
   const auto& c = m->cfg;
   const size_t rows = (size_t)batch * seq;
@@ -417,6 +489,7 @@ int fb200_llama_create(fb200_device* dev, const fb200_llama_config* cfg, fb200_l
   m->dev = dev;
   m->cfg = c;
   m->layers.resize(c.n_layer);
+  if (const char* e = getenv("FB200_FUSED")) m->fused_enabled = !(e[0] == '0' && e[1] == 0);
   std::vector<float> cs, sn;
   fb200_rope_tables_host(c.head_dim, c.max_seq_len, c.rope_theta, c.rope_factor,
                          c.rope_low_freq_factor, c.rope_high_freq_factor, c.rope_original_ctx, cs, sn);
@@ -481,6 +554,7 @@ int fb200_llama_free(fb200_llama* m) {
   if (rc) return rc;
   cudaStreamSynchronize(dev->stream);
   if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
+  if (m->prog_dev) cudaFree(m->prog_dev);
   for (auto& L : m->layers) {
     fb200_qmatrix* qs[] = {L.wq, L.wk, L.wv, L.wo, L.gate, L.up, L.down, L.gate_up};
     for (auto* q : qs) if (q) fb200_qmatrix_free(q);
@@ -583,7 +657,11 @@ int fb200_llama_forward(fb200_llama* m, const uint32_t* tokens_host, int batch, 
   if ((rc = finalize(m))) return rc;
   const size_t rows = (size_t)batch * seq;
   if ((rc = ensure_rows(m, rows))) return rc;
-  if (seq == 1) {
+  if (seq == 1 && batch == 1 && (rc = build_fused_program(m))) return rc;
+  if (seq == 1 && batch == 1 && m->fused_usable) {
+    FB_CUDA(dev, cudaMemcpyAsync(m->ids, tokens_host, 4, cudaMemcpyHostToDevice, dev->stream));
+    if ((rc = run_fused(m, 1, false))) return rc;
+  } else if (seq == 1) {
     // single-token step: replay the captured graph (capture leaves the position untouched)
     if (!m->graph_exec || m->graph_batch != batch) {
       FB_CUDA(dev, cudaMemcpyAsync(m->ids, tokens_host, rows * 4, cudaMemcpyHostToDevice, dev->stream));
@@ -627,13 +705,24 @@ int fb200_llama_generate_greedy(fb200_llama* m, const uint32_t* tokens_host, int
     m->hist_cap = steps;
     if (m->graph_exec) { cudaGraphExecDestroy(m->graph_exec); m->graph_exec = nullptr; }
   }
-  FB_CUDA(dev, cudaMemcpyAsync(m->ids, tokens_host, (size_t)batch * 4, cudaMemcpyHostToDevice, dev->stream));
-  if ((rc = ensure_graph(m, batch))) return rc;
-  FB_CUDA(dev, cudaMemcpyAsync(m->ids, tokens_host, (size_t)batch * 4, cudaMemcpyHostToDevice, dev->stream));
-  FB_CUDA(dev, cudaMemsetAsync(m->step_dev, 0, 4, dev->stream));
-  for (int s = 0; s < steps; ++s) {
-    FB_CUDA(dev, cudaGraphLaunch(m->graph_exec, dev->stream));
-    dev->launches += m->graph_kernels;
+  if (batch == 1) {
+    m->fused_valid = m->fused_valid && !m->prog_host.empty() && m->prog_host.back().hist == m->hist &&
+                     m->prog_host.back().hist_cap == m->hist_cap;
+    if ((rc = build_fused_program(m))) return rc;
+  }
+  if (batch == 1 && m->fused_usable) {
+    FB_CUDA(dev, cudaMemcpyAsync(m->ids, tokens_host, 4, cudaMemcpyHostToDevice, dev->stream));
+    FB_CUDA(dev, cudaMemsetAsync(m->step_dev, 0, 4, dev->stream));
+    if ((rc = run_fused(m, steps, true))) return rc;
+  } else {
+    FB_CUDA(dev, cudaMemcpyAsync(m->ids, tokens_host, (size_t)batch * 4, cudaMemcpyHostToDevice, dev->stream));
+    if ((rc = ensure_graph(m, batch))) return rc;
+    FB_CUDA(dev, cudaMemcpyAsync(m->ids, tokens_host, (size_t)batch * 4, cudaMemcpyHostToDevice, dev->stream));
+    FB_CUDA(dev, cudaMemsetAsync(m->step_dev, 0, 4, dev->stream));
+    for (int s = 0; s < steps; ++s) {
+      FB_CUDA(dev, cudaGraphLaunch(m->graph_exec, dev->stream));
+      dev->launches += m->graph_kernels;
+    }
   }
   m->pos += steps;
   // hist is [batch, hist_cap]; gather the first `steps` columns

@@ -49,21 +49,3 @@ __device__ __forceinline__ void emit_packed16(const fb200_packed_act& pk, int n,
     if (pk.sumsq) pk.sumsq[n >> 4] = sq;
   }
 }
-
-
-// Optional extras of a single-row product.
-struct fb200_gemv1_extra {
-  unsigned long long* argmax_key = nullptr;  // running argmax key of the outputs
-  const fb200_packed_act* x_packed = nullptr;  // take the activation row from here instead of x
-  bool x_packed_norm = false;                  // ... and divide by its RMS (weight already applied)
-  const fb200_packed_act* y_packed = nullptr;  // also emit the output row in packed form
-  const float* y_packed_norm_w = nullptr;      // multiplied by this RMSNorm weight (the next layer's)
-  const float* y_packed_add = nullptr;         // after adding this row (residual)
-};
-
-// ys[i][n_i] = epilogue(W_i . act(x)) for up to three matrices that share K and the group size
-// (single activation row); defined with the single-row kernel.
-int fb200_qgemv1_multi(fb200_device* dev, const fb200_qmatrix* const* ws, float* const* ys, int nw,
-                       const float* x, const float* xres, const float* norm_w, float eps, int epi,
-                       const float* r1, const float* r2, const fb200_gemv1_extra* extra);
-bool fb200_qgemv1_fits(const fb200_qmatrix* w);
