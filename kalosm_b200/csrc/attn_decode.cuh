@@ -59,11 +59,10 @@ __device__ __forceinline__ void dec_sync() {
 }
 
 // One (batch, kv head, split) item, executed by DEC_THREADS threads (tid = 0 .. DEC_THREADS - 1).
-// DEC_CH = keys per shared-memory chunk. PDL: the caller is a kernel launched with programmatic
+// DEC_CH = keys per shared-memory chunk; ROWS = query rows computed per KV head (>= H / Hkv). PDL: the caller is a kernel launched with programmatic
 // stream serialization, whose predecessor produced q, k_new and v_new.
-template <int D, int DEC_CH, int BAR, bool PDL>
+template <int D, int DEC_CH, int ROWS, int BAR, bool PDL>
 __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int tid) {
-  constexpr int ROWS = DEC_ROWS;
   constexpr int ATT_THREADS = DEC_THREADS;
   constexpr int KSTR = D * 2 + 64;   // bytes per staged row: consecutive keys land 64 B apart mod 128
   constexpr int DV = D / 32;
@@ -199,7 +198,7 @@ __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int t
     }
     dec_sync<BAR>();
     // ---- online softmax statistics, warp r owns row r
-    {
+    if (warp < ROWS) {
       const int r = warp;
       float mx = -INFINITY;
       for (int j = lane; j < cn; j += 32) mx = fmaxf(mx, sc[r][j]);

@@ -34,7 +34,8 @@ constexpr int FW = 16;             // warps per CTA
 constexpr int FT = FW * 32;        // threads per CTA
 constexpr int RING_BYTES = 6912;   // ring bytes per warp: 3 x 2304 (Q4_K) or 2 x 3456 (Q6_K)
 constexpr int MAX_STAGES = 4;
-constexpr int FUSED_DEC_CH = 64;   // keys per shared-memory chunk of the attention phase
+constexpr int FUSED_DEC_CH = 64;
+constexpr int FUSED_SPLIT_KEYS = 32;  // smallest share of the context an attention item takes   // keys per shared-memory chunk of the attention phase
 constexpr int SMEM_LIMIT = 227 * 1024;
 constexpr int STATIC_SMEM_RESERVE = 4096;  // static shared memory of the attention phase
 constexpr int DESC_WORDS = (int)((sizeof(fb200_fused_phase) + 15) / 16 * 4);  // 32-bit words per descriptor slot
@@ -241,6 +242,7 @@ struct Smem {
   unsigned long long* keys;   // [FW]
 };
 
+template <bool LEGACY>
 __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused_phase& P, const fb200_fused_phase* Pnext,
                            const Smem& S, WarpRing& R, Carry& C, unsigned long long* tr) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -307,11 +309,14 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
           group_ptrs_next(G, blocks16);
         }
       };
-      switch (cc.type) {
-        case FB200_Q4_K: run([&](const uint8_t* tg) { group1_q4k(G.xq, G.xscp, G.xssp, tg, L, acc_g, acc_g8); }); break;
-        case FB200_Q6_K: run([&](const uint8_t* tg) { group1_q6k(G.xq, G.xscp, G.xssp, tg, L, acc_g, acc_g8); }); break;
-        case FB200_Q8_0: run([&](const uint8_t* tg) { group1_q8_0(G.xq, G.xscp, tg, L, acc_g, acc_g8); }); break;
-        default: run([&](const uint8_t* tg) { group1_q4_0(G.xq, G.xscp, G.xssp, tg, L, acc_g, acc_g8); }); break;
+      // 32-element block types are compiled only into the kernel variants that serve them
+      if (cc.type == FB200_Q4_K) {
+        run([&](const uint8_t* tg) { group1_q4k(G.xq, G.xscp, G.xssp, tg, L, acc_g, acc_g8); });
+      } else if (cc.type == FB200_Q6_K) {
+        run([&](const uint8_t* tg) { group1_q6k(G.xq, G.xscp, G.xssp, tg, L, acc_g, acc_g8); });
+      } else if (LEGACY) {
+        if (cc.type == FB200_Q8_0) run([&](const uint8_t* tg) { group1_q8_0(G.xq, G.xscp, tg, L, acc_g, acc_g8); });
+        else run([&](const uint8_t* tg) { group1_q4_0(G.xq, G.xscp, G.xssp, tg, L, acc_g, acc_g8); });
       }
       i += kend - cc.kg;
       const int u_done = cc.u, p_done = cc.p;
@@ -477,18 +482,27 @@ __device__ __noinline__ void advance_phase(const FusedArgs& A, const fb200_fused
   *P.step_dev = step + 1;
 }
 
-template <int D>
+// The context is cut into at most att.nsplit splits of at least FUSED_SPLIT_KEYS keys: an item's
+// run time is mostly fixed latencies, so many small items finish sooner than few large ones, and
+// very short contexts run a single item per KV head with nothing to merge.
+template <int D, int ROWS>
 __device__ __noinline__ void attn_phase(const fb200_fused_phase& P, uint8_t* dsm) {
   const int tid = threadIdx.x;
   if (tid >= DEC_THREADS) return;
-  const fb200_dec_args a = P.att;
+  fb200_dec_args a = P.att;
+  const int skv = __ldcg(a.pos_dev) + 1;
+  a.nsplit = max(1, min(a.nsplit, (skv + FUSED_SPLIT_KEYS - 1) / FUSED_SPLIT_KEYS));
   const int nitems = a.b * a.hkv * a.nsplit;
   for (int item = (int)blockIdx.x; item < nitems; item += (int)gridDim.x) {
-    attn_decode_item<D, FUSED_DEC_CH, 1, false>(a, item, dsm, tid);
+    attn_decode_item<D, FUSED_DEC_CH, ROWS, 1, false>(a, item, dsm, tid);
     dec_sync<1>();
   }
 }
 
+// One kernel variant per attention shape (head size D, query rows per KV head ROWS) and per
+// family of weight types (LEGACY = the 32-element block types too): a variant carries only the
+// code it runs, which keeps the instruction footprint of a step small.
+template <int D, int ROWS, bool LEGACY>
 __global__ void __launch_bounds__(FT, 1)
 fused_step_kernel(const FusedArgs A) {
   extern __shared__ __align__(128) uint8_t smem[];
@@ -546,12 +560,11 @@ fused_step_kernel(const FusedArgs A) {
           S.xss = S.xsc + P.Kp / 16;
           const int ahead = P.next_gemv < 0 ? -1 : (P.next_gemv > ph ? P.next_gemv - ph : P.next_gemv + A.nphases - ph);
           const bool has_next = ahead > 0 && ahead <= 3 && g + ahead < total_phases;
-          gemv_phase(A, P, has_next ? desc_of(g + ahead) : nullptr, S, R, C, tr);
+          gemv_phase<LEGACY>(A, P, has_next ? desc_of(g + ahead) : nullptr, S, R, C, tr);
           break;
         }
         case FB200_PH_ATTN:
-          if (P.att_d == 128) attn_phase<128>(P, xreg);
-          else attn_phase<64>(P, xreg);
+          attn_phase<D, ROWS>(P, xreg);
           break;
         case FB200_PH_PACK:
         case FB200_PH_EMBED:
@@ -668,11 +681,28 @@ int fb200_fused_launch(fb200_device* dev, const fb200_fused_phase* prog_dev, con
     FB_CUDA(dev, cudaMemsetAsync(dev->fused, 0, cap, dev->stream));
     dev->fused_bytes = cap;
   }
-  static bool configured[64] = {false};
-  if (!configured[dev->ordinal & 63]) {
-    FB_CUDA(dev, cudaFuncSetAttribute(fused_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  // kernel variant: attention shape and weight-type family of this program
+  int att_d = 128, groups = 1;
+  bool legacy = false;
+  for (int i = 0; i < nphases; ++i) {
+    const auto& ph = prog_host[i];
+    if (ph.kind == FB200_PH_ATTN) { att_d = ph.att_d; groups = std::max(groups, ph.att.groups); }
+    if (ph.kind == FB200_PH_GEMV)
+      for (int j = 0; j < ph.nseg; ++j) legacy = legacy || ph.seg[j].type == FB200_Q4_0 || ph.seg[j].type == FB200_Q8_0;
+  }
+  void (*kern)(const FusedArgs) = nullptr;
+  int variant = 0;
+  if (att_d == 128 && groups <= 4 && !legacy) { kern = fused_step_kernel<128, 4, false>; variant = 0; }
+  else if (att_d == 128 && !legacy) { kern = fused_step_kernel<128, 8, false>; variant = 1; }
+  else if (att_d == 128) { kern = fused_step_kernel<128, 8, true>; variant = 2; }
+  else if (att_d == 64 && !legacy) { kern = fused_step_kernel<64, 8, false>; variant = 3; }
+  else if (att_d == 64) { kern = fused_step_kernel<64, 8, true>; variant = 4; }
+  else return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "fused step: head size %d", att_d);
+  static bool configured[64][5] = {};
+  if (!configured[dev->ordinal & 63][variant]) {
+    FB_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       SMEM_LIMIT - STATIC_SMEM_RESERVE));
-    configured[dev->ordinal & 63] = true;
+    configured[dev->ordinal & 63][variant] = true;
   }
   FusedArgs a = {};
   a.prog = prog_dev;
@@ -704,7 +734,7 @@ int fb200_fused_launch(fb200_device* dev, const fb200_fused_phase* prog_dev, con
   attr[0].val.cooperative = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  FB_CUDA(dev, cudaLaunchKernelEx(&cfg, fused_step_kernel, a));
+  FB_CUDA(dev, cudaLaunchKernelEx(&cfg, kern, a));
   dev->launches++;
   if (trace_dev) {
     std::vector<unsigned long long> t((size_t)nphases * 9);

@@ -78,3 +78,34 @@ def test_graph_step_equals_eager_prefill(dev):
     with pytest.raises(kb.FusorError) as e:
         gpu.forward(rng.integers(0, cfg["vocab"], size=(1, cfg["ctx"]), dtype=np.uint32))
     assert e.value.code == kb.ERR_CAPACITY
+
+
+@pytest.mark.parametrize("head_dim,n_head,n_kv_head", [(64, 4, 2), (128, 8, 2), (128, 8, 1)])
+def test_decode_over_a_long_context(dev, head_dim, n_head, n_kv_head):
+    # several attention splits per KV head (one per 128 cached keys), 4 or 8 query rows per KV
+    # head, a prompt whose length is not a multiple of the split size
+    cfg = dict(tiny_cfg(), ctx=448, head_dim=head_dim, n_head=n_head, n_kv_head=n_kv_head)
+    gpu, cpu = build_models(dev, cfg, batch=1, seed=11)
+    rng = np.random.default_rng(12)
+    prompt = rng.integers(0, cfg["vocab"], size=(1, 291), dtype=np.uint32)
+    lg, nxt = gpu.forward(prompt)
+    lo = cpu.forward(prompt)
+    assert F.rel_l2(lg, lo) < 2e-3, F.rel_l2(lg, lo)
+    tok = np.array([O.top_k(lo[0], 1)[0][0]], dtype=np.uint32)
+    for step in range(5):
+        lo = cpu.forward(tok[:, None])
+        lg, _ = gpu.forward(tok[:, None])
+        assert F.rel_l2(lg, lo) < 2e-3, (step, F.rel_l2(lg, lo))
+        tok = np.array([O.top_k(lo[0], 1)[0][0]], dtype=np.uint32)
+    # the device-side loop gives the same tokens as stepping through forward()
+    first = tok.copy()
+    toks = gpu.generate_greedy(first, 6)[0]
+    t = first.copy()
+    for step in range(6):
+        lo = cpu.forward(t[:, None])
+        want = O.top_k(lo[0], 1)[0][0]
+        if toks[step] != want:
+            assert _margin(lo)[0] < 1e-3, (step, _margin(lo)[0])
+            break
+        t = np.array([want], dtype=np.uint32)
+    assert gpu.position == 291 + 5 + 6
