@@ -71,8 +71,9 @@ __device__ __forceinline__ void grid_barrier(const FusedArgs& A, unsigned& targe
   target += gridDim.x;
   if (threadIdx.x == 0) {
     if (arrive_max) atomicMax(arrive_max, global_ns());
-    __threadfence();
-    atomicAdd(A.bar, 1u);
+    // arrival = one fire-and-forget reduction with release semantics (orders this CTA's writes,
+    // made visible to thread 0 by the barrier above, before the count)
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(A.bar) : "memory");
     unsigned polls = 0;
     while ((int)(ld_acquire_u32(A.bar) - target) < 0) {
       ++polls;

@@ -31,9 +31,13 @@ __device__ __forceinline__ void emit_packed16(const fb200_packed_act& pk, int n,
     amax = fmaxf(amax, __shfl_xor_sync(mask, amax, o, 16));
     sq += __shfl_xor_sync(mask, sq, o, 16);
   }
-  int ex = 0;
-  if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &ex);
-  const int q = valid ? __float2int_rn(value * ldexpf(64.0f * 2097152.0f, -ex)) : 0;
+  // amax = f * 2^ex with f in [0.5, 1) for normal numbers, read off the exponent field (zero,
+  // denormal and non-finite maxima take ex = 0); powers of two are built from their exponent
+  int ex = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 126;
+  if (ex <= -126 || ex > 127) ex = 0;
+  if (ex < -100) ex = -100;  // keeps 2^(27 - ex) and 2^(ex - 13) inside the normal range
+  const float qscale = __uint_as_float((uint32_t)(27 - ex + 127) << 23);  // 64 * 2^21 / 2^ex
+  const int q = valid ? __float2int_rn(value * qscale) : 0;
   float qsum = (float)q;
 #pragma unroll
   for (int o = 8; o > 0; o >>= 1) qsum += __shfl_xor_sync(mask, qsum, o, 16);
@@ -43,7 +47,7 @@ __device__ __forceinline__ void emit_packed16(const fb200_packed_act& pk, int n,
   blk[16] = (uint8_t)((q >> 14) & 0x7F); // limb 1
   blk[24] = (uint8_t)(q & 0x7F);         // limb 3
   if ((n & 15) == 0) {
-    const float sc = ldexpf(1.0f, ex - 13);
+    const float sc = __uint_as_float((uint32_t)(ex - 13 + 127) << 23);  // 2^(ex - 13)
     pk.xsc[n >> 4] = sc;
     pk.xss[n >> 4] = qsum * (1.0f / 16384.0f) * sc;
     if (pk.sumsq) pk.sumsq[n >> 4] = sq;
