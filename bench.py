@@ -32,9 +32,11 @@ sys.path.insert(0, ROOT)
 
 CFG = dict(n_layer=32, hidden=4096, ffn=14336, n_head=32, n_kv_head=8, head_dim=128, vocab=128256)
 PROMPT = 512
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the
-# profiler capture summarised under profiles/ (None until a capture of the current kernel exists)
-GEMV_TRAFFIC_BYTES = None
+# DRAM traffic of the dominant kernel (the fused decode-step kernel) per ALGORITHMIC byte, from the
+# profiler capture summarised under profiles/ (a 4-layer model of the same shapes, one step:
+# dram__bytes_read.sum + dram__bytes_write.sum = 1 013 254 656 B for 995 057 664 algorithmic bytes);
+# traffic grows in proportion to the layers, so a full launch is scaled by its algorithmic bytes.
+FUSED_TRAFFIC_PER_BYTE = 1013254656 / 995057664
 Q4_K, Q6_K, F32 = 12, 14, 0
 BLOCK_BYTES = {Q4_K: 144, Q6_K: 210}
 METRIC = "Llama-3-8B Q4_K decode tok/s @1 GPU; quant GEMV HBM GB/s vs ~8 TB/s peak"
@@ -243,8 +245,7 @@ def gemv_roofline(kb, dev, torch, stream, reps):
         w.free()
     return {"bound": "hbm", "kernel": "qgemv1_kernel<Q4_K, SwiGLU> on ffn gate+up [28672 x 4096]",
             "achieved": achieved, "peak": peak, "peak_source": which, "unit": "GB/s",
-            "frac": achieved / peak, "us_per_launch": us, "bytes_per_launch": kbytes,
-            "traffic": GEMV_TRAFFIC_BYTES}
+            "frac": achieved / peak, "us_per_launch": us, "bytes_per_launch": kbytes, "traffic": None}
 
 
 def run_gemv_only(args):
@@ -322,8 +323,8 @@ def run_ours(args):
     barrier()
     ms_e2e = f0.elapsed_time(f1)
 
-    # ---- dominant kernel alone: single-row GEMV over the gate/up matrices (SwiGLU epilogue) ----
-    roof = gemv_roofline(kb, dev, torch, stream, 8) if rank == 0 else None
+    # ---- the stand-alone single-row product (the kernel behind fb200_q_mat_mul at M = 1) ----
+    roof_gemv = gemv_roofline(kb, dev, torch, stream, 8) if rank == 0 else None
 
     t_all = [ms, ms_e2e]
     if world > 1:
@@ -340,6 +341,15 @@ def run_ours(args):
     kv = 2 * CFG["n_layer"] * CFG["n_kv_head"] * CFG["head_dim"] * 2 * (PROMPT + warmup + steps // 2) * batch
     peak, which = peaks()
     step_gbs = (wb + kv) / (ms / steps / 1e3) / 1e9
+    # dominant kernel: the fused decode-step kernel; the timed region above is `launches` launches
+    # of it (one per 256 steps) and nothing else, timed with CUDA events on its stream
+    per_launch = (wb + kv) * steps / max(1, launches)
+    roof = {"bound": "hbm",
+            "kernel": "fused_step_kernel: whole decode steps (embedding, 32 x [q/k/v, attention, o, gate/up + SwiGLU, "
+                      "down + residuals], output head + argmax) in one persistent cooperative launch",
+            "achieved": step_gbs, "peak": peak, "peak_source": which, "unit": "GB/s", "frac": step_gbs / peak,
+            "us_per_launch": ms * 1e3 / max(1, launches), "bytes_per_launch": per_launch,
+            "traffic": per_launch * FUSED_TRAFFIC_PER_BYTE if CFG["n_layer"] == 32 else None}
     # CPU baseline beside it (rank 0, N = 1 only): bounded sample of the oracle's decode step
     cpu = None
     if world == 1 and not args.no_cpu:
@@ -364,7 +374,7 @@ def run_ours(args):
             "e2e": {"value": tok_s_e2e, "unit": "tok/s", "h2d_bytes_per_step": 4 * batch,
                     "d2h_bytes_per_step": 4 * batch, "ms_per_step": ms_e2e / steps},
             "gpu_launches": int(launches), "device_status": status, "clocks": clocks,
-            "roofline": roof,
+            "roofline": roof, "roofline_gemv_alone": roof_gemv,
             "step_hbm": {"bytes_per_step": wb + kv, "achieved_gbs": step_gbs, "frac_of_peak": step_gbs / peak,
                          "peak_source": which},
             "cpu_baseline": cpu}

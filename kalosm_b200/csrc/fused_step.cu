@@ -33,7 +33,7 @@ namespace {
 constexpr int FW = 16;             // warps per CTA
 constexpr int FT = FW * 32;        // threads per CTA
 constexpr int RING_BYTES = 6912;   // ring bytes per warp: 3 x 2304 (Q4_K) or 2 x 3456 (Q6_K)
-constexpr int MAX_STAGES = 4;
+constexpr int MAX_STAGES = 2;  // ring slots per warp: a third slot measured slower, not faster
 constexpr int FUSED_DEC_CH = 64;
 constexpr int FUSED_SPLIT_KEYS = 32;  // smallest share of the context an attention item takes   // keys per shared-memory chunk of the attention phase
 constexpr int SMEM_LIMIT = 227 * 1024;
@@ -167,7 +167,10 @@ __device__ __forceinline__ void ring_issue(const WarpRing& R, int slot, int stri
   bulk_g2s(R.base + slot * stride, c.src, (uint32_t)c.tgb, R.bar0 + 8 * slot);
 }
 
-// What a warp carries from the prefetch of a product phase into that phase.
+// What a warp carries from the prefetch of a product phase into that phase. Invariant: when the
+// phase starts, exactly the items cc.i .. cc.i + n - 1 are in flight in slots 0 .. n-1 and
+// n = min(stages, items of the warp) (or n = 0 and nothing is in flight); the consumer refills
+// the slot it has just read, so slots are always used round-robin.
 struct Carry {
   Cursor cc;  // first item of the warp's share
   Cursor ic;  // next item to fetch
@@ -379,11 +382,14 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
       if (wlo == whi && cta_whole) continue;  // one warp had the whole unit and finished it
       float s0 = 0.f, s1 = 0.f;
       if (lane < 16) {
+        // warp wlo holds its piece of unit m in slot 0 if its share starts inside m, else in
+        // slot 1; every later warp starts inside m
+        int slot = r.c0 + wlo * r.per >= m * q.ipu ? 0 : 1;
         for (int w = wlo; w <= whi; ++w) {
-          const int wfirst = fdiv(r.c0 + w * r.per, q.rcp_ipu);  // first unit of warp w
-          const float* pc = S.pieces + (w * 2 + (m == wfirst ? 0 : 1)) * 32;
+          const float* pc = S.pieces + (w * 2 + slot) * 32;
           s0 += pc[lane];
           s1 += pc[16 + lane];
+          slot = 0;
         }
       }
       if (tr && m == ua) tr[6] = global_ns();
