@@ -34,9 +34,9 @@ CFG = dict(n_layer=32, hidden=4096, ffn=14336, n_head=32, n_kv_head=8, head_dim=
 PROMPT = 512
 # DRAM traffic of the dominant kernel (the fused decode-step kernel) per ALGORITHMIC byte, from the
 # profiler capture summarised under profiles/ (a 4-layer model of the same shapes, one step:
-# dram__bytes_read.sum + dram__bytes_write.sum = 1 013 254 656 B for 995 057 664 algorithmic bytes);
+# dram__bytes_read.sum + dram__bytes_write.sum = 1 002 517 760 B for 995 057 664 algorithmic bytes);
 # traffic grows in proportion to the layers, so a full launch is scaled by its algorithmic bytes.
-FUSED_TRAFFIC_PER_BYTE = 1013254656 / 995057664
+FUSED_TRAFFIC_PER_BYTE = 1002517760 / 995057664
 Q4_K, Q6_K, F32 = 12, 14, 0
 BLOCK_BYTES = {Q4_K: 144, Q6_K: 210}
 METRIC = "Llama-3-8B Q4_K decode tok/s @1 GPU; quant GEMV HBM GB/s vs ~8 TB/s peak"
@@ -216,6 +216,23 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def max_over_ranks(values, world, device):
+    """Element-wise maximum of a list of floats over all ranks of the default process group
+    (replicas are independent: the only exchange of a multi-GPU run is this timing reduction)."""
+    if world <= 1:
+        return list(values)
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor(list(values), dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
+def whole_job_rate(world, batch, steps, ms):
+    """tok/s of the whole job: every replica decodes batch * steps tokens in the slowest rank's time."""
+    return world * batch * steps / (ms / 1e3)
+
+
 def gemv_roofline(kb, dev, torch, stream, reps):
     """The dominant kernel timed alone: single-row product with SwiGLU epilogue over 16 distinct
     gate+up matrices (16 x 66 MB, larger than L2, so every launch streams from HBM)."""
@@ -326,17 +343,13 @@ def run_ours(args):
     # ---- the stand-alone single-row product (the kernel behind fb200_q_mat_mul at M = 1) ----
     roof_gemv = gemv_roofline(kb, dev, torch, stream, 8) if rank == 0 else None
 
-    t_all = [ms, ms_e2e]
-    if world > 1:
-        tt = torch.tensor(t_all, device="cuda")
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms, ms_e2e = tt.tolist()
+    ms, ms_e2e = max_over_ranks([ms, ms_e2e], world, "cuda")
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
-    tok_s = world * batch * steps / (ms / 1e3)
-    tok_s_e2e = world * batch * steps / (ms_e2e / 1e3)
+    tok_s = whole_job_rate(world, batch, steps, ms)
+    tok_s_e2e = whole_job_rate(world, batch, steps, ms_e2e)
     wb = weight_bytes_per_step(CFG)
     kv = 2 * CFG["n_layer"] * CFG["n_kv_head"] * CFG["head_dim"] * 2 * (PROMPT + warmup + steps // 2) * batch
     peak, which = peaks()

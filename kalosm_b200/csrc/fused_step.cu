@@ -160,11 +160,12 @@ struct WarpRing {
   uint32_t bar0;   // shared address of its first mbarrier
   uint32_t par;    // bit s = parity of the next completion of slot s
   uint8_t* ptr;    // generic pointer to the ring
+  uint64_t policy; // L2 policy of the weight stream (evict first)
 };
 
 __device__ __forceinline__ void ring_issue(const WarpRing& R, int slot, int stride, const Cursor& c) {
   mbar_expect_tx(R.bar0 + 8 * slot, (uint32_t)c.tgb);
-  bulk_g2s(R.base + slot * stride, c.src, (uint32_t)c.tgb, R.bar0 + 8 * slot);
+  bulk_g2s_stream(R.base + slot * stride, c.src, (uint32_t)c.tgb, R.bar0 + 8 * slot, R.policy);
 }
 
 // What a warp carries from the prefetch of a product phase into that phase. Invariant: when the
@@ -199,29 +200,48 @@ struct EpiCtx {
   unsigned long long best_key;
 };
 
+// The operands of a unit's epilogue (row `lane` of the unit): residuals, the row added before
+// packing, the norm weight folded into the packed row. Everything was produced before the phase
+// began, so a warp may fetch them long before it needs them.
+struct EpiOperands {
+  int unit;  // -1: nothing fetched
+  float res1, res2, padd, pw;
+};
+__device__ __forceinline__ EpiOperands epilogue_operands(const fb200_fused_phase& P, int unit, int lane) {
+  int sidx, tile;
+  unit_locate(P, unit, sidx, tile);
+  const int n = tile * 16 + lane;
+  const bool valid = n < P.seg[sidx].n_out;
+  const bool pack = P.yp.limbs && sidx == 0;
+  EpiOperands o;
+  o.unit = unit;
+  o.res1 = valid && P.epi == FB200_EPI_RESIDUAL ? __ldcg(P.r1 + n) : 0.f;
+  o.res2 = valid && P.epi == FB200_EPI_RESIDUAL && P.r2 ? __ldcg(P.r2 + n) : 0.f;
+  o.padd = valid && pack && P.yp_add ? __ldcg(P.yp_add + n) : 0.f;
+  o.pw = valid && pack && P.yp_norm_w ? P.yp_norm_w[n] : 1.0f;
+  return o;
+}
+
 // Epilogue of one unit; lanes 0..15 call it with the sums of row `lane` (pass 0 / pass 1).
 __device__ __noinline__ void unit_epilogue(const fb200_fused_phase& P, int unit, float s0, float s1, int lane,
-                                              EpiCtx& E) {
+                                           EpiCtx& E, const EpiOperands& pre) {
   int sidx, tile;
   unit_locate(P, unit, sidx, tile);
   const int n = tile * 16 + lane;
   const bool valid = n < P.seg[sidx].n_out;
   float* yout = P.seg[sidx].y;
   const float v0 = s0 * E.final_scale, v1 = s1 * E.final_scale;
-  // every operand the epilogue may need, fetched together (one trip to L2 instead of a chain)
   const bool pack = P.yp.limbs && sidx == 0;
-  const float res1 = valid && P.epi == FB200_EPI_RESIDUAL ? __ldcg(P.r1 + n) : 0.f;
-  const float res2 = valid && P.epi == FB200_EPI_RESIDUAL && P.r2 ? __ldcg(P.r2 + n) : 0.f;
-  const float padd = valid && pack && P.yp_add ? __ldcg(P.yp_add + n) : 0.f;
-  const float pw = valid && pack && P.yp_norm_w ? P.yp_norm_w[n] : 1.0f;
+  // operands fetched ahead by the caller, or all together now (one trip to L2 instead of a chain)
+  const EpiOperands op = pre.unit == unit ? pre : epilogue_operands(P, unit, lane);
   float out = 0.f;
   if (valid) {
     if (P.epi == FB200_EPI_SWIGLU) {
       // silu(gate) * up, fusor-ml/fusor/src/composite/activations.rs:47-64
       out = (v0 / (1.0f + expf(-v0))) * v1;
     } else if (P.epi == FB200_EPI_RESIDUAL) {
-      out = v0 + res1;
-      if (P.r2) out += res2;
+      out = v0 + op.res1;
+      if (P.r2) out += op.res2;
     } else {
       out = v0;
     }
@@ -232,8 +252,8 @@ __device__ __noinline__ void unit_epilogue(const fb200_fused_phase& P, int unit,
     }
   }
   if (pack) {
-    const float nv = out + padd;
-    emit_packed16(P.yp, n, nv * pw, nv, valid, 0x0000FFFFu);
+    const float nv = out + op.padd;
+    emit_packed16(P.yp, n, nv * op.pw, nv, valid, 0x0000FFFFu);
   }
 }
 
@@ -288,6 +308,13 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
   const PhaseLocal q = phase_local(P);
   const Range r = warp_range(q.total, q.chunk, warp);
   const Lane L = make_lane(lane);
+  // the first unit this warp will finish in the merge stage below: its epilogue operands are
+  // requested now and arrive while the warp works
+  EpiOperands pre;
+  pre.unit = -1;
+  const int ua = r.c0 < r.c1 ? fdiv(r.c0, q.rcp_ipu) : 0, ub = r.c0 < r.c1 ? fdiv(r.c1 - 1, q.rcp_ipu) : -1;
+  if (ua + warp <= ub && lane < 16 && (P.epi == FB200_EPI_RESIDUAL || P.yp_add || P.yp_norm_w))
+    pre = epilogue_operands(P, ua + warp, lane);
   if (r.w0 < r.w1) {
     if (C.n == 0) prefetch_phase(P, R, warp, lane, C);  // nothing was fetched ahead
     Cursor cc = C.cc, ic = C.ic;
@@ -351,7 +378,7 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
         const bool complete = unit_first_item == u_done * q.ipu && i == (u_done + 1) * q.ipu;
         if (lane < 16) {
           if (complete) {
-            unit_epilogue(P, u_done, pv0, pv1, lane, E);
+            unit_epilogue(P, u_done, pv0, pv1, lane, E, pre);
           } else {
             float* pc = S.pieces + (warp * 2 + (u_done == u_first ? 0 : 1)) * 32;
             pc[lane] = pv0;
@@ -374,7 +401,6 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
   // ---- units shared by several warps (summed in warp order) or several CTAs (in CTA order)
   if (r.c0 < r.c1) {
     const float rcp_per = 1.0f / (float)r.per, rcp_chunk = 1.0f / (float)q.chunk;
-    const int ua = fdiv(r.c0, q.rcp_ipu), ub = fdiv(r.c1 - 1, q.rcp_ipu);
     for (int m = ua + warp; m <= ub; m += FW) {
       const int ib = max(m * q.ipu, r.c0), ie = min((m + 1) * q.ipu, r.c1);
       const int wlo = fdiv(ib - r.c0, rcp_per), whi = fdiv(ie - 1 - r.c0, rcp_per);
@@ -394,7 +420,7 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
       }
       if (tr && m == ua) tr[6] = global_ns();
       if (cta_whole) {
-        if (lane < 16) unit_epilogue(P, m, s0, s1, lane, E);
+        if (lane < 16) unit_epilogue(P, m, s0, s1, lane, E, pre);
         __syncwarp();
         if (tr && m == ua) tr[7] = global_ns();
         continue;
@@ -421,7 +447,7 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
           t0 += __ldcg(pc + lane);
           t1 += __ldcg(pc + 16 + lane);
         }
-        unit_epilogue(P, m, t0, t1, lane, E);
+        unit_epilogue(P, m, t0, t1, lane, E, pre);
       }
       __syncwarp();
     }
@@ -527,6 +553,7 @@ fused_step_kernel(const FusedArgs A) {
   R.base = smem_u32(R.ptr);
   R.bar0 = smem_u32(bars + warp * MAX_STAGES);
   R.par = 0u;
+  R.policy = l2_evict_first_policy();
   if (lane == 0) {
     for (int s = 0; s < MAX_STAGES; ++s) mbar_init(R.bar0 + 8 * s, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

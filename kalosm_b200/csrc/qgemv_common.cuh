@@ -20,6 +20,19 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
       ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+// The same copy marked evict-first in L2: weights are read once per pass, so they should not
+// push the data that IS reused (activations, KV cache, partial sums, instructions) out of L2.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void bulk_g2s_stream(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar,
+                                                uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
+}
 // Bounded wait: gives up after ~2^22 polls, records it in the status word and lets the kernel
 // run to its end (results are then invalid, the host sees a non-zero status).
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* status) {
