@@ -37,8 +37,8 @@ PROMPT = 512
 # dram__bytes_read.sum + dram__bytes_write.sum = 1 002 517 760 B for 995 057 664 algorithmic bytes);
 # traffic grows in proportion to the layers, so a full launch is scaled by its algorithmic bytes.
 FUSED_TRAFFIC_PER_BYTE = 1002517760 / 995057664
-Q4_K, Q6_K, F32 = 12, 14, 0
-BLOCK_BYTES = {Q4_K: 144, Q6_K: 210}
+Q4_0, Q8_0, Q4_K, Q6_K, F32 = 2, 8, 12, 14, 0
+BLOCK_BYTES = {Q4_0: 18 * 8, Q8_0: 34 * 8, Q4_K: 144, Q6_K: 210}  # bytes per 256 elements
 METRIC = "Llama-3-8B Q4_K decode tok/s @1 GPU; quant GEMV HBM GB/s vs ~8 TB/s peak"
 
 
@@ -276,6 +276,77 @@ def run_gemv_only(args):
     print(json.dumps({"roofline": gemv_roofline(kb, dev, torch, stream, max(1, args.gemv_reps))}), flush=True)
 
 
+def run_sweep(args):
+    """Per-kernel table of the other configurations of the path, one JSON line each (not the bench
+    line): single-row and small-batch quantised products over the Llama-3-8B matrix shapes, and
+    decode attention over an fp16 cache. Every case rotates over enough distinct buffers to exceed
+    the L2 (126 MB) several times."""
+    import torch
+    import kalosm_b200 as kb
+    from kalosm_b200 import synth
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    dev = kb.Device(0, stream.cuda_stream)
+    peak, which = peaks()
+
+    def timed(fn, n):
+        for i in range(n):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        reps = 4
+        for _ in range(reps):
+            for i in range(n):
+                fn(i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (reps * n)
+
+    types = {"Q4_0": Q4_0, "Q8_0": Q8_0, "Q4_K": Q4_K, "Q6_K": Q6_K}
+    cases = [("Q4_0", 4096, 4096)] + [(t, n, k) for t in ("Q4_K", "Q8_0")
+                                       for (n, k) in ((4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336))] + \
+            [("Q6_K", 128256, 4096)]
+    for tname, n, k in cases:
+        ty = types[tname]
+        wbytes = qbytes(ty, n, k)
+        copies = max(2, min(24, int(600e6 // wbytes) + 1))
+        mats = []
+        for i in range(copies):
+            raw = synth.random_qweights(700 + i, 0.02, n, k, ty, device="cuda").cpu().numpy()
+            mats.append(kb.QMatrix.from_raw_bytes(dev, (n, k), raw, ty))
+        for m in (1, 8, 32):
+            x = dev.tensor(np.random.default_rng(m).standard_normal((m, k)).astype(np.float32))
+            y = dev.empty((m, n))
+            us = timed(lambda i: x.q_mat_mul(mats[i % copies], out=y), copies)
+            nbytes = wbytes + 4 * m * (k + n)
+            print(json.dumps({"case": "q_mat_mul", "type": tname, "n": n, "k": k, "m": m, "us": us,
+                              "algorithmic_bytes": nbytes, "gbs": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / peak,
+                              "peak": peak, "peak_source": which, "distinct_weight_buffers": copies}), flush=True)
+        for w in mats:
+            w.free()
+    # decode attention: one query position per sequence against L cached keys (fp16), Llama-3-8B heads
+    h, hkv, d = 32, 8, 128
+    for L in (1024, 4096, 16384):
+        for b in (1, 8, 32):
+            kv_bytes = b * L * hkv * d * 2 * 2
+            copies = max(2, min(16, int(400e6 // kv_bytes) + 1))
+            if copies * kv_bytes > 40e9:
+                continue
+            ks = [dev.tensor((np.random.default_rng(3 * i).standard_normal((b, hkv, L, d)) * 0.5).astype(np.float16))
+                  for i in range(copies)]
+            vs = [dev.tensor((np.random.default_rng(3 * i + 1).standard_normal((b, hkv, L, d)) * 0.5).astype(np.float16))
+                  for i in range(copies)]
+            q = dev.tensor(np.random.default_rng(9).standard_normal((b, h, 1, d)).astype(np.float32))
+            us = timed(lambda i: dev.flash_attention(q, ks[i % copies], vs[i % copies], 1.0 / np.sqrt(d)), copies)
+            nbytes = kv_bytes + 2 * b * h * d * 4
+            print(json.dumps({"case": "decode_attention", "batch": b, "context": L, "us": us, "algorithmic_bytes": nbytes,
+                              "gbs": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / peak, "peak": peak,
+                              "peak_source": which, "distinct_kv_buffers": copies}), flush=True)
+            del ks, vs
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -408,10 +479,14 @@ def main():
                     help="decoder layers of the model (fewer than 32 only for profiler captures; not a bench value)")
     ap.add_argument("--gemv-only", action="store_true", help="run only the dominant-kernel leg")
     ap.add_argument("--gemv-reps", type=int, default=8)
+    ap.add_argument("--sweep", action="store_true",
+                    help="per-kernel table over the other product shapes and decode attention (several JSON lines)")
     args = ap.parse_args()
     CFG["n_layer"] = args.layers
     if args.impl == "reference":
         run_reference(args)
+    elif args.sweep:
+        run_sweep(args)
     elif args.gemv_only:
         run_gemv_only(args)
     else:

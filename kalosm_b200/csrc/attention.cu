@@ -12,6 +12,7 @@
 
 #include "common.cuh"
 #include "packed_act.cuh"
+#include "attn_decode.cuh"
 
 struct fb200_kv_cache {
   fb200_device* dev = nullptr;
@@ -298,6 +299,17 @@ int kv_capacity_rule(int required, int max_len) {
 // earlier decode steps, never by the kernels just before this one) into shared memory with
 // cp.async BEFORE griddepcontrol.wait, so the cache streams in while the q/k/v projection is
 // still running; only q and the new k, v rows are read after the wait.
+// One query position per sequence against a cache that already holds every key (q already
+// rotated): the decode form of fb200_flash_attention. One CTA per (batch, KV head, split).
+constexpr int DEC_CH = 128;  // keys per shared-memory chunk
+
+template <int D, int ROWS_T>
+__global__ void __launch_bounds__(DEC_THREADS)
+attn_decode_kernel(const fb200_dec_args a) {
+  extern __shared__ __align__(128) uint8_t dsm[];
+  attn_decode_item<D, DEC_CH, ROWS_T, 0, false>(a, (int)blockIdx.x, dsm, (int)threadIdx.x);
+}
+
 }  // namespace
 
 int fb200_attention_scratch_bytes(int b, int h, int sq, int d, int nsplit, size_t* out) {
@@ -339,6 +351,32 @@ int fb200_launch_attention(fb200_device* dev, const float* q, const __half* k, c
     FB_LAUNCH_CHECK(dev);
   }
   return FB200_OK;
+}
+
+// Decode form: sq = 1, no mask. `part` holds nsplit * b * h * (d + 2) floats followed by
+// b * hkv arrival counters.
+int fb200_launch_attention_decode(fb200_device* dev, const float* q, const __half* k, const __half* v, int b,
+                                  int h, int hkv, int skv, int cap, int d, float scale, float* out, float* part,
+                                  int nsplit) {
+  fb200_dec_args a = {};
+  a.q = q; a.kc = const_cast<__half*>(k); a.vc = const_cast<__half*>(v);
+  a.pos_dev = nullptr; a.skv = skv; a.part = part; a.out = out;
+  a.done = reinterpret_cast<int*>(part + (size_t)nsplit * b * h * (d + 2));
+  a.b = b; a.h = h; a.hkv = hkv; a.groups = h / hkv; a.cap = cap; a.nsplit = nsplit; a.scale = scale;
+  FB_CUDA(dev, cudaMemsetAsync(a.done, 0, (size_t)b * hkv * sizeof(int), dev->stream));
+  const unsigned grid = (unsigned)(b * hkv * nsplit);
+  const size_t smem = dec_smem_bytes(d, DEC_CH);
+  static bool configured[64] = {false};
+  if (!configured[dev->ordinal & 63]) {
+    FB_CUDA(dev, cudaFuncSetAttribute(attn_decode_kernel<128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
+    FB_CUDA(dev, cudaFuncSetAttribute(attn_decode_kernel<128, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
+    FB_CUDA(dev, cudaFuncSetAttribute(attn_decode_kernel<64, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
+    configured[dev->ordinal & 63] = true;
+  }
+  if (d == 128 && a.groups <= 4)
+    return fb200_launch(dev, attn_decode_kernel<128, 4>, dim3(grid), dim3(DEC_THREADS), smem, false, a);
+  if (d == 128) return fb200_launch(dev, attn_decode_kernel<128, 8>, dim3(grid), dim3(DEC_THREADS), smem, false, a);
+  return fb200_launch(dev, attn_decode_kernel<64, 8>, dim3(grid), dim3(DEC_THREADS), smem, false, a);
 }
 
 int fb200_launch_kv_append(fb200_device* dev, const float* k, const float* v, __half* kc, __half* vc,
@@ -446,6 +484,16 @@ int fb200_flash_attention(fb200_device* dev, const float* q_dev, const void* k_d
     return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "attention: bad shape");
   if (mask_kind < 0 || mask_kind > 3 || (mask_kind >= 2 && !mask_dev))
     return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "attention: mask kind %d", mask_kind);
+  if (sq == 1 && skv > 0 && (mask_kind == 0 || !mask_dev) && h % hkv == 0 && h / hkv <= DEC_ROWS && (d == 64 || d == 128)) {
+    // decode form: enough (batch, KV head, split) items to fill the GPU twice, at least 64 keys each
+    int ns = (2 * dev->sm_count + b * hkv - 1) / (b * hkv);
+    ns = std::max(1, std::min(std::min(ns, 32), (skv + 63) / 64));
+    const size_t need = ((size_t)ns * b * h * (d + 2)) * sizeof(float) + (size_t)b * hkv * sizeof(int);
+    rc = fb200_ensure(dev, &dev->stage, &dev->stage_bytes, need);
+    if (rc) return rc;
+    return fb200_launch_attention_decode(dev, q_dev, (const __half*)k_dev, (const __half*)v_dev, b, h, hkv, skv,
+                                         kv_capacity, d, scale, out_dev, (float*)dev->stage, ns);
+  }
   const int nsplit = fb200_attention_nsplit(dev, b, hkv, h / hkv, sq, skv);
   size_t bytes;
   fb200_attention_scratch_bytes(b, h, sq, d, nsplit, &bytes);

@@ -19,7 +19,9 @@ struct fb200_dec_args {
   __half* vc;
   const float* rope_cos;  // [ctx, D/2]
   const float* rope_sin;
-  const int* pos_dev;   // position of the new token = number of cached keys
+  const int* pos_dev;   // position of the new token = number of cached keys; null: the cache
+                        // already holds all `skv` keys, q is already rotated, nothing is appended
+  int skv;              // number of keys when pos_dev is null
   float* part;          // [nsplit][B * H][D + 2]
   float* out;           // [B, H * D]
   int* done;            // [B * Hkv] arrival counters, zero between launches
@@ -54,7 +56,7 @@ __host__ __device__ constexpr size_t dec_smem_bytes(int d, int dec_ch) {
 // when the CTA has more warps than the team.
 template <int BAR>
 __device__ __forceinline__ void dec_sync() {
-  if (BAR == 0) dec_sync<BAR>();
+  if (BAR == 0) __syncthreads();
   else asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(DEC_THREADS) : "memory");
 }
 
@@ -83,8 +85,8 @@ __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int t
   const int kvh = bid % a.hkv;
   const int bi = bid / a.hkv;
   const int nrows = a.groups;
-  const int pos = __ldcg(a.pos_dev);
-  const int skv = pos + 1;
+  const int pos = a.pos_dev ? __ldcg(a.pos_dev) : -1;
+  const int skv = a.pos_dev ? pos + 1 : a.skv;
   const int per = (skv + a.nsplit - 1) / a.nsplit;
   const int kbeg = min(skv, split * per), kend = min(skv, kbeg + per);
   __half* kb = a.kc + ((size_t)bi * a.hkv + kvh) * (size_t)a.cap * D;
@@ -112,11 +114,15 @@ __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int t
     if (r < nrows) {
       const float* qr = a.q + ((size_t)bi * a.h + kvh * a.groups + r) * D;
       // interleaved RoPE at the new position (fusor-ml/fusor/src/composite/rope.rs:77-108)
-      const float self = __ldcg(qr + e), other = __ldcg(qr + (e ^ 1));
-      const float c = a.rope_cos[(size_t)pos * (D / 2) + (e >> 1)];
-      const float sn = a.rope_sin[(size_t)pos * (D / 2) + (e >> 1)];
-      v = (e & 1) ? __fadd_rn(__fmul_rn(other, sn), __fmul_rn(self, c))
-                  : __fsub_rn(__fmul_rn(self, c), __fmul_rn(other, sn));
+      const float self = __ldcg(qr + e);
+      v = self;
+      if (pos >= 0) {
+        const float other = __ldcg(qr + (e ^ 1));
+        const float c = a.rope_cos[(size_t)pos * (D / 2) + (e >> 1)];
+        const float sn = a.rope_sin[(size_t)pos * (D / 2) + (e >> 1)];
+        v = (e & 1) ? __fadd_rn(__fmul_rn(other, sn), __fmul_rn(self, c))
+                    : __fsub_rn(__fmul_rn(self, c), __fmul_rn(other, sn));
+      }
     }
     qs[r][e] = v;
   }
