@@ -353,18 +353,12 @@ int fb200_launch_attention(fb200_device* dev, const float* q, const __half* k, c
   return FB200_OK;
 }
 
-// Decode form: sq = 1, no mask. `part` holds nsplit * b * h * (d + 2) floats followed by
-// b * hkv arrival counters.
-int fb200_launch_attention_decode(fb200_device* dev, const float* q, const __half* k, const __half* v, int b,
-                                  int h, int hkv, int skv, int cap, int d, float scale, float* out, float* part,
-                                  int nsplit) {
-  fb200_dec_args a = {};
-  a.q = q; a.kc = const_cast<__half*>(k); a.vc = const_cast<__half*>(v);
-  a.pos_dev = nullptr; a.skv = skv; a.part = part; a.out = out;
-  a.done = reinterpret_cast<int*>(part + (size_t)nsplit * b * h * (d + 2));
-  a.b = b; a.h = h; a.hkv = hkv; a.groups = h / hkv; a.cap = cap; a.nsplit = nsplit; a.scale = scale;
-  FB_CUDA(dev, cudaMemsetAsync(a.done, 0, (size_t)b * hkv * sizeof(int), dev->stream));
-  const unsigned grid = (unsigned)(b * hkv * nsplit);
+// Launches the decode attention kernel for prepared arguments (a.done must point to b * hkv
+// zeroed arrival counters; the kernel leaves them zero again).
+int fb200_launch_attention_decode_args(fb200_device* dev, const fb200_dec_args& a, int d) {
+  if (a.h % a.hkv || a.groups > DEC_ROWS || (d != 64 && d != 128) || a.nsplit < 1 || a.nsplit > 32)
+    return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "attention_decode: unsupported head layout");
+  const unsigned grid = (unsigned)(a.b * a.hkv * a.nsplit);
   const size_t smem = dec_smem_bytes(d, DEC_CH);
   static bool configured[64] = {false};
   if (!configured[dev->ordinal & 63]) {
@@ -377,6 +371,20 @@ int fb200_launch_attention_decode(fb200_device* dev, const float* q, const __hal
     return fb200_launch(dev, attn_decode_kernel<128, 4>, dim3(grid), dim3(DEC_THREADS), smem, false, a);
   if (d == 128) return fb200_launch(dev, attn_decode_kernel<128, 8>, dim3(grid), dim3(DEC_THREADS), smem, false, a);
   return fb200_launch(dev, attn_decode_kernel<64, 8>, dim3(grid), dim3(DEC_THREADS), smem, false, a);
+}
+
+// Decode form of flash_attention: sq = 1, no mask, q already rotated, nothing appended. `part`
+// holds nsplit * b * h * (d + 2) floats followed by b * hkv arrival counters.
+int fb200_launch_attention_decode(fb200_device* dev, const float* q, const __half* k, const __half* v, int b,
+                                  int h, int hkv, int skv, int cap, int d, float scale, float* out, float* part,
+                                  int nsplit) {
+  fb200_dec_args a = {};
+  a.q = q; a.kc = const_cast<__half*>(k); a.vc = const_cast<__half*>(v);
+  a.pos_dev = nullptr; a.skv = skv; a.part = part; a.out = out;
+  a.done = reinterpret_cast<int*>(part + (size_t)nsplit * b * h * (d + 2));
+  a.b = b; a.h = h; a.hkv = hkv; a.groups = h / hkv; a.cap = cap; a.nsplit = nsplit; a.scale = scale;
+  FB_CUDA(dev, cudaMemsetAsync(a.done, 0, (size_t)b * hkv * sizeof(int), dev->stream));
+  return fb200_launch_attention_decode_args(dev, a, d);
 }
 
 int fb200_launch_kv_append(fb200_device* dev, const float* k, const float* v, __half* kc, __half* vc,

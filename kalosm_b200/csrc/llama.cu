@@ -29,6 +29,7 @@ int fb200_launch_attention(fb200_device* dev, const float* q, const __half* k, c
                            int d, float scale, const float* mask, int mask_kind, float* out,
                            float* part, int nsplit, int bshd);
 int fb200_attention_nsplit(const fb200_device* dev, int b, int hkv, int groups, int sq, int skv);
+int fb200_launch_attention_decode_args(fb200_device* dev, const fb200_dec_args& a, int d);
 bool fb200_qgemv1_fits(const fb200_qmatrix* w);
 int fb200_attention_scratch_bytes(int b, int h, int sq, int d, int nsplit, size_t* out);
 
@@ -389,17 +390,30 @@ int run_forward(fb200_llama* m, int batch, int seq) {
       if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wk, m->k, nullptr))) return rc;
       if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wv, m->v, nullptr))) return rc;
     }
-    {
+    if (seq == 1 && H / HK <= 8) {
+      // one new position per sequence: RoPE(q, k) + fp16 append + split-KV attention in one kernel
+      fb200_dec_args da = {};
+      da.q = m->q; da.k_new = m->k; da.v_new = m->v; da.kc = L.kc; da.vc = L.vc;
+      da.rope_cos = m->rope_cos; da.rope_sin = m->rope_sin; da.pos_dev = m->pos_dev;
+      da.part = m->att_part; da.out = m->att; da.done = m->att_done;
+      da.b = batch; da.h = H; da.hkv = HK; da.groups = H / HK; da.cap = c.max_seq_len; da.scale = scale;
+      int ns = (2 * dev->sm_count + batch * HK - 1) / (batch * HK);
+      ns = std::max(1, std::min(std::min(ns, 32), (c.max_seq_len + 63) / 64));
+      da.nsplit = ns;
+      if ((size_t)ns * batch * H * (D + 2) * sizeof(float) > m->att_part_bytes)
+        return fb200_fail(dev, FB200_ERR_CAPACITY, "llama: attention scratch too small");
+      if ((rc = fb200_launch_attention_decode_args(dev, da, D))) return rc;
+    } else {
       const size_t total = rows * (size_t)(H + 2 * HK) * (D / 2);
       rope_append_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(
           m->q, m->k, m->v, L.kc, L.vc, m->rope_cos, m->rope_sin, m->pos_dev, seq, H, HK, D,
           c.max_seq_len, total);
       FB_LAUNCH_CHECK(dev);
+      // mask only when seq_len > 1 (raw/mod.rs:969); strictly causal over the new positions
+      if ((rc = fb200_launch_attention(dev, m->q, L.kc, L.vc, batch, H, HK, seq, 0, m->pos_dev,
+                                       c.max_seq_len, D, scale, nullptr, seq > 1 ? 1 : 0, m->att,
+                                       m->att_part, nsplit, 1))) return rc;
     }
-    // mask only when seq_len > 1 (raw/mod.rs:969); strictly causal over the new positions
-    if ((rc = fb200_launch_attention(dev, m->q, L.kc, L.vc, batch, H, HK, seq, 0, m->pos_dev,
-                                     c.max_seq_len, D, scale, nullptr, seq > 1 ? 1 : 0, m->att,
-                                     m->att_part, nsplit, 1))) return rc;
     if ((rc = fb200_q_mat_mul(dev, m->att, rows, L.wo, m->attn_out, nullptr))) return rc;
     // ffn_norm.forward_residual_f32(attn, residual) (raw/mod.rs:1017)
     if (rows == 1 && L.gate_up) {

@@ -20,6 +20,8 @@
 // Replaces the reference's qgemv kernels (fusor-ml/tile-ir-kernels/src/kernels/qgemv.rs:356-678,
 // qgemv_q6k.rs:84-385) and their SwiGLU / residual epilogues
 // (fusor-ml/core/src/quantized/matmul/mod.rs:435-439, 666-722).
+#include <cstdlib>
+
 #include "qgemv_common.cuh"
 
 namespace {
@@ -46,18 +48,33 @@ struct GemvArgs {
 __device__ __forceinline__ uint32_t lds4(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
 __device__ __forceinline__ uint4 lds16(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
 
-// Limb bytes of 32-element chunk kc for this lane: {elements 4t..4t+3, elements 16+4t..16+4t+3}
-// of batch row 8 nt + g, one uint2 per limb.
+// What a lane needs from the packed activations for one 32-element chunk kc: limb bytes
+// {elements 4t..4t+3, elements 16+4t..16+4t+3} of batch row 8 nt + g (one uint2 per limb) and the
+// sums of the two 16-element halves for batch columns 8 nt + 2t, 2t + 1. They come from L2; the
+// group functions below request chunk k + 1 before they compute chunk k, and the first chunk of
+// the next tile-group before the last chunk of this one, so the latency is covered by the math.
 template <int NT, int NL>
-__device__ __forceinline__ void load_b(const GemvArgs& a, int kc, int g, int t, uint2 (&b)[NT][NL]) {
+struct ChunkIn {
+  uint2 b[NT][NL];
+  float2 sa[NT], sb[NT];
+};
+
+template <int NT, int NL, bool SUMS>
+__device__ __forceinline__ void load_chunk(const GemvArgs& a, int kc, int g, int t, ChunkIn<NT, NL>& c) {
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int m = 8 * nt + g;
 #pragma unroll
     for (int l = 0; l < NL; ++l) {
-      b[nt][l] = make_uint2(0u, 0u);
+      c.b[nt][l] = make_uint2(0u, 0u);
       if (m < a.M)
-        b[nt][l] = __ldg(reinterpret_cast<const uint2*>(a.xq + (((size_t)kc * NL + l) * a.Mp + m) * 32 + t * 8));
+        c.b[nt][l] = __ldg(reinterpret_cast<const uint2*>(a.xq + (((size_t)kc * NL + l) * a.Mp + m) * 32 + t * 8));
+    }
+    c.sa[nt] = make_float2(0.f, 0.f);
+    c.sb[nt] = make_float2(0.f, 0.f);
+    if (SUMS) {
+      c.sa[nt] = __ldg(reinterpret_cast<const float2*>(a.xs16 + (size_t)(2 * kc) * a.Mp + 8 * nt + 2 * t));
+      c.sb[nt] = __ldg(reinterpret_cast<const float2*>(a.xs16 + (size_t)(2 * kc + 1) * a.Mp + 8 * nt + 2 * t));
     }
   }
 }
@@ -91,72 +108,81 @@ __device__ __forceinline__ float limbs_f(const int (&c)[NL][4], int i) {
 }
 
 // acc += s * (f - centre * xs) - o * xs for the four accumulator slots of every n-tile;
-// xs = sum of the scaled activations over the scale group, per batch column.
+// xs = sum of the scaled activations over the scale group, per batch column (BOTH: both halves
+// of the chunk, else sx as given).
 template <int NT, int NL>
 __device__ __forceinline__ void apply(float (&acc)[NT][4], const int (&c)[NT][NL][4], float s_g,
                                       float s_g8, float o_g, float o_g8, float centre,
-                                      const float* xs_a, const float* xs_b, int t) {
+                                      const float2 (&sx)[NT]) {
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
-    float2 sx = make_float2(0.f, 0.f);
-    if (xs_a) {
-      sx = __ldg(reinterpret_cast<const float2*>(xs_a + 8 * nt + 2 * t));
-      if (xs_b) {
-        float2 s2 = __ldg(reinterpret_cast<const float2*>(xs_b + 8 * nt + 2 * t));
-        sx.x += s2.x; sx.y += s2.y;
-      }
-    }
-    acc[nt][0] = fmaf(s_g, limbs_f<NL>(c[nt], 0) - centre * sx.x, fmaf(-o_g, sx.x, acc[nt][0]));
-    acc[nt][1] = fmaf(s_g, limbs_f<NL>(c[nt], 1) - centre * sx.y, fmaf(-o_g, sx.y, acc[nt][1]));
-    acc[nt][2] = fmaf(s_g8, limbs_f<NL>(c[nt], 2) - centre * sx.x, fmaf(-o_g8, sx.x, acc[nt][2]));
-    acc[nt][3] = fmaf(s_g8, limbs_f<NL>(c[nt], 3) - centre * sx.y, fmaf(-o_g8, sx.y, acc[nt][3]));
+    acc[nt][0] = fmaf(s_g, limbs_f<NL>(c[nt], 0) - centre * sx[nt].x, fmaf(-o_g, sx[nt].x, acc[nt][0]));
+    acc[nt][1] = fmaf(s_g, limbs_f<NL>(c[nt], 1) - centre * sx[nt].y, fmaf(-o_g, sx[nt].y, acc[nt][1]));
+    acc[nt][2] = fmaf(s_g8, limbs_f<NL>(c[nt], 2) - centre * sx[nt].x, fmaf(-o_g8, sx[nt].x, acc[nt][2]));
+    acc[nt][3] = fmaf(s_g8, limbs_f<NL>(c[nt], 3) - centre * sx[nt].y, fmaf(-o_g8, sx[nt].y, acc[nt][3]));
   }
+}
+
+template <int NT, int NL>
+__device__ __forceinline__ void both_halves(const ChunkIn<NT, NL>& c, float2 (&sx)[NT]) {
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) sx[nt] = make_float2(c.sa[nt].x + c.sb[nt].x, c.sa[nt].y + c.sb[nt].y);
 }
 
 // ---- per-format processing of one tile-group by one warp --------------------------------------
 // Standard MMA mapping: one m16n8k32 covers the 32 elements of one scale group (two 16-element
 // groups for Q6_K, done as m16n8k16), the 8 columns are batch rows.
 
+// `cur` holds the inputs of the group's first chunk on entry and, on exit, those of chunk
+// `next_first` (the first chunk of the warp's next tile-group; -1: none).
 template <int NT, int NL>
 __device__ __forceinline__ void group_q4_0(const GemvArgs& a, const uint8_t* tg, int kg, int lane,
-                                           float (&acc)[NT][4]) {
+                                           float (&acc)[NT][4], ChunkIn<NT, NL>& cur, int next_first) {
   const int g = lane >> 2, t = lane & 3;
 #pragma unroll
   for (int blk = 0; blk < 4; ++blk) {
+    const int kc = kg * 4 + blk;
+    ChunkIn<NT, NL> nxt = cur;
+    const int kn = blk < 3 ? kc + 1 : next_first;
+    if (kn >= 0) load_chunk<NT, NL, true>(a, kn, g, t, nxt);
     const uint32_t w0 = lds4(tg + g * 64 + blk * 16 + 4 * t);
     const uint32_t w1 = lds4(tg + 512 + g * 64 + blk * 16 + 4 * t);
-    const int kc = kg * 4 + blk;
-    uint2 b[NT][NL];
-    load_b<NT, NL>(a, kc, g, t, b);
     int c[NT][NL][4];
     zero_c<NT, NL>(c);
     mma_all<false, NT, NL>(c, w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, (w0 >> 4) & 0x0F0F0F0Fu,
-                           (w1 >> 4) & 0x0F0F0F0Fu, b);
+                           (w1 >> 4) & 0x0F0F0F0Fu, cur.b);
     const float d_g = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 1024 + (g * 4 + blk) * 2));
     const float d_g8 = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 1024 + ((g + 8) * 4 + blk) * 2));
-    apply<NT, NL>(acc, c, d_g, d_g8, 0.f, 0.f, 8.0f, a.xs16 + (size_t)(2 * kc) * a.Mp,
-                  a.xs16 + (size_t)(2 * kc + 1) * a.Mp, t);
+    float2 sx[NT];
+    both_halves<NT, NL>(cur, sx);
+    apply<NT, NL>(acc, c, d_g, d_g8, 0.f, 0.f, 8.0f, sx);
+    cur = nxt;
   }
 }
 
 template <int NT, int NL>
 __device__ __forceinline__ void group_q8_0(const GemvArgs& a, const uint8_t* tg, int kg, int lane,
-                                           float (&acc)[NT][4]) {
+                                           float (&acc)[NT][4], ChunkIn<NT, NL>& cur, int next_first) {
   const int g = lane >> 2, t = lane & 3;
 #pragma unroll
   for (int blk = 0; blk < 4; ++blk) {
+    const int kc = kg * 4 + blk;
+    ChunkIn<NT, NL> nxt = cur;
+    const int kn = blk < 3 ? kc + 1 : next_first;
+    if (kn >= 0) load_chunk<NT, NL, false>(a, kn, g, t, nxt);
     const int off = g * 64 + blk * 16 + 4 * t;
     const uint32_t a0 = lds4(tg + off), a2 = lds4(tg + 512 + off);
     const uint32_t a1 = lds4(tg + 1024 + off), a3 = lds4(tg + 1536 + off);
-    const int kc = kg * 4 + blk;
-    uint2 b[NT][NL];
-    load_b<NT, NL>(a, kc, g, t, b);
     int c[NT][NL][4];
     zero_c<NT, NL>(c);
-    mma_all<true, NT, NL>(c, a0, a1, a2, a3, b);
+    mma_all<true, NT, NL>(c, a0, a1, a2, a3, cur.b);
     const float d_g = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 2048 + (g * 4 + blk) * 2));
     const float d_g8 = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 2048 + ((g + 8) * 4 + blk) * 2));
-    apply<NT, NL>(acc, c, d_g, d_g8, 0.f, 0.f, 0.f, nullptr, nullptr, t);
+    float2 sx[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) sx[nt] = make_float2(0.f, 0.f);
+    apply<NT, NL>(acc, c, d_g, d_g8, 0.f, 0.f, 0.f, sx);
+    cur = nxt;
   }
 }
 
@@ -164,7 +190,7 @@ __device__ __forceinline__ void group_q8_0(const GemvArgs& a, const uint8_t* tg,
 // two rows; the quad shares them by shuffle.
 template <int NT, int NL>
 __device__ __forceinline__ void group_q4k(const GemvArgs& a, const uint8_t* tg, int kg, int lane,
-                                          float (&acc)[NT][4]) {
+                                          float (&acc)[NT][4], ChunkIn<NT, NL>& cur, int next_first) {
   const int g = lane >> 2, t = lane & 3;
   float sc_f[2][2], mn_f[2][2];  // [row half][sub-block t + 4 i]
 #pragma unroll
@@ -194,19 +220,22 @@ __device__ __forceinline__ void group_q4k(const GemvArgs& a, const uint8_t* tg, 
       const int sb = 2 * pair + hi;
       const uint32_t mask = hi ? 0xF0F0F0F0u : 0x0F0F0F0Fu;
       const int kc = kg * 8 + sb;
-      uint2 b[NT][NL];
-      load_b<NT, NL>(a, kc, g, t, b);
+      ChunkIn<NT, NL> nxt = cur;
+      const int kn = sb < 7 ? kc + 1 : next_first;
+      if (kn >= 0) load_chunk<NT, NL, true>(a, kn, g, t, nxt);
       int c[NT][NL][4];
       zero_c<NT, NL>(c);
-      mma_all<false, NT, NL>(c, w00 & mask, w10 & mask, w01 & mask, w11 & mask, b);
+      mma_all<false, NT, NL>(c, w00 & mask, w10 & mask, w01 & mask, w11 & mask, cur.b);
       const int src = (lane & ~3) | (sb & 3);
       float s_g = __shfl_sync(0xFFFFFFFFu, sc_f[0][sb >> 2], src);
       float s_g8 = __shfl_sync(0xFFFFFFFFu, sc_f[1][sb >> 2], src);
       const float o_g = __shfl_sync(0xFFFFFFFFu, mn_f[0][sb >> 2], src);
       const float o_g8 = __shfl_sync(0xFFFFFFFFu, mn_f[1][sb >> 2], src);
       if (hi) { s_g *= 0.0625f; s_g8 *= 0.0625f; }  // high nibbles were used in place as 16 q
-      apply<NT, NL>(acc, c, s_g, s_g8, o_g, o_g8, 0.f, a.xs16 + (size_t)(2 * kc) * a.Mp,
-                    a.xs16 + (size_t)(2 * kc + 1) * a.Mp, t);
+      float2 sx[NT];
+      both_halves<NT, NL>(cur, sx);
+      apply<NT, NL>(acc, c, s_g, s_g8, o_g, o_g8, 0.f, sx);
+      cur = nxt;
     }
   }
 }
@@ -214,7 +243,7 @@ __device__ __forceinline__ void group_q4k(const GemvArgs& a, const uint8_t* tg, 
 // Q6_K: sixteen 16-element scale groups per super-block, one m16n8k16 per group and limb.
 template <int NT, int NL>
 __device__ __forceinline__ void group_q6k(const GemvArgs& a, const uint8_t* tg, int kg, int lane,
-                                          float (&acc)[NT][4]) {
+                                          float (&acc)[NT][4], ChunkIn<NT, NL>& cur, int next_first) {
   const int g = lane >> 2, t = lane & 3;
   const uint4 sc_g = lds16(tg + 3072 + g * 16);
   const uint4 sc_g8 = lds16(tg + 3072 + (g + 8) * 16);
@@ -228,8 +257,9 @@ __device__ __forceinline__ void group_q6k(const GemvArgs& a, const uint8_t* tg, 
     for (int q = 0; q < 4; ++q) {
       // groups 8c + 2q + u, u = 0, 1, are the two halves of 32-element chunk 4c + q
       const int kc = kg * 8 + c2 * 4 + q;
-      uint2 b[NT][NL];
-      load_b<NT, NL>(a, kc, g, t, b);
+      ChunkIn<NT, NL> nxt = cur;
+      const int kn = (c2 * 4 + q) < 7 ? kc + 1 : next_first;
+      if (kn >= 0) load_chunk<NT, NL, true>(a, kn, g, t, nxt);
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const int cu = c2 * 2 + u, grp = 8 * c2 + 2 * q + u;
@@ -246,12 +276,15 @@ __device__ __forceinline__ void group_q6k(const GemvArgs& a, const uint8_t* tg, 
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-          for (int l = 0; l < NL; ++l) mma_u8_k16(c[nt][l], af[0], af[1], u ? b[nt][l].y : b[nt][l].x);
+          for (int l = 0; l < NL; ++l) mma_u8_k16(c[nt][l], af[0], af[1], u ? cur.b[nt][l].y : cur.b[nt][l].x);
         const float s_g = d_g * (float)(int)(int8_t)((scw_g[grp >> 2] >> (8 * (grp & 3))) & 0xFF);
         const float s_g8 = d_g8 * (float)(int)(int8_t)((scw_g8[grp >> 2] >> (8 * (grp & 3))) & 0xFF);
-        apply<NT, NL>(acc, c, s_g, s_g8, 0.f, 0.f, 32.0f, a.xs16 + (size_t)(kg * 16 + grp) * a.Mp,
-                      nullptr, t);
+        float2 sx[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) sx[nt] = u ? cur.sb[nt] : cur.sa[nt];
+        apply<NT, NL>(acc, c, s_g, s_g8, 0.f, 0.f, 32.0f, sx);
       }
+      cur = nxt;
     }
 }
 
@@ -321,6 +354,11 @@ qgemv_kernel(const GemvArgs a) {
   // everything above touches only the weights; the activations come from the previous kernel
   pdl_wait();
 
+  constexpr int NL = Limbs<NT>::N;
+  constexpr int CHUNKS = (TYPE == FB200_Q4_0 || TYPE == FB200_Q8_0) ? 4 : 8;  // 32-element chunks per K group
+  constexpr bool SUMS = TYPE != FB200_Q8_0;
+  ChunkIn<NT, NL> cur;  // inputs of the first chunk of the warp's next tile-group
+  if (n_items > 0) load_chunk<NT, NL, SUMS>(a, warp * CHUNKS, g, t, cur);
   int item = 0;
   for (int j = 0; j < my_units; ++j) {
     const int unit = (int)blockIdx.x + j * (int)gridDim.x;
@@ -337,11 +375,13 @@ qgemv_kernel(const GemvArgs a) {
         mbar_wait(my_bar + 8 * st, (uint32_t)((item / S) & 1), a.status);
         const uint8_t* tg = my_ring + st * R::STRIDE;
         const int kg = warp + GEMV_WARPS * kk;
-        constexpr int NL = Limbs<NT>::N;
-        if (TYPE == FB200_Q4_0) group_q4_0<NT, NL>(a, tg, kg, lane, acc);
-        else if (TYPE == FB200_Q8_0) group_q8_0<NT, NL>(a, tg, kg, lane, acc);
-        else if (TYPE == FB200_Q4_K) group_q4k<NT, NL>(a, tg, kg, lane, acc);
-        else group_q6k<NT, NL>(a, tg, kg, lane, acc);
+        // first chunk of the warp's next tile-group: the next K group of this pass, or K group
+        // `warp` again when another pass or unit follows
+        const int next_first = kk + 1 < gw ? (kg + GEMV_WARPS) * CHUNKS : (item + 1 < n_items ? warp * CHUNKS : -1);
+        if (TYPE == FB200_Q4_0) group_q4_0<NT, NL>(a, tg, kg, lane, acc, cur, next_first);
+        else if (TYPE == FB200_Q8_0) group_q8_0<NT, NL>(a, tg, kg, lane, acc, cur, next_first);
+        else if (TYPE == FB200_Q4_K) group_q4k<NT, NL>(a, tg, kg, lane, acc, cur, next_first);
+        else group_q6k<NT, NL>(a, tg, kg, lane, acc, cur, next_first);
         __syncwarp();  // every lane has consumed the stage before it is refilled
         if (lane == 0 && item + S < n_items) issue(item + S);
       }
@@ -446,6 +486,368 @@ pack_x_kernel(const float* __restrict__ x, int M, int K, int Kp, int Mp, uint8_t
   }
 }
 
+// ================================================================================================
+// 2 .. 32 activation rows: weights dequantised to fp16 in registers, fp16 tensor-core MMAs.
+//
+// With several rows the limb scheme pays per 32-element chunk for every (row, batch column) pair:
+// integer sums to float, scale, offset. Here a chunk of weights is turned into fp16 once per lane
+// (byte -> 1024 + byte by a byte permute, exact subtraction, one fused multiply-add with the
+// block scale and offset) and fed to mma.m16n8k16.f16 with fp32 accumulation over the whole K:
+// the work per tile-group no longer depends on the scale structure and grows by two MMAs per
+// 8 more batch rows. Precision: weights and activations carry 11 bits (about 4e-4 relative L2 on
+// the products, inside the 2e-3 contract); the limb kernels above serve a single row (in the
+// single-row file) and, on request, 2 .. 8 rows.
+//
+// k-slots of an MMA and elements of a 32-element chunk: lane t holds elements 4t .. 4t+3 (first
+// step) and 16+4t .. 16+4t+3 (second step) of its rows, the same bytes the int8 mapping reads;
+// within a step, slots (2t, 2t+1) are elements (4t, 4t+1) and slots (2t+8, 2t+9) are (4t+2, 4t+3).
+// The activation rows are packed accordingly: per chunk and row 64 bytes, lane t's eight halves
+// at byte 16 t.
+
+__device__ __forceinline__ void mma_f16_k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                            uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+// Four unsigned bytes -> two half2 (1024 + byte each), then (v - centre) * scale - offset.
+// centre includes the 1024; scale and offset are per row.
+__device__ __forceinline__ void deq4(uint32_t w, __half2 centre, __half2 scale, __half2 offset, uint32_t& h01,
+                                     uint32_t& h23) {
+  const __half2 v01 = __hsub2(bits_h2(__byte_perm(w, 0x64646464u, 0x4140)), centre);
+  const __half2 v23 = __hsub2(bits_h2(__byte_perm(w, 0x64646464u, 0x4342)), centre);
+  h01 = h2_bits(__hfma2(v01, scale, offset));
+  h23 = h2_bits(__hfma2(v23, scale, offset));
+}
+
+template <int NT>
+struct Chunk16 { uint4 b[NT]; };
+
+template <int NT>
+__device__ __forceinline__ void load_chunk16(const GemvArgs& a, int kc, int g, int t, Chunk16<NT>& c) {
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int m = 8 * nt + g;
+    c.b[nt] = make_uint4(0u, 0u, 0u, 0u);
+    if (m < a.M) c.b[nt] = __ldg(reinterpret_cast<const uint4*>(a.xq + ((size_t)kc * a.Mp + m) * 64 + t * 16));
+  }
+}
+
+// One 32-element chunk: unsigned bytes of rows g / g+8, elements 4t.. (lo) and 16+4t.. (hi).
+template <int NT>
+__device__ __forceinline__ void chunk16(float (&acc)[NT][4], const Chunk16<NT>& x, uint32_t lo_g, uint32_t lo_g8,
+                                        uint32_t hi_g, uint32_t hi_g8, __half2 centre, __half2 s_lo_g,
+                                        __half2 s_lo_g8, __half2 s_hi_g, __half2 s_hi_g8, __half2 o_g,
+                                        __half2 o_g8) {
+  uint32_t a0, a1, a2, a3;
+  deq4(lo_g, centre, s_lo_g, o_g, a0, a2);
+  deq4(lo_g8, centre, s_lo_g8, o_g8, a1, a3);
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) mma_f16_k16(acc[nt], a0, a1, a2, a3, x.b[nt].x, x.b[nt].y);
+  deq4(hi_g, centre, s_hi_g, o_g, a0, a2);
+  deq4(hi_g8, centre, s_hi_g8, o_g8, a1, a3);
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) mma_f16_k16(acc[nt], a0, a1, a2, a3, x.b[nt].z, x.b[nt].w);
+}
+
+// `cur` holds the activations of the group's first chunk on entry and, on exit, those of chunk
+// `next_first` (the first chunk of the warp's next tile-group; -1: none).
+template <int TYPE, int NT>
+__device__ __forceinline__ void group16(const GemvArgs& a, const uint8_t* tg, int kg, int lane, float (&acc)[NT][4],
+                                        Chunk16<NT>& cur, int next_first) {
+  const int g = lane >> 2, t = lane & 3;
+  const __half2 zero2 = __float2half2_rn(0.f);
+  if constexpr (TYPE == FB200_Q4_0 || TYPE == FB200_Q8_0) {
+#pragma unroll
+    for (int blk = 0; blk < 4; ++blk) {
+      const int kc = kg * 4 + blk;
+      Chunk16<NT> nxt = cur;
+      const int kn = blk < 3 ? kc + 1 : next_first;
+      if (kn >= 0) load_chunk16<NT>(a, kn, g, t, nxt);
+      const int dofs = TYPE == FB200_Q4_0 ? 1024 : 2048;
+      const __half2 d_g = __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(tg + dofs + (g * 4 + blk) * 2)));
+      const __half2 d_g8 = __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(tg + dofs + ((g + 8) * 4 + blk) * 2)));
+      if constexpr (TYPE == FB200_Q4_0) {
+        const uint32_t w0 = lds4(tg + g * 64 + blk * 16 + 4 * t);
+        const uint32_t w1 = lds4(tg + 512 + g * 64 + blk * 16 + 4 * t);
+        chunk16<NT>(acc, cur, w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, (w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu,
+                    __float2half2_rn(1032.0f), d_g, d_g8, d_g, d_g8, zero2, zero2);  // (q - 8) d
+      } else {
+        const int off = g * 64 + blk * 16 + 4 * t;
+        const uint32_t a0 = lds4(tg + off) ^ 0x80808080u, a2 = lds4(tg + 512 + off) ^ 0x80808080u;
+        const uint32_t a1 = lds4(tg + 1024 + off) ^ 0x80808080u, a3 = lds4(tg + 1536 + off) ^ 0x80808080u;
+        chunk16<NT>(acc, cur, a0, a1, a2, a3, __float2half2_rn(1152.0f), d_g, d_g8, d_g, d_g8, zero2, zero2);  // q d
+      }
+      cur = nxt;
+    }
+  } else if constexpr (TYPE == FB200_Q4_K) {
+    // lane t of each quad decodes the 6-bit (scale, offset) of sub-blocks t and t + 4 for its two
+    // rows; the quad shares them by shuffle
+    float sc_f[2][2], mn_f[2][2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint4 hd = lds16(tg + 2048 + (g + 8 * h) * 16);
+      const float d = fb::half_bits_to_float((uint16_t)(hd.x & 0xFFFF));
+      const float dmin = fb::half_bits_to_float((uint16_t)(hd.x >> 16));
+      const uint32_t s0 = hd.y, s1 = hd.z, s2 = hd.w;
+      const uint32_t scB = (s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u);
+      const uint32_t mnB = ((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u);
+      const int sh = 8 * t;
+      sc_f[h][0] = d * (float)((s0 >> sh) & 0x3F);
+      mn_f[h][0] = dmin * (float)((s1 >> sh) & 0x3F);
+      sc_f[h][1] = d * (float)((scB >> sh) & 0xFF);
+      mn_f[h][1] = dmin * (float)((mnB >> sh) & 0xFF);
+    }
+#pragma unroll
+    for (int pair = 0; pair < 4; ++pair) {
+      const int ch = pair >> 1, ps = pair & 1;
+      const int off = g * 32 + ps * 16 + 4 * t;
+      const uint32_t w00 = lds4(tg + ((ch * 2 + 0) * 2 + 0) * 256 + off);  // row g,   elements 4t..
+      const uint32_t w01 = lds4(tg + ((ch * 2 + 0) * 2 + 1) * 256 + off);  // row g,   elements 16+4t..
+      const uint32_t w10 = lds4(tg + ((ch * 2 + 1) * 2 + 0) * 256 + off);  // row g+8
+      const uint32_t w11 = lds4(tg + ((ch * 2 + 1) * 2 + 1) * 256 + off);
+#pragma unroll
+      for (int hi = 0; hi < 2; ++hi) {
+        const int sb = 2 * pair + hi;
+        const int kc = kg * 8 + sb;
+        Chunk16<NT> nxt = cur;
+        const int kn = sb < 7 ? kc + 1 : next_first;
+        if (kn >= 0) load_chunk16<NT>(a, kn, g, t, nxt);
+        const int src = (lane & ~3) | (sb & 3);
+        const float s_g = __shfl_sync(0xFFFFFFFFu, sc_f[0][sb >> 2], src);
+        const float s_g8 = __shfl_sync(0xFFFFFFFFu, sc_f[1][sb >> 2], src);
+        const float o_g = __shfl_sync(0xFFFFFFFFu, mn_f[0][sb >> 2], src);
+        const float o_g8 = __shfl_sync(0xFFFFFFFFu, mn_f[1][sb >> 2], src);
+        const __half2 hs_g = __float2half2_rn(s_g), hs_g8 = __float2half2_rn(s_g8);
+        const __half2 ho_g = __float2half2_rn(-o_g), ho_g8 = __float2half2_rn(-o_g8);
+        const uint32_t sh4 = hi ? 4u : 0u;
+        chunk16<NT>(acc, cur, (w00 >> sh4) & 0x0F0F0F0Fu, (w10 >> sh4) & 0x0F0F0F0Fu, (w01 >> sh4) & 0x0F0F0F0Fu,
+                    (w11 >> sh4) & 0x0F0F0F0Fu, __float2half2_rn(1024.0f), hs_g, hs_g8, hs_g, hs_g8, ho_g, ho_g8);
+        cur = nxt;
+      }
+    }
+  } else {  // Q6_K: the two 16-element halves of a chunk are two scale groups
+    const uint4 sc_g = lds16(tg + 3072 + g * 16);
+    const uint4 sc_g8 = lds16(tg + 3072 + (g + 8) * 16);
+    const float d_g = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 3328 + g * 2));
+    const float d_g8 = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 3328 + (g + 8) * 2));
+    const uint32_t scw_g[4] = {sc_g.x, sc_g.y, sc_g.z, sc_g.w};
+    const uint32_t scw_g8[4] = {sc_g8.x, sc_g8.y, sc_g8.z, sc_g8.w};
+#pragma unroll
+    for (int c2 = 0; c2 < 2; ++c2)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int kc = kg * 8 + c2 * 4 + q;
+        Chunk16<NT> nxt = cur;
+        const int kn = (c2 * 4 + q) < 7 ? kc + 1 : next_first;
+        if (kn >= 0) load_chunk16<NT>(a, kn, g, t, nxt);
+        uint32_t af[2][2];  // [u][row half]
+        __half2 hs[2][2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int cu = c2 * 2 + u, grp = 8 * c2 + 2 * q + u;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t wl = lds4(tg + (cu * 2 + h) * 256 + g * 32 + (q & 1) * 16 + 4 * t);
+            const uint32_t wh = lds4(tg + 2048 + (cu * 2 + h) * 128 + g * 16 + 4 * t);
+            const uint32_t hb = q == 0 ? (wh << 4) : q == 1 ? (wh << 2) : q == 2 ? wh : (wh >> 2);
+            af[u][h] = (((q >> 1) ? (wl >> 4) : wl) & 0x0F0F0F0Fu) | (hb & 0x30303030u);
+          }
+          hs[u][0] = __float2half2_rn(d_g * (float)(int)(int8_t)((scw_g[grp >> 2] >> (8 * (grp & 3))) & 0xFF));
+          hs[u][1] = __float2half2_rn(d_g8 * (float)(int)(int8_t)((scw_g8[grp >> 2] >> (8 * (grp & 3))) & 0xFF));
+        }
+        chunk16<NT>(acc, cur, af[0][0], af[0][1], af[1][0], af[1][1], __float2half2_rn(1056.0f), hs[0][0], hs[0][1],
+                    hs[1][0], hs[1][1], zero2, zero2);  // (q - 32) d scale
+        cur = nxt;
+      }
+  }
+}
+
+// Same persistent ring structure as qgemv_kernel; EPI: 0 none, 1 residual(s), 2 SwiGLU pair.
+template <int TYPE, int NT, int EPI>
+__global__ void __launch_bounds__(GEMV_THREADS)
+qgemm16_kernel(const GemvArgs a) {
+  using R = Ring<TYPE>;
+  constexpr int NP = EPI == 2 ? 2 : 1;
+  constexpr int S = R::STAGES;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* ring = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + R::RING_BYTES);
+  float (*red)[GEMV_WARPS][NT * 8][16] =
+      reinterpret_cast<float (*)[GEMV_WARPS][NT * 8][16]>(smem + R::RING_BYTES + R::BAR_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  uint8_t* my_ring = ring + warp * S * R::STRIDE;
+  const uint32_t my_bar = smem_u32(bars + warp * S);
+
+  pdl_launch_dependents();
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < S; ++s) mbar_init(my_bar + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+
+  const int gw = a.ngroups > warp ? (a.ngroups - warp + GEMV_WARPS - 1) / GEMV_WARPS : 0;
+  const int my_units = a.nunits > (int)blockIdx.x ? (a.nunits - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int per_unit = NP * gw;
+  const int n_items = my_units * per_unit;
+  auto issue = [&](int i) {
+    const int j = i / per_unit, rem = i - j * per_unit;
+    const int p = rem / gw, kk = rem - p * gw;
+    const int tile = (int)blockIdx.x + j * (int)gridDim.x + p * a.pair_tile_offset;
+    const int kg = warp + GEMV_WARPS * kk;
+    const int st = i % S;
+    const uint8_t* src = a.w + ((size_t)tile * a.ngroups + kg) * R::TG;
+    mbar_expect_tx(my_bar + 8 * st, R::TG);
+    bulk_g2s(smem_u32(my_ring + st * R::STRIDE), src, R::TG, my_bar + 8 * st);
+  };
+  if (lane == 0) {
+    const int pre = n_items < S ? n_items : S;
+    for (int i = 0; i < pre; ++i) issue(i);
+  }
+  pdl_wait();  // the packed activations come from the kernel before this one
+
+  constexpr int CHUNKS = (TYPE == FB200_Q4_0 || TYPE == FB200_Q8_0) ? 4 : 8;
+  Chunk16<NT> cur;
+  if (n_items > 0) load_chunk16<NT>(a, warp * CHUNKS, g, t, cur);
+  int item = 0;
+  for (int j = 0; j < my_units; ++j) {
+    const int unit = (int)blockIdx.x + j * (int)gridDim.x;
+    if (j > 0) __syncthreads();  // the previous unit's reduction has read `red`
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      float acc[NT][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+      for (int kk = 0; kk < gw; ++kk, ++item) {
+        const int st = item % S;
+        mbar_wait(my_bar + 8 * st, (uint32_t)((item / S) & 1), a.status);
+        const uint8_t* tg = my_ring + st * R::STRIDE;
+        const int kg = warp + GEMV_WARPS * kk;
+        const int next_first = kk + 1 < gw ? (kg + GEMV_WARPS) * CHUNKS : (item + 1 < n_items ? warp * CHUNKS : -1);
+        group16<TYPE, NT>(a, tg, kg, lane, acc, cur, next_first);
+        __syncwarp();  // every lane has consumed the stage before it is refilled
+        if (lane == 0 && item + S < n_items) issue(item + S);
+      }
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        red[p][warp][8 * nt + 2 * t][g] = acc[nt][0];
+        red[p][warp][8 * nt + 2 * t + 1][g] = acc[nt][1];
+        red[p][warp][8 * nt + 2 * t][g + 8] = acc[nt][2];
+        red[p][warp][8 * nt + 2 * t + 1][g + 8] = acc[nt][3];
+      }
+    }
+    __syncthreads();
+    for (int o = threadIdx.x; o < NT * 8 * 16; o += GEMV_THREADS) {
+      const int m = o >> 4, r = o & 15;
+      const int n = unit * 16 + r;
+      if (m >= a.M || n >= a.n_out) continue;
+      float v[NP];
+#pragma unroll
+      for (int p = 0; p < NP; ++p) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < GEMV_WARPS; ++w) s += red[p][w][m][r];
+        v[p] = s * a.xscale[m];
+      }
+      const size_t idx = (size_t)m * a.n_out + n;
+      float out;
+      if (EPI == 2) {
+        // silu(gate) * up, fusor-ml/fusor/src/composite/activations.rs:47-64
+        const float gate = v[0];
+        out = (gate / (1.0f + expf(-gate))) * v[NP - 1];
+      } else if (EPI == 1) {
+        out = v[0] + a.r1[idx];
+        if (a.r2) out += a.r2[idx];
+      } else {
+        out = v[0];
+      }
+      a.y[idx] = out;
+    }
+  }
+}
+
+// x[M, K] f32 -> fp16 rows scaled by a power of two into (-64, 64), laid out [Kp/32][Mp][32]
+// with lane t's eight halves of a chunk (elements 4t..4t+3, 16+4t..16+4t+3) at byte 16 t.
+// One CTA per (padded) row.
+__global__ void __launch_bounds__(256)
+pack_x16_kernel(const float* __restrict__ x, int M, int K, int Kp, int Mp, __half* __restrict__ xh,
+                float* __restrict__ xscale) {
+  __shared__ float sh[8];
+  const int m = blockIdx.x;
+  const float* xr = x + (size_t)m * K;
+  float amax = 0.f;
+  if (m < M)
+    for (int k = threadIdx.x; k < K; k += 256) amax = fmaxf(amax, fabsf(xr[k]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = 0.f;
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, sh[i]);
+  int ex = 0;
+  if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &ex);
+  const float inv = ldexpf(64.0f, -ex);  // x * inv in (-64, 64)
+  if (threadIdx.x == 0) xscale[m] = ldexpf(1.0f, ex - 6);
+  for (int k = threadIdx.x; k < Kp; k += 256) {
+    const float v = (m < M && k < K) ? xr[k] * inv : 0.f;
+    const int kc = k >> 5, e = k & 31;
+    const int pos = ((e & 15) >> 2) * 8 + (e >> 4) * 4 + (e & 3);
+    xh[((size_t)kc * Mp + m) * 32 + pos] = __float2half_rn(v);
+  }
+}
+
+template <int TYPE, int NT, int EPI>
+int launch_one16(fb200_device* dev, GemvArgs& a) {
+  constexpr int SMEM = gemv_smem_bytes<TYPE, NT, EPI>();
+  static int occ[64] = {0};  // per device ordinal
+  auto kern = qgemm16_kernel<TYPE, NT, EPI>;
+  int& o = occ[dev->ordinal & 63];
+  if (o == 0) {
+    FB_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    int nb = 0;
+    FB_CUDA(dev, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, GEMV_THREADS, SMEM));
+    o = nb > 0 ? nb : 1;
+  }
+  int grid = dev->sm_count * o;
+  if (grid > a.nunits) grid = a.nunits;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(GEMV_THREADS);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = dev->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dev->pdl ? 1 : 0;
+  FB_CUDA(dev, cudaLaunchKernelEx(&cfg, kern, a));
+  dev->launches++;
+  return FB200_OK;
+}
+
+template <int TYPE, int NT>
+int launch_epi16(fb200_device* dev, GemvArgs& a, int epi) {
+  if (epi == FB200_EPI_SWIGLU) return launch_one16<TYPE, NT, 2>(dev, a);
+  if (epi == FB200_EPI_RESIDUAL) return launch_one16<TYPE, NT, 1>(dev, a);
+  return launch_one16<TYPE, NT, 0>(dev, a);
+}
+
+template <int TYPE>
+int launch_nt16(fb200_device* dev, GemvArgs& a, int nt, int epi) {
+  if (nt == 1) return launch_epi16<TYPE, 1>(dev, a, epi);
+  if (nt == 2) return launch_epi16<TYPE, 2>(dev, a, epi);
+  return launch_epi16<TYPE, 4>(dev, a, epi);
+}
+
 template <int TYPE, int NT, int EPI>
 int launch_one(fb200_device* dev, GemvArgs& a) {
   constexpr int SMEM = gemv_smem_bytes<TYPE, NT, EPI>();
@@ -506,6 +908,35 @@ int fb200_qgemv_chunk(fb200_device* dev, const fb200_qmatrix* w, const float* x,
   const int mp = nt * 8;
   const uint64_t kp = (uint64_t)w->ngroups * geo.group_elems;
   const int nl = nt == 1 ? 4 : nt == 2 ? 3 : 2;
+  // FB200_EXACT_SMALL_BATCH=1 keeps 2 .. 8 rows on the int8 limb kernel (2^-27 activations, about
+  // 1.6 times slower); by default every batch of 2 .. 32 rows takes the fp16 kernel
+  static const bool exact_small = getenv("FB200_EXACT_SMALL_BATCH") && getenv("FB200_EXACT_SMALL_BATCH")[0] == '1';
+  if (nt > 1 || !exact_small) {
+    // fp16 activations [Kp/32][Mp][32] + row scales, fp16 tensor-core kernel
+    __half* xh = reinterpret_cast<__half*>(scratch);
+    float* xscale16 = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + (size_t)kp * mp * 2);
+    pack_x16_kernel<<<mp, 256, 0, dev->stream>>>(x, mc, (int)w->k, (int)kp, mp, xh, xscale16);
+    FB_LAUNCH_CHECK(dev);
+    GemvArgs a16;
+    a16.w = w->data; a16.xq = reinterpret_cast<const uint8_t*>(xh); a16.xs16 = nullptr; a16.xscale = xscale16;
+    a16.y = y; a16.r1 = r1; a16.r2 = r2;
+    a16.M = mc; a16.Mp = mp; a16.ngroups = w->ngroups;
+    a16.nunits = w->ntiles;
+    a16.n_out = (int)w->n;
+    a16.pair_tile_offset = 0;
+    a16.status = dev->status;
+    if (epi == FB200_EPI_SWIGLU) {
+      a16.nunits = w->ntiles / 2;
+      a16.n_out = (int)(w->n / 2);
+      a16.pair_tile_offset = w->ntiles / 2;
+    }
+    switch (w->type) {
+      case FB200_Q4_0: return launch_nt16<FB200_Q4_0>(dev, a16, nt, epi);
+      case FB200_Q8_0: return launch_nt16<FB200_Q8_0>(dev, a16, nt, epi);
+      case FB200_Q4_K: return launch_nt16<FB200_Q4_K>(dev, a16, nt, epi);
+      default: return launch_nt16<FB200_Q6_K>(dev, a16, nt, epi);
+    }
+  }
   uint8_t* xq = reinterpret_cast<uint8_t*>(scratch);
   size_t off = (size_t)(kp / 32) * nl * mp * 32;
   float* xs16 = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + off);
