@@ -5,20 +5,20 @@
 // (fusor-ml/tile-ir-kernels/src/kernels/qmatmul.rs:237-349) for large M, where the small-batch
 // kernels would re-read W once per 32 rows.
 //
-// One CTA computes a 128 (weight rows) x 128 (activation rows) tile of Y^T = W . X^T:
+// One CTA computes a 128 (weight rows) x 128 or 256 (activation rows) tile of Y^T = W . X^T:
 //  * W stays quantised in HBM. The raw tile-groups of the CTA's 8 row-tiles for one K group are
 //    brought to shared memory by 1-D TMA bulk copies (double-buffered, one K group ahead);
 //    warp w dequantises row-tile w to fp16 in registers (byte -> 1024 + byte by a byte permute,
 //    exact subtraction, one fused multiply-add with block scale and offset) and stores it into
 //    the A operand buffer in the canonical K-major core-matrix layout of the MMA (8 rows x 16
 //    bytes per core matrix, no swizzle).
-//  * X is converted once per call to fp16 rows scaled by a power of two; its 128 x 64 tile goes
+//  * X is converted once per call to fp16 rows scaled by a power of two; its 128/256 x 64 tile goes
 //    to the B operand buffer with 16-byte cp.async copies in the same layout.
-//  * A single thread issues four tcgen05.mma (M = 128, N = 128, K = 16, kind::f16, fp32
+//  * A single thread issues four tcgen05.mma (M = 128, N = 128 or 256, K = 16, kind::f16, fp32
 //    accumulate) per 64-wide K block; tcgen05.commit signals an mbarrier when the block's MMAs
 //    have read their operands, which frees the buffer for the block after next, so conversion
 //    and tensor-core work overlap (two operand stages).
-//  * Epilogue: tcgen05.ld brings the 128 x 128 fp32 accumulator out of TMEM (each warp its 32
+//  * Epilogue: tcgen05.ld brings the fp32 accumulator out of TMEM (each warp its 32
 //    lanes), rows are scaled back and written, optionally with the residual adds.
 // Every wait is bounded (2^22 polls): on a time-out the status word is set and the CTA goes on
 // to release its TMEM columns and exit.
@@ -32,15 +32,23 @@ namespace {
 
 constexpr int TC_THREADS = 256;
 constexpr int BN = 128;  // weight rows per CTA tile  (M of the MMA)
-constexpr int BM = 128;  // activation rows per CTA tile (N of the MMA)
+// activation rows per CTA tile (N of the MMA): template parameter BM = 128 or 256
 constexpr int BK = 64;   // K elements per operand stage (four K = 16 MMAs)
-constexpr int OPERAND_BYTES = 128 * BK * 2;       // one A or B stage
+constexpr int A_BYTES = BN * BK * 2;              // one A stage
 constexpr int CORE_LBO = 128;                     // bytes between core matrices adjacent in K
 constexpr int CORE_SBO = (BK / 8) * 128;          // bytes between 8-row groups
 constexpr int RAW_STRIDE = 3456;                  // largest tile-group, rounded up to 128
 constexpr int RAW_BYTES = 8 * RAW_STRIDE;
-constexpr int TMEM_COLS = 128;
-constexpr int TC_SMEM = 4 * OPERAND_BYTES + 2 * RAW_BYTES + 64;
+constexpr int TC_STAGES = 3;                      // operand stages: convert / copy ahead of the MMAs
+template <int BM>
+struct Tc {
+  static constexpr int B_BYTES = BM * BK * 2;               // one B stage
+  static constexpr int STAGE = A_BYTES + B_BYTES;
+  static constexpr int SMEM = TC_STAGES * STAGE + 2 * RAW_BYTES + 128;
+  static constexpr int TMEM_COLS = BM;                      // fp32 accumulator columns
+  // instruction descriptor: fp32 accumulator, fp16 A and B, both K-major, N = BM, M = BN
+  static constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BM >> 3) << 17) | ((uint32_t)(BN >> 4) << 24);
+};
 
 struct TcArgs {
   const uint8_t* w;      // tiled weights
@@ -80,14 +88,12 @@ __device__ __forceinline__ uint64_t operand_desc(uint32_t saddr) {
          ((uint64_t)(CORE_SBO >> 4) << 32) | (1ull << 46);
 }
 
-// Instruction descriptor: fp32 accumulator, fp16 A and B, both K-major, N = 128, M = 128.
-constexpr uint32_t TC_IDESC = (1u << 4) | ((uint32_t)(BM >> 3) << 17) | ((uint32_t)(BN >> 4) << 24);
-
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t accumulate) {
   asm volatile(
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(TC_IDESC), "r"(accumulate) : "memory");
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -196,23 +202,25 @@ __device__ __forceinline__ void dequant_chunk(int type, const uint8_t* tg, int c
   }
 }
 
+template <int BM>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 qgemm_tc_kernel(const TcArgs a) {
+  using T = Tc<BM>;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* opnd = smem;                                   // [stage][A | B]
-  uint8_t* raw = smem + 4 * OPERAND_BYTES;                // [2][8 tile-groups]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(raw + 2 * RAW_BYTES);  // raw_full[2], stage_free[2], done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  uint8_t* raw = smem + TC_STAGES * T::STAGE;             // [2][8 tile-groups]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(raw + 2 * RAW_BYTES);  // raw_full[2], stage_free[TC_STAGES], done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 + TC_STAGES);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
-  const uint32_t bar_raw = smem_u32(bars), bar_free = smem_u32(bars + 2), bar_done = smem_u32(bars + 4);
+  const uint32_t bar_raw = smem_u32(bars), bar_free = smem_u32(bars + 2), bar_done = smem_u32(bars + 2 + TC_STAGES);
 
   if (tid == 0) {
-    for (int i = 0; i < 5; ++i) mbar_init(bar_raw + 8 * i, 1);
+    for (int i = 0; i < 3 + TC_STAGES; ++i) mbar_init(bar_raw + 8 * i, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(T::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -232,8 +240,23 @@ qgemm_tc_kernel(const TcArgs a) {
   if (tid == 0) issue_raw(0, 0);
 
   const int blocks_per_group = a.group_elems / BK;  // 4 (K-quants) or 2
+  const int nblocks = a.ngroups * blocks_per_group;
+  // B tile of K block `blk` -> stage blk % TC_STAGES (one cp.async group per block); the stage
+  // is free once the MMAs of block blk - TC_STAGES have read it
+  auto copy_b = [&](int blk) {
+    const int s = blk % TC_STAGES;
+    if (blk >= TC_STAGES) mbar_wait(bar_free + 8 * s, (uint32_t)((blk / TC_STAGES - 1) & 1), a.status);
+    uint8_t* bbuf = opnd + s * T::STAGE + A_BYTES;
+    const int k0 = blk * BK;
+#pragma unroll
+    for (int i = 0; i < BM * 8 / TC_THREADS; ++i) {
+      const int q = tid + TC_THREADS * i, r = q >> 3, kc8 = q & 7;
+      cp_async16(bbuf + (r >> 3) * CORE_SBO + kc8 * CORE_LBO + (r & 7) * 16, a.xh + (size_t)(m0 + r) * a.K + k0 + kc8 * 8);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  copy_b(0);
   int it = 0;
-  bool ok = true;
   for (int kg = 0; kg < a.ngroups; ++kg) {
     const int rb = kg & 1;
     if (tid == 0 && kg + 1 < a.ngroups) issue_raw(kg + 1, rb ^ 1);  // its buffer was drained one group ago
@@ -242,23 +265,19 @@ qgemm_tc_kernel(const TcArgs a) {
     RowScales S;
     if (my_tile < a.ntiles) prepare_scales(a.type, tg, lane >> 2, lane & 3, S);
     for (int b = 0; b < blocks_per_group; ++b, ++it) {
-      const int s = it & 1;
-      uint8_t* abuf = opnd + s * 2 * OPERAND_BYTES;
-      uint8_t* bbuf = abuf + OPERAND_BYTES;
-      if (it >= 2) mbar_wait(bar_free + 8 * s, (uint32_t)(((it >> 1) - 1) & 1), a.status);  // MMAs of block it - 2 are done with it
-      // B: 128 activation rows x 64 K, 16-byte chunks into core matrices
-      const int k0 = kg * a.group_elems + b * BK;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int q = tid + TC_THREADS * i, r = q >> 3, kc8 = q & 7;
-        cp_async16(bbuf + (r >> 3) * CORE_SBO + kc8 * CORE_LBO + (r & 7) * 16, a.xh + (size_t)(m0 + r) * a.K + k0 + kc8 * 8);
-      }
+      const int s = it % TC_STAGES;
+      uint8_t* abuf = opnd + s * T::STAGE;
+      uint8_t* bbuf = abuf + A_BYTES;
+      // the next block's activations start their trip now (also waits for that stage to be free;
+      // stage s itself was freed before its own B copy was issued one iteration ago)
+      if (it + 1 < nblocks) copy_b(it + 1);
+      else asm volatile("cp.async.commit_group;" ::: "memory");
       // A: this warp's row-tile, two 32-element chunks
       if (my_tile < a.ntiles) {
         dequant_chunk(a.type, tg, 2 * b, lane, S, abuf, warp, 0);
         dequant_chunk(a.type, tg, 2 * b + 1, lane, S, abuf, warp, 1);
       }
-      cp_async_wait_all();
+      asm volatile("cp.async.wait_group 1;" ::: "memory");  // block `it`'s activations have landed
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncthreads();
@@ -267,7 +286,8 @@ qgemm_tc_kernel(const TcArgs a) {
         const uint32_t sa = smem_u32(abuf), sb = smem_u32(bbuf);
 #pragma unroll
         for (int ks = 0; ks < BK / 16; ++ks)
-          tc_mma(tmem_d, operand_desc(sa + ks * 2 * CORE_LBO), operand_desc(sb + ks * 2 * CORE_LBO), (it | ks) ? 1u : 0u);
+          tc_mma(tmem_d, operand_desc(sa + ks * 2 * CORE_LBO), operand_desc(sb + ks * 2 * CORE_LBO), T::IDESC,
+                 (it | ks) ? 1u : 0u);
         tc_commit(bar_free + 8 * s);
       }
     }
@@ -275,14 +295,13 @@ qgemm_tc_kernel(const TcArgs a) {
   if (tid == 0) tc_commit(bar_done);
   mbar_wait(bar_done, 0u, a.status);
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  (void)ok;
 
-  // ---- epilogue: warp w reads TMEM lanes 32 (w % 4) .. +31 (weight rows), columns 64 (w / 4) .. +63
+  // ---- epilogue: warp w reads TMEM lanes 32 (w % 4) .. +31 (weight rows) and one half of the columns
   {
     const int n = n0 + 32 * (warp & 3) + lane;
-    const int cbase = 64 * (warp >> 2);
+    const int cbase = (BM / 2) * (warp >> 2);
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
+    for (int half = 0; half < BM / 64; ++half) {
       uint32_t v[32];
       const uint32_t taddr = tmem_d + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(cbase + 32 * half);
       asm volatile(
@@ -310,7 +329,7 @@ qgemm_tc_kernel(const TcArgs a) {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0)
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "n"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "n"(T::TMEM_COLS) : "memory");
 }
 
 // x[M, K] f32 -> fp16 rows [Mp, K] scaled by a power of two into (-64, 64); rows >= M are zero.
@@ -346,7 +365,9 @@ int fb200_qgemm(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_
   if (!enabled || !w->tiled || !tile_geom(w->type, &geo)) return 1;
   const size_t kp = (size_t)w->ngroups * geo.group_elems;
   if (kp != w->k || m > (1u << 20)) return 1;  // K is a whole number of K groups
-  const int mp = (int)((m + BM - 1) / BM) * BM;
+  // 256 activation rows per tile when that still gives every SM a tile
+  const int bm = (size_t)((w->n + BN - 1) / BN) * ((m + 255) / 256) >= (size_t)dev->sm_count ? 256 : 128;
+  const int mp = (int)((m + bm - 1) / bm) * bm;
   const size_t xbytes = (size_t)mp * w->k * 2, need = xbytes + (size_t)mp * sizeof(float);
   int rc = fb200_ensure(dev, &dev->xpack, &dev->xpack_bytes, need);
   if (rc) return rc;
@@ -361,9 +382,11 @@ int fb200_qgemm(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_
   a.group_elems = geo.group_elems; a.status = dev->status;
   static bool configured[64] = {false};
   if (!configured[dev->ordinal & 63]) {
-    FB_CUDA(dev, cudaFuncSetAttribute(qgemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM));
+    FB_CUDA(dev, cudaFuncSetAttribute(qgemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tc<128>::SMEM));
+    FB_CUDA(dev, cudaFuncSetAttribute(qgemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tc<256>::SMEM));
     configured[dev->ordinal & 63] = true;
   }
-  const dim3 grid((unsigned)((w->n + BN - 1) / BN), (unsigned)(mp / BM));
-  return fb200_launch(dev, qgemm_tc_kernel, grid, dim3(TC_THREADS), (size_t)TC_SMEM, false, a);
+  const dim3 grid((unsigned)((w->n + BN - 1) / BN), (unsigned)(mp / bm));
+  if (bm == 256) return fb200_launch(dev, qgemm_tc_kernel<256>, grid, dim3(TC_THREADS), (size_t)Tc<256>::SMEM, false, a);
+  return fb200_launch(dev, qgemm_tc_kernel<128>, grid, dim3(TC_THREADS), (size_t)Tc<128>::SMEM, false, a);
 }
