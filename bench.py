@@ -72,6 +72,15 @@ def peaks():
     return 6650.0, "fallback"
 
 
+def tensor_peak():
+    """Dense bf16 tensor-core peak in TFLOP/s (burst figure: the product kernels are timed alone)."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    return 1590.0, "fallback"
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons during the timed region."""
 
@@ -324,6 +333,17 @@ def run_sweep(args):
             print(json.dumps({"case": "q_mat_mul", "type": tname, "n": n, "k": k, "m": m, "us": us,
                               "algorithmic_bytes": nbytes, "gbs": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / peak,
                               "peak": peak, "peak_source": which, "distinct_weight_buffers": copies}), flush=True)
+        if tname != "Q4_0" and n <= 14336:
+            # prefill product (tcgen05): bound by the tensor cores, not HBM
+            tf_peak = tensor_peak()
+            for m in (512, 2048):
+                x = dev.tensor(np.random.default_rng(m).standard_normal((m, k)).astype(np.float32))
+                y = dev.empty((m, n))
+                us = timed(lambda i: x.q_mat_mul(mats[i % copies], out=y), copies)
+                tf = 2.0 * m * n * k / us / 1e6
+                print(json.dumps({"case": "q_mat_mul_prefill", "type": tname, "n": n, "k": k, "m": m, "us": us,
+                                  "tflops": tf, "frac": tf / tf_peak[0], "peak": tf_peak[0], "peak_source": tf_peak[1],
+                                  "bound": "tensor"}), flush=True)
         for w in mats:
             w.free()
     # decode attention: one query position per sequence against L cached keys (fp16), Llama-3-8B heads
@@ -367,7 +387,17 @@ def run_ours(args):
     model = build_gpu_model(dev, torch, CFG, batch, ctx, seed=1 + rank, keep=keep)
     rng = np.random.default_rng(rank)
     prompt = rng.integers(0, CFG["vocab"], size=(batch, PROMPT), dtype=np.uint32)
+    model.forward(prompt, want_logits=False)
+    # prefill of the prompt (host ids in, next token out), timed once warm; reported beside the
+    # decode metric, not part of it
+    model.reset()
+    torch.cuda.synchronize()
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record(stream)
     _, nxt = model.forward(prompt, want_logits=False)
+    p1.record(stream)
+    torch.cuda.synchronize()
+    ms_prefill = p0.elapsed_time(p1)
 
     def barrier():
         if world > 1:
@@ -459,6 +489,8 @@ def run_ours(args):
                     "d2h_bytes_per_step": 4 * batch, "ms_per_step": ms_e2e / steps},
             "gpu_launches": int(launches), "device_status": status, "clocks": clocks,
             "roofline": roof, "roofline_gemv_alone": roof_gemv,
+            "prefill": {"tokens": batch * PROMPT, "ms": ms_prefill, "tok_s": batch * PROMPT / ms_prefill * 1e3,
+                        "kernel": "quantised products on tcgen05 tensor cores (fp16 operands, fp32 TMEM accumulator)"},
             "step_hbm": {"bytes_per_step": wb + kv, "achieved_gbs": step_gbs, "frac_of_peak": step_gbs / peak,
                          "peak_source": which},
             "cpu_baseline": cpu}

@@ -10,7 +10,7 @@ int fb200_qgemv_chunk(fb200_device* dev, const fb200_qmatrix* w, const float* x,
                       int epi, const float* r1, const float* r2, void* scratch);
 int fb200_dense_matmul(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_t m, float* y);
 int fb200_qgemm(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_t m, float* y, const float* r1,
-                const float* r2);
+                const float* r2, int swiglu);
 bool fb200_qgemv1_fits(const fb200_qmatrix* w);
 int fb200_qgemv1(fb200_device* dev, const fb200_qmatrix* w, const float* x, const float* xres,
                  const float* norm_w, float eps, float* y, int epi, const float* r1, const float* r2);
@@ -340,9 +340,9 @@ int fb200_q_mat_mul(fb200_device* dev, const float* x_dev, size_t m, const fb200
   if (m == 1 && fb200_qgemv1_fits(w))
     return fb200_qgemv1(dev, w, x_dev, nullptr, nullptr, 0.f, y_dev, epi, ep ? ep->r1_dev : nullptr,
                         ep ? ep->r2_dev : nullptr);
-  if (epi != FB200_EPI_SWIGLU && m > 32) {
+  if (m > 32) {
     rc = fb200_qgemm(dev, w, x_dev, m, y_dev, epi == FB200_EPI_RESIDUAL ? ep->r1_dev : nullptr,
-                     epi == FB200_EPI_RESIDUAL ? ep->r2_dev : nullptr);
+                     epi == FB200_EPI_RESIDUAL ? ep->r2_dev : nullptr, epi == FB200_EPI_SWIGLU ? 1 : 0);
     if (rc != 1) return rc;  // 1 = shape not covered by the tensor-core GEMM; fall through
   }
   TileGeom g;

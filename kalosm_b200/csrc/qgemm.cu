@@ -5,23 +5,33 @@
 // (fusor-ml/tile-ir-kernels/src/kernels/qmatmul.rs:237-349) for large M, where the small-batch
 // kernels would re-read W once per 32 rows.
 //
-// One CTA computes a 128 (weight rows) x 128 or 256 (activation rows) tile of Y^T = W . X^T:
-//  * W stays quantised in HBM. The raw tile-groups of the CTA's 8 row-tiles for one K group are
-//    brought to shared memory by 1-D TMA bulk copies (double-buffered, one K group ahead);
-//    warp w dequantises row-tile w to fp16 in registers (byte -> 1024 + byte by a byte permute,
-//    exact subtraction, one fused multiply-add with block scale and offset) and stores it into
-//    the A operand buffer in the canonical K-major core-matrix layout of the MMA (8 rows x 16
-//    bytes per core matrix, no swizzle).
-//  * X is converted once per call to fp16 rows scaled by a power of two; its 128/256 x 64 tile goes
-//    to the B operand buffer with 16-byte cp.async copies in the same layout.
-//  * A single thread issues four tcgen05.mma (M = 128, N = 128 or 256, K = 16, kind::f16, fp32
-//    accumulate) per 64-wide K block; tcgen05.commit signals an mbarrier when the block's MMAs
-//    have read their operands, which frees the buffer for the block after next, so conversion
-//    and tensor-core work overlap (two operand stages).
-//  * Epilogue: tcgen05.ld brings the fp32 accumulator out of TMEM (each warp its 32
-//    lanes), rows are scaled back and written, optionally with the residual adds.
-// Every wait is bounded (2^22 polls): on a time-out the status word is set and the CTA goes on
-// to release its TMEM columns and exit.
+// One CTA computes a tile of NH x 128 weight rows by BM = 128 or 256 activation rows of
+// Y^T = W . X^T; the fp32 accumulators (NH x BM columns of 128 lanes) live in TMEM. The roles
+// are coupled only by mbarriers, there is no CTA-wide barrier in the main loop:
+//  * weight loader (one thread): W stays quantised in HBM; the raw tile-groups of the CTA's
+//    8 NH row-tiles for one K group come by 1-D TMA bulk copies, two K groups in flight.
+//  * conversion warps (8 NH, one per row-tile): dequantise to fp16 in registers (byte -> 1024 +
+//    byte by a byte permute, exact subtraction, one fused multiply-add with block scale and
+//    offset) and store into the A operand stage in the canonical K-major core-matrix layout of
+//    the MMA (8 rows x 16 bytes per core matrix, no swizzle); a proxy fence, then one arrive per
+//    warp on the stage's "A full" barrier.
+//  * activation loader (one thread): X is converted once per call to fp16 rows scaled by a power
+//    of two and stored tile by tile in the same operand layout, so a B stage is one contiguous
+//    bulk copy.
+//  * MMA issuer (one thread): waits for "A full" and "B full", issues 4 NH tcgen05.mma (M = 128,
+//    N = BM, K = 16, kind::f16, fp32 accumulate) per 64-wide K block; tcgen05.commit on the
+//    stage's "free" barrier hands the stage back to both producers (2..4 stages, as many as fit
+//    beside the raw buffers).
+//  * Epilogue: tcgen05.ld brings the accumulator out of TMEM (each warp its 32 lanes), rows are
+//    scaled back and written, with the residual adds or SwiGLU (gate and up rows are the two
+//    halves of one CTA, so both values of an output sit in the same TMEM lane).
+// Every wait is bounded (2^22 polls): on a time-out the status word and a give-up flag in shared
+// memory are set, the other roles leave at their next poll, and the CTA releases its TMEM
+// columns and exits. FB200_TCGEN05=0 switches the kernel off (32-row kernel in chunks);
+// FB200_TC_TILE="BM,NH" forces a tile shape (tests, tuning).
+#include <algorithm>
+#include <cstdint>
+#include <cstdio>
 #include <cstdlib>
 
 #include "qgemv_common.cuh"
@@ -30,43 +40,60 @@ int fb200_ensure(fb200_device* dev, void** buf, size_t* cur, size_t bytes);
 
 namespace {
 
-constexpr int TC_THREADS = 256;
-constexpr int BN = 128;  // weight rows per CTA tile  (M of the MMA)
+constexpr int BN = 128;  // weight rows per MMA (M of the MMA); a CTA tile holds NH such halves
 // activation rows per CTA tile (N of the MMA): template parameter BM = 128 or 256
 constexpr int BK = 64;   // K elements per operand stage (four K = 16 MMAs)
-constexpr int A_BYTES = BN * BK * 2;              // one A stage
+constexpr int A_HALF = BN * BK * 2;               // one 128-row half of an A stage
 constexpr int CORE_LBO = 128;                     // bytes between core matrices adjacent in K
 constexpr int CORE_SBO = (BK / 8) * 128;          // bytes between 8-row groups
-constexpr int RAW_STRIDE = 3456;                  // largest tile-group, rounded up to 128
-constexpr int RAW_BYTES = 8 * RAW_STRIDE;
-constexpr int TC_STAGES = 3;                      // operand stages: convert / copy ahead of the MMAs
-template <int BM>
+constexpr int MAX_STAGES = 4;
+constexpr int TAIL_BYTES = 256;                   // barriers, TMEM slot, give-up flag
+constexpr int SMEM_BUDGET = 227 * 1024;
+template <int BM, int NH>
 struct Tc {
+  static constexpr int A_BYTES = NH * A_HALF;               // one A stage
   static constexpr int B_BYTES = BM * BK * 2;               // one B stage
   static constexpr int STAGE = A_BYTES + B_BYTES;
-  static constexpr int SMEM = TC_STAGES * STAGE + 2 * RAW_BYTES + 128;
-  static constexpr int TMEM_COLS = BM;                      // fp32 accumulator columns
+  static constexpr int TMEM_COLS = NH * BM;                 // fp32 accumulator columns
+  static constexpr int DQ_WARPS = 8 * NH;                   // one warp per 16-row tile
+  static constexpr int THREADS = (DQ_WARPS + 3) * 32;       // + weight loader, activation loader, MMA issuer
   // instruction descriptor: fp32 accumulator, fp16 A and B, both K-major, N = BM, M = BN
   static constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BM >> 3) << 17) | ((uint32_t)(BN >> 4) << 24);
 };
 
 struct TcArgs {
   const uint8_t* w;      // tiled weights
-  const __half* xh;      // [Mp, K] fp16 activations (rows >= M are zero)
+  const __half* xh;      // fp16 activations, [Mp / BM][K / 64] tiles already in the operand layout
   const float* xscale;   // [Mp] power-of-two scale of each row
   float* y;              // [M, N]
   const float* r1;       // optional residuals [M, N]
   const float* r2;
   int M, N, K;
   int ngroups, ntiles, type, tgb, group_elems;
+  int stages, raw_stride;  // operand stages that fit beside the raw buffers; bytes per raw tile-group slot
+  int pair_tiles;          // SwiGLU (NH = 2): half 0 = gate rows, half 1 = up rows pair_tiles row-tiles further;
+                           // y[M, N / 2] = silu(gate) * up. 0 = plain product
   int* status;
 };
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void cp_async_wait_all() {
-  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+// Bounded wait of the pipeline roles: gives up after 2^22 polls, or as soon as another thread
+// of the CTA has given up (so a broken pipeline drains in one time-out, not one per wait).
+__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile int* dead, int* status) {
+  for (int it = 0; it < (1 << 22); ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((it & 255) == 255 && *dead) return false;
+  }
+  *dead = 1;
+  if (status) atomicExch(status, FB200_ERR_TIMEOUT);
+  return false;
 }
 __device__ __forceinline__ uint32_t h2u(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 __device__ __forceinline__ __half2 u2h(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
@@ -97,6 +124,14 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t
 }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr) : "memory");
 }
 
 // Row-tile `tile` of one K group: the four registers of 32-element chunk c for lane (g, t) --
@@ -156,10 +191,10 @@ __device__ __forceinline__ void dequant_chunk(int type, const uint8_t* tg, int c
     const uint32_t w10 = (lds4(tg + ((ch * 2 + 1) * 2 + 0) * 256 + off) >> sh4) & 0x0F0F0F0Fu;  // row g + 8
     const uint32_t w11 = (lds4(tg + ((ch * 2 + 1) * 2 + 1) * 256 + off) >> sh4) & 0x0F0F0F0Fu;
     const int src = (lane & ~3) | (c & 3);
-    const __half2 s_g = __float2half2_rn(__shfl_sync(0xFFFFFFFFu, S.sc[0][c >> 2], src));
-    const __half2 s_g8 = __float2half2_rn(__shfl_sync(0xFFFFFFFFu, S.sc[1][c >> 2], src));
-    const __half2 o_g = __float2half2_rn(-__shfl_sync(0xFFFFFFFFu, S.mn[0][c >> 2], src));
-    const __half2 o_g8 = __float2half2_rn(-__shfl_sync(0xFFFFFFFFu, S.mn[1][c >> 2], src));
+    const __half2 s_g = __float2half2_rn(__shfl_sync(0xFFFFFFFFu, ((c >> 2) ? S.sc[0][1] : S.sc[0][0]), src));
+    const __half2 s_g8 = __float2half2_rn(__shfl_sync(0xFFFFFFFFu, ((c >> 2) ? S.sc[1][1] : S.sc[1][0]), src));
+    const __half2 o_g = __float2half2_rn(-__shfl_sync(0xFFFFFFFFu, ((c >> 2) ? S.mn[0][1] : S.mn[0][0]), src));
+    const __half2 o_g8 = __float2half2_rn(-__shfl_sync(0xFFFFFFFFu, ((c >> 2) ? S.mn[1][1] : S.mn[1][0]), src));
     const __half2 ctr = __float2half2_rn(1024.0f);
     store_chunk(abuf, wrow, g, t, cib, deq4(w00, ctr, s_g, o_g), deq4(w10, ctr, s_g8, o_g8), deq4(w01, ctr, s_g, o_g),
                 deq4(w11, ctr, s_g8, o_g8));
@@ -202,21 +237,35 @@ __device__ __forceinline__ void dequant_chunk(int type, const uint8_t* tg, int c
   }
 }
 
-template <int BM>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+template <int BM, int NH>
+__global__ void __launch_bounds__(Tc<BM, NH>::THREADS, 1)
 qgemm_tc_kernel(const TcArgs a) {
-  using T = Tc<BM>;
+  using T = Tc<BM, NH>;
   extern __shared__ __align__(1024) uint8_t smem[];
-  uint8_t* opnd = smem;                                   // [stage][A | B]
-  uint8_t* raw = smem + TC_STAGES * T::STAGE;             // [2][8 tile-groups]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(raw + 2 * RAW_BYTES);  // raw_full[2], stage_free[TC_STAGES], done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 + TC_STAGES);
+  const int raw_bytes = T::DQ_WARPS * a.raw_stride;
+  uint8_t* opnd = smem;                                   // [stage][A halves | B]
+  uint8_t* raw = smem + a.stages * T::STAGE;              // [2][DQ_WARPS tile-groups]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(raw + 2 * raw_bytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
+  volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
-  const uint32_t bar_raw = smem_u32(bars), bar_free = smem_u32(bars + 2), bar_done = smem_u32(bars + 2 + TC_STAGES);
+  const int n0 = blockIdx.x * (a.pair_tiles ? BN : BN * NH), m0 = blockIdx.y * BM;
+  const uint32_t bar_raw_full = smem_u32(bars), bar_raw_free = smem_u32(bars + 2), bar_a_full = smem_u32(bars + 4),
+                 bar_b_full = smem_u32(bars + 4 + MAX_STAGES), bar_free = smem_u32(bars + 4 + 2 * MAX_STAGES),
+                 bar_done = smem_u32(bars + 4 + 3 * MAX_STAGES);
 
   if (tid == 0) {
-    for (int i = 0; i < 3 + TC_STAGES; ++i) mbar_init(bar_raw + 8 * i, 1);
+    *dead = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_raw_full + 8 * i, 1);
+      mbar_init(bar_raw_free + 8 * i, T::DQ_WARPS);
+    }
+    for (int i = 0; i < MAX_STAGES; ++i) {
+      mbar_init(bar_a_full + 8 * i, T::DQ_WARPS);
+      mbar_init(bar_b_full + 8 * i, 1);
+      mbar_init(bar_free + 8 * i, 1);
+    }
+    mbar_init(bar_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -229,81 +278,129 @@ qgemm_tc_kernel(const TcArgs a) {
   const uint32_t tmem_d = *tmem_slot;
 
   const int tile0 = n0 / 16;
-  const int my_tile = tile0 + warp;
-  const int ntile_here = min(8, a.ntiles - tile0);
-  auto issue_raw = [&](int kg, int rb) {  // thread 0
-    mbar_expect_tx(bar_raw + 8 * rb, (uint32_t)(ntile_here * a.tgb));
-    for (int i = 0; i < ntile_here; ++i)
-      bulk_g2s(smem_u32(raw + rb * RAW_BYTES + i * RAW_STRIDE), a.w + ((size_t)(tile0 + i) * a.ngroups + kg) * a.tgb,
-               (uint32_t)a.tgb, bar_raw + 8 * rb);
-  };
-  if (tid == 0) issue_raw(0, 0);
-
+  // row-tile converted by warp i, and whether the matrix has it
+  auto tile_of = [&](int i) { return a.pair_tiles ? tile0 + (i & 7) + (i >> 3) * a.pair_tiles : tile0 + i; };
+  auto has_tile = [&](int i) { return a.pair_tiles ? tile0 + (i & 7) < a.pair_tiles : tile0 + i < a.ntiles; };
   const int blocks_per_group = a.group_elems / BK;  // 4 (K-quants) or 2
   const int nblocks = a.ngroups * blocks_per_group;
-  // B tile of K block `blk` -> stage blk % TC_STAGES (one cp.async group per block); the stage
-  // is free once the MMAs of block blk - TC_STAGES have read it
-  auto copy_b = [&](int blk) {
-    const int s = blk % TC_STAGES;
-    if (blk >= TC_STAGES) mbar_wait(bar_free + 8 * s, (uint32_t)((blk / TC_STAGES - 1) & 1), a.status);
-    uint8_t* bbuf = opnd + s * T::STAGE + A_BYTES;
-    const int k0 = blk * BK;
-#pragma unroll
-    for (int i = 0; i < BM * 8 / TC_THREADS; ++i) {
-      const int q = tid + TC_THREADS * i, r = q >> 3, kc8 = q & 7;
-      cp_async16(bbuf + (r >> 3) * CORE_SBO + kc8 * CORE_LBO + (r & 7) * 16, a.xh + (size_t)(m0 + r) * a.K + k0 + kc8 * 8);
+
+  if (warp < T::DQ_WARPS) {
+    // ---- conversion: warp w turns row-tile w of each K block into fp16 operand rows
+    const bool mine = has_tile(warp);
+    uint8_t* const a_rows = opnd + (warp >> 3) * A_HALF;
+    int s = 0, round = 0;
+    bool alive = true;
+    for (int kg = 0; kg < a.ngroups && alive; ++kg) {
+      const int rb = kg & 1;
+      alive = tc_wait(bar_raw_full + 8 * rb, (uint32_t)((kg >> 1) & 1), dead, a.status);
+      if (!alive) break;
+      const uint8_t* tg = raw + rb * raw_bytes + warp * a.raw_stride;
+      RowScales S;
+      if (mine) prepare_scales(a.type, tg, lane >> 2, lane & 3, S);
+      for (int b = 0; b < blocks_per_group; ++b) {
+        // the stage is free once the MMAs of its previous use have read it
+        if (round > 0) alive = tc_wait(bar_free + 8 * s, (uint32_t)((round - 1) & 1), dead, a.status);
+        if (!alive) break;
+        uint8_t* abuf = a_rows + s * T::STAGE;
+        if (mine) {
+          dequant_chunk(a.type, tg, 2 * b, lane, S, abuf, warp & 7, 0);
+          dequant_chunk(a.type, tg, 2 * b + 1, lane, S, abuf, warp & 7, 1);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_a_full + 8 * s);
+        if (++s == a.stages) { s = 0; ++round; }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_raw_free + 8 * rb);
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  };
-  copy_b(0);
-  int it = 0;
-  for (int kg = 0; kg < a.ngroups; ++kg) {
-    const int rb = kg & 1;
-    if (tid == 0 && kg + 1 < a.ngroups) issue_raw(kg + 1, rb ^ 1);  // its buffer was drained one group ago
-    mbar_wait(bar_raw + 8 * rb, (uint32_t)((kg >> 1) & 1), a.status);
-    const uint8_t* tg = raw + rb * RAW_BYTES + warp * RAW_STRIDE;
-    RowScales S;
-    if (my_tile < a.ntiles) prepare_scales(a.type, tg, lane >> 2, lane & 3, S);
-    for (int b = 0; b < blocks_per_group; ++b, ++it) {
-      const int s = it % TC_STAGES;
-      uint8_t* abuf = opnd + s * T::STAGE;
-      uint8_t* bbuf = abuf + A_BYTES;
-      // the next block's activations start their trip now (also waits for that stage to be free;
-      // stage s itself was freed before its own B copy was issued one iteration ago)
-      if (it + 1 < nblocks) copy_b(it + 1);
-      else asm volatile("cp.async.commit_group;" ::: "memory");
-      // A: this warp's row-tile, two 32-element chunks
-      if (my_tile < a.ntiles) {
-        dequant_chunk(a.type, tg, 2 * b, lane, S, abuf, warp, 0);
-        dequant_chunk(a.type, tg, 2 * b + 1, lane, S, abuf, warp, 1);
+  } else if (warp == T::DQ_WARPS) {
+    // ---- weight loader: raw tile-groups of one K group, two groups in flight
+    if (lane == 0) {
+      int ntile_here = 0;
+      for (int i = 0; i < T::DQ_WARPS; ++i) ntile_here += has_tile(i) ? 1 : 0;
+      for (int kg = 0; kg < a.ngroups; ++kg) {
+        const int rb = kg & 1;
+        if (kg >= 2 && !tc_wait(bar_raw_free + 8 * rb, (uint32_t)(((kg >> 1) - 1) & 1), dead, a.status)) break;
+        mbar_expect_tx(bar_raw_full + 8 * rb, (uint32_t)(ntile_here * a.tgb));
+        for (int i = 0; i < T::DQ_WARPS; ++i)
+          if (has_tile(i))
+            bulk_g2s(smem_u32(raw + rb * raw_bytes + i * a.raw_stride), a.w + ((size_t)tile_of(i) * a.ngroups + kg) * a.tgb,
+                     (uint32_t)a.tgb, bar_raw_full + 8 * rb);
       }
-      asm volatile("cp.async.wait_group 1;" ::: "memory");  // block `it`'s activations have landed
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncthreads();
-      if (tid == 0) {
+    }
+  } else if (warp == T::DQ_WARPS + 1) {
+    // ---- activation loader: one bulk copy per K block (the tile is stored in operand layout)
+    if (lane == 0) {
+      const __half* src = a.xh + (size_t)blockIdx.y * nblocks * (BM * BK);
+      int s = 0, round = 0;
+      for (int blk = 0; blk < nblocks; ++blk) {
+        if (round > 0 && !tc_wait(bar_free + 8 * s, (uint32_t)((round - 1) & 1), dead, a.status)) break;
+        mbar_expect_tx(bar_b_full + 8 * s, (uint32_t)T::B_BYTES);
+        bulk_g2s(smem_u32(opnd + s * T::STAGE + T::A_BYTES), src + (size_t)blk * (BM * BK), (uint32_t)T::B_BYTES,
+                 bar_b_full + 8 * s);
+        if (++s == a.stages) { s = 0; ++round; }
+      }
+    }
+  } else {
+    // ---- MMA issuer: 4 NH instructions per K block; the commit frees the stage
+    if (lane == 0) {
+      int s = 0, round = 0;
+      bool alive = true;
+      for (int blk = 0; blk < nblocks; ++blk) {
+        alive = tc_wait(bar_a_full + 8 * s, (uint32_t)(round & 1), dead, a.status) &&
+                tc_wait(bar_b_full + 8 * s, (uint32_t)(round & 1), dead, a.status);
+        if (!alive) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t sa = smem_u32(abuf), sb = smem_u32(bbuf);
+        const uint32_t sa = smem_u32(opnd + s * T::STAGE), sb = sa + T::A_BYTES;
 #pragma unroll
-        for (int ks = 0; ks < BK / 16; ++ks)
-          tc_mma(tmem_d, operand_desc(sa + ks * 2 * CORE_LBO), operand_desc(sb + ks * 2 * CORE_LBO), T::IDESC,
-                 (it | ks) ? 1u : 0u);
+        for (int h = 0; h < NH; ++h)
+#pragma unroll
+          for (int ks = 0; ks < BK / 16; ++ks)
+            tc_mma(tmem_d + (uint32_t)(h * BM), operand_desc(sa + h * A_HALF + ks * 2 * CORE_LBO),
+                   operand_desc(sb + ks * 2 * CORE_LBO), T::IDESC, (blk | ks) ? 1u : 0u);
         tc_commit(bar_free + 8 * s);
+        if (++s == a.stages) { s = 0; ++round; }
       }
+      if (alive) tc_commit(bar_done);
     }
   }
-  if (tid == 0) tc_commit(bar_done);
-  mbar_wait(bar_done, 0u, a.status);
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-  // ---- epilogue: warp w reads TMEM lanes 32 (w % 4) .. +31 (weight rows) and one half of the columns
-  {
-    const int n = n0 + 32 * (warp & 3) + lane;
-    const int cbase = (BM / 2) * (warp >> 2);
+  // ---- epilogue: warp w reads TMEM lanes 32 (w % 4) .. +31 (weight rows) of one half and one
+  // half of that half's columns
+  if (NH == 2 && a.pair_tiles) {
+    // SwiGLU: the gate and the up value of an output sit in the same TMEM lane, BM columns apart
+    if (warp < T::DQ_WARPS && tc_wait(bar_done, 0u, dead, a.status)) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int n = n0 + 32 * (warp & 3) + lane, n_out = a.pair_tiles * 16;
+      const int cbase = (BM / 4) * (warp >> 2);
 #pragma unroll
-    for (int half = 0; half < BM / 64; ++half) {
+      for (int i = 0; i < BM / 64; ++i) {
+        uint32_t g[16], u[16];
+        const uint32_t taddr = tmem_d + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(cbase + 16 * i);
+        tmem_ld16(taddr, g);
+        tmem_ld16(taddr + BM, u);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = m0 + cbase + 16 * i + j;
+          if (m < a.M && n < n_out) {
+            // silu(gate) * up, fusor-ml/fusor/src/composite/activations.rs:47-64: x / (1 + exp(-x))
+            const float sc = a.xscale[m], gate = __uint_as_float(g[j]) * sc;
+            a.y[(size_t)m * n_out + n] = (gate / (1.0f + expf(-gate))) * (__uint_as_float(u[j]) * sc);
+          }
+        }
+      }
+    }
+  } else if (warp < T::DQ_WARPS && tc_wait(bar_done, 0u, dead, a.status)) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int part = warp >> 2, h = part >> 1;
+    const int n = n0 + h * BN + 32 * (warp & 3) + lane;
+    const int cbase = (BM / 2) * (part & 1);
+#pragma unroll
+    for (int i = 0; i < BM / 64; ++i) {
       uint32_t v[32];
-      const uint32_t taddr = tmem_d + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(cbase + 32 * half);
+      const uint32_t taddr = tmem_d + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(h * BM + cbase + 32 * i);
       asm volatile(
           "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
           "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -315,7 +412,7 @@ qgemm_tc_kernel(const TcArgs a) {
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
-        const int m = m0 + cbase + 32 * half + j;
+        const int m = m0 + cbase + 32 * i + j;
         if (m < a.M && n < a.N) {
           const size_t idx = (size_t)m * a.N + n;
           float out = __uint_as_float(v[j]) * a.xscale[m];
@@ -332,61 +429,114 @@ qgemm_tc_kernel(const TcArgs a) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "n"(T::TMEM_COLS) : "memory");
 }
 
-// x[M, K] f32 -> fp16 rows [Mp, K] scaled by a power of two into (-64, 64); rows >= M are zero.
+// x[M, K] f32 -> fp16 scaled by a power of two per row into (-64, 64), stored as [Mp / bm][K / 64]
+// tiles of bm rows x 64 values in the operand layout of the MMA (8 rows x 16 bytes per core
+// matrix, core matrices adjacent in K 128 bytes apart, 8-row groups 1024 bytes apart), so that a
+// tile is one contiguous bulk copy. One CTA per 8 rows; rows >= M are zero.
 __global__ void __launch_bounds__(256)
-pack_rows16_kernel(const float* __restrict__ x, int M, int K, __half* __restrict__ xh, float* __restrict__ xscale) {
-  __shared__ float sh[8];
-  const int m = blockIdx.x;
-  const float* xr = x + (size_t)m * K;
-  float amax = 0.f;
-  if (m < M)
-    for (int k = threadIdx.x; k < K; k += 256) amax = fmaxf(amax, fabsf(xr[k]));
+pack_rows16_kernel(const float* __restrict__ x, int M, int K, int bm, __half* __restrict__ xh, float* __restrict__ xscale) {
+  __shared__ float inv_s[8];
+  const int m0 = blockIdx.x * 8, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  {
+    const int m = m0 + warp;
+    float amax = 0.f;
+    if (m < M) {
+      const float* xr = x + (size_t)m * K;
+      for (int k = lane; k < K; k += 32) amax = fmaxf(amax, fabsf(xr[k]));
+    }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = amax;
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    if (lane == 0) {
+      int ex = 0;
+      if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &ex);
+      inv_s[warp] = ldexpf(64.0f, -ex);
+      xscale[m] = ldexpf(1.0f, ex - 6);
+    }
+  }
   __syncthreads();
-  amax = 0.f;
-  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, sh[i]);
-  int ex = 0;
-  if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &ex);
-  const float inv = ldexpf(64.0f, -ex);
-  if (threadIdx.x == 0) xscale[m] = ldexpf(1.0f, ex - 6);
-  for (int k = threadIdx.x; k < K; k += 256) xh[(size_t)m * K + k] = __float2half_rn(m < M ? xr[k] * inv : 0.f);
+  const int nkb = K / BK;
+  uint8_t* tile_row = reinterpret_cast<uint8_t*>(xh) + (size_t)(m0 / bm) * nkb * ((size_t)bm * BK * 2) + ((m0 % bm) >> 3) * CORE_SBO;
+  for (int q = threadIdx.x; q < K; q += 256) {  // K / 8 chunks of 8 values x 8 rows
+    const int r7 = q & 7, kc = q >> 3, m = m0 + r7;
+    uint4 out = make_uint4(0u, 0u, 0u, 0u);
+    if (m < M) {
+      const float4* src = reinterpret_cast<const float4*>(x + (size_t)m * K + 8 * kc);
+      const float4 lo = src[0], hi = src[1];
+      const float inv = inv_s[r7];
+      out.x = h2u(__floats2half2_rn(lo.x * inv, lo.y * inv));
+      out.y = h2u(__floats2half2_rn(lo.z * inv, lo.w * inv));
+      out.z = h2u(__floats2half2_rn(hi.x * inv, hi.y * inv));
+      out.w = h2u(__floats2half2_rn(hi.z * inv, hi.w * inv));
+    }
+    *reinterpret_cast<uint4*>(tile_row + (size_t)(kc >> 3) * ((size_t)bm * BK * 2) + (kc & 7) * CORE_LBO + r7 * 16) = out;
+  }
+}
+
+template <int BM, int NH>
+int launch_tc(fb200_device* dev, const TcArgs& a, unsigned grid_n, unsigned grid_m, int smem) {
+  using T = Tc<BM, NH>;
+  static bool configured[64] = {false};
+  if (!configured[dev->ordinal & 63]) {
+    FB_CUDA(dev, cudaFuncSetAttribute(qgemm_tc_kernel<BM, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET));
+    configured[dev->ordinal & 63] = true;
+  }
+  return fb200_launch(dev, qgemm_tc_kernel<BM, NH>, dim3(grid_n, grid_m), dim3(T::THREADS), (size_t)smem, false, a);
 }
 
 }  // namespace
 
-// y[M, N] = x[M, K] . W^T (+ r1 + r2) for M > 32. Returns 1 when the shape is not covered (the
+// y[M, N] = x[M, K] . W^T (+ r1 + r2) for M > 32; with `swiglu`, W stacks gate rows over up rows
+// and y[M, N / 2] = silu(gate) * up. Returns 1 when the shape is not covered (the
 // caller falls back to the small-batch kernel in chunks of 32 rows).
 int fb200_qgemm(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_t m, float* y, const float* r1,
-                const float* r2) {
+                const float* r2, int swiglu) {
   static const bool enabled = !(getenv("FB200_TCGEN05") && getenv("FB200_TCGEN05")[0] == '0');
   TileGeom geo;
   if (!enabled || !w->tiled || !tile_geom(w->type, &geo)) return 1;
   const size_t kp = (size_t)w->ngroups * geo.group_elems;
   if (kp != w->k || m > (1u << 20)) return 1;  // K is a whole number of K groups
-  // 256 activation rows per tile when that still gives every SM a tile
-  const int bm = (size_t)((w->n + BN - 1) / BN) * ((m + 255) / 256) >= (size_t)dev->sm_count ? 256 : 128;
+  if (reinterpret_cast<uintptr_t>(x) & 15) return 1;
+  // CTA tile: NH x 128 weight rows by bm activation rows. Cost model: waves x tile area; among
+  // equals the larger tile (fewer re-reads of the activations through L2).
+  const int raw_stride = (geo.tg_bytes + 127) & ~127;
+  int best_bm = 0, best_nh = 0, best_stages = 0;
+  size_t best_cost = ~(size_t)0;
+  int force_bm = 0, force_nh = 0;
+  if (const char* cfg = getenv("FB200_TC_TILE")) sscanf(cfg, "%d,%d", &force_bm, &force_nh);
+  // measured time per unit of tile area relative to the 256 x 256 tile, in 1/64ths
+  static const int rel_cost[2][2] = {{134, 87}, {96, 64}};  // [nh - 1][bm == 256]
+  const size_t n_rows = swiglu ? w->n / 2 : w->n;  // weight rows along the grid
+  for (int nh = 2; nh >= (swiglu ? 2 : 1); --nh)
+    for (int bm = 256; bm >= 128; bm -= 128) {
+      if ((force_bm && bm != force_bm) || (force_nh && nh != force_nh && !swiglu)) continue;
+      const int stage = nh * A_HALF + bm * BK * 2;
+      const int stages = std::min(MAX_STAGES, (SMEM_BUDGET - TAIL_BYTES - 2 * 8 * nh * raw_stride) / stage);
+      if (stages < 2) continue;
+      const size_t rows_per_cta = swiglu ? BN : BN * nh;
+      const size_t ctas = ((n_rows + rows_per_cta - 1) / rows_per_cta) * ((m + bm - 1) / bm);
+      const size_t cost = ((ctas + dev->sm_count - 1) / dev->sm_count) * (size_t)(nh * bm) * rel_cost[nh - 1][bm == 256];
+      if (cost < best_cost) { best_cost = cost; best_bm = bm; best_nh = nh; best_stages = stages; }
+    }
+  if (!best_bm) return 1;
+  const int bm = best_bm, nh = best_nh;
   const int mp = (int)((m + bm - 1) / bm) * bm;
   const size_t xbytes = (size_t)mp * w->k * 2, need = xbytes + (size_t)mp * sizeof(float);
   int rc = fb200_ensure(dev, &dev->xpack, &dev->xpack_bytes, need);
   if (rc) return rc;
   __half* xh = reinterpret_cast<__half*>(dev->xpack);
   float* xscale = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(dev->xpack) + xbytes);
-  pack_rows16_kernel<<<mp, 256, 0, dev->stream>>>(x, (int)m, (int)w->k, xh, xscale);
+  pack_rows16_kernel<<<mp / 8, 256, 0, dev->stream>>>(x, (int)m, (int)w->k, bm, xh, xscale);
   FB_LAUNCH_CHECK(dev);
   TcArgs a;
   a.w = w->data; a.xh = xh; a.xscale = xscale; a.y = y; a.r1 = r1; a.r2 = r2;
   a.M = (int)m; a.N = (int)w->n; a.K = (int)w->k;
   a.ngroups = w->ngroups; a.ntiles = w->ntiles; a.type = (int)w->type; a.tgb = geo.tg_bytes;
   a.group_elems = geo.group_elems; a.status = dev->status;
-  static bool configured[64] = {false};
-  if (!configured[dev->ordinal & 63]) {
-    FB_CUDA(dev, cudaFuncSetAttribute(qgemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tc<128>::SMEM));
-    FB_CUDA(dev, cudaFuncSetAttribute(qgemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tc<256>::SMEM));
-    configured[dev->ordinal & 63] = true;
-  }
-  const dim3 grid((unsigned)((w->n + BN - 1) / BN), (unsigned)(mp / bm));
-  if (bm == 256) return fb200_launch(dev, qgemm_tc_kernel<256>, grid, dim3(TC_THREADS), (size_t)Tc<256>::SMEM, false, a);
-  return fb200_launch(dev, qgemm_tc_kernel<128>, grid, dim3(TC_THREADS), (size_t)Tc<128>::SMEM, false, a);
+  a.stages = best_stages; a.raw_stride = raw_stride;
+  a.pair_tiles = swiglu ? w->ntiles / 2 : 0;
+  const int smem = best_stages * (nh * A_HALF + bm * BK * 2) + 2 * 8 * nh * raw_stride + TAIL_BYTES;
+  const size_t rows_per_cta = swiglu ? BN : BN * nh;
+  const unsigned gn = (unsigned)((n_rows + rows_per_cta - 1) / rows_per_cta), gm = (unsigned)(mp / bm);
+  if (nh == 2) return bm == 256 ? launch_tc<256, 2>(dev, a, gn, gm, smem) : launch_tc<128, 2>(dev, a, gn, gm, smem);
+  return bm == 256 ? launch_tc<256, 1>(dev, a, gn, gm, smem) : launch_tc<128, 1>(dev, a, gn, gm, smem);
 }

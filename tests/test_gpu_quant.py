@@ -90,6 +90,35 @@ def test_q_mat_mul_batches(dev, tname, m):
     assert F.rel_l2(y0[0], y[0]) < (1e-6 if m == 1 else TOL)
 
 
+@pytest.mark.parametrize("tname", list(TYPES))
+@pytest.mark.parametrize("tile", ["128,1", "256,1", "128,2", "256,2", ""])
+def test_prefill_product_tensor_cores(dev, tname, tile, monkeypatch):
+    # more than 32 rows: the tcgen05 kernel, every CTA tile shape (activation rows, 128-row weight
+    # halves; "" = the cost model's choice), ragged N and M, plain / residual / SwiGLU epilogues
+    monkeypatch.setenv("FB200_TC_TILE", tile)
+    ty = TYPES[tname]
+    f, k = 528, 1024  # 33 row-tiles per part: the last CTA of every tile shape is ragged
+    g_raw, u_raw = weights(31, f, k, ty), weights(32, f, k, ty)
+    gate = kb.QMatrix.from_raw_bytes(dev, (f, k), g_raw, ty)
+    up = kb.QMatrix.from_raw_bytes(dev, (f, k), u_raw, ty)
+    gu = kb.QMatrix.concat_rows([gate, up])
+    for m in (40, 300):
+        x = activations(70 + m, m, k)
+        eg, eu = O.q_mat_mul(x, g_raw, ty, f, k), O.q_mat_mul(x, u_raw, ty, f, k)
+        both = dev.tensor(x).q_mat_mul(gu).as_slice()
+        assert both.shape == (m, 2 * f)
+        assert F.rel_l2(both, np.concatenate([eg, eu], axis=1)) < TOL
+        h = dev.tensor(x).q_mat_mul(gu, epilogue=kb.EPI_SWIGLU).as_slice()
+        assert h.shape == (m, f) and F.rel_l2(h, O.silu_mul(eg, eu)) < TOL
+        r1, r2 = activations(80 + m, m, f), activations(90 + m, m, f)
+        y = dev.tensor(x).q_mat_mul(gate, epilogue=kb.EPI_RESIDUAL, r1=dev.tensor(r1), r2=dev.tensor(r2)).as_slice()
+        assert F.rel_l2(y, (eg + r1) + r2) < TOL
+        assert dev.status() == 0
+    # repeated launches agree bit for bit (fixed accumulation order in the tensor core)
+    xt = dev.tensor(activations(7, 300, k))
+    assert np.array_equal(xt.q_mat_mul(gu).as_slice(), xt.q_mat_mul(gu).as_slice())
+
+
 @pytest.mark.parametrize("tname,n,k", [("q4_0", 4096, 4096), ("q4k", 4096, 4096), ("q4k", 1024, 4096),
                                         ("q4k", 14336, 4096), ("q4k", 4096, 14336), ("q8_0", 4096, 4096),
                                         ("q6k", 1024, 4096), ("q6k", 4096, 14336)])
