@@ -365,6 +365,18 @@ def run_sweep(args):
                               "gbs": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / peak, "peak": peak,
                               "peak_source": which, "distinct_kv_buffers": copies}), flush=True)
             del ks, vs
+    # prefill attention: causal, Llama-3-8B heads, fp16 cache; causal-effective flops 2 S (S + 1) D Hq
+    tf_peak = tensor_peak()
+    for S in (512, 2048, 8192):
+        rng = np.random.default_rng(S)
+        kt = dev.tensor((rng.standard_normal((1, hkv, S, d)) * 0.5).astype(np.float16))
+        vt = dev.tensor((rng.standard_normal((1, hkv, S, d)) * 0.5).astype(np.float16))
+        q = dev.tensor(rng.standard_normal((1, h, S, d)).astype(np.float32))
+        us = timed(lambda i: dev.flash_attention(q, kt, vt, 1.0 / np.sqrt(d), mask_kind=kb.MASK_CAUSAL), 4)
+        tf = 2.0 * S * (S + 1) * d * h / us / 1e6
+        print(json.dumps({"case": "prefill_attention", "seq": S, "us": us, "tflops": tf, "frac": tf / tf_peak[0],
+                          "peak": tf_peak[0], "peak_source": tf_peak[1], "bound": "tensor"}), flush=True)
+        del kt, vt, q
 
 
 def run_ours(args):

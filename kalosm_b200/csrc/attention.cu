@@ -22,8 +22,13 @@ struct fb200_kv_cache {
   __half* v = nullptr;
 };
 
+int fb200_launch_attention_prefill(fb200_device* dev, const float* q, const __half* k, const __half* v, int b, int h,
+                                   int hkv, int sq, int skv, const int* skv_dev, int cap, int d, float scale,
+                                   int causal, float* out, int bshd);
+
 namespace {
 
+constexpr int PREFILL_MIN_ROWS = 32;  // from here on the tensor-core prefill kernel takes over
 constexpr int ROWS = 8;      // query rows per CTA
 constexpr int CHUNK = 128;   // keys per smem chunk
 constexpr int ATT_THREADS = 256;
@@ -332,6 +337,11 @@ int fb200_launch_attention(fb200_device* dev, const float* q, const __half* k, c
                            float* part, int nsplit, int bshd) {
   if (h % hkv) return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "attention: %d heads not divisible by %d kv heads", h, hkv);
   if (d != 64 && d != 128) return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "attention: head_dim %d (64 or 128 supported)", d);
+  if (sq >= PREFILL_MIN_ROWS && mask_kind <= 1) {
+    // many query positions, no mask or causal: the tensor-core kernel
+    const int rc = fb200_launch_attention_prefill(dev, q, k, v, b, h, hkv, sq, skv, skv_dev, cap, d, scale, mask_kind, out, bshd);
+    if (rc != 1) return rc;
+  }
   AttnArgs a = {};
   a.q = q; a.k = k; a.v = v; a.out = out; a.part = part; a.mask = mask; a.skv_dev = skv_dev;
   a.b = b; a.h = h; a.hkv = hkv; a.sq = sq; a.skv = skv; a.cap = cap; a.groups = h / hkv;

@@ -144,7 +144,35 @@ def test_decode_attention_tile_boundaries(dev, kv, heads):
                                    (1, 32, 8, 4, 300, 128, True), (8, 32, 8, 1, 1024, 128, False)])
 def test_attention_prefill_and_gqa(dev, shape):
     b, h, hkv, sq, skv, d, causal = shape
-    _attn_case(dev, b, h, hkv, sq, skv, d, causal, 7, 1e-3)
+    # 32 query positions and more run on fp16 tensor cores: wider absolute bound, same 2e-3 relative L2
+    _attn_case(dev, b, h, hkv, sq, skv, d, causal, 7, 1e-3 if sq < 32 else 4e-3)
+
+
+@pytest.mark.parametrize("shape", [(1, 32, 8, 512, 512, 128, True), (2, 8, 2, 100, 100, 64, True),
+                                   (1, 8, 8, 96, 300, 128, True), (1, 4, 4, 70, 200, 64, False),
+                                   (1, 32, 8, 33, 1000, 128, True), (1, 4, 1, 64, 64, 128, True),
+                                   (1, 2, 2, 65, 129, 64, True)])
+def test_prefill_attention_tensor_cores(dev, shape):
+    # 32 or more query positions, no mask or causal: the tensor-core kernel (fp16 operands, fp32
+    # accumulation: 2e-3 relative L2 against the f32 oracle). The cache is larger than the valid
+    # length and holds NaN / huge values past it: they must never reach the result.
+    b, h, hkv, sq, skv, d, causal = shape
+    rng = np.random.default_rng(sq + skv)
+    cap = skv + 37
+    q = rng.standard_normal((b, h, sq, d)).astype(np.float32)
+    k = np.full((b, hkv, cap, d), 1.0e4, np.float16)
+    v = np.full((b, hkv, cap, d), np.nan, np.float16)
+    k[:, :, :skv] = rng.standard_normal((b, hkv, skv, d))
+    v[:, :, :skv] = rng.standard_normal((b, hkv, skv, d))
+    scale = float(1.0 / np.sqrt(d))
+    exp = O.attention(q, k[:, :, :skv].astype(np.float32), v[:, :, :skv].astype(np.float32), scale, causal=causal)
+    qt, kt, vt = dev.tensor(q), dev.tensor(k), dev.tensor(v)
+    kind = kb.MASK_CAUSAL if causal else kb.MASK_NONE
+    out = dev.flash_attention(qt, kt, vt, scale, skv=skv, mask_kind=kind).as_slice()
+    assert np.all(np.isfinite(out))
+    assert F.rel_l2(out, exp) < 2e-3, F.rel_l2(out, exp)
+    assert np.max(np.abs(out - exp)) < 4e-3
+    assert np.array_equal(out, dev.flash_attention(qt, kt, vt, scale, skv=skv, mask_kind=kind).as_slice())
 
 
 def test_attention_masks_and_cache_capacity(dev):
