@@ -285,6 +285,51 @@ def run_gemv_only(args):
     print(json.dumps({"roofline": gemv_roofline(kb, dev, torch, stream, max(1, args.gemv_reps))}), flush=True)
 
 
+def run_prefill_only(args):
+    """One prefill-sized case of each tensor-core kernel (a few hundred MB on the device): the small
+    case profiler captures use. Q4_K 14336 x 4096 product at M = 2048, causal attention at S = 2048."""
+    import torch
+    import kalosm_b200 as kb
+    from kalosm_b200 import synth
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    dev = kb.Device(0, stream.cuda_stream)
+    tf_peak = tensor_peak()
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+    n, k, m = 14336, 4096, 2048
+    raw = synth.random_qweights(700, 0.02, n, k, Q4_K, device="cuda").cpu().numpy()
+    w = kb.QMatrix.from_raw_bytes(dev, (n, k), raw, Q4_K)
+    x = dev.tensor(np.random.default_rng(m).standard_normal((m, k)).astype(np.float32))
+    y = dev.empty((m, n))
+    us = timed(lambda: x.q_mat_mul(w, out=y), max(1, args.gemv_reps))
+    tf = 2.0 * m * n * k / us / 1e6
+    print(json.dumps({"case": "q_mat_mul_prefill", "type": "Q4_K", "n": n, "k": k, "m": m, "us": us, "tflops": tf,
+                      "frac": tf / tf_peak[0], "peak": tf_peak[0], "peak_source": tf_peak[1], "bound": "tensor"}), flush=True)
+    h, hkv, d, S = 32, 8, 128, 2048
+    rng = np.random.default_rng(S)
+    kt = dev.tensor((rng.standard_normal((1, hkv, S, d)) * 0.5).astype(np.float16))
+    vt = dev.tensor((rng.standard_normal((1, hkv, S, d)) * 0.5).astype(np.float16))
+    q = dev.tensor(rng.standard_normal((1, h, S, d)).astype(np.float32))
+    o = dev.empty((1, h, S, d))
+    us = timed(lambda: dev.flash_attention(q, kt, vt, 1.0 / np.sqrt(d), mask_kind=kb.MASK_CAUSAL, out=o), max(1, args.gemv_reps))
+    tf = 2.0 * S * (S + 1) * d * h / us / 1e6
+    print(json.dumps({"case": "prefill_attention", "seq": S, "us": us, "tflops": tf, "frac": tf / tf_peak[0],
+                      "peak": tf_peak[0], "peak_source": tf_peak[1], "bound": "tensor"}), flush=True)
+
+
 def run_sweep(args):
     """Per-kernel table of the other configurations of the path, one JSON line each (not the bench
     line): single-row and small-batch quantised products over the Llama-3-8B matrix shapes, and
@@ -359,7 +404,8 @@ def run_sweep(args):
             vs = [dev.tensor((np.random.default_rng(3 * i + 1).standard_normal((b, hkv, L, d)) * 0.5).astype(np.float16))
                   for i in range(copies)]
             q = dev.tensor(np.random.default_rng(9).standard_normal((b, h, 1, d)).astype(np.float32))
-            us = timed(lambda i: dev.flash_attention(q, ks[i % copies], vs[i % copies], 1.0 / np.sqrt(d)), copies)
+            o = dev.empty((b, h, 1, d))
+            us = timed(lambda i: dev.flash_attention(q, ks[i % copies], vs[i % copies], 1.0 / np.sqrt(d), out=o), copies)
             nbytes = kv_bytes + 2 * b * h * d * 4
             print(json.dumps({"case": "decode_attention", "batch": b, "context": L, "us": us, "algorithmic_bytes": nbytes,
                               "gbs": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / peak, "peak": peak,
@@ -372,7 +418,8 @@ def run_sweep(args):
         kt = dev.tensor((rng.standard_normal((1, hkv, S, d)) * 0.5).astype(np.float16))
         vt = dev.tensor((rng.standard_normal((1, hkv, S, d)) * 0.5).astype(np.float16))
         q = dev.tensor(rng.standard_normal((1, h, S, d)).astype(np.float32))
-        us = timed(lambda i: dev.flash_attention(q, kt, vt, 1.0 / np.sqrt(d), mask_kind=kb.MASK_CAUSAL), 4)
+        o = dev.empty((1, h, S, d))
+        us = timed(lambda i: dev.flash_attention(q, kt, vt, 1.0 / np.sqrt(d), mask_kind=kb.MASK_CAUSAL, out=o), 4)
         tf = 2.0 * S * (S + 1) * d * h / us / 1e6
         print(json.dumps({"case": "prefill_attention", "seq": S, "us": us, "tflops": tf, "frac": tf / tf_peak[0],
                           "peak": tf_peak[0], "peak_source": tf_peak[1], "bound": "tensor"}), flush=True)
@@ -522,6 +569,8 @@ def main():
     ap.add_argument("--layers", type=int, default=CFG["n_layer"],
                     help="decoder layers of the model (fewer than 32 only for profiler captures; not a bench value)")
     ap.add_argument("--gemv-only", action="store_true", help="run only the dominant-kernel leg")
+    ap.add_argument("--prefill-only", action="store_true",
+                    help="run one prefill product and one prefill attention (profiling case)")
     ap.add_argument("--gemv-reps", type=int, default=8)
     ap.add_argument("--sweep", action="store_true",
                     help="per-kernel table over the other product shapes and decode attention (several JSON lines)")
@@ -533,6 +582,8 @@ def main():
         run_sweep(args)
     elif args.gemv_only:
         run_gemv_only(args)
+    elif args.prefill_only:
+        run_prefill_only(args)
     else:
         run_ours(args)
 

@@ -284,13 +284,13 @@ class Device:
         return ids, vals
 
     def flash_attention(self, q: Tensor, k: Tensor, v: Tensor, scale: float, skv: int = None,
-                        mask: Tensor = None, mask_kind: int = MASK_NONE) -> Tensor:
+                        mask: Tensor = None, mask_kind: int = MASK_NONE, out: Tensor = None) -> Tensor:
         """Tensor::flash_attention (fusor/src/composite/flash_attention.rs:58-109).
         q f32 [B,H,Sq,D]; k, v fp16 [B,Hkv,cap,D] of which the first `skv` rows are valid."""
         b, h, sq, d = q.shape
         _, hkv, cap, _ = k.shape
         skv = cap if skv is None else skv
-        out = Tensor(self, q.shape)
+        out = Tensor(self, q.shape) if out is None else out
         self._check(self.lib.fb200_flash_attention(self.h, q.ptr, k.ptr, v.ptr, b, h, hkv, sq, skv,
                                                    cap, d, scale, mask.ptr if mask else None,
                                                    mask_kind, out.ptr))

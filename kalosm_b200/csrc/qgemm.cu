@@ -43,9 +43,11 @@ namespace {
 constexpr int BN = 128;  // weight rows per MMA (M of the MMA); a CTA tile holds NH such halves
 // activation rows per CTA tile (N of the MMA): template parameter BM = 128 or 256
 constexpr int BK = 64;   // K elements per operand stage (four K = 16 MMAs)
-constexpr int A_HALF = BN * BK * 2;               // one 128-row half of an A stage
+constexpr int A_SBO = (BK / 8) * 128 + 64;        // A operand: bytes between 8-row groups, padded by half a
+                                                  // core matrix so that rows g and g + 8 fall into different banks
+constexpr int A_HALF = (BN / 8) * A_SBO;          // one 128-row half of an A stage
 constexpr int CORE_LBO = 128;                     // bytes between core matrices adjacent in K
-constexpr int CORE_SBO = (BK / 8) * 128;          // bytes between 8-row groups
+constexpr int CORE_SBO = (BK / 8) * 128;          // B operand: bytes between 8-row groups
 constexpr int MAX_STAGES = 4;
 constexpr int TAIL_BYTES = 256;                   // barriers, TMEM slot, give-up flag
 constexpr int SMEM_BUDGET = 227 * 1024;
@@ -110,9 +112,9 @@ __device__ __forceinline__ uint2 deq4(uint32_t w, __half2 centre, __half2 scale,
 // Shared-memory matrix descriptor of a K-major operand without swizzle: start address, leading
 // (K direction) and stride (row-group direction) byte offsets in 16-byte units, descriptor
 // version 1.
-__device__ __forceinline__ uint64_t operand_desc(uint32_t saddr) {
+__device__ __forceinline__ uint64_t operand_desc(uint32_t saddr, uint32_t sbo) {
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(CORE_LBO >> 4) << 16) |
-         ((uint64_t)(CORE_SBO >> 4) << 32) | (1ull << 46);
+         ((uint64_t)(sbo >> 4) << 32) | (1ull << 46);
 }
 
 __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
@@ -145,15 +147,21 @@ struct RowScales {
 
 __device__ __forceinline__ void store_chunk(uint8_t* abuf, int wrow, int g, int t, int cib, uint2 lo_g, uint2 lo_g8,
                                             uint2 hi_g, uint2 hi_g8) {
-  uint8_t* base = abuf + (2 * wrow) * CORE_SBO + g * 16 + (t & 1) * 8;
-  const int klo = (4 * cib + (t >> 1)) * CORE_LBO, khi = (4 * cib + 2 + (t >> 1)) * CORE_LBO;
-  *reinterpret_cast<uint2*>(base + klo) = lo_g;
-  *reinterpret_cast<uint2*>(base + CORE_SBO + klo) = lo_g8;
-  *reinterpret_cast<uint2*>(base + khi) = hi_g;
-  *reinterpret_cast<uint2*>(base + CORE_SBO + khi) = hi_g8;
+  // In one store instruction the lanes with t < 2 write row g and the others row g + 8 (then the
+  // other way round): with the padded row-group stride the 16 lanes of a half-warp cover all 32
+  // banks once, where "every lane its row g" would put K chunks t / 2 = 0 and 1 on the same banks.
+  const bool odd = (t & 2) != 0;
+  uint8_t* base = abuf + (2 * wrow) * A_SBO + g * 16 + (t & 1) * 8 + (4 * cib + (t >> 1)) * CORE_LBO;
+  uint8_t* p1 = base + (odd ? A_SBO : 0);
+  uint8_t* p2 = base + (odd ? 0 : A_SBO);
+  *reinterpret_cast<uint2*>(p1) = odd ? lo_g8 : lo_g;
+  *reinterpret_cast<uint2*>(p2) = odd ? lo_g : lo_g8;
+  *reinterpret_cast<uint2*>(p1 + 2 * CORE_LBO) = odd ? hi_g8 : hi_g;
+  *reinterpret_cast<uint2*>(p2 + 2 * CORE_LBO) = odd ? hi_g : hi_g8;
 }
 
-__device__ __forceinline__ void prepare_scales(int type, const uint8_t* tg, int g, int t, RowScales& S) {
+template <int type>
+__device__ __forceinline__ void prepare_scales(const uint8_t* tg, int g, int t, RowScales& S) {
   if (type == FB200_Q4_K) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -178,7 +186,8 @@ __device__ __forceinline__ void prepare_scales(int type, const uint8_t* tg, int 
 }
 
 // chunk c of the tile-group (32 elements: c < 4 for Q4_0 / Q8_0, c < 8 for the K-quants)
-__device__ __forceinline__ void dequant_chunk(int type, const uint8_t* tg, int c, int lane, const RowScales& S,
+template <int type>
+__device__ __forceinline__ void dequant_chunk(const uint8_t* tg, int c, int lane, const RowScales& S,
                                               uint8_t* abuf, int wrow, int cib) {
   const int g = lane >> 2, t = lane & 3;
   const __half2 zero2 = __float2half2_rn(0.f);
@@ -237,7 +246,7 @@ __device__ __forceinline__ void dequant_chunk(int type, const uint8_t* tg, int c
   }
 }
 
-template <int BM, int NH>
+template <int BM, int NH, int TYPE>
 __global__ void __launch_bounds__(Tc<BM, NH>::THREADS, 1)
 qgemm_tc_kernel(const TcArgs a) {
   using T = Tc<BM, NH>;
@@ -281,7 +290,7 @@ qgemm_tc_kernel(const TcArgs a) {
   // row-tile converted by warp i, and whether the matrix has it
   auto tile_of = [&](int i) { return a.pair_tiles ? tile0 + (i & 7) + (i >> 3) * a.pair_tiles : tile0 + i; };
   auto has_tile = [&](int i) { return a.pair_tiles ? tile0 + (i & 7) < a.pair_tiles : tile0 + i < a.ntiles; };
-  const int blocks_per_group = a.group_elems / BK;  // 4 (K-quants) or 2
+  constexpr int blocks_per_group = (TYPE == FB200_Q4_K || TYPE == FB200_Q6_K ? 256 : 128) / BK;
   const int nblocks = a.ngroups * blocks_per_group;
 
   if (warp < T::DQ_WARPS) {
@@ -296,15 +305,16 @@ qgemm_tc_kernel(const TcArgs a) {
       if (!alive) break;
       const uint8_t* tg = raw + rb * raw_bytes + warp * a.raw_stride;
       RowScales S;
-      if (mine) prepare_scales(a.type, tg, lane >> 2, lane & 3, S);
+      if (mine) prepare_scales<TYPE>(tg, lane >> 2, lane & 3, S);
+#pragma unroll
       for (int b = 0; b < blocks_per_group; ++b) {
         // the stage is free once the MMAs of its previous use have read it
         if (round > 0) alive = tc_wait(bar_free + 8 * s, (uint32_t)((round - 1) & 1), dead, a.status);
         if (!alive) break;
         uint8_t* abuf = a_rows + s * T::STAGE;
         if (mine) {
-          dequant_chunk(a.type, tg, 2 * b, lane, S, abuf, warp & 7, 0);
-          dequant_chunk(a.type, tg, 2 * b + 1, lane, S, abuf, warp & 7, 1);
+          dequant_chunk<TYPE>(tg, 2 * b, lane, S, abuf, warp & 7, 0);
+          dequant_chunk<TYPE>(tg, 2 * b + 1, lane, S, abuf, warp & 7, 1);
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
         __syncwarp();
@@ -357,8 +367,8 @@ qgemm_tc_kernel(const TcArgs a) {
         for (int h = 0; h < NH; ++h)
 #pragma unroll
           for (int ks = 0; ks < BK / 16; ++ks)
-            tc_mma(tmem_d + (uint32_t)(h * BM), operand_desc(sa + h * A_HALF + ks * 2 * CORE_LBO),
-                   operand_desc(sb + ks * 2 * CORE_LBO), T::IDESC, (blk | ks) ? 1u : 0u);
+            tc_mma(tmem_d + (uint32_t)(h * BM), operand_desc(sa + h * A_HALF + ks * 2 * CORE_LBO, A_SBO),
+                   operand_desc(sb + ks * 2 * CORE_LBO, CORE_SBO), T::IDESC, (blk | ks) ? 1u : 0u);
         tc_commit(bar_free + 8 * s);
         if (++s == a.stages) { s = 0; ++round; }
       }
@@ -472,15 +482,26 @@ pack_rows16_kernel(const float* __restrict__ x, int M, int K, int bm, __half* __
   }
 }
 
-template <int BM, int NH>
-int launch_tc(fb200_device* dev, const TcArgs& a, unsigned grid_n, unsigned grid_m, int smem) {
+template <int BM, int NH, int TYPE>
+int launch_tc_type(fb200_device* dev, const TcArgs& a, unsigned grid_n, unsigned grid_m, int smem) {
   using T = Tc<BM, NH>;
   static bool configured[64] = {false};
   if (!configured[dev->ordinal & 63]) {
-    FB_CUDA(dev, cudaFuncSetAttribute(qgemm_tc_kernel<BM, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET));
+    FB_CUDA(dev, cudaFuncSetAttribute(qgemm_tc_kernel<BM, NH, TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET));
     configured[dev->ordinal & 63] = true;
   }
-  return fb200_launch(dev, qgemm_tc_kernel<BM, NH>, dim3(grid_n, grid_m), dim3(T::THREADS), (size_t)smem, false, a);
+  return fb200_launch(dev, qgemm_tc_kernel<BM, NH, TYPE>, dim3(grid_n, grid_m), dim3(T::THREADS), (size_t)smem, false, a);
+}
+
+template <int BM, int NH>
+int launch_tc(fb200_device* dev, const TcArgs& a, unsigned grid_n, unsigned grid_m, int smem) {
+  switch (a.type) {
+    case FB200_Q4_0: return launch_tc_type<BM, NH, FB200_Q4_0>(dev, a, grid_n, grid_m, smem);
+    case FB200_Q8_0: return launch_tc_type<BM, NH, FB200_Q8_0>(dev, a, grid_n, grid_m, smem);
+    case FB200_Q4_K: return launch_tc_type<BM, NH, FB200_Q4_K>(dev, a, grid_n, grid_m, smem);
+    case FB200_Q6_K: return launch_tc_type<BM, NH, FB200_Q6_K>(dev, a, grid_n, grid_m, smem);
+  }
+  return 1;
 }
 
 }  // namespace
