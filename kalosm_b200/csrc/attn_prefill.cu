@@ -21,6 +21,7 @@
 namespace {
 
 constexpr int PF_BQ = 64, PF_BKV = 64, PF_THREADS = 128;
+static_assert(PF_BQ == PF_BKV, "the Q tile borrows the K half of the second buffer");
 
 struct PrefillArgs {
   const float* q;      // [B, H, Sq, D] or [B, Sq, H, D]
@@ -47,7 +48,7 @@ __device__ __forceinline__ void pf_ldsm4_t(uint32_t addr, uint32_t (&r)[4]) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 __device__ __forceinline__ void pf_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -63,13 +64,14 @@ __device__ __forceinline__ uint32_t pf_pack(float lo, float hi) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(PF_THREADS)
+__global__ void __launch_bounds__(PF_THREADS, 3)
 attn_prefill_kernel(const PrefillArgs a) {
   constexpr int CH = D / 8;                    // 16-byte chunks per row
   constexpr int TILE = PF_BKV * D * 2;         // bytes of one K or V tile
   extern __shared__ __align__(128) uint8_t sm[];
-  uint8_t* Qs = sm;                            // [64][D] fp16
-  uint8_t* KV = sm + PF_BQ * D * 2;            // [2 buffers][K | V]
+  uint8_t* KV = sm;                            // [2 buffers][K | V]
+  uint8_t* Qs = sm + 2 * TILE;                 // [64][D] fp16, in the K half of buffer 1: only needed
+                                               // until the Q fragments sit in registers
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int qt = gridDim.x - 1 - blockIdx.x;   // longest key ranges first
   const int head = blockIdx.y, bi = blockIdx.z, kvh = head / a.groups;
@@ -114,6 +116,7 @@ attn_prefill_kernel(const PrefillArgs a) {
     for (int ks = 0; ks < D / 16; ++ks)
       pf_ldsm4(pf_smem(Qs) + pf_off<D>(warp * 16 + (j & 1) * 8 + r, 2 * ks + (j >> 1)), qf[ks]);
   }
+  __syncthreads();  // buffer 1 may now be overwritten by the second K/V tile
 
   float o[D / 8][4];
 #pragma unroll
@@ -135,10 +138,12 @@ attn_prefill_kernel(const PrefillArgs a) {
     // ---- S = Q K^T: 8 column tiles of 8 keys
     float s[PF_BKV / 8][4];
 #pragma unroll
-    for (int nt = 0; nt < PF_BKV / 8; ++nt) {
-      s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+    for (int nt = 0; nt < PF_BKV / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+    // K steps outermost: consecutive MMAs go to different accumulators
 #pragma unroll
-      for (int k2 = 0; k2 < D / 32; ++k2) {
+    for (int k2 = 0; k2 < D / 32; ++k2) {
+#pragma unroll
+      for (int nt = 0; nt < PF_BKV / 8; ++nt) {
         uint32_t b[4];  // keys nt*8.., K elements 32 k2 .. +31 as (b0, b1) of two k-steps
         pf_ldsm4(ks_base + pf_off<D>(nt * 8 + (lane & 7), 4 * k2 + (lane >> 3)), b);
         pf_mma(s[nt], qf[2 * k2], b[0], b[1]);
@@ -154,7 +159,7 @@ attn_prefill_kernel(const PrefillArgs a) {
     for (int nt = 0; nt < PF_BKV / 8; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        float x = s[nt][e] * a.scale_log2;
+        float x = s[nt][e];  // raw score: the (positive) scale is folded into the exponent below
         if (need_mask) {
           const int col = kt + nt * 8 + 2 * t + (e & 1), row = row_lo + (e >> 1) * 8;
           if (col >= skv || (a.causal && col > row + off)) x = -INFINITY;
@@ -167,7 +172,7 @@ attn_prefill_kernel(const PrefillArgs a) {
     for (int hrow = 0; hrow < 2; ++hrow) {
       mx[hrow] = fmaxf(mx[hrow], __shfl_xor_sync(0xFFFFFFFFu, mx[hrow], 1));
       mx[hrow] = fmaxf(mx[hrow], __shfl_xor_sync(0xFFFFFFFFu, mx[hrow], 2));
-      const float mnew = fmaxf(m_run[hrow], mx[hrow]);
+      const float mnew = fmaxf(m_run[hrow], mx[hrow] * a.scale_log2);
       msafe[hrow] = mnew == -INFINITY ? 0.f : mnew;  // a row that has seen no key yet
       alpha[hrow] = exp2f(m_run[hrow] - msafe[hrow]);
       m_run[hrow] = mnew;
@@ -177,16 +182,19 @@ attn_prefill_kernel(const PrefillArgs a) {
     for (int nt = 0; nt < PF_BKV / 8; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float p = exp2f(s[nt][e] - msafe[e >> 1]);
+        const float p = exp2f(fmaf(s[nt][e], a.scale_log2, -msafe[e >> 1]));
         s[nt][e] = p;
         psum[e >> 1] += p;
       }
     l_run[0] = l_run[0] * alpha[0] + psum[0];
     l_run[1] = l_run[1] * alpha[1] + psum[1];
+    // the running maximum settles after the first tiles: skip the rescale when no row of the warp moved
+    if (__any_sync(0xFFFFFFFFu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
-      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+      for (int i = 0; i < D / 8; ++i) {
+        o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+        o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+      }
     }
 
     // ---- O += P V: P (fp16) as the A operand, V through transposing ldmatrix
@@ -234,17 +242,17 @@ attn_prefill_kernel(const PrefillArgs a) {
 int fb200_launch_attention_prefill(fb200_device* dev, const float* q, const __half* k, const __half* v, int b, int h,
                                    int hkv, int sq, int skv, const int* skv_dev, int cap, int d, float scale,
                                    int causal, float* out, int bshd) {
-  if ((d != 64 && d != 128) || h % hkv || b > 65535 || h > 65535) return 1;
+  if ((d != 64 && d != 128) || h % hkv || b > 65535 || h > 65535 || !(scale > 0.f)) return 1;
   PrefillArgs a = {};
   a.q = q; a.k = k; a.v = v; a.out = out; a.skv_dev = skv_dev;
   a.b = b; a.h = h; a.hkv = hkv; a.sq = sq; a.skv = skv; a.cap = cap; a.groups = h / hkv; a.bshd = bshd;
   a.causal = causal; a.scale_log2 = scale * 1.4426950408889634f;
   const dim3 grid((unsigned)((sq + PF_BQ - 1) / PF_BQ), (unsigned)h, (unsigned)b);
-  const size_t smem = (size_t)(PF_BQ + 4 * PF_BKV) * d * 2;
+  const size_t smem = (size_t)(4 * PF_BKV) * d * 2;
   static bool configured[64] = {false};
   if (!configured[dev->ordinal & 63]) {
-    FB_CUDA(dev, cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (PF_BQ + 4 * PF_BKV) * 128 * 2));
-    FB_CUDA(dev, cudaFuncSetAttribute(attn_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (PF_BQ + 4 * PF_BKV) * 64 * 2));
+    FB_CUDA(dev, cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * PF_BKV * 128 * 2));
+    FB_CUDA(dev, cudaFuncSetAttribute(attn_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * PF_BKV * 64 * 2));
     configured[dev->ordinal & 63] = true;
   }
   if (d == 128) return fb200_launch(dev, attn_prefill_kernel<128>, grid, dim3(PF_THREADS), smem, false, a);
