@@ -42,7 +42,8 @@ typedef enum fb200_status {
   FB200_ERR_CUDA = -4,
   FB200_ERR_INVALID_ARGUMENT = -5,
   FB200_ERR_TIMEOUT = -6,
-  FB200_ERR_DEVICE_MISMATCH = -7
+  FB200_ERR_DEVICE_MISMATCH = -7,
+  FB200_ERR_NCCL = -8
 } fb200_status;
 
 /* ggml type ids, fusor-ml/gguf/src/lib.rs:35-50 */
@@ -248,8 +249,32 @@ FB200_API int fb200_llama_forward(fb200_llama* m, const uint32_t* tokens_host, i
  * generated ids. Only the ids cross PCIe. */
 FB200_API int fb200_llama_generate_greedy(fb200_llama* m, const uint32_t* tokens_host, int batch,
                                 int steps, uint32_t* out_host);
-/* Device pointer of the last forward pass's logits, f32 [batch, vocab]. */
+/* Device pointer of the last forward pass's logits, f32 [batch, vocab] (tensor parallel:
+ * [batch, vocab / size], this rank's rows of the output head). */
 FB200_API int fb200_llama_logits_dev(const fb200_llama* m, const float** logits_dev);
+
+/* ---- tensor parallelism (no counterpart in the reference, which runs one device) ------------
+ * One process and one device handle per GPU. Rank 0 makes an id (FB200_COMM_ID_BYTES bytes) and
+ * hands it to the other ranks by any host channel; every rank then calls fb200_comm_create, which
+ * blocks until all `size` ranks have joined (NCCL, loaded at run time: FB200_ERR_NCCL if absent).
+ * A tensor-parallel model is created from the LOCAL configuration (n_head, n_kv_head and ffn
+ * divided by size; hidden and vocab whole), attached to the communicator before any tensor is
+ * set, and given this rank's shards: attn_q / attn_k / attn_v / ffn_gate / ffn_up rows
+ * [rank * N / size, (rank + 1) * N / size), attn_output / ffn_down the matching K columns (whole
+ * quantisation blocks), output rows [rank * vocab / size, ...); token_embd and the norms whole.
+ * The partial sums of attn_output and ffn_down are added over the ranks (two all-reduces per
+ * layer) and the greedy token is the best (value, id) pair over the ranks' shards of the output
+ * head, so every rank returns the same ids. */
+#define FB200_COMM_ID_BYTES 128
+typedef struct fb200_comm fb200_comm;
+FB200_API int fb200_comm_unique_id(uint8_t* id_out, size_t id_bytes);
+FB200_API int fb200_comm_create(fb200_device* dev, int size, int rank, const uint8_t* id, size_t id_bytes,
+                                fb200_comm** out);
+FB200_API int fb200_comm_destroy(fb200_comm* c);
+/* In-place sum of buf_dev[n] (f32) over the ranks, asynchronous on the device handle's stream. */
+FB200_API int fb200_comm_all_reduce_sum(fb200_comm* c, float* buf_dev, size_t n);
+/* Must precede fb200_llama_set_tensor. The communicator must outlive the model. */
+FB200_API int fb200_llama_set_tensor_parallel(fb200_llama* m, fb200_comm* comm);
 
 #ifdef __cplusplus
 }

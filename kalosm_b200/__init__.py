@@ -25,7 +25,8 @@ BLOCK = {F32: (1, 4), F16: (1, 2), Q4_0: (32, 18), Q5_0: (32, 22), Q8_0: (32, 34
 
 OK = 0
 ERR_INVALID_SHAPE, ERR_UNSUPPORTED_DTYPE, ERR_CAPACITY, ERR_CUDA = -1, -2, -3, -4
-ERR_INVALID_ARGUMENT, ERR_TIMEOUT, ERR_DEVICE_MISMATCH = -5, -6, -7
+ERR_INVALID_ARGUMENT, ERR_TIMEOUT, ERR_DEVICE_MISMATCH, ERR_NCCL = -5, -6, -7, -8
+COMM_ID_BYTES = 128
 EPI_NONE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
 MASK_NONE, MASK_CAUSAL, MASK_QK, MASK_BATCH_KEY = 0, 1, 2, 3
 
@@ -63,7 +64,8 @@ EXPORTS = [
     "fb200_kv_cache_free", "fb200_kv_cache_reset", "fb200_kv_cache_len", "fb200_kv_cache_append",
     "fb200_kv_cache_buffers", "fb200_flash_attention", "fb200_llama_create", "fb200_llama_free",
     "fb200_llama_set_tensor", "fb200_llama_reset", "fb200_llama_position", "fb200_llama_forward",
-    "fb200_llama_generate_greedy", "fb200_llama_logits_dev",
+    "fb200_llama_generate_greedy", "fb200_llama_logits_dev", "fb200_llama_set_tensor_parallel",
+    "fb200_comm_unique_id", "fb200_comm_create", "fb200_comm_destroy", "fb200_comm_all_reduce_sum",
 ]
 
 _lib = None
@@ -125,6 +127,11 @@ def load_library():
         "fb200_llama_forward": (i32, [vp, vp, i32, i32, vp, vp]),
         "fb200_llama_generate_greedy": (i32, [vp, vp, i32, i32, vp]),
         "fb200_llama_logits_dev": (i32, [vp, pp]),
+        "fb200_llama_set_tensor_parallel": (i32, [vp, vp]),
+        "fb200_comm_unique_id": (i32, [vp, sz]),
+        "fb200_comm_create": (i32, [vp, i32, i32, vp, sz, pp]),
+        "fb200_comm_destroy": (i32, [vp]),
+        "fb200_comm_all_reduce_sum": (i32, [vp, vp, sz]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -443,23 +450,66 @@ class KvCache:
             pass
 
 
+class Comm:
+    """Tensor-parallel communicator: one rank per process and GPU (NCCL). `unique_id()` on rank 0,
+    the id travels to the other ranks by any host channel (e.g. a torch.distributed broadcast),
+    then every rank constructs its Comm; the constructor returns when all ranks have joined."""
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = (C.c_uint8 * COMM_ID_BYTES)()
+        rc = load_library().fb200_comm_unique_id(buf, COMM_ID_BYTES)
+        if rc:
+            raise FusorError(rc, "NCCL is not available (libnccl.so.2)")
+        return bytes(buf)
+
+    def __init__(self, device: Device, size: int, rank: int, unique_id: bytes):
+        self.device, self.size, self.rank = device, size, rank
+        buf = (C.c_uint8 * COMM_ID_BYTES).from_buffer_copy(unique_id)
+        out = C.c_void_p()
+        device._check(device.lib.fb200_comm_create(device.h, size, rank, buf, COMM_ID_BYTES, C.byref(out)))
+        self.h = out.value
+
+    def all_reduce_sum(self, t: Tensor) -> Tensor:
+        """In-place sum of an f32 tensor over the ranks."""
+        self.device._check(self.device.lib.fb200_comm_all_reduce_sum(self.h, t.ptr, int(np.prod(t.shape))))
+        return t
+
+    def destroy(self) -> None:
+        if self.h:
+            self.device.lib.fb200_comm_destroy(self.h)
+            self.h = None
+
+
 class Llama:
-    """Llama-architecture decoder (kalosm-llama Model::forward, raw/mod.rs:851-1049)."""
+    """Llama-architecture decoder (kalosm-llama Model::forward, raw/mod.rs:851-1049).
+
+    With `comm` the model is one rank of a tensor-parallel group: pass the WHOLE model's head and
+    FFN sizes; the local counts (divided by comm.size) go to the library, and `set_tensor` expects
+    this rank's shards (see `kalosm_b200.tp`)."""
 
     TENSORS = {"token_embd": 0, "output": 1, "attn_q": 2, "attn_k": 3, "attn_v": 4,
                "attn_output": 5, "ffn_gate": 6, "ffn_up": 7, "ffn_down": 8, "attn_norm": 9,
                "ffn_norm": 10, "output_norm": 11}
 
     def __init__(self, device: Device, *, n_layer, hidden, ffn, n_head, n_kv_head, head_dim, vocab,
-                 max_seq_len, max_batch=1, rms_eps=1e-5, rope_theta=500000.0, rope_scaling=None):
+                 max_seq_len, max_batch=1, rms_eps=1e-5, rope_theta=500000.0, rope_scaling=None, comm=None):
         self.device = device
+        self.comm = comm
+        tp = comm.size if comm is not None else 1
+        if n_head % tp or n_kv_head % tp or ffn % tp or vocab % tp:
+            raise FusorError(ERR_INVALID_SHAPE, f"heads {n_head}/{n_kv_head}, ffn {ffn} and vocab {vocab} must be "
+                                                f"divisible by the {tp} tensor-parallel ranks")
+        n_head, n_kv_head, ffn = n_head // tp, n_kv_head // tp, ffn // tp
         factor, low, high, orig = (0.0, 1.0, 4.0, max_seq_len) if rope_scaling is None else rope_scaling
         self.cfg = LlamaConfig(n_layer, hidden, ffn, n_head, n_kv_head, head_dim, vocab, max_seq_len,
                                max_batch, rms_eps, rope_theta, factor, low, high, orig)
         out = C.c_void_p()
         device._check(device.lib.fb200_llama_create(device.h, C.byref(self.cfg), C.byref(out)))
         self.h = out.value
-        self.vocab = vocab
+        self.vocab = vocab // tp  # rows of the output head on this rank = width of the logits it returns
+        if comm is not None:
+            device._check(device.lib.fb200_llama_set_tensor_parallel(self.h, comm.h))
 
     def set_tensor(self, name: str, layer: int, ggml_type: int, shape, raw) -> None:
         raw = np.ascontiguousarray(raw)

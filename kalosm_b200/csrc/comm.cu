@@ -1,0 +1,120 @@
+// Tensor-parallel communicator: one rank per GPU, NCCL over NVLink for the two all-reduces per
+// layer and the greedy-token exchange of the sharded output head.
+//
+// The reference has no multi-GPU path; the partition follows the usual split of a transformer
+// layer: q/k/v/gate/up by rows, o/down by K, one sum per pair (see tp_all_reduce in llama.cu).
+// NCCL is loaded at run time (dlopen of libnccl.so.2) so that single-GPU users of the library
+// do not need it; every entry point fails with FB200_ERR_NCCL when it is missing.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstring>
+
+#include "common.cuh"
+
+struct fb200_comm {
+  fb200_device* dev = nullptr;
+  ncclComm_t nccl = nullptr;
+  int rank = 0, size = 1;
+};
+
+namespace {
+
+struct NcclApi {
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  const char* (*GetErrorString)(ncclResult_t) = nullptr;
+  bool ok = false;
+};
+
+const NcclApi& nccl_api() {
+  static NcclApi api = [] {
+    NcclApi a;
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return a;
+    a.GetUniqueId = reinterpret_cast<decltype(a.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
+    a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
+    a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
+    a.AllReduce = reinterpret_cast<decltype(a.AllReduce)>(dlsym(h, "ncclAllReduce"));
+    a.AllGather = reinterpret_cast<decltype(a.AllGather)>(dlsym(h, "ncclAllGather"));
+    a.GetErrorString = reinterpret_cast<decltype(a.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
+    a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllReduce && a.AllGather && a.GetErrorString;
+    return a;
+  }();
+  return api;
+}
+
+int nccl_fail(fb200_device* dev, const char* what, ncclResult_t r) {
+  return fb200_fail(dev, FB200_ERR_NCCL, "%s: %s", what, nccl_api().GetErrorString(r));
+}
+
+}  // namespace
+
+// In-place sum over the ranks of buf[n] (f32), on the device handle's stream.
+int fb200_comm_all_reduce(fb200_comm* c, float* buf, size_t n) {
+  if (c->size == 1 || n == 0) return FB200_OK;
+  ncclResult_t r = nccl_api().AllReduce(buf, buf, n, ncclFloat, ncclSum, c->nccl, c->dev->stream);
+  if (r != ncclSuccess) return nccl_fail(c->dev, "all_reduce", r);
+  return FB200_OK;
+}
+
+// out[size][bytes] = every rank's in[bytes].
+int fb200_comm_all_gather_bytes(fb200_comm* c, const void* in, void* out, size_t bytes) {
+  ncclResult_t r = nccl_api().AllGather(in, out, bytes, ncclChar, c->nccl, c->dev->stream);
+  if (r != ncclSuccess) return nccl_fail(c->dev, "all_gather", r);
+  return FB200_OK;
+}
+
+int fb200_comm_rank(const fb200_comm* c) { return c->rank; }
+int fb200_comm_size(const fb200_comm* c) { return c->size; }
+fb200_device* fb200_comm_device(const fb200_comm* c) { return c->dev; }
+
+extern "C" {
+
+int fb200_comm_unique_id(uint8_t* id_out, size_t id_bytes) {
+  if (!id_out || id_bytes < sizeof(ncclUniqueId)) return FB200_ERR_INVALID_ARGUMENT;
+  if (!nccl_api().ok) return FB200_ERR_NCCL;
+  ncclUniqueId id;
+  if (nccl_api().GetUniqueId(&id) != ncclSuccess) return FB200_ERR_NCCL;
+  memset(id_out, 0, id_bytes);
+  memcpy(id_out, &id, sizeof(id));
+  return FB200_OK;
+}
+
+int fb200_comm_create(fb200_device* dev, int size, int rank, const uint8_t* id, size_t id_bytes, fb200_comm** out) {
+  if (!dev || !out) return FB200_ERR_INVALID_ARGUMENT;
+  *out = nullptr;
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  if (size < 1 || rank < 0 || rank >= size || !id || id_bytes < sizeof(ncclUniqueId))
+    return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "comm: rank %d of %d", rank, size);
+  if (!nccl_api().ok) return fb200_fail(dev, FB200_ERR_NCCL, "comm: libnccl.so.2 could not be loaded");
+  ncclUniqueId uid;
+  memcpy(&uid, id, sizeof(uid));
+  fb200_comm* c = new fb200_comm();
+  c->dev = dev; c->rank = rank; c->size = size;
+  ncclResult_t r = nccl_api().CommInitRank(&c->nccl, size, uid, rank);
+  if (r != ncclSuccess) { delete c; return nccl_fail(dev, "comm init", r); }
+  *out = c;
+  return FB200_OK;
+}
+
+int fb200_comm_destroy(fb200_comm* c) {
+  if (!c) return FB200_OK;
+  if (c->nccl) nccl_api().CommDestroy(c->nccl);
+  delete c;
+  return FB200_OK;
+}
+
+int fb200_comm_all_reduce_sum(fb200_comm* c, float* buf_dev, size_t n) {
+  if (!c || !buf_dev) return FB200_ERR_INVALID_ARGUMENT;
+  int rc = fb200_bind(c->dev);
+  if (rc) return rc;
+  return fb200_comm_all_reduce(c, buf_dev, n);
+}
+
+}  // extern "C"

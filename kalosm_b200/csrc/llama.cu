@@ -32,6 +32,12 @@ int fb200_attention_nsplit(const fb200_device* dev, int b, int hkv, int groups, 
 int fb200_launch_attention_decode_args(fb200_device* dev, const fb200_dec_args& a, int d);
 bool fb200_qgemv1_fits(const fb200_qmatrix* w);
 int fb200_attention_scratch_bytes(int b, int h, int sq, int d, int nsplit, size_t* out);
+struct fb200_comm;
+int fb200_comm_all_reduce(fb200_comm* c, float* buf, size_t n);
+int fb200_comm_all_gather_bytes(fb200_comm* c, const void* in, void* out, size_t bytes);
+int fb200_comm_rank(const fb200_comm* c);
+int fb200_comm_size(const fb200_comm* c);
+fb200_device* fb200_comm_device(const fb200_comm* c);
 
 namespace {
 
@@ -147,6 +153,11 @@ struct fb200_llama {
   bool fused_usable = false;
   std::vector<fb200_fused_phase> prog_host;
   fb200_fused_phase* prog_dev = nullptr;
+  // tensor parallelism: cfg holds the local head / ffn counts; the output head has vocab_local rows
+  fb200_comm* comm = nullptr;
+  int tp_rank = 0, tp_size = 1, vocab_local = 0;
+  float* best_val = nullptr;            // [max_batch] value of the local greedy candidate
+  unsigned long long* best_pair = nullptr;  // [(1 + size) * max_batch] (value, global id) pairs
 };
 
 namespace {
@@ -186,6 +197,8 @@ int finalize(fb200_llama* m) {
   const auto& c = m->cfg;
   if (!m->token_embd || !m->output_norm)
     return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "llama: token_embd / output_norm not set");
+  if (m->tp_size > 1 && !m->output)
+    return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "llama: a tensor-parallel model needs its shard of the output head");
   for (int i = 0; i < c.n_layer; ++i) {
     LayerW& L = m->layers[i];
     if (!L.wq || !L.wk || !L.wv || !L.wo || !L.gate || !L.up || !L.down || !L.attn_norm || !L.ffn_norm)
@@ -238,7 +251,7 @@ int build_fused_program(fb200_llama* m) {
   const auto& c = m->cfg;
   m->fused_usable = false;
   m->fused_valid = true;
-  if (!m->fused_enabled || !decode1_supported(m)) return FB200_OK;
+  if (!m->fused_enabled || m->tp_size > 1 || !decode1_supported(m)) return FB200_OK;
   const int grid = fb200_fused_grid(dev);
   const int H = c.n_head, HK = c.n_kv_head, D = c.head_dim;
   std::vector<fb200_fused_phase> prog;
@@ -363,6 +376,39 @@ int run_fused(fb200_llama* m, int steps, bool record) {
 
 // One forward pass over `seq` new positions per batch row; ids are already in m->ids.
 // Leaves logits [batch, vocab] in m->logits and the greedy ids in m->next.
+// x = (down + attn) + x, the order of attention_layer.rs:170-172 / raw/mod.rs:1036
+__global__ void add_residuals_kernel(const float* __restrict__ down, const float* __restrict__ attn,
+                                     float* __restrict__ x, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] = (down[i] + attn[i]) + x[i];
+}
+
+// Greedy candidates of the sharded output head as sortable 64-bit keys: the f32 value mapped to
+// an order-preserving unsigned integer in the high half, the global token id in the low half, so
+// that the largest key is the highest value and, among equals, the higher id. A shard without a
+// finite logit gives key 0.
+__global__ void pack_candidates_kernel(const float* __restrict__ val, const uint32_t* __restrict__ id, int batch,
+                                       uint32_t id_base, unsigned long long* __restrict__ out) {
+  const int b = threadIdx.x;
+  if (b >= batch) return;
+  unsigned long long key = 0;
+  if (id[b] != 0xFFFFFFFFu) {
+    const uint32_t u = __float_as_uint(val[b]);
+    const uint32_t ordered = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    key = ((unsigned long long)ordered << 32) | (id[b] + id_base);
+  }
+  out[b] = key;
+}
+
+__global__ void pick_candidate_kernel(const unsigned long long* __restrict__ all, int batch, int stride, int ranks,
+                                      uint32_t* __restrict__ next) {
+  const int b = threadIdx.x;
+  if (b >= batch) return;
+  unsigned long long best = 0;
+  for (int r = 0; r < ranks; ++r) best = max(best, all[(size_t)r * stride + b]);
+  next[b] = best ? (uint32_t)(best & 0xFFFFFFFFu) : 0xFFFFFFFFu;
+}
+
 int run_forward(fb200_llama* m, int batch, int seq) {
   m->used_key = false;
   fb200_device* dev = m->dev;
@@ -415,6 +461,8 @@ int run_forward(fb200_llama* m, int batch, int seq) {
                                        m->att_part, nsplit, 1))) return rc;
     }
     if ((rc = fb200_q_mat_mul(dev, m->att, rows, L.wo, m->attn_out, nullptr))) return rc;
+    // tensor parallel: this rank's heads gave a partial sum over K of the output projection
+    if (m->tp_size > 1 && (rc = fb200_comm_all_reduce(m->comm, m->attn_out, rows * (size_t)E))) return rc;
     // ffn_norm.forward_residual_f32(attn, residual) (raw/mod.rs:1017)
     if (rows == 1 && L.gate_up) {
       fb200_epilogue ep{FB200_EPI_SWIGLU, nullptr, nullptr};
@@ -431,8 +479,17 @@ int run_forward(fb200_llama* m, int batch, int seq) {
     }
     // (down(h) + attn) + residual, written over the residual stream
     // (attention_layer.rs:170-172 for one position, raw/mod.rs:1036 otherwise)
-    fb200_epilogue ep{FB200_EPI_RESIDUAL, m->attn_out, m->x};
-    if ((rc = fb200_q_mat_mul(dev, m->hbuf, rows, L.down, m->x, &ep))) return rc;
+    if (m->tp_size > 1) {
+      // partial sum over this rank's slice of the FFN width, summed over the ranks, then the residuals
+      if ((rc = fb200_q_mat_mul(dev, m->hbuf, rows, L.down, m->xn, nullptr))) return rc;
+      if ((rc = fb200_comm_all_reduce(m->comm, m->xn, rows * (size_t)E))) return rc;
+      const size_t total = rows * (size_t)E;
+      add_residuals_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(m->xn, m->attn_out, m->x, total);
+      FB_LAUNCH_CHECK(dev);
+    } else {
+      fb200_epilogue ep{FB200_EPI_RESIDUAL, m->attn_out, m->x};
+      if ((rc = fb200_q_mat_mul(dev, m->hbuf, rows, L.down, m->x, &ep))) return rc;
+    }
   }
   // final norm on the last position of every batch row, then the output projection
   fb200_qmatrix* ow = m->output ? m->output : m->token_embd;
@@ -444,7 +501,20 @@ int run_forward(fb200_llama* m, int batch, int seq) {
                                             m->output_norm, c.rms_eps, batch, E, m->last))) return rc;
     if ((rc = fb200_q_mat_mul(dev, m->last, batch, ow, m->logits, nullptr))) return rc;
   }
-  if ((rc = fb200_launch_argmax(dev, m->logits, batch, c.vocab, m->next, nullptr))) return rc;
+  if (m->tp_size == 1) return fb200_launch_argmax(dev, m->logits, batch, c.vocab, m->next, nullptr);
+  // sharded output head: the best (value, global id) pair of every rank, gathered; every rank then
+  // picks the same winner (highest value, ties -> higher id, as Tensor::top_k_pairs does)
+  if ((rc = fb200_launch_argmax(dev, m->logits, batch, m->vocab_local, m->next, m->best_val))) return rc;
+  unsigned long long* mine = m->best_pair;
+  unsigned long long* all = m->best_pair + c.max_batch;
+  const unsigned threads = batch < 64 ? 64u : (unsigned)((batch + 31) / 32) * 32u;
+  pack_candidates_kernel<<<1, threads, 0, dev->stream>>>(
+      m->best_val, m->next, batch, (uint32_t)(m->tp_rank * m->vocab_local), mine);
+  FB_LAUNCH_CHECK(dev);
+  if ((rc = fb200_comm_all_gather_bytes(m->comm, mine, all, (size_t)c.max_batch * 8))) return rc;
+  pick_candidate_kernel<<<1, threads, 0, dev->stream>>>(
+      all, batch, c.max_batch, m->tp_size, m->next);
+  FB_LAUNCH_CHECK(dev);
   return FB200_OK;
 }
 
@@ -503,6 +573,7 @@ int fb200_llama_create(fb200_device* dev, const fb200_llama_config* cfg, fb200_l
   m->dev = dev;
   m->cfg = c;
   m->layers.resize(c.n_layer);
+  m->vocab_local = c.vocab;
   if (const char* e = getenv("FB200_FUSED")) m->fused_enabled = !(e[0] == '0' && e[1] == 0);
   std::vector<float> cs, sn;
   fb200_rope_tables_host(c.head_dim, c.max_seq_len, c.rope_theta, c.rope_factor,
@@ -581,7 +652,7 @@ int fb200_llama_free(fb200_llama* m) {
   if (m->output) fb200_qmatrix_free(m->output);
   void* bufs[] = {m->output_norm, m->rope_cos, m->rope_sin, m->x, m->xn, m->q, m->k, m->v, m->att,
                   m->attn_out, m->hbuf, m->gbuf, m->last, m->logits, m->att_part, m->ids, m->next,
-                  m->hist, m->pos_dev, m->step_dev, m->argmax_key, m->att_done};
+                  m->hist, m->pos_dev, m->step_dev, m->argmax_key, m->att_done, m->best_val, m->best_pair};
   for (void* b : bufs) if (b) cudaFree(b);
   for (fb200_packed_act* p : {&m->px, &m->patt, &m->pv, &m->ph}) {
     void* pb[] = {p->limbs, p->xsc, p->xss, p->sumsq};
@@ -617,7 +688,7 @@ int fb200_llama_set_tensor(fb200_llama* m, int layer, int which, uint32_t ggml_t
   fb200_qmatrix** slot = nullptr;
   const uint64_t qd = (uint64_t)c.n_head * c.head_dim, kvd = (uint64_t)c.n_kv_head * c.head_dim;
   if (which == FB200_T_TOKEN_EMBD) { slot = &m->token_embd; en = c.vocab; ek = c.hidden; }
-  else if (which == FB200_T_OUTPUT) { slot = &m->output; en = c.vocab; ek = c.hidden; }
+  else if (which == FB200_T_OUTPUT) { slot = &m->output; en = m->vocab_local; ek = c.hidden; }
   else {
     if (layer < 0 || layer >= c.n_layer) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "llama: layer %d", layer);
     LayerW& L = m->layers[layer];
@@ -691,7 +762,7 @@ int fb200_llama_forward(fb200_llama* m, const uint32_t* tokens_host, int batch, 
   }
   m->pos += seq;
   if (logits_host)
-    FB_CUDA(dev, cudaMemcpyAsync(logits_host, m->logits, (size_t)batch * c.vocab * 4, cudaMemcpyDeviceToHost, dev->stream));
+    FB_CUDA(dev, cudaMemcpyAsync(logits_host, m->logits, (size_t)batch * m->vocab_local * 4, cudaMemcpyDeviceToHost, dev->stream));
   if (next_host)
     FB_CUDA(dev, cudaMemcpyAsync(next_host, m->next, (size_t)batch * 4, cudaMemcpyDeviceToHost, dev->stream));
   FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
@@ -745,6 +816,29 @@ int fb200_llama_generate_greedy(fb200_llama* m, const uint32_t* tokens_host, int
   FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
   for (int b = 0; b < batch; ++b)
     std::memcpy(out_host + (size_t)b * steps, tmp.data() + (size_t)b * m->hist_cap, (size_t)steps * 4);
+  return FB200_OK;
+}
+
+int fb200_llama_set_tensor_parallel(fb200_llama* m, fb200_comm* comm) {
+  if (!m || !comm) return FB200_ERR_INVALID_ARGUMENT;
+  fb200_device* dev = m->dev;
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  if (fb200_comm_device(comm) != dev)
+    return fb200_fail(dev, FB200_ERR_DEVICE_MISMATCH, "llama: the communicator lives on another device handle");
+  if (m->finalized || m->token_embd || m->output)
+    return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "llama: attach the communicator before any tensor is set");
+  const int size = fb200_comm_size(comm);
+  if (m->cfg.vocab % size)
+    return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "llama: vocab %d is not divisible by %d ranks", m->cfg.vocab, size);
+  m->comm = comm;
+  m->tp_size = size;
+  m->tp_rank = fb200_comm_rank(comm);
+  m->vocab_local = m->cfg.vocab / size;
+  if (size > 1) {
+    FB_CUDA(dev, cudaMalloc(&m->best_val, (size_t)m->cfg.max_batch * 4));
+    FB_CUDA(dev, cudaMalloc(&m->best_pair, (size_t)(1 + size) * m->cfg.max_batch * 8));
+  }
   return FB200_OK;
 }
 

@@ -2,11 +2,17 @@
 import numpy as np
 
 import kalosm_b200 as kb
+from kalosm_b200 import tp
 from oracle import oracle as O
 
 
 def tiny_cfg():
     return dict(n_layer=2, hidden=256, ffn=512, n_head=4, n_kv_head=2, head_dim=64, vocab=1024, ctx=64)
+
+
+def tp_cfg():
+    """Smallest shapes that still cut on 256-element blocks over two ranks (attn_output K = 512)."""
+    return dict(n_layer=2, hidden=512, ffn=1024, n_head=8, n_kv_head=2, head_dim=64, vocab=1024, ctx=96)
 
 
 def llama3_8b_cfg(ctx=1024):
@@ -33,17 +39,20 @@ ORACLE_NAMES = {"token_embd": "token_embd", "output": "output", "attn_q": "wq", 
                 "ffn_down": "down"}
 
 
-def build_models(dev, cfg, batch=1, seed=0, want_cpu=True, sigma=0.02):
+def build_models(dev, cfg, batch=1, seed=0, want_cpu=True, sigma=0.02, comm=None):
+    """With `comm` the GPU model is this rank's shard of the same (whole) seeded weights."""
     gpu = kb.Llama(dev, n_layer=cfg["n_layer"], hidden=cfg["hidden"], ffn=cfg["ffn"],
                    n_head=cfg["n_head"], n_kv_head=cfg["n_kv_head"], head_dim=cfg["head_dim"],
-                   vocab=cfg["vocab"], max_seq_len=cfg["ctx"], max_batch=batch)
+                   vocab=cfg["vocab"], max_seq_len=cfg["ctx"], max_batch=batch, comm=comm)
+    rank, size = (comm.rank, comm.size) if comm is not None else (0, 1)
     cpu = None
     if want_cpu:
         cpu = O.Llama(cfg["n_layer"], cfg["hidden"], cfg["ffn"], cfg["n_head"], cfg["n_kv_head"],
                       cfg["head_dim"], cfg["vocab"], cfg["ctx"], batch=batch, kv_f16=True)
     for j, (name, layer, ty, (n, k)) in enumerate(tensor_plan(cfg)):
         raw = O.random_qweights(seed * 100003 + j, sigma, n * k, ty)
-        gpu.set_tensor(name, layer, ty, (n, k), raw)
+        part, part_shape = tp.shard(name, raw, ty, (n, k), rank, size)
+        gpu.set_tensor(name, layer, ty, part_shape, part)
         if cpu:
             cpu.set_qmatrix(ORACLE_NAMES[name], layer, ty, n, k, raw)
     rng = np.random.default_rng(seed + 77)
