@@ -330,6 +330,137 @@ def run_prefill_only(args):
                       "peak": tf_peak[0], "peak_source": tf_peak[1], "bound": "tensor"}), flush=True)
 
 
+CFG70 = dict(n_layer=80, hidden=8192, ffn=28672, n_head=64, n_kv_head=8, head_dim=128, vocab=128256)
+
+
+def run_tensor_parallel(args):
+    """Llama-3-70B-shaped, all Q4_K, greedy decode with the model split over the ranks (tensor
+    parallel: one sequence group, every rank streams 1 / N of the weights per step; two all-reduces per
+    layer). One JSON line from rank 0; not the bench line (that is the 8B replica metric)."""
+    import torch
+    import torch.distributed as dist
+    import kalosm_b200 as kb
+    from kalosm_b200 import synth, tp
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    dev = kb.Device(local, stream.cuda_stream)
+    comm = None
+    if world > 1:
+        uid = [kb.Comm.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, 0)
+        comm = kb.Comm(dev, world, rank, uid[0])
+    cfg = dict(CFG70, n_layer=args.layers if args.layers != 32 else 80)
+    batch, steps, warmup, prompt_len = args.batch, args.steps, max(args.warmup, 3), args.tp_prompt
+    ctx = prompt_len + 2 * (steps + warmup) + 64
+    m = kb.Llama(dev, n_layer=cfg["n_layer"], hidden=cfg["hidden"], ffn=cfg["ffn"], n_head=cfg["n_head"],
+                 n_kv_head=cfg["n_kv_head"], head_dim=cfg["head_dim"], vocab=cfg["vocab"], max_seq_len=ctx,
+                 max_batch=batch, comm=comm)
+    e, f = cfg["hidden"], cfg["ffn"]
+    qd, kvd = cfg["n_head"] * cfg["head_dim"], cfg["n_kv_head"] * cfg["head_dim"]
+    plan = [("token_embd", -1, (cfg["vocab"], e)), ("output", -1, (cfg["vocab"], e))]
+    for i in range(cfg["n_layer"]):
+        plan += [("attn_q", i, (qd, e)), ("attn_k", i, (kvd, e)), ("attn_v", i, (kvd, e)), ("attn_output", i, (e, qd)),
+                 ("ffn_gate", i, (f, e)), ("ffn_up", i, (f, e)), ("ffn_down", i, (e, f))]
+    local_bytes = 0
+    for j, (name, layer, (n, k)) in enumerate(plan):
+        # this rank's shard is generated directly (random weights: no whole matrix to cut)
+        if name in tp.ROW_SPLIT:
+            n //= world
+        elif name in tp.COL_SPLIT:
+            k //= world
+        seed = 1000003 * (rank if name != "token_embd" else 0) + j
+        raw = synth.random_qweights(seed, 0.02, n, k, Q4_K, device="cuda").cpu().numpy()
+        m.set_tensor(name, layer, Q4_K, (n, k), raw)
+        if name != "token_embd":
+            local_bytes += raw.size
+    g = torch.Generator().manual_seed(77)
+    for i in range(cfg["n_layer"] + 1):
+        for nm in (("attn_norm", "ffn_norm") if i < cfg["n_layer"] else ("output_norm",)):
+            w = (1.0 + 0.02 * torch.randn(e, generator=g)).numpy().astype(np.float32)
+            m.set_tensor(nm, i if i < cfg["n_layer"] else -1, F32, (e,), w)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    prompt = np.random.default_rng(0).integers(0, cfg["vocab"], size=(batch, prompt_len), dtype=np.uint32)
+    m.forward(prompt, want_logits=False)
+    m.reset()
+    barrier()
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record(stream)
+    _, nxt = m.forward(prompt, want_logits=False)
+    p1.record(stream)
+    barrier()
+    ms_prefill = p0.elapsed_time(p1)
+    m.generate_greedy(nxt, warmup)
+    last = m.generate_greedy(nxt, 1)[:, -1]
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.3)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    e0.record(stream)
+    toks = m.generate_greedy(last, steps)
+    e1.record(stream)
+    barrier()
+    t1 = time.time()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop(t0, t1)
+    # the all-reduce alone: the payload of one decode step's sums, back to back
+    ar_us = None
+    if comm is not None:
+        buf = dev.tensor(np.zeros((batch, e), np.float32))
+        for _ in range(20):
+            comm.all_reduce_sum(buf)
+        barrier()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record(stream)
+        for _ in range(2 * cfg["n_layer"]):
+            comm.all_reduce_sum(buf)
+        a1.record(stream)
+        barrier()
+        ar_us = a0.elapsed_time(a1) * 1e3 / (2 * cfg["n_layer"])
+    same = True
+    if world > 1:
+        parts = [None] * world
+        dist.all_gather_object(parts, toks.tolist())
+        same = all(p == parts[0] for p in parts)
+    ms, ms_prefill = max_over_ranks([ms, ms_prefill], world, "cuda")
+    if rank == 0:
+        peak, which = peaks()
+        kv = 2 * cfg["n_layer"] * (cfg["n_kv_head"] // world) * cfg["head_dim"] * 2 * (prompt_len + warmup + steps // 2) * batch
+        gbs = (local_bytes + kv) / (ms / steps / 1e3) / 1e9
+        print(json.dumps({
+            "metric": "Llama-3-70B-shaped Q4_K greedy decode tok/s, tensor parallel", "value": batch * steps / ms * 1e3,
+            "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms / steps,
+            "higher_is_better": True, "scaling": "strong", "data": "synthetic (seeded N(0, 0.02) weights as Q4_K blocks)",
+            "config": {"workload": f"llama3-70b-shaped all-Q4_K greedy decode, TP={world}, batch {batch}, prompt "
+                                   f"{prompt_len}, {steps} steps" + ("" if cfg["n_layer"] == 80 else
+                                                                     f" (REDUCED: {cfg['n_layer']} layers)"),
+                       "parallelism": f"tp{world}"},
+            "per_gpu": {"weight_bytes_per_step": local_bytes, "kv_bytes_per_step": kv, "achieved_gbs": gbs,
+                        "peak": peak, "peak_source": which, "frac": gbs / peak},
+            "all_reduce": None if ar_us is None else {"per_step": 2 * cfg["n_layer"], "payload_bytes": batch * e * 4,
+                                                      "us_each_back_to_back": ar_us,
+                                                      "ms_per_step_alone": ar_us * 2 * cfg["n_layer"] / 1e3},
+            "prefill": {"tokens": batch * prompt_len, "ms": ms_prefill, "tok_s": batch * prompt_len / ms_prefill * 1e3},
+            "ranks_agree_on_tokens": same, "device_status": dev.status(), "clocks": clocks}), flush=True)
+    m.free()
+    if comm is not None:
+        comm.destroy()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_sweep(args):
     """Per-kernel table of the other configurations of the path, one JSON line each (not the bench
     line): single-row and small-batch quantised products over the Llama-3-8B matrix shapes, and
@@ -571,6 +702,9 @@ def main():
     ap.add_argument("--gemv-only", action="store_true", help="run only the dominant-kernel leg")
     ap.add_argument("--prefill-only", action="store_true",
                     help="run one prefill product and one prefill attention (profiling case)")
+    ap.add_argument("--tp", action="store_true",
+                    help="70B-shaped model split over the ranks (tensor parallel) instead of 8B replicas")
+    ap.add_argument("--tp-prompt", type=int, default=2048)
     ap.add_argument("--gemv-reps", type=int, default=8)
     ap.add_argument("--sweep", action="store_true",
                     help="per-kernel table over the other product shapes and decode attention (several JSON lines)")
@@ -584,6 +718,8 @@ def main():
         run_gemv_only(args)
     elif args.prefill_only:
         run_prefill_only(args)
+    elif args.tp:
+        run_tensor_parallel(args)
     else:
         run_ours(args)
 
