@@ -273,6 +273,15 @@ FB200_API int fb200_comm_create(fb200_device* dev, int size, int rank, const uin
 FB200_API int fb200_comm_destroy(fb200_comm* c);
 /* In-place sum of buf_dev[n] (f32) over the ranks, asynchronous on the device handle's stream. */
 FB200_API int fb200_comm_all_reduce_sum(fb200_comm* c, float* buf_dev, size_t n);
+/* Peer exchange of the single-sequence decode kernel (optional; without it the step uses the
+ * NCCL sums above): every rank makes a buffer for rows of row_floats floats (the model's hidden
+ * size) and gets an FB200_IPC_HANDLE_BYTES handle; the handles of all ranks, in rank order, go to
+ * every rank's _attach, which maps the peers' buffers (CUDA IPC, ranks are processes of one node
+ * with NVLink / P2P access). The decode kernel then writes its partial rows straight into the
+ * peers' buffers and sums them itself: no library collective on the step's critical path. */
+#define FB200_IPC_HANDLE_BYTES 64
+FB200_API int fb200_comm_exchange_handle(fb200_comm* c, size_t row_floats, uint8_t* handle_out, size_t handle_bytes);
+FB200_API int fb200_comm_exchange_attach(fb200_comm* c, const uint8_t* handles, size_t handle_bytes);
 /* Must precede fb200_llama_set_tensor. The communicator must outlive the model. */
 FB200_API int fb200_llama_set_tensor_parallel(fb200_llama* m, fb200_comm* comm);
 

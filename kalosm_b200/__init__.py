@@ -27,6 +27,7 @@ OK = 0
 ERR_INVALID_SHAPE, ERR_UNSUPPORTED_DTYPE, ERR_CAPACITY, ERR_CUDA = -1, -2, -3, -4
 ERR_INVALID_ARGUMENT, ERR_TIMEOUT, ERR_DEVICE_MISMATCH, ERR_NCCL = -5, -6, -7, -8
 COMM_ID_BYTES = 128
+IPC_HANDLE_BYTES = 64
 EPI_NONE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
 MASK_NONE, MASK_CAUSAL, MASK_QK, MASK_BATCH_KEY = 0, 1, 2, 3
 
@@ -66,6 +67,7 @@ EXPORTS = [
     "fb200_llama_set_tensor", "fb200_llama_reset", "fb200_llama_position", "fb200_llama_forward",
     "fb200_llama_generate_greedy", "fb200_llama_logits_dev", "fb200_llama_set_tensor_parallel",
     "fb200_comm_unique_id", "fb200_comm_create", "fb200_comm_destroy", "fb200_comm_all_reduce_sum",
+    "fb200_comm_exchange_handle", "fb200_comm_exchange_attach",
 ]
 
 _lib = None
@@ -132,6 +134,8 @@ def load_library():
         "fb200_comm_create": (i32, [vp, i32, i32, vp, sz, pp]),
         "fb200_comm_destroy": (i32, [vp]),
         "fb200_comm_all_reduce_sum": (i32, [vp, vp, sz]),
+        "fb200_comm_exchange_handle": (i32, [vp, sz, vp, sz]),
+        "fb200_comm_exchange_attach": (i32, [vp, vp, sz]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -474,6 +478,20 @@ class Comm:
         """In-place sum of an f32 tensor over the ranks."""
         self.device._check(self.device.lib.fb200_comm_all_reduce_sum(self.h, t.ptr, int(np.prod(t.shape))))
         return t
+
+    def enable_peer_exchange(self, row_floats: int, all_gather) -> None:
+        """Maps every rank's exchange buffer into every other rank (CUDA IPC), so that the
+        single-sequence decode kernel sums its partial rows over NVLink itself instead of calling
+        NCCL. `row_floats` = the model's hidden size; `all_gather(obj)` returns the list of every
+        rank's `obj` in rank order (any host channel). Call on all ranks, before the first decode
+        step of a model that uses this communicator."""
+        buf = (C.c_uint8 * IPC_HANDLE_BYTES)()
+        self.device._check(self.device.lib.fb200_comm_exchange_handle(self.h, row_floats, buf, IPC_HANDLE_BYTES))
+        handles = all_gather(bytes(buf))
+        if len(handles) != self.size:
+            raise FusorError(ERR_INVALID_ARGUMENT, "all_gather must return one handle per rank")
+        packed = (C.c_uint8 * (IPC_HANDLE_BYTES * self.size)).from_buffer_copy(b"".join(handles))
+        self.device._check(self.device.lib.fb200_comm_exchange_attach(self.h, packed, IPC_HANDLE_BYTES))
 
     def destroy(self) -> None:
         if self.h:

@@ -11,11 +11,18 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "fused_step.cuh"
 
 struct fb200_comm {
   fb200_device* dev = nullptr;
   ncclComm_t nccl = nullptr;
   int rank = 0, size = 1;
+  // exchange buffer of the fused decode kernel (layout: see fb200_fused_xchg), mapped by all peers
+  uint8_t* xbuf = nullptr;
+  uint8_t* peer[8] = {};
+  int stride = 0;
+  bool attached = false;
+  unsigned epoch = 1;  // next exchange number; arrival words start at 0
 };
 
 namespace {
@@ -69,6 +76,23 @@ int fb200_comm_all_gather_bytes(fb200_comm* c, const void* in, void* out, size_t
   return FB200_OK;
 }
 
+// Pointers of the peer exchange for a launch that performs `count` exchanges; false when the
+// peers have not been attached or a row does not fit a slot.
+bool fb200_comm_take_exchange(fb200_comm* c, int row_floats, unsigned count, fb200_fused_xchg* out) {
+  if (!c->attached || row_floats > c->stride) return false;
+  const size_t keys_off = (size_t)2 * c->size * c->stride * 4, flags_off = keys_off + (size_t)2 * c->size * 8;
+  for (int r = 0; r < c->size; ++r) {
+    out->data[r] = reinterpret_cast<float*>(c->peer[r]);
+    out->keys[r] = reinterpret_cast<unsigned long long*>(c->peer[r] + keys_off);
+    out->flags[r] = reinterpret_cast<unsigned*>(c->peer[r] + flags_off);
+  }
+  out->world = c->size; out->me = c->rank; out->stride = c->stride;
+  out->epoch_base = c->epoch;
+  c->epoch += count;
+  return true;
+}
+bool fb200_comm_exchange_ready(const fb200_comm* c, int row_floats) { return c->attached && row_floats <= c->stride; }
+
 int fb200_comm_rank(const fb200_comm* c) { return c->rank; }
 int fb200_comm_size(const fb200_comm* c) { return c->size; }
 fb200_device* fb200_comm_device(const fb200_comm* c) { return c->dev; }
@@ -103,8 +127,51 @@ int fb200_comm_create(fb200_device* dev, int size, int rank, const uint8_t* id, 
   return FB200_OK;
 }
 
+int fb200_comm_exchange_handle(fb200_comm* c, size_t row_floats, uint8_t* handle_out, size_t handle_bytes) {
+  if (!c || !handle_out || handle_bytes < sizeof(cudaIpcMemHandle_t)) return FB200_ERR_INVALID_ARGUMENT;
+  fb200_device* dev = c->dev;
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  if (c->size > 8) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "comm: the peer exchange takes at most 8 ranks");
+  if (c->xbuf || row_floats == 0 || row_floats > (1u << 24))
+    return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "comm: exchange buffer already made, or bad row size");
+  c->stride = (int)((row_floats + 31) / 32 * 32);
+  const size_t bytes = (size_t)2 * c->size * c->stride * 4 + (size_t)2 * c->size * 8 + (size_t)c->size * 4 + 256;
+  FB_CUDA(dev, cudaMalloc(&c->xbuf, bytes));
+  FB_CUDA(dev, cudaMemset(c->xbuf, 0, bytes));
+  cudaIpcMemHandle_t h;
+  FB_CUDA(dev, cudaIpcGetMemHandle(&h, c->xbuf));
+  memset(handle_out, 0, handle_bytes);
+  memcpy(handle_out, &h, sizeof(h));
+  return FB200_OK;
+}
+
+int fb200_comm_exchange_attach(fb200_comm* c, const uint8_t* handles, size_t handle_bytes) {
+  if (!c || !handles || handle_bytes < sizeof(cudaIpcMemHandle_t)) return FB200_ERR_INVALID_ARGUMENT;
+  fb200_device* dev = c->dev;
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  if (!c->xbuf || c->attached) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "comm: make the exchange handle first, attach once");
+  for (int r = 0; r < c->size; ++r) {
+    if (r == c->rank) { c->peer[r] = c->xbuf; continue; }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handles + (size_t)r * handle_bytes, sizeof(h));
+    void* p = nullptr;
+    FB_CUDA(dev, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    c->peer[r] = static_cast<uint8_t*>(p);
+  }
+  c->attached = true;
+  return FB200_OK;
+}
+
 int fb200_comm_destroy(fb200_comm* c) {
   if (!c) return FB200_OK;
+  if (c->dev && fb200_bind(c->dev) == FB200_OK) {
+    cudaStreamSynchronize(c->dev->stream);
+    for (int r = 0; r < c->size; ++r)
+      if (c->attached && r != c->rank && c->peer[r]) cudaIpcCloseMemHandle(c->peer[r]);
+    if (c->xbuf) cudaFree(c->xbuf);
+  }
   if (c->nccl) nccl_api().CommDestroy(c->nccl);
   delete c;
   return FB200_OK;

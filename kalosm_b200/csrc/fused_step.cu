@@ -49,6 +49,7 @@ struct FusedArgs {
   int* counters;   // arrival counters per unit, zero between uses
   int* status;
   unsigned long long* trace;  // optional [nphases][8] time stamps of CTA 0 in the last step (ns)
+  fb200_fused_xchg x;         // tensor-parallel exchange (world <= 1: none)
 };
 
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -198,7 +199,41 @@ __device__ __forceinline__ void prefetch_phase(const fb200_fused_phase& P, const
 struct EpiCtx {
   float final_scale;
   unsigned long long best_key;
+  const fb200_fused_xchg* xs;  // not null: rows of matrix 0 go to every rank's exchange buffer
+  int xs_off;                  // float offset of this rank's slot for the current epoch
 };
+
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Tells every peer that this rank's contribution to exchange `epoch` is complete in its buffer
+// (called by one thread after the grid barrier that followed the writes), then waits until every
+// peer has said the same here. Bounded: after 2^22 polls (or when another wait has already given
+// up) the time-out is recorded and the kernel carries on with whatever is there.
+__device__ __forceinline__ void xchg_signal_and_wait(const FusedArgs& A, unsigned epoch, bool signal) {
+  const fb200_fused_xchg& X = A.x;
+  if (signal) {
+    __threadfence_system();
+    for (int r = 0; r < X.world; ++r)
+      if (r != X.me) st_release_sys_u32(X.flags[r] + X.me, epoch);
+  }
+  for (int r = 0; r < X.world; ++r) {
+    if (r == X.me) continue;
+    bool ok = false;
+    for (int it = 0; it < (1 << 22); ++it) {
+      if ((int)(ld_acquire_sys_u32(X.flags[X.me] + r) - epoch) >= 0) { ok = true; break; }
+      if ((it & 1023) == 1023 && __ldcg(A.status) != 0) break;
+      __nanosleep(64);
+    }
+    if (!ok) { atomicExch(A.status, FB200_ERR_TIMEOUT); break; }
+  }
+}
 
 // The operands of a unit's epilogue (row `lane` of the unit): residuals, the row added before
 // packing, the norm weight folded into the packed row. Everything was produced before the phase
@@ -223,6 +258,7 @@ __device__ __forceinline__ EpiOperands epilogue_operands(const fb200_fused_phase
 }
 
 // Epilogue of one unit; lanes 0..15 call it with the sums of row `lane` (pass 0 / pass 1).
+template <bool XS>
 __device__ __noinline__ void unit_epilogue(const fb200_fused_phase& P, int unit, float s0, float s1, int lane,
                                            EpiCtx& E, const EpiOperands& pre) {
   int sidx, tile;
@@ -246,6 +282,10 @@ __device__ __noinline__ void unit_epilogue(const fb200_fused_phase& P, int unit,
       out = v0;
     }
     if (yout) yout[n] = out;
+    if (XS && E.xs && sidx == 0) {
+      // partial row of a tensor-parallel projection: straight into every rank's buffer (P2P stores)
+      for (int r = 0; r < E.xs->world; ++r) E.xs->data[r][E.xs_off + n] = out;
+    }
     if (P.argmax_key && sidx == 0) {
       const unsigned long long key = argmax_key_of(out, (uint32_t)n);
       if (key > E.best_key) E.best_key = key;
@@ -266,9 +306,9 @@ struct Smem {
   unsigned long long* keys;   // [FW]
 };
 
-template <bool LEGACY>
+template <bool LEGACY, bool XS>
 __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused_phase& P, const fb200_fused_phase* Pnext,
-                           const Smem& S, WarpRing& R, Carry& C, unsigned long long* tr) {
+                           const Smem& S, WarpRing& R, Carry& C, unsigned long long* tr, unsigned epoch) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int K = P.K, Kp = P.Kp;
 
@@ -289,6 +329,8 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
   EpiCtx E;
   E.final_scale = 1.0f;
   E.best_key = 0ull;
+  E.xs = XS && P.xs_index >= 0 && A.x.world > 1 ? &A.x : nullptr;
+  E.xs_off = XS ? (int)((epoch & 1u) * (unsigned)A.x.world + (unsigned)A.x.me) * A.x.stride : 0;
   if (P.xp_norm) {
     float ss = 0.f;
     for (int i = tid; i < (K + 15) / 16; i += FT) ss += __ldcg(P.xp.sumsq + i);
@@ -378,7 +420,7 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
         const bool complete = unit_first_item == u_done * q.ipu && i == (u_done + 1) * q.ipu;
         if (lane < 16) {
           if (complete) {
-            unit_epilogue(P, u_done, pv0, pv1, lane, E, pre);
+            unit_epilogue<XS>(P, u_done, pv0, pv1, lane, E, pre);
           } else {
             float* pc = S.pieces + (warp * 2 + (u_done == u_first ? 0 : 1)) * 32;
             pc[lane] = pv0;
@@ -420,7 +462,7 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
       }
       if (tr && m == ua) tr[6] = global_ns();
       if (cta_whole) {
-        if (lane < 16) unit_epilogue(P, m, s0, s1, lane, E, pre);
+        if (lane < 16) unit_epilogue<XS>(P, m, s0, s1, lane, E, pre);
         __syncwarp();
         if (tr && m == ua) tr[7] = global_ns();
         continue;
@@ -447,7 +489,7 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
           t0 += __ldcg(pc + lane);
           t1 += __ldcg(pc + 16 + lane);
         }
-        unit_epilogue(P, m, t0, t1, lane, E, pre);
+        unit_epilogue<XS>(P, m, t0, t1, lane, E, pre);
       }
       __syncwarp();
     }
@@ -501,10 +543,49 @@ __device__ __noinline__ void pack_phase(const fb200_fused_phase& P) {
   }
 }
 
-__device__ __noinline__ void advance_phase(const FusedArgs& A, const fb200_fused_phase& P) {
+// Sum of the ranks' partial rows (rank order: the same bits on every rank), residual rows added
+// in the order of the single-GPU epilogues, float copies and the packed row for the next product.
+__device__ __noinline__ void xsum_phase(const FusedArgs& A, const fb200_fused_phase& P, unsigned epoch) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) xchg_signal_and_wait(A, epoch, blockIdx.x == 0);
+  __syncthreads();
+  const fb200_fused_xchg& X = A.x;
+  const float* base = X.data[X.me] + (size_t)(epoch & 1u) * X.world * X.stride;
+  const int nblk = (P.K + 31) / 32;
+  for (int b = (int)blockIdx.x * FW + warp; b < nblk; b += (int)gridDim.x * FW) {
+    const int n = b * 32 + lane;
+    const bool valid = n < P.K;
+    float v = 0.f;
+    if (valid) {
+      for (int r = 0; r < X.world; ++r) v += __ldcg(base + (size_t)r * X.stride + n);
+      if (P.out_sum) P.out_sum[n] = v;
+      if (P.src) v += __ldcg(P.src + n);
+      if (P.src_add) v += __ldcg(P.src_add + n);
+      if (P.xout) P.xout[n] = v;
+    }
+    const float nv = v;
+    if (valid && P.yp_norm_w) v *= P.yp_norm_w[n];
+    emit_packed16(P.yp, n, v, nv, valid, 0xFFFFFFFFu);
+  }
+}
+
+template <bool XS>
+__device__ __noinline__ void advance_phase(const FusedArgs& A, const fb200_fused_phase& P, unsigned epoch) {
   if (blockIdx.x != 0 || threadIdx.x != 0) return;
   // the output head kept a running (value, index) maximum; 0 means no finite logit
-  const unsigned long long key = __ldcg(P.argmax_key);
+  unsigned long long key = __ldcg(P.argmax_key);
+  if (XS && A.x.world > 1 && P.xs_index >= 0) {
+    // sharded output head: every rank's best (value, global id); the largest key wins everywhere
+    const fb200_fused_xchg& X = A.x;
+    if (key) key += X.id_base;  // the id sits in the low half and stays below 2^32
+    const int slot = (int)(epoch & 1u) * X.world;
+    for (int r = 0; r < X.world; ++r) X.keys[r][slot + X.me] = key;
+    xchg_signal_and_wait(A, epoch, true);
+    for (int r = 0; r < X.world; ++r) {
+      const unsigned long long k = __ldcg(X.keys[X.me] + slot + r);
+      if (k > key) key = k;
+    }
+  }
   const uint32_t tok = key ? (uint32_t)(key & 0xFFFFFFFFull) : 0xFFFFFFFFu;
   *P.argmax_key = 0ull;
   P.next[0] = tok;
@@ -535,7 +616,7 @@ __device__ __noinline__ void attn_phase(const fb200_fused_phase& P, uint8_t* dsm
 // One kernel variant per attention shape (head size D, query rows per KV head ROWS) and per
 // family of weight types (LEGACY = the 32-element block types too): a variant carries only the
 // code it runs, which keeps the instruction footprint of a step small.
-template <int D, int ROWS, bool LEGACY>
+template <int D, int ROWS, bool LEGACY, bool XS>
 __global__ void __launch_bounds__(FT, 1)
 fused_step_kernel(const FusedArgs A) {
   extern __shared__ __align__(128) uint8_t smem[];
@@ -586,6 +667,7 @@ fused_step_kernel(const FusedArgs A) {
         load_desc(g + 3);  // into the slot of the phase that has just ended
       }
       const fb200_fused_phase& P = *desc_of(g);
+      const unsigned epoch = XS ? A.x.epoch_base + (unsigned)(step * A.x.per_step + (P.xs_index >= 0 ? P.xs_index : 0)) : 0u;
       unsigned long long* tr = A.trace && blockIdx.x == 0 && tid == 0 && step == A.nsteps - 1 ? A.trace + ph * 8 : nullptr;
       if (tr) tr[0] = global_ns();
       switch (P.kind) {
@@ -594,7 +676,7 @@ fused_step_kernel(const FusedArgs A) {
           S.xss = S.xsc + P.Kp / 16;
           const int ahead = P.next_gemv < 0 ? -1 : (P.next_gemv > ph ? P.next_gemv - ph : P.next_gemv + A.nphases - ph);
           const bool has_next = ahead > 0 && ahead <= 3 && g + ahead < total_phases;
-          gemv_phase<LEGACY>(A, P, has_next ? desc_of(g + ahead) : nullptr, S, R, C, tr);
+          gemv_phase<LEGACY, XS>(A, P, has_next ? desc_of(g + ahead) : nullptr, S, R, C, tr, epoch);
           break;
         }
         case FB200_PH_ATTN:
@@ -604,8 +686,11 @@ fused_step_kernel(const FusedArgs A) {
         case FB200_PH_EMBED:
           pack_phase(P);
           break;
+        case FB200_PH_XSUM:
+          if (XS) xsum_phase(A, P, epoch);
+          break;
         default:
-          advance_phase(A, P);
+          advance_phase<XS>(A, P, epoch);
           break;
       }
       if (tr) tr[3] = global_ns();
@@ -690,7 +775,7 @@ size_t fb200_fused_smem_bytes(const fb200_fused_phase* prog_host, int nphases) {
 }
 
 int fb200_fused_launch(fb200_device* dev, const fb200_fused_phase* prog_dev, const fb200_fused_phase* prog_host,
-                       int nphases, int nsteps, bool record_history) {
+                       int nphases, int nsteps, bool record_history, const fb200_fused_xchg* xchg) {
   if (nphases <= 0 || nsteps <= 0) return FB200_OK;
   const int grid = fb200_fused_grid(dev);
   const size_t xregion = x_region_need(prog_host, nphases);
@@ -726,13 +811,15 @@ int fb200_fused_launch(fb200_device* dev, const fb200_fused_phase* prog_dev, con
   }
   void (*kern)(const FusedArgs) = nullptr;
   int variant = 0;
-  if (att_d == 128 && groups <= 4 && !legacy) { kern = fused_step_kernel<128, 4, false>; variant = 0; }
-  else if (att_d == 128 && !legacy) { kern = fused_step_kernel<128, 8, false>; variant = 1; }
-  else if (att_d == 128) { kern = fused_step_kernel<128, 8, true>; variant = 2; }
-  else if (att_d == 64 && !legacy) { kern = fused_step_kernel<64, 8, false>; variant = 3; }
-  else if (att_d == 64) { kern = fused_step_kernel<64, 8, true>; variant = 4; }
+  const bool xs = xchg && xchg->world > 1;  // the exchange code lives in variants of its own
+  if (xs && legacy) return fb200_fail(dev, FB200_ERR_UNSUPPORTED_DTYPE, "fused step: tensor parallel needs K-quant weights");
+  if (att_d == 128 && groups <= 4 && !legacy) { kern = xs ? fused_step_kernel<128, 4, false, true> : fused_step_kernel<128, 4, false, false>; variant = xs ? 5 : 0; }
+  else if (att_d == 128 && !legacy) { kern = xs ? fused_step_kernel<128, 8, false, true> : fused_step_kernel<128, 8, false, false>; variant = xs ? 6 : 1; }
+  else if (att_d == 128) { kern = fused_step_kernel<128, 8, true, false>; variant = 2; }
+  else if (att_d == 64 && !legacy) { kern = xs ? fused_step_kernel<64, 8, false, true> : fused_step_kernel<64, 8, false, false>; variant = xs ? 7 : 3; }
+  else if (att_d == 64) { kern = fused_step_kernel<64, 8, true, false>; variant = 4; }
   else return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "fused step: head size %d", att_d);
-  static bool configured[64][5] = {};
+  static bool configured[64][8] = {};
   if (!configured[dev->ordinal & 63][variant]) {
     FB_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       SMEM_LIMIT - STATIC_SMEM_RESERVE));
@@ -749,6 +836,7 @@ int fb200_fused_launch(fb200_device* dev, const fb200_fused_phase* prog_dev, con
   a.gp = reinterpret_cast<float*>((uint8_t*)dev->fused + gp_off);
   a.counters = reinterpret_cast<int*>((uint8_t*)dev->fused + cnt_off);
   a.status = dev->status;
+  if (xchg) a.x = *xchg;
   FB_CUDA(dev, cudaMemsetAsync(a.bar, 0, 4, dev->stream));
   // FB200_FUSED_TRACE=1: per-phase time stamps of CTA 0, printed to stderr after the launch
   static const bool want_trace = getenv("FB200_FUSED_TRACE") && getenv("FB200_FUSED_TRACE")[0] == '1';

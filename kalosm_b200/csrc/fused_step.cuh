@@ -15,6 +15,26 @@ enum fb200_fused_kind {
   FB200_PH_PACK = 2,     // float row (+ row) -> packed row (optionally times a norm weight)
   FB200_PH_EMBED = 3,    // embedding row of ids[0] -> float row + packed row
   FB200_PH_ADVANCE = 4,  // greedy id from the argmax key -> ids, history; position + 1
+  FB200_PH_XSUM = 5,     // tensor parallel: signal the peers, wait for theirs, sum the ranks' partial rows in
+                         // rank order (+ residual rows) -> float row(s) + packed row
+};
+
+// Tensor-parallel exchange over peer memory (NVLink): every rank owns one buffer
+//   [2 parities][world][stride floats] partial rows | [2][world] greedy keys | [world] arrival epochs
+// that all its peers have mapped. A product phase with xs_index >= 0 writes its output rows into
+// slot [epoch & 1][this rank] of EVERY rank's buffer; the FB200_PH_XSUM phase after the grid barrier
+// publishes "epoch" in every peer's arrival word for this rank (release at system scope), waits
+// (bounded) for the peers' words to reach the epoch and sums the slots. epoch = epoch_base +
+// step * per_step + xs_index is the same number on all ranks; a rank can run at most one
+// exchange ahead of a peer, so two parities are enough.
+struct fb200_fused_xchg {
+  float* data[8];
+  unsigned long long* keys[8];
+  unsigned* flags[8];
+  int world, me, stride;
+  unsigned epoch_base;
+  int per_step;
+  unsigned id_base;  // first global token id of this rank's rows of the output head
 };
 
 struct fb200_fused_seg {
@@ -70,6 +90,12 @@ struct fb200_fused_phase {
   int* pos_dev;
   int* step_dev;
   int hist_cap;
+  // ---- tensor parallel: index of this phase's exchange within a step (-1: none). On a product
+  // phase: rows go to the peers instead of seg[0].y; on FB200_PH_XSUM: out_sum = sum over ranks,
+  // v = sum + src + src_add -> xout, packed into yp (times yp_norm_w); on FB200_PH_ADVANCE: the
+  // greedy key is exchanged and the largest wins.
+  int xs_index;
+  float* out_sum;
 };
 
 // Fills the derived fields of a product phase (units, items, chunk, ring geometry) from its
@@ -82,4 +108,4 @@ size_t fb200_fused_smem_bytes(const fb200_fused_phase* prog_host, int nphases);
 int fb200_fused_grid(const fb200_device* dev);
 // Runs `nsteps` passes over the program (device copy `prog_dev` of `prog_host`).
 int fb200_fused_launch(fb200_device* dev, const fb200_fused_phase* prog_dev, const fb200_fused_phase* prog_host,
-                       int nphases, int nsteps, bool record_history);
+                       int nphases, int nsteps, bool record_history, const fb200_fused_xchg* xchg);

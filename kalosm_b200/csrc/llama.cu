@@ -38,6 +38,8 @@ int fb200_comm_all_gather_bytes(fb200_comm* c, const void* in, void* out, size_t
 int fb200_comm_rank(const fb200_comm* c);
 int fb200_comm_size(const fb200_comm* c);
 fb200_device* fb200_comm_device(const fb200_comm* c);
+bool fb200_comm_take_exchange(fb200_comm* c, int row_floats, unsigned count, fb200_fused_xchg* out);
+bool fb200_comm_exchange_ready(const fb200_comm* c, int row_floats);
 
 namespace {
 
@@ -251,11 +253,20 @@ int build_fused_program(fb200_llama* m) {
   const auto& c = m->cfg;
   m->fused_usable = false;
   m->fused_valid = true;
-  if (!m->fused_enabled || m->tp_size > 1 || !decode1_supported(m)) return FB200_OK;
+  if (!m->fused_enabled || !decode1_supported(m)) return FB200_OK;
+  if (m->tp_size > 1 && !fb200_comm_exchange_ready(m->comm, m->cfg.hidden)) return FB200_OK;
+  if (m->tp_size > 1)  // the exchange variants of the kernel exist for K-quant weights only
+    for (const auto& L : m->layers)
+      for (const fb200_qmatrix* q : {L.wq, L.wk, L.wv, L.wo, L.gate_up, L.down})
+        if (q->type == FB200_Q4_0 || q->type == FB200_Q8_0) return FB200_OK;
   const int grid = fb200_fused_grid(dev);
   const int H = c.n_head, HK = c.n_kv_head, D = c.head_dim;
   std::vector<fb200_fused_phase> prog;
-  auto blank = [] { fb200_fused_phase p; std::memset(&p, 0, sizeof(p)); p.next_gemv = -1; return p; };
+  auto blank = [] { fb200_fused_phase p; std::memset(&p, 0, sizeof(p)); p.next_gemv = -1; p.xs_index = -1; return p; };
+  // tensor parallel: the partial rows of the o and down projections go to the peers' exchange
+  // buffers and an XSUM phase adds them up (needs the peer exchange; otherwise the step runs as
+  // separate kernels with NCCL sums)
+  const bool tp = m->tp_size > 1;
   {
     fb200_fused_phase p = blank();
     p.kind = FB200_PH_EMBED;
@@ -304,10 +315,17 @@ int build_fused_program(fb200_llama* m) {
     prog.push_back(p);
 
     const fb200_qmatrix* wo = L.wo;
-    float* wo_out = m->attn_out;
+    float* wo_out = tp ? nullptr : m->attn_out;
     if (!gemv(&wo, &wo_out, 1, FB200_EPI_NONE, p)) return FB200_OK;
     p.xp = m->patt;
-    p.yp = m->pv; p.yp_add = m->x; p.yp_norm_w = L.ffn_norm;
+    if (tp) {
+      p.xs_index = 2 * li;
+      prog.push_back(p);
+      p = blank();
+      p.kind = FB200_PH_XSUM; p.K = c.hidden; p.xs_index = 2 * li;
+      p.out_sum = m->attn_out; p.src = m->x;            // attn_out = sum; packed row = (attn_out + x) w
+    }
+    p.yp = m->pv; p.yp_add = tp ? nullptr : m->x; p.yp_norm_w = L.ffn_norm;
     prog.push_back(p);
 
     const fb200_qmatrix* gu = L.gate_up;
@@ -318,10 +336,18 @@ int build_fused_program(fb200_llama* m) {
     prog.push_back(p);
 
     const fb200_qmatrix* dn = L.down;
-    float* dn_out = m->x;
-    if (!gemv(&dn, &dn_out, 1, FB200_EPI_RESIDUAL, p)) return FB200_OK;
+    float* dn_out = tp ? nullptr : m->x;
+    if (!gemv(&dn, &dn_out, 1, tp ? FB200_EPI_NONE : FB200_EPI_RESIDUAL, p)) return FB200_OK;
     p.xp = m->ph;
-    p.r1 = m->attn_out; p.r2 = m->x;
+    if (tp) {
+      p.xs_index = 2 * li + 1;
+      prog.push_back(p);
+      p = blank();
+      p.kind = FB200_PH_XSUM; p.K = c.hidden; p.xs_index = 2 * li + 1;
+      p.src = m->attn_out; p.src_add = m->x; p.xout = m->x;   // x = (sum + attn_out) + x
+    } else {
+      p.r1 = m->attn_out; p.r2 = m->x;
+    }
     p.yp = m->px;
     p.yp_norm_w = li + 1 < c.n_layer ? m->layers[li + 1].attn_norm : m->output_norm;
     prog.push_back(p);
@@ -339,6 +365,7 @@ int build_fused_program(fb200_llama* m) {
     p.argmax_key = m->argmax_key;
     p.next = m->next; p.ids_w = m->ids; p.hist = m->hist; p.pos_dev = m->pos_dev; p.step_dev = m->step_dev;
     p.hist_cap = m->hist_cap;
+    if (tp) p.xs_index = 2 * c.n_layer;  // the greedy key of the sharded output head is exchanged too
     prog.push_back(p);
   }
   // chain the product phases (the last one wraps to the first, used when several steps run in one launch)
@@ -367,7 +394,16 @@ int run_fused(fb200_llama* m, int steps, bool record) {
   int rc;
   for (int done = 0; done < steps;) {
     const int n = std::min(steps - done, 256);  // bounded kernel run time
-    if ((rc = fb200_fused_launch(dev, m->prog_dev, m->prog_host.data(), (int)m->prog_host.size(), n, record)))
+    fb200_fused_xchg xs = {};
+    if (m->tp_size > 1) {
+      const int per_step = 2 * m->cfg.n_layer + 1;
+      if (!fb200_comm_take_exchange(m->comm, m->cfg.hidden, (unsigned)(n * per_step), &xs))
+        return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "llama: the peer exchange went away");
+      xs.per_step = per_step;
+      xs.id_base = (unsigned)(m->tp_rank * m->vocab_local);
+    }
+    if ((rc = fb200_fused_launch(dev, m->prog_dev, m->prog_host.data(), (int)m->prog_host.size(), n, record,
+                                 m->tp_size > 1 ? &xs : nullptr)))
       return rc;
     done += n;
   }

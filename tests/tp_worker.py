@@ -76,6 +76,39 @@ def main():
     assert gpu.position == 40 + 4 + 6
     assert dev.status() == 0
     gpu.free()
+
+    # one sequence: the whole step is one persistent kernel per rank; the partial rows of the o and
+    # down projections and the greedy key cross NVLink inside it (peer exchange), no NCCL call
+    comm.enable_peer_exchange(cfg["hidden"], gather)
+    one, cpu1 = build_models(dev, cfg, batch=1, seed=7, want_cpu=(rank == 0), comm=comm)
+    prompt = np.random.default_rng(8).integers(0, cfg["vocab"], size=(1, 11), dtype=np.uint32)
+    lg, nxt = one.forward(prompt)
+    launches = dev.launch_count
+    lg, nxt2 = one.forward(nxt[:, None])
+    assert dev.launch_count - launches == 1, "a single-sequence step must be one launch"
+    full = np.concatenate(gather(lg), axis=1)
+    ids = gather(nxt2)
+    assert all(np.array_equal(ids[0], i) for i in ids), ids
+    assert np.array_equal(nxt2, [O.top_k(full[0], 1)[0][0]])
+    if rank == 0:
+        cpu1.forward(prompt)
+        lo = cpu1.forward(nxt[:, None])
+        assert F.rel_l2(full, lo) < 2e-3, F.rel_l2(full, lo)
+    out = one.generate_greedy(nxt2, 12)
+    outs = gather(out)
+    assert all(np.array_equal(outs[0], o) for o in outs), outs
+    if rank == 0:
+        tok1 = nxt2.copy()
+        for step in range(12):
+            lo = cpu1.forward(tok1[:, None])
+            want = O.top_k(lo[0], 1)[0][0]
+            srt = np.sort(lo[0])
+            if out[0, step] != want:
+                assert srt[-1] - srt[-2] < 1e-3, (step, srt[-1] - srt[-2])
+                break
+            tok1 = np.array([want], dtype=np.uint32)
+    assert dev.status() == 0
+    one.free()
     comm.destroy()
     dist.barrier()
     dist.destroy_process_group()
