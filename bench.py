@@ -355,6 +355,13 @@ def run_tensor_parallel(args):
         uid = [kb.Comm.unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, 0)
         comm = kb.Comm(dev, world, rank, uid[0])
+        if not args.tp_nccl:
+            # the decode step sums its partial rows over NVLink peer memory inside the persistent kernel
+            def gather(obj):
+                parts = [None] * world
+                dist.all_gather_object(parts, obj)
+                return parts
+            comm.enable_peer_exchange(CFG70["hidden"], gather)
     cfg = dict(CFG70, n_layer=args.layers if args.layers != 32 else 80)
     batch, steps, warmup, prompt_len = args.batch, args.steps, max(args.warmup, 3), args.tp_prompt
     ctx = prompt_len + 2 * (steps + warmup) + 64
@@ -407,12 +414,14 @@ def run_tensor_parallel(args):
     time.sleep(0.3)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = dev.launch_count
     t0 = time.time()
     e0.record(stream)
     toks = m.generate_greedy(last, steps)
     e1.record(stream)
     barrier()
     t1 = time.time()
+    launches = dev.launch_count - launches0
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop(t0, t1)
     # the all-reduce alone: the payload of one decode step's sums, back to back
@@ -446,7 +455,10 @@ def run_tensor_parallel(args):
             "config": {"workload": f"llama3-70b-shaped all-Q4_K greedy decode, TP={world}, batch {batch}, prompt "
                                    f"{prompt_len}, {steps} steps" + ("" if cfg["n_layer"] == 80 else
                                                                      f" (REDUCED: {cfg['n_layer']} layers)"),
-                       "parallelism": f"tp{world}"},
+                       "parallelism": f"tp{world}",
+                       "step": ("kernel per operation, NCCL all-reduce" if args.tp_nccl or world == 1 else
+                                "one persistent kernel per rank, sums over NVLink peer memory inside it")},
+            "gpu_launches": int(launches),
             "per_gpu": {"weight_bytes_per_step": local_bytes, "kv_bytes_per_step": kv, "achieved_gbs": gbs,
                         "peak": peak, "peak_source": which, "frac": gbs / peak},
             "all_reduce": None if ar_us is None else {"per_step": 2 * cfg["n_layer"], "payload_bytes": batch * e * 4,
@@ -705,6 +717,7 @@ def main():
     ap.add_argument("--tp", action="store_true",
                     help="70B-shaped model split over the ranks (tensor parallel) instead of 8B replicas")
     ap.add_argument("--tp-prompt", type=int, default=2048)
+    ap.add_argument("--tp-nccl", action="store_true", help="with --tp: keep the decode step on NCCL all-reduces")
     ap.add_argument("--gemv-reps", type=int, default=8)
     ap.add_argument("--sweep", action="store_true",
                     help="per-kernel table over the other product shapes and decode attention (several JSON lines)")

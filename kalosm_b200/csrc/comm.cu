@@ -2,9 +2,12 @@
 // layer and the greedy-token exchange of the sharded output head.
 //
 // The reference has no multi-GPU path; the partition follows the usual split of a transformer
-// layer: q/k/v/gate/up by rows, o/down by K, one sum per pair (see tp_all_reduce in llama.cu).
+// layer: q/k/v/gate/up by rows, o/down by K, one sum per pair (run_forward in llama.cu).
 // NCCL is loaded at run time (dlopen of libnccl.so.2) so that single-GPU users of the library
 // do not need it; every entry point fails with FB200_ERR_NCCL when it is missing.
+// The communicator also owns the exchange buffer of the fused decode kernel: made here, exported
+// as a CUDA IPC handle and mapped by every peer, so that the kernel can store partial rows into
+// the peers' memory and poll arrival words without any library call (fused_step.cuh).
 #include <dlfcn.h>
 #include <nccl.h>
 
