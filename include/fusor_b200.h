@@ -282,6 +282,10 @@ FB200_API int fb200_comm_all_reduce_sum(fb200_comm* c, float* buf_dev, size_t n)
 #define FB200_IPC_HANDLE_BYTES 64
 FB200_API int fb200_comm_exchange_handle(fb200_comm* c, size_t row_floats, uint8_t* handle_out, size_t handle_bytes);
 FB200_API int fb200_comm_exchange_attach(fb200_comm* c, const uint8_t* handles, size_t handle_bytes);
+/* Diagnostic: runs the bounded arrival wait of the peer exchange on a word that nothing sets.
+ * Returns FB200_ERR_TIMEOUT after poll_limit polls and leaves that code in the handle's status
+ * word, exactly as a peer that never arrives would; the context stays usable. */
+FB200_API int fb200_exchange_wait_check(fb200_device* dev, int poll_limit);
 /* Must precede fb200_llama_set_tensor. The communicator must outlive the model. */
 FB200_API int fb200_llama_set_tensor_parallel(fb200_llama* m, fb200_comm* comm);
 

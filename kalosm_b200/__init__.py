@@ -67,7 +67,7 @@ EXPORTS = [
     "fb200_llama_set_tensor", "fb200_llama_reset", "fb200_llama_position", "fb200_llama_forward",
     "fb200_llama_generate_greedy", "fb200_llama_logits_dev", "fb200_llama_set_tensor_parallel",
     "fb200_comm_unique_id", "fb200_comm_create", "fb200_comm_destroy", "fb200_comm_all_reduce_sum",
-    "fb200_comm_exchange_handle", "fb200_comm_exchange_attach",
+    "fb200_comm_exchange_handle", "fb200_comm_exchange_attach", "fb200_exchange_wait_check",
 ]
 
 _lib = None
@@ -136,6 +136,7 @@ def load_library():
         "fb200_comm_all_reduce_sum": (i32, [vp, vp, sz]),
         "fb200_comm_exchange_handle": (i32, [vp, sz, vp, sz]),
         "fb200_comm_exchange_attach": (i32, [vp, vp, sz]),
+        "fb200_exchange_wait_check": (i32, [vp, i32]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -265,6 +266,11 @@ class Device:
         s = C.c_int()
         self._check(self.lib.fb200_device_status(self.h, C.byref(s)))
         return s.value
+
+    def exchange_wait_check(self, poll_limit: int) -> None:
+        """Bounded arrival wait of the tensor-parallel peer exchange on a word nothing sets: raises
+        FusorError(ERR_TIMEOUT) after `poll_limit` polls and leaves the code in `status()`."""
+        self._check(self.lib.fb200_exchange_wait_check(self.h, poll_limit))
 
     def tensor(self, array, dtype=None) -> Tensor:
         return Tensor.from_slice(self, array, dtype)

@@ -90,11 +90,18 @@ bool fb200_comm_take_exchange(fb200_comm* c, int row_floats, unsigned count, fb2
     out->flags[r] = reinterpret_cast<unsigned*>(c->peer[r] + flags_off);
   }
   out->world = c->size; out->me = c->rank; out->stride = c->stride;
+  out->poll_limit = FB200_XCHG_POLL_LIMIT;
   out->epoch_base = c->epoch;
   c->epoch += count;
   return true;
 }
 bool fb200_comm_exchange_ready(const fb200_comm* c, int row_floats) { return c->attached && row_floats <= c->stride; }
+
+namespace {
+__global__ void wait_check_kernel(const unsigned* word, int poll_limit, int* status) {
+  if (!fb200_wait_arrival(word, 1u, poll_limit, status)) atomicExch(status, FB200_ERR_TIMEOUT);
+}
+}  // namespace
 
 int fb200_comm_rank(const fb200_comm* c) { return c->rank; }
 int fb200_comm_size(const fb200_comm* c) { return c->size; }
@@ -165,6 +172,23 @@ int fb200_comm_exchange_attach(fb200_comm* c, const uint8_t* handles, size_t han
   }
   c->attached = true;
   return FB200_OK;
+}
+
+int fb200_exchange_wait_check(fb200_device* dev, int poll_limit) {
+  if (!dev || poll_limit < 1) return FB200_ERR_INVALID_ARGUMENT;
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  unsigned* word = nullptr;
+  FB_CUDA(dev, cudaMalloc(&word, 4));
+  FB_CUDA(dev, cudaMemsetAsync(word, 0, 4, dev->stream));
+  wait_check_kernel<<<1, 1, 0, dev->stream>>>(word, poll_limit, dev->status);
+  cudaError_t e = cudaStreamSynchronize(dev->stream);
+  cudaFree(word);
+  if (e != cudaSuccess) return fb200_fail(dev, FB200_ERR_CUDA, "wait check: %s", cudaGetErrorString(e));
+  int st = 0;
+  FB_CUDA(dev, cudaMemcpy(&st, dev->status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (st == FB200_ERR_TIMEOUT) return fb200_fail(dev, FB200_ERR_TIMEOUT, "the arrival word was not set within %d polls", poll_limit);
+  return st;
 }
 
 int fb200_comm_destroy(fb200_comm* c) {

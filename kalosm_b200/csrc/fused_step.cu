@@ -203,19 +203,15 @@ struct EpiCtx {
   int xs_off;                  // float offset of this rank's slot for the current epoch
 };
 
-__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 __device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 // Tells every peer that this rank's contribution to exchange `epoch` is complete in its buffer
 // (called by one thread after the grid barrier that followed the writes), then waits until every
-// peer has said the same here. Bounded: after 2^22 polls (or when another wait has already given
-// up) the time-out is recorded and the kernel carries on with whatever is there.
+// peer has said the same here. Bounded (fb200_wait_arrival): after poll_limit polls, or when
+// another wait has already given up, the time-out is recorded and the kernel carries on with
+// whatever is there.
 __device__ __forceinline__ void xchg_signal_and_wait(const FusedArgs& A, unsigned epoch, bool signal) {
   const fb200_fused_xchg& X = A.x;
   if (signal) {
@@ -225,13 +221,10 @@ __device__ __forceinline__ void xchg_signal_and_wait(const FusedArgs& A, unsigne
   }
   for (int r = 0; r < X.world; ++r) {
     if (r == X.me) continue;
-    bool ok = false;
-    for (int it = 0; it < (1 << 22); ++it) {
-      if ((int)(ld_acquire_sys_u32(X.flags[X.me] + r) - epoch) >= 0) { ok = true; break; }
-      if ((it & 1023) == 1023 && __ldcg(A.status) != 0) break;
-      __nanosleep(64);
+    if (!fb200_wait_arrival(X.flags[X.me] + r, epoch, X.poll_limit, A.status)) {
+      atomicExch(A.status, FB200_ERR_TIMEOUT);
+      break;
     }
-    if (!ok) { atomicExch(A.status, FB200_ERR_TIMEOUT); break; }
   }
 }
 

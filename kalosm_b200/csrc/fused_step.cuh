@@ -35,7 +35,26 @@ struct fb200_fused_xchg {
   unsigned epoch_base;
   int per_step;
   unsigned id_base;  // first global token id of this rank's rows of the output head
+  int poll_limit;    // polls of one arrival word before the wait gives up
 };
+
+constexpr int FB200_XCHG_POLL_LIMIT = 1 << 22;
+
+#ifdef __CUDACC__
+// Bounded wait for an arrival word (written by a peer with release at system scope) to reach
+// `epoch`. Gives up after `poll_limit` polls, or at once when another wait has already set the
+// status word; returns false then (the caller records FB200_ERR_TIMEOUT and carries on).
+__device__ __forceinline__ bool fb200_wait_arrival(const unsigned* word, unsigned epoch, int poll_limit, const int* status) {
+  for (int it = 0; it < poll_limit; ++it) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(word) : "memory");
+    if ((int)(v - epoch) >= 0) return true;
+    if ((it & 1023) == 1023 && __ldcg(status) != 0) return false;
+    __nanosleep(64);
+  }
+  return false;
+}
+#endif
 
 struct fb200_fused_seg {
   const uint8_t* w;  // tiled weight bytes

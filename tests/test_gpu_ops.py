@@ -195,3 +195,19 @@ def test_attention_masks_and_cache_capacity(dev):
     out = dev.flash_attention(dev.tensor(q), dev.tensor(k), dev.tensor(v), scale, skv=skv,
                               mask=dev.tensor(bk), mask_kind=kb.MASK_BATCH_KEY).as_slice()
     assert np.max(np.abs(out - O.attention(q, kf, vf, scale, mask=bk, mask_kind=1))) < 1e-3
+
+
+def test_peer_exchange_wait_is_bounded(dev):
+    # a peer that never arrives: the wait gives up after its poll limit, the handle's status word
+    # says so, and the GPU keeps working (no trap, no hang); a handle of its own keeps the
+    # session handle's status clean
+    other = kb.Device(0)
+    assert other.status() == 0
+    with pytest.raises(kb.FusorError) as e:
+        other.exchange_wait_check(4096)
+    assert e.value.code == kb.ERR_TIMEOUT
+    assert other.status() == kb.ERR_TIMEOUT
+    x = other.tensor(np.ones((2, 8), np.float32))
+    assert np.array_equal(x.as_slice(), np.ones((2, 8), np.float32))
+    other.close()
+    assert dev.status() == 0
