@@ -63,3 +63,26 @@ def build_models(dev, cfg, batch=1, seed=0, want_cpu=True, sigma=0.02, comm=None
             if cpu:
                 cpu.set_norm(nm, i if i < cfg["n_layer"] else -1, w)
     return gpu, cpu
+
+
+def write_checkpoint(path, cfg, seed=0, sigma=0.02):
+    """The same seeded model as build_models, as a GGUF file (kalosm_b200.gguf.write_gguf)."""
+    from kalosm_b200 import gguf
+    md = {"general.architecture": (gguf.STRING, "llama"), "llama.block_count": (gguf.U32, cfg["n_layer"]),
+          "llama.embedding_length": (gguf.U32, cfg["hidden"]), "llama.feed_forward_length": (gguf.U32, cfg["ffn"]),
+          "llama.attention.head_count": (gguf.U32, cfg["n_head"]),
+          "llama.attention.head_count_kv": (gguf.U32, cfg["n_kv_head"]),
+          "llama.attention.key_length": (gguf.U32, cfg["head_dim"]),
+          "llama.context_length": (gguf.U32, cfg["ctx"]),
+          "llama.attention.layer_norm_rms_epsilon": (gguf.F32, 1e-5), "llama.rope.freq_base": (gguf.F32, 500000.0)}
+    tensors = []
+    for j, (name, layer, ty, (n, k)) in enumerate(tensor_plan(cfg)):
+        full = f"{name}.weight" if layer < 0 else f"blk.{layer}.{name}.weight"
+        tensors.append((full, (n, k), ty, O.random_qweights(seed * 100003 + j, sigma, n * k, ty)))
+    rng = np.random.default_rng(seed + 77)
+    for i in range(cfg["n_layer"] + 1):
+        for nm in (("attn_norm", "ffn_norm") if i < cfg["n_layer"] else ("output_norm",)):
+            w = (1.0 + 0.02 * rng.standard_normal(cfg["hidden"])).astype(np.float32)
+            full = f"blk.{i}.{nm}.weight" if i < cfg["n_layer"] else "output_norm.weight"
+            tensors.append((full, (cfg["hidden"],), kb.F32, w))
+    gguf.write_gguf(path, md, tensors)

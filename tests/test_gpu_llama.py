@@ -5,7 +5,7 @@ import pytest
 import fixtures as F
 import kalosm_b200 as kb
 from gpu_util import dev  # noqa: F401
-from llama_util import build_models, tiny_cfg
+from llama_util import build_models, tiny_cfg, write_checkpoint
 from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -109,3 +109,20 @@ def test_decode_over_a_long_context(dev, head_dim, n_head, n_kv_head):
             break
         t = np.array([want], dtype=np.uint32)
     assert gpu.position == 291 + 5 + 6
+
+
+def test_model_loaded_from_a_gguf_file_equals_the_directly_built_one(dev, tmp_path):
+    # checkpoint -> GGUF file -> kalosm_b200.gguf.load_llama: same bytes on the device as setting
+    # the tensors one by one, so logits and greedy ids agree bit for bit
+    from kalosm_b200 import gguf
+    cfg = tiny_cfg()
+    path = tmp_path / "tiny.gguf"
+    write_checkpoint(path, cfg, seed=9)
+    direct, cpu = build_models(dev, cfg, batch=1, seed=9)
+    loaded = gguf.load_llama(dev, path, max_batch=1)
+    prompt = np.random.default_rng(10).integers(0, cfg["vocab"], size=(1, 7), dtype=np.uint32)
+    lg_a, nxt_a = direct.forward(prompt)
+    lg_b, nxt_b = loaded.forward(prompt)
+    assert np.array_equal(lg_a, lg_b) and np.array_equal(nxt_a, nxt_b)
+    assert F.rel_l2(lg_b, cpu.forward(prompt)) < 2e-3
+    assert np.array_equal(direct.generate_greedy(nxt_a, 8), loaded.generate_greedy(nxt_b, 8))
