@@ -19,6 +19,11 @@
 //    the NEXT product phase, so the weight stream continues across the grid barrier;
 //  * activations arrive packed (int8 limbs, per-16 scales and sums) and are copied to shared
 //    memory once per CTA; the per-tile-group math is that of the single-row kernel.
+// Tensor parallel (variants with XS = true): the ranks' kernels run side by side, one per GPU;
+// the o and down projections store their partial rows into every rank's exchange buffer (peer
+// memory over NVLink), arrival words written with release at system scope tell the peers, and
+// an XSUM phase adds the ranks' rows in rank order; the greedy key of the sharded output head
+// is exchanged the same way (fused_step.cuh: fb200_fused_xchg).
 // Everything another CTA wrote during the kernel is read through L2 (ld.global.cg).
 // All waits are bounded: a wait that gives up sets the device status word and the kernel runs to
 // its end without waiting again.
