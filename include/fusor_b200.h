@@ -67,8 +67,25 @@ FB200_API const char* fb200_last_error(const fb200_device* dev);
 /* Number of kernels this library has launched through the handle since creation. */
 FB200_API uint64_t fb200_launch_count(const fb200_device* dev);
 /* Device-side status word: 0 unless a kernel recorded a fault it recovered from (bounded
- * wait ran out, bad index skipped). Reading it synchronises the stream. */
+ * wait ran out, bad index skipped). Reading it synchronises the stream. While the word is set,
+ * every blocking entry point (fb200_device_synchronize, fb200_download, fb200_llama_forward,
+ * fb200_llama_generate_greedy, fb200_llama_generate_sampled) returns FB200_ERR_TIMEOUT after its
+ * synchronisation: the reference reports a failed dispatch when the result is read back
+ * (Tensor::as_slice, fusor-ml/fusor/src/lib.rs:364-368), this is the same point. */
 FB200_API int fb200_device_status(fb200_device* dev, int* status_out);
+/* Resets the status word to 0 after the caller has dealt with the failure (results produced while
+ * it was set are invalid; a tensor-parallel communicator that saw the time-out stays closed and
+ * has to be made again). */
+FB200_API int fb200_device_clear_status(fb200_device* dev);
+/* Scratch buffers of the handle (packed activations, normalised rows, host staging) replace the
+ * reference's BufferPool (fusor-ml/tile-ir-runtime/src/buffer_pool.rs:74-260). A budget of
+ * `bytes` (0 = unlimited; also FB200_SCRATCH_LIMIT in the environment at creation) makes a call
+ * that would grow them beyond it fail with FB200_ERR_CAPACITY instead of allocating. */
+FB200_API int fb200_device_set_scratch_limit(fb200_device* dev, size_t bytes);
+/* Poison mode (also FB200_POISON=1 at creation): freshly allocated scratch is filled with 0xFF
+ * bytes (NaN as f32 / f16), the analogue of the pool's poison fill (buffer_pool.rs:198-207,
+ * fusor/src/device.rs:113-118); a kernel that reads scratch nobody wrote then shows in its output. */
+FB200_API int fb200_device_set_poison(fb200_device* dev, int enable);
 
 /* ---- tensors: Tensor::from_slice / as_slice, fusor-ml/fusor/src/lib.rs:356-368 -----------------
  * Tensors are contiguous row-major device buffers; shapes travel as arguments. */
@@ -140,12 +157,19 @@ FB200_API int fb200_rms_norm_q_mat_mul(fb200_device* dev, const float* x_dev,
  * application that forbids allocation after initialisation -- call this instead. The scratch is
  * a fixed 4 MiB array inside the library image (every GPU that loads the library carries it
  * until the process exits); neither this function nor anything it calls allocates or frees
- * device or host memory.
+ * device or host memory through the CUDA allocator or the C/C++ heap (refusals write their text
+ * into fixed storage inside the handle).
  *   - y[M, N] = x[M, K] . W^T, 1 <= M <= 32, W of type Q4_0 / Q8_0 / Q4_K / Q6_K, no epilogue.
+ *   - Every row count, M = 1 included, runs the fp16 tensor-core kernel of the 2..32-row path
+ *     (11-bit operands, about 5e-4 relative L2 against fp32; fb200_q_mat_mul sends a single row to
+ *     its integer-limb kernel instead, which needs no scratch and is closer to fp32).
+ *   - Warm-up: the first call per device looks up the array's device address, and the first call
+ *     per (weight type, row bucket 1..8 / 9..16 / 17..32) sets that kernel variant's shared-memory
+ *     attribute and, under CUDA's lazy loading, loads its code. Make one call of every
+ *     combination you will use before entering the region that must not allocate, and before
+ *     any stream capture.
  *   - FB200_ERR_CAPACITY when M > 32 or when the packed activations (about 136 bytes per
  *     element of K for 17..32 rows, 68 for 9..16, 34 for 1..8) exceed the 4 MiB array.
- *   - The first call on a device looks up the array's device address; make that call before
- *     starting any stream capture.
  *   - All calls share the one array and it keeps the previous call's contents; each call
  *     rewrites everything it reads, so nothing needs clearing, but two calls whose kernels
  *     overlap on the GPU (different streams or device handles) race on it. Keep calls on one
@@ -194,6 +218,11 @@ FB200_API int fb200_kv_cache_create(fb200_device* dev, int batch, int n_kv_head,
 FB200_API int fb200_kv_cache_free(fb200_kv_cache* c);
 FB200_API int fb200_kv_cache_reset(fb200_kv_cache* c);
 FB200_API int fb200_kv_cache_len(const fb200_kv_cache* c, int* len_out, int* capacity_out);
+/* Drops the positions from `len` on (0 <= len <= current length): the tokens a session shares
+ * with its cache stay, the rest is recomputed. The reference trims its cache this way before it
+ * re-prefills (models/kalosm-llama/src/raw/mod.rs:769-793, TensorCache truncation in
+ * fusor-ml/fusor/src/cache/tensor_cache.rs:175-202). */
+FB200_API int fb200_kv_cache_truncate(fb200_kv_cache* c, int len);
 /* k, v f32 [B, Hkv, S, D]; rounded to fp16 and stored at positions len .. len + S. */
 FB200_API int fb200_kv_cache_append(fb200_kv_cache* c, const float* k_dev, const float* v_dev, int s);
 /* Device pointers of the fp16 K and V buffers ([B, Hkv, capacity, D]). */
@@ -238,6 +267,10 @@ FB200_API int fb200_llama_free(fb200_llama* m);
 FB200_API int fb200_llama_set_tensor(fb200_llama* m, int layer, int which, uint32_t ggml_type,
                            uint64_t n, uint64_t k, const void* bytes_host, size_t nbytes);
 FB200_API int fb200_llama_reset(fb200_llama* m);
+/* Rewinds the model's KV caches to the first `len` positions (0 <= len <= position): the next
+ * forward pass continues from there (raw/mod.rs:769-793 keeps the common prefix of the cached
+ * and the new tokens and re-runs the rest). */
+FB200_API int fb200_llama_truncate(fb200_llama* m, int len);
 FB200_API int fb200_llama_position(const fb200_llama* m, int* pos_out);
 /* tokens_host [batch, seq] u32. Runs the forward pass over `seq` new positions and writes the
  * logits of the last position, f32 [batch, vocab], to logits_host if not NULL, and the greedy

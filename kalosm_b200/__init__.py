@@ -56,15 +56,16 @@ class LlamaConfig(C.Structure):
 
 EXPORTS = [
     "fb200_device_create", "fb200_device_destroy", "fb200_device_synchronize", "fb200_last_error",
-    "fb200_launch_count", "fb200_device_status", "fb200_malloc", "fb200_free", "fb200_upload",
+    "fb200_launch_count", "fb200_device_status", "fb200_device_clear_status",
+    "fb200_device_set_scratch_limit", "fb200_device_set_poison", "fb200_malloc", "fb200_free", "fb200_upload",
     "fb200_download", "fb200_memset", "fb200_qmatrix_from_raw_bytes", "fb200_qmatrix_free",
     "fb200_qmatrix_shape", "fb200_qmatrix_ggml_type", "fb200_qmatrix_nbytes",
     "fb200_qmatrix_dequantize", "fb200_qmatrix_concat_rows", "fb200_q_mat_mul",
     "fb200_q_mat_mul_host", "fb200_q_mat_mul_noalloc", "fb200_rms_norm_q_mat_mul", "fb200_rms_norm", "fb200_silu_mul", "fb200_rope_tables",
     "fb200_rope_pair", "fb200_embedding_lookup", "fb200_argmax", "fb200_kv_cache_create",
-    "fb200_kv_cache_free", "fb200_kv_cache_reset", "fb200_kv_cache_len", "fb200_kv_cache_append",
+    "fb200_kv_cache_free", "fb200_kv_cache_reset", "fb200_kv_cache_truncate", "fb200_kv_cache_len", "fb200_kv_cache_append",
     "fb200_kv_cache_buffers", "fb200_flash_attention", "fb200_llama_create", "fb200_llama_free",
-    "fb200_llama_set_tensor", "fb200_llama_reset", "fb200_llama_position", "fb200_llama_forward",
+    "fb200_llama_set_tensor", "fb200_llama_reset", "fb200_llama_truncate", "fb200_llama_position", "fb200_llama_forward",
     "fb200_llama_generate_greedy", "fb200_llama_logits_dev", "fb200_llama_set_tensor_parallel",
     "fb200_comm_unique_id", "fb200_comm_create", "fb200_comm_destroy", "fb200_comm_all_reduce_sum",
     "fb200_comm_exchange_handle", "fb200_comm_exchange_attach", "fb200_exchange_wait_check",
@@ -91,6 +92,9 @@ def load_library():
         "fb200_last_error": (C.c_char_p, [vp]),
         "fb200_launch_count": (u64, [vp]),
         "fb200_device_status": (i32, [vp, C.POINTER(i32)]),
+        "fb200_device_clear_status": (i32, [vp]),
+        "fb200_device_set_scratch_limit": (i32, [vp, sz]),
+        "fb200_device_set_poison": (i32, [vp, i32]),
         "fb200_malloc": (i32, [vp, sz, pp]),
         "fb200_free": (i32, [vp, vp]),
         "fb200_upload": (i32, [vp, vp, vp, sz]),
@@ -116,6 +120,7 @@ def load_library():
         "fb200_kv_cache_create": (i32, [vp, i32, i32, i32, i32, pp]),
         "fb200_kv_cache_free": (i32, [vp]),
         "fb200_kv_cache_reset": (i32, [vp]),
+        "fb200_kv_cache_truncate": (i32, [vp, i32]),
         "fb200_kv_cache_len": (i32, [vp, C.POINTER(i32), C.POINTER(i32)]),
         "fb200_kv_cache_append": (i32, [vp, vp, vp, i32]),
         "fb200_kv_cache_buffers": (i32, [vp, pp, pp]),
@@ -125,6 +130,7 @@ def load_library():
         "fb200_llama_free": (i32, [vp]),
         "fb200_llama_set_tensor": (i32, [vp, i32, i32, u32, u64, u64, vp, sz]),
         "fb200_llama_reset": (i32, [vp]),
+        "fb200_llama_truncate": (i32, [vp, i32]),
         "fb200_llama_position": (i32, [vp, C.POINTER(i32)]),
         "fb200_llama_forward": (i32, [vp, vp, i32, i32, vp, vp]),
         "fb200_llama_generate_greedy": (i32, [vp, vp, i32, i32, vp]),
@@ -192,11 +198,21 @@ class Tensor:
         m = int(np.prod(self.shape[:-1], dtype=np.int64)) if len(self.shape) > 1 else 1
         n_out = n // 2 if epilogue == EPI_SWIGLU else n
         out_shape = (self.shape[:-1] if len(self.shape) > 1 else ()) + (n_out,)
+        for name, t in (("out", out), ("r1", r1), ("r2", r2)):
+            self._require_f32(name, t, m * n_out)
         y = out if out is not None else Tensor(self.device, out_shape, np.float32)
         ep = _Epilogue(epilogue, r1.ptr if r1 is not None else None, r2.ptr if r2 is not None else None)
         d = self.device
         d._check(d.lib.fb200_q_mat_mul(d.h, self.ptr, m, w.h, y.ptr, C.byref(ep)))
         return y
+
+    def _require_f32(self, name: str, t: Optional["Tensor"], elems: int) -> None:
+        """Refuses a caller-supplied buffer the library would otherwise write or read out of bounds."""
+        if t is None:
+            return
+        if t.dtype != np.float32 or t.nbytes < elems * 4 or t.device is not self.device:
+            raise FusorError(ERR_INVALID_SHAPE, f"{name} must be an f32 tensor of at least {elems} elements on the "
+                                                f"same device handle (got {t.dtype}, {t.nbytes} bytes)")
 
     def q_mat_mul_noalloc(self, w: "QMatrix", out: "Tensor") -> "Tensor":
         """self [M <= 32, K] . W^T into the caller's `out`, through the entry point that never
@@ -206,6 +222,7 @@ class Tensor:
         if k != w.shape[1]:
             raise FusorError(ERR_INVALID_SHAPE, f"lhs columns ({k}) != weight in_features ({w.shape[1]})")
         m = int(np.prod(self.shape[:-1], dtype=np.int64)) if len(self.shape) > 1 else 1
+        self._require_f32("out", out, m * w.shape[0])
         d = self.device
         d._check(d.lib.fb200_q_mat_mul_noalloc(d.h, self.ptr, m, w.h, out.ptr))
         return out
@@ -266,6 +283,18 @@ class Device:
         s = C.c_int()
         self._check(self.lib.fb200_device_status(self.h, C.byref(s)))
         return s.value
+
+    def clear_status(self) -> None:
+        """Resets the device status word after a reported time-out."""
+        self._check(self.lib.fb200_device_clear_status(self.h))
+
+    def set_scratch_limit(self, nbytes: int) -> None:
+        """Budget of the handle's scratch buffers (0 = unlimited): growing beyond it fails with ERR_CAPACITY."""
+        self._check(self.lib.fb200_device_set_scratch_limit(self.h, int(nbytes)))
+
+    def set_poison(self, enable: bool) -> None:
+        """Fill freshly allocated scratch with NaN bytes (debug aid)."""
+        self._check(self.lib.fb200_device_set_poison(self.h, 1 if enable else 0))
 
     def exchange_wait_check(self, poll_limit: int) -> None:
         """Bounded arrival wait of the tensor-parallel peer exchange on a word nothing sets: raises
@@ -439,6 +468,10 @@ class KvCache:
     def reset(self):
         self.device.lib.fb200_kv_cache_reset(self.h)
 
+    def truncate(self, length: int) -> None:
+        """Keeps the first `length` positions."""
+        self.device._check(self.device.lib.fb200_kv_cache_truncate(self.h, length))
+
     @property
     def current_seq_len(self) -> int:
         n, c = C.c_int(), C.c_int()
@@ -546,6 +579,10 @@ class Llama:
 
     def reset(self) -> None:
         self.device._check(self.device.lib.fb200_llama_reset(self.h))
+
+    def truncate(self, length: int) -> None:
+        """Rewinds the KV caches to the first `length` positions."""
+        self.device._check(self.device.lib.fb200_llama_truncate(self.h, length))
 
     @property
     def position(self) -> int:

@@ -17,16 +17,17 @@ int fb200_qgemv1(fb200_device* dev, const fb200_qmatrix* w, const float* x, cons
 int fb200_launch_rms_norm(fb200_device* dev, const float* x, const float* res, const float* w,
                           const float* b, float eps, size_t rows, size_t n, float* y);
 
-static thread_local std::string g_global_err;
+static thread_local char g_global_err[512] = {0};
 
+// Records the text of an error in fixed storage (the handle's, or a per-thread buffer when there
+// is no handle) and returns `code`. No heap allocation on any path, so entry points that promise
+// not to allocate may fail through it.
 int fb200_fail(fb200_device* dev, int code, const char* fmt, ...) {
-  char buf[512];
+  char* dst = dev ? dev->err : g_global_err;
   va_list ap;
   va_start(ap, fmt);
-  vsnprintf(buf, sizeof(buf), fmt, ap);
+  vsnprintf(dst, 512, fmt, ap);
   va_end(ap);
-  if (dev) dev->err = buf;
-  else g_global_err = buf;
   return code;
 }
 
@@ -36,17 +37,39 @@ int fb200_bind(fb200_device* dev) {
   return FB200_OK;
 }
 
+// Scratch buffers of a handle (packed activations, normalised rows, host staging) replace the
+// reference's BufferPool (fusor-ml/tile-ir-runtime/src/buffer_pool.rs:74-260): a buffer only ever
+// grows, its bytes count against the handle's optional budget, and in poison mode fresh scratch
+// is filled with 0xFF bytes (NaN as f32/f16), the analogue of the pool's poison fill
+// (buffer_pool.rs:198-207), so a kernel that reads scratch it never wrote shows up in the result.
 int fb200_ensure(fb200_device* dev, void** buf, size_t* cur, size_t bytes) {
   if (*cur >= bytes) return FB200_OK;
+  const size_t want = bytes + bytes / 4 + 4096;
+  if (dev->scratch_limit && dev->scratch_total - *cur + want > dev->scratch_limit)
+    return fb200_fail(dev, FB200_ERR_CAPACITY, "scratch: %zu more bytes would exceed the handle's budget of %zu (in use %zu)",
+                      want, dev->scratch_limit, dev->scratch_total);
   if (*buf) {
     FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
     FB_CUDA(dev, cudaFree(*buf));
+    dev->scratch_total -= *cur;
     *buf = nullptr;
     *cur = 0;
   }
-  size_t want = bytes + bytes / 4 + 4096;
+  dev->scratch_gen++;
   FB_CUDA(dev, cudaMalloc(buf, want));
   *cur = want;
+  dev->scratch_total += want;
+  if (dev->poison) FB_CUDA(dev, cudaMemsetAsync(*buf, 0xFF, want, dev->stream));
+  return FB200_OK;
+}
+
+int fb200_sync_check(fb200_device* dev) {
+  FB_CUDA(dev, cudaMemcpyAsync(dev->status_host, dev->status, sizeof(int), cudaMemcpyDeviceToHost, dev->stream));
+  FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  if (*dev->status_host != 0)
+    return fb200_fail(dev, FB200_ERR_TIMEOUT,
+                      "device status %d: a bounded wait inside a kernel gave up, results since then are invalid "
+                      "(fb200_device_clear_status resets the word)", *dev->status_host);
   return FB200_OK;
 }
 
@@ -77,11 +100,16 @@ int fb200_device_create(int ordinal, void* stream, fb200_device** out) {
   }
   cudaDeviceGetAttribute(&d->sm_count, cudaDevAttrMultiProcessorCount, ordinal);
   if (const char* e = getenv("FB200_PDL")) d->pdl = e[0] != '0';
+  if (const char* e = getenv("FB200_POISON")) d->poison = e[0] == '1';
+  if (const char* e = getenv("FB200_SCRATCH_LIMIT")) d->scratch_limit = (size_t)strtoull(e, nullptr, 10);
   if ((e = cudaMalloc(&d->status, sizeof(int))) != cudaSuccess ||
-      (e = cudaMemsetAsync(d->status, 0, sizeof(int), d->stream)) != cudaSuccess) {
+      (e = cudaMemsetAsync(d->status, 0, sizeof(int), d->stream)) != cudaSuccess ||
+      (e = cudaMallocHost(&d->status_host, sizeof(int))) != cudaSuccess) {
+    if (d->status) cudaFree(d->status);
     delete d;
     return fb200_fail(nullptr, FB200_ERR_CUDA, "status word: %s", cudaGetErrorString(e));
   }
+  *d->status_host = 0;
   *out = d;
   return FB200_OK;
 }
@@ -94,6 +122,7 @@ int fb200_device_destroy(fb200_device* dev) {
   if (dev->stage) cudaFree(dev->stage);
   if (dev->normed) cudaFree(dev->normed);
   if (dev->status) cudaFree(dev->status);
+  if (dev->status_host) cudaFreeHost(dev->status_host);
   if (dev->fused) cudaFree(dev->fused);
   if (dev->own_stream) cudaStreamDestroy(dev->stream);
   delete dev;
@@ -103,12 +132,32 @@ int fb200_device_destroy(fb200_device* dev) {
 int fb200_device_synchronize(fb200_device* dev) {
   int rc = fb200_bind(dev);
   if (rc) return rc;
+  return fb200_sync_check(dev);
+}
+
+int fb200_device_clear_status(fb200_device* dev) {
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  FB_CUDA(dev, cudaMemsetAsync(dev->status, 0, sizeof(int), dev->stream));
   FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  *dev->status_host = 0;
+  return FB200_OK;
+}
+
+int fb200_device_set_scratch_limit(fb200_device* dev, size_t bytes) {
+  if (!dev) return FB200_ERR_INVALID_ARGUMENT;
+  dev->scratch_limit = bytes;
+  return FB200_OK;
+}
+
+int fb200_device_set_poison(fb200_device* dev, int enable) {
+  if (!dev) return FB200_ERR_INVALID_ARGUMENT;
+  dev->poison = enable != 0;
   return FB200_OK;
 }
 
 const char* fb200_last_error(const fb200_device* dev) {
-  return dev ? dev->err.c_str() : g_global_err.c_str();
+  return dev ? dev->err : g_global_err;
 }
 
 uint64_t fb200_launch_count(const fb200_device* dev) { return dev ? dev->launches : 0; }
@@ -156,8 +205,7 @@ int fb200_download(fb200_device* dev, void* dst_host, const void* src_dev, size_
   if (rc) return rc;
   if (bytes)
     FB_CUDA(dev, cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, dev->stream));
-  FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
-  return FB200_OK;
+  return fb200_sync_check(dev);
 }
 
 int fb200_memset(fb200_device* dev, void* dst_dev, int value, size_t bytes) {

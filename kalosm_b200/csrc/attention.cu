@@ -440,6 +440,14 @@ int fb200_kv_cache_reset(fb200_kv_cache* c) {
   return FB200_OK;
 }
 
+int fb200_kv_cache_truncate(fb200_kv_cache* c, int len) {
+  if (!c) return FB200_ERR_INVALID_ARGUMENT;
+  if (len < 0 || len > c->len)
+    return fb200_fail(c->dev, FB200_ERR_INVALID_ARGUMENT, "kv cache: cannot truncate %d positions to %d", c->len, len);
+  c->len = len;  // rows past len stay allocated and are overwritten by the next append
+  return FB200_OK;
+}
+
 int fb200_kv_cache_len(const fb200_kv_cache* c, int* len_out, int* capacity_out) {
   if (!c) return FB200_ERR_INVALID_ARGUMENT;
   if (len_out) *len_out = c->len;

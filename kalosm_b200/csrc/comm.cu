@@ -11,6 +11,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -26,6 +27,9 @@ struct fb200_comm {
   int stride = 0;
   bool attached = false;
   unsigned epoch = 1;  // next exchange number; arrival words start at 0
+  // set after a wait inside a kernel gave up: the ranks' epochs and arrival words no longer agree,
+  // so every further collective on this communicator is refused until it is made again
+  bool broken = false;
 };
 
 namespace {
@@ -43,8 +47,11 @@ struct NcclApi {
 const NcclApi& nccl_api() {
   static NcclApi api = [] {
     NcclApi a;
-    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
-    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    // FB200_NCCL_LIB names the library to load instead of the default (a deployment with its own
+    // NCCL build; the tests point it at a missing file to see the FB200_ERR_NCCL path)
+    const char* named = getenv("FB200_NCCL_LIB");
+    void* h = named && named[0] ? dlopen(named, RTLD_NOW | RTLD_GLOBAL) : dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h && !(named && named[0])) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
     if (!h) return a;
     a.GetUniqueId = reinterpret_cast<decltype(a.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
     a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
@@ -62,11 +69,17 @@ int nccl_fail(fb200_device* dev, const char* what, ncclResult_t r) {
   return fb200_fail(dev, FB200_ERR_NCCL, "%s: %s", what, nccl_api().GetErrorString(r));
 }
 
+int broken_fail(fb200_comm* c) {
+  return fb200_fail(c->dev, FB200_ERR_TIMEOUT,
+                    "comm: an exchange timed out earlier; the ranks are out of step, destroy the communicator and make a new one");
+}
+
 }  // namespace
 
 // In-place sum over the ranks of buf[n] (f32), on the device handle's stream.
 int fb200_comm_all_reduce(fb200_comm* c, float* buf, size_t n) {
   if (c->size == 1 || n == 0) return FB200_OK;
+  if (c->broken) return broken_fail(c);
   ncclResult_t r = nccl_api().AllReduce(buf, buf, n, ncclFloat, ncclSum, c->nccl, c->dev->stream);
   if (r != ncclSuccess) return nccl_fail(c->dev, "all_reduce", r);
   return FB200_OK;
@@ -74,6 +87,7 @@ int fb200_comm_all_reduce(fb200_comm* c, float* buf, size_t n) {
 
 // out[size][bytes] = every rank's in[bytes].
 int fb200_comm_all_gather_bytes(fb200_comm* c, const void* in, void* out, size_t bytes) {
+  if (c->broken) return broken_fail(c);
   ncclResult_t r = nccl_api().AllGather(in, out, bytes, ncclChar, c->nccl, c->dev->stream);
   if (r != ncclSuccess) return nccl_fail(c->dev, "all_gather", r);
   return FB200_OK;
@@ -82,7 +96,7 @@ int fb200_comm_all_gather_bytes(fb200_comm* c, const void* in, void* out, size_t
 // Pointers of the peer exchange for a launch that performs `count` exchanges; false when the
 // peers have not been attached or a row does not fit a slot.
 bool fb200_comm_take_exchange(fb200_comm* c, int row_floats, unsigned count, fb200_fused_xchg* out) {
-  if (!c->attached || row_floats > c->stride) return false;
+  if (!c->attached || c->broken || row_floats > c->stride) return false;
   const size_t keys_off = (size_t)2 * c->size * c->stride * 4, flags_off = keys_off + (size_t)2 * c->size * 8;
   for (int r = 0; r < c->size; ++r) {
     out->data[r] = reinterpret_cast<float*>(c->peer[r]);
@@ -96,6 +110,7 @@ bool fb200_comm_take_exchange(fb200_comm* c, int row_floats, unsigned count, fb2
   return true;
 }
 bool fb200_comm_exchange_ready(const fb200_comm* c, int row_floats) { return c->attached && row_floats <= c->stride; }
+void fb200_comm_mark_broken(fb200_comm* c) { if (c) c->broken = true; }
 
 namespace {
 __global__ void wait_check_kernel(const unsigned* word, int poll_limit, int* status) {

@@ -18,7 +18,7 @@ struct fb200_device {
   bool own_stream = false;
   int sm_count = 148;
   bool pdl = true;  // launch with programmatic stream serialization (FB200_PDL=0 turns it off)
-  std::string err;
+  char err[512] = {0};  // text of the last error; fixed storage, so failing never allocates
   uint64_t launches = 0;
   // scratch for packed activations (fp16 fragments, group sums, row scales); grown on demand
   void* xpack = nullptr;
@@ -29,8 +29,15 @@ struct fb200_device {
   // staging for the *_host entry points
   void* stage = nullptr;
   size_t stage_bytes = 0;
-  // device status word (set by kernels that recover from a fault)
+  // device status word (set by kernels that recover from a fault) and its pinned host mirror
   int* status = nullptr;
+  int* status_host = nullptr;
+  // scratch accounting: bytes currently held by the buffers above, optional cap (0 = none),
+  // generation (bumped whenever a scratch buffer moves, so that captured graphs which recorded
+  // its address know they are stale), poison mode (new scratch is filled with 0xFF bytes = NaN)
+  size_t scratch_total = 0, scratch_limit = 0;
+  uint64_t scratch_gen = 0;
+  bool poison = false;
   // scratch of the fused decode-step kernel: grid barrier word, split-unit partials, counters
   void* fused = nullptr;
   size_t fused_bytes = 0;
@@ -94,6 +101,9 @@ inline int fb200_launch(fb200_device* dev, void (*kern)(KArgs...), dim3 grid, di
 
 // Makes the handle's device current for the calling thread.
 int fb200_bind(fb200_device* dev);
+// Synchronises the handle's stream and reads the device status word with it: FB200_ERR_TIMEOUT
+// (and the text of fb200_last_error) when a kernel recorded a wait that gave up, else FB200_OK.
+int fb200_sync_check(fb200_device* dev);
 // Ensures a scratch buffer of at least `bytes` (never shrinks).
 int fb200_ensure(fb200_device* dev, void** buf, size_t* cur, size_t bytes);
 

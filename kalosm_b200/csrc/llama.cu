@@ -40,6 +40,7 @@ int fb200_comm_size(const fb200_comm* c);
 fb200_device* fb200_comm_device(const fb200_comm* c);
 bool fb200_comm_take_exchange(fb200_comm* c, int row_floats, unsigned count, fb200_fused_xchg* out);
 bool fb200_comm_exchange_ready(const fb200_comm* c, int row_floats);
+void fb200_comm_mark_broken(fb200_comm* c);
 
 namespace {
 
@@ -149,6 +150,7 @@ struct fb200_llama {
   cudaGraphExec_t graph_exec = nullptr;
   int graph_batch = 0;
   uint64_t graph_kernels = 0;  // kernels inside the captured step
+  uint64_t graph_gen = 0;      // the handle's scratch generation the capture recorded addresses of
   // single-sequence step as one persistent kernel: its program (host and device copies)
   bool fused_enabled = true;   // FB200_FUSED=0 keeps the multi-kernel step
   bool fused_valid = false;    // the program matches the current buffers
@@ -398,7 +400,7 @@ int run_fused(fb200_llama* m, int steps, bool record) {
     if (m->tp_size > 1) {
       const int per_step = 2 * m->cfg.n_layer + 1;
       if (!fb200_comm_take_exchange(m->comm, m->cfg.hidden, (unsigned)(n * per_step), &xs))
-        return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "llama: the peer exchange went away");
+        return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "llama: the peer exchange is not available (detached, or closed after a time-out)");
       xs.per_step = per_step;
       xs.id_base = (unsigned)(m->tp_rank * m->vocab_local);
     }
@@ -563,8 +565,11 @@ int launch_advance(fb200_llama* m, int batch, int advance, bool record) {
 
 // Captures embed -> layers -> logits -> argmax -> advance for one token per batch row.
 int ensure_graph(fb200_llama* m, int batch) {
-  if (m->graph_exec && m->graph_batch == batch) return FB200_OK;
   fb200_device* dev = m->dev;
+  // The captured kernels hold the addresses of the handle's shared scratch buffers (packed
+  // activations, normalised rows). Another model or a larger product on the same handle may have
+  // moved them since: the generation counter tells, and the step is captured again.
+  if (m->graph_exec && m->graph_batch == batch && m->graph_gen == dev->scratch_gen) return FB200_OK;
   if (m->graph_exec) { cudaGraphExecDestroy(m->graph_exec); m->graph_exec = nullptr; }
   // make sure every lazily grown scratch buffer already has its final size
   int rc = run_forward(m, batch, 1);
@@ -585,7 +590,17 @@ int ensure_graph(fb200_llama* m, int batch) {
   cudaGraphDestroy(graph);
   if (e != cudaSuccess) return fb200_fail(dev, FB200_ERR_CUDA, "graph instantiate: %s", cudaGetErrorString(e));
   m->graph_batch = batch;
+  m->graph_gen = dev->scratch_gen;
   return FB200_OK;
+}
+
+// After a blocking call's work is enqueued: synchronise and surface a recorded time-out. Under
+// tensor parallelism a time-out leaves the ranks' exchange epochs out of step, so the
+// communicator is closed for further use.
+int finish_blocking(fb200_llama* m) {
+  const int rc = fb200_sync_check(m->dev);
+  if (rc == FB200_ERR_TIMEOUT && m->comm) fb200_comm_mark_broken(m->comm);
+  return rc;
 }
 
 }  // namespace
@@ -758,6 +773,20 @@ int fb200_llama_reset(fb200_llama* m) {
   return FB200_OK;
 }
 
+int fb200_llama_truncate(fb200_llama* m, int len) {
+  if (!m) return FB200_ERR_INVALID_ARGUMENT;
+  fb200_device* dev = m->dev;
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  if (len < 0 || len > m->pos)
+    return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "llama: cannot truncate %d positions to %d", m->pos, len);
+  // the caches keep their rows; positions >= len are overwritten as the sequence grows again
+  m->pos = len;
+  FB_CUDA(dev, cudaMemcpyAsync(m->pos_dev, &m->pos, 4, cudaMemcpyHostToDevice, dev->stream));
+  FB_CUDA(dev, cudaStreamSynchronize(dev->stream));  // the copy reads a member that may change right after
+  return FB200_OK;
+}
+
 int fb200_llama_position(const fb200_llama* m, int* pos_out) {
   if (!m || !pos_out) return FB200_ERR_INVALID_ARGUMENT;
   *pos_out = m->pos;
@@ -784,7 +813,7 @@ int fb200_llama_forward(fb200_llama* m, const uint32_t* tokens_host, int batch, 
     if ((rc = run_fused(m, 1, false))) return rc;
   } else if (seq == 1) {
     // single-token step: replay the captured graph (capture leaves the position untouched)
-    if (!m->graph_exec || m->graph_batch != batch) {
+    if (!m->graph_exec || m->graph_batch != batch || m->graph_gen != dev->scratch_gen) {
       FB_CUDA(dev, cudaMemcpyAsync(m->ids, tokens_host, rows * 4, cudaMemcpyHostToDevice, dev->stream));
       if ((rc = ensure_graph(m, batch))) return rc;
     }
@@ -801,8 +830,7 @@ int fb200_llama_forward(fb200_llama* m, const uint32_t* tokens_host, int batch, 
     FB_CUDA(dev, cudaMemcpyAsync(logits_host, m->logits, (size_t)batch * m->vocab_local * 4, cudaMemcpyDeviceToHost, dev->stream));
   if (next_host)
     FB_CUDA(dev, cudaMemcpyAsync(next_host, m->next, (size_t)batch * 4, cudaMemcpyDeviceToHost, dev->stream));
-  FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
-  return FB200_OK;
+  return finish_blocking(m);
 }
 
 int fb200_llama_generate_greedy(fb200_llama* m, const uint32_t* tokens_host, int batch, int steps,
@@ -849,7 +877,7 @@ int fb200_llama_generate_greedy(fb200_llama* m, const uint32_t* tokens_host, int
   // hist is [batch, hist_cap]; gather the first `steps` columns
   std::vector<uint32_t> tmp((size_t)batch * m->hist_cap);
   FB_CUDA(dev, cudaMemcpyAsync(tmp.data(), m->hist, tmp.size() * 4, cudaMemcpyDeviceToHost, dev->stream));
-  FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  if ((rc = finish_blocking(m))) return rc;
   for (int b = 0; b < batch; ++b)
     std::memcpy(out_host + (size_t)b * steps, tmp.data() + (size_t)b * m->hist_cap, (size_t)steps * 4);
   return FB200_OK;

@@ -20,6 +20,7 @@
 // Replaces the reference's qgemv kernels (fusor-ml/tile-ir-kernels/src/kernels/qgemv.rs:356-678,
 // qgemv_q6k.rs:84-385) and their SwiGLU / residual epilogues
 // (fusor-ml/core/src/quantized/matmul/mod.rs:435-439, 666-722).
+#include <atomic>
 #include <cstdlib>
 
 #include "qgemv_common.cuh"
@@ -981,8 +982,9 @@ static __device__ __align__(256) uint8_t g_static_xpack[FB200_STATIC_SCRATCH_BYT
 namespace {
 // Device address of g_static_xpack per device ordinal. In host code the array's name is only a
 // handle for the runtime; the address a kernel can use comes from cudaGetSymbolAddress, asked
-// once per device with that device current.
-void* g_static_xpack_addr[64] = {nullptr};
+// once per device with that device current. Atomic because two handles of one device may be
+// driven by two host threads (both would store the same address).
+std::atomic<void*> g_static_xpack_addr[64];
 }  // namespace
 
 extern "C" int fb200_q_mat_mul_noalloc(fb200_device* dev, const float* x_dev, size_t m,
@@ -1011,7 +1013,7 @@ extern "C" int fb200_q_mat_mul_noalloc(fb200_device* dev, const float* x_dev, si
                       "q_mat_mul_noalloc: %zu rows x K = %llu need %zu bytes of packed activations, the "
                       "built-in scratch holds %zu",
                       m, (unsigned long long)w->k, need, (size_t)FB200_STATIC_SCRATCH_BYTES);
-  void*& scratch = g_static_xpack_addr[dev->ordinal];
+  void* scratch = g_static_xpack_addr[dev->ordinal].load(std::memory_order_acquire);
   if (!scratch) {
     // first call on this device: resolve the array's device address (device is current)
     void* p = nullptr;
@@ -1019,6 +1021,7 @@ extern "C" int fb200_q_mat_mul_noalloc(fb200_device* dev, const float* x_dev, si
     if (e != cudaSuccess || !p)
       return fb200_fail(dev, FB200_ERR_CUDA, "q_mat_mul_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
     scratch = p;
+    g_static_xpack_addr[dev->ordinal].store(p, std::memory_order_release);
   }
   // Nothing in the scratch has to start at zero: the pack kernel rewrites every byte the
   // product kernel reads (limbs of padded rows are never loaded, their sums are written as 0).

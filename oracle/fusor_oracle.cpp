@@ -883,6 +883,15 @@ ORACLE_API void oracle_llama_reset(void* h) {
 
 ORACLE_API int oracle_llama_pos(void* h) { return ((Llama*)h)->pos; }
 
+// Keeps the first `len` cached positions (the reference trims its caches to the common prefix of
+// cached and new tokens and re-runs the rest, models/kalosm-llama/src/raw/mod.rs:769-793).
+ORACLE_API int oracle_llama_truncate(void* h, int len) {
+  Llama* m = (Llama*)h;
+  if (len < 0 || len > m->pos) return -1;
+  m->pos = len;
+  return 0;
+}
+
 namespace {
 
 void qmm(const QMat& w, const float* x, size_t m, float* y) {

@@ -65,6 +65,7 @@ def lib():
             "oracle_llama_set_norm": (i32, [vp, i32, i32, f32p, sz]),
             "oracle_llama_reset": (None, [vp]),
             "oracle_llama_pos": (i32, [vp]),
+            "oracle_llama_truncate": (i32, [vp, i32]),
             "oracle_llama_forward": (i32, [vp, u32p, i32, f32p]),
         }
         for name, (res, args) in sigs.items():
@@ -231,6 +232,10 @@ class Llama:
 
     def reset(self):
         lib().oracle_llama_reset(self.h)
+
+    def truncate(self, length):
+        if lib().oracle_llama_truncate(self.h, length):
+            raise ValueError(f"cannot truncate {self.pos} positions to {length}")
 
     @property
     def pos(self):

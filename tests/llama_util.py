@@ -22,7 +22,7 @@ def llama3_8b_cfg(ctx=1024):
 
 def tensor_plan(cfg):
     """(name, which_layer, ggml type, [N, K]) in Q4_K_M style: Q4_K body, Q6_K for attn_v,
-    ffn_down and the output head (BASELINE configs[3])."""
+    ffn_down and the output head."""
     e, f = cfg["hidden"], cfg["ffn"]
     qd, kvd = cfg["n_head"] * cfg["head_dim"], cfg["n_kv_head"] * cfg["head_dim"]
     plan = [("token_embd", -1, O.Q4K, (cfg["vocab"], e)), ("output", -1, O.Q6K, (cfg["vocab"], e))]
@@ -39,8 +39,10 @@ ORACLE_NAMES = {"token_embd": "token_embd", "output": "output", "attn_q": "wq", 
                 "ffn_down": "down"}
 
 
-def build_models(dev, cfg, batch=1, seed=0, want_cpu=True, sigma=0.02, comm=None):
-    """With `comm` the GPU model is this rank's shard of the same (whole) seeded weights."""
+def build_models(dev, cfg, batch=1, seed=0, want_cpu=True, sigma=0.02, comm=None, tied=False):
+    """With `comm` the GPU model is this rank's shard of the same (whole) seeded weights. With
+    `tied` the GPU model gets no output head and must fall back to the embedding matrix
+    (models/kalosm-llama/src/raw/mod.rs:480-486), as the oracle does when it has no head."""
     gpu = kb.Llama(dev, n_layer=cfg["n_layer"], hidden=cfg["hidden"], ffn=cfg["ffn"],
                    n_head=cfg["n_head"], n_kv_head=cfg["n_kv_head"], head_dim=cfg["head_dim"],
                    vocab=cfg["vocab"], max_seq_len=cfg["ctx"], max_batch=batch, comm=comm)
@@ -51,6 +53,8 @@ def build_models(dev, cfg, batch=1, seed=0, want_cpu=True, sigma=0.02, comm=None
                       cfg["head_dim"], cfg["vocab"], cfg["ctx"], batch=batch, kv_f16=True)
     for j, (name, layer, ty, (n, k)) in enumerate(tensor_plan(cfg)):
         raw = O.random_qweights(seed * 100003 + j, sigma, n * k, ty)
+        if tied and name == "output":
+            continue
         part, part_shape = tp.shard(name, raw, ty, (n, k), rank, size)
         gpu.set_tensor(name, layer, ty, part_shape, part)
         if cpu:

@@ -5,7 +5,7 @@ import pytest
 import fixtures as F
 import kalosm_b200 as kb
 from gpu_util import dev  # noqa: F401
-from llama_util import build_models, tiny_cfg, write_checkpoint
+from llama_util import build_models, llama3_8b_cfg, tiny_cfg, write_checkpoint
 from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -126,3 +126,91 @@ def test_model_loaded_from_a_gguf_file_equals_the_directly_built_one(dev, tmp_pa
     assert np.array_equal(lg_a, lg_b) and np.array_equal(nxt_a, nxt_b)
     assert F.rel_l2(lg_b, cpu.forward(prompt)) < 2e-3
     assert np.array_equal(direct.generate_greedy(nxt_a, 8), loaded.generate_greedy(nxt_b, 8))
+
+
+def test_decoder_at_llama3_8b_widths(dev):
+    # the program the benchmark times, two layers deep: hidden 4096, FFN 14336, 32/8 heads of 128,
+    # vocabulary 128256, Q4_K body with Q6_K attn_v / ffn_down / output head. Checks the prompt
+    # pass, single steps through forward() (one fused launch per step) and 32 greedy ids out of
+    # one generate_greedy launch (the persistent kernel running 32 steps) against the oracle.
+    cfg = dict(llama3_8b_cfg(ctx=256), n_layer=2)
+    gpu, cpu = build_models(dev, cfg, batch=1, seed=7)
+    rng = np.random.default_rng(8)
+    prompt = rng.integers(0, cfg["vocab"], size=(1, 64), dtype=np.uint32)
+    lg, nxt = gpu.forward(prompt)
+    lo = cpu.forward(prompt)
+    assert lg.shape == (1, cfg["vocab"])
+    assert F.rel_l2(lg, lo) < 2e-3, F.rel_l2(lg, lo)
+    tok = np.array([O.top_k(lo[0], 1)[0][0]], dtype=np.uint32)
+    assert nxt[0] == tok[0] or _margin(lo)[0] < 4 * np.max(np.abs(lg - lo))
+    for step in range(6):
+        lo = cpu.forward(tok[:, None])
+        lg, nxt = gpu.forward(tok[:, None])
+        err = np.max(np.abs(lg - lo))
+        assert F.rel_l2(lg, lo) < 2e-3, (step, F.rel_l2(lg, lo))
+        want = O.top_k(lo[0], 1)[0][0]
+        assert nxt[0] == want or _margin(lo)[0] < 4 * err, (step, nxt[0], want)
+        tok = np.array([want], dtype=np.uint32)
+    first = tok.copy()
+    gpu_tokens = gpu.generate_greedy(first, 32)[0]
+    assert dev.status() == 0
+    t = first.copy()
+    for step in range(32):
+        lo = cpu.forward(t[:, None])
+        want = O.top_k(lo[0], 1)[0][0]
+        if gpu_tokens[step] != want:
+            # an undecidable step (top-1 / top-2 closer than the logit error) ends the comparison
+            assert _margin(lo)[0] < 2e-3 * np.abs(lo).max(), (step, _margin(lo)[0])
+            assert step > 8, step
+            break
+        t = np.array([want], dtype=np.uint32)
+    assert gpu.position == 64 + 6 + 32
+
+
+def test_tied_embeddings(dev):
+    # no output tensor: the head falls back to token_embd (models/kalosm-llama/src/raw/mod.rs:480-486)
+    cfg = tiny_cfg()
+    gpu, cpu = build_models(dev, cfg, batch=1, seed=21, tied=True)
+    prompt = np.random.default_rng(22).integers(0, cfg["vocab"], size=(1, 7), dtype=np.uint32)
+    lg, nxt = gpu.forward(prompt)
+    lo = cpu.forward(prompt)
+    assert F.rel_l2(lg, lo) < 2e-3
+    tok = np.array([O.top_k(lo[0], 1)[0][0]], dtype=np.uint32)
+    for _ in range(3):
+        lo = cpu.forward(tok[:, None])
+        lg, _ = gpu.forward(tok[:, None])
+        assert F.rel_l2(lg, lo) < 2e-3
+        tok = np.array([O.top_k(lo[0], 1)[0][0]], dtype=np.uint32)
+
+
+def test_captured_step_survives_scratch_growth(dev):
+    # a multi-sequence decode step is a captured CUDA graph that recorded the address of the
+    # handle's packed-activation scratch; a larger product on the same handle moves that scratch.
+    # The next step must notice and run on the new buffer (compared with the oracle).
+    own = kb.Device(0)
+    cfg = tiny_cfg()
+    gpu, cpu = build_models(own, cfg, batch=2, seed=31)
+    rng = np.random.default_rng(32)
+    prompt = rng.integers(0, cfg["vocab"], size=(2, 5), dtype=np.uint32)
+    gpu.forward(prompt)
+    lo = cpu.forward(prompt)
+    tok = np.array([O.top_k(lo[b], 1)[0][0] for b in range(2)], dtype=np.uint32)
+    lg, _ = gpu.forward(tok[:, None])          # captures the graph
+    lo = cpu.forward(tok[:, None])
+    assert F.rel_l2(lg, lo) < 2e-3
+    # 32 rows of K = 16384: far more packed activations than the tiny model ever needed
+    ty, n, k = O.Q4K, 32, 16384
+    raw = O.random_qweights(5, 0.02, n * k, ty)
+    w = kb.QMatrix.from_raw_bytes(own, (n, k), raw, ty)
+    x = rng.standard_normal((32, k)).astype(np.float32)
+    y = own.tensor(x).q_mat_mul(w).as_slice()
+    assert F.rel_l2(y, O.q_mat_mul(x, raw, ty, n, k)) < 2e-3
+    for _ in range(2):
+        tok = np.array([O.top_k(lo[b], 1)[0][0] for b in range(2)], dtype=np.uint32)
+        lg, _ = gpu.forward(tok[:, None])
+        lo = cpu.forward(tok[:, None])
+        assert F.rel_l2(lg, lo) < 2e-3
+    assert own.status() == 0
+    gpu.free()
+    w.free()
+    own.close()

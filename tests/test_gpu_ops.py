@@ -175,6 +175,43 @@ def test_prefill_attention_tensor_cores(dev, shape):
     assert np.array_equal(out, dev.flash_attention(qt, kt, vt, scale, skv=skv, mask_kind=kind).as_slice())
 
 
+@pytest.mark.parametrize("s", [2048, 8192])
+def test_prefill_attention_long_causal(dev, s):
+    # causal prefill at the long sequence lengths of the sweep (32 query heads, 8 KV heads, head
+    # size 128). Row i of a causal pass is the unmasked attention of that one query over keys
+    # 0..i, which is how the oracle checks a sample of rows without an S x S score matrix.
+    b, h, hkv, d = 1, 32, 8, 128
+    rng = np.random.default_rng(s)
+    q = rng.standard_normal((b, h, s, d), dtype=np.float32)
+    k = rng.standard_normal((b, hkv, s, d), dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal((b, hkv, s, d), dtype=np.float32).astype(np.float16)
+    scale = float(1.0 / np.sqrt(d))
+    out = dev.flash_attention(dev.tensor(q), dev.tensor(k), dev.tensor(v), scale, mask_kind=kb.MASK_CAUSAL).as_slice()
+    assert np.all(np.isfinite(out))
+    rows = sorted({0, 1, 63, 64, 127, 128, s // 2 - 1, s // 2, s - 65, s - 64, s - 1} | set(rng.choice(s, 12).tolist()))
+    for i in rows:
+        exp = O.attention(q[:, :, i:i + 1], k[:, :, :i + 1].astype(np.float32), v[:, :, :i + 1].astype(np.float32), scale)
+        err = F.rel_l2(out[:, :, i:i + 1], exp)
+        assert err < 2e-3, (s, i, err)
+    assert dev.status() == 0
+
+
+@pytest.mark.parametrize("b,l", [(8, 4096), (8, 16384), (32, 4096)])
+def test_decode_attention_long_contexts(dev, b, l):
+    # one query position per sequence against a long fp16 cache (the split-KV decode kernel)
+    h, hkv, d = 32, 8, 128
+    rng = np.random.default_rng(b * l)
+    q = rng.standard_normal((b, h, 1, d), dtype=np.float32)
+    k = rng.standard_normal((b, hkv, l, d), dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal((b, hkv, l, d), dtype=np.float32).astype(np.float16)
+    scale = float(1.0 / np.sqrt(d))
+    out = dev.flash_attention(dev.tensor(q), dev.tensor(k), dev.tensor(v), scale).as_slice()
+    exp = O.attention(q, k.astype(np.float32), v.astype(np.float32), scale)
+    assert F.rel_l2(out, exp) < 2e-3, F.rel_l2(out, exp)
+    assert np.max(np.abs(out - exp)) < 5e-3
+    assert dev.status() == 0
+
+
 def test_attention_masks_and_cache_capacity(dev):
     rng = np.random.default_rng(8)
     b, h, hkv, sq, skv, d, cap = 2, 4, 2, 6, 10, 64, 32
@@ -200,7 +237,8 @@ def test_attention_masks_and_cache_capacity(dev):
 def test_peer_exchange_wait_is_bounded(dev):
     # a peer that never arrives: the wait gives up after its poll limit, the handle's status word
     # says so, and the GPU keeps working (no trap, no hang); a handle of its own keeps the
-    # session handle's status clean
+    # session handle's status clean. While the word is set every blocking call reports the
+    # time-out; clearing the word brings the handle back.
     other = kb.Device(0)
     assert other.status() == 0
     with pytest.raises(kb.FusorError) as e:
@@ -208,6 +246,37 @@ def test_peer_exchange_wait_is_bounded(dev):
     assert e.value.code == kb.ERR_TIMEOUT
     assert other.status() == kb.ERR_TIMEOUT
     x = other.tensor(np.ones((2, 8), np.float32))
+    with pytest.raises(kb.FusorError) as e:  # the read-back is where a failed step surfaces
+        x.as_slice()
+    assert e.value.code == kb.ERR_TIMEOUT and "status" in str(e.value)
+    with pytest.raises(kb.FusorError) as e:
+        other.synchronize()
+    assert e.value.code == kb.ERR_TIMEOUT
+    other.clear_status()
+    assert other.status() == 0
+    other.synchronize()
     assert np.array_equal(x.as_slice(), np.ones((2, 8), np.float32))
     other.close()
     assert dev.status() == 0
+
+
+def test_scratch_budget_and_poison(dev):
+    # a handle with a scratch budget refuses a product whose packed activations do not fit
+    # (instead of allocating), and serves it once the budget is lifted; in poison mode fresh
+    # scratch starts as NaN bytes and the result is still exact, i.e. nothing reads scratch it
+    # did not write
+    other = kb.Device(0)
+    ty, n, k = O.Q4K, 64, 8192
+    raw = weights(12, n, k, ty)
+    w = kb.QMatrix.from_raw_bytes(other, (n, k), raw, ty)
+    x = np.random.default_rng(3).standard_normal((8, k)).astype(np.float32)
+    other.set_scratch_limit(64 << 10)
+    with pytest.raises(kb.FusorError) as e:
+        other.tensor(x).q_mat_mul(w)
+    assert e.value.code == kb.ERR_CAPACITY and "budget" in str(e.value)
+    other.set_scratch_limit(0)
+    other.set_poison(True)
+    y = other.tensor(x).q_mat_mul(w).as_slice()
+    assert F.rel_l2(y, O.q_mat_mul(x, raw, ty, n, k)) < 2e-3
+    w.free()
+    other.close()

@@ -119,23 +119,53 @@ def test_prefill_product_tensor_cores(dev, tname, tile, monkeypatch):
     assert np.array_equal(xt.q_mat_mul(gu).as_slice(), xt.q_mat_mul(gu).as_slice())
 
 
+def _sampled_columns(raw, ty, n, k, cols):
+    """Raw GGUF bytes of the rows `cols` of an [n, k] matrix (rows are contiguous block runs)."""
+    bs, bb = O.BLOCK[ty]
+    row_bytes = k // bs * bb
+    return np.concatenate([raw[c * row_bytes:(c + 1) * row_bytes] for c in cols])
+
+
 @pytest.mark.parametrize("tname,n,k", [("q4_0", 4096, 4096), ("q4k", 4096, 4096), ("q4k", 1024, 4096),
                                         ("q4k", 14336, 4096), ("q4k", 4096, 14336), ("q8_0", 4096, 4096),
-                                        ("q6k", 1024, 4096), ("q6k", 4096, 14336)])
+                                        ("q8_0", 14336, 4096), ("q6k", 1024, 4096), ("q6k", 4096, 14336)])
 def test_q_mat_mul_llama_shapes(dev, tname, n, k):
+    # the projection shapes of a Llama-3-8B layer at every row count of the sweep: one row (integer
+    # limb kernel), 8 and 32 rows (fp16 mma kernel), 512 and 2048 rows (tcgen05 kernel). The oracle
+    # runs on a sample of output columns (and, for the large row counts, of activation rows: rows
+    # are independent) to keep the CPU time bounded.
     ty = TYPES[tname]
     raw = weights(n + k, n, k, ty)
     w = kb.QMatrix.from_raw_bytes(dev, (n, k), raw, ty)
-    for m in (1, 8):
+    cols = np.sort(np.random.default_rng(1).choice(n, 256, replace=False))
+    sub = _sampled_columns(raw, ty, n, k, cols)
+    for m in (1, 8, 32, 512, 2048):
         x = activations(m + 3, m, k)
         y = dev.tensor(x).q_mat_mul(w).as_slice()
-        cols = np.random.default_rng(1).choice(n, 256, replace=False)
-        # oracle on a sample of the output columns keeps the CPU time bounded
-        bs, bb = O.BLOCK[ty]
-        row_bytes = k // bs * bb
-        sub = np.concatenate([raw[c * row_bytes:(c + 1) * row_bytes] for c in cols])
-        exp = O.q_mat_mul(x, sub, ty, len(cols), k)
-        assert F.rel_l2(y[:, cols], exp) < TOL, (tname, n, k, m, F.rel_l2(y[:, cols], exp))
+        assert y.shape == (m, n)
+        rows = np.arange(m) if m <= 32 else np.sort(np.random.default_rng(m).choice(m, 16, replace=False))
+        exp = O.q_mat_mul(x[rows], sub, ty, len(cols), k)
+        err = F.rel_l2(y[np.ix_(rows, cols)], exp)
+        assert err < TOL, (tname, n, k, m, err)
+    assert dev.status() == 0
+
+
+def test_q_mat_mul_output_head(dev):
+    # the 128256 x 4096 Q6_K output head (the largest matrix of the decoder, 431 MB) stand-alone
+    ty, n, k = O.Q6K, 128256, 4096
+    raw = weights(99, n, k, ty)
+    w = kb.QMatrix.from_raw_bytes(dev, (n, k), raw, ty)
+    assert w.nbytes == 430940160
+    rng = np.random.default_rng(5)
+    cols = np.sort(np.concatenate([rng.choice(n, 500, replace=False), [0, 15, 16, n - 17, n - 16, n - 1]]))
+    sub = _sampled_columns(raw, ty, n, k, cols)
+    for m in (1, 8):
+        x = activations(m + 40, m, k)
+        y = dev.tensor(x).q_mat_mul(w).as_slice()
+        assert y.shape == (m, n) and np.all(np.isfinite(y))
+        err = F.rel_l2(y[:, cols], O.q_mat_mul(x, sub, ty, len(cols), k))
+        assert err < TOL, (m, err)
+    assert dev.status() == 0
 
 
 def test_repeatable_bitwise(dev):

@@ -5,8 +5,11 @@ budget frozen after start-up, allocator locks held by the calling thread, alloca
 by the embedding application). fb200_q_mat_mul_noalloc serves them from a fixed scratch array
 inside the library. Here it is driven through the C ABI twice in a row per case, with different
 inputs, and compared with fb200_q_mat_mul at the tolerance the other product tests use (2e-3
-relative L2; both run the same kernels, so they agree far more closely), then checked for its
-documented refusals.
+relative L2). For 2..32 rows both entry points run the same fp16 kernel and agree far more
+closely; a single row goes to the integer-limb kernel in fb200_q_mat_mul but to the fp16 kernel
+here, so that case really compares two kernels. Between the two calls a product of another
+shape and row bucket runs through the same shared array, so the second call starts from stale
+contents it must overwrite. The documented refusals are checked last.
 """
 import numpy as np
 import pytest
@@ -28,6 +31,13 @@ def test_noalloc_matches_regular_entry_point_twice(dev, tname, m):
     raw = weights(41, n, k, ty)
     w = kb.QMatrix.from_raw_bytes(dev, (n, k), raw, ty)
     out = dev.empty((m, n))  # allocated before the calls under test
+    # another shape (larger K, another row bucket) that shares the scratch array between the calls
+    m2 = 20 if m <= 16 else 5
+    n2, k2 = 48, 4096
+    raw2 = weights(43, n2, k2, ty)
+    w2 = kb.QMatrix.from_raw_bytes(dev, (n2, k2), raw2, ty)
+    x2 = activations(7 + m, m2, k2)
+    out2 = dev.empty((m2, n2))
     for call in range(2):
         x = activations(100 * call + m, m, k)
         xt = dev.tensor(x)
@@ -38,6 +48,9 @@ def test_noalloc_matches_regular_entry_point_twice(dev, tname, m):
         assert np.all(np.isfinite(got))
         assert F.rel_l2(got, ref) < TOL, (tname, m, call, F.rel_l2(got, ref))
         assert F.rel_l2(got, O.q_mat_mul(x, raw, ty, n, k)) < TOL
+        if call == 0:
+            got2 = dev.tensor(x2).q_mat_mul_noalloc(w2, out2).as_slice()
+            assert F.rel_l2(got2, O.q_mat_mul(x2, raw2, ty, n2, k2)) < TOL
     assert dev.status() == 0
 
 
