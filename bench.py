@@ -333,70 +333,11 @@ def run_prefill_only(args):
 CFG70 = dict(n_layer=80, hidden=8192, ffn=28672, n_head=64, n_kv_head=8, head_dim=128, vocab=128256)
 
 
-def run_tensor_parallel(args):
-    """Llama-3-70B-shaped, all Q4_K, greedy decode with the model split over the ranks (tensor
-    parallel: one sequence group, every rank streams 1 / N of the weights per step; two all-reduces per
-    layer). One JSON line from rank 0; not the bench line (that is the 8B replica metric)."""
-    import torch
-    import torch.distributed as dist
-    import kalosm_b200 as kb
-    from kalosm_b200 import synth, tp
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    stream = torch.cuda.Stream()
-    torch.cuda.set_stream(stream)
-    dev = kb.Device(local, stream.cuda_stream)
-    comm = None
-    if world > 1:
-        uid = [kb.Comm.unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(uid, 0)
-        comm = kb.Comm(dev, world, rank, uid[0])
-        if not args.tp_nccl:
-            # the decode step sums its partial rows over NVLink peer memory inside the persistent kernel
-            def gather(obj):
-                parts = [None] * world
-                dist.all_gather_object(parts, obj)
-                return parts
-            comm.enable_peer_exchange(CFG70["hidden"], gather)
-    cfg = dict(CFG70, n_layer=args.layers if args.layers != 32 else 80)
-    batch, steps, warmup, prompt_len = args.batch, args.steps, max(args.warmup, 3), args.tp_prompt
-    ctx = prompt_len + 2 * (steps + warmup) + 64
-    m = kb.Llama(dev, n_layer=cfg["n_layer"], hidden=cfg["hidden"], ffn=cfg["ffn"], n_head=cfg["n_head"],
-                 n_kv_head=cfg["n_kv_head"], head_dim=cfg["head_dim"], vocab=cfg["vocab"], max_seq_len=ctx,
-                 max_batch=batch, comm=comm)
-    e, f = cfg["hidden"], cfg["ffn"]
-    qd, kvd = cfg["n_head"] * cfg["head_dim"], cfg["n_kv_head"] * cfg["head_dim"]
-    plan = [("token_embd", -1, (cfg["vocab"], e)), ("output", -1, (cfg["vocab"], e))]
-    for i in range(cfg["n_layer"]):
-        plan += [("attn_q", i, (qd, e)), ("attn_k", i, (kvd, e)), ("attn_v", i, (kvd, e)), ("attn_output", i, (e, qd)),
-                 ("ffn_gate", i, (f, e)), ("ffn_up", i, (f, e)), ("ffn_down", i, (e, f))]
-    local_bytes = 0
-    for j, (name, layer, (n, k)) in enumerate(plan):
-        # this rank's shard is generated directly (random weights: no whole matrix to cut)
-        if name in tp.ROW_SPLIT:
-            n //= world
-        elif name in tp.COL_SPLIT:
-            k //= world
-        seed = 1000003 * (rank if name != "token_embd" else 0) + j
-        raw = synth.random_qweights(seed, 0.02, n, k, Q4_K, device="cuda").cpu().numpy()
-        m.set_tensor(name, layer, Q4_K, (n, k), raw)
-        if name != "token_embd":
-            local_bytes += raw.size
-    g = torch.Generator().manual_seed(77)
-    for i in range(cfg["n_layer"] + 1):
-        for nm in (("attn_norm", "ffn_norm") if i < cfg["n_layer"] else ("output_norm",)):
-            w = (1.0 + 0.02 * torch.randn(e, generator=g)).numpy().astype(np.float32)
-            m.set_tensor(nm, i if i < cfg["n_layer"] else -1, F32, (e,), w)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
+def _tp_measure(torch, dist, kb, dev, stream, m, comm, cfg, rank, world, local, batch, steps, warmup, prompt_len,
+                local_bytes, use_nccl, barrier):
+    """One batch size of the tensor-parallel leg on an already loaded model."""
+    e = cfg["hidden"]
+    m.reset()
     prompt = np.random.default_rng(0).integers(0, cfg["vocab"], size=(batch, prompt_len), dtype=np.uint32)
     m.forward(prompt, want_logits=False)
     m.reset()
@@ -444,11 +385,13 @@ def run_tensor_parallel(args):
         dist.all_gather_object(parts, toks.tolist())
         same = all(p == parts[0] for p in parts)
     ms, ms_prefill = max_over_ranks([ms, ms_prefill], world, "cuda")
+    status = dev.status()
+    out = None
     if rank == 0:
         peak, which = peaks()
         kv = 2 * cfg["n_layer"] * (cfg["n_kv_head"] // world) * cfg["head_dim"] * 2 * (prompt_len + warmup + steps // 2) * batch
         gbs = (local_bytes + kv) / (ms / steps / 1e3) / 1e9
-        print(json.dumps({
+        out = {
             "metric": "Llama-3-70B-shaped Q4_K greedy decode tok/s, tensor parallel", "value": batch * steps / ms * 1e3,
             "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms / steps,
             "higher_is_better": True, "scaling": "strong", "data": "synthetic (seeded N(0, 0.02) weights as Q4_K blocks)",
@@ -456,7 +399,7 @@ def run_tensor_parallel(args):
                                    f"{prompt_len}, {steps} steps" + ("" if cfg["n_layer"] == 80 else
                                                                      f" (REDUCED: {cfg['n_layer']} layers)"),
                        "parallelism": f"tp{world}",
-                       "step": ("kernel per operation, NCCL all-reduce" if args.tp_nccl or world == 1 else
+                       "step": ("kernel per operation, NCCL all-reduce" if use_nccl or world == 1 or batch > 1 else
                                 "one persistent kernel per rank, sums over NVLink peer memory inside it")},
             "gpu_launches": int(launches),
             "per_gpu": {"weight_bytes_per_step": local_bytes, "kv_bytes_per_step": kv, "achieved_gbs": gbs,
@@ -465,12 +408,101 @@ def run_tensor_parallel(args):
                                                       "us_each_back_to_back": ar_us,
                                                       "ms_per_step_alone": ar_us * 2 * cfg["n_layer"] / 1e3},
             "prefill": {"tokens": batch * prompt_len, "ms": ms_prefill, "tok_s": batch * prompt_len / ms_prefill * 1e3},
-            "ranks_agree_on_tokens": same, "device_status": dev.status(), "clocks": clocks}), flush=True)
+            "ranks_agree_on_tokens": same, "device_status": status, "clocks": clocks}
+    return out
+
+
+def tensor_parallel_leg(args, torch, dist, kb, dev, stream, rank, world, local, batches, steps, warmup, prompt_len,
+                        n_layer=80, use_nccl=False):
+    """Llama-3-70B-shaped, all Q4_K, greedy decode with the model split over the ranks (tensor
+    parallel: every rank streams 1 / N of the weights per step; two sums over the ranks per layer).
+    One model, measured once per entry of `batches`. Every rank calls this; rank 0 gets the list of
+    result dictionaries (one per batch), the others None."""
+    from kalosm_b200 import synth, tp
+    comm = None
+    if world > 1:
+        uid = [kb.Comm.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, 0)
+        comm = kb.Comm(dev, world, rank, uid[0])
+        if not use_nccl:
+            # the decode step sums its partial rows over NVLink peer memory inside the persistent kernel
+            def gather(obj):
+                parts = [None] * world
+                dist.all_gather_object(parts, obj)
+                return parts
+            comm.enable_peer_exchange(CFG70["hidden"], gather)
+    cfg = dict(CFG70, n_layer=n_layer)
+    ctx = prompt_len + 2 * (steps + warmup) + 64
+    m = kb.Llama(dev, n_layer=cfg["n_layer"], hidden=cfg["hidden"], ffn=cfg["ffn"], n_head=cfg["n_head"],
+                 n_kv_head=cfg["n_kv_head"], head_dim=cfg["head_dim"], vocab=cfg["vocab"], max_seq_len=ctx,
+                 max_batch=max(batches), comm=comm)
+    e, f = cfg["hidden"], cfg["ffn"]
+    qd, kvd = cfg["n_head"] * cfg["head_dim"], cfg["n_kv_head"] * cfg["head_dim"]
+    plan = [("token_embd", -1, (cfg["vocab"], e)), ("output", -1, (cfg["vocab"], e))]
+    for i in range(cfg["n_layer"]):
+        plan += [("attn_q", i, (qd, e)), ("attn_k", i, (kvd, e)), ("attn_v", i, (kvd, e)), ("attn_output", i, (e, qd)),
+                 ("ffn_gate", i, (f, e)), ("ffn_up", i, (f, e)), ("ffn_down", i, (e, f))]
+    local_bytes = 0
+    for j, (name, layer, (n, k)) in enumerate(plan):
+        # this rank's shard is generated directly (random weights: no whole matrix to cut)
+        if name in tp.ROW_SPLIT:
+            n //= world
+        elif name in tp.COL_SPLIT:
+            k //= world
+        seed = 1000003 * (rank if name != "token_embd" else 0) + j
+        raw = synth.random_qweights(seed, 0.02, n, k, Q4_K, device="cuda").cpu().numpy()
+        m.set_tensor(name, layer, Q4_K, (n, k), raw)
+        if name != "token_embd":
+            local_bytes += raw.size
+    g = torch.Generator().manual_seed(77)
+    for i in range(cfg["n_layer"] + 1):
+        for nm in (("attn_norm", "ffn_norm") if i < cfg["n_layer"] else ("output_norm",)):
+            w = (1.0 + 0.02 * torch.randn(e, generator=g)).numpy().astype(np.float32)
+            m.set_tensor(nm, i if i < cfg["n_layer"] else -1, F32, (e,), w)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    results = []
+    for batch in batches:
+        results.append(_tp_measure(torch, dist, kb, dev, stream, m, comm, cfg, rank, world, local, batch, steps,
+                                   warmup, prompt_len, local_bytes, use_nccl, barrier))
+    out = results if rank == 0 else None
     m.free()
     if comm is not None:
         comm.destroy()
+    return out
+
+
+def run_tensor_parallel(args):
+    """`--tp`: only the tensor-parallel leg, one JSON line from rank 0 (not the bench line: that is the
+    8B replica metric). Exits non-zero when a kernel recorded a time-out or the ranks disagree."""
+    import torch
+    import torch.distributed as dist
+    import kalosm_b200 as kb
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    dev = kb.Device(local, stream.cuda_stream)
+    outs = tensor_parallel_leg(args, torch, dist, kb, dev, stream, rank, world, local, [args.batch], args.steps,
+                               max(args.warmup, 3), args.tp_prompt, n_layer=args.layers if args.layers != 32 else 80,
+                               use_nccl=args.tp_nccl)
+    bad = 0
+    if rank == 0:
+        out = outs[0]
+        print(json.dumps(out), flush=True)
+        bad = int(out["device_status"] != 0 or not out["ranks_agree_on_tokens"])
     if world > 1:
         dist.destroy_process_group()
+    if bad:
+        sys.exit(3)
 
 
 def run_sweep(args):
@@ -607,46 +639,96 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---- device-resident loop (value) ----------------------------------------------------
+    # The timed region is EXACTLY `steps` decode steps, bracketed by barrier + synchronize. It is
+    # repeated (the KV caches rewound to the same position each time, so every repetition covers
+    # the same contexts) until about a second of GPU time has been measured; the reported time is
+    # the median repetition of the per-repetition maximum over ranks.
     model.generate_greedy(nxt, warmup)
     last = model.generate_greedy(nxt, 1)[:, -1]
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start_pos = model.position
     sampler = ClockSampler(local)
     sampler.start()
     time.sleep(0.3)
-    barrier()
-    launches0 = dev.launch_count
+
+    def bail_if_any(reason):
+        """Ends the job on every rank (non-zero exit) when any rank has a reason to; a rank that
+        left alone would strand the others in the next barrier."""
+        flag = max_over_ranks([1.0 if reason else 0.0], world, "cuda")[0]
+        if reason:
+            sys.stderr.write(f"bench (rank {rank}): {reason}\n")
+        if flag:
+            if world > 1:
+                dist.destroy_process_group()
+            sys.exit(3)
+
+    def timed_generate():
+        model.truncate(start_pos)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n0 = dev.launch_count
+        e0.record(stream)
+        out = model.generate_greedy(last, steps)
+        e1.record(stream)
+        barrier()
+        return max_over_ranks([e0.elapsed_time(e1)], world, "cuda")[0], dev.launch_count - n0, out
+
     t0 = time.time()
-    e0.record(stream)
-    toks = model.generate_greedy(last, steps)
-    e1.record(stream)
-    barrier()
+    first_ms, launches, toks = timed_generate()
+    repeats = int(min(32, max(3, np.ceil(1000.0 / max(first_ms, 1e-3)))))
+    rep_ms = [first_ms]
+    differ = False
+    for _ in range(repeats - 1):
+        ms_i, launches, toks_i = timed_generate()
+        rep_ms.append(ms_i)
+        differ = differ or not np.array_equal(toks_i, toks)
     t1 = time.time()
-    launches = dev.launch_count - launches0
-    ms = e0.elapsed_time(e1)
+    ms = float(np.median(rep_ms))
     clocks = sampler.stop(t0, t1)
     status = dev.status()
+    bail_if_any(f"device status {status} after the timed region (a wait inside a kernel gave up)" if status else
+                "two repetitions of the same greedy decode gave different tokens" if differ else None)
 
     # ---- end to end: one fb200_llama_forward per step, ids through pinned host memory -------
     pinned = torch.empty(batch, dtype=torch.int32).pin_memory()
-    pinned.copy_(torch.from_numpy(toks[:, -1].astype(np.int32)))
     tok = pinned.numpy().view(np.uint32)
+
+    def timed_forward_steps():
+        model.truncate(start_pos)
+        tok[:] = last
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record(stream)
+        for _ in range(steps):
+            _, n2 = model.forward(tok.reshape(batch, 1), want_logits=False)
+            tok[:] = n2
+        f1.record(stream)
+        barrier()
+        return max_over_ranks([f0.elapsed_time(f1)], world, "cuda")[0]
+
+    model.truncate(start_pos)
+    tok[:] = last
     for _ in range(3):
         _, n2 = model.forward(tok.reshape(batch, 1), want_logits=False)
         tok[:] = n2
-    barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record(stream)
-    for _ in range(steps):
-        _, n2 = model.forward(tok.reshape(batch, 1), want_logits=False)
-        tok[:] = n2
-    f1.record(stream)
-    barrier()
-    ms_e2e = f0.elapsed_time(f1)
+    e2e_ms = [timed_forward_steps() for _ in range(repeats)]
+    ms_e2e = float(np.median(e2e_ms))
+    bail_if_any(None if np.array_equal(tok, toks[:, -1]) else
+                "stepping through forward() and the device-resident loop gave different tokens")
 
     # ---- the stand-alone single-row product (the kernel behind fb200_q_mat_mul at M = 1) ----
     roof_gemv = gemv_roofline(kb, dev, torch, stream, 8) if rank == 0 else None
 
-    ms, ms_e2e = max_over_ranks([ms, ms_e2e], world, "cuda")
+    # ---- tensor parallel (only when the job has more than one GPU): the 70B-shaped model split over
+    # the same ranks, reported under its own key; `value` stays the replica metric
+    tp_leg = None
+    if world > 1 and not args.no_tp:
+        model.free()
+        model = None
+        try:
+            tp_leg = tensor_parallel_leg(args, torch, dist, kb, dev, stream, rank, world, local, [1, 8], 128, 3,
+                                         args.tp_prompt)
+        except kb.FusorError as exc:  # every rank runs the same calls, so a refusal is raised on all of them
+            tp_leg = [{"error": str(exc)}]
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -654,7 +736,7 @@ def run_ours(args):
     tok_s = whole_job_rate(world, batch, steps, ms)
     tok_s_e2e = whole_job_rate(world, batch, steps, ms_e2e)
     wb = weight_bytes_per_step(CFG)
-    kv = 2 * CFG["n_layer"] * CFG["n_kv_head"] * CFG["head_dim"] * 2 * (PROMPT + warmup + steps // 2) * batch
+    kv = 2 * CFG["n_layer"] * CFG["n_kv_head"] * CFG["head_dim"] * 2 * (PROMPT + warmup + 1 + steps // 2) * batch
     peak, which = peaks()
     step_gbs = (wb + kv) / (ms / steps / 1e3) / 1e9
     # dominant kernel: the fused decode-step kernel; the timed region above is `launches` launches
@@ -690,12 +772,17 @@ def run_ours(args):
             "e2e": {"value": tok_s_e2e, "unit": "tok/s", "h2d_bytes_per_step": 4 * batch,
                     "d2h_bytes_per_step": 4 * batch, "ms_per_step": ms_e2e / steps},
             "gpu_launches": int(launches), "device_status": status, "clocks": clocks,
+            "timing": {"repeats": repeats, "ms_per_repeat": rep_ms, "reported": "median repetition, each the maximum over ranks",
+                       "e2e_ms_per_repeat": e2e_ms},
             "roofline": roof, "roofline_gemv_alone": roof_gemv,
             "prefill": {"tokens": batch * PROMPT, "ms": ms_prefill, "tok_s": batch * PROMPT / ms_prefill * 1e3,
                         "kernel": "quantised products on tcgen05 tensor cores (fp16 operands, fp32 TMEM accumulator)"},
             "step_hbm": {"bytes_per_step": wb + kv, "achieved_gbs": step_gbs, "frac_of_peak": step_gbs / peak,
                          "peak_source": which},
             "cpu_baseline": cpu}
+    if tp_leg is not None:
+        line["tensor_parallel"] = {"tp": world, "model": "llama3-70b-shaped, all Q4_K, prompt %d, 128 greedy steps" % args.tp_prompt,
+                                   "by_batch": tp_leg}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -718,6 +805,7 @@ def main():
                     help="70B-shaped model split over the ranks (tensor parallel) instead of 8B replicas")
     ap.add_argument("--tp-prompt", type=int, default=2048)
     ap.add_argument("--tp-nccl", action="store_true", help="with --tp: keep the decode step on NCCL all-reduces")
+    ap.add_argument("--no-tp", action="store_true", help="with --gpus N > 1: skip the tensor-parallel leg after the replicas")
     ap.add_argument("--gemv-reps", type=int, default=8)
     ap.add_argument("--sweep", action="store_true",
                     help="per-kernel table over the other product shapes and decode attention (several JSON lines)")

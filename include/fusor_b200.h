@@ -207,6 +207,44 @@ FB200_API int fb200_embedding_lookup(fb200_device* dev, const fb200_qmatrix* w, 
  * logit, ties -> higher token id. ids_dev [rows] u32, vals_dev [rows] f32 (may be NULL). */
 FB200_API int fb200_argmax(fb200_device* dev, const float* logits_dev, size_t rows, size_t n,
                  uint32_t* ids_dev, float* vals_dev);
+/* Tensor::top_k_pairs(k), fusor-ml/fusor/src/lib.rs:416-453 (GPU form:
+ * fusor-ml/core/src/mir/kernel_backend/sampling_topk.rs): per row the k highest finite logits in
+ * descending order, ties -> higher token id. ids_dev [rows, k] u32, vals_dev [rows, k] f32 (may
+ * be NULL); a row with fewer than k finite logits is padded with id 0xFFFFFFFF / value -inf.
+ * 1 <= k <= FB200_SAMPLER_MAX_TOP_K. */
+#define FB200_SAMPLER_MAX_TOP_K 1024
+FB200_API int fb200_top_k(fb200_device* dev, const float* logits_dev, size_t rows, size_t n, int k,
+                          uint32_t* ids_dev, float* vals_dev);
+
+/* ---- on-device samplers: models/kalosm-llama/src/sampler.rs:44-311 (CPU) and
+ * fusor-ml/core/src/sampling/{pipeline,row_kernels,processors}.rs (GPU) ------------------------
+ * Field meanings are those of GpuSamplerConfig (models/kalosm-llama/src/lib.rs:477-488). Per
+ * logit: non-finite values are dropped, tokens among the last repetition_penalty_range previous
+ * tokens are penalised (repetition_penalty > 1: positive logits divided, others multiplied), the
+ * result is divided by the temperature (if not 0). The top_k survivors, sorted descending (ties
+ * -> higher id), then go through min-p, top-p and a cumulative walk against a uniform draw
+ * (standard; temperature <= 0 returns the first), or through the surprise cut-off and mu update
+ * of Mirostat 2. The uniform draw is a counter-based function of (seed, counter, row) instead of
+ * the reference's rand::StdRng stream: equal inputs give equal tokens on every run. */
+typedef enum fb200_sampler_strategy { FB200_SAMPLER_STANDARD = 0, FB200_SAMPLER_MIROSTAT2 = 1 } fb200_sampler_strategy;
+typedef struct fb200_sampler_config {
+  int strategy;
+  float temperature;
+  float repetition_penalty;
+  int repetition_penalty_range;
+  int top_k;      /* 1 .. FB200_SAMPLER_MAX_TOP_K */
+  float top_p;    /* >= 1 or NaN: off */
+  float min_p;    /* <= 0 or NaN: off */
+  float tau, eta, mu; /* Mirostat 2: target surprise, learning rate, initial mu */
+  uint64_t seed;
+} fb200_sampler_config;
+/* One sampling step over logits_dev [rows, n]. prev_dev [rows, prev_stride] u32 holds each row's
+ * previous tokens, the first prev_len of them valid (NULL / 0: none). counter selects the draw.
+ * mu_dev [rows] f32 is the Mirostat state (read and updated; NULL for the standard sampler).
+ * ids_dev [rows] receives the sampled ids (0xFFFFFFFF for a row without a finite logit). */
+FB200_API int fb200_sample(fb200_device* dev, const float* logits_dev, size_t rows, size_t n,
+                           const fb200_sampler_config* cfg, const uint32_t* prev_dev, size_t prev_stride,
+                           int prev_len, uint64_t counter, float* mu_dev, uint32_t* ids_dev);
 
 /* ---- KV cache: KvCache / TensorCache, fusor-ml/fusor/src/cache/kv_cache.rs:12-68 ----------------
  * Layout [B, Hkv, capacity, D], fp16 on the device (the reference's cache is f32). Capacity
@@ -282,6 +320,14 @@ FB200_API int fb200_llama_forward(fb200_llama* m, const uint32_t* tokens_host, i
  * generated ids. Only the ids cross PCIe. */
 FB200_API int fb200_llama_generate_greedy(fb200_llama* m, const uint32_t* tokens_host, int batch,
                                 int steps, uint32_t* out_host);
+/* Sampled decode: like fb200_llama_generate_greedy, but every step's token comes from the sampler
+ * (fb200_sampler_config) run on the device over that step's logits; the penalty window is the
+ * session's own token history (every token fed to or produced by the model since the last
+ * reset), the draw counter is the token's position. All steps are enqueued without waiting for
+ * any of them, the run-ahead of models/kalosm-llama/src/model/inference.rs:41-170; only the ids
+ * come back. Not available on a tensor-parallel model (the logits are sharded). */
+FB200_API int fb200_llama_generate_sampled(fb200_llama* m, const uint32_t* tokens_host, int batch, int steps,
+                                           const fb200_sampler_config* cfg, uint32_t* out_host);
 /* Device pointer of the last forward pass's logits, f32 [batch, vocab] (tensor parallel:
  * [batch, vocab / size], this rank's rows of the output head). */
 FB200_API int fb200_llama_logits_dev(const fb200_llama* m, const float** logits_dev);

@@ -40,6 +40,23 @@ class FusorError(RuntimeError):
         self.code = code
 
 
+class SamplerConfig(C.Structure):
+    """fb200_sampler_config; fields as GpuSamplerConfig (models/kalosm-llama/src/lib.rs:477-488)."""
+    _fields_ = [("strategy", C.c_int), ("temperature", C.c_float), ("repetition_penalty", C.c_float),
+                ("repetition_penalty_range", C.c_int), ("top_k", C.c_int), ("top_p", C.c_float),
+                ("min_p", C.c_float), ("tau", C.c_float), ("eta", C.c_float), ("mu", C.c_float),
+                ("seed", C.c_uint64)]
+
+    def __init__(self, strategy=0, temperature=1.0, repetition_penalty=1.0, repetition_penalty_range=64,
+                 top_k=64, top_p=float("nan"), min_p=float("nan"), tau=5.0, eta=0.1, mu=10.0, seed=0):
+        super().__init__(strategy, temperature, repetition_penalty, repetition_penalty_range, top_k, top_p,
+                         min_p, tau, eta, mu, seed)
+
+
+SAMPLER_STANDARD, SAMPLER_MIROSTAT2 = 0, 1
+SAMPLER_MAX_TOP_K = 1024
+
+
 class _Epilogue(C.Structure):
     _fields_ = [("kind", C.c_int), ("r1", C.c_void_p), ("r2", C.c_void_p)]
 
@@ -62,7 +79,8 @@ EXPORTS = [
     "fb200_qmatrix_shape", "fb200_qmatrix_ggml_type", "fb200_qmatrix_nbytes",
     "fb200_qmatrix_dequantize", "fb200_qmatrix_concat_rows", "fb200_q_mat_mul",
     "fb200_q_mat_mul_host", "fb200_q_mat_mul_noalloc", "fb200_rms_norm_q_mat_mul", "fb200_rms_norm", "fb200_silu_mul", "fb200_rope_tables",
-    "fb200_rope_pair", "fb200_embedding_lookup", "fb200_argmax", "fb200_kv_cache_create",
+    "fb200_rope_pair", "fb200_embedding_lookup", "fb200_argmax", "fb200_top_k", "fb200_sample",
+    "fb200_llama_generate_sampled", "fb200_kv_cache_create",
     "fb200_kv_cache_free", "fb200_kv_cache_reset", "fb200_kv_cache_truncate", "fb200_kv_cache_len", "fb200_kv_cache_append",
     "fb200_kv_cache_buffers", "fb200_flash_attention", "fb200_llama_create", "fb200_llama_free",
     "fb200_llama_set_tensor", "fb200_llama_reset", "fb200_llama_truncate", "fb200_llama_position", "fb200_llama_forward",
@@ -117,6 +135,9 @@ def load_library():
         "fb200_rope_pair": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32]),
         "fb200_embedding_lookup": (i32, [vp, vp, vp, sz, vp]),
         "fb200_argmax": (i32, [vp, vp, sz, sz, vp, vp]),
+        "fb200_top_k": (i32, [vp, vp, sz, sz, i32, vp, vp]),
+        "fb200_sample": (i32, [vp, vp, sz, sz, C.POINTER(SamplerConfig), vp, sz, i32, u64, vp, vp]),
+        "fb200_llama_generate_sampled": (i32, [vp, vp, i32, i32, C.POINTER(SamplerConfig), vp]),
         "fb200_kv_cache_create": (i32, [vp, i32, i32, i32, i32, pp]),
         "fb200_kv_cache_free": (i32, [vp]),
         "fb200_kv_cache_reset": (i32, [vp]),
@@ -328,6 +349,27 @@ class Device:
         ids, vals = Tensor(self, (rows,), np.uint32), Tensor(self, (rows,), np.float32)
         self._check(self.lib.fb200_argmax(self.h, logits.ptr, rows, n, ids.ptr, vals.ptr))
         return ids, vals
+
+    def top_k(self, logits: Tensor, k: int):
+        """Tensor::top_k_pairs (fusor/src/lib.rs:416-453): (ids [rows, k], values [rows, k]), descending,
+        ties -> higher id."""
+        n = logits.shape[-1]
+        rows = logits.nbytes // 4 // n
+        ids, vals = Tensor(self, (rows, k), np.uint32), Tensor(self, (rows, k), np.float32)
+        self._check(self.lib.fb200_top_k(self.h, logits.ptr, rows, n, k, ids.ptr, vals.ptr))
+        return ids, vals
+
+    def sample(self, logits: Tensor, cfg: "SamplerConfig", previous: Tensor = None, counter: int = 0,
+               mu: Tensor = None) -> Tensor:
+        """One step of the on-device sampler over logits [rows, n]; previous [rows, L] u32."""
+        n = logits.shape[-1]
+        rows = logits.nbytes // 4 // n
+        ids = Tensor(self, (rows,), np.uint32)
+        plen = previous.shape[-1] if previous is not None else 0
+        self._check(self.lib.fb200_sample(self.h, logits.ptr, rows, n, C.byref(cfg),
+                                          previous.ptr if previous is not None else None, plen, plen, counter,
+                                          mu.ptr if mu is not None else None, ids.ptr))
+        return ids
 
     def flash_attention(self, q: Tensor, k: Tensor, v: Tensor, scale: float, skv: int = None,
                         mask: Tensor = None, mask_kind: int = MASK_NONE, out: Tensor = None) -> Tensor:
@@ -607,6 +649,14 @@ class Llama:
         out = np.empty((t.size, steps), dtype=np.uint32)
         d = self.device
         d._check(d.lib.fb200_llama_generate_greedy(self.h, _hp(t), t.size, steps, _hp(out)))
+        return out
+
+    def generate_sampled(self, tokens, steps: int, cfg: "SamplerConfig") -> np.ndarray:
+        """Sampled decode on the device (run-ahead: no logits or ids cross PCIe until the end)."""
+        t = np.ascontiguousarray(tokens, dtype=np.uint32).reshape(-1)
+        out = np.empty((t.size, steps), dtype=np.uint32)
+        d = self.device
+        d._check(d.lib.fb200_llama_generate_sampled(self.h, _hp(t), t.size, steps, C.byref(cfg), _hp(out)))
         return out
 
     def free(self) -> None:

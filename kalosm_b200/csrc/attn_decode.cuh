@@ -28,6 +28,7 @@ struct fb200_dec_args {
   fb200_packed_act out_packed;  // optional: the merged rows also in packed form (row of H * D)
   int b, h, hkv, groups, cap, nsplit;
   float scale;
+  int pos_plus1;        // > 0: *pos_dev + 1, already read by the caller (saves a dependent load); 0: not known
 };
 
 namespace {
@@ -75,7 +76,6 @@ __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int t
   float (*sc)[DEC_CH] = reinterpret_cast<float (*)[DEC_CH]>(qs + ROWS);              // [ROWS][DEC_CH]
   float (*ored)[ROWS][D] = reinterpret_cast<float (*)[ROWS][D]>(dsm);                // aliases kbuf/vbuf
   __shared__ float alpha[ROWS], row_m[ROWS], row_l[ROWS];
-  __shared__ float wsplit[ROWS][32], inv_l[ROWS];
   __shared__ int is_last;
   static_assert((ATT_THREADS / 32) * ROWS * D * 4 <= 2 * DEC_CH * KSTR, "reduction buffer must fit the staging area");
 
@@ -85,7 +85,7 @@ __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int t
   const int kvh = bid % a.hkv;
   const int bi = bid / a.hkv;
   const int nrows = a.groups;
-  const int pos = a.pos_dev ? __ldcg(a.pos_dev) : -1;
+  const int pos = a.pos_dev ? (a.pos_plus1 > 0 ? a.pos_plus1 - 1 : __ldcg(a.pos_dev)) : -1;
   const int skv = a.pos_dev ? pos + 1 : a.skv;
   const int per = (skv + a.nsplit - 1) / a.nsplit;
   const int kbeg = min(skv, split * per), kend = min(skv, kbeg + per);
@@ -283,28 +283,11 @@ __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int t
   dec_sync<BAR>();
   if (!is_last) return;
   __threadfence();
-  for (int i = tid; i < nrows * 32; i += ATT_THREADS) {
-    const int r = i >> 5, s0 = i & 31;
-    const size_t grow = (size_t)bi * a.h + kvh * a.groups + r;
-    wsplit[r][s0] = s0 < a.nsplit ? __ldcg(a.part + ((size_t)s0 * rows_all + grow) * (D + 2) + D) : -INFINITY;
-  }
-  dec_sync<BAR>();
-  if (warp < nrows) {
-    // warp r: weights exp(m_s - max m) and the merged normaliser of row r
-    const int r = warp;
-    const size_t grow = (size_t)bi * a.h + kvh * a.groups + r;
-    const float m = wsplit[r][lane];
-    float mx = m;
-#pragma unroll
-    for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o2));
-    const float wgt = (m == -INFINITY) ? 0.f : __expf(m - mx);
-    float l = lane < a.nsplit ? __ldcg(a.part + ((size_t)lane * rows_all + grow) * (D + 2) + D + 1) * wgt : 0.f;
-#pragma unroll
-    for (int o2 = 16; o2 > 0; o2 >>= 1) l += __shfl_xor_sync(0xFFFFFFFFu, l, o2);
-    wsplit[r][lane] = wgt;
-    if (lane == 0) inv_l[r] = l > 0.f ? 1.0f / l : 0.f;
-  }
-  dec_sync<BAR>();
+  // Merge in split order. Every thread owns one output element (r, e) per pass and needs, for its
+  // row, all splits' maxima and normalisers and its own column of all partial rows: all of these
+  // loads are issued before the first use, so the merge costs one trip to L2, not one per step.
+  // Lane s of a warp holds split s's maximum and normaliser; the weights travel by shuffle.
+  constexpr int MAXS = 32;
   for (int i0 = 0; i0 < nrows * D; i0 += ATT_THREADS) {
     const int i = i0 + tid;
     const bool valid = i < nrows * D;
@@ -312,10 +295,24 @@ __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int t
     const size_t grow = (size_t)bi * a.h + kvh * a.groups + r;
     float acc = 0.f;
     if (valid) {
-#pragma unroll 8
-      for (int s0 = 0; s0 < a.nsplit; ++s0)
-        acc = fmaf(__ldcg(a.part + ((size_t)s0 * rows_all + grow) * (D + 2) + e), wsplit[r][s0], acc);
-      acc *= inv_l[r];
+      // (a warp's 32 consecutive elements share the row r: D is a multiple of 32)
+      const float* base = a.part + grow * (D + 2);
+      const size_t sstride = rows_all * (D + 2);
+      const float pm = lane < a.nsplit ? __ldcg(base + lane * sstride + D) : -INFINITY;  // lane s: split s
+      const float pl = lane < a.nsplit ? __ldcg(base + lane * sstride + D + 1) : 0.f;
+      float pv[MAXS];
+#pragma unroll
+      for (int s0 = 0; s0 < MAXS; ++s0) pv[s0] = s0 < a.nsplit ? __ldcg(base + s0 * sstride + e) : 0.f;
+      float mx = pm;
+#pragma unroll
+      for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o2));
+      const float wgt = (pm == -INFINITY) ? 0.f : __expf(pm - mx);
+      float l = pl * wgt;
+#pragma unroll
+      for (int o2 = 16; o2 > 0; o2 >>= 1) l += __shfl_xor_sync(0xFFFFFFFFu, l, o2);
+#pragma unroll
+      for (int s0 = 0; s0 < MAXS; ++s0) acc = fmaf(pv[s0], __shfl_sync(0xFFFFFFFFu, wgt, s0), acc);
+      acc *= l > 0.f ? 1.0f / l : 0.f;
       if (a.out) a.out[grow * D + e] = acc;
     }
     // packed rows are single-sequence; nrows * D is a multiple of 32, so `valid` is warp-uniform

@@ -63,9 +63,9 @@ __device__ __forceinline__ unsigned long long global_ns() {
   return t;
 }
 
-__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
+__device__ __forceinline__ unsigned ld_relaxed_u32(const unsigned* p) {
   unsigned v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
 
@@ -80,13 +80,15 @@ __device__ __forceinline__ void grid_barrier(const FusedArgs& A, unsigned& targe
     // arrival = one fire-and-forget reduction with release semantics (orders this CTA's writes,
     // made visible to thread 0 by the barrier above, before the count)
     asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(A.bar) : "memory");
+    // polls are relaxed loads (no ordering work per poll); one acquire fence after the last one
+    // orders everything this CTA reads next behind the arrivals it has seen
     unsigned polls = 0;
-    while ((int)(ld_acquire_u32(A.bar) - target) < 0) {
+    while ((int)(ld_relaxed_u32(A.bar) - target) < 0) {
       ++polls;
       if ((polls & 1023u) == 0u && __ldcg(A.status) != 0) break;
       if (polls > (1u << 24)) { atomicExch(A.status, FB200_ERR_TIMEOUT); break; }
     }
-    __threadfence();
+    asm volatile("fence.acq_rel.gpu;" ::: "memory");
   }
   __syncthreads();
 }
@@ -602,7 +604,8 @@ __device__ __noinline__ void attn_phase(const fb200_fused_phase& P, uint8_t* dsm
   const int tid = threadIdx.x;
   if (tid >= DEC_THREADS) return;
   fb200_dec_args a = P.att;
-  const int skv = __ldcg(a.pos_dev) + 1;
+  a.pos_plus1 = __ldcg(a.pos_dev) + 1;
+  const int skv = a.pos_plus1;
   a.nsplit = max(1, min(a.nsplit, (skv + FUSED_SPLIT_KEYS - 1) / FUSED_SPLIT_KEYS));
   const int nitems = a.b * a.hkv * a.nsplit;
   for (int item = (int)blockIdx.x; item < nitems; item += (int)gridDim.x) {

@@ -41,6 +41,9 @@ fb200_device* fb200_comm_device(const fb200_comm* c);
 bool fb200_comm_take_exchange(fb200_comm* c, int row_floats, unsigned count, fb200_fused_xchg* out);
 bool fb200_comm_exchange_ready(const fb200_comm* c, int row_floats);
 void fb200_comm_mark_broken(fb200_comm* c);
+int fb200_launch_sampler(fb200_device* dev, const float* logits, size_t rows, size_t n, const fb200_sampler_config* c,
+                         const uint32_t* prev, size_t prev_stride, int prev_len, unsigned long long counter, float* mu,
+                         uint32_t* ids, uint32_t* also0, size_t stride0, uint32_t* also1, size_t stride1);
 
 namespace {
 
@@ -140,6 +143,10 @@ struct fb200_llama {
   size_t att_part_bytes = 0;
   uint32_t *ids = nullptr, *next = nullptr, *hist = nullptr;
   int hist_cap = 0;
+  // every token fed to or produced by the model since the last reset, [max_batch, max_seq_len + 1]:
+  // the penalty window of the samplers
+  uint32_t* tok_hist = nullptr;
+  float* mu_dev = nullptr;  // [max_batch] Mirostat 2 state of a sampled decode
   int *pos_dev = nullptr, *step_dev = nullptr;
   unsigned long long* argmax_key = nullptr;
   int* att_done = nullptr;  // arrival counters of the attention splits, one per (batch, kv head)
@@ -649,6 +656,9 @@ int fb200_llama_create(fb200_device* dev, const fb200_llama_config* cfg, fb200_l
   FB_CUDA(dev, cudaMalloc(&m->hist, (size_t)c.max_batch * m->hist_cap * 4));
   FB_CUDA(dev, cudaMemset(m->pos_dev, 0, 4));
   FB_CUDA(dev, cudaMemset(m->step_dev, 0, 4));
+  FB_CUDA(dev, cudaMalloc(&m->tok_hist, (size_t)c.max_batch * (c.max_seq_len + 1) * 4));
+  FB_CUDA(dev, cudaMemset(m->tok_hist, 0, (size_t)c.max_batch * (c.max_seq_len + 1) * 4));
+  FB_CUDA(dev, cudaMalloc(&m->mu_dev, (size_t)c.max_batch * 4));
   FB_CUDA(dev, cudaMalloc(&m->att_done, (size_t)c.max_batch * c.n_kv_head * sizeof(int)));
   FB_CUDA(dev, cudaMemset(m->att_done, 0, (size_t)c.max_batch * c.n_kv_head * sizeof(int)));
   FB_CUDA(dev, cudaMalloc(&m->argmax_key, 8));
@@ -703,7 +713,8 @@ int fb200_llama_free(fb200_llama* m) {
   if (m->output) fb200_qmatrix_free(m->output);
   void* bufs[] = {m->output_norm, m->rope_cos, m->rope_sin, m->x, m->xn, m->q, m->k, m->v, m->att,
                   m->attn_out, m->hbuf, m->gbuf, m->last, m->logits, m->att_part, m->ids, m->next,
-                  m->hist, m->pos_dev, m->step_dev, m->argmax_key, m->att_done, m->best_val, m->best_pair};
+                  m->hist, m->pos_dev, m->step_dev, m->argmax_key, m->att_done, m->best_val, m->best_pair,
+                  m->tok_hist, m->mu_dev};
   for (void* b : bufs) if (b) cudaFree(b);
   for (fb200_packed_act* p : {&m->px, &m->patt, &m->pv, &m->ph}) {
     void* pb[] = {p->limbs, p->xsc, p->xss, p->sumsq};
@@ -807,6 +818,8 @@ int fb200_llama_forward(fb200_llama* m, const uint32_t* tokens_host, int batch, 
   if ((rc = finalize(m))) return rc;
   const size_t rows = (size_t)batch * seq;
   if ((rc = ensure_rows(m, rows))) return rc;
+  FB_CUDA(dev, cudaMemcpy2DAsync(m->tok_hist + m->pos, (size_t)(c.max_seq_len + 1) * 4, tokens_host, (size_t)seq * 4,
+                                 (size_t)seq * 4, batch, cudaMemcpyHostToDevice, dev->stream));
   if (seq == 1 && batch == 1 && (rc = build_fused_program(m))) return rc;
   if (seq == 1 && batch == 1 && m->fused_usable) {
     FB_CUDA(dev, cudaMemcpyAsync(m->ids, tokens_host, 4, cudaMemcpyHostToDevice, dev->stream));
@@ -873,6 +886,11 @@ int fb200_llama_generate_greedy(fb200_llama* m, const uint32_t* tokens_host, int
       dev->launches += m->graph_kernels;
     }
   }
+  // the session's token history: the fed tokens at the old position, the generated ones after it
+  FB_CUDA(dev, cudaMemcpy2DAsync(m->tok_hist + m->pos, (size_t)(c.max_seq_len + 1) * 4, tokens_host, 4, 4, batch,
+                                 cudaMemcpyHostToDevice, dev->stream));
+  FB_CUDA(dev, cudaMemcpy2DAsync(m->tok_hist + m->pos + 1, (size_t)(c.max_seq_len + 1) * 4, m->hist,
+                                 (size_t)m->hist_cap * 4, (size_t)steps * 4, batch, cudaMemcpyDeviceToDevice, dev->stream));
   m->pos += steps;
   // hist is [batch, hist_cap]; gather the first `steps` columns
   std::vector<uint32_t> tmp((size_t)batch * m->hist_cap);
@@ -880,6 +898,66 @@ int fb200_llama_generate_greedy(fb200_llama* m, const uint32_t* tokens_host, int
   if ((rc = finish_blocking(m))) return rc;
   for (int b = 0; b < batch; ++b)
     std::memcpy(out_host + (size_t)b * steps, tmp.data() + (size_t)b * m->hist_cap, (size_t)steps * 4);
+  return FB200_OK;
+}
+
+namespace {
+__global__ void fill_f32_kernel(float* p, float v, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = v;
+}
+}  // namespace
+
+int fb200_llama_generate_sampled(fb200_llama* m, const uint32_t* tokens_host, int batch, int steps,
+                                 const fb200_sampler_config* cfg, uint32_t* out_host) {
+  if (!m) return FB200_ERR_INVALID_ARGUMENT;
+  fb200_device* dev = m->dev;
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  const auto& c = m->cfg;
+  if (!tokens_host || !out_host || !cfg || batch <= 0 || batch > c.max_batch || steps <= 0)
+    return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "generate_sampled: batch %d steps %d", batch, steps);
+  if (m->tp_size > 1)
+    return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "generate_sampled: a tensor-parallel model holds only a shard of the logits");
+  if (m->pos + steps > c.max_seq_len)
+    return fb200_fail(dev, FB200_ERR_CAPACITY, "generate_sampled: position %d + %d exceeds max_seq_len %d", m->pos, steps, c.max_seq_len);
+  if ((rc = finalize(m))) return rc;
+  if ((rc = ensure_rows(m, batch))) return rc;
+  if (batch == 1 && (rc = build_fused_program(m))) return rc;
+  const size_t hstride = (size_t)c.max_seq_len + 1;
+  FB_CUDA(dev, cudaMemcpyAsync(m->ids, tokens_host, (size_t)batch * 4, cudaMemcpyHostToDevice, dev->stream));
+  if (!(batch == 1 && m->fused_usable)) {
+    if ((rc = ensure_graph(m, batch))) return rc;  // may run a warm-up pass over the ids
+    FB_CUDA(dev, cudaMemcpyAsync(m->ids, tokens_host, (size_t)batch * 4, cudaMemcpyHostToDevice, dev->stream));
+  }
+  FB_CUDA(dev, cudaMemcpy2DAsync(m->tok_hist + m->pos, hstride * 4, tokens_host, 4, 4, batch, cudaMemcpyHostToDevice,
+                                 dev->stream));
+  if (cfg->strategy == FB200_SAMPLER_MIROSTAT2) {
+    fill_f32_kernel<<<1, 256, 0, dev->stream>>>(m->mu_dev, cfg->mu, batch < 256 ? batch : 256);
+    FB_LAUNCH_CHECK(dev);
+    if (batch > 256) return fb200_fail(dev, FB200_ERR_CAPACITY, "generate_sampled: at most 256 sequences");
+  }
+  const int pos0 = m->pos;
+  for (int s = 0; s < steps; ++s) {
+    // one new position per sequence (leaves the logits in m->logits and advances the position) ...
+    if (batch == 1 && m->fused_usable) {
+      if ((rc = run_fused(m, 1, false))) return rc;
+    } else {
+      FB_CUDA(dev, cudaGraphLaunch(m->graph_exec, dev->stream));
+      dev->launches += m->graph_kernels;
+    }
+    // ... then the sampler: its id replaces the greedy one as the next step's input and joins the history
+    const int seen = pos0 + s + 1;  // tokens of the session so far, the one just consumed included
+    if ((rc = fb200_launch_sampler(dev, m->logits, (size_t)batch, (size_t)c.vocab, cfg, m->tok_hist, hstride, seen,
+                                   (unsigned long long)seen, m->mu_dev, m->next, m->ids, 1, m->tok_hist + seen, hstride)))
+      return rc;
+  }
+  m->pos += steps;
+  std::vector<uint32_t> tmp((size_t)batch * steps);
+  FB_CUDA(dev, cudaMemcpy2DAsync(tmp.data(), (size_t)steps * 4, m->tok_hist + pos0 + 1, hstride * 4, (size_t)steps * 4,
+                                 batch, cudaMemcpyDeviceToHost, dev->stream));
+  if ((rc = finish_blocking(m))) return rc;
+  std::memcpy(out_host, tmp.data(), tmp.size() * 4);
   return FB200_OK;
 }
 

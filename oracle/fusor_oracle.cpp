@@ -625,6 +625,144 @@ ORACLE_API int oracle_top_k(const float* logits, size_t n, int k, uint32_t* ids,
   return (int)top.size();
 }
 
+
+// ---- samplers: models/kalosm-llama/src/sampler.rs ----------------------------------------------
+// The uniform draw: the reference takes rand::StdRng (third-party); the CUDA path and this oracle
+// use the same counter-based function instead (splitmix64 finaliser of seed, counter and row),
+// top 24 bits as a float in [0, 1 - 2^-24] (the reference clamps to RANDOM_MAX = 0.99999994).
+static float sampler_uniform(uint64_t seed, uint64_t counter, uint32_t row) {
+  uint64_t z = seed + 0x9E3779B97F4A7C15ull * (counter * 65536ull + (uint64_t)row + 1ull);
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z ^= z >> 31;
+  return (float)(z >> 40) * (1.0f / 16777216.0f);
+}
+
+namespace {
+struct SLogit { uint32_t id; float logit; };
+struct WLogit { SLogit l; float w; };
+const float S_EPSILON = 1.0e-20f;  // sampler.rs:6
+
+float normalized_probability(float v, float dflt) {  // sampler.rs:305-311
+  if (!std::isfinite(v)) return dflt;
+  return std::min(std::max(v, 0.0f), 1.0f);
+}
+
+// process_logit (sampler.rs:262-295) over all logits, then sort_logits_desc (:252-259) and the
+// top_k cut (:154-166)
+std::vector<SLogit> processed_top(const float* logits, size_t n, float temperature, float rep_penalty, int range,
+                                  int top_k, const uint32_t* prev, int prev_len) {
+  // previous_tokens_for_config, sampler.rs:297-303
+  int len = std::min(prev_len, range);
+  if (len < 0) len = 0;
+  const uint32_t* pv = prev ? prev + (prev_len - len) : nullptr;
+  std::vector<SLogit> top;
+  top.reserve(n);
+  for (size_t i = 0; i < n; ++i) {
+    float value = logits[i];
+    if (!std::isfinite(value)) continue;
+    if (rep_penalty > 1.0f && pv && std::find(pv, pv + len, (uint32_t)i) != pv + len) {
+      if (value <= 0.0f) value *= rep_penalty;
+      else value /= rep_penalty;
+    }
+    if (temperature != 0.0f) value /= temperature;
+    if (!std::isfinite(value)) continue;
+    top.push_back({(uint32_t)i, value});
+  }
+  // f32::total_cmp descending, then token id descending
+  auto ord = [](float f) { uint32_t b; std::memcpy(&b, &f, 4); return (b & 0x80000000u) ? ~b : (b | 0x80000000u); };
+  std::sort(top.begin(), top.end(), [&](const SLogit& a, const SLogit& b) {
+    uint32_t oa = ord(a.logit), ob = ord(b.logit);
+    if (oa != ob) return oa > ob;
+    return a.id > b.id;
+  });
+  top_k = std::max(top_k, 1);
+  if ((int)top.size() > top_k) top.resize(top_k);
+  return top;
+}
+}  // namespace
+
+// One draw of CpuStandardSampler (strategy 0, sampler.rs:135-241) or CpuMirostat2Sampler (strategy
+// 1, :44-133). Returns the token id, or 0xFFFFFFFF when no logit survives. *margin (optional) is
+// the distance, relative to the candidates' total weight, between the draw's threshold and the
+// nearest cumulative sum: a tiny margin means one ulp of an exponential can change the token.
+ORACLE_API uint32_t oracle_sample(const float* logits, size_t n, int strategy, float temperature, float rep_penalty,
+                                  int range, int top_k, float top_p_in, float min_p_in, float tau, float eta, float* mu,
+                                  const uint32_t* prev, int prev_len, uint64_t seed, uint64_t counter, uint32_t row,
+                                  float* margin) {
+  if (margin) *margin = 1.0f;
+  std::vector<SLogit> top = processed_top(logits, n, temperature, rep_penalty, range, top_k, prev, prev_len);
+  if (top.empty()) return 0xFFFFFFFFu;
+  const float u = sampler_uniform(seed, counter, row);
+  const float max = top[0].logit;
+  auto note = [&](float cum, float thr, float total) {
+    if (margin) *margin = std::min(*margin, std::fabs(cum - thr) / total);
+  };
+  if (strategy == 0) {
+    if (temperature <= 0.0f) return top[0].id;
+    std::vector<WLogit> cand;
+    for (auto& l : top) cand.push_back({l, std::exp(l.logit - max)});
+    float min_p = normalized_probability(min_p_in, 0.0f);
+    if (min_p > 0.0f) {
+      float thr = cand[0].w * min_p;
+      std::vector<WLogit> kept;
+      for (auto& c : cand) if (c.w >= thr) kept.push_back(c);
+      cand.swap(kept);
+    }
+    float top_p = normalized_probability(top_p_in, 1.0f);
+    if (top_p < 1.0f) {
+      float total = 0.f;
+      for (auto& c : cand) total += c.w;
+      total = std::max(total, S_EPSILON);
+      float thr = total * top_p, cum = 0.f;
+      size_t cutoff = 0;
+      for (size_t i = 0; i < cand.size(); ++i) {
+        cum += cand[i].w;
+        cutoff = i + 1;
+        note(cum, thr, total);
+        if (cum >= thr) break;
+      }
+      cand.resize(std::max<size_t>(cutoff, 1));
+    }
+    float total = 0.f;
+    for (auto& c : cand) total += c.w;
+    total = std::max(total, S_EPSILON);
+    float thr = u * total, cum = 0.f;
+    for (auto& c : cand) {
+      cum += c.w;
+      note(cum, thr, total);
+      if (cum >= thr) return c.l.id;
+    }
+    return cand.back().l.id;
+  }
+  // Mirostat 2
+  float total = 0.f;
+  for (auto& l : top) total += std::exp(l.logit - max);
+  total = std::max(total, S_EPSILON);
+  size_t cutoff = top.size();
+  for (size_t i = 0; i < top.size(); ++i) {
+    float p = std::max(std::exp(top[i].logit - max) / total, S_EPSILON);
+    if (-std::log2(p) > *mu) { cutoff = std::max<size_t>(i, 1); break; }
+  }
+  cutoff = std::min(cutoff, top.size());
+  float csum = 0.f;
+  for (size_t i = 0; i < cutoff; ++i) csum += std::exp(top[i].logit - max);
+  csum = std::max(csum, S_EPSILON);
+  float thr = u * csum, cum = 0.f;
+  SLogit sel = top[0];
+  float selw = std::exp(sel.logit - max);
+  for (size_t i = 0; i < cutoff; ++i) {
+    float w = std::exp(top[i].logit - max);
+    cum += w;
+    note(cum, thr, csum);
+    if (cum >= thr) { sel = top[i]; selw = w; break; }
+  }
+  float psel = std::max(selw / csum, S_EPSILON);
+  float next_mu = *mu - eta * (-std::log2(psel) - tau);
+  if (std::isfinite(next_mu)) *mu = next_mu;
+  return sel.id;
+}
+
 // ---- synthetic-weight quantisers ------------------------------------------------------------
 // The reference only loads pre-quantised GGUF files; it has no f32 -> Q4_0/Q4_K/Q6_K encoder.
 // These encoders are this project's own (simple min/max and absmax rounding). Their only duty

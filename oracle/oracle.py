@@ -56,6 +56,8 @@ def lib():
                                         f32p, i32, i32, f32p]),
             "oracle_kv_capacity": (sz, [sz, sz]),
             "oracle_top_k": (i32, [f32p, sz, i32, u32p, f32p]),
+            "oracle_sample": (u32, [f32p, sz, i32, f32, f32, i32, i32, f32, f32, f32, f32, f32p, u32p, i32, u64, u64,
+                                    u32, f32p]),
             "oracle_quantize": (i32, [f32p, sz, u32, u8p]),
             "oracle_normal": (None, [u64, f32, sz, f32p]),
             "oracle_random_qweights": (i32, [u64, f32, sz, u32, u8p]),
@@ -176,6 +178,21 @@ def top_k(logits, k):
     vals = np.empty(max(k, 1), dtype=np.float32)
     n = lib().oracle_top_k(_p(logits), logits.size, k, _p(ids), _p(vals))
     return ids[:n], vals[:n]
+
+
+def sample(logits, *, strategy=0, temperature=1.0, repetition_penalty=1.0, repetition_penalty_range=64, top_k=64,
+           top_p=float("nan"), min_p=float("nan"), tau=5.0, eta=0.1, mu=None, previous=None, seed=0, counter=0, row=0):
+    """One draw of the reference's CPU sampler (models/kalosm-llama/src/sampler.rs) on one row of logits.
+    Returns (token id, margin, new mu): margin = relative distance of the draw from the nearest
+    cumulative boundary; mu only for Mirostat 2 (strategy 1)."""
+    logits = _f32(logits).reshape(-1)
+    prev = None if previous is None else np.ascontiguousarray(previous, dtype=np.uint32).reshape(-1)
+    mu_arr = np.array([10.0 if mu is None else mu], dtype=np.float32)
+    margin = np.ones(1, dtype=np.float32)
+    tok = lib().oracle_sample(_p(logits), logits.size, strategy, temperature, repetition_penalty,
+                              repetition_penalty_range, top_k, top_p, min_p, tau, eta, _p(mu_arr), _p(prev),
+                              0 if prev is None else prev.size, seed, counter, row, _p(margin))
+    return int(tok), float(margin[0]), float(mu_arr[0])
 
 
 def quantize(x, ty):

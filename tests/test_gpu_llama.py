@@ -130,27 +130,46 @@ def test_model_loaded_from_a_gguf_file_equals_the_directly_built_one(dev, tmp_pa
 
 def test_decoder_at_llama3_8b_widths(dev):
     # the program the benchmark times, two layers deep: hidden 4096, FFN 14336, 32/8 heads of 128,
-    # vocabulary 128256, Q4_K body with Q6_K attn_v / ffn_down / output head. Checks the prompt
-    # pass, single steps through forward() (one fused launch per step) and 32 greedy ids out of
-    # one generate_greedy launch (the persistent kernel running 32 steps) against the oracle.
+    # vocabulary 128256, Q4_K body with Q6_K attn_v / ffn_down / output head.
     cfg = dict(llama3_8b_cfg(ctx=256), n_layer=2)
     gpu, cpu = build_models(dev, cfg, batch=1, seed=7)
     rng = np.random.default_rng(8)
     prompt = rng.integers(0, cfg["vocab"], size=(1, 64), dtype=np.uint32)
-    lg, nxt = gpu.forward(prompt)
     lo = cpu.forward(prompt)
+    want = O.top_k(lo[0], 1)[0][0]
+    # (1) The prompt pass runs the products and the attention on fp16 tensor-core operands. Each
+    # of its 15 operations is held to 2e-3 relative L2 on its own (test_gpu_quant, test_gpu_ops);
+    # chained through two layers and the head the rounding compounds (about sqrt(15) x 5e-4 per
+    # operation, amplified by the norms), so the end-to-end bound for the logits is 8e-3, and the
+    # greedy id must agree unless the oracle's own margin is inside the logit error.
+    lg, nxt = gpu.forward(prompt)
     assert lg.shape == (1, cfg["vocab"])
-    assert F.rel_l2(lg, lo) < 2e-3, F.rel_l2(lg, lo)
-    tok = np.array([O.top_k(lo[0], 1)[0][0]], dtype=np.uint32)
-    assert nxt[0] == tok[0] or _margin(lo)[0] < 4 * np.max(np.abs(lg - lo))
+    err = F.rel_l2(lg, lo)
+    print(f"8B-width prefill (tensor cores): rel-L2 of the logits {err:.2e}")
+    assert err < 8e-3, err
+    assert nxt[0] == want or _margin(lo)[0] < 4 * np.max(np.abs(lg - lo))
+    # (2) The decode path (the fused persistent kernel: integer-limb products, exact to ~1e-6) is
+    # held to 2e-3 on the logits of every step. To keep the prompt pass's fp16 rounding out of its
+    # KV cache, the same prompt is fed again position by position through that path.
+    gpu.reset()
+    for i in range(prompt.shape[1]):
+        lg, nxt = gpu.forward(prompt[:, i:i + 1])
+    err = F.rel_l2(lg, lo)
+    print(f"8B-width prompt through the decode path: rel-L2 of the logits {err:.2e}")
+    assert err < 2e-3, err
+    assert nxt[0] == want or _margin(lo)[0] < 4 * np.max(np.abs(lg - lo))
+    tok = np.array([want], dtype=np.uint32)
+    worst = 0.0
     for step in range(6):
         lo = cpu.forward(tok[:, None])
         lg, nxt = gpu.forward(tok[:, None])
-        err = np.max(np.abs(lg - lo))
+        worst = max(worst, F.rel_l2(lg, lo))
         assert F.rel_l2(lg, lo) < 2e-3, (step, F.rel_l2(lg, lo))
         want = O.top_k(lo[0], 1)[0][0]
-        assert nxt[0] == want or _margin(lo)[0] < 4 * err, (step, nxt[0], want)
+        assert nxt[0] == want or _margin(lo)[0] < 4 * np.max(np.abs(lg - lo)), (step, nxt[0], want)
         tok = np.array([want], dtype=np.uint32)
+    print(f"8B-width decode steps: worst rel-L2 of the logits {worst:.2e}")
+    # (3) 32 greedy ids out of ONE generate_greedy launch (the persistent kernel running 32 steps)
     first = tok.copy()
     gpu_tokens = gpu.generate_greedy(first, 32)[0]
     assert dev.status() == 0

@@ -274,3 +274,27 @@ def test_frozen_conformance_vectors():
             assert np.array_equal(O.q_mat_mul(x, raw, ty, n, k), gold[name + "_y"])
     finally:
         O.set_threads(0)
+
+
+def test_sampler_properties_of_the_reference_tests():
+    # models/kalosm-llama/src/sampler.rs:372-441 restated on the oracle's samplers (with the
+    # counter-based draw in place of rand::StdRng): flat logits reach past the first sorted
+    # candidate, top-p 0.5 keeps the first two of four, min-p 0.1 keeps only the leader, and
+    # Mirostat's cut-off keeps every candidate when no surprise exceeds mu.
+    flat = np.zeros(4, np.float32)
+    assert {O.sample(flat, top_k=4, seed=s)[0] for s in range(64)} - {3}
+    assert {O.sample(flat, top_k=4, seed=s, strategy=1, mu=10.0)[0] for s in range(64)} - {3}
+    assert {O.sample(flat, top_k=4, top_p=0.5, seed=s)[0] for s in range(64)} <= {2, 3}
+    assert O.sample(np.array([-5.0, -4.0, -3.0, 0.0], np.float32), top_k=4, min_p=0.1, seed=0)[0] == 3
+    # sort order: descending value, ties -> higher id (sampler.rs:252-259); temperature 0 = first
+    assert O.sample(np.array([1.0, 2.0, 2.0, 0.5], np.float32), temperature=0.0, top_k=2)[0] == 2
+    # repetition penalty (sampler.rs:272-279): positive logits divided, non-positive multiplied
+    lg = np.array([2.0, 1.9, -0.1, -0.2], np.float32)
+    assert O.sample(lg, temperature=0.0, top_k=4, repetition_penalty=2.0, previous=[0])[0] == 1
+    assert O.sample(lg, temperature=0.0, top_k=4, repetition_penalty=2.0, previous=[0, 1])[0] == 1
+    assert O.sample(lg, temperature=0.0, top_k=4, repetition_penalty=30.0, previous=[0, 1])[0] == 1
+    assert O.sample(lg, temperature=0.0, top_k=4, repetition_penalty=30.0, previous=[0, 1, 2])[0] == 1
+    # only the last `range` previous tokens count (sampler.rs:297-303)
+    assert O.sample(lg, temperature=0.0, top_k=4, repetition_penalty=2.0, repetition_penalty_range=1,
+                    previous=[0, 3])[0] == 0
+    assert O.sample(np.full(8, np.nan, np.float32), top_k=4)[0] == 0xFFFFFFFF
