@@ -126,14 +126,16 @@ FB200_API int fb200_qmatrix_concat_rows(const fb200_qmatrix* const* ms, int n, f
  *   FB200_EPI_RESIDUAL  y = (W.x + r1) + r2          (r2 may be NULL) — down/O projection with
  *                       residual adds, models/kalosm-llama/src/raw/attention_layer.rs:147-174
  *   FB200_EPI_SWIGLU    W is [gate; up] row-concatenated (2F rows); y[M, F] =
- *                       silu(gate.x) * (up.x) — attention_layer.rs:184-196 */
+ *                       silu(gate.x) * (up.x) — attention_layer.rs:184-196
+ *   FB200_EPI_BIAS      y = W.x + bias, bias = r1 of shape [N] shared by all rows — Linear with a
+ *                       bias, fusor-ml/fusor/src/layers/linear.rs:93-121 (r2 must be NULL) */
 typedef enum fb200_epilogue_kind {
-  FB200_EPI_NONE = 0, FB200_EPI_RESIDUAL = 1, FB200_EPI_SWIGLU = 2
+  FB200_EPI_NONE = 0, FB200_EPI_RESIDUAL = 1, FB200_EPI_SWIGLU = 2, FB200_EPI_BIAS = 3
 } fb200_epilogue_kind;
 
 typedef struct fb200_epilogue {
   int kind;
-  const float* r1_dev; /* [M, N] */
+  const float* r1_dev; /* [M, N]; FB200_EPI_BIAS: [N] */
   const float* r2_dev; /* [M, N] or NULL */
 } fb200_epilogue;
 
@@ -304,6 +306,11 @@ FB200_API int fb200_llama_free(fb200_llama* m);
  * (raw/mod.rs:480-486). */
 FB200_API int fb200_llama_set_tensor(fb200_llama* m, int layer, int which, uint32_t ggml_type,
                            uint64_t n, uint64_t k, const void* bytes_host, size_t nbytes);
+/* The rope_freqs.weight tensor of a checkpoint (head_dim / 2 f32 values): multiplied into the
+ * inverse frequencies after the Llama-3 scaling, as create_inverse_frequency does
+ * (models/kalosm-llama/src/raw/rope.rs:9-52; loaded at raw/mod.rs:417-421). Rebuilds the model's
+ * RoPE tables; call before the first forward pass. */
+FB200_API int fb200_llama_set_rope_freqs(fb200_llama* m, const float* weights_host, size_t n);
 FB200_API int fb200_llama_reset(fb200_llama* m);
 /* Rewinds the model's KV caches to the first `len` positions (0 <= len <= position): the next
  * forward pass continues from there (raw/mod.rs:769-793 keeps the common prefix of the cached

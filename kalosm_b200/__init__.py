@@ -28,7 +28,7 @@ ERR_INVALID_SHAPE, ERR_UNSUPPORTED_DTYPE, ERR_CAPACITY, ERR_CUDA = -1, -2, -3, -
 ERR_INVALID_ARGUMENT, ERR_TIMEOUT, ERR_DEVICE_MISMATCH, ERR_NCCL = -5, -6, -7, -8
 COMM_ID_BYTES = 128
 IPC_HANDLE_BYTES = 64
-EPI_NONE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+EPI_NONE, EPI_RESIDUAL, EPI_SWIGLU, EPI_BIAS = 0, 1, 2, 3
 MASK_NONE, MASK_CAUSAL, MASK_QK, MASK_BATCH_KEY = 0, 1, 2, 3
 
 
@@ -83,7 +83,7 @@ EXPORTS = [
     "fb200_llama_generate_sampled", "fb200_kv_cache_create",
     "fb200_kv_cache_free", "fb200_kv_cache_reset", "fb200_kv_cache_truncate", "fb200_kv_cache_len", "fb200_kv_cache_append",
     "fb200_kv_cache_buffers", "fb200_flash_attention", "fb200_llama_create", "fb200_llama_free",
-    "fb200_llama_set_tensor", "fb200_llama_reset", "fb200_llama_truncate", "fb200_llama_position", "fb200_llama_forward",
+    "fb200_llama_set_tensor", "fb200_llama_set_rope_freqs", "fb200_llama_reset", "fb200_llama_truncate", "fb200_llama_position", "fb200_llama_forward",
     "fb200_llama_generate_greedy", "fb200_llama_logits_dev", "fb200_llama_set_tensor_parallel",
     "fb200_comm_unique_id", "fb200_comm_create", "fb200_comm_destroy", "fb200_comm_all_reduce_sum",
     "fb200_comm_exchange_handle", "fb200_comm_exchange_attach", "fb200_exchange_wait_check",
@@ -150,6 +150,7 @@ def load_library():
         "fb200_llama_create": (i32, [vp, C.POINTER(LlamaConfig), pp]),
         "fb200_llama_free": (i32, [vp]),
         "fb200_llama_set_tensor": (i32, [vp, i32, i32, u32, u64, u64, vp, sz]),
+        "fb200_llama_set_rope_freqs": (i32, [vp, vp, sz]),
         "fb200_llama_reset": (i32, [vp]),
         "fb200_llama_truncate": (i32, [vp, i32]),
         "fb200_llama_position": (i32, [vp, C.POINTER(i32)]),
@@ -220,7 +221,7 @@ class Tensor:
         n_out = n // 2 if epilogue == EPI_SWIGLU else n
         out_shape = (self.shape[:-1] if len(self.shape) > 1 else ()) + (n_out,)
         for name, t in (("out", out), ("r1", r1), ("r2", r2)):
-            self._require_f32(name, t, m * n_out)
+            self._require_f32(name, t, n_out if name == "r1" and epilogue == EPI_BIAS else m * n_out)
         y = out if out is not None else Tensor(self.device, out_shape, np.float32)
         ep = _Epilogue(epilogue, r1.ptr if r1 is not None else None, r2.ptr if r2 is not None else None)
         d = self.device
@@ -618,6 +619,11 @@ class Llama:
         d = self.device
         d._check(d.lib.fb200_llama_set_tensor(self.h, layer, self.TENSORS[name], ggml_type, n, k,
                                               _hp(raw8), raw8.size))
+
+    def set_rope_freqs(self, weights) -> None:
+        """rope_freqs.weight of a checkpoint: per-frequency factors multiplied into the inverse frequencies."""
+        w = np.ascontiguousarray(weights, dtype=np.float32).reshape(-1)
+        self.device._check(self.device.lib.fb200_llama_set_rope_freqs(self.h, _hp(w), w.size))
 
     def reset(self) -> None:
         self.device._check(self.device.lib.fb200_llama_reset(self.h))

@@ -3,14 +3,16 @@
 #include <cstdlib>
 #include <cstring>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "common.cuh"
 
 size_t fb200_xpack_bytes(int mp, uint64_t kp);
 int fb200_qgemv_chunk(fb200_device* dev, const fb200_qmatrix* w, const float* x, int mc, float* y,
-                      int epi, const float* r1, const float* r2, void* scratch);
+                      int epi, const float* r1, const float* r2, void* scratch, bool r1_is_bias);
 int fb200_dense_matmul(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_t m, float* y);
-int fb200_qgemm(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_t m, float* y, const float* r1,
-                const float* r2, int swiglu);
+int fb200_qgemm(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_t m, float* y, bool r1_is_bias,
+                const float* r1, const float* r2, int swiglu);
 bool fb200_qgemv1_fits(const fb200_qmatrix* w);
 int fb200_qgemv1(fb200_device* dev, const fb200_qmatrix* w, const float* x, const float* xres,
                  const float* norm_w, float eps, float* y, int epi, const float* r1, const float* r2);
@@ -29,6 +31,29 @@ int fb200_fail(fb200_device* dev, int code, const char* fmt, ...) {
   vsnprintf(dst, 512, fmt, ap);
   va_end(ap);
   return code;
+}
+
+fb200_op_trace::fb200_op_trace(fb200_device* d, const char* n, double b) : dev(d), name(n), bytes(b), timed(false) {
+  nvtxRangePushA(name);
+  if (!dev || !dev->trace || dev->capturing) return;
+  if (dev->trace_depth++ == 0 && dev->trace_ev[0]) {
+    timed = cudaEventRecord(dev->trace_ev[0], dev->stream) == cudaSuccess;
+  }
+}
+
+fb200_op_trace::~fb200_op_trace() {
+  nvtxRangePop();
+  if (!dev || !dev->trace || dev->capturing) return;
+  --dev->trace_depth;
+  if (!timed) return;
+  float ms = 0.f;
+  if (cudaEventRecord(dev->trace_ev[1], dev->stream) == cudaSuccess &&
+      cudaEventSynchronize(dev->trace_ev[1]) == cudaSuccess &&
+      cudaEventElapsedTime(&ms, dev->trace_ev[0], dev->trace_ev[1]) == cudaSuccess) {
+    const double us = (double)ms * 1e3;
+    if (bytes > 0) fprintf(stderr, "fb200 trace: %-26s %10.2f us %9.1f GB/s\n", name, us, bytes / us / 1e3);
+    else fprintf(stderr, "fb200 trace: %-26s %10.2f us\n", name, us);
+  }
 }
 
 int fb200_bind(fb200_device* dev) {
@@ -101,6 +126,9 @@ int fb200_device_create(int ordinal, void* stream, fb200_device** out) {
   cudaDeviceGetAttribute(&d->sm_count, cudaDevAttrMultiProcessorCount, ordinal);
   if (const char* e = getenv("FB200_PDL")) d->pdl = e[0] != '0';
   if (const char* e = getenv("FB200_POISON")) d->poison = e[0] == '1';
+  if (const char* e = getenv("FB200_TRACE")) d->trace = e[0] == '1';
+  if (d->trace && (cudaEventCreate(&d->trace_ev[0]) != cudaSuccess || cudaEventCreate(&d->trace_ev[1]) != cudaSuccess))
+    d->trace = false;
   if (const char* e = getenv("FB200_SCRATCH_LIMIT")) d->scratch_limit = (size_t)strtoull(e, nullptr, 10);
   if ((e = cudaMalloc(&d->status, sizeof(int))) != cudaSuccess ||
       (e = cudaMemsetAsync(d->status, 0, sizeof(int), d->stream)) != cudaSuccess ||
@@ -123,6 +151,7 @@ int fb200_device_destroy(fb200_device* dev) {
   if (dev->normed) cudaFree(dev->normed);
   if (dev->status) cudaFree(dev->status);
   if (dev->status_host) cudaFreeHost(dev->status_host);
+  for (cudaEvent_t e : dev->trace_ev) if (e) cudaEventDestroy(e);
   if (dev->fused) cudaFree(dev->fused);
   if (dev->own_stream) cudaStreamDestroy(dev->stream);
   delete dev;
@@ -373,11 +402,20 @@ int fb200_q_mat_mul(fb200_device* dev, const float* x_dev, size_t m, const fb200
   if (!w || !x_dev || !y_dev) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "q_mat_mul: null argument");
   if (w->dev != dev)
     return fb200_fail(dev, FB200_ERR_DEVICE_MISMATCH, "q_mat_mul: weight lives on another device handle");
-  const int epi = ep ? ep->kind : FB200_EPI_NONE;
-  if (epi < 0 || epi > 2) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "q_mat_mul: epilogue kind %d", epi);
-  if (epi == FB200_EPI_RESIDUAL && !ep->r1_dev)
-    return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "q_mat_mul: residual epilogue without r1");
+  int epi = ep ? ep->kind : FB200_EPI_NONE;
+  if (epi < 0 || epi > 3) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "q_mat_mul: epilogue kind %d", epi);
+  if ((epi == FB200_EPI_RESIDUAL || epi == FB200_EPI_BIAS) && !ep->r1_dev)
+    return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "q_mat_mul: residual / bias epilogue without r1");
+  // Linear's bias (fusor-ml/fusor/src/layers/linear.rs:93-121) is the residual epilogue with one
+  // row shared by all activation rows
+  const bool bias = epi == FB200_EPI_BIAS;
+  if (bias) {
+    if (ep->r2_dev) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "q_mat_mul: the bias epilogue takes r1 only");
+    epi = FB200_EPI_RESIDUAL;
+  }
   if (m == 0 || w->n == 0) return FB200_OK;
+  fb200_op_trace scope(dev, m == 1 ? "q_mat_mul (1 row)" : m <= 32 ? "q_mat_mul (2..32 rows)" : "q_mat_mul (> 32 rows)",
+                       (double)w->raw_nbytes + 4.0 * (double)m * (double)(w->k + w->n));
   if (!w->tiled) {
     if (epi != FB200_EPI_NONE)
       return fb200_fail(dev, FB200_ERR_UNSUPPORTED_DTYPE, "q_mat_mul: epilogues need Q4_0/Q8_0/Q4_K/Q6_K weights");
@@ -389,7 +427,7 @@ int fb200_q_mat_mul(fb200_device* dev, const float* x_dev, size_t m, const fb200
     return fb200_qgemv1(dev, w, x_dev, nullptr, nullptr, 0.f, y_dev, epi, ep ? ep->r1_dev : nullptr,
                         ep ? ep->r2_dev : nullptr);
   if (m > 32) {
-    rc = fb200_qgemm(dev, w, x_dev, m, y_dev, epi == FB200_EPI_RESIDUAL ? ep->r1_dev : nullptr,
+    rc = fb200_qgemm(dev, w, x_dev, m, y_dev, bias, epi == FB200_EPI_RESIDUAL ? ep->r1_dev : nullptr,
                      epi == FB200_EPI_RESIDUAL ? ep->r2_dev : nullptr, epi == FB200_EPI_SWIGLU ? 1 : 0);
     if (rc != 1) return rc;  // 1 = shape not covered by the tensor-core GEMM; fall through
   }
@@ -402,8 +440,8 @@ int fb200_q_mat_mul(fb200_device* dev, const float* x_dev, size_t m, const fb200
   for (size_t m0 = 0; m0 < m; m0 += 32) {
     const int mc = (int)((m - m0) < 32 ? (m - m0) : 32);
     rc = fb200_qgemv_chunk(dev, w, x_dev + m0 * w->k, mc, y_dev + m0 * n_out, epi,
-                           ep && ep->r1_dev ? ep->r1_dev + m0 * n_out : nullptr,
-                           ep && ep->r2_dev ? ep->r2_dev + m0 * n_out : nullptr, dev->xpack);
+                           ep && ep->r1_dev ? ep->r1_dev + (bias ? 0 : m0 * n_out) : nullptr,
+                           ep && ep->r2_dev ? ep->r2_dev + m0 * n_out : nullptr, dev->xpack, bias);
     if (rc) return rc;
   }
   return FB200_OK;
@@ -418,7 +456,13 @@ int fb200_rms_norm_q_mat_mul(fb200_device* dev, const float* x_dev, const float*
     return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "rms_norm_q_mat_mul: null argument");
   if (w->dev != dev)
     return fb200_fail(dev, FB200_ERR_DEVICE_MISMATCH, "rms_norm_q_mat_mul: weight lives on another device handle");
+  fb200_epilogue one_row;
+  if (ep && ep->kind == FB200_EPI_BIAS && m == 1 && ep->r1_dev && !ep->r2_dev) {
+    one_row = {FB200_EPI_RESIDUAL, ep->r1_dev, nullptr};  // one activation row: a bias row is a residual row
+    ep = &one_row;
+  }
   const int epi = ep ? ep->kind : FB200_EPI_NONE;
+  fb200_op_trace scope(dev, "rms_norm + q_mat_mul", (double)w->raw_nbytes + 4.0 * (double)m * (double)(w->k + w->n));
   if (m == 1 && w->tiled && fb200_qgemv1_fits(w) && epi >= 0 && epi <= 2 &&
       !(epi == FB200_EPI_SWIGLU && (w->ntiles % 2 != 0 || w->n % 32 != 0)) &&
       !(epi == FB200_EPI_RESIDUAL && !ep->r1_dev))

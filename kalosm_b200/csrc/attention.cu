@@ -510,6 +510,8 @@ int fb200_flash_attention(fb200_device* dev, const float* q_dev, const void* k_d
     return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "attention: bad shape");
   if (mask_kind < 0 || mask_kind > 3 || (mask_kind >= 2 && !mask_dev))
     return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "attention: mask kind %d", mask_kind);
+  fb200_op_trace scope(dev, sq == 1 ? "attention (decode)" : "attention (prefill)",
+                       4.0 * (double)b * hkv * (double)skv * d + 8.0 * (double)b * h * (double)sq * d);
   if (sq == 1 && skv > 0 && (mask_kind == 0 || !mask_dev) && h % hkv == 0 && h / hkv <= DEC_ROWS && (d == 64 || d == 128)) {
     // decode form: enough (batch, KV head, split) items to fill the GPU twice, at least 64 keys each
     int ns = (2 * dev->sm_count + b * hkv - 1) / (b * hkv);

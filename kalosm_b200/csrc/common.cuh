@@ -38,6 +38,11 @@ struct fb200_device {
   size_t scratch_total = 0, scratch_limit = 0;
   uint64_t scratch_gen = 0;
   bool poison = false;
+  // FB200_TRACE=1: every operation entry point reports its device time (and GB/s of the bytes it
+  // must move) on stderr; off inside a stream capture
+  bool trace = false, capturing = false;
+  int trace_depth = 0;
+  cudaEvent_t trace_ev[2] = {nullptr, nullptr};
   // scratch of the fused decode-step kernel: grid barrier word, split-unit partials, counters
   void* fused = nullptr;
   size_t fused_bytes = 0;
@@ -98,6 +103,20 @@ inline int fb200_launch(fb200_device* dev, void (*kern)(KArgs...), dim3 grid, di
   dev->launches++;
   return FB200_OK;
 }
+
+// Scope of one operation for the per-operation trace (the counterpart of the reference's
+// tracing spans around a forward pass, models/kalosm-llama/src/model/mod.rs:48-74, 112-116): an
+// NVTX range named after the operation, and with FB200_TRACE=1 a line on stderr with the
+// operation's device time in microseconds and the GB/s of its algorithmic bytes. Timing an
+// operation waits for it, so the trace serialises the stream; nested scopes report the outermost.
+struct fb200_op_trace {
+  fb200_device* dev;
+  const char* name;
+  double bytes;
+  bool timed;
+  fb200_op_trace(fb200_device* dev, const char* name, double bytes);
+  ~fb200_op_trace();
+};
 
 // Makes the handle's device current for the calling thread.
 int fb200_bind(fb200_device* dev);

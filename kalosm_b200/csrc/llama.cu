@@ -17,8 +17,8 @@
 #include "packed_act.cuh"
 
 void fb200_rope_tables_host(int head_dim, int ctx, float theta, float factor, float low_ff,
-                            float high_ff, int original_ctx, std::vector<float>& cs,
-                            std::vector<float>& sn);
+                            float high_ff, int original_ctx, const float* freq_weight,
+                            std::vector<float>& cs, std::vector<float>& sn);
 int fb200_launch_rms_norm_strided(fb200_device* dev, const float* x, size_t x_stride,
                                   const float* res, const float* w, float eps, size_t rows,
                                   size_t n, float* y);
@@ -586,8 +586,10 @@ int ensure_graph(fb200_llama* m, int batch) {
   const uint64_t launches_before = dev->launches;
   cudaGraph_t graph = nullptr;
   FB_CUDA(dev, cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeThreadLocal));
+  dev->capturing = true;  // no event timing inside a capture
   rc = run_forward(m, batch, 1);
   if (!rc) rc = launch_advance(m, batch, 1, true);
+  dev->capturing = false;
   cudaError_t e = cudaStreamEndCapture(dev->stream, &graph);
   m->graph_kernels = dev->launches - launches_before;
   dev->launches = launches_before;  // capture enqueues nothing
@@ -635,7 +637,7 @@ int fb200_llama_create(fb200_device* dev, const fb200_llama_config* cfg, fb200_l
   if (const char* e = getenv("FB200_FUSED")) m->fused_enabled = !(e[0] == '0' && e[1] == 0);
   std::vector<float> cs, sn;
   fb200_rope_tables_host(c.head_dim, c.max_seq_len, c.rope_theta, c.rope_factor,
-                         c.rope_low_freq_factor, c.rope_high_freq_factor, c.rope_original_ctx, cs, sn);
+                         c.rope_low_freq_factor, c.rope_high_freq_factor, c.rope_original_ctx, nullptr, cs, sn);
   FB_CUDA(dev, cudaMalloc(&m->rope_cos, cs.size() * 4));
   FB_CUDA(dev, cudaMalloc(&m->rope_sin, sn.size() * 4));
   FB_CUDA(dev, cudaMemcpy(m->rope_cos, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice));
@@ -771,6 +773,24 @@ int fb200_llama_set_tensor(fb200_llama* m, int layer, int which, uint32_t ggml_t
   if (*slot) { fb200_qmatrix_free(*slot); *slot = nullptr; }
   const uint64_t shape[2] = {n, k};
   return fb200_qmatrix_from_raw_bytes(dev, shape, 2, bytes_host, nbytes, ggml_type, slot);
+}
+
+int fb200_llama_set_rope_freqs(fb200_llama* m, const float* weights_host, size_t n) {
+  if (!m) return FB200_ERR_INVALID_ARGUMENT;
+  fb200_device* dev = m->dev;
+  int rc = fb200_bind(dev);
+  if (rc) return rc;
+  const auto& c = m->cfg;
+  if (m->finalized) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "llama: the RoPE tables are frozen after the first forward pass");
+  if (!weights_host || n != (size_t)c.head_dim / 2)
+    return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "llama: rope_freqs needs head_dim / 2 = %d values, got %zu", c.head_dim / 2, n);
+  std::vector<float> cs, sn;
+  fb200_rope_tables_host(c.head_dim, c.max_seq_len, c.rope_theta, c.rope_factor, c.rope_low_freq_factor,
+                         c.rope_high_freq_factor, c.rope_original_ctx, weights_host, cs, sn);
+  FB_CUDA(dev, cudaMemcpyAsync(m->rope_cos, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, dev->stream));
+  FB_CUDA(dev, cudaMemcpyAsync(m->rope_sin, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice, dev->stream));
+  FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  return FB200_OK;
 }
 
 int fb200_llama_reset(fb200_llama* m) {

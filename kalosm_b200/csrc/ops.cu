@@ -127,9 +127,11 @@ argmax_kernel(const float* __restrict__ logits, size_t n, uint32_t* __restrict__
 }  // namespace
 
 // Host-side table build, models/kalosm-llama/src/raw/rope.rs:9-85 (f32 arithmetic as there).
+// `freq_weight` (optional, head_dim / 2 values): the rope_freqs.weight tensor of a checkpoint, which
+// the reference multiplies into the inverse frequencies after the scaling (rope.rs:40-49).
 void fb200_rope_tables_host(int head_dim, int ctx, float theta, float factor, float low_ff,
-                            float high_ff, int original_ctx, std::vector<float>& cs,
-                            std::vector<float>& sn) {
+                            float high_ff, int original_ctx, const float* freq_weight,
+                            std::vector<float>& cs, std::vector<float>& sn) {
   const int half = head_dim / 2;
   std::vector<float> inv(half);
   for (int i = 0; i < half; ++i) inv[i] = 1.0f / powf(theta, (float)(2 * i) / (float)head_dim);
@@ -147,6 +149,8 @@ void fb200_rope_tables_host(int head_dim, int ctx, float theta, float factor, fl
       }
     }
   }
+  if (freq_weight)
+    for (int i = 0; i < half; ++i) inv[i] = inv[i] * freq_weight[i];
   cs.resize((size_t)ctx * half);
   sn.resize((size_t)ctx * half);
   for (int p = 0; p < ctx; ++p)
@@ -202,6 +206,7 @@ int fb200_rms_norm(fb200_device* dev, const float* x_dev, const float* residual_
   int rc = fb200_bind(dev);
   if (rc) return rc;
   if (!x_dev || !weight_dev || !y_dev) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "rms_norm: null argument");
+  fb200_op_trace scope(dev, "rms_norm", 8.0 * (double)rows * (double)n);
   return fb200_launch_rms_norm(dev, x_dev, residual_dev, weight_dev, bias_dev, eps, rows, n, y_dev);
 }
 
@@ -210,6 +215,7 @@ int fb200_silu_mul(fb200_device* dev, const float* gate_dev, const float* up_dev
   int rc = fb200_bind(dev);
   if (rc) return rc;
   if (n == 0) return FB200_OK;
+  fb200_op_trace scope(dev, "silu_mul", 12.0 * (double)n);
   silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(gate_dev, up_dev, n, out_dev);
   FB_LAUNCH_CHECK(dev);
   return FB200_OK;
@@ -224,7 +230,7 @@ int fb200_rope_tables(fb200_device* dev, int head_dim, int ctx, float theta, flo
     return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "rope_tables: head_dim %d ctx %d", head_dim, ctx);
   std::vector<float> cs, sn;
   fb200_rope_tables_host(head_dim, ctx, theta, factor, low_freq_factor, high_freq_factor,
-                         original_ctx, cs, sn);
+                         original_ctx, nullptr, cs, sn);
   FB_CUDA(dev, cudaMemcpyAsync(cos_dev, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, dev->stream));
   FB_CUDA(dev, cudaMemcpyAsync(sin_dev, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice, dev->stream));
   FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
@@ -237,6 +243,7 @@ int fb200_rope_pair(fb200_device* dev, float* q_dev, float* k_dev, int b, int h,
   int rc = fb200_bind(dev);
   if (rc) return rc;
   if (d % 2) return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "rope: odd head_dim %d", d);
+  fb200_op_trace scope(dev, "rope", 8.0 * (double)b * (double)(h + hkv) * (double)s * (double)d);
   if (q_dev && (rc = fb200_launch_rope(dev, q_dev, b, h, s, d, cos_dev, sin_dev, start_pos, interleaved))) return rc;
   if (k_dev && (rc = fb200_launch_rope(dev, k_dev, b, hkv, s, d, cos_dev, sin_dev, start_pos, interleaved))) return rc;
   return FB200_OK;
@@ -247,6 +254,7 @@ int fb200_embedding_lookup(fb200_device* dev, const fb200_qmatrix* w, const uint
   int rc = fb200_bind(dev);
   if (rc) return rc;
   if (!w || w->dev != dev) return fb200_fail(dev, FB200_ERR_DEVICE_MISMATCH, "embedding: bad weight handle");
+  fb200_op_trace scope(dev, "embedding", 4.0 * (double)n_ids * (double)w->k);
   return fb200_launch_dequantize_rows(dev, w, ids_dev, n_ids, out_dev);
 }
 
@@ -254,6 +262,7 @@ int fb200_argmax(fb200_device* dev, const float* logits_dev, size_t rows, size_t
                  uint32_t* ids_dev, float* vals_dev) {
   int rc = fb200_bind(dev);
   if (rc) return rc;
+  fb200_op_trace scope(dev, "argmax", 4.0 * (double)rows * (double)n);
   return fb200_launch_argmax(dev, logits_dev, rows, n, ids_dev, vals_dev);
 }
 

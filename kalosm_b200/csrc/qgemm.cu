@@ -68,8 +68,9 @@ struct TcArgs {
   const __half* xh;      // fp16 activations, [Mp / BM][K / 64] tiles already in the operand layout
   const float* xscale;   // [Mp] power-of-two scale of each row
   float* y;              // [M, N]
-  const float* r1;       // optional residuals [M, N]
+  const float* r1;       // optional residuals [M, N], or one bias row [N] when r1_stride is 0
   const float* r2;
+  int r1_stride;
   int M, N, K;
   int ngroups, ntiles, type, tgb, group_elems;
   int stages, raw_stride;  // operand stages that fit beside the raw buffers; bytes per raw tile-group slot
@@ -426,7 +427,7 @@ qgemm_tc_kernel(const TcArgs a) {
         if (m < a.M && n < a.N) {
           const size_t idx = (size_t)m * a.N + n;
           float out = __uint_as_float(v[j]) * a.xscale[m];
-          if (a.r1) out += a.r1[idx];
+          if (a.r1) out += a.r1[(size_t)m * a.r1_stride + n];
           if (a.r2) out += a.r2[idx];
           a.y[idx] = out;
         }
@@ -509,7 +510,7 @@ int launch_tc(fb200_device* dev, const TcArgs& a, unsigned grid_n, unsigned grid
 // y[M, N] = x[M, K] . W^T (+ r1 + r2) for M > 32; with `swiglu`, W stacks gate rows over up rows
 // and y[M, N / 2] = silu(gate) * up. Returns 1 when the shape is not covered (the
 // caller falls back to the small-batch kernel in chunks of 32 rows).
-int fb200_qgemm(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_t m, float* y, const float* r1,
+int fb200_qgemm(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_t m, float* y, bool r1_is_bias, const float* r1,
                 const float* r2, int swiglu) {
   static const bool enabled = !(getenv("FB200_TCGEN05") && getenv("FB200_TCGEN05")[0] == '0');
   TileGeom geo;
@@ -550,6 +551,7 @@ int fb200_qgemm(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_
   FB_LAUNCH_CHECK(dev);
   TcArgs a;
   a.w = w->data; a.xh = xh; a.xscale = xscale; a.y = y; a.r1 = r1; a.r2 = r2;
+  a.r1_stride = r1_is_bias ? 0 : (int)w->n;
   a.M = (int)m; a.N = (int)w->n; a.K = (int)w->k;
   a.ngroups = w->ngroups; a.ntiles = w->ntiles; a.type = (int)w->type; a.tgb = geo.tg_bytes;
   a.group_elems = geo.group_elems; a.status = dev->status;

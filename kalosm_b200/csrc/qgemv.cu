@@ -36,8 +36,9 @@ struct GemvArgs {
   const float* xs16;    // [Kp/16][Mp] sums of the scaled activations (centres and offsets)
   const float* xscale;  // [Mp] power-of-two output scales
   float* y;             // [M, Nout]
-  const float* r1;
+  const float* r1;      // residual rows [M, Nout], or one bias row [Nout] when r1_stride is 0
   const float* r2;
+  int r1_stride;        // elements between consecutive rows of r1
   int M, Mp;
   int n_out;    // logical output columns (N, or N/2 for SwiGLU)
   int ngroups;  // K groups per tile
@@ -414,7 +415,7 @@ qgemv_kernel(const GemvArgs a) {
         float gate = v[0];
         out = (gate / (1.0f + expf(-gate))) * v[NP - 1];
       } else if (EPI == 1) {
-        out = v[0] + a.r1[idx];
+        out = v[0] + a.r1[(size_t)m * a.r1_stride + n];
         if (a.r2) out += a.r2[idx];
       } else {
         out = v[0];
@@ -766,7 +767,7 @@ qgemm16_kernel(const GemvArgs a) {
         const float gate = v[0];
         out = (gate / (1.0f + expf(-gate))) * v[NP - 1];
       } else if (EPI == 1) {
-        out = v[0] + a.r1[idx];
+        out = v[0] + a.r1[(size_t)m * a.r1_stride + n];
         if (a.r2) out += a.r2[idx];
       } else {
         out = v[0];
@@ -902,7 +903,7 @@ size_t fb200_xpack_bytes(int mp, uint64_t kp) {
 
 // y[m0 .. m0+mc) = x . W^T for a chunk of at most 32 activation rows, using `scratch`.
 int fb200_qgemv_chunk(fb200_device* dev, const fb200_qmatrix* w, const float* x, int mc, float* y,
-                      int epi, const float* r1, const float* r2, void* scratch) {
+                      int epi, const float* r1, const float* r2, void* scratch, bool r1_is_bias) {
   TileGeom geo;
   tile_geom(w->type, &geo);
   const int nt = mc <= 8 ? 1 : mc <= 16 ? 2 : 4;
@@ -921,6 +922,7 @@ int fb200_qgemv_chunk(fb200_device* dev, const fb200_qmatrix* w, const float* x,
     GemvArgs a16;
     a16.w = w->data; a16.xq = reinterpret_cast<const uint8_t*>(xh); a16.xs16 = nullptr; a16.xscale = xscale16;
     a16.y = y; a16.r1 = r1; a16.r2 = r2;
+    a16.r1_stride = r1_is_bias ? 0 : (int)(epi == FB200_EPI_SWIGLU ? w->n / 2 : w->n);
     a16.M = mc; a16.Mp = mp; a16.ngroups = w->ngroups;
     a16.nunits = w->ntiles;
     a16.n_out = (int)w->n;
@@ -949,6 +951,7 @@ int fb200_qgemv_chunk(fb200_device* dev, const fb200_qmatrix* w, const float* x,
   FB_LAUNCH_CHECK(dev);
   GemvArgs a;
   a.w = w->data; a.xq = xq; a.xs16 = xs16; a.xscale = xscale; a.y = y; a.r1 = r1; a.r2 = r2;
+  a.r1_stride = r1_is_bias ? 0 : (int)(epi == FB200_EPI_SWIGLU ? w->n / 2 : w->n);
   a.M = mc; a.Mp = mp; a.ngroups = w->ngroups;
   a.nunits = w->ntiles;
   a.n_out = (int)w->n;
@@ -1025,5 +1028,5 @@ extern "C" int fb200_q_mat_mul_noalloc(fb200_device* dev, const float* x_dev, si
   }
   // Nothing in the scratch has to start at zero: the pack kernel rewrites every byte the
   // product kernel reads (limbs of padded rows are never loaded, their sums are written as 0).
-  return fb200_qgemv_chunk(dev, w, x_dev, (int)m, y_dev, FB200_EPI_NONE, nullptr, nullptr, scratch);
+  return fb200_qgemv_chunk(dev, w, x_dev, (int)m, y_dev, FB200_EPI_NONE, nullptr, nullptr, scratch, false);
 }

@@ -11,7 +11,7 @@
 //     (standard, :144-240) or the surprise cut-off and mu update (Mirostat 2, :58-133).
 // The reference draws its uniform number from rand's StdRng, which is a third-party stream cipher
 // generator; here the draw is a counter-based function of (seed, counter, row) (the splitmix64
-// finaliser), which the CPU oracle restates, so both sides see the same number.
+// finaliser), which the CPU restatement used by the tests repeats, so both sides see the same number.
 //
 // One CTA of 1024 threads per row. A (processed value, token id) pair is one 64-bit key whose
 // unsigned order is exactly the reference's sort order, so "top k, sorted" = the k largest keys:
@@ -351,6 +351,7 @@ int fb200_top_k(fb200_device* dev, const float* logits_dev, size_t rows, size_t 
   SampleArgs a = {};
   a.logits = logits_dev; a.n = n; a.k = k; a.mode = 0;
   a.ids = ids_dev; a.vals = vals_dev;
+  fb200_op_trace scope(dev, "top_k", 4.0 * (double)rows * (double)n);
   return launch_sample(dev, a, rows, false);
 }
 
@@ -359,6 +360,7 @@ int fb200_sample(fb200_device* dev, const float* logits_dev, size_t rows, size_t
                  uint32_t* ids_dev) {
   int rc = fb200_bind(dev);
   if (rc) return rc;
+  fb200_op_trace scope(dev, "sample", 4.0 * (double)rows * (double)n);
   return fb200_launch_sampler(dev, logits_dev, rows, n, cfg, prev_dev, prev_stride, prev_len, counter, mu_dev, ids_dev,
                               nullptr, 0, nullptr, 0);
 }

@@ -161,6 +161,7 @@ def write_gguf(path, metadata, tensors, alignment=None):
             f.write(raw.tobytes())
 
 
+DEFAULT_ROPE_FREQUENCY = 1_000_000.0  # raw/mod.rs:104, used when .rope.freq_base is absent (:385-388)
 LAYER_TENSORS = ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down", "attn_norm", "ffn_norm")
 
 
@@ -170,6 +171,10 @@ def llama_config(g):
     arch = md.get("general.architecture")
     if not isinstance(arch, str):
         raise GgufError("general.architecture is missing")
+    if arch != "llama":
+        # qwen2 (half-split RoPE, biases), gemma (sliding windows, q/k norms), phi (fused qkv) are read
+        # by the reference (raw/mod.rs:488-646) but not built here: refuse instead of mis-running them
+        raise GgufError(f"architecture {arch!r} is not supported (only 'llama')")
 
     def get(key, default=None):
         v = md.get(arch + key, default)
@@ -180,27 +185,40 @@ def llama_config(g):
     if "token_embd.weight" not in g.tensors:
         raise GgufError("token_embd.weight is missing")
     return dict(n_layer=int(get(".block_count")), hidden=hidden, ffn=int(get(".feed_forward_length")),
-                n_head=heads, n_kv_head=int(get(".attention.head_count_kv", heads)),
+                n_head=heads, n_kv_head=int(get(".attention.head_count_kv")),
                 head_dim=int(get(".attention.key_length", hidden // heads)),
                 vocab=int(g.tensors["token_embd.weight"][0][0]), ctx=int(get(".context_length")),
                 rms_eps=float(get(".attention.layer_norm_rms_epsilon")),
-                rope_theta=float(get(".rope.freq_base", 10000.0)))
+                rope_theta=float(get(".rope.freq_base", DEFAULT_ROPE_FREQUENCY)))
 
 
-def load_llama(device, path, max_seq_len=None, max_batch=1, comm=None):
+def load_llama(device, path, max_seq_len=None, max_batch=1, comm=None, rope_scaling=None):
     """Builds a `kalosm_b200.Llama` from a GGUF checkpoint (tensor names of raw/mod.rs:473-646;
     a missing output.weight ties the head to the embedding, :480-486). With `comm` every rank loads
-    its shard (kalosm_b200.tp)."""
+    its shard (kalosm_b200.tp). `rope_scaling` = (factor, low_freq_factor, high_freq_factor,
+    original_context) is an argument here as it is of Model::from_var_source (raw/mod.rs:271; the
+    reference does not read it from the file either); a `rope_freqs.weight` tensor in the file is
+    multiplied into the inverse frequencies (raw/mod.rs:417-421, rope.rs:40-49). Metadata keys
+    `<arch>.rope.scaling.*` are refused rather than ignored: they ask for a scaling this loader
+    would otherwise silently drop."""
     from . import F32 as F32_TYPE, Llama
     g = GgufFile(path)
     c = llama_config(g)
     rank, size = (comm.rank, comm.size) if comm is not None else (0, 1)
+    scaling_keys = [k for k in g.metadata if ".rope.scaling." in k]
+    if scaling_keys and rope_scaling is None:
+        raise GgufError(f"the file asks for RoPE scaling ({', '.join(sorted(scaling_keys))}); pass rope_scaling=")
     if size > 1 and "output.weight" not in g.tensors:
         raise GgufError("a tensor-parallel model needs output.weight (tied embeddings are not sharded)")
     m = Llama(device, n_layer=c["n_layer"], hidden=c["hidden"], ffn=c["ffn"], n_head=c["n_head"],
               n_kv_head=c["n_kv_head"], head_dim=c["head_dim"], vocab=c["vocab"],
               max_seq_len=max_seq_len or c["ctx"], max_batch=max_batch, rms_eps=c["rms_eps"],
-              rope_theta=c["rope_theta"], comm=comm)
+              rope_theta=c["rope_theta"], rope_scaling=rope_scaling, comm=comm)
+    if "rope_freqs.weight" in g.tensors:
+        shape, ty, _ = g.tensors["rope_freqs.weight"]
+        if ty != F32_TYPE or int(np.prod(shape)) != c["head_dim"] // 2:
+            raise GgufError("rope_freqs.weight must be head_dim / 2 f32 values")
+        m.set_rope_freqs(np.frombuffer(bytes(g.tensor_bytes("rope_freqs.weight")), dtype=np.float32))
 
     def put(short, layer, name):
         shape, ty, _ = g.tensors[name]

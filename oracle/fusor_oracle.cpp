@@ -473,9 +473,22 @@ ORACLE_API void oracle_silu_mul(const float* gate, const float* up, size_t n, fl
 // RoPE tables: base_inverse_frequency (fusor-ml/fusor/src/composite/rope.rs:241-246) and the
 // outer product with positions followed by sin/cos (models/kalosm-llama/src/raw/rope.rs:63-85).
 // Llama-3 frequency scaling (kalosm-llama raw/rope.rs:21-38) applies when factor > 0.
+// freq_weight (optional): rope_freqs.weight, multiplied into the inverse frequencies after the
+// scaling (models/kalosm-llama/src/raw/rope.rs:40-49).
+ORACLE_API void oracle_rope_tables_w(int head_dim, int ctx, float theta, float factor,
+                                     float low_freq_factor, float high_freq_factor,
+                                     int original_ctx, const float* freq_weight, float* cos_out, float* sin_out);
+
 ORACLE_API void oracle_rope_tables(int head_dim, int ctx, float theta, float factor,
                                    float low_freq_factor, float high_freq_factor,
                                    int original_ctx, float* cos_out, float* sin_out) {
+  oracle_rope_tables_w(head_dim, ctx, theta, factor, low_freq_factor, high_freq_factor, original_ctx, nullptr,
+                       cos_out, sin_out);
+}
+
+ORACLE_API void oracle_rope_tables_w(int head_dim, int ctx, float theta, float factor,
+                                     float low_freq_factor, float high_freq_factor,
+                                     int original_ctx, const float* freq_weight, float* cos_out, float* sin_out) {
   int half = head_dim / 2;
   std::vector<float> inv(half);
   for (int i = 0; i < half; ++i)
@@ -495,6 +508,8 @@ ORACLE_API void oracle_rope_tables(int head_dim, int ctx, float theta, float fac
       }
     }
   }
+  if (freq_weight)
+    for (int i = 0; i < half; ++i) inv[i] = inv[i] * freq_weight[i];
   for (int p = 0; p < ctx; ++p)
     for (int i = 0; i < half; ++i) {
       float a = (float)p * inv[i];
@@ -980,6 +995,15 @@ ORACLE_API void* oracle_llama_create(int n_layer, int hidden, int ffn, int n_hea
 }
 
 ORACLE_API void oracle_llama_free(void* h) { delete (Llama*)h; }
+
+// RoPE scaling (an argument of Model::from_var_source, raw/mod.rs:271) and rope_freqs.weight
+// (raw/mod.rs:417-421): rebuilds the tables.
+ORACLE_API void oracle_llama_set_rope(void* h, float factor, float low_freq_factor, float high_freq_factor,
+                                      int original_ctx, const float* freq_weight) {
+  Llama* m = (Llama*)h;
+  oracle_rope_tables_w(m->head_dim, m->ctx, m->theta, factor, low_freq_factor, high_freq_factor, original_ctx,
+                       freq_weight, m->cos.data(), m->sin.data());
+}
 
 // which: 0 token_embd, 1 output, 2 wq, 3 wk, 4 wv, 5 wo, 6 gate, 7 up, 8 down (layer ignored for 0/1)
 ORACLE_API int oracle_llama_set_qmatrix(void* h, int layer, int which, uint32_t ty, size_t n,

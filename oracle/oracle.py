@@ -63,6 +63,8 @@ def lib():
             "oracle_random_qweights": (i32, [u64, f32, sz, u32, u8p]),
             "oracle_llama_create": (vp, [i32] * 8 + [f32, f32, i32, i32]),
             "oracle_llama_free": (None, [vp]),
+            "oracle_llama_set_rope": (None, [vp, f32, f32, f32, i32, f32p]),
+            "oracle_rope_tables_w": (None, [i32, i32, f32, f32, f32, f32, i32, f32p, f32p, f32p]),
             "oracle_llama_set_qmatrix": (i32, [vp, i32, i32, u32, sz, sz, u8p, sz]),
             "oracle_llama_set_norm": (i32, [vp, i32, i32, f32p, sz]),
             "oracle_llama_reset": (None, [vp]),
@@ -246,6 +248,12 @@ class Llama:
         rc = lib().oracle_llama_set_norm(self.h, layer, self.NORMS[name], _p(w), w.size)
         if rc:
             raise ValueError(f"set_norm {name} rc={rc}")
+
+    def set_rope(self, scaling=None, freq_weight=None):
+        """RoPE scaling (factor, low_freq_factor, high_freq_factor, original_ctx) and/or rope_freqs.weight."""
+        factor, low, high, orig = (0.0, 1.0, 4.0, self.cfg["ctx"]) if scaling is None else scaling
+        fw = None if freq_weight is None else _f32(freq_weight)
+        lib().oracle_llama_set_rope(self.h, factor, low, high, orig, _p(fw))
 
     def reset(self):
         lib().oracle_llama_reset(self.h)

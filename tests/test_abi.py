@@ -48,3 +48,40 @@ def test_product_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text.lower() or f == "__init__.py" and "oracle" not in text, (dirpath, f)
+
+
+def test_binding_refuses_buffers_the_library_would_overrun():
+    # caller-supplied outputs and residuals are checked on the host before the C call: the library
+    # trusts their size, so an undersized buffer would become an out-of-bounds device write
+    import types
+    import numpy as np
+    dev = types.SimpleNamespace(lib=None, h=1)
+    w = types.SimpleNamespace(shape=(64, 128), h=2)
+    x = kb.Tensor(dev, (4, 128), np.float32, ptr=1)
+    cases = {
+        "small": kb.Tensor(dev, (4, 32), np.float32, ptr=1),
+        "wrong dtype": kb.Tensor(dev, (4, 64), np.float16, ptr=1),
+        "other device": kb.Tensor(types.SimpleNamespace(lib=None, h=3), (4, 64), np.float32, ptr=1),
+    }
+    for what, bad in cases.items():
+        for call in (lambda: x.q_mat_mul(w, out=bad), lambda: x.q_mat_mul_noalloc(w, bad),
+                     lambda: x.q_mat_mul(w, epilogue=kb.EPI_RESIDUAL, r1=bad)):
+            try:
+                call()
+            except kb.FusorError as e:
+                assert e.code == kb.ERR_INVALID_SHAPE, what
+            else:
+                raise AssertionError(f"{what}: not refused")
+
+
+def test_missing_nccl_is_an_error_code():
+    # FB200_NCCL_LIB points the run-time loader at a file that does not exist: the communicator
+    # entry points answer FB200_ERR_NCCL instead of crashing (fresh process: the lookup is cached)
+    import subprocess
+    import sys
+    code = ("import kalosm_b200 as kb, ctypes as C; L = kb.load_library(); "
+            "buf = (C.c_uint8 * kb.COMM_ID_BYTES)(); print(L.fb200_comm_unique_id(buf, kb.COMM_ID_BYTES))")
+    out = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, FB200_NCCL_LIB="/nonexistent/libnccl.so.2"),
+                         capture_output=True, text=True, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert out.returncode == 0, out.stderr
+    assert int(out.stdout.strip().splitlines()[-1]) == kb.ERR_NCCL

@@ -80,3 +80,73 @@ def test_tensor_checks_and_llama_config(tmp_path):
     gguf.write_gguf(p, md, [("token_embd.weight", (1024, 256), O.Q4K, emb)])
     with pytest.raises(gguf.GgufError):
         gguf.llama_config(gguf.GgufFile(p))
+
+
+def _tiny_md(**over):
+    md = {"general.architecture": (gguf.STRING, "llama"), "llama.block_count": (gguf.U32, 1),
+          "llama.embedding_length": (gguf.U32, 256), "llama.feed_forward_length": (gguf.U32, 512),
+          "llama.attention.head_count": (gguf.U32, 4), "llama.attention.head_count_kv": (gguf.U32, 2),
+          "llama.context_length": (gguf.U32, 64), "llama.attention.layer_norm_rms_epsilon": (gguf.F32, 1e-5)}
+    md.update(over)
+    return {k: v for k, v in md.items() if v is not None}
+
+
+def test_loader_defaults_and_refusals(tmp_path):
+    # what Model::from_var_source does with the same files (models/kalosm-llama/src/raw/mod.rs:377-434):
+    # rope.freq_base defaults to DEFAULT_ROPE_FREQUENCY (:104, :385-388); head_count_kv is mandatory
+    # (:379); other architectures need code paths this build does not have
+    emb = O.random_qweights(2, 0.02, 1024 * 256, O.Q4K)
+    p = tmp_path / "m.gguf"
+    gguf.write_gguf(p, _tiny_md(), [("token_embd.weight", (1024, 256), O.Q4K, emb)])
+    assert gguf.llama_config(gguf.GgufFile(p))["rope_theta"] == 1_000_000.0
+    gguf.write_gguf(p, _tiny_md(**{"llama.attention.head_count_kv": None}), [("token_embd.weight", (1024, 256), O.Q4K, emb)])
+    with pytest.raises(gguf.GgufError) as e:
+        gguf.llama_config(gguf.GgufFile(p))
+    assert "head_count_kv" in str(e.value)
+    for arch in ("qwen2", "gemma3", "phi3"):
+        md = {k.replace("llama.", arch + "."): v for k, v in _tiny_md().items()}
+        md["general.architecture"] = (gguf.STRING, arch)
+        gguf.write_gguf(p, md, [("token_embd.weight", (1024, 256), O.Q4K, emb)])
+        with pytest.raises(gguf.GgufError) as e:
+            gguf.llama_config(gguf.GgufFile(p))
+        assert arch in str(e.value)
+    # a file that asks for RoPE scaling is refused unless the caller supplies the scaling (no device needed:
+    # the refusal comes before anything is built)
+    gguf.write_gguf(p, _tiny_md(**{"llama.rope.scaling.factor": (gguf.F32, 8.0)}),
+                    [("token_embd.weight", (1024, 256), O.Q4K, emb)])
+    with pytest.raises(gguf.GgufError) as e:
+        gguf.load_llama(None, p)
+    assert "rope.scaling" in str(e.value)
+
+
+def test_reader_against_the_gguf_package_writer(tmp_path):
+    # the container format pinned independently of this repository's own writer: a file written by
+    # the third-party `gguf` package (llama.cpp's Python writer) must read back identically
+    pkg = pytest.importorskip("gguf")
+    if not hasattr(pkg, "GGUFWriter"):
+        pytest.skip("the installed gguf package has no writer")
+    path = tmp_path / "pkg.gguf"
+    w = pkg.GGUFWriter(str(path), "llama")
+    w.add_uint32("llama.block_count", 3)
+    w.add_float32("llama.rope.freq_base", 500000.0)
+    w.add_string("general.name", "pinned")
+    w.add_array("tokenizer.ggml.tokens", ["a", "bc", "def"])
+    w.add_bool("llama.flag", True)
+    f32 = np.arange(24, dtype=np.float32).reshape(4, 6)
+    q8 = O.random_qweights(3, 0.02, 8 * 64, O.Q8_0)
+    q4k = O.random_qweights(4, 0.02, 2 * 512, O.Q4K)
+    w.add_tensor("dense", f32)
+    w.add_tensor("q8", q8.reshape(8, 64 // 32 * 34), raw_dtype=pkg.GGMLQuantizationType.Q8_0)
+    w.add_tensor("q4k", q4k.reshape(2, 512 // 256 * 144), raw_dtype=pkg.GGMLQuantizationType.Q4_K)
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()
+    g = gguf.GgufFile(path)
+    assert g.metadata["general.architecture"] == "llama" and g.metadata["llama.block_count"] == 3
+    assert g.metadata["llama.rope.freq_base"] == 500000.0 and g.metadata["general.name"] == "pinned"
+    assert g.metadata["tokenizer.ggml.tokens"] == ["a", "bc", "def"] and g.metadata["llama.flag"] is True
+    assert g.tensors["dense"][:2] == ((4, 6), 0)
+    assert np.array_equal(np.frombuffer(bytes(g.tensor_bytes("dense")), np.float32).reshape(4, 6), f32)
+    assert g.tensors["q8"][:2] == ((8, 64), O.Q8_0) and np.array_equal(g.tensor_bytes("q8"), q8)
+    assert g.tensors["q4k"][:2] == ((2, 512), O.Q4K) and np.array_equal(g.tensor_bytes("q4k"), q4k)

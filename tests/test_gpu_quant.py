@@ -219,6 +219,14 @@ def test_epilogues(dev):
         y = dev.tensor(x).q_mat_mul(gate, epilogue=kb.EPI_RESIDUAL, r1=dev.tensor(r1),
                                     r2=dev.tensor(r2)).as_slice()
         assert F.rel_l2(y, (O.q_mat_mul(x, g_raw, ty, f, k) + r1) + r2) < TOL
+    # Linear with a bias (fusor-ml/fusor/src/layers/linear.rs:93-121): one [N] row added to every output row,
+    # through the single-row, the small-batch and the tensor-core kernels
+    bias = activations(77, 1, f)[0]
+    for m in (1, 6, 20, 40, 300):
+        x = activations(200 + m, m, k)
+        y = dev.tensor(x).q_mat_mul(gate, epilogue=kb.EPI_BIAS, r1=dev.tensor(bias)).as_slice()
+        assert y.shape == (m, f)
+        assert F.rel_l2(y, O.q_mat_mul(x, g_raw, ty, f, k) + bias[None, :]) < TOL, m
     # mismatched parts: None, as QMatrix::concat_rows does
     other = kb.QMatrix.from_raw_bytes(dev, (f, k), weights(3, f, k, O.Q6K), O.Q6K)
     assert kb.QMatrix.concat_rows([gate, other]) is None

@@ -290,10 +290,11 @@ def test_sampler_properties_of_the_reference_tests():
     assert O.sample(np.array([1.0, 2.0, 2.0, 0.5], np.float32), temperature=0.0, top_k=2)[0] == 2
     # repetition penalty (sampler.rs:272-279): positive logits divided, non-positive multiplied
     lg = np.array([2.0, 1.9, -0.1, -0.2], np.float32)
-    assert O.sample(lg, temperature=0.0, top_k=4, repetition_penalty=2.0, previous=[0])[0] == 1
-    assert O.sample(lg, temperature=0.0, top_k=4, repetition_penalty=2.0, previous=[0, 1])[0] == 1
-    assert O.sample(lg, temperature=0.0, top_k=4, repetition_penalty=30.0, previous=[0, 1])[0] == 1
-    assert O.sample(lg, temperature=0.0, top_k=4, repetition_penalty=30.0, previous=[0, 1, 2])[0] == 1
+    assert O.sample(lg, temperature=0.0, top_k=4, repetition_penalty=2.0, previous=[0])[0] == 1      # 1.0 < 1.9
+    assert O.sample(lg, temperature=0.0, top_k=4, repetition_penalty=2.0, previous=[0, 1])[0] == 0   # 1.0 > 0.95
+    assert O.sample(np.array([-0.1, -0.15], np.float32), temperature=0.0, top_k=2, repetition_penalty=2.0,
+                    previous=[0])[0] == 1                                                            # -0.2 < -0.15
+    assert O.sample(lg, temperature=0.0, top_k=4, repetition_penalty=1.0, previous=[0])[0] == 0      # <= 1: off
     # only the last `range` previous tokens count (sampler.rs:297-303)
     assert O.sample(lg, temperature=0.0, top_k=4, repetition_penalty=2.0, repetition_penalty_range=1,
                     previous=[0, 3])[0] == 0
