@@ -16,7 +16,8 @@ from typing import Optional, Sequence
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libfusor_b200.so")
+# FB200_LIB_PATH selects another build of the library (a deployment's own location, or a variant under test)
+LIB_PATH = os.environ.get("FB200_LIB_PATH") or os.path.join(_HERE, "libfusor_b200.so")
 
 # ggml type ids (fusor-ml/gguf/src/lib.rs:35-50)
 F32, F16, Q4_0, Q5_0, Q8_0, Q4_K, Q5_K, Q6_K = 0, 1, 2, 6, 8, 12, 13, 14

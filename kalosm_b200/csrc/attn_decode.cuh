@@ -29,6 +29,15 @@ struct fb200_dec_args {
   int b, h, hkv, groups, cap, nsplit;
   float scale;
   int pos_plus1;        // > 0: *pos_dev + 1, already read by the caller (saves a dependent load); 0: not known
+  // flagged rows (persistent decode kernel without grid barriers between its phases): q, k_new
+  // and v_new arrive as f32 granules {value, epoch} that the item polls, and the merged output
+  // leaves as a flagged packed row
+  const uint2* q_ll;
+  const uint2* k_ll;
+  const uint2* v_ll;
+  fb200_ll_act out_ll;
+  unsigned ep_in, ep_out;
+  int* status;          // device status word for waits that give up
 };
 
 namespace {
@@ -64,7 +73,24 @@ __device__ __forceinline__ void dec_sync() {
 // One (batch, kv head, split) item, executed by DEC_THREADS threads (tid = 0 .. DEC_THREADS - 1).
 // DEC_CH = keys per shared-memory chunk; ROWS = query rows computed per KV head (>= H / Hkv). PDL: the caller is a kernel launched with programmatic
 // stream serialization, whose predecessor produced q, k_new and v_new.
-template <int D, int DEC_CH, int ROWS, int BAR, bool PDL>
+// Two neighbouring f32 granules (elements 2p, 2p + 1) of a flagged row, polled until both carry
+// `epoch` (bounded, like every wait).
+__device__ __forceinline__ float2 ld_ll_pair(const uint2* p, uint32_t epoch, int* status) {
+  const uint4* line = reinterpret_cast<const uint4*>(p);
+  uint4 v = ld_ll_line(line);
+  int polls = 0;
+  while (v.y != epoch || v.w != epoch) {
+    if (++polls > FB200_LL_POLL_LIMIT || ((polls & 63) == 0 && __ldcg(status) != 0)) {
+      atomicExch(status, FB200_ERR_TIMEOUT);
+      break;
+    }
+    v = ld_ll_line(line);
+  }
+  return make_float2(__uint_as_float(v.x), __uint_as_float(v.z));
+}
+
+// LLIO: q / k_new / v_new come in and the merged row goes out as flagged rows (see DecArgs).
+template <int D, int DEC_CH, int ROWS, int BAR, bool PDL, bool LLIO = false>
 __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int tid) {
   constexpr int ATT_THREADS = DEC_THREADS;
   constexpr int KSTR = D * 2 + 64;   // bytes per staged row: consecutive keys land 64 B apart mod 128
@@ -112,12 +138,20 @@ __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int t
     const int r = i / D, e = i % D;
     float v = 0.f;
     if (r < nrows) {
-      const float* qr = a.q + ((size_t)bi * a.h + kvh * a.groups + r) * D;
+      const size_t qoff = ((size_t)bi * a.h + kvh * a.groups + r) * D;
+      const float* qr = a.q + qoff;
       // interleaved RoPE at the new position (fusor-ml/fusor/src/composite/rope.rs:77-108)
-      const float self = __ldcg(qr + e);
+      float self, other = 0.f;
+      if constexpr (LLIO) {
+        const float2 pr = ld_ll_pair(a.q_ll + qoff + (e & ~1), a.ep_in, a.status);
+        self = (e & 1) ? pr.y : pr.x;
+        other = (e & 1) ? pr.x : pr.y;
+      } else {
+        self = __ldcg(qr + e);
+        if (pos >= 0) other = __ldcg(qr + (e ^ 1));
+      }
       v = self;
       if (pos >= 0) {
-        const float other = __ldcg(qr + (e ^ 1));
         const float c = a.rope_cos[(size_t)pos * (D / 2) + (e >> 1)];
         const float sn = a.rope_sin[(size_t)pos * (D / 2) + (e >> 1)];
         v = (e & 1) ? __fadd_rn(__fmul_rn(other, sn), __fmul_rn(self, c))
@@ -133,10 +167,19 @@ __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int t
     const float* kn = a.k_new + ((size_t)bi * a.hkv + kvh) * D;
     const float* vn = a.v_new + ((size_t)bi * a.hkv + kvh) * D;
     const float c = a.rope_cos[(size_t)pos * (D / 2) + p], sn = a.rope_sin[(size_t)pos * (D / 2) + p];
-    const float x0 = __ldcg(kn + 2 * p), x1 = __ldcg(kn + 2 * p + 1);
+    float x0, x1, v0, v1;
+    if constexpr (LLIO) {
+      const size_t koff = ((size_t)bi * a.hkv + kvh) * D + 2 * p;
+      const float2 kp = ld_ll_pair(a.k_ll + koff, a.ep_in, a.status);
+      const float2 vp = ld_ll_pair(a.v_ll + koff, a.ep_in, a.status);
+      x0 = kp.x; x1 = kp.y; v0 = vp.x; v1 = vp.y;
+    } else {
+      x0 = __ldcg(kn + 2 * p); x1 = __ldcg(kn + 2 * p + 1);
+      v0 = __ldcg(vn + 2 * p); v1 = __ldcg(vn + 2 * p + 1);
+    }
     const __half2 kh = __floats2half2_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn)),
                                          __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c)));
-    const __half2 vh = __floats2half2_rn(__ldcg(vn + 2 * p), __ldcg(vn + 2 * p + 1));
+    const __half2 vh = __floats2half2_rn(v0, v1);
     *reinterpret_cast<__half2*>(kb + (size_t)pos * D + 2 * p) = kh;
     *reinterpret_cast<__half2*>(vb + (size_t)pos * D + 2 * p) = vh;
     if (pos - kbeg < DEC_CH) {
@@ -316,8 +359,12 @@ __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int t
       if (a.out) a.out[grow * D + e] = acc;
     }
     // packed rows are single-sequence; nrows * D is a multiple of 32, so `valid` is warp-uniform
-    if (a.out_packed.limbs && bi == 0 && valid)
-      emit_packed16(a.out_packed, (int)(grow * D) + e, acc, acc, true, 0xFFFFFFFFu);
+    if constexpr (LLIO) {
+      if (bi == 0 && valid) emit_ll16(a.out_ll, (int)(grow * D) + e, acc, acc, true, 0xFFFFFFFFu, a.ep_out);
+    } else {
+      if (a.out_packed.limbs && bi == 0 && valid)
+        emit_packed16(a.out_packed, (int)(grow * D) + e, acc, acc, true, 0xFFFFFFFFu);
+    }
   }
 }
 

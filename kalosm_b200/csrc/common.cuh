@@ -46,6 +46,9 @@ struct fb200_device {
   // scratch of the fused decode-step kernel: grid barrier word, split-unit partials, counters
   void* fused = nullptr;
   size_t fused_bytes = 0;
+  // next epoch of the flagged rows of the fused decode kernel (one per phase executed; never 0,
+  // the value of freshly cleared buffers)
+  uint32_t ll_epoch = 1;
 };
 
 // Quantised (or dense) weight matrix [N, K] in tile-interleaved device storage.

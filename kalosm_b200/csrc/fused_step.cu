@@ -24,6 +24,12 @@
 // memory over NVLink), arrival words written with release at system scope tell the peers, and
 // an XSUM phase adds the ranks' rows in rank order; the greedy key of the sharded output head
 // is exchanged the same way (fused_step.cuh: fb200_fused_xchg).
+// Single-GPU programs of K-quant weights run the variants with LL = true: no grid barrier inside a
+// step. Every activation that crosses CTAs (packed rows, q / k / v, the residual stream, the
+// attention output) travels as flagged rows (packed_act.cuh: payload word + epoch in one 8-byte
+// store, polled by the reader), so a phase boundary costs one store and one load through L2
+// instead of fence -> barrier -> reload, and CTAs without work in a phase run ahead to the next.
+// Only the greedy-token hand-over at the end of a step (argmax key -> ids) keeps two barriers.
 // Everything another CTA wrote during the kernel is read through L2 (ld.global.cg).
 // All waits are bounded: a wait that gives up sets the device status word and the kernel runs to
 // its end without waiting again.
@@ -31,7 +37,7 @@
 #include <cstdlib>
 
 #include "fused_step.cuh"
-#include "qgemv1_groups.cuh"
+#include "qgemv1_groups2.cuh"
 
 namespace {
 
@@ -39,11 +45,17 @@ constexpr int FW = 16;             // warps per CTA
 constexpr int FT = FW * 32;        // threads per CTA
 constexpr int RING_BYTES = 6912;   // ring bytes per warp: 3 x 2304 (Q4_K) or 2 x 3456 (Q6_K)
 constexpr int MAX_STAGES = 2;  // ring slots per warp: a third slot measured slower, not faster
+// Ring of the barrier-free variants: the same bytes per warp, Q4_K phases may use a third slot. A larger
+// ring was measured and is far slower: shared memory beyond ~185 KB leaves the L1 too small for the
+// kernel's register spills (local memory), and those then travel to L2.
+constexpr int RING_BYTES_LL = 6912;
+constexpr int MAX_STAGES_LL = 3;
 constexpr int FUSED_DEC_CH = 64;
 constexpr int FUSED_SPLIT_KEYS = 32;  // smallest share of the context an attention item takes   // keys per shared-memory chunk of the attention phase
 constexpr int SMEM_LIMIT = 227 * 1024;
 constexpr int STATIC_SMEM_RESERVE = 4096;  // static shared memory of the attention phase
 constexpr int DESC_WORDS = (int)((sizeof(fb200_fused_phase) + 15) / 16 * 4);  // 32-bit words per descriptor slot
+constexpr int DESC_SLOTS = 5;
 
 struct FusedArgs {
   const fb200_fused_phase* prog;
@@ -55,6 +67,7 @@ struct FusedArgs {
   int* status;
   unsigned long long* trace;  // optional [nphases][8] time stamps of CTA 0 in the last step (ns)
   fb200_fused_xchg x;         // tensor-parallel exchange (world <= 1: none)
+  unsigned epoch_base;        // flagged rows: epoch of phase 0 of this launch
 };
 
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -208,6 +221,7 @@ struct EpiCtx {
   unsigned long long best_key;
   const fb200_fused_xchg* xs;  // not null: rows of matrix 0 go to every rank's exchange buffer
   int xs_off;                  // float offset of this rank's slot for the current epoch
+  unsigned ep;                 // flagged rows: epoch of the current phase
 };
 
 __device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v) {
@@ -241,35 +255,68 @@ __device__ __forceinline__ void xchg_signal_and_wait(const FusedArgs& A, unsigne
 struct EpiOperands {
   int unit;  // -1: nothing fetched
   float res1, res2, padd, pw;
+  // flagged rows: bit i set = operand i (res1, res2, padd) was read before its producer had
+  // published it; it is polled where the value is used, so that fetching ahead never waits
+  unsigned stale;
 };
-__device__ __forceinline__ EpiOperands epilogue_operands(const fb200_fused_phase& P, int unit, int lane) {
+template <bool LL>
+__device__ __forceinline__ EpiOperands epilogue_operands(const fb200_fused_phase& P, int unit, int lane, const EpiCtx& E) {
   int sidx, tile;
   unit_locate(P, unit, sidx, tile);
   const int n = tile * 16 + lane;
   const bool valid = n < P.seg[sidx].n_out;
-  const bool pack = P.yp.limbs && sidx == 0;
   EpiOperands o;
   o.unit = unit;
-  o.res1 = valid && P.epi == FB200_EPI_RESIDUAL ? __ldcg(P.r1 + n) : 0.f;
-  o.res2 = valid && P.epi == FB200_EPI_RESIDUAL && P.r2 ? __ldcg(P.r2 + n) : 0.f;
-  o.padd = valid && pack && P.yp_add ? __ldcg(P.yp_add + n) : 0.f;
-  o.pw = valid && pack && P.yp_norm_w ? P.yp_norm_w[n] : 1.0f;
+  if constexpr (LL) {
+    const bool pack = P.yll.g && sidx == 0;
+    o.res1 = o.res2 = o.padd = 0.f;
+    o.stale = 0u;
+    if (valid && P.epi == FB200_EPI_RESIDUAL) {
+      const uint2 g = ld_ll_granule(P.r1l + n);
+      o.res1 = __uint_as_float(g.x);
+      if (g.y != E.ep - (unsigned)P.r1_back) o.stale |= 1u;
+    }
+    if (valid && P.epi == FB200_EPI_RESIDUAL && P.r2l) {
+      const uint2 g = ld_ll_granule(P.r2l + n);
+      o.res2 = __uint_as_float(g.x);
+      if (g.y != E.ep - (unsigned)P.r2_back) o.stale |= 2u;
+    }
+    if (valid && pack && P.addl) {
+      const uint2 g = ld_ll_granule(P.addl + n);
+      o.padd = __uint_as_float(g.x);
+      if (g.y != E.ep - (unsigned)P.add_back) o.stale |= 4u;
+    }
+    o.pw = valid && pack && P.yp_norm_w ? P.yp_norm_w[n] : 1.0f;
+  } else {
+    const bool pack = P.yp.limbs && sidx == 0;
+    o.stale = 0u;
+    o.res1 = valid && P.epi == FB200_EPI_RESIDUAL ? __ldcg(P.r1 + n) : 0.f;
+    o.res2 = valid && P.epi == FB200_EPI_RESIDUAL && P.r2 ? __ldcg(P.r2 + n) : 0.f;
+    o.padd = valid && pack && P.yp_add ? __ldcg(P.yp_add + n) : 0.f;
+    o.pw = valid && pack && P.yp_norm_w ? P.yp_norm_w[n] : 1.0f;
+  }
   return o;
 }
 
 // Epilogue of one unit; lanes 0..15 call it with the sums of row `lane` (pass 0 / pass 1).
-template <bool XS>
+template <bool XS, bool LL>
 __device__ __noinline__ void unit_epilogue(const fb200_fused_phase& P, int unit, float s0, float s1, int lane,
-                                           EpiCtx& E, const EpiOperands& pre) {
+                                           EpiCtx& E, const EpiOperands& pre, int* A_status) {
   int sidx, tile;
   unit_locate(P, unit, sidx, tile);
   const int n = tile * 16 + lane;
   const bool valid = n < P.seg[sidx].n_out;
   float* yout = P.seg[sidx].y;
   const float v0 = s0 * E.final_scale, v1 = s1 * E.final_scale;
-  const bool pack = P.yp.limbs && sidx == 0;
+  const bool pack = (LL ? P.yll.g != nullptr : P.yp.limbs != nullptr) && sidx == 0;
   // operands fetched ahead by the caller, or all together now (one trip to L2 instead of a chain)
-  const EpiOperands op = pre.unit == unit ? pre : epilogue_operands(P, unit, lane);
+  EpiOperands op = pre.unit == unit ? pre : epilogue_operands<LL>(P, unit, lane, E);
+  const bool has_r2 = LL ? P.r2l != nullptr : P.r2 != nullptr;
+  if constexpr (LL) {
+    if (op.stale & 1u) op.res1 = ld_ll_f32(P.r1l + n, E.ep - (unsigned)P.r1_back, A_status);
+    if (op.stale & 2u) op.res2 = ld_ll_f32(P.r2l + n, E.ep - (unsigned)P.r2_back, A_status);
+    if (op.stale & 4u) op.padd = ld_ll_f32(P.addl + n, E.ep - (unsigned)P.add_back, A_status);
+  }
   float out = 0.f;
   if (valid) {
     if (P.epi == FB200_EPI_SWIGLU) {
@@ -277,11 +324,12 @@ __device__ __noinline__ void unit_epilogue(const fb200_fused_phase& P, int unit,
       out = (v0 / (1.0f + expf(-v0))) * v1;
     } else if (P.epi == FB200_EPI_RESIDUAL) {
       out = v0 + op.res1;
-      if (P.r2) out += op.res2;
+      if (has_r2) out += op.res2;
     } else {
       out = v0;
     }
     if (yout) yout[n] = out;
+    if (LL && P.seg[sidx].yl) st_ll(P.seg[sidx].yl + n, __float_as_uint(out), E.ep);
     if (XS && E.xs && sidx == 0) {
       // partial row of a tensor-parallel projection: straight into every rank's buffer (P2P stores)
       for (int r = 0; r < E.xs->world; ++r) E.xs->data[r][E.xs_off + n] = out;
@@ -293,8 +341,77 @@ __device__ __noinline__ void unit_epilogue(const fb200_fused_phase& P, int unit,
   }
   if (pack) {
     const float nv = out + op.padd;
-    emit_packed16(P.yp, n, nv * op.pw, nv, valid, 0x0000FFFFu);
+    if constexpr (LL) emit_ll16(P.yll, n, nv * op.pw, nv, valid, 0x0000FFFFu, E.ep);
+    else emit_packed16(P.yp, n, nv * op.pw, nv, valid, 0x0000FFFFu);
   }
+}
+
+// ---- flagged activation row -> shared memory -------------------------------------------------
+// Every thread takes the 16-byte lines tid, tid + FT, ... of the row (6 lines per 16-element
+// block: 4 of limbs, 1 of scale and sum, 1 of the sum of squares), keeps up to LL_BATCH of them
+// in flight, and polls each until its epoch is the expected one. Returns this thread's share of
+// the sum of squares (added in line order: the result does not depend on timing).
+constexpr int LL_BATCH = 12;
+
+// `with_sumsq` false: the consumer does not normalise, the sixth line of every block is not read.
+__device__ __noinline__ float load_act_ll(const fb200_ll_act& row, int K, int Kp, uint8_t* xl, float2* xsp,
+                                             unsigned epoch, int* status, bool with_sumsq) {
+  const int tid = threadIdx.x;
+  const int nblk = (K + 15) / 16;  // blocks the producers publish; the padding up to Kp is zero-filled here
+  const int per = with_sumsq ? 6 : 5;  // lines read per block
+  const float rcp_per = with_sumsq ? 1.0f / 6.0f : 0.2f;
+  const int nlines = nblk * per;
+  const uint4* src = reinterpret_cast<const uint4*>(row.g);
+  float ss = 0.f;
+  for (int l0 = tid; l0 < nlines; l0 += FT * LL_BATCH) {
+    uint4 v[LL_BATCH];
+    float sq[LL_BATCH];
+    unsigned pending = 0u;
+#pragma unroll
+    for (int j = 0; j < LL_BATCH; ++j) {
+      const int l = l0 + j * FT;
+      sq[j] = 0.f;
+      if (l < nlines) {
+        const int b = fdiv(l, rcp_per);
+        v[j] = ld_ll_line(src + b * FB200_LL_LINES + (l - per * b));
+        pending |= 1u << j;
+      }
+    }
+    int polls = 0;
+    while (pending) {
+#pragma unroll
+      for (int j = 0; j < LL_BATCH; ++j) {
+        if (!((pending >> j) & 1u)) continue;
+        const int l = l0 + j * FT;
+        const int b = fdiv(l, rcp_per), line = l - per * b;
+        if (v[j].y == epoch && (line == 5 || v[j].w == epoch)) {
+          if (line < 4) {
+            const int B = 2 * b + (line >> 1);
+            *reinterpret_cast<uint2*>(xl + limb2_off(B) + (line & 1) * 8) = make_uint2(v[j].x, v[j].z);
+          } else if (line == 4) {
+            xsp[b] = make_float2(__uint_as_float(v[j].x), __uint_as_float(v[j].z));  // {xsc, xss}
+          } else {
+            sq[j] = __uint_as_float(v[j].x);
+          }
+          pending &= ~(1u << j);
+        } else {
+          v[j] = ld_ll_line(src + b * FB200_LL_LINES + line);
+        }
+      }
+      if (pending && (++polls > FB200_LL_POLL_LIMIT || ((polls & 63) == 0 && __ldcg(status) != 0))) {
+        atomicExch(status, FB200_ERR_TIMEOUT);
+        break;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < LL_BATCH; ++j) ss += sq[j];
+  }
+  for (int b = nblk + tid; b < Kp / 16; b += FT) {
+    xsp[b] = make_float2(0.f, 0.f);
+    *reinterpret_cast<uint4*>(xl + limb2_off(2 * b)) = make_uint4(0u, 0u, 0u, 0u);
+    *reinterpret_cast<uint4*>(xl + limb2_off(2 * b + 1)) = make_uint4(0u, 0u, 0u, 0u);
+  }
+  return ss;
 }
 
 struct Smem {
@@ -306,12 +423,40 @@ struct Smem {
   unsigned long long* keys;   // [FW]
 };
 
-template <bool LEGACY, bool XS>
+// (Inlined on purpose: as a separate function, with its state passed by reference or copied, the
+// product loop measured 25 % slower.)
+template <bool LEGACY, bool XS, bool LL>
 __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused_phase& P, const fb200_fused_phase* Pnext,
-                           const Smem& S, WarpRing& R, Carry& C, unsigned long long* tr, unsigned epoch) {
+                           const Smem& S, WarpRing& R, Carry& C, unsigned long long* tr, unsigned epoch, unsigned lep) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int K = P.K, Kp = P.Kp;
+  const PhaseLocal q = phase_local(P);
+  const Range r = warp_range(q.total, q.chunk, warp);
+  const bool has_items = r.c0 < r.c1;  // the same for every thread of the CTA
 
+  EpiCtx E;
+  E.final_scale = 1.0f;
+  E.best_key = 0ull;
+  E.xs = XS && P.xs_index >= 0 && A.x.world > 1 ? &A.x : nullptr;
+  E.xs_off = XS ? (int)((epoch & 1u) * (unsigned)A.x.world + (unsigned)A.x.me) * A.x.stride : 0;
+  E.ep = lep;
+  if constexpr (LL) {
+    // ---- activation row: poll the producers' flagged row straight into shared memory. A CTA
+    // without items in this phase needs no activations and goes on to the next phase.
+    if (has_items) {
+      float ss = load_act_ll(P.xll, K, Kp, S.xl, reinterpret_cast<float2*>(S.xsc), lep - 1u, A.status, P.xp_norm != 0);
+      if (P.xp_norm) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+        if (lane == 0) S.tmp[warp] = ss;
+        __syncthreads();
+        ss = 0.f;
+        for (int i = 0; i < FW; ++i) ss += S.tmp[i];
+        E.final_scale = 1.0f / sqrtf(ss / (float)K + P.eps);
+      }
+      __syncthreads();
+    }
+  } else {
   // ---- activation row: limbs, scales, sums -> shared memory (asynchronous 16-byte copies through
   // L2, all in flight at once); 1/rms from the producer's sums of squares
   {
@@ -326,11 +471,6 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
     uint4* d2 = reinterpret_cast<uint4*>(S.xss);
     for (int i = tid; i < Kp / 64; i += FT) { cp_async16(d1 + i, s1 + i); cp_async16(d2 + i, s2 + i); }
   }
-  EpiCtx E;
-  E.final_scale = 1.0f;
-  E.best_key = 0ull;
-  E.xs = XS && P.xs_index >= 0 && A.x.world > 1 ? &A.x : nullptr;
-  E.xs_off = XS ? (int)((epoch & 1u) * (unsigned)A.x.world + (unsigned)A.x.me) * A.x.stride : 0;
   if (P.xp_norm) {
     float ss = 0.f;
     for (int i = tid; i < (K + 15) / 16; i += FT) ss += __ldcg(P.xp.sumsq + i);
@@ -344,19 +484,18 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
   }
   cp_async_wait_all();
   __syncthreads();
+  }
   if (tr) tr[1] = global_ns();
 
   // ---- this warp's share: runs of items inside one (unit, pass), K group after K group
-  const PhaseLocal q = phase_local(P);
-  const Range r = warp_range(q.total, q.chunk, warp);
   const Lane L = make_lane(lane);
   // the first unit this warp will finish in the merge stage below: its epilogue operands are
   // requested now and arrive while the warp works
   EpiOperands pre;
   pre.unit = -1;
   const int ua = r.c0 < r.c1 ? fdiv(r.c0, q.rcp_ipu) : 0, ub = r.c0 < r.c1 ? fdiv(r.c1 - 1, q.rcp_ipu) : -1;
-  if (ua + warp <= ub && lane < 16 && (P.epi == FB200_EPI_RESIDUAL || P.yp_add || P.yp_norm_w))
-    pre = epilogue_operands(P, ua + warp, lane);
+  if (ua + warp <= ub && lane < 16 && (P.epi == FB200_EPI_RESIDUAL || (LL ? P.addl != nullptr : P.yp_add != nullptr) || P.yp_norm_w))
+    pre = epilogue_operands<LL>(P, ua + warp, lane, E);
   if (r.w0 < r.w1) {
     if (C.n == 0) prefetch_phase(P, R, warp, lane, C);  // nothing was fetched ahead
     Cursor cc = C.cc, ic = C.ic;
@@ -367,18 +506,35 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
     while (i < r.w1) {
       const int kend = min(q.ng, cc.kg + (r.w1 - i));
       float acc_g = 0.f, acc_g8 = 0.f;
+      auto refill = [&]() {
+        __syncwarp();
+        if (ic.i < r.w1) {  // refill the slot just consumed
+          if (lane == 0) ring_issue(R, slot, q.stride, ic);
+          cur_next(P, q, ic);
+        }
+        R.par ^= 1u << slot;
+        slot = slot + 1 == q.stages ? 0 : slot + 1;
+      };
+      if constexpr (LL) {
+        Group2Ptrs G = group2_ptrs(L, S.xl, reinterpret_cast<const float2*>(S.xsc), cc.kg, blocks16);
+        auto run = [&](auto group_fn) {
+          for (int kg = cc.kg; kg < kend; ++kg) {
+            mbar_wait(R.bar0 + 8 * slot, (R.par >> slot) & 1u, A.status);
+            group_fn(R.ptr + slot * q.stride, G);
+            refill();
+            group2_ptrs_next(G, blocks16);
+          }
+        };
+        // the barrier-free variants exist for K-quant programs only
+        if (cc.type == FB200_Q4_K) run([&](const uint8_t* tg, const Group2Ptrs& G2) { group2_q4k(G2.xq, G2.xsp, tg, L, acc_g, acc_g8); });
+        else run([&](const uint8_t* tg, const Group2Ptrs& G2) { group2_q6k(G2.xq, G2.xsp, tg, L, acc_g, acc_g8); });
+      } else {
       GroupPtrs G = group_ptrs(L, S.xl, S.xsc, S.xss, cc.kg, blocks16);
       auto run = [&](auto group_fn) {
         for (int kg = cc.kg; kg < kend; ++kg) {
           mbar_wait(R.bar0 + 8 * slot, (R.par >> slot) & 1u, A.status);
           group_fn(R.ptr + slot * q.stride);
-          __syncwarp();
-          if (ic.i < r.w1) {  // refill the slot just consumed
-            if (lane == 0) ring_issue(R, slot, q.stride, ic);
-            cur_next(P, q, ic);
-          }
-          R.par ^= 1u << slot;
-          slot = slot + 1 == q.stages ? 0 : slot + 1;
+          refill();
           group_ptrs_next(G, blocks16);
         }
       };
@@ -390,6 +546,7 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
       } else if (LEGACY) {
         if (cc.type == FB200_Q8_0) run([&](const uint8_t* tg) { group1_q8_0(G.xq, G.xscp, tg, L, acc_g, acc_g8); });
         else run([&](const uint8_t* tg) { group1_q4_0(G.xq, G.xscp, G.xssp, tg, L, acc_g, acc_g8); });
+      }
       }
       i += kend - cc.kg;
       const int u_done = cc.u, p_done = cc.p;
@@ -420,7 +577,7 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
         const bool complete = unit_first_item == u_done * q.ipu && i == (u_done + 1) * q.ipu;
         if (lane < 16) {
           if (complete) {
-            unit_epilogue<XS>(P, u_done, pv0, pv1, lane, E, pre);
+            unit_epilogue<XS, LL>(P, u_done, pv0, pv1, lane, E, pre, A.status);
           } else {
             float* pc = S.pieces + (warp * 2 + (u_done == u_first ? 0 : 1)) * 32;
             pc[lane] = pv0;
@@ -462,7 +619,7 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
       }
       if (tr && m == ua) tr[6] = global_ns();
       if (cta_whole) {
-        if (lane < 16) unit_epilogue<XS>(P, m, s0, s1, lane, E, pre);
+        if (lane < 16) unit_epilogue<XS, LL>(P, m, s0, s1, lane, E, pre, A.status);
         __syncwarp();
         if (tr && m == ua) tr[7] = global_ns();
         continue;
@@ -489,12 +646,13 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
           t0 += __ldcg(pc + lane);
           t1 += __ldcg(pc + 16 + lane);
         }
-        unit_epilogue<XS>(P, m, t0, t1, lane, E, pre);
+        unit_epilogue<XS, LL>(P, m, t0, t1, lane, E, pre, A.status);
       }
       __syncwarp();
     }
   }
   if (tr) tr[5] = global_ns();
+  if (LL && A.trace && tid == 0) atomicMax(A.trace + (size_t)A.nphases * 8 + (int)(lep - A.epoch_base) % A.nphases, global_ns());
   if (P.argmax_key) {
     // one atomic per CTA: lanes -> warp -> CTA maximum of the running keys
     unsigned long long k = E.best_key;
@@ -528,7 +686,8 @@ __device__ __forceinline__ float pack_source(const fb200_fused_phase& P, uint32_
   return v;
 }
 
-__device__ __noinline__ void pack_phase(const fb200_fused_phase& P) {
+template <bool LL>
+__device__ __noinline__ void pack_phase(const fb200_fused_phase& P, unsigned lep) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nblk = (P.K + 31) / 32;
   const uint32_t id = P.kind == FB200_PH_EMBED ? __ldcg(P.ids) : 0u;
@@ -537,9 +696,11 @@ __device__ __noinline__ void pack_phase(const fb200_fused_phase& P) {
     const bool valid = n < P.K;
     float v = valid ? pack_source(P, id, n) : 0.f;
     if (valid && P.xout) P.xout[n] = v;
+    if (LL && valid && P.xoutl) st_ll(P.xoutl + n, __float_as_uint(v), lep);
     const float nv = v;
     if (valid && P.yp_norm_w) v *= P.yp_norm_w[n];
-    emit_packed16(P.yp, n, v, nv, valid, 0xFFFFFFFFu);
+    if constexpr (LL) emit_ll16(P.yll, n, v, nv, valid, 0xFFFFFFFFu, lep);
+    else emit_packed16(P.yp, n, v, nv, valid, 0xFFFFFFFFu);
   }
 }
 
@@ -599,17 +760,20 @@ __device__ __noinline__ void advance_phase(const FusedArgs& A, const fb200_fused
 // The context is cut into at most att.nsplit splits of at least FUSED_SPLIT_KEYS keys: an item's
 // run time is mostly fixed latencies, so many small items finish sooner than few large ones, and
 // very short contexts run a single item per KV head with nothing to merge.
-template <int D, int ROWS>
-__device__ __noinline__ void attn_phase(const fb200_fused_phase& P, uint8_t* dsm) {
+template <int D, int ROWS, bool LL>
+__device__ __noinline__ void attn_phase(const fb200_fused_phase& P, uint8_t* dsm, unsigned lep, int* status) {
   const int tid = threadIdx.x;
   if (tid >= DEC_THREADS) return;
   fb200_dec_args a = P.att;
   a.pos_plus1 = __ldcg(a.pos_dev) + 1;
   const int skv = a.pos_plus1;
   a.nsplit = max(1, min(a.nsplit, (skv + FUSED_SPLIT_KEYS - 1) / FUSED_SPLIT_KEYS));
+  a.ep_in = lep - 1u;
+  a.ep_out = lep;
+  a.status = status;
   const int nitems = a.b * a.hkv * a.nsplit;
   for (int item = (int)blockIdx.x; item < nitems; item += (int)gridDim.x) {
-    attn_decode_item<D, FUSED_DEC_CH, ROWS, 1, false>(a, item, dsm, tid);
+    attn_decode_item<D, FUSED_DEC_CH, ROWS, 1, false, LL>(a, item, dsm, tid);
     dec_sync<1>();
   }
 }
@@ -617,75 +781,91 @@ __device__ __noinline__ void attn_phase(const fb200_fused_phase& P, uint8_t* dsm
 // One kernel variant per attention shape (head size D, query rows per KV head ROWS) and per
 // family of weight types (LEGACY = the 32-element block types too): a variant carries only the
 // code it runs, which keeps the instruction footprint of a step small.
-template <int D, int ROWS, bool LEGACY, bool XS>
+// LL: the phases of a step exchange flagged rows instead of meeting at grid barriers.
+template <int D, int ROWS, bool LEGACY, bool XS, bool LL>
 __global__ void __launch_bounds__(FT, 1)
 fused_step_kernel(const FusedArgs A) {
+  static_assert(!(LL && (XS || LEGACY)), "barrier-free variants: single GPU, K-quant weights");
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* ring = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FW * RING_BYTES);
-  uint8_t* xreg = smem + FW * RING_BYTES + FW * MAX_STAGES * 8;
+  constexpr int RB = LL ? RING_BYTES_LL : RING_BYTES;
+  constexpr int MS = LL ? MAX_STAGES_LL : MAX_STAGES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FW * RB);
+  uint8_t* xreg = smem + FW * RB + FW * MS * 8;
   Smem S;
   S.xl = xreg;
   S.pieces = reinterpret_cast<float*>(xreg + A.xregion);
   S.tmp = S.pieces + FW * 2 * 32;
   S.keys = reinterpret_cast<unsigned long long*>(S.tmp + 32);
   WarpRing R;
-  R.ptr = ring + warp * RING_BYTES;
+  R.ptr = ring + warp * RB;
   R.base = smem_u32(R.ptr);
-  R.bar0 = smem_u32(bars + warp * MAX_STAGES);
+  R.bar0 = smem_u32(bars + warp * MS);
   R.par = 0u;
   R.policy = l2_evict_first_policy();
   if (lane == 0) {
-    for (int s = 0; s < MAX_STAGES; ++s) mbar_init(R.bar0 + 8 * s, 1);
+    for (int s = 0; s < MS; ++s) mbar_init(R.bar0 + 8 * s, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
 
-  // Phase descriptors live in shared memory: a window of four consecutive phases (the current one
-  // and the next three, which always include the next product phase), refilled one per phase.
+  // Phase descriptors live in shared memory: a window of five consecutive phases (the current one,
+  // the next three, which always include the next product phase, and the one being fetched). The
+  // descriptor of phase g + 4 is copied asynchronously while phase g runs, so that its trip to L2
+  // never sits between two phases.
   uint32_t* sdesc = reinterpret_cast<uint32_t*>(S.keys + 32);
   const int total_phases = A.nsteps * A.nphases;
-  auto desc_of = [&](int g) { return reinterpret_cast<const fb200_fused_phase*>(sdesc + (g & 3) * DESC_WORDS); };
+  auto desc_of = [&](int g) { return reinterpret_cast<const fb200_fused_phase*>(sdesc + (g % DESC_SLOTS) * DESC_WORDS); };
   auto load_desc = [&](int g) {
     if (g >= total_phases) return;
-    const uint32_t* src = reinterpret_cast<const uint32_t*>(A.prog + g % A.nphases);
-    uint32_t* dst = sdesc + (g & 3) * DESC_WORDS;
-    for (int i = tid; i < DESC_WORDS; i += FT) dst[i] = src[i];
+    const uint4* src = reinterpret_cast<const uint4*>(A.prog + g % A.nphases);
+    uint4* dst = reinterpret_cast<uint4*>(sdesc + (g % DESC_SLOTS) * DESC_WORDS);
+    for (int i = tid; i < DESC_WORDS / 4; i += FT) cp_async16(dst + i, src + i);
   };
-  for (int g = 0; g < 4; ++g) load_desc(g);
+  for (int g = 0; g < DESC_SLOTS - 1; ++g) load_desc(g);
+  cp_async_wait_all();
   __syncthreads();
 
   unsigned target = 0u;
   Carry C;
   C.n = 0;
-  if (A.first_gemv >= 0 && A.first_gemv < 4) prefetch_phase(*desc_of(A.first_gemv), R, warp, lane, C);
+  if (A.first_gemv >= 0 && A.first_gemv < DESC_SLOTS - 1) prefetch_phase(*desc_of(A.first_gemv), R, warp, lane, C);
   int g = 0;
+  int prev_kind = -1;
   for (int step = 0; step < A.nsteps; ++step) {
     for (int ph = 0; ph < A.nphases; ++ph, ++g) {
-      if (g) {
-        grid_barrier(A, target, A.trace && step == A.nsteps - 1 ? A.trace + (size_t)A.nphases * 8 + ph : nullptr);
-        load_desc(g + 3);  // into the slot of the phase that has just ended
-      }
       const fb200_fused_phase& P = *desc_of(g);
+      if (g) {
+        // Flagged rows carry their own readiness, so a barrier-free variant meets only where plain
+        // memory changes hands: the greedy-token hand-over (argmax key -> ADVANCE -> next EMBED).
+        const bool meet = !LL || P.kind == FB200_PH_ADVANCE || prev_kind == FB200_PH_ADVANCE;
+        if (meet)
+          grid_barrier(A, target, A.trace && step == A.nsteps - 1 ? A.trace + (size_t)A.nphases * 8 + ph : nullptr);
+        else
+          __syncthreads();  // every warp is done with the previous phase (descriptor slot, activation region)
+      }
+      load_desc(g + DESC_SLOTS - 1);  // into the slot of the phase that has just ended; waited for below
+      prev_kind = P.kind;
       const unsigned epoch = XS ? A.x.epoch_base + (unsigned)(step * A.x.per_step + (P.xs_index >= 0 ? P.xs_index : 0)) : 0u;
+      const unsigned lep = A.epoch_base + (unsigned)g;  // flagged rows: this phase's epoch
       unsigned long long* tr = A.trace && blockIdx.x == 0 && tid == 0 && step == A.nsteps - 1 ? A.trace + ph * 8 : nullptr;
       if (tr) tr[0] = global_ns();
       switch (P.kind) {
         case FB200_PH_GEMV: {
-          S.xsc = reinterpret_cast<float*>(S.xl + (size_t)P.Kp * 4);
+          S.xsc = reinterpret_cast<float*>(S.xl + (LL ? ((size_t)P.Kp / 8 * 18 + 63) / 64 * 64 : (size_t)P.Kp * 4));
           S.xss = S.xsc + P.Kp / 16;
           const int ahead = P.next_gemv < 0 ? -1 : (P.next_gemv > ph ? P.next_gemv - ph : P.next_gemv + A.nphases - ph);
           const bool has_next = ahead > 0 && ahead <= 3 && g + ahead < total_phases;
-          gemv_phase<LEGACY, XS>(A, P, has_next ? desc_of(g + ahead) : nullptr, S, R, C, tr, epoch);
+          gemv_phase<LEGACY, XS, LL>(A, P, has_next ? desc_of(g + ahead) : nullptr, S, R, C, tr, epoch, lep);
           break;
         }
         case FB200_PH_ATTN:
-          attn_phase<D, ROWS>(P, xreg);
+          attn_phase<D, ROWS, LL>(P, xreg, lep, A.status);
           break;
         case FB200_PH_PACK:
         case FB200_PH_EMBED:
-          pack_phase(P);
+          pack_phase<LL>(P, lep);
           break;
         case FB200_PH_XSUM:
           if (XS) xsum_phase(A, P, epoch);
@@ -695,23 +875,24 @@ fused_step_kernel(const FusedArgs A) {
           break;
       }
       if (tr) tr[3] = global_ns();
+      cp_async_wait_all();  // this thread's part of the descriptor fetched during the phase (the meeting above publishes it)
     }
   }
 }
 
-size_t x_region_need(const fb200_fused_phase* prog, int nphases) {
+size_t x_region_need(const fb200_fused_phase* prog, int nphases, bool flagged) {
   size_t need = 0;
   for (int i = 0; i < nphases; ++i) {
     const auto& p = prog[i];
-    if (p.kind == FB200_PH_GEMV) need = std::max(need, (size_t)p.Kp * 4 + (size_t)p.Kp / 16 * 8);
+    if (p.kind == FB200_PH_GEMV) need = std::max(need, flagged ? (size_t)p.Kp / 8 * 18 + 64 + (size_t)p.Kp / 16 * 8 : (size_t)p.Kp * 4 + (size_t)p.Kp / 16 * 8);
     if (p.kind == FB200_PH_ATTN) need = std::max(need, dec_smem_bytes(p.att_d, FUSED_DEC_CH));
   }
   return (need + 127) / 128 * 128;
 }
 
-size_t smem_total(size_t xregion) {
-  return (size_t)FW * RING_BYTES + (size_t)FW * MAX_STAGES * 8 + xregion + (size_t)FW * 2 * 32 * 4 + 32 * 4 +
-         32 * 8 + 4 * DESC_WORDS * 4;
+size_t smem_total(size_t xregion, bool flagged) {
+  return (size_t)FW * (flagged ? RING_BYTES_LL : RING_BYTES) + (size_t)FW * (flagged ? MAX_STAGES_LL : MAX_STAGES) * 8 + xregion + (size_t)FW * 2 * 32 * 4 + 32 * 4 +
+         32 * 8 + DESC_SLOTS * DESC_WORDS * 4;
 }
 
 }  // namespace
@@ -719,7 +900,7 @@ size_t smem_total(size_t xregion) {
 int fb200_fused_grid(const fb200_device* dev) { return dev->sm_count; }
 
 bool fb200_fused_gemv_phase(fb200_fused_phase* p, const fb200_qmatrix* const* ws, float* const* ys, int nw,
-                            int epi, int grid) {
+                            int epi, int grid, bool flagged) {
   if (nw < 1 || nw > 3 || (epi != FB200_EPI_NONE && nw != 1)) return false;
   TileGeom geo0;
   if (!tile_geom(ws[0]->type, &geo0)) return false;
@@ -766,21 +947,42 @@ bool fb200_fused_gemv_phase(fb200_fused_phase* p, const fb200_qmatrix* const* ws
   // is then shared between CTAs and nothing has to be merged through global memory.
   const long long aligned = (long long)((p->nunits + grid - 1) / grid) * p->ipu;
   if (aligned * 5 <= (long long)p->chunk * 6) p->chunk = (int)aligned;
-  p->stages = std::min(MAX_STAGES, RING_BYTES / p->stride);
+  p->stages = flagged ? std::min(MAX_STAGES_LL, RING_BYTES_LL / p->stride) : std::min(MAX_STAGES, RING_BYTES / p->stride);
+  if (const char* e = getenv("FB200_FUSED_STAGES")) p->stages = std::max(1, std::min(p->stages, atoi(e)));
   return p->stages >= 1;
 }
 
-size_t fb200_fused_smem_bytes(const fb200_fused_phase* prog_host, int nphases) {
-  const size_t total = smem_total(x_region_need(prog_host, nphases));
+size_t fb200_fused_smem_bytes(const fb200_fused_phase* prog_host, int nphases, bool flagged) {
+  const size_t total = smem_total(x_region_need(prog_host, nphases, flagged), flagged);
   return total + STATIC_SMEM_RESERVE <= (size_t)SMEM_LIMIT ? total : 0;
 }
 
+namespace {
+// attention shape and weight-type family of a program
+void program_shape(const fb200_fused_phase* prog_host, int nphases, int* att_d, int* groups, bool* legacy) {
+  *att_d = 128; *groups = 1; *legacy = false;
+  for (int i = 0; i < nphases; ++i) {
+    const auto& ph = prog_host[i];
+    if (ph.kind == FB200_PH_ATTN) { *att_d = ph.att_d; *groups = std::max(*groups, ph.att.groups); }
+    if (ph.kind == FB200_PH_GEMV)
+      for (int j = 0; j < ph.nseg; ++j) *legacy = *legacy || ph.seg[j].type == FB200_Q4_0 || ph.seg[j].type == FB200_Q8_0;
+  }
+}
+}  // namespace
+
+bool fb200_fused_flagged_available(const fb200_fused_phase* prog_host, int nphases) {
+  int att_d, groups;
+  bool legacy;
+  program_shape(prog_host, nphases, &att_d, &groups, &legacy);
+  return !legacy && (att_d == 128 || att_d == 64);
+}
+
 int fb200_fused_launch(fb200_device* dev, const fb200_fused_phase* prog_dev, const fb200_fused_phase* prog_host,
-                       int nphases, int nsteps, bool record_history, const fb200_fused_xchg* xchg) {
+                       int nphases, int nsteps, bool record_history, const fb200_fused_xchg* xchg, bool flagged) {
   if (nphases <= 0 || nsteps <= 0) return FB200_OK;
   const int grid = fb200_fused_grid(dev);
-  const size_t xregion = x_region_need(prog_host, nphases);
-  const size_t smem = fb200_fused_smem_bytes(prog_host, nphases);
+  const size_t xregion = x_region_need(prog_host, nphases, flagged);
+  const size_t smem = fb200_fused_smem_bytes(prog_host, nphases, flagged);
   if (!smem) return fb200_fail(dev, FB200_ERR_CAPACITY, "fused step: the program does not fit in shared memory");
   int max_units = 1, first = -1;
   for (int i = 0; i < nphases; ++i)
@@ -802,25 +1004,27 @@ int fb200_fused_launch(fb200_device* dev, const fb200_fused_phase* prog_dev, con
     dev->fused_bytes = cap;
   }
   // kernel variant: attention shape and weight-type family of this program
-  int att_d = 128, groups = 1;
-  bool legacy = false;
-  for (int i = 0; i < nphases; ++i) {
-    const auto& ph = prog_host[i];
-    if (ph.kind == FB200_PH_ATTN) { att_d = ph.att_d; groups = std::max(groups, ph.att.groups); }
-    if (ph.kind == FB200_PH_GEMV)
-      for (int j = 0; j < ph.nseg; ++j) legacy = legacy || ph.seg[j].type == FB200_Q4_0 || ph.seg[j].type == FB200_Q8_0;
-  }
+  int att_d, groups;
+  bool legacy;
+  program_shape(prog_host, nphases, &att_d, &groups, &legacy);
   void (*kern)(const FusedArgs) = nullptr;
   int variant = 0;
   const bool xs = xchg && xchg->world > 1;  // the exchange code lives in variants of its own
   if (xs && legacy) return fb200_fail(dev, FB200_ERR_UNSUPPORTED_DTYPE, "fused step: tensor parallel needs K-quant weights");
-  if (att_d == 128 && groups <= 4 && !legacy) { kern = xs ? fused_step_kernel<128, 4, false, true> : fused_step_kernel<128, 4, false, false>; variant = xs ? 5 : 0; }
-  else if (att_d == 128 && !legacy) { kern = xs ? fused_step_kernel<128, 8, false, true> : fused_step_kernel<128, 8, false, false>; variant = xs ? 6 : 1; }
-  else if (att_d == 128) { kern = fused_step_kernel<128, 8, true, false>; variant = 2; }
-  else if (att_d == 64 && !legacy) { kern = xs ? fused_step_kernel<64, 8, false, true> : fused_step_kernel<64, 8, false, false>; variant = xs ? 7 : 3; }
-  else if (att_d == 64) { kern = fused_step_kernel<64, 8, true, false>; variant = 4; }
+  if (flagged && (xs || legacy)) return fb200_fail(dev, FB200_ERR_INVALID_ARGUMENT, "fused step: no barrier-free variant for this program");
+  if (flagged) {
+    if (att_d == 128 && groups <= 4) { kern = fused_step_kernel<128, 4, false, false, true>; variant = 8; }
+    else if (att_d == 128) { kern = fused_step_kernel<128, 8, false, false, true>; variant = 9; }
+    else if (att_d == 64) { kern = fused_step_kernel<64, 8, false, false, true>; variant = 10; }
+    else return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "fused step: head size %d", att_d);
+  }
+  else if (att_d == 128 && groups <= 4 && !legacy) { kern = xs ? fused_step_kernel<128, 4, false, true, false> : fused_step_kernel<128, 4, false, false, false>; variant = xs ? 5 : 0; }
+  else if (att_d == 128 && !legacy) { kern = xs ? fused_step_kernel<128, 8, false, true, false> : fused_step_kernel<128, 8, false, false, false>; variant = xs ? 6 : 1; }
+  else if (att_d == 128) { kern = fused_step_kernel<128, 8, true, false, false>; variant = 2; }
+  else if (att_d == 64 && !legacy) { kern = xs ? fused_step_kernel<64, 8, false, true, false> : fused_step_kernel<64, 8, false, false, false>; variant = xs ? 7 : 3; }
+  else if (att_d == 64) { kern = fused_step_kernel<64, 8, true, false, false>; variant = 4; }
   else return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "fused step: head size %d", att_d);
-  static bool configured[64][8] = {};
+  static bool configured[64][12] = {};
   if (!configured[dev->ordinal & 63][variant]) {
     FB_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       SMEM_LIMIT - STATIC_SMEM_RESERVE));
@@ -838,6 +1042,14 @@ int fb200_fused_launch(fb200_device* dev, const fb200_fused_phase* prog_dev, con
   a.counters = reinterpret_cast<int*>((uint8_t*)dev->fused + cnt_off);
   a.status = dev->status;
   if (xchg) a.x = *xchg;
+  if (flagged) {
+    // one epoch per phase executed; 0 is the value of cleared buffers and is skipped when the
+    // 32-bit counter wraps (readers compare for equality, so old epochs never match new ones)
+    const uint32_t count = (uint32_t)nsteps * (uint32_t)nphases;
+    if (dev->ll_epoch + count < dev->ll_epoch || dev->ll_epoch == 0) dev->ll_epoch = 1;
+    a.epoch_base = dev->ll_epoch;
+    dev->ll_epoch += count;
+  }
   FB_CUDA(dev, cudaMemsetAsync(a.bar, 0, 4, dev->stream));
   // FB200_FUSED_TRACE=1: per-phase time stamps of CTA 0, printed to stderr after the launch
   static const bool want_trace = getenv("FB200_FUSED_TRACE") && getenv("FB200_FUSED_TRACE")[0] == '1';
@@ -868,7 +1080,10 @@ int fb200_fused_launch(fb200_device* dev, const fb200_fused_phase* prog_dev, con
     for (int i = 0; i < nphases; ++i) {
       const unsigned long long* q = t.data() + (size_t)i * 8;
       const double t0 = (double)(q[0] - t[0]) / 1e3;
-      const double ta = i ? ((double)q[0] - (double)t[(size_t)nphases * 8 + i]) / 1e3 : 0.0;
+      // barriers: phase start minus the last CTA's arrival; flagged rows: end of this CTA's activation
+      // load minus the moment the last producer CTA of the previous phase finished its epilogues
+      const double ta = !i ? 0.0 : flagged ? ((double)q[1] - (double)t[(size_t)nphases * 8 + i - 1]) / 1e3
+                                           : ((double)q[0] - (double)t[(size_t)nphases * 8 + i]) / 1e3;
       if (prog_host[i].kind == FB200_PH_GEMV)
         fprintf(stderr, "  %3d gemv  %9.2f [%5.2f] %7.2f %7.2f %7.2f  (items %d, K %d; own loop %.2f, sync %.2f, merge %.2f = sum %.2f + epilogue %.2f + rest)\n",
                 i, t0, ta, (double)(q[1] - q[0]) / 1e3, (double)(q[2] - q[1]) / 1e3, (double)(q[3] - q[2]) / 1e3,

@@ -59,13 +59,14 @@ __device__ __forceinline__ bool fb200_wait_arrival(const unsigned* word, unsigne
 struct fb200_fused_seg {
   const uint8_t* w;  // tiled weight bytes
   float* y;          // optional float output row
+  uint2* yl;         // optional output row as f32 granules {value, epoch} (flagged rows)
   int type;          // ggml type id
   int tg;            // bytes per tile-group
   int units;         // tiles (tile pairs for SwiGLU) of this matrix
   int n_out;         // logical outputs
 };
 
-struct fb200_fused_phase {
+struct alignas(16) fb200_fused_phase {  // 16-byte multiples: descriptors are copied with 16-byte asynchronous copies
   int kind;
   int next_gemv;  // index of the next product phase in execution order (may wrap to the next step), -1: none
   // ---- FB200_PH_GEMV: up to three matrices that share the activation row
@@ -109,6 +110,16 @@ struct fb200_fused_phase {
   int* pos_dev;
   int* step_dev;
   int hist_cap;
+  // ---- flagged rows (single-GPU kernel variants without grid barriers between phases): the same
+  // operands as above, published by their producers as {data, epoch} granules (packed_act.cuh)
+  // that the consumer polls. *_back = how many phases before this one the producer ran.
+  fb200_ll_act xll;   // activation row (producer: the phase before)
+  fb200_ll_act yll;   // packed output (also of EMBED)
+  const uint2* r1l;   // residual epilogue operands as f32 granules
+  const uint2* r2l;
+  const uint2* addl;  // yp_add
+  int r1_back, r2_back, add_back;
+  uint2* xoutl;       // EMBED: the float row as granules
   // ---- tensor parallel: index of this phase's exchange within a step (-1: none). On a product
   // phase: rows go to the peers instead of seg[0].y; on FB200_PH_XSUM: out_sum = sum over ranks,
   // v = sum + src + src_add -> xout, packed into yp (times yp_norm_w); on FB200_PH_ADVANCE: the
@@ -120,11 +131,14 @@ struct fb200_fused_phase {
 // Fills the derived fields of a product phase (units, items, chunk, ring geometry) from its
 // matrices; `grid` = CTAs of the launch. Returns false if the matrices cannot share a phase.
 bool fb200_fused_gemv_phase(fb200_fused_phase* p, const fb200_qmatrix* const* ws, float* const* ys, int nw,
-                            int epi, int grid);
+                            int epi, int grid, bool flagged);
 // Shared memory the program needs; 0 if it does not fit.
-size_t fb200_fused_smem_bytes(const fb200_fused_phase* prog_host, int nphases);
+size_t fb200_fused_smem_bytes(const fb200_fused_phase* prog_host, int nphases, bool flagged = false);
 // Number of CTAs of a launch on this device.
 int fb200_fused_grid(const fb200_device* dev);
 // Runs `nsteps` passes over the program (device copy `prog_dev` of `prog_host`).
+// `flagged`: the program carries flagged rows; the launch takes the barrier-free kernel variant.
 int fb200_fused_launch(fb200_device* dev, const fb200_fused_phase* prog_dev, const fb200_fused_phase* prog_host,
-                       int nphases, int nsteps, bool record_history, const fb200_fused_xchg* xchg);
+                       int nphases, int nsteps, bool record_history, const fb200_fused_xchg* xchg, bool flagged);
+// True when a program of these matrix types and attention shape has a barrier-free variant.
+bool fb200_fused_flagged_available(const fb200_fused_phase* prog_host, int nphases);

@@ -152,6 +152,18 @@ struct fb200_llama {
   int* att_done = nullptr;  // arrival counters of the attention splits, one per (batch, kv head)
   // single-row step: activation rows travel between kernels in the products' operand form
   fb200_packed_act px, patt, pv, ph;  // residual stream, attention output, attn_out + x, SwiGLU output
+  // the same rows (and q / k / v, the residual stream and the attention projection as f32) as flagged
+  // rows for the barrier-free variants of the persistent kernel: one slab, zero at creation
+  uint8_t* ll_slab = nullptr;
+  fb200_ll_act px_ll, patt_ll, pv_ll, ph_ll;
+  uint2 *q_ll = nullptr, *k_ll = nullptr, *v_ll = nullptr, *x_ll = nullptr, *attn_ll = nullptr;
+  // FB200_FUSED_LL=1 selects the barrier-free variants. Off by default: they are correct (parity
+  // tests run both forms) but measured slower so far (2.2 - 2.6 ms per step of the 8B-shaped model
+  // against 2.03 ms with grid barriers): the trip a flagged row saves at each phase boundary is
+  // outweighed by slower epilogues (8-byte flagged stores), the 86 KB polled row in front of the
+  // down projection and a product loop that gets fewer registers.
+  bool fused_flagged = false;
+  bool fused_is_flagged = false;  // the current program uses the flagged rows
   bool used_key = false;  // the last forward pass left its greedy id in argmax_key, not in next
   // CUDA graph of a single-token step, per batch size
   cudaGraphExec_t graph_exec = nullptr;
@@ -276,6 +288,17 @@ int build_fused_program(fb200_llama* m) {
   // buffers and an XSUM phase adds them up (needs the peer exchange; otherwise the step runs as
   // separate kernels with NCCL sums)
   const bool tp = m->tp_size > 1;
+  // the barrier-free variants: one GPU, K-quant weights (decided before the phases are laid out: their
+  // weight ring is deeper)
+  bool kquant = true;
+  for (const auto& L : m->layers)
+    for (const fb200_qmatrix* q : {L.wq, L.wk, L.wv, L.wo, L.gate_up, L.down})
+      kquant = kquant && (q->type == FB200_Q4_K || q->type == FB200_Q6_K);
+  {
+    const fb200_qmatrix* ow = m->output ? m->output : m->token_embd;
+    kquant = kquant && (ow->type == FB200_Q4_K || ow->type == FB200_Q6_K);
+  }
+  const bool flagged = m->fused_flagged && !tp && kquant;
   {
     fb200_fused_phase p = blank();
     p.kind = FB200_PH_EMBED;
@@ -293,6 +316,8 @@ int build_fused_program(fb200_llama* m) {
     p.xout = m->x;
     p.yp = m->px;
     p.yp_norm_w = m->layers[0].attn_norm;
+    p.xoutl = m->x_ll; p.yll = m->px_ll;
+    if (flagged) p.xout = nullptr;
     prog.push_back(p);
   }
   int nsplit = grid / HK;
@@ -302,7 +327,7 @@ int build_fused_program(fb200_llama* m) {
   auto gemv = [&](const fb200_qmatrix* const* ws, float* const* ys, int nw, int epi, fb200_fused_phase& p) {
     p = blank();
     p.eps = c.rms_eps;
-    return fb200_fused_gemv_phase(&p, ws, ys, nw, epi, grid);
+    return fb200_fused_gemv_phase(&p, ws, ys, nw, epi, grid, flagged);
   };
   for (int li = 0; li < c.n_layer; ++li) {
     LayerW& L = m->layers[li];
@@ -311,6 +336,8 @@ int build_fused_program(fb200_llama* m) {
     float* qkv_out[3] = {m->q, m->k, m->v};
     if (!gemv(qkv, qkv_out, 3, FB200_EPI_NONE, p)) return FB200_OK;
     p.xp = m->px; p.xp_norm = 1;
+    p.xll = m->px_ll; p.seg[0].yl = m->q_ll; p.seg[1].yl = m->k_ll; p.seg[2].yl = m->v_ll;
+    if (flagged) p.seg[0].y = p.seg[1].y = p.seg[2].y = nullptr;  // the flagged rows are the only copy
     prog.push_back(p);
 
     p = blank();
@@ -321,12 +348,17 @@ int build_fused_program(fb200_llama* m) {
     p.att.part = m->att_part; p.att.out = nullptr; p.att.done = m->att_done; p.att.out_packed = m->patt;
     p.att.b = 1; p.att.h = H; p.att.hkv = HK; p.att.groups = H / HK; p.att.cap = c.max_seq_len;
     p.att.nsplit = nsplit; p.att.scale = (float)(1.0 / sqrt((double)D));
+    p.att.q_ll = m->q_ll; p.att.k_ll = m->k_ll; p.att.v_ll = m->v_ll; p.att.out_ll = m->patt_ll;
     prog.push_back(p);
 
     const fb200_qmatrix* wo = L.wo;
     float* wo_out = tp ? nullptr : m->attn_out;
     if (!gemv(&wo, &wo_out, 1, FB200_EPI_NONE, p)) return FB200_OK;
     p.xp = m->patt;
+    // flagged rows: attn_out as granules; the packed row is (attn_out + x) times the FFN norm weight, x
+    // published three phases earlier (the previous layer's down projection, or the embedding)
+    p.xll = m->patt_ll; p.seg[0].yl = m->attn_ll; p.yll = m->pv_ll; p.addl = m->x_ll; p.add_back = 3;
+    if (flagged) p.seg[0].y = nullptr;
     if (tp) {
       p.xs_index = 2 * li;
       prog.push_back(p);
@@ -342,12 +374,17 @@ int build_fused_program(fb200_llama* m) {
     if (!gemv(&gu, &gu_out, 1, FB200_EPI_SWIGLU, p)) return FB200_OK;
     p.xp = m->pv; p.xp_norm = 1;
     p.yp = m->ph;
+    p.xll = m->pv_ll; p.yll = m->ph_ll;
     prog.push_back(p);
 
     const fb200_qmatrix* dn = L.down;
     float* dn_out = tp ? nullptr : m->x;
     if (!gemv(&dn, &dn_out, 1, tp ? FB200_EPI_NONE : FB200_EPI_RESIDUAL, p)) return FB200_OK;
     p.xp = m->ph;
+    // flagged rows: x = (down + attn_out) + x with attn_out from two phases back and x from five
+    p.xll = m->ph_ll; p.seg[0].yl = m->x_ll; p.yll = m->px_ll;
+    p.r1l = m->attn_ll; p.r1_back = 2; p.r2l = m->x_ll; p.r2_back = 5;
+    if (flagged) p.seg[0].y = nullptr;
     if (tp) {
       p.xs_index = 2 * li + 1;
       prog.push_back(p);
@@ -367,6 +404,7 @@ int build_fused_program(fb200_llama* m) {
     float* lg = m->logits;
     if (!gemv(&ow, &lg, 1, FB200_EPI_NONE, p)) return FB200_OK;
     p.xp = m->px; p.xp_norm = 1;
+    p.xll = m->px_ll;
     p.argmax_key = m->argmax_key;
     prog.push_back(p);
     p = blank();
@@ -386,7 +424,10 @@ int build_fused_program(fb200_llama* m) {
     prev = i;
   }
   if (prev >= 0) prog[prev].next_gemv = first;
-  if (!fb200_fused_smem_bytes(prog.data(), (int)prog.size())) return FB200_OK;
+  // the barrier-free variants: one GPU, K-quant weights
+  m->fused_is_flagged = flagged && fb200_fused_flagged_available(prog.data(), (int)prog.size());
+  if (flagged && !m->fused_is_flagged) return FB200_OK;  // laid out for a variant that does not exist
+  if (!fb200_fused_smem_bytes(prog.data(), (int)prog.size(), m->fused_is_flagged)) return FB200_OK;
   FB_CUDA(dev, cudaStreamSynchronize(dev->stream));
   if (m->prog_dev) { cudaFree(m->prog_dev); m->prog_dev = nullptr; }
   FB_CUDA(dev, cudaMalloc(&m->prog_dev, prog.size() * sizeof(fb200_fused_phase)));
@@ -412,7 +453,7 @@ int run_fused(fb200_llama* m, int steps, bool record) {
       xs.id_base = (unsigned)(m->tp_rank * m->vocab_local);
     }
     if ((rc = fb200_fused_launch(dev, m->prog_dev, m->prog_host.data(), (int)m->prog_host.size(), n, record,
-                                 m->tp_size > 1 ? &xs : nullptr)))
+                                 m->tp_size > 1 ? &xs : nullptr, m->fused_is_flagged)))
       return rc;
     done += n;
   }
@@ -684,6 +725,24 @@ int fb200_llama_create(fb200_device* dev, const fb200_llama_config* cfg, fb200_l
         (prc = packed(&m->patt, (size_t)c.n_head * c.head_dim)) || (prc = packed(&m->ph, c.ffn)))
       return prc;
   }
+  {
+    // flagged rows: packed rows take 96 bytes per 16 elements, f32 rows 8 bytes per element
+    auto padded = [](size_t n) { return (n + 255) / 256 * 256 + 256; };
+    const size_t qd = (size_t)c.n_head * c.head_dim, kvd = (size_t)c.n_kv_head * c.head_dim;
+    const size_t packed_n[4] = {padded(c.hidden), padded(qd), padded(c.hidden), padded(c.ffn)};
+    const size_t f32_n[5] = {padded(qd), padded(kvd), padded(kvd), padded(c.hidden), padded(c.hidden)};
+    size_t bytes = 0;
+    for (size_t n : packed_n) bytes += n / 16 * FB200_LL_GRANULES * sizeof(uint2);
+    for (size_t n : f32_n) bytes += n * sizeof(uint2);
+    FB_CUDA(dev, cudaMalloc(&m->ll_slab, bytes));
+    FB_CUDA(dev, cudaMemset(m->ll_slab, 0, bytes));
+    uint8_t* p = m->ll_slab;
+    fb200_ll_act* rows[4] = {&m->px_ll, &m->patt_ll, &m->pv_ll, &m->ph_ll};
+    for (int i = 0; i < 4; ++i) { rows[i]->g = reinterpret_cast<uint2*>(p); p += packed_n[i] / 16 * FB200_LL_GRANULES * sizeof(uint2); }
+    uint2** f32s[5] = {&m->q_ll, &m->k_ll, &m->v_ll, &m->x_ll, &m->attn_ll};
+    for (int i = 0; i < 5; ++i) { *f32s[i] = reinterpret_cast<uint2*>(p); p += f32_n[i] * sizeof(uint2); }
+    if (const char* e = getenv("FB200_FUSED_LL")) m->fused_flagged = e[0] == '1' && e[1] == 0;
+  }
   // attention split scratch: the largest a forward pass can ask for is bounded by 64 splits of
   // a single-token step or one split set of a whole-context prefill
   size_t a1, a2;
@@ -716,7 +775,7 @@ int fb200_llama_free(fb200_llama* m) {
   void* bufs[] = {m->output_norm, m->rope_cos, m->rope_sin, m->x, m->xn, m->q, m->k, m->v, m->att,
                   m->attn_out, m->hbuf, m->gbuf, m->last, m->logits, m->att_part, m->ids, m->next,
                   m->hist, m->pos_dev, m->step_dev, m->argmax_key, m->att_done, m->best_val, m->best_pair,
-                  m->tok_hist, m->mu_dev};
+                  m->tok_hist, m->mu_dev, m->ll_slab};
   for (void* b : bufs) if (b) cudaFree(b);
   for (fb200_packed_act* p : {&m->px, &m->patt, &m->pv, &m->ph}) {
     void* pb[] = {p->limbs, p->xsc, p->xss, p->sumsq};

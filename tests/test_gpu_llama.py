@@ -38,7 +38,9 @@ def test_prefill_and_decode_logits(dev, batch):
     assert gpu.position == 9 + 6
 
 
-def test_greedy_tokens_match_for_32_steps(dev):
+@pytest.mark.parametrize("flagged_rows", [False, True], ids=["grid-barriers", "flagged-rows"])
+def test_greedy_tokens_match_for_32_steps(dev, flagged_rows, monkeypatch):
+    monkeypatch.setenv("FB200_FUSED_LL", "1" if flagged_rows else "0")
     # first 32 greedy tokens identical on a random-weight model; a step whose oracle top-1/top-2
     # margin is below the measured logit error is indeterminate and re-synchronised
     cfg = tiny_cfg()
@@ -80,8 +82,10 @@ def test_graph_step_equals_eager_prefill(dev):
     assert e.value.code == kb.ERR_CAPACITY
 
 
+@pytest.mark.parametrize("flagged_rows", [False, True], ids=["grid-barriers", "flagged-rows"])
 @pytest.mark.parametrize("head_dim,n_head,n_kv_head", [(64, 4, 2), (128, 8, 2), (128, 8, 1)])
-def test_decode_over_a_long_context(dev, head_dim, n_head, n_kv_head):
+def test_decode_over_a_long_context(dev, head_dim, n_head, n_kv_head, flagged_rows, monkeypatch):
+    monkeypatch.setenv("FB200_FUSED_LL", "1" if flagged_rows else "0")
     # several attention splits per KV head (one per 128 cached keys), 4 or 8 query rows per KV
     # head, a prompt whose length is not a multiple of the split size
     cfg = dict(tiny_cfg(), ctx=448, head_dim=head_dim, n_head=n_head, n_kv_head=n_kv_head)
@@ -128,7 +132,11 @@ def test_model_loaded_from_a_gguf_file_equals_the_directly_built_one(dev, tmp_pa
     assert np.array_equal(direct.generate_greedy(nxt_a, 8), loaded.generate_greedy(nxt_b, 8))
 
 
-def test_decoder_at_llama3_8b_widths(dev):
+@pytest.mark.parametrize("flagged_rows", [False, True], ids=["grid-barriers", "flagged-rows"])
+def test_decoder_at_llama3_8b_widths(dev, flagged_rows, monkeypatch):
+    # both forms of the persistent decode kernel: phases separated by grid barriers (the default) and
+    # the barrier-free variant whose phases exchange flagged rows (two-limb activations)
+    monkeypatch.setenv("FB200_FUSED_LL", "1" if flagged_rows else "0")
     # the program the benchmark times, two layers deep: hidden 4096, FFN 14336, 32/8 heads of 128,
     # vocabulary 128256, Q4_K body with Q6_K attn_v / ffn_down / output head.
     cfg = dict(llama3_8b_cfg(ctx=256), n_layer=2)

@@ -112,36 +112,42 @@ def test_mirostat2_matches_the_oracle(dev):
 
 @pytest.mark.parametrize("batch", [1, 2])
 def test_generate_sampled_matches_stepwise_oracle(dev, batch):
-    # the device-resident sampled loop (fused step or captured graph + sampler kernel per step,
-    # nothing read back in between) against forward passes and draws of the oracle
+    # The device-resident sampled loop (fused step or captured graph + sampler kernel per step,
+    # nothing read back in between). Its tokens are replayed through forward() on the same model
+    # (the same kernels, so the same logits bit for bit) and every draw is repeated by the oracle's
+    # sampler on those logits with the session's history as penalty window and the position as
+    # draw counter. Logit parity with the oracle's forward pass is the subject of test_gpu_llama.
     cfg = tiny_cfg()
     gpu, cpu = build_models(dev, cfg, batch=batch, seed=41)
     rng = np.random.default_rng(42)
     prompt = rng.integers(0, cfg["vocab"], size=(batch, 6), dtype=np.uint32)
-    _, first = gpu.forward(prompt)
-    lo = cpu.forward(prompt)
-    first = np.array([O.top_k(lo[b], 1)[0][0] for b in range(batch)], dtype=np.uint32)
+    lg, first = gpu.forward(prompt)
+    assert F.rel_l2(lg, cpu.forward(prompt)) < 2e-3
     scfg = dict(temperature=0.9, top_k=30, top_p=0.95, repetition_penalty=1.2, repetition_penalty_range=16)
     steps = 12
     got = gpu.generate_sampled(first, steps, kb.SamplerConfig(seed=5, **scfg))
-    assert got.shape == (batch, steps)
+    assert got.shape == (batch, steps) and gpu.position == 6 + steps
+    assert dev.status() == 0
+    gpu.reset()
+    gpu.forward(prompt)
     history = [list(prompt[b]) + [int(first[b])] for b in range(batch)]
     tok = first.copy()
-    alive = [True] * batch
+    decided = 0
     for s in range(steps):
-        lo = cpu.forward(tok[:, None])
+        lg, _ = gpu.forward(tok[:, None])
         for b in range(batch):
-            want, margin, _ = O.sample(lo[b], previous=np.array(history[b], np.uint32), seed=5,
+            want, margin, _ = O.sample(lg[b], previous=np.array(history[b], np.uint32), seed=5,
                                        counter=len(history[b]), row=b, **scfg)
-            if alive[b] and got[b, s] != want:
-                # logits differ by ~1e-6 between the two sides: only a draw next to a boundary may flip
-                assert margin < 1e-3, (b, s, margin)
-                alive[b] = False
-            nxt = int(got[b, s]) if alive[b] else want
-            history[b].append(nxt)
-            tok[b] = nxt
-        if not all(alive):
-            break
-    assert s >= 4
-    assert gpu.position == 6 + steps
-    assert dev.status() == 0
+            if margin > 1e-5:  # otherwise one ulp of an exponential decides
+                assert got[b, s] == want, (b, s, margin)
+                decided += 1
+            history[b].append(int(got[b, s]))
+            tok[b] = got[b, s]
+    assert decided >= steps * batch // 2
+    # the samplers do not disturb greedy decoding afterwards: temperature 0 = greedy ids
+    gpu.reset()
+    _, first = gpu.forward(prompt)
+    greedy = gpu.generate_greedy(first, 6)
+    gpu.reset()
+    gpu.forward(prompt)
+    assert np.array_equal(gpu.generate_sampled(first, 6, kb.SamplerConfig(temperature=0.0, top_k=5)), greedy)
