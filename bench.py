@@ -602,6 +602,10 @@ def run_sweep(args):
 
 
 def run_ours(args):
+    # stdout carries exactly one line, the JSON record: whatever libraries print while they start
+    # (NCCL announces its version on stdout) goes to stderr instead
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     import torch
     import torch.distributed as dist
     import kalosm_b200 as kb
@@ -783,6 +787,8 @@ def run_ours(args):
     if tp_leg is not None:
         line["tensor_parallel"] = {"tp": world, "model": "llama3-70b-shaped, all Q4_K, prompt %d, 128 greedy steps" % args.tp_prompt,
                                    "by_batch": tp_leg}
+    sys.stdout.flush()
+    os.dup2(real_stdout, 1)
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

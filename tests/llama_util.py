@@ -10,9 +10,11 @@ def tiny_cfg():
     return dict(n_layer=2, hidden=256, ffn=512, n_head=4, n_kv_head=2, head_dim=64, vocab=1024, ctx=64)
 
 
-def tp_cfg():
-    """Smallest shapes that still cut on 256-element blocks over two ranks (attn_output K = 512)."""
-    return dict(n_layer=2, hidden=512, ffn=1024, n_head=8, n_kv_head=2, head_dim=64, vocab=1024, ctx=96)
+def tp_cfg(world=2):
+    """Smallest shapes that still cut on 256-element blocks over `world` ranks: every rank gets four
+    query heads, one KV head and 512 FFN columns (attn_output K = 256 per rank, ffn_down K = 512)."""
+    return dict(n_layer=2, hidden=512, ffn=512 * world, n_head=4 * world, n_kv_head=world, head_dim=64,
+                vocab=1024, ctx=96)
 
 
 def llama3_8b_cfg(ctx=1024):

@@ -1,4 +1,6 @@
-"""Tensor-parallel decoder on two GPUs against the oracle (skipped on a single-GPU box)."""
+"""Tensor-parallel decoder on 2, 4 and 8 GPUs against the oracle (each case is skipped on a box with
+fewer GPUs). One process per GPU under torch.distributed.run; NVLS off so that a rank that failed
+could not leave the others bound to a multicast object."""
 import os
 import subprocess
 import sys
@@ -9,13 +11,15 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def test_two_rank_tensor_parallel_llama_matches_oracle():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tensor_parallel_llama_matches_oracle(world):
     import torch
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-           "--master-addr", "127.0.0.1", "--master-port", "29741", os.path.join(ROOT, "tests", "tp_worker.py")]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
+           "--master-addr", "127.0.0.1", "--master-port", str(29741 + world), os.path.join(ROOT, "tests", "tp_worker.py")]
     p = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900)
     assert p.returncode == 0, p.stdout[-4000:]
-    assert "TP_OK rank 0" in p.stdout and "TP_OK rank 1" in p.stdout, p.stdout[-4000:]
+    for r in range(world):
+        assert f"TP_OK rank {r}" in p.stdout, p.stdout[-4000:]

@@ -42,7 +42,7 @@ def main():
     t = dev.tensor(np.full((3, 5), float(rank + 1), np.float32))
     assert np.all(comm.all_reduce_sum(t).as_slice() == world * (world + 1) / 2)
 
-    cfg, batch = tp_cfg(), 2
+    cfg, batch = tp_cfg(world), 2
     gpu, cpu = build_models(dev, cfg, batch=batch, seed=5, want_cpu=(rank == 0), comm=comm)
     prompt = np.random.default_rng(6).integers(0, cfg["vocab"], size=(batch, 40), dtype=np.uint32)
     lg, nxt = gpu.forward(prompt)
