@@ -147,6 +147,7 @@ int fb200_device_destroy(fb200_device* dev) {
   cudaSetDevice(dev->ordinal);
   cudaStreamSynchronize(dev->stream);
   if (dev->xpack) cudaFree(dev->xpack);
+  if (dev->argmax_part) cudaFree(dev->argmax_part);
   if (dev->stage) cudaFree(dev->stage);
   if (dev->normed) cudaFree(dev->normed);
   if (dev->status) cudaFree(dev->status);

@@ -306,13 +306,24 @@ int kv_capacity_rule(int required, int max_len) {
 // still running; only q and the new k, v rows are read after the wait.
 // One query position per sequence against a cache that already holds every key (q already
 // rotated): the decode form of fb200_flash_attention. One CTA per (batch, KV head, split).
-constexpr int DEC_CH = 128;  // keys per shared-memory chunk
+constexpr int DEC_CH = 64;   // keys per shared-memory chunk
+constexpr int DEC_NB = 2;    // two staging buffers: the next chunk is copied while this one is used
 
 template <int D, int ROWS_T>
 __global__ void __launch_bounds__(DEC_THREADS)
-attn_decode_kernel(const fb200_dec_args a) {
+attn_decode_kernel(const fb200_dec_args a0) {
   extern __shared__ __align__(128) uint8_t dsm[];
-  attn_decode_item<D, DEC_CH, ROWS_T, 0, false>(a, (int)blockIdx.x, dsm, (int)threadIdx.x);
+  // The launch provides nsplit splits per (batch, kv head) for the longest context; a short context
+  // uses the first few of them (at least min_keys keys each) and the other CTAs have nothing to do.
+  fb200_dec_args a = a0;
+  const int skv = a.pos_dev ? __ldcg(a.pos_dev) + 1 : a.skv;
+  const int mk = a.min_keys > 0 ? a.min_keys : 64;
+  const int ns = max(1, min(a.nsplit, (skv + mk - 1) / mk));
+  const int split = (int)blockIdx.x % a.nsplit, rest = (int)blockIdx.x / a.nsplit;
+  if (split >= ns) return;
+  if (a.pos_dev) a.pos_plus1 = skv;
+  a.nsplit = ns;
+  attn_decode_item<D, DEC_CH, ROWS_T, 0, false, false, DEC_NB>(a, rest * ns + split, dsm, (int)threadIdx.x);
 }
 
 }  // namespace
@@ -369,7 +380,7 @@ int fb200_launch_attention_decode_args(fb200_device* dev, const fb200_dec_args& 
   if (a.h % a.hkv || a.groups > DEC_ROWS || (d != 64 && d != 128) || a.nsplit < 1 || a.nsplit > 32)
     return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "attention_decode: unsupported head layout");
   const unsigned grid = (unsigned)(a.b * a.hkv * a.nsplit);
-  const size_t smem = dec_smem_bytes(d, DEC_CH);
+  const size_t smem = dec_smem_bytes(d, DEC_CH, DEC_NB);
   static bool configured[64] = {false};
   if (!configured[dev->ordinal & 63]) {
     FB_CUDA(dev, cudaFuncSetAttribute(attn_decode_kernel<128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));

@@ -29,6 +29,8 @@ struct fb200_dec_args {
   int b, h, hkv, groups, cap, nsplit;
   float scale;
   int pos_plus1;        // > 0: *pos_dev + 1, already read by the caller (saves a dependent load); 0: not known
+  int min_keys;         // stand-alone kernel: a split takes at least this many keys (0: 64), so short
+                        // contexts run fewer splits than the launch provided
   // flagged rows (persistent decode kernel without grid barriers between its phases): q, k_new
   // and v_new arrive as f32 granules {value, epoch} that the item polls, and the merged output
   // leaves as a flagged packed row
@@ -56,10 +58,15 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
 __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's committed copy groups are still in flight.
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// Bytes of dynamic shared memory one item needs.
-__host__ __device__ constexpr size_t dec_smem_bytes(int d, int dec_ch) {
-  return (size_t)2 * dec_ch * (d * 2 + 64) + (size_t)DEC_ROWS * d * 4 + (size_t)DEC_ROWS * dec_ch * 4;
+// Bytes of dynamic shared memory one item needs (nb = staging buffers: 1, or 2 to copy the next
+// chunk of keys while the current one is being used).
+__host__ __device__ constexpr size_t dec_smem_bytes(int d, int dec_ch, int nb = 1) {
+  return (size_t)nb * 2 * dec_ch * (d * 2 + 64) + (size_t)DEC_ROWS * d * 4 + (size_t)DEC_ROWS * dec_ch * 4;
 }
 
 // Barrier of the 256 threads that work on an item: the whole CTA (BAR = 0) or a named barrier
@@ -90,15 +97,18 @@ __device__ __forceinline__ float2 ld_ll_pair(const uint2* p, uint32_t epoch, int
 }
 
 // LLIO: q / k_new / v_new come in and the merged row goes out as flagged rows (see DecArgs).
-template <int D, int DEC_CH, int ROWS, int BAR, bool PDL, bool LLIO = false>
+// NB = 2: two staging buffers; the copy of chunk i + 1 runs while chunk i is being used, so a long
+// key range streams at the memory system's pace instead of paying its latency once per chunk.
+template <int D, int DEC_CH, int ROWS, int BAR, bool PDL, bool LLIO = false, int NB = 1>
 __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int tid) {
   constexpr int ATT_THREADS = DEC_THREADS;
   constexpr int KSTR = D * 2 + 64;   // bytes per staged row: consecutive keys land 64 B apart mod 128
   constexpr int DV = D / 32;
   constexpr int NC = D / 8;          // 16-byte chunks per row
-  uint8_t* kbuf = dsm;                                   // [DEC_CH][KSTR]
+  uint8_t* kbuf = dsm;                                   // [DEC_CH][KSTR], buffer b at + b * BUFB
   uint8_t* vbuf = dsm + DEC_CH * KSTR;                   // [DEC_CH][KSTR]
-  float (*qs)[D] = reinterpret_cast<float (*)[D]>(dsm + 2 * DEC_CH * KSTR);          // [ROWS][D]
+  constexpr int BUFB = 2 * DEC_CH * KSTR;                // bytes of one staging buffer (keys + values)
+  float (*qs)[D] = reinterpret_cast<float (*)[D]>(dsm + NB * BUFB);                  // [ROWS][D]
   float (*sc)[DEC_CH] = reinterpret_cast<float (*)[DEC_CH]>(qs + ROWS);              // [ROWS][DEC_CH]
   float (*ored)[ROWS][D] = reinterpret_cast<float (*)[ROWS][D]>(dsm);                // aliases kbuf/vbuf
   __shared__ float alpha[ROWS], row_m[ROWS], row_l[ROWS];
@@ -119,17 +129,25 @@ __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int t
   __half* vb = a.vc + ((size_t)bi * a.hkv + kvh) * (size_t)a.cap * D;
 
   // stage chunk [c0, c0 + cn) of the cached rows (the new row `pos` is filled in separately)
-  auto stage = [&](int c0, int cn) {
+  auto stage = [&](int c0, int cn, int buf) {
     for (int i = tid; i < cn * NC * 2; i += ATT_THREADS) {
       const int which = i / (cn * NC), rem = i - which * (cn * NC);
       const int j = rem / NC, c = rem - j * NC;
       if (c0 + j == pos) continue;
       const __half* src = (which ? vb : kb) + (size_t)(c0 + j) * D + c * 8;
-      cp_async16((which ? vbuf : kbuf) + j * KSTR + c * 16, src);
+      cp_async16((which ? vbuf : kbuf) + buf * BUFB + j * KSTR + c * 16, src);
     }
   };
+  // the row of the new position, appended by this item a moment ago, goes into a staged chunk by hand
+  auto patch_new_row = [&](int c0, int buf) {
+    *reinterpret_cast<__half2*>(kbuf + buf * BUFB + (pos - c0) * KSTR + 4 * tid) =
+        *reinterpret_cast<const __half2*>(kb + (size_t)pos * D + 2 * tid);
+    *reinterpret_cast<__half2*>(vbuf + buf * BUFB + (pos - c0) * KSTR + 4 * tid) =
+        *reinterpret_cast<const __half2*>(vb + (size_t)pos * D + 2 * tid);
+  };
   const int cn0 = min(DEC_CH, kend - kbeg);
-  if (cn0 > 0) stage(kbeg, cn0);
+  if (cn0 > 0) stage(kbeg, cn0, 0);
+  if (NB > 1) cp_async_commit();
   if (tid < ROWS) { row_m[tid] = -INFINITY; row_l[tid] = 0.f; }
 
   if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");  // q, k_new, v_new come from the kernel before this one
@@ -194,20 +212,34 @@ __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int t
 #pragma unroll
     for (int e = 0; e < DV; ++e) o[r][e] = 0.f;
 
+  int buf = 0;
   for (int c0 = kbeg; c0 < kend; c0 += DEC_CH) {
     const int cn = min(DEC_CH, kend - c0);
-    if (c0 > kbeg) {
-      dec_sync<BAR>();  // the previous chunk has been consumed
-      stage(c0, cn);
-      if (has_new && pos >= c0 && pos < c0 + cn && tid < D / 2) {
-        *reinterpret_cast<__half2*>(kbuf + (pos - c0) * KSTR + 4 * tid) =
-            *reinterpret_cast<const __half2*>(kb + (size_t)pos * D + 2 * tid);
-        *reinterpret_cast<__half2*>(vbuf + (pos - c0) * KSTR + 4 * tid) =
-            *reinterpret_cast<const __half2*>(vb + (size_t)pos * D + 2 * tid);
+    if constexpr (NB > 1) {
+      // copy the next chunk into the other buffer (everyone has finished with it: it held chunk
+      // c0 - DEC_CH), then wait for this chunk only
+      const int cnext = c0 + DEC_CH;
+      if (c0 > kbeg) dec_sync<BAR>();
+      if (cnext < kend) {
+        const int cnn = min(DEC_CH, kend - cnext);
+        stage(cnext, cnn, buf ^ 1);
+        if (has_new && pos >= cnext && pos < cnext + cnn && tid < D / 2) patch_new_row(cnext, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait_group<1>();
+      } else {
+        cp_async_wait_group<0>();
       }
+    } else {
+      if (c0 > kbeg) {
+        dec_sync<BAR>();  // the previous chunk has been consumed
+        stage(c0, cn, 0);
+        if (has_new && pos >= c0 && pos < c0 + cn && tid < D / 2) patch_new_row(c0, 0);
+      }
+      cp_async_wait_all();
     }
-    cp_async_wait_all();
     dec_sync<BAR>();
+    const uint8_t* kcur = kbuf + buf * BUFB;
+    const uint8_t* vcur = vbuf + buf * BUFB;
     // ---- scores: 4 lanes per key (16-byte chunks sub, sub + 4, ...), 64 keys per CTA pass
     for (int j0 = 0; j0 < cn; j0 += 64) {
       const int j = j0 + warp * 8 + (lane >> 2);
@@ -219,7 +251,7 @@ __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int t
 #pragma unroll
         for (int v8 = 0; v8 < NC / 4; ++v8) {
           const int c = v8 * 4 + sub;
-          const uint4 raw = *reinterpret_cast<const uint4*>(kbuf + j * KSTR + c * 16);
+          const uint4 raw = *reinterpret_cast<const uint4*>(kcur + j * KSTR + c * 16);
           const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
           float kf[8];
 #pragma unroll
@@ -280,7 +312,7 @@ __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int t
     }
     for (int j = warp; j < cn; j += ATT_THREADS / 32) {
       float vf[DV];
-      const uint8_t* vp = vbuf + j * KSTR + lane * DV * 2;
+      const uint8_t* vp = vcur + j * KSTR + lane * DV * 2;
       if constexpr (DV == 4) {
         const uint2 raw = *reinterpret_cast<const uint2*>(vp);
         const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
@@ -297,6 +329,7 @@ __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int t
         for (int e = 0; e < DV; ++e) o[r][e] = fmaf(p, vf[e], o[r][e]);
       }
     }
+    if (NB > 1) buf ^= 1;
   }
   dec_sync<BAR>();  // staging area is free: reuse it for the cross-warp reduction
 #pragma unroll
@@ -305,6 +338,31 @@ __device__ void attn_decode_item(const DecArgs& a, int item, uint8_t* dsm, int t
     for (int e = 0; e < DV; ++e) ored[warp][r][lane * DV + e] = o[r][e];
   dec_sync<BAR>();
   const size_t rows_all = (size_t)a.b * a.h;
+  if (a.nsplit == 1) {
+    // a single split: nothing to merge, the normalised rows go straight out (the same arithmetic as
+    // the merge below with one partial of weight 1)
+    for (int i0 = 0; i0 < nrows * D; i0 += ATT_THREADS) {
+      const int i = i0 + tid;
+      const bool valid = i < nrows * D;
+      const int r = valid ? i / D : 0, e = i % D;
+      const size_t grow = (size_t)bi * a.h + kvh * a.groups + r;
+      float acc = 0.f;
+      if (valid) {
+#pragma unroll
+        for (int w = 0; w < ATT_THREADS / 32; ++w) acc += ored[w][r][e];
+        const float l = row_l[r];
+        acc *= l > 0.f ? 1.0f / l : 0.f;
+        if (a.out) a.out[grow * D + e] = acc;
+      }
+      if constexpr (LLIO) {
+        if (bi == 0 && valid) emit_ll16(a.out_ll, (int)(grow * D) + e, acc, acc, true, 0xFFFFFFFFu, a.ep_out);
+      } else {
+        if (a.out_packed.limbs && bi == 0 && valid)
+          emit_packed16(a.out_packed, (int)(grow * D) + e, acc, acc, true, 0xFFFFFFFFu);
+      }
+    }
+    return;
+  }
   for (int i = tid; i < nrows * D; i += ATT_THREADS) {
     const int r = i / D, e = i % D;
     float s = 0.f;

@@ -26,6 +26,9 @@ struct fb200_device {
   // normalised activations of rms_norm_q_mat_mul when the fused kernel does not apply
   void* normed = nullptr;
   size_t normed_bytes = 0;
+  // partial results of the greedy pick over wide rows
+  void* argmax_part = nullptr;
+  size_t argmax_part_bytes = 0;
   // staging for the *_host entry points
   void* stage = nullptr;
   size_t stage_bytes = 0;

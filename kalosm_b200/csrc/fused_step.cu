@@ -35,6 +35,7 @@
 // its end without waiting again.
 #include <algorithm>
 #include <cstdlib>
+#include <vector>
 
 #include "fused_step.cuh"
 #include "qgemv1_groups2.cuh"
@@ -214,6 +215,27 @@ __device__ __forceinline__ void prefetch_phase(const fb200_fused_phase& P, const
     cur_next(P, q, C.ic);
   }
   C.n = n;
+}
+
+// Asks L2 for `bytes` (a multiple of 16) at p: no shared memory, no barrier, nothing to wait for.
+__device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
+// This warp's share of product phase P from item `skip` on, at most `cap` items, into L2: one
+// request per run of consecutive tile-groups (the K groups of one tile are contiguous).
+__device__ __noinline__ void l2_prefetch_share(const fb200_fused_phase& P, int warp, int lane, int skip, int cap) {
+  const PhaseLocal q = phase_local(P);
+  const Range r = warp_range(q.total, q.chunk, warp);
+  int i = min(r.w0 + skip, r.w1);
+  const int end = min(r.w1, i + cap);
+  while (i < end) {
+    Cursor c;
+    cur_init(P, q, c, i);
+    const int run = min(end - i, q.ng - c.kg);
+    if (lane == 0) l2_prefetch(c.src, (uint32_t)(run * c.tgb));
+    i += run;
+  }
 }
 
 struct EpiCtx {
@@ -427,7 +449,7 @@ struct Smem {
 // product loop measured 25 % slower.)
 template <bool LEGACY, bool XS, bool LL>
 __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused_phase& P, const fb200_fused_phase* Pnext,
-                           const Smem& S, WarpRing& R, Carry& C, unsigned long long* tr, unsigned epoch, unsigned lep) {
+                           const fb200_fused_phase* Pf0, const fb200_fused_phase* Pf1, const Smem& S, WarpRing& R, Carry& C, unsigned long long* tr, unsigned epoch, unsigned lep) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int K = P.K, Kp = P.Kp;
   const PhaseLocal q = phase_local(P);
@@ -594,6 +616,10 @@ __device__ __forceinline__ void gemv_phase(const FusedArgs& A, const fb200_fused
   // ---- the ring is free: fetch the first slots of the next product phase
   C.n = 0;
   if (Pnext) prefetch_phase(*Pnext, R, warp, lane, C);
+  // ... and ask L2 for the rest of it and for the phases the plan names: HBM keeps streaming while
+  // the CTAs merge, meet, run attention and reload activations
+  if (Pf0) l2_prefetch_share(*Pf0, warp, lane, P.pf_skip[0], P.pf_cap[0]);
+  if (Pf1) l2_prefetch_share(*Pf1, warp, lane, P.pf_skip[1], P.pf_cap[1]);
   __syncthreads();
   if (tr) tr[2] = global_ns();
 
@@ -857,7 +883,11 @@ fused_step_kernel(const FusedArgs A) {
           S.xss = S.xsc + P.Kp / 16;
           const int ahead = P.next_gemv < 0 ? -1 : (P.next_gemv > ph ? P.next_gemv - ph : P.next_gemv + A.nphases - ph);
           const bool has_next = ahead > 0 && ahead <= 3 && g + ahead < total_phases;
-          gemv_phase<LEGACY, XS, LL>(A, P, has_next ? desc_of(g + ahead) : nullptr, S, R, C, tr, epoch, lep);
+          auto planned = [&](int j) -> const fb200_fused_phase* {
+            const int off = P.pf_off[j];
+            return off > 0 && off < DESC_SLOTS - 1 && g + off < total_phases ? desc_of(g + off) : nullptr;
+          };
+          gemv_phase<LEGACY, XS, LL>(A, P, has_next ? desc_of(g + ahead) : nullptr, planned(0), planned(1), S, R, C, tr, epoch, lep);
           break;
         }
         case FB200_PH_ATTN:
@@ -950,6 +980,55 @@ bool fb200_fused_gemv_phase(fb200_fused_phase* p, const fb200_qmatrix* const* ws
   p->stages = flagged ? std::min(MAX_STAGES_LL, RING_BYTES_LL / p->stride) : std::min(MAX_STAGES, RING_BYTES / p->stride);
   if (const char* e = getenv("FB200_FUSED_STAGES")) p->stages = std::max(1, std::min(p->stages, atoi(e)));
   return p->stages >= 1;
+}
+
+void fb200_fused_plan_prefetch(fb200_fused_phase* prog, int nphases, int grid, size_t ahead_bytes) {
+  std::vector<int> gv;
+  for (int i = 0; i < nphases; ++i) {
+    if (prog[i].kind != FB200_PH_GEMV) continue;
+    gv.push_back(i);
+    for (int j = 0; j < 2; ++j) prog[i].pf_off[j] = prog[i].pf_skip[j] = prog[i].pf_cap[j] = 0;
+  }
+  const int n = (int)gv.size();
+  if (n < 2 || ahead_bytes == 0) return;
+  const int warps = grid * FW;
+  // weight bytes of a phase and the items per warp that fit the bound (a phase larger than the bound,
+  // the output head, is requested in part)
+  auto phase_bytes = [&](const fb200_fused_phase& p) {
+    size_t b = 0;
+    const int npass = p.epi == FB200_EPI_SWIGLU ? 2 : 1;
+    for (int s = 0; s < p.nseg; ++s) b += (size_t)p.seg[s].units * npass * p.ngroups * p.seg[s].tg;
+    return b;
+  };
+  // Walk the cyclic chain of product phases twice (the second lap is the steady state that is kept).
+  // front = product phases after the current one whose shares have been requested already.
+  int front = 0;
+  for (int lap = 0; lap < 2; ++lap) {
+    for (int s = 0; s < n; ++s) {
+      fb200_fused_phase& p = prog[gv[s]];
+      int slots = 0;
+      for (int j = 0; j < 2; ++j) p.pf_off[j] = p.pf_skip[j] = p.pf_cap[j] = 0;
+      for (int d = 1; d <= 2 && slots < 2; ++d) {
+        const int t = gv[(s + d) % n];
+        int off = t - gv[s];
+        if (off <= 0) off += nphases;
+        if (off >= DESC_SLOTS - 1) break;  // outside the descriptor window of the kernel
+        size_t pending = 0;  // bytes requested and not yet consumed once phase d ahead is added
+        for (int e = 1; e <= d; ++e) pending += std::min(phase_bytes(prog[gv[(s + e) % n]]), ahead_bytes);
+        if (pending > ahead_bytes && d > 1) break;
+        if (d <= front) continue;  // requested when an earlier phase ended
+        const fb200_fused_phase& q = prog[t];
+        p.pf_off[slots] = off;
+        p.pf_skip[slots] = d == 1 ? q.stages : 0;  // the ring takes the first items of the next product phase
+        p.pf_cap[slots] = 1 << 20;
+        if (phase_bytes(q) > ahead_bytes)  // only d == 1 gets here: the first ahead_bytes of the phase
+          p.pf_cap[slots] = (int)std::max<size_t>(1, ahead_bytes / ((size_t)warps * (size_t)q.stride));
+        ++slots;
+        front = d;
+      }
+      front = std::max(front - 1, 0);
+    }
+  }
 }
 
 size_t fb200_fused_smem_bytes(const fb200_fused_phase* prog_host, int nphases, bool flagged) {

@@ -126,12 +126,21 @@ struct alignas(16) fb200_fused_phase {  // 16-byte multiples: descriptors are co
   // greedy key is exchanged and the largest wins.
   int xs_index;
   float* out_sum;
+  // ---- L2 plan of a product phase (fb200_fused_plan_prefetch): a warp that has consumed its share of
+  // this phase asks L2 for its share of the product phases pf_off[j] phases further on (0: none),
+  // from item pf_skip[j] of that share (the items before go to the ring) and at most pf_cap[j] items.
+  int pf_off[2], pf_skip[2], pf_cap[2];
 };
 
 // Fills the derived fields of a product phase (units, items, chunk, ring geometry) from its
 // matrices; `grid` = CTAs of the launch. Returns false if the matrices cannot share a phase.
 bool fb200_fused_gemv_phase(fb200_fused_phase* p, const fb200_qmatrix* const* ws, float* const* ys, int nw,
                             int epi, int grid, bool flagged);
+// Fills the L2 plan of every product phase of a complete program (next_gemv already chained):
+// which later phases' weights a warp requests into L2 when its share of a phase ends, so that HBM
+// keeps streaming through barriers, attention phases and activation reloads. `ahead_bytes` bounds
+// the weight bytes requested but not yet consumed (they must fit in L2 beside everything else).
+void fb200_fused_plan_prefetch(fb200_fused_phase* prog, int nphases, int grid, size_t ahead_bytes);
 // Shared memory the program needs; 0 if it does not fit.
 size_t fb200_fused_smem_bytes(const fb200_fused_phase* prog_host, int nphases, bool flagged = false);
 // Number of CTAs of a launch on this device.

@@ -28,6 +28,15 @@ int fb200_launch_attention(fb200_device* dev, const float* q, const __half* k, c
                            int b, int h, int hkv, int sq, int skv, const int* skv_dev, int cap,
                            int d, float scale, const float* mask, int mask_kind, float* out,
                            float* part, int nsplit, int bshd);
+size_t fb200_xpack_bytes(int mp, uint64_t kp);
+int fb200_pack16_rows(int mc);
+uint64_t fb200_qmatrix_kp(const fb200_qmatrix* w);
+int fb200_pack_x16(fb200_device* dev, const float* x, int mc, uint64_t k, uint64_t kp, void* scratch, const void** xh,
+                   const float** xscale);
+int fb200_norm_pack_x16(fb200_device* dev, const float* x, size_t x_stride, const float* res, const float* w, float eps,
+                        int mc, uint64_t k, uint64_t kp, void* scratch, const void** xh, const float** xscale);
+int fb200_qgemm16_packed(fb200_device* dev, const fb200_qmatrix* w, const void* xh, const float* xscale16, int mc, int mp,
+                         float* y, int epi, const float* r1, const float* r2, bool r1_is_bias);
 int fb200_attention_nsplit(const fb200_device* dev, int b, int hkv, int groups, int sq, int skv);
 int fb200_launch_attention_decode_args(fb200_device* dev, const fb200_dec_args& a, int d);
 bool fb200_qgemv1_fits(const fb200_qmatrix* w);
@@ -424,6 +433,12 @@ int build_fused_program(fb200_llama* m) {
     prev = i;
   }
   if (prev >= 0) prog[prev].next_gemv = first;
+  {
+    // weights requested into L2 ahead of their phase; FB200_FUSED_L2_AHEAD_MB = 0 turns the plan off
+    size_t ahead_mb = 0;
+    if (const char* e = getenv("FB200_FUSED_L2_AHEAD_MB")) ahead_mb = (size_t)std::max(0, atoi(e));
+    fb200_fused_plan_prefetch(prog.data(), (int)prog.size(), fb200_fused_grid(dev), ahead_mb << 20);
+  }
   // the barrier-free variants: one GPU, K-quant weights
   m->fused_is_flagged = flagged && fb200_fused_flagged_available(prog.data(), (int)prog.size());
   if (flagged && !m->fused_is_flagged) return FB200_OK;  // laid out for a variant that does not exist
@@ -509,6 +524,24 @@ int run_forward(fb200_llama* m, int batch, int seq) {
   fb200_attention_scratch_bytes(batch, H, seq, D, nsplit, &part_bytes);
   if (part_bytes > m->att_part_bytes)
     return fb200_fail(dev, FB200_ERR_CAPACITY, "llama: attention scratch too small");
+  // 2..32 sequences, one new position each: activations are packed once per distinct input row
+  // set (the fused norm writes the packed form directly) and the products take the packed rows
+  bool packed = seq == 1 && rows >= 2 && rows <= 32;
+  uint64_t kp_e = 0, kp_o = 0, kp_d = 0;
+  for (int li = 0; li < c.n_layer && packed; ++li) {
+    const LayerW& L = m->layers[li];
+    packed = L.gate_up && L.wq->tiled && L.wk->tiled && L.wv->tiled && L.wo->tiled && L.gate_up->tiled && L.down->tiled;
+    if (!packed) break;
+    const uint64_t e = fb200_qmatrix_kp(L.wq), o = fb200_qmatrix_kp(L.wo), d = fb200_qmatrix_kp(L.down);
+    packed = fb200_qmatrix_kp(L.wk) == e && fb200_qmatrix_kp(L.wv) == e && fb200_qmatrix_kp(L.gate_up) == e &&
+             (li == 0 || (e == kp_e && o == kp_o && d == kp_d)) && e <= 8192;
+    kp_e = e; kp_o = o; kp_d = d;
+  }
+  const int mp = fb200_pack16_rows((int)rows);
+  const void* xh = nullptr;
+  const float* xs = nullptr;
+  if (packed && (rc = fb200_ensure(dev, &dev->xpack, &dev->xpack_bytes, fb200_xpack_bytes(32, std::max(std::max(kp_e, kp_o), kp_d)))))
+    return rc;
   for (int li = 0; li < c.n_layer; ++li) {
     LayerW& L = m->layers[li];
     if (rows == 1) {
@@ -516,6 +549,12 @@ int run_forward(fb200_llama* m, int batch, int seq) {
       if ((rc = fb200_rms_norm_q_mat_mul(dev, m->x, nullptr, L.attn_norm, c.rms_eps, 1, L.wq, m->q, nullptr))) return rc;
       if ((rc = fb200_rms_norm_q_mat_mul(dev, m->x, nullptr, L.attn_norm, c.rms_eps, 1, L.wk, m->k, nullptr))) return rc;
       if ((rc = fb200_rms_norm_q_mat_mul(dev, m->x, nullptr, L.attn_norm, c.rms_eps, 1, L.wv, m->v, nullptr))) return rc;
+    } else if (packed) {
+      // 2..32 sequences: the norm writes the packed fp16 fragments the three projections share
+      if ((rc = fb200_norm_pack_x16(dev, m->x, E, nullptr, L.attn_norm, c.rms_eps, (int)rows, E, kp_e, dev->xpack, &xh, &xs))) return rc;
+      if ((rc = fb200_qgemm16_packed(dev, L.wq, xh, xs, (int)rows, mp, m->q, FB200_EPI_NONE, nullptr, nullptr, false))) return rc;
+      if ((rc = fb200_qgemm16_packed(dev, L.wk, xh, xs, (int)rows, mp, m->k, FB200_EPI_NONE, nullptr, nullptr, false))) return rc;
+      if ((rc = fb200_qgemm16_packed(dev, L.wv, xh, xs, (int)rows, mp, m->v, FB200_EPI_NONE, nullptr, nullptr, false))) return rc;
     } else {
       if ((rc = fb200_launch_rms_norm_strided(dev, m->x, E, nullptr, L.attn_norm, c.rms_eps, rows, E, m->xn))) return rc;
       if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wq, m->q, nullptr))) return rc;
@@ -532,6 +571,9 @@ int run_forward(fb200_llama* m, int batch, int seq) {
       int ns = (2 * dev->sm_count + batch * HK - 1) / (batch * HK);
       ns = std::max(1, std::min(std::min(ns, 32), (c.max_seq_len + 63) / 64));
       da.nsplit = ns;
+      // many sequences: the (batch, kv head) pairs alone fill the GPU, so a context is cut only
+      // when it is long
+      da.min_keys = batch * HK >= dev->sm_count / 2 ? 256 : 64;
       if ((size_t)ns * batch * H * (D + 2) * sizeof(float) > m->att_part_bytes)
         return fb200_fail(dev, FB200_ERR_CAPACITY, "llama: attention scratch too small");
       if ((rc = fb200_launch_attention_decode_args(dev, da, D))) return rc;
@@ -546,13 +588,21 @@ int run_forward(fb200_llama* m, int batch, int seq) {
                                        c.max_seq_len, D, scale, nullptr, seq > 1 ? 1 : 0, m->att,
                                        m->att_part, nsplit, 1))) return rc;
     }
-    if ((rc = fb200_q_mat_mul(dev, m->att, rows, L.wo, m->attn_out, nullptr))) return rc;
+    if (packed) {
+      if ((rc = fb200_pack_x16(dev, m->att, (int)rows, L.wo->k, kp_o, dev->xpack, &xh, &xs))) return rc;
+      if ((rc = fb200_qgemm16_packed(dev, L.wo, xh, xs, (int)rows, mp, m->attn_out, FB200_EPI_NONE, nullptr, nullptr, false))) return rc;
+    } else if ((rc = fb200_q_mat_mul(dev, m->att, rows, L.wo, m->attn_out, nullptr))) {
+      return rc;
+    }
     // tensor parallel: this rank's heads gave a partial sum over K of the output projection
     if (m->tp_size > 1 && (rc = fb200_comm_all_reduce(m->comm, m->attn_out, rows * (size_t)E))) return rc;
     // ffn_norm.forward_residual_f32(attn, residual) (raw/mod.rs:1017)
     if (rows == 1 && L.gate_up) {
       fb200_epilogue ep{FB200_EPI_SWIGLU, nullptr, nullptr};
       if ((rc = fb200_rms_norm_q_mat_mul(dev, m->attn_out, m->x, L.ffn_norm, c.rms_eps, 1, L.gate_up, m->hbuf, &ep))) return rc;
+    } else if (packed) {
+      if ((rc = fb200_norm_pack_x16(dev, m->attn_out, E, m->x, L.ffn_norm, c.rms_eps, (int)rows, E, kp_e, dev->xpack, &xh, &xs))) return rc;
+      if ((rc = fb200_qgemm16_packed(dev, L.gate_up, xh, xs, (int)rows, mp, m->hbuf, FB200_EPI_SWIGLU, nullptr, nullptr, false))) return rc;
     } else if (L.gate_up) {
       if ((rc = fb200_launch_rms_norm_strided(dev, m->attn_out, E, m->x, L.ffn_norm, c.rms_eps, rows, E, m->xn))) return rc;
       fb200_epilogue ep{FB200_EPI_SWIGLU, nullptr, nullptr};
@@ -565,9 +615,14 @@ int run_forward(fb200_llama* m, int batch, int seq) {
     }
     // (down(h) + attn) + residual, written over the residual stream
     // (attention_layer.rs:170-172 for one position, raw/mod.rs:1036 otherwise)
-    if (m->tp_size > 1) {
+    if (packed && (rc = fb200_pack_x16(dev, m->hbuf, (int)rows, L.down->k, kp_d, dev->xpack, &xh, &xs))) return rc;
+    if (packed && m->tp_size == 1) {
+      if ((rc = fb200_qgemm16_packed(dev, L.down, xh, xs, (int)rows, mp, m->x, FB200_EPI_RESIDUAL, m->attn_out, m->x, false))) return rc;
+    } else if (m->tp_size > 1) {
       // partial sum over this rank's slice of the FFN width, summed over the ranks, then the residuals
-      if ((rc = fb200_q_mat_mul(dev, m->hbuf, rows, L.down, m->xn, nullptr))) return rc;
+      if (packed) rc = fb200_qgemm16_packed(dev, L.down, xh, xs, (int)rows, mp, m->xn, FB200_EPI_NONE, nullptr, nullptr, false);
+      else rc = fb200_q_mat_mul(dev, m->hbuf, rows, L.down, m->xn, nullptr);
+      if (rc) return rc;
       if ((rc = fb200_comm_all_reduce(m->comm, m->xn, rows * (size_t)E))) return rc;
       const size_t total = rows * (size_t)E;
       add_residuals_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(m->xn, m->attn_out, m->x, total);

@@ -190,10 +190,71 @@ int fb200_launch_rope(fb200_device* dev, float* x, int b, int heads, int s, int 
   return FB200_OK;
 }
 
+// Two steps for wide rows: ARGMAX_PARTS CTAs per row leave their best (value, index) as an ordered
+// 64-bit key (value in the high half, mapped so that unsigned order = float order; index in the
+// low half, so that equal values resolve to the higher index), then one thread per row takes the
+// largest key. One CTA per row would read a 128 256-wide row at a fraction of the bandwidth.
+constexpr int ARGMAX_PARTS = 16;
+
+__global__ void __launch_bounds__(512)
+argmax_parts_kernel(const float* __restrict__ logits, size_t n, unsigned long long* __restrict__ part) {
+  __shared__ unsigned long long sk[16];
+  const float* row = logits + (size_t)blockIdx.y * n;
+  const size_t per = (n + ARGMAX_PARTS - 1) / ARGMAX_PARTS;
+  const size_t i0 = (size_t)blockIdx.x * per, i1 = i0 + per < n ? i0 + per : n;
+  unsigned long long best = 0ull;  // 0: no finite value seen
+  for (size_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+    const float v = row[i];
+    if (!isfinite(v)) continue;
+    const uint32_t u = __float_as_uint(v);
+    const uint32_t ordered = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    const unsigned long long key = ((unsigned long long)ordered << 32) | (uint32_t)i;
+    if (key > best) best = key;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+    if (other > best) best = other;
+  }
+  if ((threadIdx.x & 31) == 0) sk[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i)
+      if (sk[i] > best) best = sk[i];
+    part[(size_t)blockIdx.y * ARGMAX_PARTS + blockIdx.x] = best;
+  }
+}
+
+__global__ void argmax_pick_kernel(const unsigned long long* __restrict__ part, int rows, uint32_t* __restrict__ ids,
+                                   float* __restrict__ vals) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  unsigned long long best = 0ull;
+  for (int i = 0; i < ARGMAX_PARTS; ++i) {
+    const unsigned long long k = part[(size_t)r * ARGMAX_PARTS + i];
+    if (k > best) best = k;
+  }
+  ids[r] = best ? (uint32_t)(best & 0xFFFFFFFFull) : 0xFFFFFFFFu;
+  if (vals) {
+    const uint32_t o = (uint32_t)(best >> 32);
+    vals[r] = best ? __uint_as_float((o & 0x80000000u) ? (o & 0x7FFFFFFFu) : ~o) : -INFINITY;
+  }
+}
+
 int fb200_launch_argmax(fb200_device* dev, const float* logits, size_t rows, size_t n,
                         uint32_t* ids, float* vals) {
   if (rows == 0) return FB200_OK;
-  argmax_kernel<<<(unsigned)rows, 1024, 0, dev->stream>>>(logits, n, ids, vals);
+  if (n < 16384 || rows > 65535) {
+    argmax_kernel<<<(unsigned)rows, 1024, 0, dev->stream>>>(logits, n, ids, vals);
+    FB_LAUNCH_CHECK(dev);
+    return FB200_OK;
+  }
+  int rc = fb200_ensure(dev, &dev->argmax_part, &dev->argmax_part_bytes, rows * ARGMAX_PARTS * sizeof(unsigned long long));
+  if (rc) return rc;
+  unsigned long long* part = reinterpret_cast<unsigned long long*>(dev->argmax_part);
+  argmax_parts_kernel<<<dim3(ARGMAX_PARTS, (unsigned)rows), 512, 0, dev->stream>>>(logits, n, part);
+  FB_LAUNCH_CHECK(dev);
+  argmax_pick_kernel<<<(unsigned)((rows + 127) / 128), 128, 0, dev->stream>>>(part, (int)rows, ids, vals);
   FB_LAUNCH_CHECK(dev);
   return FB200_OK;
 }

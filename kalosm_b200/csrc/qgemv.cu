@@ -526,6 +526,53 @@ __device__ __forceinline__ void deq4(uint32_t w, __half2 centre, __half2 scale, 
   h23 = h2_bits(__hfma2(v23, scale, offset));
 }
 
+// ---- block scales in half precision ------------------------------------------------------------
+// The fp16 kernels multiply every weight by its block scale in half precision. The scales are small
+// integers times an fp16 block factor, so they are built with half arithmetic alone (integer n as
+// the half 1024 + n minus 1024, then one rounded product: the same bits as the fp32 product
+// rounded to half) instead of int -> float -> half conversions, which share one slow pipe.
+
+// Q4_K header of rows g (h = 0) and g + 8 (h = 1): sm[h][j] = half2 {d * scale, -dmin * min} of
+// sub-block t + 4 j (get_scale_min_k4 of the GGUF block).
+__device__ __forceinline__ void q4k_scales_h2(const uint8_t* tg, int g, int t, uint32_t (&sm)[2][2]) {
+  const __half2 c1024 = __float2half2_rn(1024.0f);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint4 hd = lds16(tg + 2048 + (g + 8 * h) * 16);
+    const __half2 dd = bits_h2(hd.x ^ 0x80000000u);  // {d, -dmin}
+    const uint32_t s0 = hd.y, s1 = hd.z, s2 = hd.w;
+    const uint32_t scB = (s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u);
+    const uint32_t mnB = ((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u);
+    const int sh = 8 * t;
+    const uint32_t p0 = ((s0 >> sh) & 0x3Fu) | (((s1 >> sh) & 0x3Fu) << 16);
+    const uint32_t p1 = ((scB >> sh) & 0xFFu) | (((mnB >> sh) & 0xFFu) << 16);
+    sm[h][0] = h2_bits(__hmul2(__hsub2(bits_h2(p0 | 0x64006400u), c1024), dd));
+    sm[h][1] = h2_bits(__hmul2(__hsub2(bits_h2(p1 | 0x64006400u), c1024), dd));
+  }
+}
+// Scales and (negated) offsets of sub-block sb for this lane's rows, from the lane of the quad that
+// decoded them.
+__device__ __forceinline__ void q4k_chunk_scales(const uint32_t (&sm)[2][2], int lane, int sb, __half2& s_g, __half2& s_g8,
+                                                 __half2& o_g, __half2& o_g8) {
+  const int src = (lane & ~3) | (sb & 3);
+  const uint32_t v0 = __shfl_sync(0xFFFFFFFFu, sm[0][sb >> 2], src);
+  const uint32_t v1 = __shfl_sync(0xFFFFFFFFu, sm[1][sb >> 2], src);
+  s_g = bits_h2(__byte_perm(v0, v0, 0x1010));
+  o_g = bits_h2(__byte_perm(v0, v0, 0x3232));
+  s_g8 = bits_h2(__byte_perm(v1, v1, 0x1010));
+  o_g8 = bits_h2(__byte_perm(v1, v1, 0x3232));
+}
+// Q6_K: the int8 scales of the two 16-element groups of chunk (c2, q) of one row, times d, each
+// duplicated into a half2. xw = the row's 16 scale bytes with the sign bit flipped (v + 128).
+__device__ __forceinline__ void q6k_chunk_scales(const uint32_t (&xw)[4], __half2 d2, int c2, int q, __half2& s_u0,
+                                                 __half2& s_u1) {
+  const uint32_t w = xw[2 * c2 + (q >> 1)];
+  const uint32_t pair = (q & 1) ? __byte_perm(w, 0x64646464u, 0x4342) : __byte_perm(w, 0x64646464u, 0x4140);
+  const uint32_t sv = h2_bits(__hmul2(__hsub2(bits_h2(pair), __float2half2_rn(1152.0f)), d2));
+  s_u0 = bits_h2(__byte_perm(sv, sv, 0x1010));
+  s_u1 = bits_h2(__byte_perm(sv, sv, 0x3232));
+}
+
 template <int NT>
 struct Chunk16 { uint4 b[NT]; };
 
@@ -589,21 +636,8 @@ __device__ __forceinline__ void group16(const GemvArgs& a, const uint8_t* tg, in
   } else if constexpr (TYPE == FB200_Q4_K) {
     // lane t of each quad decodes the 6-bit (scale, offset) of sub-blocks t and t + 4 for its two
     // rows; the quad shares them by shuffle
-    float sc_f[2][2], mn_f[2][2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const uint4 hd = lds16(tg + 2048 + (g + 8 * h) * 16);
-      const float d = fb::half_bits_to_float((uint16_t)(hd.x & 0xFFFF));
-      const float dmin = fb::half_bits_to_float((uint16_t)(hd.x >> 16));
-      const uint32_t s0 = hd.y, s1 = hd.z, s2 = hd.w;
-      const uint32_t scB = (s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u);
-      const uint32_t mnB = ((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u);
-      const int sh = 8 * t;
-      sc_f[h][0] = d * (float)((s0 >> sh) & 0x3F);
-      mn_f[h][0] = dmin * (float)((s1 >> sh) & 0x3F);
-      sc_f[h][1] = d * (float)((scB >> sh) & 0xFF);
-      mn_f[h][1] = dmin * (float)((mnB >> sh) & 0xFF);
-    }
+    uint32_t sm[2][2];
+    q4k_scales_h2(tg, g, t, sm);
 #pragma unroll
     for (int pair = 0; pair < 4; ++pair) {
       const int ch = pair >> 1, ps = pair & 1;
@@ -619,13 +653,8 @@ __device__ __forceinline__ void group16(const GemvArgs& a, const uint8_t* tg, in
         Chunk16<NT> nxt = cur;
         const int kn = sb < 7 ? kc + 1 : next_first;
         if (kn >= 0) load_chunk16<NT>(a, kn, g, t, nxt);
-        const int src = (lane & ~3) | (sb & 3);
-        const float s_g = __shfl_sync(0xFFFFFFFFu, sc_f[0][sb >> 2], src);
-        const float s_g8 = __shfl_sync(0xFFFFFFFFu, sc_f[1][sb >> 2], src);
-        const float o_g = __shfl_sync(0xFFFFFFFFu, mn_f[0][sb >> 2], src);
-        const float o_g8 = __shfl_sync(0xFFFFFFFFu, mn_f[1][sb >> 2], src);
-        const __half2 hs_g = __float2half2_rn(s_g), hs_g8 = __float2half2_rn(s_g8);
-        const __half2 ho_g = __float2half2_rn(-o_g), ho_g8 = __float2half2_rn(-o_g8);
+        __half2 hs_g, hs_g8, ho_g, ho_g8;
+        q4k_chunk_scales(sm, lane, sb, hs_g, hs_g8, ho_g, ho_g8);
         const uint32_t sh4 = hi ? 4u : 0u;
         chunk16<NT>(acc, cur, (w00 >> sh4) & 0x0F0F0F0Fu, (w10 >> sh4) & 0x0F0F0F0Fu, (w01 >> sh4) & 0x0F0F0F0Fu,
                     (w11 >> sh4) & 0x0F0F0F0Fu, __float2half2_rn(1024.0f), hs_g, hs_g8, hs_g, hs_g8, ho_g, ho_g8);
@@ -635,10 +664,10 @@ __device__ __forceinline__ void group16(const GemvArgs& a, const uint8_t* tg, in
   } else {  // Q6_K: the two 16-element halves of a chunk are two scale groups
     const uint4 sc_g = lds16(tg + 3072 + g * 16);
     const uint4 sc_g8 = lds16(tg + 3072 + (g + 8) * 16);
-    const float d_g = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 3328 + g * 2));
-    const float d_g8 = fb::half_bits_to_float(*reinterpret_cast<const uint16_t*>(tg + 3328 + (g + 8) * 2));
-    const uint32_t scw_g[4] = {sc_g.x, sc_g.y, sc_g.z, sc_g.w};
-    const uint32_t scw_g8[4] = {sc_g8.x, sc_g8.y, sc_g8.z, sc_g8.w};
+    const __half2 d_g = __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(tg + 3328 + g * 2)));
+    const __half2 d_g8 = __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(tg + 3328 + (g + 8) * 2)));
+    const uint32_t scw_g[4] = {sc_g.x ^ 0x80808080u, sc_g.y ^ 0x80808080u, sc_g.z ^ 0x80808080u, sc_g.w ^ 0x80808080u};
+    const uint32_t scw_g8[4] = {sc_g8.x ^ 0x80808080u, sc_g8.y ^ 0x80808080u, sc_g8.z ^ 0x80808080u, sc_g8.w ^ 0x80808080u};
 #pragma unroll
     for (int c2 = 0; c2 < 2; ++c2)
 #pragma unroll
@@ -651,7 +680,7 @@ __device__ __forceinline__ void group16(const GemvArgs& a, const uint8_t* tg, in
         __half2 hs[2][2];
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-          const int cu = c2 * 2 + u, grp = 8 * c2 + 2 * q + u;
+          const int cu = c2 * 2 + u;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const uint32_t wl = lds4(tg + (cu * 2 + h) * 256 + g * 32 + (q & 1) * 16 + 4 * t);
@@ -659,9 +688,9 @@ __device__ __forceinline__ void group16(const GemvArgs& a, const uint8_t* tg, in
             const uint32_t hb = q == 0 ? (wh << 4) : q == 1 ? (wh << 2) : q == 2 ? wh : (wh >> 2);
             af[u][h] = (((q >> 1) ? (wl >> 4) : wl) & 0x0F0F0F0Fu) | (hb & 0x30303030u);
           }
-          hs[u][0] = __float2half2_rn(d_g * (float)(int)(int8_t)((scw_g[grp >> 2] >> (8 * (grp & 3))) & 0xFF));
-          hs[u][1] = __float2half2_rn(d_g8 * (float)(int)(int8_t)((scw_g8[grp >> 2] >> (8 * (grp & 3))) & 0xFF));
         }
+        q6k_chunk_scales(scw_g, d_g, c2, q, hs[0][0], hs[1][0]);
+        q6k_chunk_scales(scw_g8, d_g8, c2, q, hs[0][1], hs[1][1]);
         chunk16<NT>(acc, cur, af[0][0], af[0][1], af[1][0], af[1][1], __float2half2_rn(1056.0f), hs[0][0], hs[0][1],
                     hs[1][0], hs[1][1], zero2, zero2);  // (q - 32) d scale
         cur = nxt;
@@ -777,6 +806,216 @@ qgemm16_kernel(const GemvArgs a) {
   }
 }
 
+// ---- K-stationary form of the fp16 kernel ------------------------------------------------------
+// With 2..32 activation rows a tile-group of W (1.1 - 3.4 KB) meets 4 - 16 KB of activations.
+// Here every warp of a CTA owns ONE K group and keeps the MMA B fragments of all activation
+// rows for that group in registers; the CTA walks an equal contiguous share of the 16-row tiles of
+// W, warp w multiplying tile-group (tile, w), and the warps' partial tiles meet in shared memory
+// once per tile (summed in warp order). Activations are read from L2 once per CTA instead of once
+// per tile-group. Serves matrices of at most W K groups (K <= 4096 for the 256-element block types
+// with 16 warps); longer rows take the streamed kernel above.
+template <int TYPE, int W>
+struct RingS {
+  static constexpr int TG = Ring<TYPE>::TG;
+  static constexpr int STRIDE = Ring<TYPE>::STRIDE;
+  static constexpr int FIT = (168 * 1024) / (W * STRIDE);
+  static constexpr int STAGES = FIT > 6 ? 6 : FIT;
+  static constexpr int RING_BYTES = W * STAGES * STRIDE;
+  static constexpr int BAR_BYTES = W * STAGES * 8;
+};
+
+template <int TYPE, int NT, int W>
+constexpr int gemm16s_smem_bytes() {
+  return RingS<TYPE, W>::RING_BYTES + RingS<TYPE, W>::BAR_BYTES + 2 * W * NT * 8 * 16 * (int)sizeof(float);
+}
+
+// group16 with the activations of the K group already in registers (x[chunk]).
+template <int TYPE, int NT, int CHUNKS>
+__device__ __forceinline__ void group16r(const uint8_t* tg, int lane, float (&acc)[NT][4],
+                                         const Chunk16<NT> (&x)[CHUNKS]) {
+  const int g = lane >> 2, t = lane & 3;
+  const __half2 zero2 = __float2half2_rn(0.f);
+  if constexpr (TYPE == FB200_Q4_0 || TYPE == FB200_Q8_0) {
+#pragma unroll
+    for (int blk = 0; blk < 4; ++blk) {
+      const int dofs = TYPE == FB200_Q4_0 ? 1024 : 2048;
+      const __half2 d_g = __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(tg + dofs + (g * 4 + blk) * 2)));
+      const __half2 d_g8 = __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(tg + dofs + ((g + 8) * 4 + blk) * 2)));
+      if constexpr (TYPE == FB200_Q4_0) {
+        const uint32_t w0 = lds4(tg + g * 64 + blk * 16 + 4 * t);
+        const uint32_t w1 = lds4(tg + 512 + g * 64 + blk * 16 + 4 * t);
+        chunk16<NT>(acc, x[blk], w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, (w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu,
+                    __float2half2_rn(1032.0f), d_g, d_g8, d_g, d_g8, zero2, zero2);  // (q - 8) d
+      } else {
+        const int off = g * 64 + blk * 16 + 4 * t;
+        const uint32_t a0 = lds4(tg + off) ^ 0x80808080u, a2 = lds4(tg + 512 + off) ^ 0x80808080u;
+        const uint32_t a1 = lds4(tg + 1024 + off) ^ 0x80808080u, a3 = lds4(tg + 1536 + off) ^ 0x80808080u;
+        chunk16<NT>(acc, x[blk], a0, a1, a2, a3, __float2half2_rn(1152.0f), d_g, d_g8, d_g, d_g8, zero2, zero2);  // q d
+      }
+    }
+  } else if constexpr (TYPE == FB200_Q4_K) {
+    uint32_t sm[2][2];
+    q4k_scales_h2(tg, g, t, sm);
+#pragma unroll
+    for (int pair = 0; pair < 4; ++pair) {
+      const int ch = pair >> 1, ps = pair & 1;
+      const int off = g * 32 + ps * 16 + 4 * t;
+      const uint32_t w00 = lds4(tg + ((ch * 2 + 0) * 2 + 0) * 256 + off);
+      const uint32_t w01 = lds4(tg + ((ch * 2 + 0) * 2 + 1) * 256 + off);
+      const uint32_t w10 = lds4(tg + ((ch * 2 + 1) * 2 + 0) * 256 + off);
+      const uint32_t w11 = lds4(tg + ((ch * 2 + 1) * 2 + 1) * 256 + off);
+#pragma unroll
+      for (int hi = 0; hi < 2; ++hi) {
+        const int sb = 2 * pair + hi;
+        __half2 hs_g, hs_g8, ho_g, ho_g8;
+        q4k_chunk_scales(sm, lane, sb, hs_g, hs_g8, ho_g, ho_g8);
+        const uint32_t sh4 = hi ? 4u : 0u;
+        chunk16<NT>(acc, x[sb], (w00 >> sh4) & 0x0F0F0F0Fu, (w10 >> sh4) & 0x0F0F0F0Fu, (w01 >> sh4) & 0x0F0F0F0Fu,
+                    (w11 >> sh4) & 0x0F0F0F0Fu, __float2half2_rn(1024.0f), hs_g, hs_g8, hs_g, hs_g8, ho_g, ho_g8);
+      }
+    }
+  } else {  // Q6_K
+    const uint4 sc_g = lds16(tg + 3072 + g * 16);
+    const uint4 sc_g8 = lds16(tg + 3072 + (g + 8) * 16);
+    const __half2 d_g = __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(tg + 3328 + g * 2)));
+    const __half2 d_g8 = __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(tg + 3328 + (g + 8) * 2)));
+    const uint32_t scw_g[4] = {sc_g.x ^ 0x80808080u, sc_g.y ^ 0x80808080u, sc_g.z ^ 0x80808080u, sc_g.w ^ 0x80808080u};
+    const uint32_t scw_g8[4] = {sc_g8.x ^ 0x80808080u, sc_g8.y ^ 0x80808080u, sc_g8.z ^ 0x80808080u, sc_g8.w ^ 0x80808080u};
+#pragma unroll
+    for (int c2 = 0; c2 < 2; ++c2)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t af[2][2];  // [u][row half]
+        __half2 hs[2][2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int cu = c2 * 2 + u;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t wl = lds4(tg + (cu * 2 + h) * 256 + g * 32 + (q & 1) * 16 + 4 * t);
+            const uint32_t wh = lds4(tg + 2048 + (cu * 2 + h) * 128 + g * 16 + 4 * t);
+            const uint32_t hb = q == 0 ? (wh << 4) : q == 1 ? (wh << 2) : q == 2 ? wh : (wh >> 2);
+            af[u][h] = (((q >> 1) ? (wl >> 4) : wl) & 0x0F0F0F0Fu) | (hb & 0x30303030u);
+          }
+        }
+        q6k_chunk_scales(scw_g, d_g, c2, q, hs[0][0], hs[1][0]);
+        q6k_chunk_scales(scw_g8, d_g8, c2, q, hs[0][1], hs[1][1]);
+        chunk16<NT>(acc, x[c2 * 4 + q], af[0][0], af[0][1], af[1][0], af[1][1], __float2half2_rn(1056.0f), hs[0][0],
+                    hs[0][1], hs[1][0], hs[1][1], zero2, zero2);  // (q - 32) d scale
+      }
+  }
+}
+
+template <int TYPE, int NT, int EPI, int W>
+__global__ void __launch_bounds__(W * 32, 1)
+qgemm16s_kernel(const GemvArgs a) {
+  using R = RingS<TYPE, W>;
+  constexpr int NP = EPI == 2 ? 2 : 1;
+  constexpr int S = R::STAGES;
+  constexpr int CHUNKS = (TYPE == FB200_Q4_0 || TYPE == FB200_Q8_0) ? 4 : 8;
+  constexpr int OUTS = NT * 8 * 16;  // outputs of one unit and pass
+  constexpr int THREADS = W * 32;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* ring = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + R::RING_BYTES);
+  // [2][W][NT * 8][16]: index 0/1 = unit parity (one pass per unit) or pass (SwiGLU pairs)
+  float (*red)[W][NT * 8][16] = reinterpret_cast<float (*)[W][NT * 8][16]>(smem + R::RING_BYTES + R::BAR_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  uint8_t* my_ring = ring + warp * S * R::STRIDE;
+  const uint32_t my_bar = smem_u32(bars + warp * S);
+
+  pdl_launch_dependents();
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < S; ++s) mbar_init(my_bar + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+
+  // this CTA's share of the units; warp w owns K group w
+  const int base = a.nunits / (int)gridDim.x, rem = a.nunits - base * (int)gridDim.x;
+  const int q0 = (int)blockIdx.x * base + min((int)blockIdx.x, rem), q1 = q0 + base + ((int)blockIdx.x < rem ? 1 : 0);
+  const bool active = warp < a.ngroups;
+  const int n_items = active ? (q1 - q0) * NP : 0;
+  auto issue = [&](int i) {
+    const int u = q0 + i / NP, p = i - (i / NP) * NP;
+    const int tile = u + p * a.pair_tile_offset;
+    const int st = i % S;
+    const uint8_t* src = a.w + ((size_t)tile * a.ngroups + warp) * R::TG;
+    mbar_expect_tx(my_bar + 8 * st, R::TG);
+    bulk_g2s(smem_u32(my_ring + st * R::STRIDE), src, R::TG, my_bar + 8 * st);
+  };
+  if (lane == 0) {
+    const int pre = n_items < S ? n_items : S;
+    for (int i = 0; i < pre; ++i) issue(i);
+  }
+  pdl_wait();  // the packed activations come from the kernel before this one
+
+  Chunk16<NT> xr[CHUNKS];
+  if (n_items > 0) {
+#pragma unroll
+    for (int ch = 0; ch < CHUNKS; ++ch) load_chunk16<NT>(a, warp * CHUNKS + ch, g, t, xr[ch]);
+  }
+  const int nw = min(W, a.ngroups);  // warps that contribute to a tile
+  int item = 0;
+  for (int u = q0; u < q1; ++u) {
+    const int par = (u - q0) & 1;
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      if (!active) continue;
+      float acc[NT][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+      const int st = item % S;
+      mbar_wait(my_bar + 8 * st, (uint32_t)((item / S) & 1), a.status);
+      group16r<TYPE, NT, CHUNKS>(my_ring + st * R::STRIDE, lane, acc, xr);
+      __syncwarp();  // every lane has consumed the stage before it is refilled
+      if (lane == 0 && item + S < n_items) issue(item + S);
+      ++item;
+      float (*rw)[16] = red[NP == 1 ? par : p][warp];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        rw[8 * nt + 2 * t][g] = acc[nt][0];
+        rw[8 * nt + 2 * t + 1][g] = acc[nt][1];
+        rw[8 * nt + 2 * t][g + 8] = acc[nt][2];
+        rw[8 * nt + 2 * t + 1][g + 8] = acc[nt][3];
+      }
+    }
+    __syncthreads();
+    // ---- the warps' partial tiles, summed in warp (= K group) order
+    for (int o = threadIdx.x; o < OUTS; o += THREADS) {
+      const int m = o >> 4, r = o & 15;
+      const int n = u * 16 + r;
+      if (m >= a.M || n >= a.n_out) continue;
+      float v[NP];
+#pragma unroll
+      for (int p = 0; p < NP; ++p) {
+        float sum = 0.f;
+        for (int w = 0; w < nw; ++w) sum += red[NP == 1 ? par : p][w][m][r];
+        v[p] = sum * a.xscale[m];
+      }
+      const size_t idx = (size_t)m * a.n_out + n;
+      float out;
+      if (EPI == 2) {
+        // silu(gate) * up, fusor-ml/fusor/src/composite/activations.rs:47-64
+        const float gate = v[0];
+        out = (gate / (1.0f + expf(-gate))) * v[NP - 1];
+      } else if (EPI == 1) {
+        out = v[0] + a.r1[(size_t)m * a.r1_stride + n];
+        if (a.r2) out += a.r2[idx];
+      } else {
+        out = v[0];
+      }
+      a.y[idx] = out;
+    }
+    if (NP == 2) __syncthreads();  // both halves of `red` are rewritten by the next unit
+  }
+}
+
 // x[M, K] f32 -> fp16 rows scaled by a power of two into (-64, 64), laid out [Kp/32][Mp][32]
 // with lane t's eight halves of a chunk (elements 4t..4t+3, 16+4t..16+4t+3) at byte 16 t.
 // One CTA per (padded) row.
@@ -805,6 +1044,164 @@ pack_x16_kernel(const float* __restrict__ x, int M, int K, int Kp, int Mp, __hal
     const int pos = ((e & 15) >> 2) * 8 + (e >> 4) * 4 + (e & 3);
     xh[((size_t)kc * Mp + m) * 32 + pos] = __float2half_rn(v);
   }
+}
+
+// RMS norm (optionally of x + res) and the packing of pack_x16_kernel in one pass over the row:
+// y = ((x [+ res]) / rms) * w exactly as rms_norm_kernel computes it, then the row's power-of-two
+// scale and the fp16 fragments. One CTA per (padded) row; rows of x are x_stride elements apart,
+// rows of res are contiguous. EPT = elements a thread keeps in registers (K <= 256 * EPT).
+template <int EPT>
+__global__ void __launch_bounds__(256)
+norm_pack_x16_kernel(const float* __restrict__ x, size_t x_stride, const float* __restrict__ res,
+                     const float* __restrict__ w, float eps, int M, int K, int Kp, int Mp, __half* __restrict__ xh,
+                     float* __restrict__ xscale) {
+  __shared__ float sh[8];
+  __shared__ float bc;
+  const int m = blockIdx.x;
+  const float* xr = x + (size_t)m * x_stride;
+  const float* rr = res ? res + (size_t)m * K : nullptr;
+  float v[EPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPT; ++i) {
+    const int k = threadIdx.x + 256 * i;
+    v[i] = 0.f;
+    if (m < M && k < K) v[i] = rr ? xr[k] + rr[k] : xr[k];
+    ss = fmaf(v[i], v[i], ss);
+  }
+  // sum of squares in the order of rms_norm_kernel: per thread over k = tid, tid + 256, ..; lanes; warps
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < 8; ++i) t += sh[i];
+    bc = t;
+  }
+  __syncthreads();
+  const float rms = sqrtf(bc / (float)K + eps);
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPT; ++i) {
+    const int k = threadIdx.x + 256 * i;
+    if (m < M && k < K) v[i] = (v[i] / rms) * w[k];
+    amax = fmaxf(amax, fabsf(v[i]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = 0.f;
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, sh[i]);
+  int ex = 0;
+  if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &ex);
+  const float inv = ldexpf(64.0f, -ex);  // y * inv in (-64, 64)
+  if (threadIdx.x == 0) xscale[m] = ldexpf(1.0f, ex - 6);
+#pragma unroll
+  for (int i = 0; i < EPT; ++i) {
+    const int k = threadIdx.x + 256 * i;
+    if (k >= Kp) continue;
+    const int kc = k >> 5, e = k & 31;
+    const int pos = ((e & 15) >> 2) * 8 + (e >> 4) * 4 + (e & 3);
+    xh[((size_t)kc * Mp + m) * 32 + pos] = __float2half_rn(v[i] * inv);
+  }
+}
+
+// The two kernels above read their rows with dependent scalar loads (a few microseconds of pure
+// latency per launch). These forms issue every load of a row (x, the residual row, the norm
+// weights) as independent 16-byte loads before the first use, keep the row in registers, and
+// store four packed halves at a time. They need 16-byte aligned rows and K a multiple of 4;
+// V4 = float4 per thread (K <= 1024 * V4). NORM: rms_norm(x [+ res]) * w first, else x as it is.
+template <int V4, bool NORM>
+__global__ void __launch_bounds__(256)
+pack_x16v_kernel(const float* __restrict__ x, size_t x_stride, const float* __restrict__ res,
+                 const float* __restrict__ w, float eps, int M, int K, int Kp, int Mp, __half* __restrict__ xh,
+                 float* __restrict__ xscale) {
+  __shared__ float sh[8];
+  __shared__ float bc;
+  const int m = blockIdx.x;
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 v[V4], r4[V4], w4[V4];
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * x_stride);
+  const float4* rr = reinterpret_cast<const float4*>(res ? res + (size_t)m * K : nullptr);
+  const float4* wr = reinterpret_cast<const float4*>(w);
+  const bool row = m < M;
+#pragma unroll
+  for (int i = 0; i < V4; ++i) {
+    const int k4 = threadIdx.x + 256 * i;
+    const bool in = row && 4 * k4 < K;
+    v[i] = in ? __ldg(xr + k4) : zero4;
+    r4[i] = (NORM && in && rr) ? __ldg(rr + k4) : zero4;
+    w4[i] = (NORM && in) ? __ldg(wr + k4) : zero4;
+  }
+  if (NORM) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < V4; ++i) {
+      if (rr) { v[i].x += r4[i].x; v[i].y += r4[i].y; v[i].z += r4[i].z; v[i].w += r4[i].w; }
+      ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+      ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int i = 0; i < 8; ++i) t += sh[i];
+      bc = t;
+    }
+    __syncthreads();
+    // mean of squares, + eps, sqrt, divide, * weight (fusor-ml/fusor/src/composite/normalization.rs:404-461)
+    const float rms = sqrtf(bc / (float)K + eps);
+#pragma unroll
+    for (int i = 0; i < V4; ++i) {
+      v[i].x = (v[i].x / rms) * w4[i].x; v[i].y = (v[i].y / rms) * w4[i].y;
+      v[i].z = (v[i].z / rms) * w4[i].z; v[i].w = (v[i].w / rms) * w4[i].w;
+    }
+    __syncthreads();  // sh is reused below
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < V4; ++i)
+    amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v[i].x), fabsf(v[i].y))), fmaxf(fabsf(v[i].z), fabsf(v[i].w)));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = 0.f;
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, sh[i]);
+  int ex = 0;
+  if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &ex);
+  const float inv = ldexpf(64.0f, -ex);  // row * inv in (-64, 64)
+  if (threadIdx.x == 0) xscale[m] = ldexpf(1.0f, ex - 6);
+#pragma unroll
+  for (int i = 0; i < V4; ++i) {
+    const int k = 4 * (threadIdx.x + 256 * i);
+    if (k >= Kp) continue;
+    const int kc = k >> 5, e = k & 31;
+    const int pos = ((e & 15) >> 2) * 8 + (e >> 4) * 4;  // e is a multiple of 4: four consecutive slots
+    const __half2 lo = __floats2half2_rn(v[i].x * inv, v[i].y * inv), hi = __floats2half2_rn(v[i].z * inv, v[i].w * inv);
+    *reinterpret_cast<uint2*>(xh + ((size_t)kc * Mp + m) * 32 + pos) =
+        make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+  }
+}
+
+template <bool NORM>
+bool launch_pack_x16v(fb200_device* dev, const float* x, size_t x_stride, const float* res, const float* w, float eps,
+                      int mc, uint64_t k, uint64_t kp, int mp, __half* h, float* sc) {
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(res) | reinterpret_cast<uintptr_t>(w);
+  if ((bits & 15u) || (x_stride & 3u) || (k & 3u) || kp > 1024u * 16u) return false;
+  const int K = (int)k, Kp = (int)kp;
+  if (kp <= 1024u * 4u)
+    pack_x16v_kernel<4, NORM><<<mp, 256, 0, dev->stream>>>(x, x_stride, res, w, eps, mc, K, Kp, mp, h, sc);
+  else if (kp <= 1024u * 8u)
+    pack_x16v_kernel<8, NORM><<<mp, 256, 0, dev->stream>>>(x, x_stride, res, w, eps, mc, K, Kp, mp, h, sc);
+  else
+    pack_x16v_kernel<16, NORM><<<mp, 256, 0, dev->stream>>>(x, x_stride, res, w, eps, mc, K, Kp, mp, h, sc);
+  return true;
 }
 
 template <int TYPE, int NT, int EPI>
@@ -848,6 +1245,51 @@ int launch_nt16(fb200_device* dev, GemvArgs& a, int nt, int epi) {
   if (nt == 1) return launch_epi16<TYPE, 1>(dev, a, epi);
   if (nt == 2) return launch_epi16<TYPE, 2>(dev, a, epi);
   return launch_epi16<TYPE, 4>(dev, a, epi);
+}
+
+// Warps per CTA of the K-stationary kernel: 16 while the activation fragments of a K group fit
+// beside everything else in 128 registers per thread (up to 16 rows), 8 for 17..32 rows.
+constexpr int gemm16s_warps(int nt) { return nt == 4 ? 8 : 16; }
+
+template <int TYPE, int NT, int EPI>
+int launch_one16s(fb200_device* dev, GemvArgs& a) {
+  constexpr int W = gemm16s_warps(NT);
+  constexpr int SMEM = gemm16s_smem_bytes<TYPE, NT, W>();
+  static bool configured[64] = {false};  // per device ordinal
+  auto kern = qgemm16s_kernel<TYPE, NT, EPI, W>;
+  if (!configured[dev->ordinal & 63]) {
+    FB_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    configured[dev->ordinal & 63] = true;
+  }
+  int grid = dev->sm_count;
+  if (grid > a.nunits) grid = a.nunits;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(W * 32);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = dev->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dev->pdl ? 1 : 0;
+  FB_CUDA(dev, cudaLaunchKernelEx(&cfg, kern, a));
+  dev->launches++;
+  return FB200_OK;
+}
+
+template <int TYPE, int NT>
+int launch_epi16s(fb200_device* dev, GemvArgs& a, int epi) {
+  if (epi == FB200_EPI_SWIGLU) return launch_one16s<TYPE, NT, 2>(dev, a);
+  if (epi == FB200_EPI_RESIDUAL) return launch_one16s<TYPE, NT, 1>(dev, a);
+  return launch_one16s<TYPE, NT, 0>(dev, a);
+}
+
+template <int TYPE>
+int launch_nt16s(fb200_device* dev, GemvArgs& a, int nt, int epi) {
+  if (nt == 1) return launch_epi16s<TYPE, 1>(dev, a, epi);
+  if (nt == 2) return launch_epi16s<TYPE, 2>(dev, a, epi);
+  return launch_epi16s<TYPE, 4>(dev, a, epi);
 }
 
 template <int TYPE, int NT, int EPI>
@@ -901,6 +1343,89 @@ size_t fb200_xpack_bytes(int mp, uint64_t kp) {
          (size_t)mp * sizeof(float) + 256;
 }
 
+// Product of at most 32 activation rows that are already packed (fb200_pack_x16: fp16 fragments
+// [Kp/32][Mp][32] and the rows' power-of-two scales).
+int fb200_qgemm16_packed(fb200_device* dev, const fb200_qmatrix* w, const void* xh, const float* xscale16, int mc, int mp,
+                         float* y, int epi, const float* r1, const float* r2, bool r1_is_bias) {
+  const int nt = mp / 8;
+  GemvArgs a16 = {};
+  a16.w = w->data; a16.xq = reinterpret_cast<const uint8_t*>(xh); a16.xs16 = nullptr; a16.xscale = xscale16;
+  a16.y = y; a16.r1 = r1; a16.r2 = r2;
+  a16.r1_stride = r1_is_bias ? 0 : (int)(epi == FB200_EPI_SWIGLU ? w->n / 2 : w->n);
+  a16.M = mc; a16.Mp = mp; a16.ngroups = w->ngroups;
+  a16.nunits = w->ntiles;
+  a16.n_out = (int)w->n;
+  a16.pair_tile_offset = 0;
+  a16.status = dev->status;
+  if (epi == FB200_EPI_SWIGLU) {
+    a16.nunits = w->ntiles / 2;
+    a16.n_out = (int)(w->n / 2);
+    a16.pair_tile_offset = w->ntiles / 2;
+  }
+  // FB200_GEMM16_STREAMED=1 keeps every shape on the streamed kernel (for comparisons)
+  static const bool streamed_only = getenv("FB200_GEMM16_STREAMED") && getenv("FB200_GEMM16_STREAMED")[0] == '1';
+  if (w->ngroups <= gemm16s_warps(nt) && !streamed_only) {
+    switch (w->type) {
+      case FB200_Q4_0: return launch_nt16s<FB200_Q4_0>(dev, a16, nt, epi);
+      case FB200_Q8_0: return launch_nt16s<FB200_Q8_0>(dev, a16, nt, epi);
+      case FB200_Q4_K: return launch_nt16s<FB200_Q4_K>(dev, a16, nt, epi);
+      default: return launch_nt16s<FB200_Q6_K>(dev, a16, nt, epi);
+    }
+  }
+  switch (w->type) {
+    case FB200_Q4_0: return launch_nt16<FB200_Q4_0>(dev, a16, nt, epi);
+    case FB200_Q8_0: return launch_nt16<FB200_Q8_0>(dev, a16, nt, epi);
+    case FB200_Q4_K: return launch_nt16<FB200_Q4_K>(dev, a16, nt, epi);
+    default: return launch_nt16<FB200_Q6_K>(dev, a16, nt, epi);
+  }
+}
+
+// Padded inner size of a tiled matrix (what the packed activations must cover).
+uint64_t fb200_qmatrix_kp(const fb200_qmatrix* w) {
+  TileGeom geo;
+  if (!w->tiled || !tile_geom(w->type, &geo)) return 0;
+  return (uint64_t)w->ngroups * geo.group_elems;
+}
+
+// Rows per packed batch: 8, 16 or 32.
+int fb200_pack16_rows(int mc) { return mc <= 8 ? 8 : mc <= 16 ? 16 : 32; }
+
+// x[mc, K] f32 -> the packed form of fb200_qgemm16_packed in `scratch` (fb200_xpack_bytes(mp, kp) bytes).
+int fb200_pack_x16(fb200_device* dev, const float* x, int mc, uint64_t k, uint64_t kp, void* scratch, const void** xh,
+                   const float** xscale) {
+  const int mp = fb200_pack16_rows(mc);
+  __half* h = reinterpret_cast<__half*>(scratch);
+  float* sc = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + (size_t)kp * mp * 2);
+  if (!launch_pack_x16v<false>(dev, x, (size_t)k, nullptr, nullptr, 0.f, mc, k, kp, mp, h, sc))
+    pack_x16_kernel<<<mp, 256, 0, dev->stream>>>(x, mc, (int)k, (int)kp, mp, h, sc);
+  FB_LAUNCH_CHECK(dev);
+  *xh = h;
+  *xscale = sc;
+  return FB200_OK;
+}
+
+// rms_norm(x [+ res]) * w of mc rows, packed like fb200_pack_x16. Returns 1 when K is beyond what
+// the fused kernel keeps in registers (the caller then normalises and packs in two steps).
+int fb200_norm_pack_x16(fb200_device* dev, const float* x, size_t x_stride, const float* res, const float* w, float eps,
+                        int mc, uint64_t k, uint64_t kp, void* scratch, const void** xh, const float** xscale) {
+  const int mp = fb200_pack16_rows(mc);
+  __half* h = reinterpret_cast<__half*>(scratch);
+  float* sc = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + (size_t)kp * mp * 2);
+  if (launch_pack_x16v<true>(dev, x, x_stride, res, w, eps, mc, k, kp, mp, h, sc)) {
+  } else if (kp <= 256 * 8)
+    norm_pack_x16_kernel<8><<<mp, 256, 0, dev->stream>>>(x, x_stride, res, w, eps, mc, (int)k, (int)kp, mp, h, sc);
+  else if (kp <= 256 * 16)
+    norm_pack_x16_kernel<16><<<mp, 256, 0, dev->stream>>>(x, x_stride, res, w, eps, mc, (int)k, (int)kp, mp, h, sc);
+  else if (kp <= 256 * 32)
+    norm_pack_x16_kernel<32><<<mp, 256, 0, dev->stream>>>(x, x_stride, res, w, eps, mc, (int)k, (int)kp, mp, h, sc);
+  else
+    return 1;
+  FB_LAUNCH_CHECK(dev);
+  *xh = h;
+  *xscale = sc;
+  return FB200_OK;
+}
+
 // y[m0 .. m0+mc) = x . W^T for a chunk of at most 32 activation rows, using `scratch`.
 int fb200_qgemv_chunk(fb200_device* dev, const fb200_qmatrix* w, const float* x, int mc, float* y,
                       int epi, const float* r1, const float* r2, void* scratch, bool r1_is_bias) {
@@ -914,31 +1439,11 @@ int fb200_qgemv_chunk(fb200_device* dev, const fb200_qmatrix* w, const float* x,
   // 1.6 times slower); by default every batch of 2 .. 32 rows takes the fp16 kernel
   static const bool exact_small = getenv("FB200_EXACT_SMALL_BATCH") && getenv("FB200_EXACT_SMALL_BATCH")[0] == '1';
   if (nt > 1 || !exact_small) {
-    // fp16 activations [Kp/32][Mp][32] + row scales, fp16 tensor-core kernel
-    __half* xh = reinterpret_cast<__half*>(scratch);
-    float* xscale16 = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + (size_t)kp * mp * 2);
-    pack_x16_kernel<<<mp, 256, 0, dev->stream>>>(x, mc, (int)w->k, (int)kp, mp, xh, xscale16);
-    FB_LAUNCH_CHECK(dev);
-    GemvArgs a16;
-    a16.w = w->data; a16.xq = reinterpret_cast<const uint8_t*>(xh); a16.xs16 = nullptr; a16.xscale = xscale16;
-    a16.y = y; a16.r1 = r1; a16.r2 = r2;
-    a16.r1_stride = r1_is_bias ? 0 : (int)(epi == FB200_EPI_SWIGLU ? w->n / 2 : w->n);
-    a16.M = mc; a16.Mp = mp; a16.ngroups = w->ngroups;
-    a16.nunits = w->ntiles;
-    a16.n_out = (int)w->n;
-    a16.pair_tile_offset = 0;
-    a16.status = dev->status;
-    if (epi == FB200_EPI_SWIGLU) {
-      a16.nunits = w->ntiles / 2;
-      a16.n_out = (int)(w->n / 2);
-      a16.pair_tile_offset = w->ntiles / 2;
-    }
-    switch (w->type) {
-      case FB200_Q4_0: return launch_nt16<FB200_Q4_0>(dev, a16, nt, epi);
-      case FB200_Q8_0: return launch_nt16<FB200_Q8_0>(dev, a16, nt, epi);
-      case FB200_Q4_K: return launch_nt16<FB200_Q4_K>(dev, a16, nt, epi);
-      default: return launch_nt16<FB200_Q6_K>(dev, a16, nt, epi);
-    }
+    const void* xh;
+    const float* xscale16;
+    int rc = fb200_pack_x16(dev, x, mc, w->k, kp, scratch, &xh, &xscale16);
+    if (rc) return rc;
+    return fb200_qgemm16_packed(dev, w, xh, xscale16, mc, mp, y, epi, r1, r2, r1_is_bias);
   }
   uint8_t* xq = reinterpret_cast<uint8_t*>(scratch);
   size_t off = (size_t)(kp / 32) * nl * mp * 32;
