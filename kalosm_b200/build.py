@@ -10,10 +10,10 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libfusor_b200.so")
-SOURCES = ["api.cu", "repack.cu", "qgemv.cu", "qgemv1.cu", "dense.cu", "qgemm.cu", "ops.cu", "attention.cu", "attn_prefill.cu",
+SOURCES = ["api.cu", "repack.cu", "qgemv.cu", "qgemv1.cu", "dense.cu", "qgemm.cu", "ops.cu", "attention.cu", "attn_prefill.cu", "attn_decode_tc.cu",
            "fused_step.cu", "llama.cu", "comm.cu", "sampling.cu"]
 HEADERS = ["common.cuh", "formats.cuh", "qgemv_common.cuh", "qgemv1_groups.cuh", "packed_act.cuh",
-           "attn_decode.cuh", "fused_step.cuh", os.path.join("..", "..", "include", "fusor_b200.h")]
+           "attn_decode.cuh", "attn_mma.cuh", "qgemv1_groups2.cuh", "fused_step.cuh", os.path.join("..", "..", "include", "fusor_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 

@@ -26,6 +26,8 @@ int fb200_launch_attention_prefill(fb200_device* dev, const float* q, const __ha
                                    int hkv, int sq, int skv, const int* skv_dev, int cap, int d, float scale,
                                    int causal, float* out, int bshd);
 
+int fb200_launch_attention_decode_tc(fb200_device* dev, const fb200_dec_args& a, int d);
+
 namespace {
 
 constexpr int PREFILL_MIN_ROWS = 32;  // from here on the tensor-core prefill kernel takes over
@@ -377,6 +379,12 @@ int fb200_launch_attention(fb200_device* dev, const float* q, const __half* k, c
 // Launches the decode attention kernel for prepared arguments (a.done must point to b * hkv
 // zeroed arrival counters; the kernel leaves them zero again).
 int fb200_launch_attention_decode_args(fb200_device* dev, const fb200_dec_args& a, int d) {
+  // the tensor-core kernel covers every layout of the models; FB200_ATTN_DECODE_TC=0 keeps the scalar kernel
+  static const bool no_tc = getenv("FB200_ATTN_DECODE_TC") && getenv("FB200_ATTN_DECODE_TC")[0] == '0';
+  if (!no_tc) {
+    const int rc = fb200_launch_attention_decode_tc(dev, a, d);
+    if (rc != 1) return rc;
+  }
   if (a.h % a.hkv || a.groups > DEC_ROWS || (d != 64 && d != 128) || a.nsplit < 1 || a.nsplit > 32)
     return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "attention_decode: unsupported head layout");
   const unsigned grid = (unsigned)(a.b * a.hkv * a.nsplit);
@@ -524,8 +532,8 @@ int fb200_flash_attention(fb200_device* dev, const float* q_dev, const void* k_d
   fb200_op_trace scope(dev, sq == 1 ? "attention (decode)" : "attention (prefill)",
                        4.0 * (double)b * hkv * (double)skv * d + 8.0 * (double)b * h * (double)sq * d);
   if (sq == 1 && skv > 0 && (mask_kind == 0 || !mask_dev) && h % hkv == 0 && h / hkv <= DEC_ROWS && (d == 64 || d == 128)) {
-    // decode form: enough (batch, KV head, split) items to fill the GPU twice, at least 64 keys each
-    int ns = (2 * dev->sm_count + b * hkv - 1) / (b * hkv);
+    // decode form: as many (batch, KV head, split) items as run side by side (two per SM), at least 64 keys each
+    int ns = 2 * dev->sm_count / (b * hkv);
     ns = std::max(1, std::min(std::min(ns, 32), (skv + 63) / 64));
     const size_t need = ((size_t)ns * b * h * (d + 2)) * sizeof(float) + (size_t)b * hkv * sizeof(int);
     rc = fb200_ensure(dev, &dev->stage, &dev->stage_bytes, need);

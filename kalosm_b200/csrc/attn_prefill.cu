@@ -14,9 +14,7 @@
 // the exp2 domain, probabilities are rounded to fp16 for the second product. Tiles strictly
 // below the diagonal skip the mask arithmetic; CTAs with the longest key range are scheduled
 // first. The key count may come from device memory (graph replay).
-#include <cuda_fp16.h>
-
-#include "common.cuh"
+#include "attn_mma.cuh"
 
 namespace {
 
@@ -32,36 +30,6 @@ struct PrefillArgs {
   int b, h, hkv, sq, skv, cap, groups, bshd, causal;
   float scale_log2;    // scale * log2(e)
 };
-
-__device__ __forceinline__ uint32_t pf_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-// byte offset of 16-byte chunk `chunk` of row `row` (rows of D fp16), chunks XOR-swizzled by the row
-template <int D>
-__device__ __forceinline__ uint32_t pf_off(int row, int chunk) {
-  return (uint32_t)(row * (D * 2) + ((chunk ^ (row & 7)) << 4));
-}
-__device__ __forceinline__ void pf_ldsm4(uint32_t addr, uint32_t (&r)[4]) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void pf_ldsm4_t(uint32_t addr, uint32_t (&r)[4]) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void pf_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// 16-byte asynchronous copy; copies nothing and zero-fills when !valid
-__device__ __forceinline__ void pf_cp16(uint32_t dst, const void* src, bool valid) {
-  const int n = valid ? 16 : 0;
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
-}
-__device__ __forceinline__ uint32_t pf_pack(float lo, float hi) {
-  __half2 h = __floats2half2_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
 
 template <int D>
 __global__ void __launch_bounds__(PF_THREADS, 3)

@@ -37,6 +37,8 @@ int fb200_norm_pack_x16(fb200_device* dev, const float* x, size_t x_stride, cons
                         int mc, uint64_t k, uint64_t kp, void* scratch, const void** xh, const float** xscale);
 int fb200_qgemm16_packed(fb200_device* dev, const fb200_qmatrix* w, const void* xh, const float* xscale16, int mc, int mp,
                          float* y, int epi, const float* r1, const float* r2, bool r1_is_bias);
+int fb200_qgemm16_packed_multi(fb200_device* dev, const fb200_qmatrix* const* ws, float* const* ys, int nw, const void* xh,
+                               const float* xscale16, int mc, int mp);
 int fb200_attention_nsplit(const fb200_device* dev, int b, int hkv, int groups, int sq, int skv);
 int fb200_launch_attention_decode_args(fb200_device* dev, const fb200_dec_args& a, int d);
 bool fb200_qgemv1_fits(const fb200_qmatrix* w);
@@ -552,9 +554,15 @@ int run_forward(fb200_llama* m, int batch, int seq) {
     } else if (packed) {
       // 2..32 sequences: the norm writes the packed fp16 fragments the three projections share
       if ((rc = fb200_norm_pack_x16(dev, m->x, E, nullptr, L.attn_norm, c.rms_eps, (int)rows, E, kp_e, dev->xpack, &xh, &xs))) return rc;
-      if ((rc = fb200_qgemm16_packed(dev, L.wq, xh, xs, (int)rows, mp, m->q, FB200_EPI_NONE, nullptr, nullptr, false))) return rc;
-      if ((rc = fb200_qgemm16_packed(dev, L.wk, xh, xs, (int)rows, mp, m->k, FB200_EPI_NONE, nullptr, nullptr, false))) return rc;
-      if ((rc = fb200_qgemm16_packed(dev, L.wv, xh, xs, (int)rows, mp, m->v, FB200_EPI_NONE, nullptr, nullptr, false))) return rc;
+      const fb200_qmatrix* qkv_w[3] = {L.wq, L.wk, L.wv};
+      float* qkv_y[3] = {m->q, m->k, m->v};
+      rc = fb200_qgemm16_packed_multi(dev, qkv_w, qkv_y, 3, xh, xs, (int)rows, mp);
+      if (rc == 1) {  // not covered by the joint launch: one product after the other
+        for (int i = 0; i < 3; ++i)
+          if ((rc = fb200_qgemm16_packed(dev, qkv_w[i], xh, xs, (int)rows, mp, qkv_y[i], FB200_EPI_NONE, nullptr, nullptr, false)))
+            return rc;
+      }
+      if (rc) return rc;
     } else {
       if ((rc = fb200_launch_rms_norm_strided(dev, m->x, E, nullptr, L.attn_norm, c.rms_eps, rows, E, m->xn))) return rc;
       if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wq, m->q, nullptr))) return rc;
@@ -568,12 +576,13 @@ int run_forward(fb200_llama* m, int batch, int seq) {
       da.rope_cos = m->rope_cos; da.rope_sin = m->rope_sin; da.pos_dev = m->pos_dev;
       da.part = m->att_part; da.out = m->att; da.done = m->att_done;
       da.b = batch; da.h = H; da.hkv = HK; da.groups = H / HK; da.cap = c.max_seq_len; da.scale = scale;
-      int ns = (2 * dev->sm_count + batch * HK - 1) / (batch * HK);
-      ns = std::max(1, std::min(std::min(ns, 32), (c.max_seq_len + 63) / 64));
-      da.nsplit = ns;
       // many sequences: the (batch, kv head) pairs alone fill the GPU, so a context is cut only
-      // when it is long
+      // when it is long. The launch provides the splits of the longest context the cache can hold;
+      // the kernel uses those its actual context needs.
       da.min_keys = batch * HK >= dev->sm_count / 2 ? 256 : 64;
+      int ns = 2 * dev->sm_count / (batch * HK);  // two CTAs per SM: all splits run side by side
+      ns = std::max(1, std::min(std::min(ns, 32), (c.max_seq_len + da.min_keys - 1) / da.min_keys));
+      da.nsplit = ns;
       if ((size_t)ns * batch * H * (D + 2) * sizeof(float) > m->att_part_bytes)
         return fb200_fail(dev, FB200_ERR_CAPACITY, "llama: attention scratch too small");
       if ((rc = fb200_launch_attention_decode_args(dev, da, D))) return rc;

@@ -45,6 +45,14 @@ struct GemvArgs {
   int pair_tile_offset;  // SwiGLU: tile index distance between the gate and the up tile
   int nunits;            // work units: tiles, or (gate, up) tile pairs
   int* status;           // device status word (bounded waits that ran out are recorded here)
+  // several matrices that share the activation rows in one launch (qgemm16s_multi_kernel): the
+  // units of matrix 0 come first, then those of matrix 1, ...
+  int nseg;
+  struct Seg {
+    const uint8_t* w;
+    float* y;
+    int n_out, units, type;
+  } seg[3];
 };
 
 __device__ __forceinline__ uint32_t lds4(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
@@ -1247,6 +1255,113 @@ int launch_nt16(fb200_device* dev, GemvArgs& a, int nt, int epi) {
   return launch_epi16<TYPE, 4>(dev, a, epi);
 }
 
+// The K-stationary kernel over up to three K-quant matrices (Q4_K / Q6_K, mixed) that share the
+// activation rows, e.g. the q, k and v projections of a layer: one launch, one read of the
+// activations, and the tiles of all matrices form one list that is cut into equal shares.
+template <int NT, int W>
+struct RingM {
+  static constexpr int STRIDE = Ring<FB200_Q6_K>::STRIDE;  // the larger of the two tile-groups
+  static constexpr int FIT = (168 * 1024) / (W * STRIDE);
+  static constexpr int STAGES = FIT > 6 ? 6 : FIT;
+  static constexpr int RING_BYTES = W * STAGES * STRIDE;
+  static constexpr int BAR_BYTES = W * STAGES * 8;
+  static constexpr int SMEM = RING_BYTES + BAR_BYTES + 2 * W * NT * 8 * 16 * (int)sizeof(float);
+};
+
+template <int NT, int W>
+__global__ void __launch_bounds__(W * 32, 1)
+qgemm16s_multi_kernel(const GemvArgs a) {
+  using R = RingM<NT, W>;
+  constexpr int S = R::STAGES;
+  constexpr int CHUNKS = 8;
+  constexpr int OUTS = NT * 8 * 16;
+  constexpr int THREADS = W * 32;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* ring = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + R::RING_BYTES);
+  float (*red)[W][NT * 8][16] = reinterpret_cast<float (*)[W][NT * 8][16]>(smem + R::RING_BYTES + R::BAR_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  uint8_t* my_ring = ring + warp * S * R::STRIDE;
+  const uint32_t my_bar = smem_u32(bars + warp * S);
+
+  pdl_launch_dependents();
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < S; ++s) mbar_init(my_bar + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+
+  const int base = a.nunits / (int)gridDim.x, rem = a.nunits - base * (int)gridDim.x;
+  const int q0 = (int)blockIdx.x * base + min((int)blockIdx.x, rem), q1 = q0 + base + ((int)blockIdx.x < rem ? 1 : 0);
+  const bool active = warp < a.ngroups;
+  const int n_items = active ? q1 - q0 : 0;
+  // unit -> (matrix, tile)
+  auto locate = [&](int u, int& sidx, int& tile) {
+    sidx = 0; tile = u;
+    if (a.nseg > 1 && tile >= a.seg[0].units) { tile -= a.seg[0].units; sidx = 1; }
+    if (a.nseg > 2 && sidx == 1 && tile >= a.seg[1].units) { tile -= a.seg[1].units; sidx = 2; }
+  };
+  auto issue = [&](int i) {
+    int sidx, tile;
+    locate(q0 + i, sidx, tile);
+    const uint32_t tg = a.seg[sidx].type == FB200_Q4_K ? Ring<FB200_Q4_K>::TG : Ring<FB200_Q6_K>::TG;
+    const int st = i % S;
+    const uint8_t* src = a.seg[sidx].w + ((size_t)tile * a.ngroups + warp) * tg;
+    mbar_expect_tx(my_bar + 8 * st, tg);
+    bulk_g2s(smem_u32(my_ring + st * R::STRIDE), src, tg, my_bar + 8 * st);
+  };
+  if (lane == 0) {
+    const int pre = n_items < S ? n_items : S;
+    for (int i = 0; i < pre; ++i) issue(i);
+  }
+  pdl_wait();  // the packed activations come from the kernel before this one
+
+  Chunk16<NT> xr[CHUNKS];
+  if (n_items > 0) {
+#pragma unroll
+    for (int ch = 0; ch < CHUNKS; ++ch) load_chunk16<NT>(a, warp * CHUNKS + ch, g, t, xr[ch]);
+  }
+  const int nw = min(W, a.ngroups);
+  for (int u = q0; u < q1; ++u) {
+    const int item = u - q0, par = item & 1;
+    int sidx, tile;
+    locate(u, sidx, tile);
+    if (active) {
+      float acc[NT][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+      const int st = item % S;
+      mbar_wait(my_bar + 8 * st, (uint32_t)((item / S) & 1), a.status);
+      if (a.seg[sidx].type == FB200_Q4_K) group16r<FB200_Q4_K, NT, CHUNKS>(my_ring + st * R::STRIDE, lane, acc, xr);
+      else group16r<FB200_Q6_K, NT, CHUNKS>(my_ring + st * R::STRIDE, lane, acc, xr);
+      __syncwarp();
+      if (lane == 0 && item + S < n_items) issue(item + S);
+      float (*rw)[16] = red[par][warp];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        rw[8 * nt + 2 * t][g] = acc[nt][0];
+        rw[8 * nt + 2 * t + 1][g] = acc[nt][1];
+        rw[8 * nt + 2 * t][g + 8] = acc[nt][2];
+        rw[8 * nt + 2 * t + 1][g + 8] = acc[nt][3];
+      }
+    }
+    __syncthreads();
+    for (int o = threadIdx.x; o < OUTS; o += THREADS) {
+      const int m = o >> 4, r = o & 15;
+      const int n = tile * 16 + r;
+      if (m >= a.M || n >= a.seg[sidx].n_out) continue;
+      float sum = 0.f;
+      for (int w = 0; w < nw; ++w) sum += red[par][w][m][r];
+      a.seg[sidx].y[(size_t)m * a.seg[sidx].n_out + n] = sum * a.xscale[m];
+    }
+  }
+}
+
 // Warps per CTA of the K-stationary kernel: 16 while the activation fragments of a K group fit
 // beside everything else in 128 registers per thread (up to 16 rows), 8 for 17..32 rows.
 constexpr int gemm16s_warps(int nt) { return nt == 4 ? 8 : 16; }
@@ -1385,6 +1500,60 @@ uint64_t fb200_qmatrix_kp(const fb200_qmatrix* w) {
   TileGeom geo;
   if (!w->tiled || !tile_geom(w->type, &geo)) return 0;
   return (uint64_t)w->ngroups * geo.group_elems;
+}
+
+// Up to three products over the same packed rows in one launch (no epilogue). Covers Q4_K / Q6_K
+// matrices of at most 16 K groups and up to 16 rows; returns 1 otherwise (the caller then launches
+// the products one by one).
+int fb200_qgemm16_packed_multi(fb200_device* dev, const fb200_qmatrix* const* ws, float* const* ys, int nw, const void* xh,
+                               const float* xscale16, int mc, int mp) {
+  const int nt = mp / 8;
+  if (nw < 1 || nw > 3 || nt > 2) return 1;
+  GemvArgs a = {};
+  a.xq = reinterpret_cast<const uint8_t*>(xh); a.xscale = xscale16;
+  a.M = mc; a.Mp = mp; a.ngroups = ws[0]->ngroups; a.status = dev->status;
+  a.nseg = nw;
+  for (int i = 0; i < nw; ++i) {
+    if (!ws[i]->tiled || (ws[i]->type != FB200_Q4_K && ws[i]->type != FB200_Q6_K) || ws[i]->ngroups != a.ngroups ||
+        ws[i]->k != ws[0]->k)
+      return 1;
+    a.seg[i].w = ws[i]->data; a.seg[i].y = ys[i]; a.seg[i].n_out = (int)ws[i]->n; a.seg[i].units = ws[i]->ntiles;
+    a.seg[i].type = (int)ws[i]->type;
+    a.nunits += ws[i]->ntiles;
+  }
+  if (a.ngroups > 16 || a.nunits < 1) return 1;
+  static const bool streamed_only = getenv("FB200_GEMM16_STREAMED") && getenv("FB200_GEMM16_STREAMED")[0] == '1';
+  if (streamed_only) return 1;
+  int grid = dev->sm_count < a.nunits ? dev->sm_count : a.nunits;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(16 * 32);
+  cfg.stream = dev->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dev->pdl ? 1 : 0;
+  static bool configured[64][2] = {};
+  if (nt == 1) {
+    auto kern = qgemm16s_multi_kernel<1, 16>;
+    if (!configured[dev->ordinal & 63][0]) {
+      FB_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RingM<1, 16>::SMEM));
+      configured[dev->ordinal & 63][0] = true;
+    }
+    cfg.dynamicSmemBytes = RingM<1, 16>::SMEM;
+    FB_CUDA(dev, cudaLaunchKernelEx(&cfg, kern, a));
+  } else {
+    auto kern = qgemm16s_multi_kernel<2, 16>;
+    if (!configured[dev->ordinal & 63][1]) {
+      FB_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RingM<2, 16>::SMEM));
+      configured[dev->ordinal & 63][1] = true;
+    }
+    cfg.dynamicSmemBytes = RingM<2, 16>::SMEM;
+    FB_CUDA(dev, cudaLaunchKernelEx(&cfg, kern, a));
+  }
+  dev->launches++;
+  return FB200_OK;
 }
 
 // Rows per packed batch: 8, 16 or 32.
