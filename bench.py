@@ -242,17 +242,17 @@ def whole_job_rate(world, batch, steps, ms):
     return world * batch * steps / (ms / 1e3)
 
 
-def gemv_roofline(kb, dev, torch, stream, reps):
-    """The dominant kernel timed alone: single-row product with SwiGLU epilogue over 16 distinct
-    gate+up matrices (16 x 66 MB, larger than L2, so every launch streams from HBM)."""
+def gemv_roofline(kb, dev, torch, stream, reps, rows=1):
+    """The dominant kernel timed alone: product of `rows` activation rows with SwiGLU epilogue over 16
+    distinct gate+up matrices (16 x 66 MB, larger than L2, so every launch streams from HBM)."""
     from kalosm_b200 import synth
     f, e = CFG["ffn"], CFG["hidden"]
     mats = []
     for i in range(16):
         raw = synth.random_qweights(900 + i, 0.02, 2 * f, e, Q4_K, device="cuda").cpu().numpy()
         mats.append(kb.QMatrix.from_raw_bytes(dev, (2 * f, e), raw, Q4_K))
-    x = dev.tensor(np.random.default_rng(5).standard_normal((1, e)).astype(np.float32))
-    y = dev.empty((1, f))
+    x = dev.tensor(np.random.default_rng(5).standard_normal((rows, e)).astype(np.float32))
+    y = dev.empty((rows, f))
     for w in mats:
         x.q_mat_mul(w, epilogue=kb.EPI_SWIGLU, out=y)
     torch.cuda.synchronize()
@@ -264,12 +264,15 @@ def gemv_roofline(kb, dev, torch, stream, reps):
     g1.record(stream)
     torch.cuda.synchronize()
     us = g0.elapsed_time(g1) * 1e3 / (reps * len(mats))
-    kbytes = qbytes(Q4_K, 2 * f, e)
+    kbytes = qbytes(Q4_K, 2 * f, e) + (0 if rows == 1 else 4 * rows * (e + f))
     peak, which = peaks()
     achieved = kbytes / us / 1e3
     for w in mats:
         w.free()
-    return {"bound": "hbm", "kernel": "qgemv1_kernel<Q4_K, SwiGLU> on ffn gate+up [28672 x 4096]",
+    name = ("qgemv1_kernel<Q4_K, SwiGLU>" if rows == 1 else
+            f"pack_x16v_kernel + qgemm16s_kernel<Q4_K, SwiGLU> ({rows} rows)" if rows <= 16 else
+            f"pack_x16v_kernel + qgemm16_kernel<Q4_K, SwiGLU> ({rows} rows)")
+    return {"bound": "hbm", "kernel": name + " on ffn gate+up [28672 x 4096]",
             "achieved": achieved, "peak": peak, "peak_source": which, "unit": "GB/s",
             "frac": achieved / peak, "us_per_launch": us, "bytes_per_launch": kbytes, "traffic": None}
 
@@ -282,7 +285,38 @@ def run_gemv_only(args):
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
     dev = kb.Device(0, stream.cuda_stream)
-    print(json.dumps({"roofline": gemv_roofline(kb, dev, torch, stream, max(1, args.gemv_reps))}), flush=True)
+    print(json.dumps({"roofline": gemv_roofline(kb, dev, torch, stream, max(1, args.gemv_reps), rows=max(1, min(32, args.batch)))}),
+          flush=True)
+
+
+def run_attn_decode_only(args):
+    """One decode-attention case (batch 32, 4096 cached keys, Llama-3-8B heads: 0.54 GB of fp16 K and V per
+    launch, two distinct caches): the small case profiler captures use."""
+    import torch
+    import kalosm_b200 as kb
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    dev = kb.Device(0, stream.cuda_stream)
+    b, h, hkv, d, L = 32, 32, 8, 128, 4096
+    ks = [dev.tensor((np.random.default_rng(3 * i).standard_normal((b, hkv, L, d)) * 0.5).astype(np.float16)) for i in range(2)]
+    vs = [dev.tensor((np.random.default_rng(3 * i + 1).standard_normal((b, hkv, L, d)) * 0.5).astype(np.float16)) for i in range(2)]
+    q = dev.tensor(np.random.default_rng(9).standard_normal((b, h, 1, d)).astype(np.float32))
+    o = dev.empty((b, h, 1, d))
+    for i in range(4):
+        dev.flash_attention(q, ks[i % 2], vs[i % 2], 1.0 / np.sqrt(d), out=o)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(16):
+        dev.flash_attention(q, ks[i % 2], vs[i % 2], 1.0 / np.sqrt(d), out=o)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / 16
+    nbytes = b * L * hkv * d * 2 * 2 + 2 * b * h * d * 4
+    peak, which = peaks()
+    print(json.dumps({"case": "decode_attention", "batch": b, "context": L, "us": us, "algorithmic_bytes": nbytes,
+                      "gbs": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / peak, "peak": peak, "peak_source": which}), flush=True)
 
 
 def run_prefill_only(args):
@@ -719,6 +753,25 @@ def run_ours(args):
     bail_if_any(None if np.array_equal(tok, toks[:, -1]) else
                 "stepping through forward() and the device-resident loop gave different tokens")
 
+    # ---- optional: device time per kernel of the decode step (CUPTI through torch.profiler; the
+    # profiled steps are extra steps after the timed regions, never part of a reported number)
+    kernel_table = None
+    if args.kernel_table and rank == 0:
+        from torch.profiler import ProfilerActivity, profile
+        model.truncate(start_pos)
+        n_prof = 8
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            model.generate_greedy(last, n_prof)
+            torch.cuda.synchronize()
+        rows = []
+        for ev in prof.key_averages():
+            t = getattr(ev, "device_time_total", None)
+            t = ev.cuda_time_total if t is None else t
+            if t > 0:
+                rows.append({"kernel": ev.key[:120], "us_per_step": t / n_prof, "launches_per_step": ev.count / n_prof})
+        rows.sort(key=lambda r: -r["us_per_step"])
+        kernel_table = {"steps": n_prof, "device_us_per_step": sum(r["us_per_step"] for r in rows), "kernels": rows[:24]}
+
     # ---- the stand-alone single-row product (the kernel behind fb200_q_mat_mul at M = 1) ----
     roof_gemv = gemv_roofline(kb, dev, torch, stream, 8) if rank == 0 else None
 
@@ -784,6 +837,8 @@ def run_ours(args):
             "step_hbm": {"bytes_per_step": wb + kv, "achieved_gbs": step_gbs, "frac_of_peak": step_gbs / peak,
                          "peak_source": which},
             "cpu_baseline": cpu}
+    if kernel_table is not None:
+        line["kernel_table"] = kernel_table
     if tp_leg is not None:
         line["tensor_parallel"] = {"tp": world, "model": "llama3-70b-shaped, all Q4_K, prompt %d, 128 greedy steps" % args.tp_prompt,
                                    "by_batch": tp_leg}
@@ -805,6 +860,8 @@ def main():
     ap.add_argument("--layers", type=int, default=CFG["n_layer"],
                     help="decoder layers of the model (fewer than 32 only for profiler captures; not a bench value)")
     ap.add_argument("--gemv-only", action="store_true", help="run only the dominant-kernel leg")
+    ap.add_argument("--attn-decode-only", action="store_true",
+                    help="run only one decode-attention case (batch 32, 4096 keys): the small case of profiler captures")
     ap.add_argument("--prefill-only", action="store_true",
                     help="run one prefill product and one prefill attention (profiling case)")
     ap.add_argument("--tp", action="store_true",
@@ -813,6 +870,8 @@ def main():
     ap.add_argument("--tp-nccl", action="store_true", help="with --tp: keep the decode step on NCCL all-reduces")
     ap.add_argument("--no-tp", action="store_true", help="with --gpus N > 1: skip the tensor-parallel leg after the replicas")
     ap.add_argument("--gemv-reps", type=int, default=8)
+    ap.add_argument("--kernel-table", action="store_true",
+                    help="add the device time per kernel of 8 extra decode steps (torch.profiler) as `kernel_table`")
     ap.add_argument("--sweep", action="store_true",
                     help="per-kernel table over the other product shapes and decode attention (several JSON lines)")
     args = ap.parse_args()
@@ -823,6 +882,8 @@ def main():
         run_sweep(args)
     elif args.gemv_only:
         run_gemv_only(args)
+    elif args.attn_decode_only:
+        run_attn_decode_only(args)
     elif args.prefill_only:
         run_prefill_only(args)
     elif args.tp:

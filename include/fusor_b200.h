@@ -166,8 +166,10 @@ FB200_API int fb200_rms_norm_q_mat_mul(fb200_device* dev, const float* x_dev,
  *     (11-bit operands, about 5e-4 relative L2 against fp32; fb200_q_mat_mul sends a single row to
  *     its integer-limb kernel instead, which needs no scratch and is closer to fp32).
  *   - Warm-up: the first call per device looks up the array's device address, and the first call
- *     per (weight type, row bucket 1..8 / 9..16 / 17..32) sets that kernel variant's shared-memory
- *     attribute and, under CUDA's lazy loading, loads its code. Make one call of every
+ *     per (weight type, row bucket 1..8 / 9..16 / 17..32, K) sets that kernel variant's
+ *     shared-memory attribute and, under CUDA's lazy loading, loads its code (K selects the
+ *     variant: rows of at most 16 block groups take another product kernel than longer rows, and
+ *     the packing kernel has variants for K up to 4096 / 8192 / 16384). Make one call of every
  *     combination you will use before entering the region that must not allocate, and before
  *     any stream capture.
  *   - FB200_ERR_CAPACITY when M > 32 or when the packed activations (about 136 bytes per
