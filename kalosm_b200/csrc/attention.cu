@@ -27,6 +27,9 @@ int fb200_launch_attention_prefill(fb200_device* dev, const float* q, const __ha
                                    int causal, float* out, int bshd);
 
 int fb200_launch_attention_decode_tc(fb200_device* dev, const fb200_dec_args& a, int d);
+int fb200_launch_attention_prefill_tc(fb200_device* dev, const float* q, const __half* k, const __half* v, int b, int h,
+                                      int hkv, int sq, int skv, const int* skv_dev, int cap, int d, float scale,
+                                      int causal, float* out, int bshd);
 
 namespace {
 
@@ -351,8 +354,11 @@ int fb200_launch_attention(fb200_device* dev, const float* q, const __half* k, c
   if (h % hkv) return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "attention: %d heads not divisible by %d kv heads", h, hkv);
   if (d != 64 && d != 128) return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "attention: head_dim %d (64 or 128 supported)", d);
   if (sq >= PREFILL_MIN_ROWS && mask_kind <= 1) {
-    // many query positions, no mask or causal: the tensor-core kernel
-    const int rc = fb200_launch_attention_prefill(dev, q, k, v, b, h, hkv, sq, skv, skv_dev, cap, d, scale, mask_kind, out, bshd);
+    // many query positions, no mask or causal: the tensor-core kernels (tcgen05 for head size 128
+    // and at least half a 128-row tile of queries, mma.sync otherwise)
+    int rc = 1;
+    if (sq >= 64) rc = fb200_launch_attention_prefill_tc(dev, q, k, v, b, h, hkv, sq, skv, skv_dev, cap, d, scale, mask_kind, out, bshd);
+    if (rc == 1) rc = fb200_launch_attention_prefill(dev, q, k, v, b, h, hkv, sq, skv, skv_dev, cap, d, scale, mask_kind, out, bshd);
     if (rc != 1) return rc;
   }
   AttnArgs a = {};
