@@ -10,9 +10,10 @@
 //
 // One CTA = 128 query rows of one head: 128 softmax threads (thread r owns query row r, which is
 // also lane r of the CTA's TMEM columns, so the softmax statistics of a row never leave a thread)
-// and one more warp whose first lane issues the MMAs. The roles meet only at mbarriers (operands
-// ready: 128 arrivals; product done: tcgen05.commit); there is no CTA-wide barrier in the loop, so
-// the issue latency of the MMAs is never on the softmax threads' path.
+// one warp whose first lane issues the MMAs and one whose first lane requests the K and V tiles
+// (TMA). The roles meet only at mbarriers (tile landed: the copy's byte count; P written: 128
+// arrivals; product done: tcgen05.commit); there is no CTA-wide barrier in the loop, and neither
+// the issue latency of the MMAs nor the copies are on the softmax threads' path.
 // Per tile t of 64 keys:
 //   S_t = Q K_t^T   8 tcgen05.mma (M = 128 queries, N = 64 keys, K = 16 of the head size) into one of
 //                   two S buffers in TMEM; it is issued one tile ahead, so it runs while the threads
@@ -27,25 +28,30 @@
 // TMEM) and the running sum are rescaled only when the maximum has grown by more than 2^8 since
 // the last rescale (a warp-uniform decision; tcgen05.ld, multiply, tcgen05.st), so P stays below
 // 256 (exact range of fp16) and most tiles never touch O outside the MMA.
-// Q, K and V sit in shared memory in the canonical core-matrix layout of the MMA without swizzle
-// (8 rows x 16 bytes per core matrix); K and V tiles are double-buffered by 16-byte cp.async
-// (rows past the valid length zero-filled). Two CTAs share an SM (99 KB of shared memory and 256
-// TMEM columns each). Tiles above the diagonal are never visited; CTAs with the longest key range
+// Q sits in shared memory in the canonical core-matrix layout of the MMA without swizzle (8 rows x
+// 16 bytes per core matrix, written by the softmax threads). K and V tiles come by tensor TMA
+// (cp.async.bulk.tensor, two boxes of 64 keys x 64 dims per tile, 128-byte swizzle; rows past the
+// valid length are outside the tensor map and arrive as zeros), two tiles ahead, and are read by
+// the MMA through 128-byte-swizzle descriptors: K as a K-major operand, V as an MN-major one, as
+// it lies in the cache. Two CTAs share an SM (112 KB of shared memory and 256 TMEM columns each). Tiles above the diagonal are never visited; CTAs with the longest key range
 // start first.
 // Every mbarrier wait is bounded: a wait that gives up sets the device status word and a flag in
 // shared memory, every later wait of the CTA then returns at once, the CTA runs through its loop
 // without waiting (results invalid, nothing stored), frees its TMEM columns and exits.
+#include <cuda.h>
+
 #include "attn_mma.cuh"
 #include "qgemv_common.cuh"
 
 namespace {
 
 constexpr int XQ = 128, XK = 64, XD = 128, X_THREADS = 128;  // X_THREADS: the softmax threads (one per query row)
-constexpr int X_BLOCK = X_THREADS + 32;                       // + one warp whose first lane issues the MMAs
+constexpr int X_BLOCK = X_THREADS + 64;                       // + the MMA issuer's warp + the copy requester's warp
 constexpr int X_Q_BYTES = XQ * XD * 2;   // 32 KB
 constexpr int X_KV_BYTES = XK * XD * 2;  // 16 KB per K or V tile
 constexpr int X_TAIL = 256;              // barriers, TMEM slot, give-up flag
-constexpr int X_SMEM = X_Q_BYTES + 4 * X_KV_BYTES + X_TAIL;
+constexpr int X_KBUFS = 3, X_VBUFS = 2;   // K tiles are requested three tiles ahead, V tiles two
+constexpr int X_SMEM = X_Q_BYTES + (X_KBUFS + X_VBUFS) * X_KV_BYTES + X_TAIL;
 constexpr int X_TMEM_COLS = 256;         // S buffers: columns 0..63 and 64..127; O: columns 128..255
 constexpr float X_RESCALE = 8.0f;        // log2 of the growth of a row maximum that triggers a rescale of O
 
@@ -57,9 +63,12 @@ struct XArgs {
   const int* skv_dev;  // if not null: valid keys = *skv_dev + sq
   int b, h, hkv, sq, skv, cap, groups, bshd, causal;
   float scale_log2;    // scale * log2(e)
-  int v_lbo, v_sbo;    // descriptor strides of the MN-major V operand (bytes)
+  int k_lbo, v_lbo, v_sbo;  // descriptor strides (bytes) of the swizzled operands
   int* status;
 };
+// descriptor strides (bytes) of the swizzled operands, and the layout code of the 128-byte swizzle
+constexpr uint32_t X_SW128 = 2;
+constexpr uint32_t X_BOX_BYTES = XK * 64 * 2;  // one TMA box: 64 keys x 64 dims of fp16 = 8 KB
 
 __device__ __forceinline__ bool x_wait(uint32_t bar, uint32_t parity, volatile int* dead, int* status) {
   for (int it = 0; it < (1 << 22); ++it) {
@@ -80,8 +89,16 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 // Shared-memory matrix descriptor without swizzle: start address, leading and stride byte offsets
 // in 16-byte units, descriptor version 1.
-__device__ __forceinline__ uint64_t x_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46);
+__device__ __forceinline__ uint64_t x_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo, uint32_t layout = 0) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46) |
+         ((uint64_t)layout << 61);
+}
+// One box of a 3-D tensor map (dims, keys, sequence x KV head) into shared memory; completion is
+// counted in bytes on the mbarrier.
+__device__ __forceinline__ void x_tma_box(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void x_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -125,13 +142,6 @@ __device__ __forceinline__ float x_ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 16-byte asynchronous copy past L1; zero-fills when !valid. (Every copy fetches a whole 32-byte
-// sector, so L2 delivers twice the bytes; the form through L1 shares sectors between lanes and
-// halves that traffic but measured 15 % slower.)
-__device__ __forceinline__ void x_cp16(uint32_t dst, const void* src, bool valid) {
-  const int n = valid ? 16 : 0;
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
-}
 // Byte offset of the 16-byte chunk `chunk` (8 K elements) of row `row` in a K-major operand whose K
 // extent is `kchunks` chunks: core matrices of a row group side by side along K, row groups behind.
 __device__ __forceinline__ uint32_t x_kmajor(int row, int chunk, int kchunks) {
@@ -139,17 +149,19 @@ __device__ __forceinline__ uint32_t x_kmajor(int row, int chunk, int kchunks) {
 }
 
 __global__ void __launch_bounds__(X_BLOCK, 2)
-attn_prefill_tc_kernel(const XArgs a) {
-  extern __shared__ __align__(128) uint8_t sm[];
+attn_prefill_tc_kernel(const XArgs a, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
+  extern __shared__ __align__(1024) uint8_t sm[];  // the swizzled tiles need 1024-byte alignment (checked below)
   uint8_t* Qs = sm;
-  uint8_t* KVs = sm + X_Q_BYTES;  // [2 buffers][K | V]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + X_Q_BYTES + 4 * X_KV_BYTES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  uint8_t* Ks = sm + X_Q_BYTES;                        // [X_KBUFS][2 boxes]
+  uint8_t* Vs = Ks + X_KBUFS * X_KV_BYTES;             // [X_VBUFS][2 boxes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + X_VBUFS * X_KV_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // bar_s: S_t complete (one per S buffer); bar_o: O += P V_t complete; bar_kfull: K tile staged (128 arrivals);
-  // bar_pfull: P written and V tile staged (128 arrivals)
-  const uint32_t bar_s = smem_u32(bars), bar_o = smem_u32(bars + 2), bar_kfull = smem_u32(bars + 3), bar_pfull = smem_u32(bars + 4);
+  // bar_s[2]: S_t complete (one per S buffer); bar_o: O += P V_t complete; bar_kfull[3], bar_vfull[2]: tile
+  // landed (byte count of its two boxes); bar_pfull: P written (128 arrivals)
+  const uint32_t bar_s = smem_u32(bars), bar_o = smem_u32(bars + 2), bar_kfull = smem_u32(bars + 3),
+                 bar_vfull = smem_u32(bars + 6), bar_pfull = smem_u32(bars + 8);
 
   const int qt = gridDim.x - 1 - blockIdx.x;  // longest key ranges first
   const int head = blockIdx.y, bi = blockIdx.z, kvh = head / a.groups;
@@ -160,15 +172,19 @@ attn_prefill_tc_kernel(const XArgs a) {
   const int ntiles = (kmax + XK - 1) / XK;
   const size_t q_row = a.bshd ? (size_t)a.h * XD : (size_t)XD;
   const size_t q_base = (size_t)bi * a.h * a.sq * XD + (a.bshd ? (size_t)head * XD : (size_t)head * a.sq * XD);
-  const __half* kb = a.k + ((size_t)bi * a.hkv + kvh) * (size_t)a.cap * XD;
-  const __half* vb = a.v + ((size_t)bi * a.hkv + kvh) * (size_t)a.cap * XD;
+  const int plane = bi * a.hkv + kvh;  // third coordinate of the tensor maps
 
   if (tid == 0) {
     *dead = 0;
+    if (smem_u32(sm) & 1023u) {  // never seen; the MMA would read the tiles with the wrong swizzle phase
+      *dead = 1;
+      atomicExch(a.status, FB200_ERR_TIMEOUT);
+    }
     mbar_init(bar_s, 1);
     mbar_init(bar_s + 8, 1);
     mbar_init(bar_o, 1);
-    mbar_init(bar_kfull, X_THREADS);
+    for (int i = 0; i < X_KBUFS; ++i) mbar_init(bar_kfull + 8 * i, 1);
+    for (int i = 0; i < X_VBUFS; ++i) mbar_init(bar_vfull + 8 * i, 1);
     mbar_init(bar_pfull, X_THREADS);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -176,85 +192,8 @@ attn_prefill_tc_kernel(const XArgs a) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(X_TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-
-  // A warp's copy instruction moves 8 rows x 4 chunks: the 8 rows of a chunk are one core matrix
-  // (128 contiguous bytes of shared memory, all 32 banks once), and a row's 4 chunks are 64
-  // contiguous bytes of global memory (whole sectors).
-  // One commit group per call, empty when the tile does not exist, so that "all but the two newest
-  // groups have landed" means the same thing in every iteration.
-  // K tile: K-major (N = keys, K = head size). V tile: MN-major (N = dims, K = keys): the 16 bytes
-  // of a cache row chunk are 8 dims of one key = one row of a core matrix whose 8 rows are 8 keys.
-  auto load_k = [&](int tile) {
-    if (tile < ntiles) {
-      const int kt = tile * XK;
-      const uint32_t dst = pf_smem(KVs + (tile & 1) * 2 * X_KV_BYTES);
-#pragma unroll
-      for (int i = 0; i < XK * (XD / 8) / X_THREADS; ++i) {
-        const int id = warp * (XK * (XD / 8) / X_THREADS) + i;  // (row group, four chunks) handled by this warp now
-        const int row = (id >> 2) * 8 + (lane & 7), c = (id & 3) * 4 + (lane >> 3);
-        const bool valid = kt + row < skv;
-        x_cp16(dst + x_kmajor(row, c, XD / 8), kb + (size_t)(valid ? kt + row : 0) * XD + c * 8, valid);
-      }
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  };
-  auto load_v = [&](int tile) {
-    if (tile < ntiles) {
-      const int kt = tile * XK;
-      const uint32_t dst = pf_smem(KVs + (tile & 1) * 2 * X_KV_BYTES + X_KV_BYTES);
-#pragma unroll
-      for (int i = 0; i < XK * (XD / 8) / X_THREADS; ++i) {
-        const int id = warp * (XK * (XD / 8) / X_THREADS) + i;
-        const int row = (id >> 2) * 8 + (lane & 7), c = (id & 3) * 4 + (lane >> 3);
-        const bool valid = kt + row < skv;
-        x_cp16(dst + (uint32_t)(c * (XK / 8) * 128 + (row >> 3) * 128 + (row & 7) * 16),
-                vb + (size_t)(valid ? kt + row : 0) * XD + c * 8, valid);
-      }
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  };
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();  // barriers initialised, TMEM columns allocated
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem = *tmem_slot;
-  // instruction descriptors: fp32 accumulator, fp16 operands, M = 128; S: N = 64, both K-major; O: N = 128, B MN-major
-  constexpr uint32_t IDESC_S = (1u << 4) | ((uint32_t)(XK >> 3) << 17) | ((uint32_t)(XQ >> 4) << 24);
-  constexpr uint32_t IDESC_O = (1u << 4) | (1u << 16) | ((uint32_t)(XD >> 3) << 17) | ((uint32_t)(XQ >> 4) << 24);
-
-  if (warp == X_THREADS / 32) {
-    // ---- MMA issuer: S_0, then per tile S_(t+1) (runs under the softmax of tile t) and O += P V_t
-    if (lane == 0 && ntiles > 0) {
-      auto issue_s = [&](int tile) {  // S buffer tile & 1 = Q . K_tile^T
-        x_wait(bar_kfull, (uint32_t)(tile & 1), dead, a.status);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t ks = pf_smem(KVs + (tile & 1) * 2 * X_KV_BYTES);
-#pragma unroll
-        for (int s = 0; s < XD / 16; ++s)
-          x_mma(tmem + (uint32_t)((tile & 1) * XK), x_desc(pf_smem(Qs) + s * 256, 128, (XD / 8) * 128),
-                x_desc(ks + s * 256, 128, (XD / 8) * 128), IDESC_S, s ? 1u : 0u);
-        x_commit(bar_s + 8 * (tile & 1));
-      };
-      issue_s(0);
-      for (int tile = 0; tile < ntiles; ++tile) {
-        if (tile + 1 < ntiles) issue_s(tile + 1);
-        x_wait(bar_pfull, (uint32_t)(tile & 1), dead, a.status);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t vs = pf_smem(KVs + (tile & 1) * 2 * X_KV_BYTES + X_KV_BYTES);
-#pragma unroll
-        for (int s = 0; s < XK / 16; ++s)
-          x_mma_ta(tmem + 2 * XK, tmem + (uint32_t)((tile & 1) * XK + s * 8),
-                   x_desc(vs + s * 256, (uint32_t)a.v_lbo, (uint32_t)a.v_sbo), IDESC_O, (tile | s) ? 1u : 0u);
-        x_commit(bar_o);
-      }
-    }
-  } else {
-    // ---- softmax threads
-    const uint32_t tmem_lane = tmem + ((uint32_t)(32 * warp) << 16);  // this warp's 32 lanes
-    // commit order: K0, K1, V0, then per tile t: K(t+2) (after the first hand-over), V(t+1) (after the second)
-    load_k(0);
-    load_k(1);
-    load_v(0);
-    // Q tile: f32 -> fp16 into the K-major operand layout (rows past Sq are zero)
+  // Q tile: f32 -> fp16 into the K-major operand layout (rows past Sq are zero), by the softmax threads
+  if (warp < X_THREADS / 32) {
     for (int id = warp; id < (XQ / 8) * (XD / 32); id += X_THREADS / 32) {
       const int row = (id >> 2) * 8 + (lane & 7), c = (id & 3) * 4 + (lane >> 3);
       float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f), x1 = x0;
@@ -266,25 +205,74 @@ attn_prefill_tc_kernel(const XArgs a) {
       *reinterpret_cast<uint4*>(Qs + x_kmajor(row, c, XD / 8)) =
           make_uint4(pf_pack(x0.x, x0.y), pf_pack(x0.z, x0.w), pf_pack(x1.x, x1.y), pf_pack(x1.z, x1.w));
     }
-    asm volatile("cp.async.wait_group 2;" ::: "memory");  // K0
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // this thread's copies / stores -> tensor-core reads
-    mbar_arrive(bar_kfull);  // phase 0: Q and K0 are staged
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // these stores -> tensor-core reads
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();  // barriers initialised, TMEM columns allocated, Q staged
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+  // instruction descriptors: fp32 accumulator, fp16 operands, M = 128; S: N = 64, both K-major; O: N = 128, B MN-major
+  constexpr uint32_t IDESC_S = (1u << 4) | ((uint32_t)(XK >> 3) << 17) | ((uint32_t)(XQ >> 4) << 24);
+  constexpr uint32_t IDESC_O = (1u << 4) | (1u << 16) | ((uint32_t)(XD >> 3) << 17) | ((uint32_t)(XQ >> 4) << 24);
 
+  if (warp == X_THREADS / 32 + 1) {
+    // ---- copy requester: K0..K2, V0, V1, then K(t+3) when S_t has completed and V(t+2) when
+    // O += P V_t has. A tile is two boxes (dims 0..63 and 64..127) of 64 keys.
+    if (lane == 0 && ntiles > 0) {
+      auto fetch = [&](const CUtensorMap* map, int tile, uint32_t dst, uint32_t bar) {
+        mbar_expect_tx(bar, 2 * X_BOX_BYTES);
+        x_tma_box(dst, map, 0, tile * XK, plane, bar);
+        x_tma_box(dst + X_BOX_BYTES, map, 64, tile * XK, plane, bar);
+      };
+      const uint32_t k0 = pf_smem(Ks), v0 = pf_smem(Vs);
+      for (int t = 0; t < X_KBUFS && t < ntiles; ++t) fetch(&kmap, t, k0 + t * X_KV_BYTES, bar_kfull + 8 * t);
+      for (int t = 0; t < X_VBUFS && t < ntiles; ++t) fetch(&vmap, t, v0 + t * X_KV_BYTES, bar_vfull + 8 * t);
+      for (int tile = 0; tile + X_VBUFS < ntiles; ++tile) {
+        x_wait(bar_s + 8 * (tile & 1), (uint32_t)((tile >> 1) & 1), dead, a.status);  // K buffer of tile t is free
+        if (tile + X_KBUFS < ntiles)
+          fetch(&kmap, tile + X_KBUFS, k0 + (tile % X_KBUFS) * X_KV_BYTES, bar_kfull + 8 * (tile % X_KBUFS));
+        x_wait(bar_o, (uint32_t)(tile & 1), dead, a.status);  // V buffer of tile t is free
+        fetch(&vmap, tile + X_VBUFS, v0 + (tile % X_VBUFS) * X_KV_BYTES, bar_vfull + 8 * (tile % X_VBUFS));
+      }
+    }
+  } else if (warp == X_THREADS / 32) {
+    // ---- MMA issuer: S_0, then per tile S_(t+1) (runs under the softmax of tile t) and O += P V_t
+    if (lane == 0 && ntiles > 0) {
+      auto issue_s = [&](int tile) {  // S buffer tile & 1 = Q . K_tile^T
+        x_wait(bar_kfull + 8 * (tile % X_KBUFS), (uint32_t)((tile / X_KBUFS) & 1), dead, a.status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t ks = pf_smem(Ks + (tile % X_KBUFS) * X_KV_BYTES);
+#pragma unroll
+        for (int s = 0; s < XD / 16; ++s)  // k-step s: box s / 4, 32 bytes further inside the 128-byte rows per step
+          x_mma(tmem + (uint32_t)((tile & 1) * XK), x_desc(pf_smem(Qs) + s * 256, 128, (XD / 8) * 128),
+                x_desc(ks + (s >> 2) * X_BOX_BYTES + (s & 3) * 32, (uint32_t)a.k_lbo, 1024, X_SW128), IDESC_S, s ? 1u : 0u);
+        x_commit(bar_s + 8 * (tile & 1));
+      };
+      issue_s(0);
+      for (int tile = 0; tile < ntiles; ++tile) {
+        if (tile + 1 < ntiles) issue_s(tile + 1);
+        x_wait(bar_pfull, (uint32_t)(tile & 1), dead, a.status);
+        x_wait(bar_vfull + 8 * (tile % X_VBUFS), (uint32_t)((tile / X_VBUFS) & 1), dead, a.status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t vs = pf_smem(Vs + (tile % X_VBUFS) * X_KV_BYTES);
+#pragma unroll
+        for (int s = 0; s < XK / 16; ++s)  // k-step s: 16 keys = 16 rows of 128 bytes further
+          x_mma_ta(tmem + 2 * XK, tmem + (uint32_t)((tile & 1) * XK + s * 8),
+                   x_desc(vs + s * 2048, (uint32_t)a.v_lbo, (uint32_t)a.v_sbo, X_SW128), IDESC_O, (tile | s) ? 1u : 0u);
+        x_commit(bar_o);
+      }
+    }
+  } else {
+    // ---- softmax threads
+    const uint32_t tmem_lane = tmem + ((uint32_t)(32 * warp) << 16);  // this warp's 32 lanes
     float m_ref = -INFINITY;  // the maximum the exponentials and O currently refer to (scaled, log2 domain)
     float l_run = 0.f;
     const int row = q0 + tid;
 
     for (int tile = 0; tile < ntiles; ++tile) {
       const int sb = tile & 1;
-      x_wait(bar_s + 8 * sb, (uint32_t)((tile >> 1) & 1), dead, a.status);  // S_t is there, its K buffer is free
+      x_wait(bar_s + 8 * sb, (uint32_t)((tile >> 1) & 1), dead, a.status);  // S_t is there
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      asm volatile("cp.async.wait_group 1;" ::: "memory");  // K(t+1) has landed (only V_t may still be in flight)
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(bar_kfull);  // phase t + 1 (this thread has long finished reading the S buffer S_(t+1) goes to)
-      // New copies are issued after the proxy fence, never just before it: the fence waits for the
-      // copies its thread has in flight, which would put their latency on the tile's critical path.
-      load_k(tile + 2);
 
       // ---- this thread's row of S: mask, running maximum and sum
       const int kt = tile * XK;
@@ -322,12 +310,10 @@ attn_prefill_tc_kernel(const XArgs a) {
       // product into that buffer, S_(t+2), is issued behind O += P V_t)
       x_st32(tmem_lane + (uint32_t)(sb * XK), pk);
 
-      // ---- the previous tile's O += P V has completed: P, its V buffer and O may be touched
-      if (tile > 0) {
+      // ---- O is rescaled only after the previous tile's O += P V has completed
+      if (tile > 0 && __any_sync(0xFFFFFFFFu, grow)) {
         x_wait(bar_o, (uint32_t)((tile - 1) & 1), dead, a.status);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      }
-      if (tile > 0 && __any_sync(0xFFFFFFFFu, grow)) {
 #pragma unroll
         for (int c = 0; c < XD / 32; ++c) {
           uint32_t ov[32];
@@ -337,14 +323,10 @@ attn_prefill_tc_kernel(const XArgs a) {
           for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
           x_st32(tmem_lane + 2 * XK + 32 * c, ov);
         }
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      asm volatile("cp.async.wait_group 1;" ::: "memory");  // V_t has landed (only K(t+2) may still be in flight)
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(bar_pfull);  // phase t
-      load_v(tile + 1);  // its buffer held V_(t-1), whose product has completed
     }
 
     // ---- the last product, then normalise and store (nothing is stored after a wait has given up)
@@ -379,24 +361,57 @@ attn_prefill_tc_kernel(const XArgs a) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(X_TMEM_COLS) : "memory");
 }
 
+// cuTensorMapEncodeTiled of the driver, looked up once (the library does not link against libcuda)
+typedef CUresult (*x_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+x_encode_fn x_encoder() {
+  static x_encode_fn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<x_encode_fn>(p);
+  }();
+  return fn;
+}
+// fp16 cache [planes][cap][128] seen as (dims, keys, planes) with `rows` valid keys per plane; boxes
+// of 64 dims x 64 keys, 128-byte swizzle, zeros outside.
+bool x_make_map(CUtensorMap* map, const __half* base, int rows, int cap, int planes) {
+  x_encode_fn enc = x_encoder();
+  if (!enc) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)XD, (cuuint64_t)rows, (cuuint64_t)planes};
+  const cuuint64_t strides[2] = {(cuuint64_t)XD * 2, (cuuint64_t)cap * XD * 2};
+  const cuuint32_t box[3] = {64, (cuuint32_t)XK, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<__half*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
 
-// Covers: head size 128, no mask or causal, 16-byte aligned q / out rows. Returns 1 when the shape
-// is not covered (the caller then runs the mma.sync kernel). FB200_ATTN_TCGEN05=0 switches it off.
+// Covers: head size 128, no mask or causal, 16-byte aligned q / out / cache, the number of keys known
+// on the host (skv > 0; skv_dev, if given, must hold skv - sq). Returns 1 when the shape is not
+// covered (the caller then runs the mma.sync kernel). FB200_ATTN_TCGEN05=0 switches it off.
 int fb200_launch_attention_prefill_tc(fb200_device* dev, const float* q, const __half* k, const __half* v, int b, int h,
                                       int hkv, int sq, int skv, const int* skv_dev, int cap, int d, float scale,
                                       int causal, float* out, int bshd) {
   static const bool off = getenv("FB200_ATTN_TCGEN05") && getenv("FB200_ATTN_TCGEN05")[0] == '0';
-  if (off || d != XD || h % hkv || b > 65535 || h > 65535 || !(scale > 0.f)) return 1;
-  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 15u) return 1;
+  if (off || d != XD || h % hkv || b > 65535 || h > 65535 || !(scale > 0.f) || skv <= 0 || skv > cap) return 1;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(k) |
+       reinterpret_cast<uintptr_t>(v)) & 15u)
+    return 1;
+  CUtensorMap kmap, vmap;
+  if (!x_make_map(&kmap, k, skv, cap, b * hkv) || !x_make_map(&vmap, v, skv, cap, b * hkv)) return 1;
   XArgs a = {};
   a.q = q; a.k = k; a.v = v; a.out = out; a.skv_dev = skv_dev;
   a.b = b; a.h = h; a.hkv = hkv; a.sq = sq; a.skv = skv; a.cap = cap; a.groups = h / hkv; a.bshd = bshd;
   a.causal = causal; a.scale_log2 = scale * 1.4426950408889634f;
-  // V operand (MN-major, no swizzle): core matrices of 8 keys x 8 dims; 128 bytes between core
-  // matrices adjacent along the keys (K), 1024 bytes between core matrices adjacent along the dims
-  a.v_lbo = 128;
-  a.v_sbo = (XK / 8) * 128;
+  a.k_lbo = 16;           // not used by a swizzled K-major operand
+  a.v_lbo = X_BOX_BYTES;  // MN-major V: between the two 64-dim boxes
+  a.v_sbo = 1024;         // ... and between groups of 8 keys
   a.status = dev->status;
   const dim3 grid((unsigned)((sq + XQ - 1) / XQ), (unsigned)h, (unsigned)b);
   static bool configured[64] = {false};
@@ -404,5 +419,5 @@ int fb200_launch_attention_prefill_tc(fb200_device* dev, const float* q, const _
     FB_CUDA(dev, cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, X_SMEM));
     configured[dev->ordinal & 63] = true;
   }
-  return fb200_launch(dev, attn_prefill_tc_kernel, grid, dim3(X_BLOCK), (size_t)X_SMEM, false, a);
+  return fb200_launch(dev, attn_prefill_tc_kernel, grid, dim3(X_BLOCK), (size_t)X_SMEM, false, a, kmap, vmap);
 }

@@ -593,7 +593,9 @@ int run_forward(fb200_llama* m, int batch, int seq) {
           c.max_seq_len, total);
       FB_LAUNCH_CHECK(dev);
       // mask only when seq_len > 1 (raw/mod.rs:969); strictly causal over the new positions
-      if ((rc = fb200_launch_attention(dev, m->q, L.kc, L.vc, batch, H, HK, seq, 0, m->pos_dev,
+      // keys = position + seq: known on the host (the tcgen05 kernel needs it for its tensor maps) and
+      // on the device (pos_dev, for kernels inside a captured graph)
+      if ((rc = fb200_launch_attention(dev, m->q, L.kc, L.vc, batch, H, HK, seq, seq > 1 ? m->pos + seq : 0, m->pos_dev,
                                        c.max_seq_len, D, scale, nullptr, seq > 1 ? 1 : 0, m->att,
                                        m->att_part, nsplit, 1))) return rc;
     }
