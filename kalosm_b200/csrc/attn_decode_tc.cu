@@ -33,7 +33,10 @@ constexpr int TC_STAGES = 3;     // staged tiles (two CTAs per SM: 2 x 96 KB of 
 template <int N>
 __device__ __forceinline__ void tc_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int D>
+// PDL: launched with programmatic stream serialization; everything that does not depend on the
+// kernel before (the position, the cached keys and values of earlier positions) is requested
+// before griddepcontrol.wait, q and the new k / v after it.
+template <int D, bool PDL>
 __global__ void __launch_bounds__(TC_THREADS, 2)
 attn_decode_tc_kernel(const fb200_dec_args a0) {
   constexpr int CH = D / 8;             // 16-byte chunks per row
@@ -90,6 +93,10 @@ attn_decode_tc_kernel(const fb200_dec_args a0) {
   };
 #pragma unroll
   for (int i = 0; i < TC_STAGES - 1; ++i) fetch(i);
+  if (PDL) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
 
   // ---- the new position: rotate k, append k and v (fp16), keep the pair for the staged tile
   uint32_t knew = 0u, vnew = 0u;
@@ -322,11 +329,18 @@ int fb200_launch_attention_decode_tc(fb200_device* dev, const fb200_dec_args& a,
   const unsigned grid = (unsigned)(a.b * a.hkv * a.nsplit);
   const size_t smem = (size_t)(TC_STAGES * 2 * TC_KEYS + TC_ROWS) * d * 2;
   static bool configured[64] = {false};
+  // with a device-resident position the kernel is part of a decode step: its predecessor produced q, k, v
+  const bool pdl = a.pos_dev != nullptr;
   if (!configured[dev->ordinal & 63]) {
-    FB_CUDA(dev, cudaFuncSetAttribute(attn_decode_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (TC_STAGES * 2 * TC_KEYS + TC_ROWS) * 128 * 2));
-    FB_CUDA(dev, cudaFuncSetAttribute(attn_decode_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (TC_STAGES * 2 * TC_KEYS + TC_ROWS) * 64 * 2));
+    const int bytes128 = (TC_STAGES * 2 * TC_KEYS + TC_ROWS) * 128 * 2, bytes64 = (TC_STAGES * 2 * TC_KEYS + TC_ROWS) * 64 * 2;
+    FB_CUDA(dev, cudaFuncSetAttribute(attn_decode_tc_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes128));
+    FB_CUDA(dev, cudaFuncSetAttribute(attn_decode_tc_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes128));
+    FB_CUDA(dev, cudaFuncSetAttribute(attn_decode_tc_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes64));
+    FB_CUDA(dev, cudaFuncSetAttribute(attn_decode_tc_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes64));
     configured[dev->ordinal & 63] = true;
   }
-  if (d == 128) return fb200_launch(dev, attn_decode_tc_kernel<128>, dim3(grid), dim3(TC_THREADS), smem, false, a);
-  return fb200_launch(dev, attn_decode_tc_kernel<64>, dim3(grid), dim3(TC_THREADS), smem, false, a);
+  if (d == 128 && pdl) return fb200_launch(dev, attn_decode_tc_kernel<128, true>, dim3(grid), dim3(TC_THREADS), smem, true, a);
+  if (d == 128) return fb200_launch(dev, attn_decode_tc_kernel<128, false>, dim3(grid), dim3(TC_THREADS), smem, false, a);
+  if (pdl) return fb200_launch(dev, attn_decode_tc_kernel<64, true>, dim3(grid), dim3(TC_THREADS), smem, true, a);
+  return fb200_launch(dev, attn_decode_tc_kernel<64, false>, dim3(grid), dim3(TC_THREADS), smem, false, a);
 }

@@ -579,7 +579,7 @@ int run_forward(fb200_llama* m, int batch, int seq) {
       // many sequences: the (batch, kv head) pairs alone fill the GPU, so a context is cut only
       // when it is long. The launch provides the splits of the longest context the cache can hold;
       // the kernel uses those its actual context needs.
-      da.min_keys = batch * HK >= dev->sm_count / 2 ? 256 : 64;
+      da.min_keys = batch * HK >= dev->sm_count / 2 ? 1024 : 64;
       int ns = 2 * dev->sm_count / (batch * HK);  // two CTAs per SM: all splits run side by side
       ns = std::max(1, std::min(std::min(ns, 32), (c.max_seq_len + da.min_keys - 1) / da.min_keys));
       da.nsplit = ns;

@@ -1132,6 +1132,8 @@ pack_x16v_kernel(const float* __restrict__ x, size_t x_stride, const float* __re
   const int m = blockIdx.x;
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
   float4 v[V4], r4[V4], w4[V4];
+  pdl_launch_dependents();  // the product that follows may start fetching its weights
+  pdl_wait();               // the rows come from the kernel before this one
   const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * x_stride);
   const float4* rr = reinterpret_cast<const float4*>(res ? res + (size_t)m * K : nullptr);
   const float4* wr = reinterpret_cast<const float4*>(w);
@@ -1203,12 +1205,15 @@ bool launch_pack_x16v(fb200_device* dev, const float* x, size_t x_stride, const 
   const uintptr_t bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(res) | reinterpret_cast<uintptr_t>(w);
   if ((bits & 15u) || (x_stride & 3u) || (k & 3u) || kp > 1024u * 16u) return false;
   const int K = (int)k, Kp = (int)kp;
+  // launched with programmatic stream serialization: the kernel starts while its predecessor drains
+  // and waits (griddepcontrol.wait) before it reads the rows
   if (kp <= 1024u * 4u)
-    pack_x16v_kernel<4, NORM><<<mp, 256, 0, dev->stream>>>(x, x_stride, res, w, eps, mc, K, Kp, mp, h, sc);
+    fb200_launch(dev, pack_x16v_kernel<4, NORM>, dim3(mp), dim3(256), 0, true, x, x_stride, res, w, eps, mc, K, Kp, mp, h, sc);
   else if (kp <= 1024u * 8u)
-    pack_x16v_kernel<8, NORM><<<mp, 256, 0, dev->stream>>>(x, x_stride, res, w, eps, mc, K, Kp, mp, h, sc);
+    fb200_launch(dev, pack_x16v_kernel<8, NORM>, dim3(mp), dim3(256), 0, true, x, x_stride, res, w, eps, mc, K, Kp, mp, h, sc);
   else
-    pack_x16v_kernel<16, NORM><<<mp, 256, 0, dev->stream>>>(x, x_stride, res, w, eps, mc, K, Kp, mp, h, sc);
+    fb200_launch(dev, pack_x16v_kernel<16, NORM>, dim3(mp), dim3(256), 0, true, x, x_stride, res, w, eps, mc, K, Kp, mp, h, sc);
+  dev->launches--;  // counted by the caller's product, as the plain packing launch is
   return true;
 }
 
