@@ -526,10 +526,15 @@ __device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cas
 
 // Four unsigned bytes -> two half2 (1024 + byte each), then (v - centre) * scale - offset.
 // centre includes the 1024; scale and offset are per row.
+// HIGH: the bytes hold a nibble in their upper half (byte = 16 n, taken from the packed word with a
+// mask alone, no shift); under the exponent of 64 a byte counts sixteenths, so the half is 64 + n
+// and the centre includes the 64.
+template <bool HIGH = false>
 __device__ __forceinline__ void deq4(uint32_t w, __half2 centre, __half2 scale, __half2 offset, uint32_t& h01,
                                      uint32_t& h23) {
-  const __half2 v01 = __hsub2(bits_h2(__byte_perm(w, 0x64646464u, 0x4140)), centre);
-  const __half2 v23 = __hsub2(bits_h2(__byte_perm(w, 0x64646464u, 0x4342)), centre);
+  constexpr uint32_t MAGIC = HIGH ? 0x54545454u : 0x64646464u;
+  const __half2 v01 = __hsub2(bits_h2(__byte_perm(w, MAGIC, 0x4140)), centre);
+  const __half2 v23 = __hsub2(bits_h2(__byte_perm(w, MAGIC, 0x4342)), centre);
   h01 = h2_bits(__hfma2(v01, scale, offset));
   h23 = h2_bits(__hfma2(v23, scale, offset));
 }
@@ -595,18 +600,18 @@ __device__ __forceinline__ void load_chunk16(const GemvArgs& a, int kc, int g, i
 }
 
 // One 32-element chunk: unsigned bytes of rows g / g+8, elements 4t.. (lo) and 16+4t.. (hi).
-template <int NT>
+template <int NT, bool HIGH = false>
 __device__ __forceinline__ void chunk16(float (&acc)[NT][4], const Chunk16<NT>& x, uint32_t lo_g, uint32_t lo_g8,
                                         uint32_t hi_g, uint32_t hi_g8, __half2 centre, __half2 s_lo_g,
                                         __half2 s_lo_g8, __half2 s_hi_g, __half2 s_hi_g8, __half2 o_g,
                                         __half2 o_g8) {
   uint32_t a0, a1, a2, a3;
-  deq4(lo_g, centre, s_lo_g, o_g, a0, a2);
-  deq4(lo_g8, centre, s_lo_g8, o_g8, a1, a3);
+  deq4<HIGH>(lo_g, centre, s_lo_g, o_g, a0, a2);
+  deq4<HIGH>(lo_g8, centre, s_lo_g8, o_g8, a1, a3);
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) mma_f16_k16(acc[nt], a0, a1, a2, a3, x.b[nt].x, x.b[nt].y);
-  deq4(hi_g, centre, s_hi_g, o_g, a0, a2);
-  deq4(hi_g8, centre, s_hi_g8, o_g8, a1, a3);
+  deq4<HIGH>(hi_g, centre, s_hi_g, o_g, a0, a2);
+  deq4<HIGH>(hi_g8, centre, s_hi_g8, o_g8, a1, a3);
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) mma_f16_k16(acc[nt], a0, a1, a2, a3, x.b[nt].z, x.b[nt].w);
 }
@@ -663,9 +668,12 @@ __device__ __forceinline__ void group16(const GemvArgs& a, const uint8_t* tg, in
         if (kn >= 0) load_chunk16<NT>(a, kn, g, t, nxt);
         __half2 hs_g, hs_g8, ho_g, ho_g8;
         q4k_chunk_scales(sm, lane, sb, hs_g, hs_g8, ho_g, ho_g8);
-        const uint32_t sh4 = hi ? 4u : 0u;
-        chunk16<NT>(acc, cur, (w00 >> sh4) & 0x0F0F0F0Fu, (w10 >> sh4) & 0x0F0F0F0Fu, (w01 >> sh4) & 0x0F0F0F0Fu,
-                    (w11 >> sh4) & 0x0F0F0F0Fu, __float2half2_rn(1024.0f), hs_g, hs_g8, hs_g, hs_g8, ho_g, ho_g8);
+        if (hi == 0)
+          chunk16<NT, false>(acc, cur, w00 & 0x0F0F0F0Fu, w10 & 0x0F0F0F0Fu, w01 & 0x0F0F0F0Fu, w11 & 0x0F0F0F0Fu,
+                             __float2half2_rn(1024.0f), hs_g, hs_g8, hs_g, hs_g8, ho_g, ho_g8);
+        else
+          chunk16<NT, true>(acc, cur, w00 & 0xF0F0F0F0u, w10 & 0xF0F0F0F0u, w01 & 0xF0F0F0F0u, w11 & 0xF0F0F0F0u,
+                            __float2half2_rn(64.0f), hs_g, hs_g8, hs_g, hs_g8, ho_g, ho_g8);
         cur = nxt;
       }
     }
@@ -877,9 +885,12 @@ __device__ __forceinline__ void group16r(const uint8_t* tg, int lane, float (&ac
         const int sb = 2 * pair + hi;
         __half2 hs_g, hs_g8, ho_g, ho_g8;
         q4k_chunk_scales(sm, lane, sb, hs_g, hs_g8, ho_g, ho_g8);
-        const uint32_t sh4 = hi ? 4u : 0u;
-        chunk16<NT>(acc, x[sb], (w00 >> sh4) & 0x0F0F0F0Fu, (w10 >> sh4) & 0x0F0F0F0Fu, (w01 >> sh4) & 0x0F0F0F0Fu,
-                    (w11 >> sh4) & 0x0F0F0F0Fu, __float2half2_rn(1024.0f), hs_g, hs_g8, hs_g, hs_g8, ho_g, ho_g8);
+        if (hi == 0)
+          chunk16<NT, false>(acc, x[sb], w00 & 0x0F0F0F0Fu, w10 & 0x0F0F0F0Fu, w01 & 0x0F0F0F0Fu, w11 & 0x0F0F0F0Fu,
+                             __float2half2_rn(1024.0f), hs_g, hs_g8, hs_g, hs_g8, ho_g, ho_g8);
+        else
+          chunk16<NT, true>(acc, x[sb], w00 & 0xF0F0F0F0u, w10 & 0xF0F0F0F0u, w01 & 0xF0F0F0F0u, w11 & 0xF0F0F0F0u,
+                            __float2half2_rn(64.0f), hs_g, hs_g8, hs_g, hs_g8, ho_g, ho_g8);
       }
     }
   } else {  // Q6_K
