@@ -289,6 +289,67 @@ def run_gemv_only(args):
           flush=True)
 
 
+def run_q5_only(args):
+    """Products with Q5_K (the kernel that reads GGUF byte order) and Q5_0 weights (widened to Q8_0 tiles) on the FFN up shape
+    [14336 x 4096] at 1, 8 and 32 activation rows: 8 distinct matrices per type (8 x 40 MB, larger than L2).
+    Quant bytes are random, block scales in a realistic range; bytes per launch = the matrix + f32 rows in and out."""
+    import torch
+    import kalosm_b200 as kb
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    dev = kb.Device(0, stream.cuda_stream)
+    n, k = CFG["ffn"], CFG["hidden"]
+    peak, which = peaks()
+    out = []
+    for ty, name, be, bb in ((13, "Q5_K", 256, 176), (6, "Q5_0", 32, 22)):
+        mats = []
+        for i in range(8):
+            rng = np.random.default_rng(40 + i)
+            raw = rng.integers(0, 256, size=(n * k // be, bb), dtype=np.uint8)
+            d = rng.uniform(1e-4 if be == 256 else 1e-3, 2e-4 if be == 256 else 2e-3, size=(raw.shape[0], 1)).astype(np.float16)
+            raw[:, 0:2] = d.view(np.uint8)
+            if be == 256:
+                raw[:, 2:4] = d.view(np.uint8)
+            mats.append(kb.QMatrix.from_raw_bytes(dev, (n, k), raw.reshape(-1), ty))
+        for rows in (1, 8, 32):
+            x = dev.tensor(np.random.default_rng(5).standard_normal((rows, k)).astype(np.float32))
+            y = dev.empty((rows, n))
+            for w in mats:
+                x.q_mat_mul(w, out=y)
+            torch.cuda.synchronize()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = max(1, args.gemv_reps)
+            g0.record(stream)
+            for _ in range(reps):
+                for w in mats:
+                    x.q_mat_mul(w, out=y)
+            g1.record(stream)
+            torch.cuda.synchronize()
+            us = g0.elapsed_time(g1) * 1e3 / (reps * len(mats))
+            kbytes = n * k // be * bb + 4 * rows * (n + k)
+            # device time of each kernel of the product (CUPTI, one extra pass over the matrices, not timed above)
+            kern = {}
+            prof = None
+            if args.kernel_table:
+                from torch.profiler import ProfilerActivity, profile
+                with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                    for w in mats:
+                        x.q_mat_mul(w, out=y)
+                    torch.cuda.synchronize()
+            for ev in (prof.key_averages() if prof is not None else []):
+                t = getattr(ev, "device_time_total", None)
+                t = ev.cuda_time_total if t is None else t
+                if t > 0:
+                    kern[ev.key.replace("void ", "").replace("(anonymous namespace)::", "").split("(")[0][:40]] = round(t / len(mats), 2)
+            out.append({"kernel": f"product with {name} weights ({rows} rows) on [{n} x {k}]", "bound": "hbm",
+                        "us_per_launch": us, "bytes_per_launch": kbytes, "achieved": kbytes / us / 1e3, "peak": peak,
+                        "peak_source": which, "unit": "GB/s", "frac": kbytes / us / 1e3 / peak, "device_us_per_kernel": kern})
+        for w in mats:
+            w.free()
+    print(json.dumps({"q5_products": out}), flush=True)
+
+
 def run_attn_decode_only(args):
     """One decode-attention case (batch 32, 4096 cached keys, Llama-3-8B heads: 0.54 GB of fp16 K and V per
     launch, two distinct caches): the small case profiler captures use."""
@@ -860,6 +921,7 @@ def main():
     ap.add_argument("--layers", type=int, default=CFG["n_layer"],
                     help="decoder layers of the model (fewer than 32 only for profiler captures; not a bench value)")
     ap.add_argument("--gemv-only", action="store_true", help="run only the dominant-kernel leg")
+    ap.add_argument("--q5-only", action="store_true", help="time the Q5_K / Q5_0 products at 1, 8 and 32 rows")
     ap.add_argument("--attn-decode-only", action="store_true",
                     help="run only one decode-attention case (batch 32, 4096 keys): the small case of profiler captures")
     ap.add_argument("--prefill-only", action="store_true",
@@ -882,6 +944,8 @@ def main():
         run_sweep(args)
     elif args.gemv_only:
         run_gemv_only(args)
+    elif args.q5_only:
+        run_q5_only(args)
     elif args.attn_decode_only:
         run_attn_decode_only(args)
     elif args.prefill_only:

@@ -102,7 +102,10 @@ FB200_API int fb200_memset(fb200_device* dev, void* dst_dev, int value, size_t b
  * reference panics, cpu/src/quantized.rs:54-69); unknown types give
  * FB200_ERR_UNSUPPORTED_DTYPE (GgufReadError::UnsupportedDType). F32/F16 are accepted as dense.
  * On the device the blocks are stored in a tile-interleaved order (same bytes, permuted) so
- * that warps read them with coalesced 128-bit loads. */
+ * that warps read them with coalesced 128-bit loads. Two types are stored otherwise: Q5_0 as Q8_0
+ * tiles (the same scale, the 5-bit integer widened to 8 bits: the same values, 34 instead of 22
+ * bytes per block of device memory) and Q5_K in the byte order of the file. The type and byte
+ * count reported by fb200_qmatrix_ggml_type / fb200_qmatrix_nbytes are always the file's. */
 FB200_API int fb200_qmatrix_from_raw_bytes(fb200_device* dev, const uint64_t* shape, int rank,
                                  const void* bytes_host, size_t nbytes, uint32_t ggml_type,
                                  fb200_qmatrix** out);
@@ -161,7 +164,7 @@ FB200_API int fb200_rms_norm_q_mat_mul(fb200_device* dev, const float* x_dev,
  * until the process exits); neither this function nor anything it calls allocates or frees
  * device or host memory through the CUDA allocator or the C/C++ heap (refusals write their text
  * into fixed storage inside the handle).
- *   - y[M, N] = x[M, K] . W^T, 1 <= M <= 32, W of type Q4_0 / Q8_0 / Q4_K / Q6_K, no epilogue.
+ *   - y[M, N] = x[M, K] . W^T, 1 <= M <= 32, W of type Q4_0 / Q5_0 / Q8_0 / Q4_K / Q6_K, no epilogue.
  *   - Every row count, M = 1 included, runs the fp16 tensor-core kernel of the 2..32-row path
  *     (11-bit operands, about 5e-4 relative L2 against fp32; fb200_q_mat_mul sends a single row to
  *     its integer-limb kernel instead, which needs no scratch and is closer to fp32).

@@ -10,7 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libfusor_b200.so")
-SOURCES = ["api.cu", "repack.cu", "qgemv.cu", "qgemv1.cu", "dense.cu", "qgemm.cu", "ops.cu", "attention.cu", "attn_prefill.cu", "attn_prefill_tc.cu", "attn_decode_tc.cu",
+SOURCES = ["api.cu", "repack.cu", "qgemv.cu", "qgemv1.cu", "q5gemv.cu", "dense.cu", "qgemm.cu", "ops.cu", "attention.cu", "attn_prefill.cu", "attn_prefill_tc.cu", "attn_decode_tc.cu",
            "fused_step.cu", "llama.cu", "comm.cu", "sampling.cu"]
 HEADERS = ["common.cuh", "formats.cuh", "qgemv_common.cuh", "qgemv1_groups.cuh", "packed_act.cuh",
            "attn_decode.cuh", "attn_mma.cuh", "qgemv1_groups2.cuh", "fused_step.cuh", os.path.join("..", "..", "include", "fusor_b200.h")]

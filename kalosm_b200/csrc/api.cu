@@ -8,6 +8,9 @@
 #include "common.cuh"
 
 size_t fb200_xpack_bytes(int mp, uint64_t kp);
+bool fb200_q5_covers(const fb200_qmatrix* w);
+int fb200_q5_mat_mul(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_t m, float* y, const float* r1,
+                     const float* r2, bool r1_is_bias);
 int fb200_qgemv_chunk(fb200_device* dev, const fb200_qmatrix* w, const float* x, int mc, float* y,
                       int epi, const float* r1, const float* r2, void* scratch, bool r1_is_bias);
 int fb200_dense_matmul(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_t m, float* y);
@@ -271,16 +274,22 @@ int fb200_qmatrix_from_raw_bytes(fb200_device* dev, const uint64_t* shape, int r
   if (n >= (1ull << 31) || k >= (1ull << 31))
     return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "dimension too large");
   fb200_qmatrix* q = new fb200_qmatrix();
-  q->dev = dev; q->type = ggml_type; q->n = n; q->k = k; q->raw_nbytes = nbytes;
+  q->dev = dev; q->type = ggml_type; q->source_type = ggml_type; q->n = n; q->k = k; q->raw_nbytes = nbytes;
+  // Q5_0 is stored as Q8_0 tiles (the same scale, the 5-bit integer widened to 8 bits: identical
+  // values, 34 instead of 22 bytes per block) and takes the Q8_0 kernels
+  const bool widen = ggml_type == FB200_Q5_0;
+  if (widen) q->type = FB200_Q8_0;
   TileGeom g;
   uint8_t* raw_dev = nullptr;
+  uint8_t* wide_dev = nullptr;
   auto cleanup = [&](int code) {
     if (raw_dev) cudaFree(raw_dev);
+    if (wide_dev) cudaFree(wide_dev);
     if (q->data) cudaFree(q->data);
     delete q;
     return code;
   };
-  if (tile_geom(ggml_type, &g)) {
+  if (tile_geom(q->type, &g)) {
     q->tiled = true;
     q->ntiles = (int)((n + 15) / 16);
     q->ngroups = (int)((k + g.group_elems - 1) / g.group_elems);
@@ -292,13 +301,23 @@ int fb200_qmatrix_from_raw_bytes(fb200_device* dev, const uint64_t* shape, int r
         e = cudaMemcpyAsync(raw_dev, bytes_host, nbytes, cudaMemcpyHostToDevice, dev->stream);
       if (e != cudaSuccess)
         return cleanup(fb200_fail(dev, FB200_ERR_CUDA, "QMatrix upload: %s", cudaGetErrorString(e)));
-      rc = fb200_launch_repack(dev, ggml_type, raw_dev, n, k, q->data, q->ntiles, q->ngroups, 0);
+      if (widen) {
+        const uint64_t nblocks = n * (k / 32);
+        e = cudaMalloc(&wide_dev, nblocks * 34 ? nblocks * 34 : 1);
+        if (e != cudaSuccess)
+          return cleanup(fb200_fail(dev, FB200_ERR_CUDA, "QMatrix upload: %s", cudaGetErrorString(e)));
+        rc = fb200_launch_widen_q5_0(dev, raw_dev, nblocks, wide_dev);
+        if (rc) return cleanup(rc);
+      }
+      rc = fb200_launch_repack(dev, q->type, widen ? wide_dev : raw_dev, n, k, q->data, q->ntiles, q->ngroups, 0);
       if (rc) return cleanup(rc);
       e = cudaStreamSynchronize(dev->stream);
       if (e != cudaSuccess)
         return cleanup(fb200_fail(dev, FB200_ERR_CUDA, "QMatrix repack: %s", cudaGetErrorString(e)));
       cudaFree(raw_dev);
       raw_dev = nullptr;
+      if (wide_dev) cudaFree(wide_dev);
+      wide_dev = nullptr;
     }
   } else {
     q->tiled = false;
@@ -336,7 +355,7 @@ int fb200_qmatrix_shape(const fb200_qmatrix* q, uint64_t* n_out, uint64_t* k_out
 
 int fb200_qmatrix_ggml_type(const fb200_qmatrix* q, uint32_t* type_out) {
   if (!q || !type_out) return FB200_ERR_INVALID_ARGUMENT;
-  *type_out = q->type;
+  *type_out = q->source_type;
   return FB200_OK;
 }
 
@@ -364,7 +383,7 @@ int fb200_qmatrix_concat_rows(const fb200_qmatrix* const* ms, int n, fb200_qmatr
   for (int i = 0; i < n; ++i) {
     if (!ms[i] || ms[i]->dev != dev)
       return fb200_fail(dev, FB200_ERR_DEVICE_MISMATCH, "concat_rows: matrices on different devices");
-    if (ms[i]->type != ms[0]->type || ms[i]->k != ms[0]->k || !ms[i]->tiled)
+    if (ms[i]->type != ms[0]->type || ms[i]->source_type != ms[0]->source_type || ms[i]->k != ms[0]->k || !ms[i]->tiled)
       return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "concat_rows: needs one quantised type and one K");
     if (i + 1 < n && ms[i]->n % 16 != 0)
       return fb200_fail(dev, FB200_ERR_INVALID_SHAPE, "concat_rows: N of part %d is not a multiple of 16", i);
@@ -418,8 +437,14 @@ int fb200_q_mat_mul(fb200_device* dev, const float* x_dev, size_t m, const fb200
   fb200_op_trace scope(dev, m == 1 ? "q_mat_mul (1 row)" : m <= 32 ? "q_mat_mul (2..32 rows)" : "q_mat_mul (> 32 rows)",
                        (double)w->raw_nbytes + 4.0 * (double)m * (double)(w->k + w->n));
   if (!w->tiled) {
+    if (fb200_q5_covers(w)) {
+      if (epi == FB200_EPI_SWIGLU)
+        return fb200_fail(dev, FB200_ERR_UNSUPPORTED_DTYPE, "q_mat_mul: no SwiGLU epilogue for Q5_K weights");
+      return fb200_q5_mat_mul(dev, w, x_dev, m, y_dev, epi == FB200_EPI_RESIDUAL ? ep->r1_dev : nullptr,
+                              epi == FB200_EPI_RESIDUAL ? ep->r2_dev : nullptr, bias);
+    }
     if (epi != FB200_EPI_NONE)
-      return fb200_fail(dev, FB200_ERR_UNSUPPORTED_DTYPE, "q_mat_mul: epilogues need Q4_0/Q8_0/Q4_K/Q6_K weights");
+      return fb200_fail(dev, FB200_ERR_UNSUPPORTED_DTYPE, "q_mat_mul: epilogues need quantised weights");
     return fb200_dense_matmul(dev, w, x_dev, m, y_dev);
   }
   if (epi == FB200_EPI_SWIGLU && (w->ntiles % 2 != 0 || w->n % 32 != 0))

@@ -57,7 +57,8 @@ struct fb200_device {
 // Quantised (or dense) weight matrix [N, K] in tile-interleaved device storage.
 struct fb200_qmatrix {
   fb200_device* dev = nullptr;
-  uint32_t type = 0;
+  uint32_t type = 0;         // type of the stored blocks: what the kernels dispatch on
+  uint32_t source_type = 0;  // type of the GGUF bytes the matrix was built from (differs for Q5_0, stored as Q8_0)
   uint64_t n = 0, k = 0;
   uint64_t raw_nbytes = 0;  // size of the GGUF byte stream this matrix was built from
   // tiled storage
@@ -171,6 +172,7 @@ inline bool block_geom(uint32_t type, int* elems, int* bytes) {
 // internal launchers (defined in the .cu files)
 int fb200_launch_repack(fb200_device* dev, uint32_t type, const uint8_t* raw_dev, uint64_t n,
                         uint64_t k, uint8_t* tiled_dev, int ntiles, int ngroups, int tile0);
+int fb200_launch_widen_q5_0(fb200_device* dev, const uint8_t* q5_dev, uint64_t nblocks, uint8_t* q8_dev);
 int fb200_launch_dequantize(fb200_device* dev, const fb200_qmatrix* q, float* out_dev);
 int fb200_launch_dequantize_rows(fb200_device* dev, const fb200_qmatrix* q,
                                  const uint32_t* ids_dev, size_t n_ids, float* out_dev);

@@ -1690,7 +1690,7 @@ extern "C" int fb200_q_mat_mul_noalloc(fb200_device* dev, const float* x_dev, si
     return fb200_fail(dev, FB200_ERR_DEVICE_MISMATCH, "q_mat_mul_noalloc: weight lives on another device handle");
   if (!w->tiled)
     return fb200_fail(dev, FB200_ERR_UNSUPPORTED_DTYPE,
-                      "q_mat_mul_noalloc: only Q4_0, Q8_0, Q4_K and Q6_K weights are supported");
+                      "q_mat_mul_noalloc: only Q4_0, Q5_0, Q8_0, Q4_K and Q6_K weights are supported");
   if (m == 0 || w->n == 0) return FB200_OK;
   if (m > 32)
     return fb200_fail(dev, FB200_ERR_CAPACITY, "q_mat_mul_noalloc: %zu activation rows, at most 32 per call", m);

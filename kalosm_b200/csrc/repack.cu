@@ -25,6 +25,27 @@ __global__ void repack_kernel(uint32_t type, const uint8_t* __restrict__ raw, ui
   tiled[idx] = v;
 }
 
+// Q5_0 blocks {f16 d, u32 qh, qs[16]} -> Q8_0 blocks {f16 d, i8 q[32]} with q = q5 - 16: the same
+// d and the same integers, so (q5 - 16) * d dequantises to the same bits from either form
+// (BlockQ5_0::dequantize / BlockQ8_0::dequantize, fusor-ml/gguf/src/lib.rs:1046-1073, 1284-1288).
+// One thread per output byte.
+__global__ void widen_q5_0_kernel(const uint8_t* __restrict__ q5, uint64_t total, uint8_t* __restrict__ q8) {
+  const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const uint64_t blk = idx / 34;
+  const int o = (int)(idx % 34);
+  const uint8_t* b = q5 + blk * 22;
+  if (o < 2) {
+    q8[idx] = b[o];
+    return;
+  }
+  const int i = o - 2, p = i & 15;
+  const uint32_t qh = (uint32_t)b[2] | ((uint32_t)b[3] << 8) | ((uint32_t)b[4] << 16) | ((uint32_t)b[5] << 24);
+  const int nib = i < 16 ? (b[6 + p] & 0xF) : (b[6 + p] >> 4);
+  const int hi = (qh >> i) & 1;
+  q8[idx] = (uint8_t)(int8_t)((nib | (hi << 4)) - 16);
+}
+
 __global__ void dequant_tiled_kernel(uint32_t type, const uint8_t* __restrict__ tiled, uint64_t n,
                                      uint64_t k, int ngroups, int group_elems, int tg_bytes,
                                      float* __restrict__ out) {
@@ -86,6 +107,14 @@ int fb200_launch_repack(fb200_device* dev, uint32_t type, const uint8_t* raw_dev
   repack_kernel<<<(unsigned)nblk, 256, 0, dev->stream>>>(
       type, raw_dev, n, row_bytes, blocks_per_row, g.block_bytes, g.group_elems / g.block_elems,
       tiled_dev, ngroups, g.tg_bytes, tile0, total);
+  FB_LAUNCH_CHECK(dev);
+  return FB200_OK;
+}
+
+int fb200_launch_widen_q5_0(fb200_device* dev, const uint8_t* q5_dev, uint64_t nblocks, uint8_t* q8_dev) {
+  const uint64_t total = nblocks * 34;
+  if (total == 0) return FB200_OK;
+  widen_q5_0_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(q5_dev, total, q8_dev);
   FB_LAUNCH_CHECK(dev);
   return FB200_OK;
 }

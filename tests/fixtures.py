@@ -130,3 +130,64 @@ def rel_l2(a, b):
     b = np.asarray(b, dtype=np.float64).ravel()
     den = np.linalg.norm(b)
     return float(np.linalg.norm(a - b) / den) if den > 0 else float(np.linalg.norm(a - b))
+
+
+# ---- encoders for the two 5-bit formats -----------------------------------------------------------
+# Only the tests need them (seeded weights with realistic statistics); parity is judged on the
+# bytes they produce, through the oracle's decoder. Round-to-nearest on a min/max grid.
+
+def quantize_q5_0(x):
+    """f32 [..., 32 n] -> Q5_0 bytes: d = (value of largest magnitude) / -16, q = round(x / d) + 16."""
+    xb = np.asarray(x, dtype=np.float32).reshape(-1, 32)
+    idx = np.argmax(np.abs(xb), axis=1)
+    d = (xb[np.arange(xb.shape[0]), idx] / np.float32(-16.0)).astype(np.float16)
+    df = d.astype(np.float32)
+    inv = np.where(df != 0, 1.0 / np.where(df != 0, df, 1), 0).astype(np.float32)
+    q = np.clip(np.floor(xb * inv[:, None] + 16.5), 0, 31).astype(np.uint32)
+    lo, hi = q[:, :16], q[:, 16:]
+    qs = ((lo & 15) | ((hi & 15) << 4)).astype(np.uint8)
+    sh = np.arange(16, dtype=np.uint32)
+    qh = (((lo >> 4) << sh).sum(axis=1) | ((hi >> 4) << (sh + 16)).sum(axis=1)).astype(np.uint32)
+    out = np.empty((xb.shape[0], 22), dtype=np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+    out[:, 2:6] = qh.view(np.uint8).reshape(-1, 4)
+    out[:, 6:] = qs
+    return out.reshape(-1)
+
+
+def quantize_q5k(x):
+    """f32 [..., 256 n] -> Q5_K bytes: per 32-element sub-block a 6-bit (scale, min) pair against the
+    super-block's f16 d / dmin, 5-bit quants; byte layout of BlockQ5K (gguf/src/lib.rs:1819-1861)."""
+    xb = np.asarray(x, dtype=np.float32).reshape(-1, 8, 32)
+    nb = xb.shape[0]
+    mn = np.maximum(-xb.min(axis=2), 0)
+    scale = (xb.max(axis=2) + mn) / np.float32(31.0)
+    d = (scale.max(axis=1) / np.float32(63.0)).astype(np.float16)
+    dmin = (mn.max(axis=1) / np.float32(63.0)).astype(np.float16)
+    df, dmf = d.astype(np.float32), dmin.astype(np.float32)
+    sc = np.clip(np.rint(np.divide(scale, df[:, None], out=np.zeros_like(scale), where=df[:, None] > 0)), 0, 63).astype(np.uint32)
+    m = np.clip(np.rint(np.divide(mn, dmf[:, None], out=np.zeros_like(mn), where=dmf[:, None] > 0)), 0, 63).astype(np.uint32)
+    step = df[:, None] * sc
+    q = np.divide(xb + (dmf[:, None] * m)[:, :, None], step[:, :, None], out=np.zeros_like(xb), where=step[:, :, None] > 0)
+    q = np.clip(np.rint(q), 0, 31).astype(np.uint32)
+    out = np.zeros((nb, 176), dtype=np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+    out[:, 2:4] = dmin.view(np.uint8).reshape(-1, 2)
+    s = np.zeros((nb, 12), dtype=np.uint32)
+    s[:, 0:4] = (sc[:, 0:4] & 63) | ((sc[:, 4:8] >> 4) << 6)
+    s[:, 4:8] = (m[:, 0:4] & 63) | ((m[:, 4:8] >> 4) << 6)
+    s[:, 8:12] = (sc[:, 4:8] & 15) | ((m[:, 4:8] & 15) << 4)
+    out[:, 4:16] = s.astype(np.uint8)
+    qh = np.zeros((nb, 32), dtype=np.uint32)
+    for j in range(8):
+        qh |= (q[:, j, :] >> 4) << j
+    out[:, 16:48] = qh.astype(np.uint8)
+    for c in range(4):
+        out[:, 48 + 32 * c:80 + 32 * c] = ((q[:, 2 * c, :] & 15) | ((q[:, 2 * c + 1, :] & 15) << 4)).astype(np.uint8)
+    return out.reshape(-1)
+
+
+def random_q5_weights(seed, sigma, n, k, ty):
+    """Seeded N(0, sigma) [n, k] weights in Q5_0 / Q5_K bytes."""
+    w = O.normal(seed, sigma, n * k)
+    return quantize_q5_0(w) if ty == O.Q5_0 else quantize_q5k(w)

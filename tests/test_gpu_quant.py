@@ -288,3 +288,71 @@ def test_single_row_large_k_and_tail_tiles(dev):
         y = dev.tensor(x).q_mat_mul(w).as_slice()
         assert F.rel_l2(y, O.q_mat_mul(x, raw, ty, n, k)) < TOL
     assert dev.status() == 0
+
+
+Q5_TYPES = {"q5_0": O.Q5_0, "q5k": O.Q5K}
+
+
+@pytest.mark.parametrize("tname", list(Q5_TYPES))
+@pytest.mark.parametrize("m", [1, 2, 5, 8, 9, 16, 17, 32, 33, 70])
+def test_q5_products(dev, tname, m):
+    # Q5_K stays in GGUF byte order and takes a kernel of its own; Q5_0 is widened to Q8_0 tiles
+    # when the matrix is built (BlockQ5_0 / BlockQ5K, fusor-ml/gguf/src/lib.rs:1046-1073, 1819-1861).
+    # Every row bucket (1, 2..8 / 16 / 32 packed rows, more than 32), N not a multiple of 16, K a
+    # multiple of the block size only; dequantize stays bit-exact and the type reported is the file's
+    ty = Q5_TYPES[tname]
+    n, k = 273, 1024 if ty == O.Q5K else 1056
+    raw = F.random_q5_weights(17, 0.02, n, k, ty)
+    w = kb.QMatrix.from_raw_bytes(dev, (n, k), raw, ty)
+    assert w.ggml_type == ty and w.nbytes == raw.size
+    assert np.array_equal(w.dequantize().as_slice().view(np.uint32),
+                          O.dequantize(raw, ty, n * k).reshape(n, k).view(np.uint32))
+    x = activations(200 + m, m, k) + np.float32(0.75)  # a mean far from zero: the offsets of Q5_K matter
+    y = dev.tensor(x).q_mat_mul(w).as_slice()
+    exp = O.q_mat_mul(x, raw, ty, n, k)
+    assert y.shape == (m, n)
+    assert F.rel_l2(y, exp) < TOL, F.rel_l2(y, exp)
+    assert np.array_equal(y, dev.tensor(x).q_mat_mul(w).as_slice())  # fixed summation order
+    assert dev.status() == 0
+
+
+@pytest.mark.parametrize("tname,n,k", [("q5k", 4096, 4096), ("q5k", 4096, 14336), ("q5_0", 4096, 4096),
+                                        ("q5_0", 1024, 4096)])
+def test_q5_products_llama_shapes(dev, tname, n, k):
+    ty = Q5_TYPES[tname]
+    raw = F.random_q5_weights(n + k, 0.02, n, k, ty)
+    w = kb.QMatrix.from_raw_bytes(dev, (n, k), raw, ty)
+    cols = np.sort(np.random.default_rng(2).choice(n, 128, replace=False))
+    sub = _sampled_columns(raw, ty, n, k, cols)
+    for m in (1, 8, 32):
+        x = activations(300 + m, m, k)
+        y = dev.tensor(x).q_mat_mul(w).as_slice()
+        exp = O.q_mat_mul(x, sub, ty, len(cols), k)
+        assert F.rel_l2(y[:, cols], exp) < TOL, (m, F.rel_l2(y[:, cols], exp))
+
+
+def test_q5_epilogues(dev):
+    # bias and residual rows are added by the product kernel; SwiGLU is refused for Q5_K (Q5_0, stored
+    # as Q8_0 tiles, takes every epilogue of that type)
+    for ty, k in ((O.Q5_0, 512), (O.Q5K, 512)):
+        n = 96
+        raw = F.random_q5_weights(23, 0.02, n, k, ty)
+        w = kb.QMatrix.from_raw_bytes(dev, (n, k), raw, ty)
+        for m in (1, 7, 40):
+            x = activations(400 + m, m, k)
+            exp = O.q_mat_mul(x, raw, ty, n, k)
+            r1, r2 = activations(410 + m, m, n), activations(420 + m, m, n)
+            y = dev.tensor(x).q_mat_mul(w, epilogue=kb.EPI_RESIDUAL, r1=dev.tensor(r1), r2=dev.tensor(r2)).as_slice()
+            assert F.rel_l2(y, (exp + r1) + r2) < TOL
+            bias = activations(430, 1, n)[0]
+            y = dev.tensor(x).q_mat_mul(w, epilogue=kb.EPI_BIAS, r1=dev.tensor(bias)).as_slice()
+            assert F.rel_l2(y, exp + bias[None, :]) < TOL
+        if ty == O.Q5_0:
+            x = activations(440, 3, k)
+            exp = O.q_mat_mul(x, raw, ty, n, k)
+            h = dev.tensor(x).q_mat_mul(w, epilogue=kb.EPI_SWIGLU).as_slice()
+            assert F.rel_l2(h, O.silu_mul(exp[:, :n // 2], exp[:, n // 2:])) < TOL
+            continue
+        with pytest.raises(kb.FusorError) as e:
+            dev.tensor(activations(1, 2, k)).q_mat_mul(w, epilogue=kb.EPI_SWIGLU)
+        assert e.value.code == kb.ERR_UNSUPPORTED_DTYPE
