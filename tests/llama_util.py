@@ -41,10 +41,11 @@ ORACLE_NAMES = {"token_embd": "token_embd", "output": "output", "attn_q": "wq", 
                 "ffn_down": "down"}
 
 
-def build_models(dev, cfg, batch=1, seed=0, want_cpu=True, sigma=0.02, comm=None, tied=False):
+def build_models(dev, cfg, batch=1, seed=0, want_cpu=True, sigma=0.02, comm=None, tied=False, types=None):
     """With `comm` the GPU model is this rank's shard of the same (whole) seeded weights. With
     `tied` the GPU model gets no output head and must fall back to the embedding matrix
-    (models/kalosm-llama/src/raw/mod.rs:480-486), as the oracle does when it has no head."""
+    (models/kalosm-llama/src/raw/mod.rs:480-486), as the oracle does when it has no head.
+    `types` overrides the block type per tensor name (Q5_0 / Q5_K come from the tests' own encoders)."""
     gpu = kb.Llama(dev, n_layer=cfg["n_layer"], hidden=cfg["hidden"], ffn=cfg["ffn"],
                    n_head=cfg["n_head"], n_kv_head=cfg["n_kv_head"], head_dim=cfg["head_dim"],
                    vocab=cfg["vocab"], max_seq_len=cfg["ctx"], max_batch=batch, comm=comm)
@@ -54,7 +55,12 @@ def build_models(dev, cfg, batch=1, seed=0, want_cpu=True, sigma=0.02, comm=None
         cpu = O.Llama(cfg["n_layer"], cfg["hidden"], cfg["ffn"], cfg["n_head"], cfg["n_kv_head"],
                       cfg["head_dim"], cfg["vocab"], cfg["ctx"], batch=batch, kv_f16=True)
     for j, (name, layer, ty, (n, k)) in enumerate(tensor_plan(cfg)):
-        raw = O.random_qweights(seed * 100003 + j, sigma, n * k, ty)
+        ty = (types or {}).get(name, ty)
+        if ty in (O.Q5_0, O.Q5K):
+            import fixtures
+            raw = fixtures.random_q5_weights(seed * 100003 + j, sigma, n, k, ty)
+        else:
+            raw = O.random_qweights(seed * 100003 + j, sigma, n * k, ty)
         if tied and name == "output":
             continue
         part, part_shape = tp.shard(name, raw, ty, (n, k), rank, size)

@@ -38,6 +38,31 @@ def test_prefill_and_decode_logits(dev, batch):
     assert gpu.position == 9 + 6
 
 
+@pytest.mark.parametrize("batch", [1, 3])
+def test_decoder_with_five_bit_weights(dev, batch):
+    # a Q5_K_M-style mix: Q5_K body, Q6_K for attn_v / ffn_down / output, Q5_0 embeddings. Q5_K matrices
+    # stay in file order (their own product kernel, no fused decode step), Q5_0 ones become Q8_0 tiles.
+    cfg = tiny_cfg()
+    types = {"token_embd": O.Q5_0, "attn_q": O.Q5K, "attn_k": O.Q5K, "attn_output": O.Q5K, "ffn_gate": O.Q5K,
+             "ffn_up": O.Q5K}
+    gpu, cpu = build_models(dev, cfg, batch=batch, seed=41, types=types)
+    prompt = np.random.default_rng(42).integers(0, cfg["vocab"], size=(batch, 40), dtype=np.uint32)
+    lg, nxt = gpu.forward(prompt)
+    lo = cpu.forward(prompt)
+    assert F.rel_l2(lg, lo) < 4e-3, F.rel_l2(lg, lo)  # 40 rows: fp16 operands in every product of the chain
+    tok = np.array([O.top_k(lo[b], 1)[0][0] for b in range(batch)], dtype=np.uint32)
+    for step in range(6):
+        lo = cpu.forward(tok[:, None])
+        lg, nxt = gpu.forward(tok[:, None])
+        err = np.max(np.abs(lg - lo))
+        assert F.rel_l2(lg, lo) < 4e-3, (step, F.rel_l2(lg, lo))
+        want = np.array([O.top_k(lo[b], 1)[0][0] for b in range(batch)])
+        decided = _margin(lo) > 4 * err
+        assert np.array_equal(nxt[decided], want[decided])
+        tok = want.astype(np.uint32)
+    assert dev.status() == 0
+
+
 @pytest.mark.parametrize("flagged_rows", [False, True], ids=["grid-barriers", "flagged-rows"])
 def test_greedy_tokens_match_for_32_steps(dev, flagged_rows, monkeypatch):
     monkeypatch.setenv("FB200_FUSED_LL", "1" if flagged_rows else "0")
