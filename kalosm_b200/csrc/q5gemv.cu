@@ -24,6 +24,10 @@
 //
 // Bytes read per launch = the bytes of W + the packed activations (from L2 after the first CTA).
 // The kernel is bound by instruction issue (the integer pipe that unpacks the quants), not by HBM.
+#include <cstdlib>
+#include <cstring>
+
+#include <cuda.h>
 #include <cuda_fp16.h>
 
 #include "qgemv_common.cuh"
@@ -192,8 +196,12 @@ struct Q5KSmem {
 };
 
 // y[m, n] = xscale[m] * sum_k xh[m, k] * W[n, k] (+ r1 + r2) for M <= 8 NT activation rows.
-template <int NT>
-__global__ void __launch_bounds__(Q5K_WARPS * 32, 1) q5k_gemv_kernel(const Q5Args a) {
+// TENSOR: a stage arrives as one box of a 2-D tensor map over W ([N rows] x [row bytes as 32-bit
+// words], box = 44 words x 16 rows; rows beyond N arrive as zeros) instead of 16 row copies: the
+// copy engine takes one request per 2816 bytes instead of one per 176, which is what bounds the
+// kernel otherwise.
+template <int NT, bool TENSOR>
+__global__ void __launch_bounds__(Q5K_WARPS * 32, 1) q5k_gemv_kernel(const Q5Args a, const __grid_constant__ CUtensorMap wmap) {
   using SM = Q5KSmem<NT>;
   constexpr int S = SM::STAGES;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -205,7 +213,7 @@ __global__ void __launch_bounds__(Q5K_WARPS * 32, 1) q5k_gemv_kernel(const Q5Arg
   const uint32_t my_bar = smem_u32(bars + warp * S);
   if (lane == 0) {
 #pragma unroll
-    for (int s = 0; s < S; ++s) mbar_init(my_bar + 8 * s, 16);  // one arrival per copying lane
+    for (int s = 0; s < S; ++s) mbar_init(my_bar + 8 * s, TENSOR ? 1 : 16);  // one arrival per copying lane
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncwarp();
@@ -215,16 +223,25 @@ __global__ void __launch_bounds__(Q5K_WARPS * 32, 1) q5k_gemv_kernel(const Q5Arg
   const int my_tiles = a.ntiles > (int)blockIdx.x ? (a.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
   const int n_items = my_tiles * bw;
   const uint64_t pol = l2_evict_first_policy();
-  auto issue = [&](int i) {  // lanes 0..15: lane = row of the tile (rows beyond N repeat the last row)
+  auto issue = [&](int i) {  // TENSOR: lane 0; else lanes 0..15, lane = row of the tile (rows beyond N repeat the last row)
     const int j = i / bw, kk = i - j * bw;
     const int tile = (int)blockIdx.x + j * (int)gridDim.x;
     const int st = i % S;
-    const uint8_t* src =
-        a.w + (uint64_t)min(tile * 16 + lane, a.N - 1) * a.row_bytes + (size_t)(warp + Q5K_WARPS * kk) * 176;
-    mbar_expect_tx(my_bar + 8 * st, 176);
-    bulk_g2s_stream(smem_u32(my_ring + st * Q5K_STAGE + lane * 176), src, 176, my_bar + 8 * st, pol);
+    if constexpr (TENSOR) {
+      mbar_expect_tx(my_bar + 8 * st, Q5K_STAGE);
+      asm volatile(
+          "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+          ::"r"(smem_u32(my_ring + st * Q5K_STAGE)), "l"(&wmap), "r"((warp + Q5K_WARPS * kk) * 44), "r"(tile * 16),
+            "r"(my_bar + 8 * st), "l"(pol) : "memory");
+    } else {
+      const uint8_t* src =
+          a.w + (uint64_t)min(tile * 16 + lane, a.N - 1) * a.row_bytes + (size_t)(warp + Q5K_WARPS * kk) * 176;
+      mbar_expect_tx(my_bar + 8 * st, 176);
+      bulk_g2s_stream(smem_u32(my_ring + st * Q5K_STAGE + lane * 176), src, 176, my_bar + 8 * st, pol);
+    }
   };
-  if (lane < 16) {
+  const bool copier = TENSOR ? lane == 0 : lane < 16;
+  if (copier) {
     const int pre = n_items < S ? n_items : S;
     for (int i = 0; i < pre; ++i) issue(i);
   }
@@ -253,7 +270,7 @@ __global__ void __launch_bounds__(Q5K_WARPS * 32, 1) q5k_gemv_kernel(const Q5Arg
       const int next_kc0 = kk + 1 < bw ? (warp + Q5K_WARPS * (kk + 1)) * 8 : (item + 1 < n_items ? warp * 8 : -1);
       step_q5k<NT>(xl, chunk_bytes, r, (warp + Q5K_WARPS * kk) * 8, next_kc0, xp, acc);
       __syncwarp();  // every lane has read the stage before it is refilled
-      if (lane < 16 && item + S < n_items) issue(item + S);
+      if (copier && item + S < n_items) issue(item + S);
     }
     float (*rb)[NT * 4][32] = red[j & 1];
 #pragma unroll
@@ -265,17 +282,56 @@ __global__ void __launch_bounds__(Q5K_WARPS * 32, 1) q5k_gemv_kernel(const Q5Arg
   }
 }
 
-template <int NT>
-int launch_q5k(fb200_device* dev, const Q5Args& a) {
+typedef CUresult (*q5_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+q5_encode_fn q5_encoder() {
+  static q5_encode_fn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<q5_encode_fn>(p);
+  }();
+  return fn;
+}
+
+// W as [N][row_bytes / 4] 32-bit words, boxes of 44 words (one block) x 16 rows.
+bool q5_make_map(CUtensorMap* map, const Q5Args& a) {
+  q5_encode_fn enc = q5_encoder();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)(a.row_bytes / 4), (cuuint64_t)a.N};
+  const cuuint64_t strides[1] = {(cuuint64_t)a.row_bytes};
+  const cuuint32_t box[2] = {44, 16};
+  const cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(a.w), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int NT, bool TENSOR>
+int launch_q5k_form(fb200_device* dev, const Q5Args& a, const CUtensorMap& map) {
   static bool attr_set[64] = {};
   if (dev->ordinal < 0 || dev->ordinal >= 64 || !attr_set[dev->ordinal]) {
-    FB_CUDA(dev, cudaFuncSetAttribute(q5k_gemv_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Q5KSmem<NT>::BYTES));
+    FB_CUDA(dev, cudaFuncSetAttribute(q5k_gemv_kernel<NT, TENSOR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Q5KSmem<NT>::BYTES));
     if (dev->ordinal >= 0 && dev->ordinal < 64) attr_set[dev->ordinal] = true;
   }
   const int grid = a.ntiles < dev->sm_count ? a.ntiles : dev->sm_count;
-  q5k_gemv_kernel<NT><<<grid, Q5K_WARPS * 32, Q5KSmem<NT>::BYTES, dev->stream>>>(a);
+  q5k_gemv_kernel<NT, TENSOR><<<grid, Q5K_WARPS * 32, Q5KSmem<NT>::BYTES, dev->stream>>>(a, map);
   FB_LAUNCH_CHECK(dev);
   return FB200_OK;
+}
+
+// FB200_Q5K_TENSOR_TMA=0 keeps the per-row copies (also taken when the driver offers no tensor-map encoder).
+template <int NT>
+int launch_q5k(fb200_device* dev, const Q5Args& a) {
+  static const bool rows_only = getenv("FB200_Q5K_TENSOR_TMA") && getenv("FB200_Q5K_TENSOR_TMA")[0] == '0';
+  CUtensorMap map;
+  if (!rows_only && q5_make_map(&map, a)) return launch_q5k_form<NT, true>(dev, a, map);
+  memset(&map, 0, sizeof(map));
+  return launch_q5k_form<NT, false>(dev, a, map);
 }
 
 int launch_q5(fb200_device* dev, const Q5Args& a, int nt) {
