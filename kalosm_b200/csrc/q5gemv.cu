@@ -8,9 +8,10 @@
 //  * One persistent CTA of 16 warps per SM walks over tiles of 16 consecutive rows of W. The warps
 //    take the 176-byte blocks of those rows in turn (warp w: blocks w, w + 16, ..) and their
 //    partial sums are added in a fixed order in shared memory. Every warp keeps a ring of stages
-//    in shared memory, each stage the same block of the 16 rows, filled by 16 bulk copies
-//    (cp.async.bulk, one per lane) that stay several stages ahead of the arithmetic, across tile
-//    boundaries.
+//    in shared memory, each stage the same block of the 16 rows, fetched as one box of a 2-D
+//    tensor map over W (cp.async.bulk.tensor.2d; 16 separate 176-byte row copies per stage run
+//    into the request rate of the copy engine); the fetches stay several stages ahead of the
+//    arithmetic, across tile boundaries.
 //  * Lane (g = lane / 4, t = lane % 4) expands rows g and g + 8. Of every 32-element sub-block it
 //    takes elements 4t .. 4t+3 and 16+4t .. 16+4t+3: two words 16 bytes apart of the quant field,
 //    whose fifth bits sit at the same bit of four bytes of the high-bit field (one shift).
@@ -211,6 +212,7 @@ __global__ void __launch_bounds__(Q5K_WARPS * 32, 1) q5k_gemv_kernel(const Q5Arg
   const int g = lane >> 2, t = lane & 3;
   uint8_t* my_ring = smem + warp * S * Q5K_STAGE;
   const uint32_t my_bar = smem_u32(bars + warp * S);
+  pdl_launch_dependents();
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < S; ++s) mbar_init(my_bar + 8 * s, TENSOR ? 1 : 16);  // one arrival per copying lane
@@ -245,6 +247,9 @@ __global__ void __launch_bounds__(Q5K_WARPS * 32, 1) q5k_gemv_kernel(const Q5Arg
     const int pre = n_items < S ? n_items : S;
     for (int i = 0; i < pre; ++i) issue(i);
   }
+  // everything above touches only the weights; the packed activations come from the kernel before
+  // this one (launched with programmatic stream serialization: it may still be running)
+  pdl_wait();
   const uint8_t* xl = a.xh + g * 64 + t * 16;
   const int chunk_bytes = a.Mp * 64;
   XPipe<NT> xp;
@@ -319,9 +324,8 @@ int launch_q5k_form(fb200_device* dev, const Q5Args& a, const CUtensorMap& map) 
     if (dev->ordinal >= 0 && dev->ordinal < 64) attr_set[dev->ordinal] = true;
   }
   const int grid = a.ntiles < dev->sm_count ? a.ntiles : dev->sm_count;
-  q5k_gemv_kernel<NT, TENSOR><<<grid, Q5K_WARPS * 32, Q5KSmem<NT>::BYTES, dev->stream>>>(a, map);
-  FB_LAUNCH_CHECK(dev);
-  return FB200_OK;
+  return fb200_launch(dev, q5k_gemv_kernel<NT, TENSOR>, dim3(grid), dim3(Q5K_WARPS * 32), (size_t)Q5KSmem<NT>::BYTES, true,
+                      a, map);
 }
 
 // FB200_Q5K_TENSOR_TMA=0 keeps the per-row copies (also taken when the driver offers no tensor-map encoder).
