@@ -830,19 +830,40 @@ qgemm16_kernel(const GemvArgs a) {
 // once per tile (summed in warp order). Activations are read from L2 once per CTA instead of once
 // per tile-group. Serves matrices of at most W K groups (K <= 4096 for the 256-element block types
 // with 16 warps); longer rows take the streamed kernel above.
-template <int TYPE, int W>
+// Partial tiles of the warps meet in shared memory in the order of the MMA fragments: warp w, slot
+// 4 nt + i, lane -- conflict-free for the writers (consecutive lanes) and for the readers. The warp
+// stride is padded by two floats so that two threads that add different halves of the warps for
+// the same output read different banks.
+template <int NT>
+struct Red16 {
+  static constexpr int OUTS = NT * 8 * 16;   // outputs of one unit and pass
+  static constexpr int WSTRIDE = OUTS + 2;   // floats between the partial tiles of two warps
+  // fragment slot 4 nt + i of lane (g, t) -> activation row m and row r of the 16-row tile
+  __device__ static void where(int v, int& m, int& r) {
+    const int idx = v >> 5, ln = v & 31;
+    m = 8 * (idx >> 2) + 2 * (ln & 3) + (idx & 1);
+    r = (ln >> 2) + 8 * ((idx >> 1) & 1);
+  }
+};
+
+template <int TYPE, int W, int BUDGET_KB = 168>
 struct RingS {
   static constexpr int TG = Ring<TYPE>::TG;
   static constexpr int STRIDE = Ring<TYPE>::STRIDE;
-  static constexpr int FIT = (168 * 1024) / (W * STRIDE);
+  static constexpr int FIT = (BUDGET_KB * 1024) / (W * STRIDE);
   static constexpr int STAGES = FIT > 6 ? 6 : FIT;
   static constexpr int RING_BYTES = W * STAGES * STRIDE;
   static constexpr int BAR_BYTES = W * STAGES * 8;
 };
 
-template <int TYPE, int NT, int W>
+// Shared memory of qgemm16s_kernel: ring, barriers, and the partial tiles of two consecutive units
+// (NP passes each), so that one CTA barrier per unit is enough.
+template <int NP>
+constexpr int gemm16s_budget_kb() { return NP == 2 ? 150 : 168; }
+template <int TYPE, int NT, int W, int NP>
 constexpr int gemm16s_smem_bytes() {
-  return RingS<TYPE, W>::RING_BYTES + RingS<TYPE, W>::BAR_BYTES + 2 * W * NT * 8 * 16 * (int)sizeof(float);
+  using R = RingS<TYPE, W, gemm16s_budget_kb<NP>()>;
+  return R::RING_BYTES + R::BAR_BYTES + 2 * NP * W * Red16<NT>::WSTRIDE * (int)sizeof(float);
 }
 
 // group16 with the activations of the K group already in registers (x[chunk]).
@@ -928,17 +949,21 @@ __device__ __forceinline__ void group16r(const uint8_t* tg, int lane, float (&ac
 template <int TYPE, int NT, int EPI, int W>
 __global__ void __launch_bounds__(W * 32, 1)
 qgemm16s_kernel(const GemvArgs a) {
-  using R = RingS<TYPE, W>;
   constexpr int NP = EPI == 2 ? 2 : 1;
+  using R = RingS<TYPE, W, gemm16s_budget_kb<NP>()>;
+  using RD = Red16<NT>;
   constexpr int S = R::STAGES;
   constexpr int CHUNKS = (TYPE == FB200_Q4_0 || TYPE == FB200_Q8_0) ? 4 : 8;
-  constexpr int OUTS = NT * 8 * 16;  // outputs of one unit and pass
+  constexpr int OUTS = RD::OUTS;
   constexpr int THREADS = W * 32;
+  // threads that share one output (each adds the partial tiles of W / SPLIT warps, then a shuffle tree)
+  constexpr int SPLIT = THREADS > OUTS ? THREADS / OUTS : 1;
+  constexpr int PER = W / SPLIT;
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* ring = smem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + R::RING_BYTES);
-  // [2][W][NT * 8][16]: index 0/1 = unit parity (one pass per unit) or pass (SwiGLU pairs)
-  float (*red)[W][NT * 8][16] = reinterpret_cast<float (*)[W][NT * 8][16]>(smem + R::RING_BYTES + R::BAR_BYTES);
+  // [unit parity][pass][warp][fragment slot x lane (+ pad)]
+  float (*red)[NP][W][RD::WSTRIDE] = reinterpret_cast<float (*)[NP][W][RD::WSTRIDE]>(smem + R::RING_BYTES + R::BAR_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -981,57 +1006,66 @@ qgemm16s_kernel(const GemvArgs a) {
   int item = 0;
   for (int u = q0; u < q1; ++u) {
     const int par = (u - q0) & 1;
+    if (active) {
 #pragma unroll
-    for (int p = 0; p < NP; ++p) {
-      if (!active) continue;
-      float acc[NT][4];
+      for (int p = 0; p < NP; ++p) {
+        float acc[NT][4];
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
-      const int st = item % S;
-      mbar_wait(my_bar + 8 * st, (uint32_t)((item / S) & 1), a.status);
-      group16r<TYPE, NT, CHUNKS>(my_ring + st * R::STRIDE, lane, acc, xr);
-      __syncwarp();  // every lane has consumed the stage before it is refilled
-      if (lane == 0 && item + S < n_items) issue(item + S);
-      ++item;
-      float (*rw)[16] = red[NP == 1 ? par : p][warp];
+          for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+        const int st = item % S;
+        mbar_wait(my_bar + 8 * st, (uint32_t)((item / S) & 1), a.status);
+        group16r<TYPE, NT, CHUNKS>(my_ring + st * R::STRIDE, lane, acc, xr);
+        __syncwarp();  // every lane has consumed the stage before it is refilled
+        if (lane == 0 && item + S < n_items) issue(item + S);
+        ++item;
+        float* rw = red[par][p][warp];
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        rw[8 * nt + 2 * t][g] = acc[nt][0];
-        rw[8 * nt + 2 * t + 1][g] = acc[nt][1];
-        rw[8 * nt + 2 * t][g + 8] = acc[nt][2];
-        rw[8 * nt + 2 * t + 1][g + 8] = acc[nt][3];
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) rw[(nt * 4 + i) * 32 + lane] = acc[nt][i];
       }
     }
+    // One barrier per unit: the buffers of this parity are next written two units from now, behind
+    // the barrier of the unit in between, which every reader of this unit reaches only after reading.
     __syncthreads();
-    // ---- the warps' partial tiles, summed in warp (= K group) order
-    for (int o = threadIdx.x; o < OUTS; o += THREADS) {
-      const int m = o >> 4, r = o & 15;
-      const int n = u * 16 + r;
-      if (m >= a.M || n >= a.n_out) continue;
-      float v[NP];
+    // ---- the warps' partial tiles, summed in a fixed order: PER consecutive warps (= K groups) per
+    // thread, then the SPLIT threads of an output
+    for (int v = threadIdx.x / SPLIT; v < OUTS; v += THREADS / SPLIT) {
+      const int part = threadIdx.x % SPLIT;
+      float val[NP];
 #pragma unroll
       for (int p = 0; p < NP; ++p) {
         float sum = 0.f;
-        for (int w = 0; w < nw; ++w) sum += red[NP == 1 ? par : p][w][m][r];
-        v[p] = sum * a.xscale[m];
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+          const int w = part * PER + i;
+          if (w < nw) sum += red[par][p][w][v];
+        }
+#pragma unroll
+        for (int o = 1; o < SPLIT; o <<= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+        val[p] = sum;
       }
+      int m, r;
+      RD::where(v, m, r);
+      const int n = u * 16 + r;
+      if (part != 0 || m >= a.M || n >= a.n_out) continue;
+      const float xs = a.xscale[m];
       const size_t idx = (size_t)m * a.n_out + n;
       float out;
       if (EPI == 2) {
         // silu(gate) * up, fusor-ml/fusor/src/composite/activations.rs:47-64
-        const float gate = v[0];
-        out = (gate / (1.0f + expf(-gate))) * v[NP - 1];
+        const float gate = val[0] * xs;
+        out = (gate / (1.0f + expf(-gate))) * (val[NP - 1] * xs);
       } else if (EPI == 1) {
-        out = v[0] + a.r1[(size_t)m * a.r1_stride + n];
+        out = val[0] * xs + a.r1[(size_t)m * a.r1_stride + n];
         if (a.r2) out += a.r2[idx];
       } else {
-        out = v[0];
+        out = val[0] * xs;
       }
       a.y[idx] = out;
     }
-    if (NP == 2) __syncthreads();  // both halves of `red` are rewritten by the next unit
   }
 }
 
@@ -1385,7 +1419,7 @@ constexpr int gemm16s_warps(int nt) { return nt == 4 ? 8 : 16; }
 template <int TYPE, int NT, int EPI>
 int launch_one16s(fb200_device* dev, GemvArgs& a) {
   constexpr int W = gemm16s_warps(NT);
-  constexpr int SMEM = gemm16s_smem_bytes<TYPE, NT, W>();
+  constexpr int SMEM = gemm16s_smem_bytes<TYPE, NT, W, EPI == 2 ? 2 : 1>();
   static bool configured[64] = {false};  // per device ordinal
   auto kern = qgemm16s_kernel<TYPE, NT, EPI, W>;
   if (!configured[dev->ordinal & 63]) {
