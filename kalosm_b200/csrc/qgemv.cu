@@ -1315,7 +1315,7 @@ struct RingM {
   static constexpr int STAGES = FIT > 6 ? 6 : FIT;
   static constexpr int RING_BYTES = W * STAGES * STRIDE;
   static constexpr int BAR_BYTES = W * STAGES * 8;
-  static constexpr int SMEM = RING_BYTES + BAR_BYTES + 2 * W * NT * 8 * 16 * (int)sizeof(float);
+  static constexpr int SMEM = RING_BYTES + BAR_BYTES + 2 * W * Red16<NT>::WSTRIDE * (int)sizeof(float);
 };
 
 template <int NT, int W>
@@ -1324,12 +1324,16 @@ qgemm16s_multi_kernel(const GemvArgs a) {
   using R = RingM<NT, W>;
   constexpr int S = R::STAGES;
   constexpr int CHUNKS = 8;
-  constexpr int OUTS = NT * 8 * 16;
+  using RD = Red16<NT>;
+  constexpr int OUTS = RD::OUTS;
   constexpr int THREADS = W * 32;
+  constexpr int SPLIT = THREADS > OUTS ? THREADS / OUTS : 1;  // threads that share one output
+  constexpr int PER = W / SPLIT;
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* ring = smem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + R::RING_BYTES);
-  float (*red)[W][NT * 8][16] = reinterpret_cast<float (*)[W][NT * 8][16]>(smem + R::RING_BYTES + R::BAR_BYTES);
+  // [unit parity][warp][fragment slot x lane (+ pad)]
+  float (*red)[W][RD::WSTRIDE] = reinterpret_cast<float (*)[W][RD::WSTRIDE]>(smem + R::RING_BYTES + R::BAR_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -1391,22 +1395,28 @@ qgemm16s_multi_kernel(const GemvArgs a) {
       else group16r<FB200_Q6_K, NT, CHUNKS>(my_ring + st * R::STRIDE, lane, acc, xr);
       __syncwarp();
       if (lane == 0 && item + S < n_items) issue(item + S);
-      float (*rw)[16] = red[par][warp];
+      float* rw = red[par][warp];
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        rw[8 * nt + 2 * t][g] = acc[nt][0];
-        rw[8 * nt + 2 * t + 1][g] = acc[nt][1];
-        rw[8 * nt + 2 * t][g + 8] = acc[nt][2];
-        rw[8 * nt + 2 * t + 1][g + 8] = acc[nt][3];
-      }
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) rw[(nt * 4 + i) * 32 + lane] = acc[nt][i];
     }
     __syncthreads();
-    for (int o = threadIdx.x; o < OUTS; o += THREADS) {
-      const int m = o >> 4, r = o & 15;
-      const int n = tile * 16 + r;
-      if (m >= a.M || n >= a.seg[sidx].n_out) continue;
+    // PER consecutive warps (= K groups) per thread, then the SPLIT threads of an output: a fixed order
+    for (int v = threadIdx.x / SPLIT; v < OUTS; v += THREADS / SPLIT) {
+      const int part = threadIdx.x % SPLIT;
       float sum = 0.f;
-      for (int w = 0; w < nw; ++w) sum += red[par][w][m][r];
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int w = part * PER + i;
+        if (w < nw) sum += red[par][w][v];
+      }
+#pragma unroll
+      for (int o = 1; o < SPLIT; o <<= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+      int m, r;
+      RD::where(v, m, r);
+      const int n = tile * 16 + r;
+      if (part != 0 || m >= a.M || n >= a.seg[sidx].n_out) continue;
       a.seg[sidx].y[(size_t)m * a.seg[sidx].n_out + n] = sum * a.xscale[m];
     }
   }
