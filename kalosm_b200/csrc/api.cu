@@ -156,6 +156,9 @@ int fb200_device_destroy(fb200_device* dev) {
   if (dev->status) cudaFree(dev->status);
   if (dev->status_host) cudaFreeHost(dev->status_host);
   for (cudaEvent_t e : dev->trace_ev) if (e) cudaEventDestroy(e);
+  for (cudaStream_t st : dev->side_stream) if (st) cudaStreamDestroy(st);
+  for (cudaEvent_t e : dev->join_ev) if (e) cudaEventDestroy(e);
+  if (dev->fork_ev) cudaEventDestroy(dev->fork_ev);
   if (dev->fused) cudaFree(dev->fused);
   if (dev->own_stream) cudaStreamDestroy(dev->stream);
   delete dev;

@@ -18,6 +18,10 @@ struct fb200_device {
   bool own_stream = false;
   int sm_count = 148;
   bool pdl = true;  // launch with programmatic stream serialization (FB200_PDL=0 turns it off)
+  // side streams (created on first use) for independent products that do not fill the GPU one at a
+  // time: forked from `stream` behind fork_ev, joined back through join_ev
+  cudaStream_t side_stream[2] = {nullptr, nullptr};
+  cudaEvent_t fork_ev = nullptr, join_ev[2] = {nullptr, nullptr};
   char err[512] = {0};  // text of the last error; fixed storage, so failing never allocates
   uint64_t launches = 0;
   // scratch for packed activations (fp16 fragments, group sums, row scales); grown on demand

@@ -30,6 +30,7 @@ int fb200_launch_attention(fb200_device* dev, const float* q, const __half* k, c
                            float* part, int nsplit, int bshd);
 size_t fb200_xpack_bytes(int mp, uint64_t kp);
 int fb200_pack16_rows(int mc);
+int fb200_qgemm_group(fb200_device* dev, const fb200_qmatrix* const* ws, float* const* ys, int n, const float* x, size_t m);
 uint64_t fb200_qmatrix_kp(const fb200_qmatrix* w);
 int fb200_pack_x16(fb200_device* dev, const float* x, int mc, uint64_t k, uint64_t kp, void* scratch, const void** xh,
                    const float** xscale);
@@ -565,9 +566,16 @@ int run_forward(fb200_llama* m, int batch, int seq) {
       if (rc) return rc;
     } else {
       if ((rc = fb200_launch_rms_norm_strided(dev, m->x, E, nullptr, L.attn_norm, c.rms_eps, rows, E, m->xn))) return rc;
-      if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wq, m->q, nullptr))) return rc;
-      if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wk, m->k, nullptr))) return rc;
-      if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wv, m->v, nullptr))) return rc;
+      // a prompt pass: the three projections side by side (each alone fills a fraction of the SMs)
+      const fb200_qmatrix* qkv_w[3] = {L.wq, L.wk, L.wv};
+      float* qkv_y[3] = {m->q, m->k, m->v};
+      rc = rows > 32 ? fb200_qgemm_group(dev, qkv_w, qkv_y, 3, m->xn, rows) : 1;
+      if (rc == 1) {
+        if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wq, m->q, nullptr))) return rc;
+        if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wk, m->k, nullptr))) return rc;
+        if ((rc = fb200_q_mat_mul(dev, m->xn, rows, L.wv, m->v, nullptr))) return rc;
+      }
+      if (rc) return rc;
     }
     if (seq == 1 && H / HK <= 8) {
       // one new position per sequence: RoPE(q, k) + fp16 append + split-KV attention in one kernel

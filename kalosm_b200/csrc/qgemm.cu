@@ -505,6 +505,56 @@ int launch_tc(fb200_device* dev, const TcArgs& a, unsigned grid_n, unsigned grid
   return 1;
 }
 
+// Tile shape of one product: NH x 128 weight rows by bm activation rows, and the operand stages that
+// fit. Returns false when no shape fits.
+struct TcShape { int bm = 0, nh = 0, stages = 0; size_t ctas = 0, cost = 0; };
+
+// measured time per unit of tile area relative to the 256 x 256 tile, in 1/64ths
+static const int kRelCost[2][2] = {{134, 87}, {96, 64}};  // [nh - 1][bm == 256]
+
+bool tc_shape(const fb200_qmatrix* w, const TileGeom& geo, size_t m, int swiglu, int bm, int nh, TcShape* out) {
+  const int raw_stride = (geo.tg_bytes + 127) & ~127;
+  const int stage = nh * A_HALF + bm * BK * 2;
+  const int stages = std::min(MAX_STAGES, (SMEM_BUDGET - TAIL_BYTES - 2 * 8 * nh * raw_stride) / stage);
+  if (stages < 2) return false;
+  const size_t n_rows = swiglu ? w->n / 2 : w->n;  // weight rows along the grid
+  const size_t rows_per_cta = swiglu ? BN : BN * nh;
+  out->bm = bm; out->nh = nh; out->stages = stages;
+  out->ctas = ((n_rows + rows_per_cta - 1) / rows_per_cta) * ((m + bm - 1) / bm);
+  out->cost = (size_t)(nh * bm) * kRelCost[nh - 1][bm == 256];  // time of one CTA
+  return true;
+}
+
+bool tc_covers(const fb200_qmatrix* w, const float* x, size_t m, TileGeom* geo) {
+  static const bool enabled = !(getenv("FB200_TCGEN05") && getenv("FB200_TCGEN05")[0] == '0');
+  if (!enabled || !w->tiled || !tile_geom(w->type, geo)) return false;
+  const size_t kp = (size_t)w->ngroups * geo->group_elems;
+  if (kp != w->k || m > (1u << 20)) return false;  // K is a whole number of K groups
+  return (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+}
+
+// Launches the product of packed rows (xh, xscale: pack_rows16_kernel with this bm) on dev->stream.
+int tc_launch(fb200_device* dev, const fb200_qmatrix* w, const TileGeom& geo, const TcShape& sh, const __half* xh,
+              const float* xscale, size_t m, float* y, bool r1_is_bias, const float* r1, const float* r2, int swiglu) {
+  const int bm = sh.bm, nh = sh.nh;
+  const int raw_stride = (geo.tg_bytes + 127) & ~127;
+  const int mp = (int)((m + bm - 1) / bm) * bm;
+  TcArgs a;
+  a.w = w->data; a.xh = xh; a.xscale = xscale; a.y = y; a.r1 = r1; a.r2 = r2;
+  a.r1_stride = r1_is_bias ? 0 : (int)w->n;
+  a.M = (int)m; a.N = (int)w->n; a.K = (int)w->k;
+  a.ngroups = w->ngroups; a.ntiles = w->ntiles; a.type = (int)w->type; a.tgb = geo.tg_bytes;
+  a.group_elems = geo.group_elems; a.status = dev->status;
+  a.stages = sh.stages; a.raw_stride = raw_stride;
+  a.pair_tiles = swiglu ? w->ntiles / 2 : 0;
+  const int smem = sh.stages * (nh * A_HALF + bm * BK * 2) + 2 * 8 * nh * raw_stride + TAIL_BYTES;
+  const size_t n_rows = swiglu ? w->n / 2 : w->n;
+  const size_t rows_per_cta = swiglu ? BN : BN * nh;
+  const unsigned gn = (unsigned)((n_rows + rows_per_cta - 1) / rows_per_cta), gm = (unsigned)(mp / bm);
+  if (nh == 2) return bm == 256 ? launch_tc<256, 2>(dev, a, gn, gm, smem) : launch_tc<128, 2>(dev, a, gn, gm, smem);
+  return bm == 256 ? launch_tc<256, 1>(dev, a, gn, gm, smem) : launch_tc<128, 1>(dev, a, gn, gm, smem);
+}
+
 }  // namespace
 
 // y[M, N] = x[M, K] . W^T (+ r1 + r2) for M > 32; with `swiglu`, W stacks gate rows over up rows
@@ -512,54 +562,98 @@ int launch_tc(fb200_device* dev, const TcArgs& a, unsigned grid_n, unsigned grid
 // caller falls back to the small-batch kernel in chunks of 32 rows).
 int fb200_qgemm(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_t m, float* y, bool r1_is_bias, const float* r1,
                 const float* r2, int swiglu) {
-  static const bool enabled = !(getenv("FB200_TCGEN05") && getenv("FB200_TCGEN05")[0] == '0');
   TileGeom geo;
-  if (!enabled || !w->tiled || !tile_geom(w->type, &geo)) return 1;
-  const size_t kp = (size_t)w->ngroups * geo.group_elems;
-  if (kp != w->k || m > (1u << 20)) return 1;  // K is a whole number of K groups
-  if (reinterpret_cast<uintptr_t>(x) & 15) return 1;
-  // CTA tile: NH x 128 weight rows by bm activation rows. Cost model: waves x tile area; among
-  // equals the larger tile (fewer re-reads of the activations through L2).
-  const int raw_stride = (geo.tg_bytes + 127) & ~127;
-  int best_bm = 0, best_nh = 0, best_stages = 0;
-  size_t best_cost = ~(size_t)0;
+  if (!tc_covers(w, x, m, &geo)) return 1;
+  // CTA tile: cost model waves x time of one CTA; among equals the larger tile (fewer re-reads of
+  // the activations through L2).
   int force_bm = 0, force_nh = 0;
   if (const char* cfg = getenv("FB200_TC_TILE")) sscanf(cfg, "%d,%d", &force_bm, &force_nh);
-  // measured time per unit of tile area relative to the 256 x 256 tile, in 1/64ths
-  static const int rel_cost[2][2] = {{134, 87}, {96, 64}};  // [nh - 1][bm == 256]
-  const size_t n_rows = swiglu ? w->n / 2 : w->n;  // weight rows along the grid
+  TcShape best;
+  size_t best_cost = ~(size_t)0;
   for (int nh = 2; nh >= (swiglu ? 2 : 1); --nh)
     for (int bm = 256; bm >= 128; bm -= 128) {
       if ((force_bm && bm != force_bm) || (force_nh && nh != force_nh && !swiglu)) continue;
-      const int stage = nh * A_HALF + bm * BK * 2;
-      const int stages = std::min(MAX_STAGES, (SMEM_BUDGET - TAIL_BYTES - 2 * 8 * nh * raw_stride) / stage);
-      if (stages < 2) continue;
-      const size_t rows_per_cta = swiglu ? BN : BN * nh;
-      const size_t ctas = ((n_rows + rows_per_cta - 1) / rows_per_cta) * ((m + bm - 1) / bm);
-      const size_t cost = ((ctas + dev->sm_count - 1) / dev->sm_count) * (size_t)(nh * bm) * rel_cost[nh - 1][bm == 256];
-      if (cost < best_cost) { best_cost = cost; best_bm = bm; best_nh = nh; best_stages = stages; }
+      TcShape sh;
+      if (!tc_shape(w, geo, m, swiglu, bm, nh, &sh)) continue;
+      const size_t cost = ((sh.ctas + dev->sm_count - 1) / dev->sm_count) * sh.cost;
+      if (cost < best_cost) { best_cost = cost; best = sh; }
     }
-  if (!best_bm) return 1;
-  const int bm = best_bm, nh = best_nh;
-  const int mp = (int)((m + bm - 1) / bm) * bm;
+  if (!best.bm) return 1;
+  const int mp = (int)((m + best.bm - 1) / best.bm) * best.bm;
   const size_t xbytes = (size_t)mp * w->k * 2, need = xbytes + (size_t)mp * sizeof(float);
   int rc = fb200_ensure(dev, &dev->xpack, &dev->xpack_bytes, need);
   if (rc) return rc;
   __half* xh = reinterpret_cast<__half*>(dev->xpack);
   float* xscale = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(dev->xpack) + xbytes);
-  pack_rows16_kernel<<<mp / 8, 256, 0, dev->stream>>>(x, (int)m, (int)w->k, bm, xh, xscale);
+  pack_rows16_kernel<<<mp / 8, 256, 0, dev->stream>>>(x, (int)m, (int)w->k, best.bm, xh, xscale);
   FB_LAUNCH_CHECK(dev);
-  TcArgs a;
-  a.w = w->data; a.xh = xh; a.xscale = xscale; a.y = y; a.r1 = r1; a.r2 = r2;
-  a.r1_stride = r1_is_bias ? 0 : (int)w->n;
-  a.M = (int)m; a.N = (int)w->n; a.K = (int)w->k;
-  a.ngroups = w->ngroups; a.ntiles = w->ntiles; a.type = (int)w->type; a.tgb = geo.tg_bytes;
-  a.group_elems = geo.group_elems; a.status = dev->status;
-  a.stages = best_stages; a.raw_stride = raw_stride;
-  a.pair_tiles = swiglu ? w->ntiles / 2 : 0;
-  const int smem = best_stages * (nh * A_HALF + bm * BK * 2) + 2 * 8 * nh * raw_stride + TAIL_BYTES;
-  const size_t rows_per_cta = swiglu ? BN : BN * nh;
-  const unsigned gn = (unsigned)((n_rows + rows_per_cta - 1) / rows_per_cta), gm = (unsigned)(mp / bm);
-  if (nh == 2) return bm == 256 ? launch_tc<256, 2>(dev, a, gn, gm, smem) : launch_tc<128, 2>(dev, a, gn, gm, smem);
-  return bm == 256 ? launch_tc<256, 1>(dev, a, gn, gm, smem) : launch_tc<128, 1>(dev, a, gn, gm, smem);
+  return tc_launch(dev, w, geo, best, xh, xscale, m, y, r1_is_bias, r1, r2, swiglu);
+}
+
+// Up to three products of the same rows (the q, k and v projections of a prompt pass):
+// ys[i][M, N_i] = x[M, K] . W_i^T. One of them alone leaves most SMs idle (a 1024-row matrix at
+// 512 rows is 16..32 CTA tiles, each walking the whole K), so the rows are packed once and the
+// products run side by side: the first on the handle's stream, the others on side streams forked
+// behind the packing kernel and joined again before the call returns to the stream. Returns 1 when
+// the shapes are not covered (the caller issues the products one after the other).
+int fb200_qgemm_group(fb200_device* dev, const fb200_qmatrix* const* ws, float* const* ys, int n, const float* x, size_t m) {
+  static const bool off = getenv("FB200_TC_GROUP") && getenv("FB200_TC_GROUP")[0] == '0';
+  if (off || n < 2 || n > 3 || m <= 32 || getenv("FB200_TC_TILE")) return 1;
+  TileGeom geo[3];
+  for (int i = 0; i < n; ++i)
+    if (!ws[i] || !tc_covers(ws[i], x, m, &geo[i]) || ws[i]->k != ws[0]->k) return 1;
+  // one bm for all (they share the packed rows), nh per matrix; cost = waves of all CTAs together x
+  // the time of the slowest CTA
+  TcShape best[3];
+  size_t best_cost = ~(size_t)0;
+  for (int bm = 256; bm >= 128; bm -= 128)
+    for (int mask = 0; mask < (1 << n); ++mask) {
+      TcShape sh[3];
+      size_t ctas = 0, slowest = 0;
+      bool ok = true;
+      for (int i = 0; i < n && ok; ++i) {
+        ok = tc_shape(ws[i], geo[i], m, 0, bm, (mask >> i) & 1 ? 2 : 1, &sh[i]);
+        if (ok) { ctas += sh[i].ctas; slowest = std::max(slowest, sh[i].cost); }
+      }
+      if (!ok) continue;
+      const size_t cost = ((ctas + dev->sm_count - 1) / dev->sm_count) * slowest;
+      if (cost < best_cost) { best_cost = cost; for (int i = 0; i < n; ++i) best[i] = sh[i]; }
+    }
+  if (best_cost == ~(size_t)0) return 1;
+  for (int i = 0; i < n - 1; ++i) {
+    if (!dev->side_stream[i]) FB_CUDA(dev, cudaStreamCreateWithFlags(&dev->side_stream[i], cudaStreamNonBlocking));
+    if (!dev->join_ev[i]) FB_CUDA(dev, cudaEventCreateWithFlags(&dev->join_ev[i], cudaEventDisableTiming));
+  }
+  if (!dev->fork_ev) FB_CUDA(dev, cudaEventCreateWithFlags(&dev->fork_ev, cudaEventDisableTiming));
+  const int bm = best[0].bm;
+  const int mp = (int)((m + bm - 1) / bm) * bm;
+  const size_t xbytes = (size_t)mp * ws[0]->k * 2, need = xbytes + (size_t)mp * sizeof(float);
+  int rc = fb200_ensure(dev, &dev->xpack, &dev->xpack_bytes, need);
+  if (rc) return rc;
+  __half* xh = reinterpret_cast<__half*>(dev->xpack);
+  float* xscale = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(dev->xpack) + xbytes);
+  pack_rows16_kernel<<<mp / 8, 256, 0, dev->stream>>>(x, (int)m, (int)ws[0]->k, bm, xh, xscale);
+  FB_LAUNCH_CHECK(dev);
+  FB_CUDA(dev, cudaEventRecord(dev->fork_ev, dev->stream));
+  cudaStream_t main_stream = dev->stream;
+  // the largest product stays on the handle's stream
+  int first = 0;
+  for (int i = 1; i < n; ++i) if (best[i].ctas > best[first].ctas) first = i;
+  int side = 0;
+  for (int i = 0; i < n && !rc; ++i) {
+    if (i == first) continue;
+    cudaStream_t st = dev->side_stream[side];
+    FB_CUDA(dev, cudaStreamWaitEvent(st, dev->fork_ev, 0));
+    dev->stream = st;  // the launch helpers take the handle's stream
+    rc = tc_launch(dev, ws[i], geo[i], best[i], xh, xscale, m, ys[i], false, nullptr, nullptr, 0);
+    dev->stream = main_stream;
+    if (!rc) {
+      FB_CUDA(dev, cudaEventRecord(dev->join_ev[side], st));
+      ++side;
+    }
+  }
+  if (!rc) rc = tc_launch(dev, ws[first], geo[first], best[first], xh, xscale, m, ys[first], false, nullptr, nullptr, 0);
+  // join whatever was forked, also after a failed launch: the stream must not run ahead of its side streams
+  for (int j = 0; j < side; ++j) FB_CUDA(dev, cudaStreamWaitEvent(main_stream, dev->join_ev[j], 0));
+  return rc;
 }

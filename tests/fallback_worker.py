@@ -48,11 +48,11 @@ def attention(dev, cases):
         print(f"ok attention b{b} h{h}/{hkv} q{sq} kv{skv} d{d}: {err:.1e}")
 
 
-def decoder(dev, batch):
+def decoder(dev, batch, prompt_len=9):
     """Prompt pass and six steps of a two-layer decoder at `batch` sequences."""
     cfg = tiny_cfg()
     gpu, cpu = build_models(dev, cfg, batch=batch, seed=31)
-    prompt = np.random.default_rng(32).integers(0, cfg["vocab"], size=(batch, 9), dtype=np.uint32)
+    prompt = np.random.default_rng(32).integers(0, cfg["vocab"], size=(batch, prompt_len), dtype=np.uint32)
     lg, nxt = gpu.forward(prompt)
     lo = cpu.forward(prompt)
     assert F.rel_l2(lg, lo) < 8e-3
@@ -80,6 +80,8 @@ def main(what):
     elif what == "prefill_mma":     # FB200_ATTN_TCGEN05=0: prompt attention on the mma.sync kernel
         attention(dev, [(1, 8, 2, 128, 128, 128, True), (1, 8, 8, 200, 200, 128, True),
                         (2, 4, 2, 64, 320, 128, False)])
+    elif what == "prefill_sequential":  # FB200_TC_GROUP=0: q, k, v of a prompt pass one after the other
+        decoder(dev, 1, prompt_len=48)
     else:
         raise SystemExit(f"unknown case {what}")
     assert dev.status() == 0

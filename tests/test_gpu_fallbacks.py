@@ -18,6 +18,7 @@ WORKER = os.path.join(os.path.dirname(os.path.abspath(__file__)), "fallback_work
     ("exact_small", "FB200_EXACT_SMALL_BATCH", "1"),
     ("decode_scalar", "FB200_ATTN_DECODE_TC", "0"),
     ("prefill_mma", "FB200_ATTN_TCGEN05", "0"),
+    ("prefill_sequential", "FB200_TC_GROUP", "0"),
 ])
 def test_alternative_kernel(what, var, value):
     out = subprocess.run([sys.executable, WORKER, what], env=dict(os.environ, **{var: value}),
