@@ -443,43 +443,56 @@ qgemm_tc_kernel(const TcArgs a) {
 // x[M, K] f32 -> fp16 scaled by a power of two per row into (-64, 64), stored as [Mp / bm][K / 64]
 // tiles of bm rows x 64 values in the operand layout of the MMA (8 rows x 16 bytes per core
 // matrix, core matrices adjacent in K 128 bytes apart, 8-row groups 1024 bytes apart), so that a
-// tile is one contiguous bulk copy. One CTA per 8 rows; rows >= M are zero.
+// tile is one contiguous bulk copy. One CTA per PACK_ROWS rows (512 rows give 128 CTAs); two warps
+// find the maximum of a row with independent 16-byte loads; rows >= M are zero.
+constexpr int PACK_ROWS = 4;
 __global__ void __launch_bounds__(256)
 pack_rows16_kernel(const float* __restrict__ x, int M, int K, int bm, __half* __restrict__ xh, float* __restrict__ xscale) {
-  __shared__ float inv_s[8];
-  const int m0 = blockIdx.x * 8, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __shared__ float part[8];
+  __shared__ float inv_s[PACK_ROWS];
+  const int m0 = blockIdx.x * PACK_ROWS, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   {
-    const int m = m0 + warp;
+    const int row = warp % PACK_ROWS, half = warp / PACK_ROWS;  // 8 warps: two per row, half of K each
+    const int m = m0 + row;
     float amax = 0.f;
     if (m < M) {
-      const float* xr = x + (size_t)m * K;
-      for (int k = lane; k < K; k += 32) amax = fmaxf(amax, fabsf(xr[k]));
+      const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * K) + (size_t)half * (K / 8);
+      const int n4 = K / 8;  // float4 per half row (K is a multiple of 64)
+#pragma unroll 8
+      for (int i = lane; i < n4; i += 32) {
+        const float4 v = __ldg(xr + i);
+        amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+      }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-    if (lane == 0) {
-      int ex = 0;
-      if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &ex);
-      inv_s[warp] = ldexpf(64.0f, -ex);
-      xscale[m] = ldexpf(1.0f, ex - 6);
-    }
+    if (lane == 0) part[warp] = amax;
+  }
+  __syncthreads();
+  if (threadIdx.x < PACK_ROWS) {
+    const float amax = fmaxf(part[threadIdx.x], part[threadIdx.x + PACK_ROWS]);
+    int ex = 0;
+    if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &ex);
+    inv_s[threadIdx.x] = ldexpf(64.0f, -ex);
+    xscale[m0 + threadIdx.x] = ldexpf(1.0f, ex - 6);
   }
   __syncthreads();
   const int nkb = K / BK;
-  uint8_t* tile_row = reinterpret_cast<uint8_t*>(xh) + (size_t)(m0 / bm) * nkb * ((size_t)bm * BK * 2) + ((m0 % bm) >> 3) * CORE_SBO;
-  for (int q = threadIdx.x; q < K; q += 256) {  // K / 8 chunks of 8 values x 8 rows
-    const int r7 = q & 7, kc = q >> 3, m = m0 + r7;
+  uint8_t* tile_row = reinterpret_cast<uint8_t*>(xh) + (size_t)(m0 / bm) * nkb * ((size_t)bm * BK * 2) +
+                      ((m0 % bm) >> 3) * CORE_SBO + (m0 & 7) * 16;
+  for (int q = threadIdx.x; q < K / 8 * PACK_ROWS; q += 256) {  // K / 8 chunks of 8 values x PACK_ROWS rows
+    const int r = q % PACK_ROWS, kc = q / PACK_ROWS, m = m0 + r;
     uint4 out = make_uint4(0u, 0u, 0u, 0u);
     if (m < M) {
       const float4* src = reinterpret_cast<const float4*>(x + (size_t)m * K + 8 * kc);
-      const float4 lo = src[0], hi = src[1];
-      const float inv = inv_s[r7];
+      const float4 lo = __ldg(src), hi = __ldg(src + 1);
+      const float inv = inv_s[r];
       out.x = h2u(__floats2half2_rn(lo.x * inv, lo.y * inv));
       out.y = h2u(__floats2half2_rn(lo.z * inv, lo.w * inv));
       out.z = h2u(__floats2half2_rn(hi.x * inv, hi.y * inv));
       out.w = h2u(__floats2half2_rn(hi.z * inv, hi.w * inv));
     }
-    *reinterpret_cast<uint4*>(tile_row + (size_t)(kc >> 3) * ((size_t)bm * BK * 2) + (kc & 7) * CORE_LBO + r7 * 16) = out;
+    *reinterpret_cast<uint4*>(tile_row + (size_t)(kc >> 3) * ((size_t)bm * BK * 2) + (kc & 7) * CORE_LBO + r * 16) = out;
   }
 }
 
@@ -585,7 +598,7 @@ int fb200_qgemm(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_
   if (rc) return rc;
   __half* xh = reinterpret_cast<__half*>(dev->xpack);
   float* xscale = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(dev->xpack) + xbytes);
-  pack_rows16_kernel<<<mp / 8, 256, 0, dev->stream>>>(x, (int)m, (int)w->k, best.bm, xh, xscale);
+  pack_rows16_kernel<<<mp / PACK_ROWS, 256, 0, dev->stream>>>(x, (int)m, (int)w->k, best.bm, xh, xscale);
   FB_LAUNCH_CHECK(dev);
   return tc_launch(dev, w, geo, best, xh, xscale, m, y, r1_is_bias, r1, r2, swiglu);
 }
@@ -632,7 +645,7 @@ int fb200_qgemm_group(fb200_device* dev, const fb200_qmatrix* const* ws, float* 
   if (rc) return rc;
   __half* xh = reinterpret_cast<__half*>(dev->xpack);
   float* xscale = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(dev->xpack) + xbytes);
-  pack_rows16_kernel<<<mp / 8, 256, 0, dev->stream>>>(x, (int)m, (int)ws[0]->k, bm, xh, xscale);
+  pack_rows16_kernel<<<mp / PACK_ROWS, 256, 0, dev->stream>>>(x, (int)m, (int)ws[0]->k, bm, xh, xscale);
   FB_LAUNCH_CHECK(dev);
   FB_CUDA(dev, cudaEventRecord(dev->fork_ev, dev->stream));
   cudaStream_t main_stream = dev->stream;
