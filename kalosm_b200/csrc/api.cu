@@ -153,6 +153,7 @@ int fb200_device_destroy(fb200_device* dev) {
   if (dev->argmax_part) cudaFree(dev->argmax_part);
   if (dev->stage) cudaFree(dev->stage);
   if (dev->normed) cudaFree(dev->normed);
+  if (dev->splitk) cudaFree(dev->splitk);
   if (dev->status) cudaFree(dev->status);
   if (dev->status_host) cudaFreeHost(dev->status_host);
   for (cudaEvent_t e : dev->trace_ev) if (e) cudaEventDestroy(e);

@@ -27,6 +27,9 @@ struct fb200_device {
   // scratch for packed activations (fp16 fragments, group sums, row scales); grown on demand
   void* xpack = nullptr;
   size_t xpack_bytes = 0;
+  // partial products of a split-K prefill product
+  void* splitk = nullptr;
+  size_t splitk_bytes = 0;
   // normalised activations of rms_norm_q_mat_mul when the fused kernel does not apply
   void* normed = nullptr;
   size_t normed_bytes = 0;

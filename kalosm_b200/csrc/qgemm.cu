@@ -76,6 +76,8 @@ struct TcArgs {
   int stages, raw_stride;  // operand stages that fit beside the raw buffers; bytes per raw tile-group slot
   int pair_tiles;          // SwiGLU (NH = 2): half 0 = gate rows, half 1 = up rows pair_tiles row-tiles further;
                            // y[M, N / 2] = silu(gate) * up. 0 = plain product
+  int kg_per;              // K groups per split (grid.z splits; = ngroups without split-K). Split z covers the
+                           // K groups z kg_per .. and writes its partial product to y + z M N (no residuals)
   int* status;
 };
 
@@ -292,7 +294,11 @@ qgemm_tc_kernel(const TcArgs a) {
   auto tile_of = [&](int i) { return a.pair_tiles ? tile0 + (i & 7) + (i >> 3) * a.pair_tiles : tile0 + i; };
   auto has_tile = [&](int i) { return a.pair_tiles ? tile0 + (i & 7) < a.pair_tiles : tile0 + i < a.ntiles; };
   constexpr int blocks_per_group = (TYPE == FB200_Q4_K || TYPE == FB200_Q6_K ? 256 : 128) / BK;
-  const int nblocks = a.ngroups * blocks_per_group;
+  // this CTA's K groups: kg0 .. kg0 + ngr - 1 (all of them without split-K); the loops below count
+  // from 0 (barrier phases), only addresses use kg0
+  const int kg0 = (int)blockIdx.z * a.kg_per;
+  const int ngr = min(a.kg_per, a.ngroups - kg0);
+  const int nblocks = ngr * blocks_per_group;
 
   if (warp < T::DQ_WARPS) {
     // ---- conversion: warp w turns row-tile w of each K block into fp16 operand rows
@@ -300,7 +306,7 @@ qgemm_tc_kernel(const TcArgs a) {
     uint8_t* const a_rows = opnd + (warp >> 3) * A_HALF;
     int s = 0, round = 0;
     bool alive = true;
-    for (int kg = 0; kg < a.ngroups && alive; ++kg) {
+    for (int kg = 0; kg < ngr && alive; ++kg) {
       const int rb = kg & 1;
       alive = tc_wait(bar_raw_full + 8 * rb, (uint32_t)((kg >> 1) & 1), dead, a.status);
       if (!alive) break;
@@ -330,20 +336,20 @@ qgemm_tc_kernel(const TcArgs a) {
     if (lane == 0) {
       int ntile_here = 0;
       for (int i = 0; i < T::DQ_WARPS; ++i) ntile_here += has_tile(i) ? 1 : 0;
-      for (int kg = 0; kg < a.ngroups; ++kg) {
+      for (int kg = 0; kg < ngr; ++kg) {
         const int rb = kg & 1;
         if (kg >= 2 && !tc_wait(bar_raw_free + 8 * rb, (uint32_t)(((kg >> 1) - 1) & 1), dead, a.status)) break;
         mbar_expect_tx(bar_raw_full + 8 * rb, (uint32_t)(ntile_here * a.tgb));
         for (int i = 0; i < T::DQ_WARPS; ++i)
           if (has_tile(i))
-            bulk_g2s(smem_u32(raw + rb * raw_bytes + i * a.raw_stride), a.w + ((size_t)tile_of(i) * a.ngroups + kg) * a.tgb,
-                     (uint32_t)a.tgb, bar_raw_full + 8 * rb);
+            bulk_g2s(smem_u32(raw + rb * raw_bytes + i * a.raw_stride),
+                     a.w + ((size_t)tile_of(i) * a.ngroups + kg0 + kg) * a.tgb, (uint32_t)a.tgb, bar_raw_full + 8 * rb);
       }
     }
   } else if (warp == T::DQ_WARPS + 1) {
     // ---- activation loader: one bulk copy per K block (the tile is stored in operand layout)
     if (lane == 0) {
-      const __half* src = a.xh + (size_t)blockIdx.y * nblocks * (BM * BK);
+      const __half* src = a.xh + ((size_t)blockIdx.y * a.ngroups + kg0) * blocks_per_group * (BM * BK);
       int s = 0, round = 0;
       for (int blk = 0; blk < nblocks; ++blk) {
         if (round > 0 && !tc_wait(bar_free + 8 * s, (uint32_t)((round - 1) & 1), dead, a.status)) break;
@@ -429,7 +435,7 @@ qgemm_tc_kernel(const TcArgs a) {
           float out = __uint_as_float(v[j]) * a.xscale[m];
           if (a.r1) out += a.r1[(size_t)m * a.r1_stride + n];
           if (a.r2) out += a.r2[idx];
-          a.y[idx] = out;
+          a.y[(size_t)blockIdx.z * a.M * a.N + idx] = out;
         }
       }
     }
@@ -497,30 +503,30 @@ pack_rows16_kernel(const float* __restrict__ x, int M, int K, int bm, __half* __
 }
 
 template <int BM, int NH, int TYPE>
-int launch_tc_type(fb200_device* dev, const TcArgs& a, unsigned grid_n, unsigned grid_m, int smem) {
+int launch_tc_type(fb200_device* dev, const TcArgs& a, unsigned grid_n, unsigned grid_m, unsigned grid_z, int smem) {
   using T = Tc<BM, NH>;
   static bool configured[64] = {false};
   if (!configured[dev->ordinal & 63]) {
     FB_CUDA(dev, cudaFuncSetAttribute(qgemm_tc_kernel<BM, NH, TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET));
     configured[dev->ordinal & 63] = true;
   }
-  return fb200_launch(dev, qgemm_tc_kernel<BM, NH, TYPE>, dim3(grid_n, grid_m), dim3(T::THREADS), (size_t)smem, false, a);
+  return fb200_launch(dev, qgemm_tc_kernel<BM, NH, TYPE>, dim3(grid_n, grid_m, grid_z), dim3(T::THREADS), (size_t)smem, false, a);
 }
 
 template <int BM, int NH>
-int launch_tc(fb200_device* dev, const TcArgs& a, unsigned grid_n, unsigned grid_m, int smem) {
+int launch_tc(fb200_device* dev, const TcArgs& a, unsigned grid_n, unsigned grid_m, unsigned grid_z, int smem) {
   switch (a.type) {
-    case FB200_Q4_0: return launch_tc_type<BM, NH, FB200_Q4_0>(dev, a, grid_n, grid_m, smem);
-    case FB200_Q8_0: return launch_tc_type<BM, NH, FB200_Q8_0>(dev, a, grid_n, grid_m, smem);
-    case FB200_Q4_K: return launch_tc_type<BM, NH, FB200_Q4_K>(dev, a, grid_n, grid_m, smem);
-    case FB200_Q6_K: return launch_tc_type<BM, NH, FB200_Q6_K>(dev, a, grid_n, grid_m, smem);
+    case FB200_Q4_0: return launch_tc_type<BM, NH, FB200_Q4_0>(dev, a, grid_n, grid_m, grid_z, smem);
+    case FB200_Q8_0: return launch_tc_type<BM, NH, FB200_Q8_0>(dev, a, grid_n, grid_m, grid_z, smem);
+    case FB200_Q4_K: return launch_tc_type<BM, NH, FB200_Q4_K>(dev, a, grid_n, grid_m, grid_z, smem);
+    case FB200_Q6_K: return launch_tc_type<BM, NH, FB200_Q6_K>(dev, a, grid_n, grid_m, grid_z, smem);
   }
   return 1;
 }
 
 // Tile shape of one product: NH x 128 weight rows by bm activation rows, and the operand stages that
 // fit. Returns false when no shape fits.
-struct TcShape { int bm = 0, nh = 0, stages = 0; size_t ctas = 0, cost = 0; };
+struct TcShape { int bm = 0, nh = 0, stages = 0, split = 1; size_t ctas = 0, cost = 0; };
 
 // measured time per unit of tile area relative to the 256 x 256 tile, in 1/64ths
 static const int kRelCost[2][2] = {{134, 87}, {96, 64}};  // [nh - 1][bm == 256]
@@ -546,26 +552,71 @@ bool tc_covers(const fb200_qmatrix* w, const float* x, size_t m, TileGeom* geo) 
   return (reinterpret_cast<uintptr_t>(x) & 15) == 0;
 }
 
+// y = p[0] + p[1] + .. (+ r1 + r2): the partial products of a split-K launch, added in split order.
+__global__ void __launch_bounds__(256)
+splitk_add_kernel(const float4* __restrict__ parts, int nsplit, size_t n4, int ncols4, const float* __restrict__ r1,
+                  int r1_stride, const float* __restrict__ r2, float4* __restrict__ y) {
+  const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n4) return;
+  float4 acc = __ldg(parts + i);
+  for (int s = 1; s < nsplit; ++s) {
+    const float4 v = __ldg(parts + (size_t)s * n4 + i);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  if (r1) {
+    const size_t m = i / (size_t)ncols4, c = i - m * (size_t)ncols4;
+    const float4 v = __ldg(reinterpret_cast<const float4*>(r1 + m * (size_t)r1_stride) + c);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  if (r2) {
+    const float4 v = __ldg(reinterpret_cast<const float4*>(r2) + i);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  y[i] = acc;
+}
+
 // Launches the product of packed rows (xh, xscale: pack_rows16_kernel with this bm) on dev->stream.
+// With sh.split > 1 the K groups are cut into sh.split ranges (grid.z), every range writes its
+// partial product into the handle's split-K scratch and a second kernel adds them (+ residuals).
 int tc_launch(fb200_device* dev, const fb200_qmatrix* w, const TileGeom& geo, const TcShape& sh, const __half* xh,
               const float* xscale, size_t m, float* y, bool r1_is_bias, const float* r1, const float* r2, int swiglu) {
   const int bm = sh.bm, nh = sh.nh;
   const int raw_stride = (geo.tg_bytes + 127) & ~127;
   const int mp = (int)((m + bm - 1) / bm) * bm;
+  const int split = swiglu ? 1 : sh.split;
+  float* parts = nullptr;
+  if (split > 1) {
+    int rc = fb200_ensure(dev, &dev->splitk, &dev->splitk_bytes, (size_t)split * m * w->n * sizeof(float));
+    if (rc) return rc;
+    parts = reinterpret_cast<float*>(dev->splitk);
+  }
   TcArgs a;
-  a.w = w->data; a.xh = xh; a.xscale = xscale; a.y = y; a.r1 = r1; a.r2 = r2;
+  a.w = w->data; a.xh = xh; a.xscale = xscale;
+  a.y = split > 1 ? parts : y;
+  a.r1 = split > 1 ? nullptr : r1;
+  a.r2 = split > 1 ? nullptr : r2;
   a.r1_stride = r1_is_bias ? 0 : (int)w->n;
   a.M = (int)m; a.N = (int)w->n; a.K = (int)w->k;
   a.ngroups = w->ngroups; a.ntiles = w->ntiles; a.type = (int)w->type; a.tgb = geo.tg_bytes;
   a.group_elems = geo.group_elems; a.status = dev->status;
   a.stages = sh.stages; a.raw_stride = raw_stride;
   a.pair_tiles = swiglu ? w->ntiles / 2 : 0;
+  a.kg_per = (w->ngroups + split - 1) / split;
+  const unsigned gz = (unsigned)((w->ngroups + a.kg_per - 1) / a.kg_per);  // every range holds at least one K group
   const int smem = sh.stages * (nh * A_HALF + bm * BK * 2) + 2 * 8 * nh * raw_stride + TAIL_BYTES;
   const size_t n_rows = swiglu ? w->n / 2 : w->n;
   const size_t rows_per_cta = swiglu ? BN : BN * nh;
   const unsigned gn = (unsigned)((n_rows + rows_per_cta - 1) / rows_per_cta), gm = (unsigned)(mp / bm);
-  if (nh == 2) return bm == 256 ? launch_tc<256, 2>(dev, a, gn, gm, smem) : launch_tc<128, 2>(dev, a, gn, gm, smem);
-  return bm == 256 ? launch_tc<256, 1>(dev, a, gn, gm, smem) : launch_tc<128, 1>(dev, a, gn, gm, smem);
+  int rc;
+  if (nh == 2) rc = bm == 256 ? launch_tc<256, 2>(dev, a, gn, gm, gz, smem) : launch_tc<128, 2>(dev, a, gn, gm, gz, smem);
+  else rc = bm == 256 ? launch_tc<256, 1>(dev, a, gn, gm, gz, smem) : launch_tc<128, 1>(dev, a, gn, gm, gz, smem);
+  if (rc || split == 1) return rc;
+  const size_t n4 = m * w->n / 4;
+  splitk_add_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, dev->stream>>>(
+      reinterpret_cast<const float4*>(parts), (int)gz, n4, (int)(w->n / 4), r1, r1_is_bias ? 0 : (int)w->n, r2,
+      reinterpret_cast<float4*>(y));
+  FB_LAUNCH_CHECK(dev);
+  return FB200_OK;
 }
 
 }  // namespace
@@ -592,6 +643,35 @@ int fb200_qgemm(fb200_device* dev, const fb200_qmatrix* w, const float* x, size_
       if (cost < best_cost) { best_cost = cost; best = sh; }
     }
   if (!best.bm) return 1;
+  // Split-K (plain and residual epilogues, 16-byte aligned outputs, at least 2048 values of K per range):
+  // the K groups in 2 or 4 ranges side by side (grid.z) when that lets a larger, more efficient tile
+  // fill the SMs. Times in ns, from measurements at 512 rows: a 256 x 256 tile takes 4 us per 256 values
+  // of K (the other shapes in proportion to the table above), a CTA costs 8 us beside its K loop, the
+  // ranges write split x the output at about 3 TB/s and the adding kernel takes 2 us + (split + 1)
+  // passes over the output at 7 TB/s.
+  static const bool no_split = getenv("FB200_TC_SPLITK") && getenv("FB200_TC_SPLITK")[0] == '0';
+  const bool may_split = !no_split && !swiglu && !force_bm && !force_nh && w->n % 4 == 0 &&
+                         ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(r1) | reinterpret_cast<uintptr_t>(r2)) & 15) == 0;
+  if (may_split) {
+    const double unit_ns = 4000.0 * ((double)w->k / 256.0) / 32768.0, out_bytes = (double)m * (double)w->n * 4.0;
+    auto total_ns = [&](const TcShape& sh, int split) {
+      const double waves = (double)((sh.ctas * split + dev->sm_count - 1) / dev->sm_count);
+      double t = waves * ((double)sh.cost * unit_ns / split + 8000.0);
+      if (split > 1) t += split * out_bytes / 3000.0 + 2000.0 + (split + 1) * out_bytes / 7000.0;
+      return t;
+    };
+    double best_ns = 0.9 * total_ns(best, 1);  // a split has to promise a tenth less
+    for (int split = 2; split <= 4; split *= 2) {
+      if (w->k / split < 2048 || w->ngroups < 2 * split) break;
+      for (int nh = 2; nh >= 1; --nh)
+        for (int bm = 256; bm >= 128; bm -= 128) {
+          TcShape sh;
+          if (!tc_shape(w, geo, m, 0, bm, nh, &sh)) continue;
+          const double t = total_ns(sh, split);
+          if (t < best_ns) { best_ns = t; best = sh; best.split = split; }
+        }
+    }
+  }
   const int mp = (int)((m + best.bm - 1) / best.bm) * best.bm;
   const size_t xbytes = (size_t)mp * w->k * 2, need = xbytes + (size_t)mp * sizeof(float);
   int rc = fb200_ensure(dev, &dev->xpack, &dev->xpack_bytes, need);
