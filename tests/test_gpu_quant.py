@@ -128,7 +128,8 @@ def _sampled_columns(raw, ty, n, k, cols):
 
 @pytest.mark.parametrize("tname,n,k", [("q4_0", 4096, 4096), ("q4k", 4096, 4096), ("q4k", 1024, 4096),
                                         ("q4k", 14336, 4096), ("q4k", 4096, 14336), ("q8_0", 4096, 4096),
-                                        ("q8_0", 14336, 4096), ("q6k", 1024, 4096), ("q6k", 4096, 14336)])
+                                        ("q8_0", 14336, 4096), ("q8_0", 4096, 14336), ("q6k", 1024, 4096),
+                                        ("q6k", 4096, 14336)])
 def test_q_mat_mul_llama_shapes(dev, tname, n, k):
     # the projection shapes of a Llama-3-8B layer at every row count of the sweep: one row (integer
     # limb kernel), 8 and 32 rows (fp16 mma kernel), 512 and 2048 rows (tcgen05 kernel). The oracle
@@ -356,3 +357,27 @@ def test_q5_epilogues(dev):
         with pytest.raises(kb.FusorError) as e:
             dev.tensor(activations(1, 2, k)).q_mat_mul(w, epilogue=kb.EPI_SWIGLU)
         assert e.value.code == kb.ERR_UNSUPPORTED_DTYPE
+
+
+@pytest.mark.parametrize("tname", ["q4k", "q6k", "q8_0"])
+def test_prefill_product_split_k(dev, tname):
+    # long rows, few tiles: the tcgen05 product cuts K into ranges (grid.z) and a second kernel adds the
+    # partial products in range order, together with the residual or bias rows; ragged N and M
+    ty = TYPES[tname]
+    n, k = 1000, 8192
+    raw = weights(61, n, k, ty)
+    w = kb.QMatrix.from_raw_bytes(dev, (n, k), raw, ty)
+    for m in (300, 513):
+        x = activations(600 + m, m, k)
+        exp = O.q_mat_mul(x, raw, ty, n, k)
+        xt = dev.tensor(x)
+        y = xt.q_mat_mul(w).as_slice()
+        assert F.rel_l2(y, exp) < TOL, (tname, m, F.rel_l2(y, exp))
+        assert np.array_equal(y, xt.q_mat_mul(w).as_slice())
+        r1, r2 = activations(610 + m, m, n), activations(620 + m, m, n)
+        y = xt.q_mat_mul(w, epilogue=kb.EPI_RESIDUAL, r1=dev.tensor(r1), r2=dev.tensor(r2)).as_slice()
+        assert F.rel_l2(y, (exp + r1) + r2) < TOL
+        bias = activations(630, 1, n)[0]
+        y = xt.q_mat_mul(w, epilogue=kb.EPI_BIAS, r1=dev.tensor(bias)).as_slice()
+        assert F.rel_l2(y, exp + bias[None, :]) < TOL
+    assert dev.status() == 0
