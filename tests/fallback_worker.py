@@ -80,6 +80,15 @@ def main(what):
     elif what == "prefill_mma":     # FB200_ATTN_TCGEN05=0: prompt attention on the mma.sync kernel
         attention(dev, [(1, 8, 2, 128, 128, 128, True), (1, 8, 8, 200, 200, 128, True),
                         (2, 4, 2, 64, 320, 128, False)])
+    elif what == "q5k_row_copies":   # FB200_Q5K_TENSOR_TMA=0: Q5_K stages fetched by 16 row copies
+        for n, k in ((273, 1024), (512, 4096)):
+            raw = F.random_q5_weights(71, 0.02, n, k, O.Q5K)
+            w = kb.QMatrix.from_raw_bytes(dev, (n, k), raw, O.Q5K)
+            for m in (1, 8, 16, 32, 40):
+                x = O.normal(700 + m, 1.0, m * k).reshape(m, k) + np.float32(0.5)
+                err = F.rel_l2(dev.tensor(x).q_mat_mul(w).as_slice(), O.q_mat_mul(x, raw, O.Q5K, n, k))
+                assert err < TOL, (n, k, m, err)
+                print(f"ok Q5_K {n}x{k} rows {m}: {err:.1e}")
     elif what == "prefill_sequential":  # FB200_TC_GROUP=0: q, k, v of a prompt pass one after the other
         decoder(dev, 1, prompt_len=48)
     else:

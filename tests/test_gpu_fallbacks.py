@@ -19,6 +19,7 @@ WORKER = os.path.join(os.path.dirname(os.path.abspath(__file__)), "fallback_work
     ("decode_scalar", "FB200_ATTN_DECODE_TC", "0"),
     ("prefill_mma", "FB200_ATTN_TCGEN05", "0"),
     ("prefill_sequential", "FB200_TC_GROUP", "0"),
+    ("q5k_row_copies", "FB200_Q5K_TENSOR_TMA", "0"),
 ])
 def test_alternative_kernel(what, var, value):
     out = subprocess.run([sys.executable, WORKER, what], env=dict(os.environ, **{var: value}),
