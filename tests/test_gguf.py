@@ -150,3 +150,31 @@ def test_reader_against_the_gguf_package_writer(tmp_path):
     assert np.array_equal(np.frombuffer(bytes(g.tensor_bytes("dense")), np.float32).reshape(4, 6), f32)
     assert g.tensors["q8"][:2] == ((8, 64), O.Q8_0) and np.array_equal(g.tensor_bytes("q8"), q8)
     assert g.tensors["q4k"][:2] == ((2, 512), O.Q4K) and np.array_equal(g.tensor_bytes("q4k"), q4k)
+
+
+def test_five_bit_tensors_round_trip_and_shard(tmp_path):
+    # Q5_0 (22-byte blocks) and Q5_K (176-byte blocks) through the container and the tensor-parallel
+    # cuts: row shards and column shards dequantise (oracle) to the matching part of the whole matrix
+    import fixtures as F
+    from kalosm_b200 import tp
+    n, k = 8, 1024
+    mats = {O.Q5_0: F.random_q5_weights(3, 0.02, n, k, O.Q5_0), O.Q5K: F.random_q5_weights(4, 0.02, n, k, O.Q5K)}
+    path = tmp_path / "q5.gguf"
+    gguf.write_gguf(path, {"general.architecture": (gguf.STRING, "llama")},
+                    [("a", (n, k), O.Q5_0, mats[O.Q5_0]), ("b", (n, k), O.Q5K, mats[O.Q5K])])
+    g = gguf.GgufFile(path)
+    for name, ty in (("a", O.Q5_0), ("b", O.Q5K)):
+        assert g.tensors[name][:2] == ((n, k), ty)
+        assert g.tensor_nbytes(name) == O.nbytes_for(ty, n * k)
+        raw = np.frombuffer(bytes(g.tensor_bytes(name)), np.uint8)
+        assert np.array_equal(raw, mats[ty])
+        whole = O.dequantize(raw, ty, n * k).reshape(n, k)
+        for rank in range(2):
+            part, shape = tp.shard("attn_q", raw, ty, (n, k), rank, 2)
+            assert shape == (n // 2, k)
+            assert np.array_equal(O.dequantize(part, ty, part.size // O.BLOCK[ty][1] * O.BLOCK[ty][0]).reshape(shape),
+                                  whole[rank * n // 2:(rank + 1) * n // 2])
+            part, shape = tp.shard("ffn_down", raw, ty, (n, k), rank, 2)
+            assert shape == (n, k // 2)
+            assert np.array_equal(O.dequantize(part, ty, part.size // O.BLOCK[ty][1] * O.BLOCK[ty][0]).reshape(shape),
+                                  whole[:, rank * k // 2:(rank + 1) * k // 2])
